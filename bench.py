@@ -1,0 +1,283 @@
+"""Benchmark of the compiled training step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config bert_tiny] [--impl ours|reference]
+
+One step is one pass of the training step (forward, loss, backward, AdamW) over one synthetic
+MLM batch of 32 sequences per GPU. Prints ONE JSON line (rank 0). `value` is batches of 32
+sequences trained per second over the whole job with the batch resident in HBM; `e2e` is the same
+through the host loop of the C ABI with a new host batch every step (host-to-device copy of the
+batch, tokens and scalars, device-to-host read of every loss, inside the timed region).
+`roofline` describes the kernel with the largest share of a profiled step; `cpu_baseline` is the
+CPU oracle (a port of the reference's single-threaded interpreter) timed on this host.
+`--impl reference` times that CPU port alone with every host thread.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from modelspec_b200 import models, synthetic  # noqa: E402
+
+METRIC = "train_steps_per_sec"
+UNIT = "steps/s (batches of 32 sequences, whole job)"
+
+
+def workload(name):
+    cfg = models.CONFIGS[name]
+    if cfg["kind"] != "bert":
+        raise SystemExit("bench.py measures the BERT-shaped configurations")
+    return cfg
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [l.strip().split(", ") for l in open(self.file.name) if l.strip()]
+        os.unlink(self.file.name)
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if len(r) > col and r[col].strip().lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_steps(source, masked, vocab, seq, batch, steps, threads, warmup=0):
+    """Times `steps` steps of the CPU oracle; returns seconds per step (median)."""
+    import oracle_lib
+    oracle_lib.lib().orc_set_threads(threads)
+    t = oracle_lib.Trainer(source, masked)
+    times = []
+    for k in range(warmup + steps):
+        for name, value in synthetic.mlm_batch(k, vocab=vocab, seq=seq, batch=batch).items():
+            t.set_input(name, value)
+        t0 = time.perf_counter()
+        t.step(k, warmup + steps)
+        if k >= warmup:
+            times.append(time.perf_counter() - t0)
+    oracle_lib.lib().orc_set_threads(os.cpu_count() or 1)
+    return float(np.median(times)), times
+
+
+def reference_arm(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    steps = max(1, min(args.steps, 12))
+    warm = min(args.warmup, 1)
+    source = cfg["source"](steps=steps + warm, warmup_steps=1)
+    masked = models.default_masked_rows(cfg["rows"])
+    sec, times = cpu_steps(source, masked, cfg["vocab"], cfg["seq"], cfg["batch"], steps, threads, warm)
+    value = 1.0 / sec
+    sample = "%d of the %d asked steps of the full workload (%d warm-up), CPU port of the reference interpreter, %d threads" % (
+        steps, args.steps, warm, threads)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.config, "global_batch": cfg["batch"], "seq_len": cfg["seq"], "vocab": cfg["vocab"],
+                   "masked_rows": masked},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--config", default="bert_tiny")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-steps", type=int, default=3, help="steps of the single-threaded CPU baseline (rank 0, N=1)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = workload(args.config)
+    if args.impl == "reference":
+        reference_arm(args, cfg)
+        return
+
+    import modelspec_b200 as M
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE is %d" % (args.gpus, world))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    W, K = max(args.warmup, 3), args.steps
+    total = W + K
+    source = cfg["source"](steps=2 * total + 8, warmup_steps=max(1, total // 10))
+    masked = models.default_masked_rows(cfg["rows"])
+    device = M.Device(local)
+    run = M.Training(device, source, masked)
+    plan = run.step_plan
+    stats = plan.stats()
+    batch_of = lambda k: synthetic.mlm_batch(k, vocab=cfg["vocab"], seq=cfg["seq"], batch=cfg["batch"],
+                                             row_offset=rank * cfg["rows"])
+
+    def barrier():
+        plan.sync()
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident leg: the batch, tokens and scalars stay staged; no host copy ---------
+    for name, value in batch_of(0).items():
+        run.set_input(name, value)
+    for k in range(W):
+        run.step(k, 2 * total + 8)
+    barrier()
+    plan.elapsed_ms()
+    sampler = ClockSampler(local)
+    step_ms = []
+    chunk = 10
+    done = 0
+    while done < K:
+        n = min(chunk, K - done)
+        for _ in range(n):
+            plan.run()   # same staged inputs: nothing is uploaded
+        ms, counted = plan.elapsed_ms()
+        step_ms += [ms / counted] * counted
+        done += n
+    barrier()
+    clocks = sampler.stop()
+    resident_ms = max_over_ranks(float(np.sum(step_ms))) / K
+    median_ms = float(np.median(step_ms))
+
+    # ---- end-to-end leg: a new pinned host batch every step, every loss read back -----------
+    batches = [batch_of(W + k) for k in range(K)]
+    h2d = stats["upload_bytes_per_step"]
+    barrier()
+    t0 = time.perf_counter()
+    plan.elapsed_ms()
+    lag = 4
+    losses = []
+    for k in range(K):
+        for name, value in batches[k].items():
+            run.set_input(name, value)
+        run.step(total + k, 2 * total + 8)
+        if k >= lag:
+            losses.append(run.loss_of(total + k - lag))
+    for k in range(max(0, K - lag), K):
+        losses.append(run.loss_of(total + k))
+    e2e_device_ms, _ = plan.elapsed_ms()
+    barrier()
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max_over_ranks(max(e2e_device_ms, e2e_wall_ms)) / K
+    assert all(np.isfinite(l) for l in losses), "a loss of the timed run is not finite"
+
+    # ---- one profiled step: which kernel dominates, and its roofline ---------------------------
+    prof = plan.profile_step()
+    by_kernel = {}
+    for kernel, ms, nbytes, flop in prof:
+        e = by_kernel.setdefault(kernel, {"launches": 0, "ms": 0.0, "bytes": 0, "flop": 0})
+        e["launches"] += 1; e["ms"] += ms; e["bytes"] += nbytes; e["flop"] += flop
+    profiled_ms = sum(e["ms"] for e in by_kernel.values())
+    top = max(by_kernel, key=lambda kname: by_kernel[kname]["ms"])
+    pk = peaks()
+    e = by_kernel[top]
+    if top in ("matmul", "attention_forward", "attention_grad_q", "attention_grad_kv"):
+        achieved = e["flop"] / (e["ms"] * 1e-3) / 1e12
+        roofline = {"kernel": top, "bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["bf16_tflops"], "traffic": None}
+    else:
+        achieved = e["bytes"] / (e["ms"] * 1e-3) / 1e9
+        roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "traffic": None}
+    roofline.update({"peak_source": pk["source"], "launches_per_step": e["launches"], "share_of_step": e["ms"] / profiled_ms,
+                     "ms_per_step": e["ms"], "algorithmic_bytes": e["bytes"], "algorithmic_flop": e["flop"]})
+    shares = {kname: round(v["ms"] / profiled_ms, 4) for kname, v in sorted(by_kernel.items(), key=lambda kv: -kv[1]["ms"])}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        src = cfg["source"](steps=args.cpu_steps, warmup_steps=1)
+        sec, _ = cpu_steps(src, masked, cfg["vocab"], cfg["seq"], cfg["batch"], args.cpu_steps, 1)
+        cpu_baseline = {"value": 1.0 / sec, "unit": UNIT, "cores": 1, "kind": "port", "ms_per_step": sec * 1e3,
+                        "sample": "%d full steps of the same workload, single thread as the reference interpreter runs" % args.cpu_steps}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": world * 1e3 / resident_ms, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": resident_ms, "median_ms_per_step": median_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "tokens_per_sec": world * cfg["rows"] * 1e3 / resident_ms,
+            "config": {"workload": args.config, "global_batch": cfg["batch"] * world, "seq_len": cfg["seq"], "vocab": cfg["vocab"],
+                       "masked_rows": masked, "parallelism": "dp%d" % world,
+                       "l2": "each step streams %.0f MB of intermediates (> 126 MB L2)" % (stats["algorithmic_bytes_per_step"] / 1e6)},
+            "clocks": clocks,
+            "e2e": {"value": world * 1e3 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 8, "losses_read": len(losses)},
+            "gpu_launches": stats["launches_per_step"] * K,
+            "launches_per_step": stats["launches_per_step"],
+            "roofline": roofline, "kernel_shares": shares, "profiled_step_ms": profiled_ms,
+            "algorithmic_bytes_per_step": stats["algorithmic_bytes_per_step"],
+            "matmul_flop_per_step": stats["matmul_flop_per_step"],
+            "cpu_baseline": cpu_baseline,
+        }))
+    run.destroy()
+    device.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

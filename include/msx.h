@@ -1,0 +1,241 @@
+/* msx: the C ABI of the B200 CUDA backend for ModelSpec's compiled training step.
+ *
+ * This is the boundary a `cuda` sibling of the reference's `vulkan` runtime module binds: plain
+ * C, opaque handles, host pointers and byte counts, an int status from every call, no exceptions
+ * and no unbounded waits. The shim owns every device allocation, stream, graph and communicator;
+ * the caller owns host memory, which is copied before a call returns.
+ *
+ * What crosses the boundary is the training step in the text form the reference already prints
+ * (`modelspec ir --stage training`, crates/modelspec-core/src/ir/print.rs:55-166): the tensor-SSA
+ * program with its parameter table, optimizer line, subgraph tags and output roles. The shim
+ * does its own fusion, liveness and buffer reuse over that program, as the reference's scheduler
+ * does for Vulkan (crates/modelspec-core/src/schedule.rs:759-1484), and refuses a program holding
+ * an op it has no kernel for (the reference's E-TARGET-011, schedule.rs:155-159).
+ */
+#ifndef MSX_H
+#define MSX_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct msx_device msx_device;
+typedef struct msx_plan msx_plan;
+
+/* Status codes. The message of the last failure on a handle is msx_last_error(). */
+enum {
+    MSX_OK = 0,
+    MSX_BAD_ARGUMENT = 1,   /* null handle, unknown name, wrong byte count */
+    MSX_NO_DEVICE = 2,      /* no CUDA device at that ordinal, or it is not sm_100 */
+    MSX_OUT_OF_MEMORY = 3,
+    MSX_UNSUPPORTED = 4,    /* an op with no CUDA kernel, or malformed IR */
+    MSX_LAUNCH_FAILED = 5,  /* a CUDA call failed; the message holds its name */
+    MSX_NON_FINITE = 6,     /* reserved for the host loop's E-TRAIN-001 check */
+    MSX_TIMEOUT = 7,        /* a bounded wait ran out */
+    MSX_BAD_INPUT = 8       /* an input the reference's interpreter refuses: id or label out of
+                               range, key mask not 0/1, negative or non-finite loss weight */
+};
+
+/* Plan flags. */
+enum {
+    MSX_PLAN_DEFAULT = 0,
+    MSX_PLAN_NO_GRAPH = 1   /* launch kernels one by one instead of through one CUDA graph */
+};
+
+typedef struct msx_stats {
+    uint64_t launches_per_step;   /* kernels of one step, as scheduled */
+    uint64_t nodes;               /* IR nodes of the program */
+    uint64_t live_nodes;          /* nodes an output depends on */
+    uint64_t arena_bytes;         /* intermediate values after liveness reuse */
+    uint64_t unshared_bytes;      /* the same values with one buffer each */
+    uint64_t param_bytes;         /* parameters (and moments, when the step has them) */
+    uint64_t upload_bytes_per_step;
+    uint64_t steps_run;
+    uint64_t algorithmic_bytes_per_step; /* sum over launches of bytes read + written, the
+                                            reference's counting rule (ir/kernel.rs:1562-1579) */
+    uint64_t matmul_flop_per_step;       /* 2 m k n over the step's matmuls */
+} msx_stats;
+
+/* Replaces the device-selection half of vulkan::runner::on_device
+ * (crates/modelspec-runtime/src/vulkan/runner.rs:412-436). */
+int msx_open(int ordinal, msx_device** out);
+void msx_close(msx_device* device);
+
+/* The message of the last failure: of `device`, or of the last msx_open when `device` is null. */
+const char* msx_last_error(const msx_device* device);
+
+/* Builds the execution plan of one program: the part of train_stepwise_profiled that creates
+ * buffers and pipelines (vulkan/stepwise.rs:548-642). `ir_text` is a training step or a bare
+ * tensor program (a forward program for the final loss line and for `infer`). `seed` keys the
+ * dropout masks. `shares`, when not null, is a plan of the same device whose parameter buffers
+ * this plan reads by canonical path instead of allocating its own (the reference runs its loss
+ * and prediction steps on the training run's buffers, vulkan/runner.rs:541-566). */
+int msx_plan_create(msx_device* device, const char* ir_text, uint64_t seed, uint32_t flags,
+                    msx_plan* shares, msx_plan** out);
+void msx_plan_destroy(msx_plan* plan);
+
+/* Host inputs of a step, in node order: the data declarations, masked-row inputs, dropout tokens
+ * and optimizer scalars (schedule::host_inputs, schedule.rs:723-750). AdamW moments are not
+ * among them: they live on the device (msx_moment_upload). */
+uint32_t msx_plan_input_count(const msx_plan* plan);
+const char* msx_plan_input_name(const msx_plan* plan, uint32_t index);
+uint64_t msx_plan_input_bytes(const msx_plan* plan, uint32_t index);
+int msx_plan_input_is_i32(const msx_plan* plan, uint32_t index);
+
+uint32_t msx_plan_param_count(const msx_plan* plan);
+const char* msx_plan_param_path(const msx_plan* plan, uint32_t index);
+uint64_t msx_plan_param_bytes(const msx_plan* plan, uint32_t index);
+
+/* Parameter and moment transfer; `which` is 'm' or 'v'. Uploads and downloads are ordered after
+ * every step already submitted. Replaces the upload at vulkan/stepwise.rs:605-642 and the
+ * read-back of Run::state. */
+int msx_param_upload(msx_plan* plan, uint32_t index, const void* host, uint64_t bytes);
+int msx_param_download(msx_plan* plan, uint32_t index, void* host, uint64_t bytes);
+int msx_moment_upload(msx_plan* plan, uint32_t index, char which, const void* host, uint64_t bytes);
+int msx_moment_download(msx_plan* plan, uint32_t index, char which, void* host, uint64_t bytes);
+
+/* Stages one host input of the next step. The bytes are checked the way the reference's
+ * interpreter checks them before a run (cpu/interpreter.rs:700-715, :1146-1170, :1238-1254) and
+ * copied; MSX_BAD_INPUT names the first offending element. An input not staged again keeps its
+ * last value. */
+int msx_set_input(msx_plan* plan, const char* name, const void* host, uint64_t bytes);
+
+/* First element index of this plan's rows in the global batch, for dropout masks that must
+ * match a single-device run over the whole batch (cpu/interpreter.rs:848-849); 0 by default.
+ * `rows_before` counts rows of the leading dimension held by lower ranks. */
+int msx_set_shard(msx_plan* plan, uint64_t rows_before, uint64_t global_rows);
+
+/* Submits one step: the staged inputs are copied to the device and every kernel of the plan is
+ * enqueued; returns without waiting. The loss of the step is read by msx_loss. Replaces one
+ * recorded step of a segment (vulkan/stepwise.rs:975-1100). */
+int msx_run(msx_plan* plan);
+
+/* Waits for every submitted step (bounded by `timeout_ms`, MSX_TIMEOUT past it) and returns the
+ * loss of the last one. */
+int msx_loss(msx_plan* plan, float* loss, uint32_t timeout_ms);
+
+/* The loss of submitted step `step_number` (counted from 0 over the plan's life) without waiting
+ * for later steps; the last 8 submitted steps keep theirs. Lets a host read losses a few steps
+ * behind the one it submits, as the reference observes a segment while the next one runs
+ * (vulkan/stepwise.rs:976-1100). */
+int msx_loss_of(msx_plan* plan, uint64_t step_number, float* loss, uint32_t timeout_ms);
+uint64_t msx_steps_submitted(const msx_plan* plan);
+
+/* Waits for every submitted step. */
+int msx_sync(msx_plan* plan, uint32_t timeout_ms);
+
+/* Reads the value `%value_id` of the last step. Every output of the program can be read (the
+ * loss, the gradients; of a bare program, its outputs); other values are refused because their
+ * storage is reused. */
+int msx_value_download(msx_plan* plan, uint32_t value_id, void* host, uint64_t bytes);
+
+int msx_plan_stats(const msx_plan* plan, msx_stats* out);
+
+/* One line per scheduled kernel: `<index> <kernel> <value> reads ... writes ...`, the CUDA
+ * counterpart of the `plan step` listing of `modelspec ir --stage kernel` (ir/print.rs:226-266).
+ * Copies at most `capacity` bytes, NUL-terminated; returns the bytes needed. */
+uint64_t msx_plan_describe(const msx_plan* plan, char* out, uint64_t capacity);
+
+/* Per-launch device times of one step run kernel by kernel with a CUDA event after each launch
+ * (not through the graph): the counterpart of the reference's `--profile` timestamps
+ * (vulkan/profile.rs:1-60). `launch_ms` takes launches_per_step floats. The step is a real one:
+ * parameters are updated. msx_launch_kernel / _bytes / _flop give each launch's kernel name and
+ * its bytes read + written and FLOP by the reference's counting rule (ir/kernel.rs:1221-1306,
+ * :1562-1579). */
+int msx_profile_step(msx_plan* plan, float* launch_ms, uint32_t capacity);
+const char* msx_launch_kernel(const msx_plan* plan, uint32_t launch);
+uint64_t msx_launch_bytes(const msx_plan* plan, uint32_t launch);
+uint64_t msx_launch_flop(const msx_plan* plan, uint32_t launch);
+
+/* The same listing for a program without building a plan (no device needed), followed by one
+ * line of totals: what `modelspec ir --stage kernel` is to the Vulkan backend. Returns 0 with
+ * the reason in msx_last_error(NULL) when the program cannot be scheduled. */
+uint64_t msx_schedule_describe(const char* ir_text, char* out, uint64_t capacity);
+
+/* Device time of the steps run since the last call, in milliseconds, measured with CUDA events
+ * on the plan's stream around each msx_run: the reference's training clock (cli/src/train.rs:
+ * 17-33). Waits for the submitted steps. */
+int msx_elapsed_ms(msx_plan* plan, double* total_ms, uint64_t* steps);
+
+/* Data-parallel training over the GPUs of one box: every rank holds a plan of the same step
+ * compiled for its shard of the batch; gradients are summed across ranks in buckets on a side
+ * stream before the update. The reference has no counterpart (it is single-device).
+ * `unique_id` is 128 bytes, made by rank 0 with msx_comm_unique_id and handed to the others by
+ * the caller. */
+int msx_comm_unique_id(void* unique_id_128);
+int msx_comm_init(msx_plan* plan, int rank, int world, const void* unique_id_128);
+
+/* ---- The training run above the plan -------------------------------------------------------
+ *
+ * The host loop of `train --backend cuda`, mirroring the reference's device runner
+ * vulkan::stepwise::train_stepwise_on_device (crates/modelspec-runtime/src/vulkan/stepwise.rs:
+ * 289-296, :400-) and the CPU loop it is compared with, train::runner::run_checked
+ * (crates/modelspec-runtime/src/train/runner.rs:365-512): parameters drawn by their
+ * initializers, per step the AdamW scalars of t = step + 1, the dropout token of every site,
+ * the masked-row gather of the batch, one submitted step; the loss of step k is the loss before
+ * update k; the final loss is the dropout-free forward program on the final parameters. */
+typedef struct msx_training msx_training;
+
+/* Compiles `source` (`.mspec`), builds the step plan and the forward plan on shared parameter
+ * buffers, and uploads the initial parameters (Philox stream 0 under the train block's seed).
+ * `masked_rows` as in msx_compile; `flags` are plan flags. */
+int msx_training_create(msx_device* device, const char* source, uint64_t masked_rows, uint32_t flags,
+                        msx_training** out);
+void msx_training_destroy(msx_training* training);
+msx_plan* msx_training_step_plan(msx_training* training);
+msx_plan* msx_training_forward_plan(msx_training* training);
+uint64_t msx_training_steps(const msx_training* training);   /* `steps` of the train block */
+uint64_t msx_training_seed(const msx_training* training);
+/* The message of the last failure of a msx_training_* call on `training`. */
+const char* msx_training_last_error(const msx_training* training);
+
+/* Sets one declared `input` or `target` of the batch for the steps that follow (the dense feed
+ * of train/data.rs:14-35; block k of a `--data` file is what the caller passes before step k). */
+int msx_training_set_input(msx_training* training, const char* name, const void* host, uint64_t bytes);
+
+/* The reference's synthetic batch (train/data.rs:189-212): the one f32 input standard normal,
+ * key masks all ones, the target the prediction of a teacher drawn on the teacher stream, run on
+ * the device. Refused unless the block declares one f32 input besides key masks and one f32
+ * target. */
+int msx_training_synthetic(msx_training* training);
+
+/* Copies the current batch's declared input `name` out (after msx_training_synthetic). */
+int msx_training_get_input(msx_training* training, const char* name, void* host, uint64_t bytes);
+
+/* Submits step `step` of a run that ends at `end` (steps are counted from 0; `end` is
+ * start + steps); returns without waiting. MSX_BAD_INPUT when the batch selects more rows than
+ * the masked-row gather holds (the reference's E-DATA-012). */
+int msx_training_step(msx_training* training, uint64_t step, uint64_t end);
+
+/* Loss of run step `step` (as passed to msx_training_step), readable while later steps are in
+ * flight; only the last 8 submitted steps keep theirs. */
+int msx_training_loss_of(msx_training* training, uint64_t step, float* loss);
+
+/* Loss of the last submitted step (waits for it). MSX_NON_FINITE when it is NaN or infinite
+ * (the reference's E-TRAIN-001, train/runner.rs:162-228). */
+int msx_training_loss(msx_training* training, float* loss);
+
+/* The final loss line: the forward program, dropout the identity, on the current parameters and
+ * the current batch. */
+int msx_training_final_loss(msx_training* training, float* loss);
+
+/* E-TRAIN-001 over the state: MSX_NON_FINITE naming the first parameter or moment that holds a
+ * NaN or an infinity. Reads every parameter back; call it at the cadence the host can afford. */
+int msx_training_check_finite(msx_training* training);
+
+/* The `.mspec` front door, for hosts without the reference's compiler: lowers the train block
+ * of `source`, differentiates it and attaches its optimizer. `which` is "step", "forward" (the
+ * dropout-free program of the final loss line) or "tensor". `masked_rows` is the capacity of
+ * the masked-row gather (passes/masked_rows.rs:117-206), 0 for none. Copies at most `capacity`
+ * bytes; returns the bytes needed, or 0 on failure with the message in msx_last_error(NULL).
+ * Mirrors compile::compile_training_with (crates/modelspec-core/src/compile.rs:85-116). */
+uint64_t msx_compile(const char* source, const char* which, uint64_t masked_rows, char* out,
+                     uint64_t capacity);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MSX_H */

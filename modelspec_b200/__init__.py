@@ -1,0 +1,307 @@
+"""modelspec_b200: a B200 (sm_100a) CUDA backend for ModelSpec's compiled training step.
+
+The product is the shared library `libmsx.so` beside this file (C ABI in `include/msx.h`). This
+module is a thin ctypes binding of that ABI for tests, the benchmark and Python hosts; it holds
+no arithmetic. There is no CPU fallback: without the library, or without a B200, every call that
+would compute raises.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmsx.so")
+
+OK, BAD_ARGUMENT, NO_DEVICE, OUT_OF_MEMORY, UNSUPPORTED, LAUNCH_FAILED, NON_FINITE, TIMEOUT, BAD_INPUT = range(9)
+PLAN_DEFAULT, PLAN_NO_GRAPH = 0, 1
+
+STATUS_NAMES = ["MSX_OK", "MSX_BAD_ARGUMENT", "MSX_NO_DEVICE", "MSX_OUT_OF_MEMORY", "MSX_UNSUPPORTED",
+                "MSX_LAUNCH_FAILED", "MSX_NON_FINITE", "MSX_TIMEOUT", "MSX_BAD_INPUT"]
+
+
+class MsxError(RuntimeError):
+    def __init__(self, status, message):
+        name = STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else str(status)
+        super().__init__("%s: %s" % (name, message))
+        self.status = status
+        self.message = message
+
+
+class Stats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "launches_per_step", "nodes", "live_nodes", "arena_bytes", "unshared_bytes", "param_bytes",
+        "upload_bytes_per_step", "steps_run", "algorithmic_bytes_per_step", "matmul_flop_per_step")]
+
+
+# Every function include/msx.h declares: name -> (restype, argtypes).
+_P = C.c_void_p
+SIGNATURES = {
+    "msx_open": (C.c_int, [C.c_int, C.POINTER(_P)]),
+    "msx_close": (None, [_P]),
+    "msx_last_error": (C.c_char_p, [_P]),
+    "msx_plan_create": (C.c_int, [_P, C.c_char_p, C.c_uint64, C.c_uint32, _P, C.POINTER(_P)]),
+    "msx_plan_destroy": (None, [_P]),
+    "msx_plan_input_count": (C.c_uint32, [_P]),
+    "msx_plan_input_name": (C.c_char_p, [_P, C.c_uint32]),
+    "msx_plan_input_bytes": (C.c_uint64, [_P, C.c_uint32]),
+    "msx_plan_input_is_i32": (C.c_int, [_P, C.c_uint32]),
+    "msx_plan_param_count": (C.c_uint32, [_P]),
+    "msx_plan_param_path": (C.c_char_p, [_P, C.c_uint32]),
+    "msx_plan_param_bytes": (C.c_uint64, [_P, C.c_uint32]),
+    "msx_param_upload": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64]),
+    "msx_param_download": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64]),
+    "msx_moment_upload": (C.c_int, [_P, C.c_uint32, C.c_char, _P, C.c_uint64]),
+    "msx_moment_download": (C.c_int, [_P, C.c_uint32, C.c_char, _P, C.c_uint64]),
+    "msx_set_input": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64]),
+    "msx_set_shard": (C.c_int, [_P, C.c_uint64, C.c_uint64]),
+    "msx_run": (C.c_int, [_P]),
+    "msx_loss": (C.c_int, [_P, C.POINTER(C.c_float), C.c_uint32]),
+    "msx_sync": (C.c_int, [_P, C.c_uint32]),
+    "msx_loss_of": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_float), C.c_uint32]),
+    "msx_steps_submitted": (C.c_uint64, [_P]),
+    "msx_profile_step": (C.c_int, [_P, C.POINTER(C.c_float), C.c_uint32]),
+    "msx_launch_kernel": (C.c_char_p, [_P, C.c_uint32]),
+    "msx_launch_bytes": (C.c_uint64, [_P, C.c_uint32]),
+    "msx_launch_flop": (C.c_uint64, [_P, C.c_uint32]),
+    "msx_training_loss_of": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_float)]),
+    "msx_value_download": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64]),
+    "msx_plan_stats": (C.c_int, [_P, C.POINTER(Stats)]),
+    "msx_plan_describe": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
+    "msx_schedule_describe": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_uint64]),
+    "msx_elapsed_ms": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
+    "msx_comm_unique_id": (C.c_int, [_P]),
+    "msx_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P]),
+    "msx_training_create": (C.c_int, [_P, C.c_char_p, C.c_uint64, C.c_uint32, C.POINTER(_P)]),
+    "msx_training_destroy": (None, [_P]),
+    "msx_training_step_plan": (_P, [_P]),
+    "msx_training_forward_plan": (_P, [_P]),
+    "msx_training_steps": (C.c_uint64, [_P]),
+    "msx_training_seed": (C.c_uint64, [_P]),
+    "msx_training_last_error": (C.c_char_p, [_P]),
+    "msx_training_set_input": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64]),
+    "msx_training_synthetic": (C.c_int, [_P]),
+    "msx_training_get_input": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64]),
+    "msx_training_step": (C.c_int, [_P, C.c_uint64, C.c_uint64]),
+    "msx_training_loss": (C.c_int, [_P, C.POINTER(C.c_float)]),
+    "msx_training_final_loss": (C.c_int, [_P, C.POINTER(C.c_float)]),
+    "msx_training_check_finite": (C.c_int, [_P]),
+    "msx_compile": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_uint64, C.c_char_p, C.c_uint64]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library. Raises when it has not been built: there is no other compute path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                "%s is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(or `python modelspec_b200/_build.py`); modelspec_b200 has no fallback path" % LIB_PATH)
+        L = C.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = L
+    return _lib
+
+
+def _text(call):
+    """Calls `call(buffer, capacity)` twice: once for the size, once for the bytes."""
+    n = call(None, 0)
+    if n == 0:
+        raise MsxError(UNSUPPORTED, lib().msx_last_error(None).decode())
+    buf = C.create_string_buffer(n)
+    call(buf, n)
+    return buf.value.decode()
+
+
+def compile_mspec(source, which="step", masked_rows=0):
+    """`.mspec` source to the text of its training step ("step"), its dropout-free forward
+    program ("forward") or its lowered tensor program ("tensor")."""
+    return _text(lambda buf, cap: lib().msx_compile(source.encode(), which.encode(), masked_rows, buf, cap))
+
+
+def schedule_describe(ir_text):
+    """The kernel launches the backend schedules for a program, one per line; needs no GPU."""
+    return _text(lambda buf, cap: lib().msx_schedule_describe(ir_text.encode(), buf, cap))
+
+
+def _host(array):
+    a = np.asarray(array)
+    if a.dtype.kind in "iu":
+        return np.ascontiguousarray(a, dtype=np.int32)
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class Device:
+    def __init__(self, ordinal=0):
+        h = _P()
+        rc = lib().msx_open(ordinal, C.byref(h))
+        if rc != OK:
+            raise MsxError(rc, lib().msx_last_error(None).decode())
+        self.h = h
+        self.ordinal = ordinal
+
+    def error(self):
+        return lib().msx_last_error(self.h).decode()
+
+    def check(self, rc):
+        if rc != OK:
+            raise MsxError(rc, self.error())
+
+    def close(self):
+        if self.h:
+            lib().msx_close(self.h)
+            self.h = None
+
+
+class Plan:
+    """One program's execution plan on one device (msx_plan)."""
+
+    def __init__(self, device, ir_text=None, seed=0, flags=PLAN_DEFAULT, shares=None, handle=None):
+        self.device = device
+        self.owned = handle is None
+        if handle is None:
+            h = _P()
+            device.check(lib().msx_plan_create(device.h, ir_text.encode(), seed, flags,
+                                               shares.h if shares is not None else None, C.byref(h)))
+            handle = h
+        self.h = handle
+
+    def destroy(self):
+        if self.h and self.owned:
+            lib().msx_plan_destroy(self.h)
+        self.h = None
+
+    def inputs(self):
+        L = lib()
+        return [(L.msx_plan_input_name(self.h, i).decode(), L.msx_plan_input_bytes(self.h, i),
+                 bool(L.msx_plan_input_is_i32(self.h, i))) for i in range(L.msx_plan_input_count(self.h))]
+
+    def params(self):
+        L = lib()
+        return [(L.msx_plan_param_path(self.h, i).decode(), L.msx_plan_param_bytes(self.h, i))
+                for i in range(L.msx_plan_param_count(self.h))]
+
+    def param_upload(self, index, array):
+        a = _host(array)
+        self.device.check(lib().msx_param_upload(self.h, index, a.ctypes.data, a.nbytes))
+
+    def param_download(self, index):
+        out = np.empty(self.params()[index][1] // 4, dtype=np.float32)
+        self.device.check(lib().msx_param_download(self.h, index, out.ctypes.data, out.nbytes))
+        return out
+
+    def moment_upload(self, index, which, array):
+        a = _host(array)
+        self.device.check(lib().msx_moment_upload(self.h, index, which.encode(), a.ctypes.data, a.nbytes))
+
+    def moment_download(self, index, which):
+        out = np.empty(self.params()[index][1] // 4, dtype=np.float32)
+        self.device.check(lib().msx_moment_download(self.h, index, which.encode(), out.ctypes.data, out.nbytes))
+        return out
+
+    def set_input(self, name, array):
+        a = _host(array)
+        self.device.check(lib().msx_set_input(self.h, name.encode(), a.ctypes.data, a.nbytes))
+
+    def set_shard(self, rows_before, global_rows):
+        self.device.check(lib().msx_set_shard(self.h, rows_before, global_rows))
+
+    def run(self):
+        self.device.check(lib().msx_run(self.h))
+
+    def sync(self, timeout_ms=0):
+        self.device.check(lib().msx_sync(self.h, timeout_ms))
+
+    def loss(self, timeout_ms=0):
+        out = C.c_float()
+        self.device.check(lib().msx_loss(self.h, C.byref(out), timeout_ms))
+        return np.float32(out.value)
+
+    def value(self, value_id, count, dtype=np.float32):
+        out = np.empty(count, dtype=dtype)
+        self.device.check(lib().msx_value_download(self.h, value_id, out.ctypes.data, out.nbytes))
+        return out
+
+    def stats(self):
+        s = Stats()
+        self.device.check(lib().msx_plan_stats(self.h, C.byref(s)))
+        return {n: getattr(s, n) for n, _ in Stats._fields_}
+
+    def describe(self):
+        return _text(lambda buf, cap: lib().msx_plan_describe(self.h, buf, cap))
+
+    def profile_step(self):
+        """Runs one step launch by launch; returns [(kernel, ms, bytes, flop)] per launch."""
+        n = self.stats()["launches_per_step"]
+        ms = (C.c_float * n)()
+        self.device.check(lib().msx_profile_step(self.h, ms, n))
+        L = lib()
+        return [(L.msx_launch_kernel(self.h, i).decode(), float(ms[i]), L.msx_launch_bytes(self.h, i),
+                 L.msx_launch_flop(self.h, i)) for i in range(n)]
+
+    def elapsed_ms(self):
+        total, steps = C.c_double(), C.c_uint64()
+        self.device.check(lib().msx_elapsed_ms(self.h, C.byref(total), C.byref(steps)))
+        return total.value, steps.value
+
+
+class Training:
+    """One training run (msx_training): the host loop of `train --backend cuda`."""
+
+    def __init__(self, device, source, masked_rows=0, flags=PLAN_DEFAULT):
+        self.device = device
+        h = _P()
+        device.check(lib().msx_training_create(device.h, source.encode(), masked_rows, flags, C.byref(h)))
+        self.h = h
+        self.steps = lib().msx_training_steps(h)
+        self.seed = lib().msx_training_seed(h)
+        self.step_plan = Plan(device, handle=_P(lib().msx_training_step_plan(h)))
+        self.forward_plan = Plan(device, handle=_P(lib().msx_training_forward_plan(h)))
+
+    def check(self, rc):
+        if rc != OK:
+            raise MsxError(rc, lib().msx_training_last_error(self.h).decode())
+
+    def destroy(self):
+        if self.h:
+            lib().msx_training_destroy(self.h)
+            self.h = None
+
+    def set_input(self, name, array):
+        a = _host(array)
+        self.check(lib().msx_training_set_input(self.h, name.encode(), a.ctypes.data, a.nbytes))
+
+    def get_input(self, name, count, dtype=np.float32):
+        out = np.empty(count, dtype=dtype)
+        self.check(lib().msx_training_get_input(self.h, name.encode(), out.ctypes.data, out.nbytes))
+        return out
+
+    def synthetic(self):
+        self.check(lib().msx_training_synthetic(self.h))
+
+    def step(self, k, end):
+        self.check(lib().msx_training_step(self.h, k, end))
+
+    def loss(self):
+        out = C.c_float()
+        self.check(lib().msx_training_loss(self.h, C.byref(out)))
+        return np.float32(out.value)
+
+    def loss_of(self, k):
+        out = C.c_float()
+        self.check(lib().msx_training_loss_of(self.h, k, C.byref(out)))
+        return np.float32(out.value)
+
+    def final_loss(self):
+        out = C.c_float()
+        self.check(lib().msx_training_final_loss(self.h, C.byref(out)))
+        return np.float32(out.value)
+
+    def check_finite(self):
+        self.check(lib().msx_training_check_finite(self.h))

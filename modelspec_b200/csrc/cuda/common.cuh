@@ -1,0 +1,114 @@
+// Shared device helpers and the host-side launch check.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+namespace msx {
+namespace k {
+
+struct CudaError : std::runtime_error {
+    cudaError_t code;
+    CudaError(const std::string& what, cudaError_t c) : std::runtime_error(what), code(c) {}
+};
+
+inline void check(cudaError_t e, const char* what) {
+    if (e != cudaSuccess)
+        throw CudaError(std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")", e);
+}
+
+// After a kernel launch: reports a launch-configuration error without synchronising.
+inline void check_launch(const char* kernel) { check(cudaPeekAtLastError(), kernel); }
+
+// ---- GELU, the tanh form evaluated as x / (1 + exp(-2u)) -------------------------------------
+// The operation order is the reference's (crates/modelspec-runtime/src/cpu/interpreter.rs:
+// 1553-1587); the constants are the nearest f32 to sqrt(2/pi) and 0.044715.
+__device__ __forceinline__ float gelu_twice_inner(float x) {
+    const float scale = 0.7978845608028654f, cubic = 0.044715f;
+    return 2.0f * scale * (x + cubic * x * x * x);
+}
+__device__ __forceinline__ float logistic(float v) { return 1.0f / (1.0f + expf(0.0f - v)); }
+__device__ __forceinline__ float gelu_value(float x) { return x * logistic(gelu_twice_inner(x)); }
+__device__ __forceinline__ float gelu_grad_value(float x, float g) {
+    const float scale = 0.7978845608028654f, cubic = 0.044715f;
+    float v = gelu_twice_inner(x);
+    float s = logistic(v), r = logistic(0.0f - v);
+    float slope = scale * (1.0f + 3.0f * cubic * x * x);
+    return (s + 2.0f * (s * x) * r * slope) * g;
+}
+
+// ---- Philox4x32-10, word 0 of the block ------------------------------------------------------
+// Counter [c0, c1, c2, c3], key [k0, k1] (Salmon et al., SC 2011); the reference draws a dropout
+// decision from word 0 alone (crates/modelspec-runtime/src/train/init.rs:91-112, :160-165).
+__device__ __forceinline__ uint32_t philox_word0(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                                 uint32_t k0, uint32_t k1) {
+    const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+    for (int round = 0; round < 10; ++round) {
+        if (round > 0) {
+            k0 += W0;
+            k1 += W1;
+        }
+        uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
+        uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
+        uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+        c0 = n0;
+        c1 = lo1;
+        c2 = n2;
+        c3 = lo0;
+    }
+    return c0;
+}
+
+// ---- reductions ------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `shared` holds 33 T.
+template <class T> __device__ __forceinline__ T block_sum(T v, T* shared) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) shared[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        T t = lane < warps ? shared[lane] : T(0);
+        t = warp_sum(t);
+        if (lane == 0) shared[32] = t;
+    }
+    __syncthreads();
+    return shared[32];
+}
+__device__ __forceinline__ float block_max(float v, float* shared) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) shared[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < warps ? shared[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) shared[32] = t;
+    }
+    __syncthreads();
+    return shared[32];
+}
+
+}  // namespace k
+}  // namespace msx

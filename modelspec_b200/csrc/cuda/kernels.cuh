@@ -1,0 +1,126 @@
+// Launchers of the sm_100a kernels of the training step. Every launcher enqueues on `stream` and
+// returns; none allocates or synchronises. Pointers are device pointers unless named `h_`.
+//
+// The translation units are compiled with -fmad=false: a multiply and an add written apart stay
+// two rounded operations, and every fused multiply-add is written as fmaf. That keeps each
+// kernel's rounding sequence the one its comment states.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace msx {
+namespace k {
+
+// ---- pointwise (pointwise.cu) -----------------------------------------------------------------
+enum class Binary : int { Add, Sub, Mul, Div };
+// out[i] = a[i] op b[i]; an operand with `*_scalar` set is one element read for every i.
+void binary(cudaStream_t s, Binary op, const float* a, bool a_scalar, const float* b, bool b_scalar,
+            float* out, uint64_t n);
+enum class Unary : int { Relu, Sqrt, Gelu, Copy };
+void unary(cudaStream_t s, Unary op, const float* a, float* out, uint64_t n);
+// out[i] = a[i] > 0 ? g[i] : 0 (relu) or gelu'(a[i]) * g[i] (gelu).
+void relu_grad(cudaStream_t s, const float* a, const float* g, float* out, uint64_t n);
+void gelu_grad(cudaStream_t s, const float* a, const float* g, float* out, uint64_t n);
+void fill_from_scalar(cudaStream_t s, const float* scalar, float* out, uint64_t n);
+// out[r, c] = x[r, c] + b[c]
+void add_rows(cudaStream_t s, const float* x, const float* b, float* out, uint64_t rows, uint64_t h);
+// out[c, r] = a[r, c]
+void transpose(cudaStream_t s, const float* a, float* out, uint64_t rows, uint64_t cols);
+
+// Philox4x32-10 dropout: element i (global index index_base + i) is kept iff word 0 of
+// philox([index, 4, token[0], token[1]], [seed lo, seed hi]) >= threshold; kept -> x * scale,
+// dropped -> +0. `token` is the i32[2] device input of the site.
+void dropout(cudaStream_t s, const float* x, const int32_t* token, uint64_t seed, uint32_t threshold,
+             float scale, uint64_t index_base, float* out, uint64_t n);
+
+// ---- reductions (reduce.cu) -------------------------------------------------------------------
+// Whole-tensor sums in f64, rounded to f32 once. `scratch` holds at least reduce_scratch_doubles()
+// doubles.
+uint64_t reduce_scratch_doubles();
+void reduce_sum(cudaStream_t s, const float* a, uint64_t n, bool mean, double* scratch, float* out);
+void mse(cudaStream_t s, const float* a, const float* b, uint64_t n, double* scratch, float* out);
+// out[c] = sum over rows of g[r, c]. `scratch` holds sum_rows_scratch_floats(rows, h) floats.
+uint32_t sum_rows_chunks(uint64_t rows);
+uint64_t sum_rows_scratch_floats(uint64_t rows, uint64_t h);
+void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out);
+
+// ---- row kernels (rowwise.cu) -----------------------------------------------------------------
+void layer_norm(cudaStream_t s, const float* x, const float* gamma, const float* beta, float* out,
+                uint64_t rows, uint64_t h);
+void layer_norm_grad_x(cudaStream_t s, const float* x, const float* gamma, const float* g, float* out,
+                       uint64_t rows, uint64_t h);
+// dgamma[c] = sum_r g[r, c] * xhat[r, c]; dbeta[c] = sum_r g[r, c] when dbeta is not null.
+// `scratch` holds layer_norm_grad_gamma_scratch_floats(rows, h) floats.
+uint64_t layer_norm_grad_gamma_scratch_floats(uint64_t rows, uint64_t h);
+void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float* scratch,
+                           float* dgamma, float* dbeta, uint64_t rows, uint64_t h);
+void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t k);
+void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, uint64_t rows, uint64_t k);
+// Row losses max + ln(sum exp(x - max)) - x[label] into row_loss[rows], then
+// loss = sum w * l / sum w (f64 sums, one rounding; 0 when the weights sum to 0).
+void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
+                   float* row_loss, double* scratch, float* loss, uint64_t rows, uint64_t v);
+// out[n, c] = g * w[n] / f32(sum w) * (softmax(logits[n])[c] - [c == labels[n]]); all 0 when the
+// weights sum to 0. `denominator` is a one-float scratch.
+void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
+                        const float* g, double* scratch, float* denominator, float* out, uint64_t rows,
+                        uint64_t v);
+
+// ---- embedding (embedding.cu) -----------------------------------------------------------------
+// out[n, :] = table[ids[n], :]; an id outside [0, rows) writes zeros and raises bit 0 of *status.
+void embedding(cudaStream_t s, const float* table, const int32_t* ids, float* out, uint64_t n,
+               uint64_t rows, uint64_t h, uint32_t* status);
+// out = zeros[rows, h] with g[n, :] added to row ids[n] in ascending n: bit-exact with a
+// sequential loop. `scratch` holds embedding_grad_scratch_ints(n, rows) ints.
+uint64_t embedding_grad_scratch_ints(uint64_t n, uint64_t rows);
+void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* out, uint64_t n,
+                    uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status);
+
+// ---- matmul (gemm.cu) -------------------------------------------------------------------------
+// C[m, n] = op(A) x op(B) (+ bias[n]) with each element one ascending-k fused chain starting
+// from its first product. `a_t`: A is stored [k, m] and read transposed; `b_t`: B stored [n, k].
+void matmul(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c,
+            uint64_t m, uint64_t n, uint64_t k);
+
+// ---- attention (attention.cu) -----------------------------------------------------------------
+struct AttentionShape {
+    uint32_t batch, q_len, k_len, heads, head_dim;  // q rows = batch * q_len, k rows = batch * k_len
+};
+// Row statistics shared by the backward kernels: stats[(row * heads + head) * 3 + {0, 1, 2}] =
+// max score, sum of exp(score - max), sum_j P[row, j] dP[row, j].
+uint64_t attention_stats_floats(AttentionShape shape);
+void attention_forward(cudaStream_t s, const float* q, const float* k, const float* v, const float* mask,
+                       float* out, AttentionShape shape);
+// Writes `stats`; `dq` may be null when only the statistics are wanted.
+void attention_grad_q(cudaStream_t s, const float* q, const float* k, const float* v, const float* mask,
+                      const float* g, float* stats, float* dq, AttentionShape shape);
+// Reads the `stats` attention_grad_q wrote for the same operands; dk and dv may each be null.
+void attention_grad_kv(cudaStream_t s, const float* q, const float* k, const float* v, const float* mask,
+                       const float* g, const float* stats, float* dk, float* dv, AttentionShape shape);
+
+// ---- optimizer (optimizer.cu) -----------------------------------------------------------------
+struct UpdateTensor {
+    float* p;
+    const float* g;
+    float* m;
+    float* v;
+    uint64_t count;
+};
+struct AdamWConstants {
+    float beta1, rest1, beta2, rest2, eps, weight_decay;
+};
+// One launch over every tensor of `d_tensors` (a device array of `tensors` entries; `chunks` =
+// d_chunk_tensor/d_chunk_start entries of kUpdateChunk elements each). p, m, v are updated in
+// place with the reference's 16 rounded f32 operations per element.
+constexpr uint32_t kUpdateChunk = 4096;
+void adamw(cudaStream_t s, const UpdateTensor* d_tensors, const uint32_t* d_chunk_tensor,
+           const uint32_t* d_chunk_start, uint32_t chunks, AdamWConstants c, const float* lr_t,
+           const float* c1, const float* c2);
+// p -= lr * g, `lr` a device scalar.
+void sgd(cudaStream_t s, const UpdateTensor* d_tensors, const uint32_t* d_chunk_tensor,
+         const uint32_t* d_chunk_start, uint32_t chunks, const float* lr);
+
+}  // namespace k
+}  // namespace msx

@@ -1,0 +1,128 @@
+// Whole-tensor sums (reduce_sum, mean, mse) and column sums (sum_rows).
+//
+// The reference sums a whole tensor sequentially in f64 and rounds once to f32
+// (crates/modelspec-runtime/src/cpu/interpreter.rs:903-917, :1913-1921). Here the f64 partial
+// sums are combined as a tree; the f64 result differs from the sequential one by a few units of
+// 2^-53 relative, so the rounded f32 is the same except across a rounding boundary (tolerance
+// class, deterministic). Column sums (the bias gradients, interpreter.rs:943-958) are f32 in two
+// stages: rows are split into chunks summed in ascending order, then the chunk sums are added in
+// ascending order; the split changes the rounding sequence (tolerance class, deterministic).
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace msx {
+namespace k {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr uint32_t kMaxBlocks = 592;  // 4 per SM
+
+enum class Whole : int { Sum, SquaredDifference };
+
+template <Whole KIND>
+__global__ void whole_stage1(const float* __restrict__ a, const float* __restrict__ b, uint64_t n,
+                             double* __restrict__ partial) {
+    __shared__ double shared[33];
+    double acc = 0.0;
+    uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t j = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n; j += stride) {
+        if (KIND == Whole::Sum) {
+            acc += static_cast<double>(a[j]);
+        } else {
+            double d = static_cast<double>(a[j]) - static_cast<double>(b[j]);
+            acc = fma(d, d, acc);
+        }
+    }
+    double total = block_sum(acc, shared);
+    if (threadIdx.x == 0) partial[blockIdx.x] = total;
+}
+
+__global__ void whole_stage2(const double* __restrict__ partial, uint32_t blocks, double divisor,
+                             float* __restrict__ out) {
+    __shared__ double shared[33];
+    double acc = 0.0;
+    for (uint32_t j = threadIdx.x; j < blocks; j += blockDim.x) acc += partial[j];
+    double total = block_sum(acc, shared);
+    if (threadIdx.x == 0) out[0] = static_cast<float>(total / divisor);
+}
+
+uint32_t whole_blocks(uint64_t n) {
+    uint64_t b = (n + kThreads * 4 - 1) / (kThreads * 4);
+    return static_cast<uint32_t>(b < 1 ? 1 : (b > kMaxBlocks ? kMaxBlocks : b));
+}
+
+// Block (32, 8): lane = column of a 32-column tile, each of the 8 warps takes every 8th row of
+// the block's row chunk.
+__global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint32_t h, uint32_t rows_per_chunk,
+                                float* __restrict__ partial) {
+    __shared__ float shared[8][32];
+    uint32_t c = blockIdx.x * 32 + threadIdx.x;
+    uint32_t r0 = blockIdx.y * rows_per_chunk;
+    uint32_t r1 = min(rows, r0 + rows_per_chunk);
+    float acc = 0.0f;
+    if (c < h)
+        for (uint32_t r = r0 + threadIdx.y; r < r1; r += 8) acc += g[static_cast<uint64_t>(r) * h + c];
+    shared[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < h) {
+        float total = shared[0][threadIdx.x];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) total += shared[w][threadIdx.x];
+        partial[static_cast<uint64_t>(blockIdx.y) * h + c] = total;
+    }
+}
+
+__global__ void sum_rows_stage2(const float* __restrict__ partial, uint32_t chunks, uint32_t h,
+                                float* __restrict__ out) {
+    uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= h) return;
+    float total = partial[c];
+    for (uint32_t k = 1; k < chunks; ++k) total += partial[static_cast<uint64_t>(k) * h + c];
+    out[c] = total;
+}
+
+}  // namespace
+
+uint32_t sum_rows_chunks(uint64_t rows) {
+    uint64_t chunks = (rows + 127) / 128;
+    return static_cast<uint32_t>(chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks));
+}
+
+uint64_t reduce_scratch_doubles() { return kMaxBlocks; }
+
+void reduce_sum(cudaStream_t s, const float* a, uint64_t n, bool mean, double* scratch, float* out) {
+    uint32_t blocks = whole_blocks(n);
+    whole_stage1<Whole::Sum><<<blocks, kThreads, 0, s>>>(a, nullptr, n, scratch);
+    check_launch("reduce_sum");
+    whole_stage2<<<1, kThreads, 0, s>>>(scratch, blocks, mean ? static_cast<double>(n) : 1.0, out);
+    check_launch("reduce_sum");
+}
+
+void mse(cudaStream_t s, const float* a, const float* b, uint64_t n, double* scratch, float* out) {
+    uint32_t blocks = whole_blocks(n);
+    whole_stage1<Whole::SquaredDifference><<<blocks, kThreads, 0, s>>>(a, b, n, scratch);
+    check_launch("mse");
+    whole_stage2<<<1, kThreads, 0, s>>>(scratch, blocks, static_cast<double>(n), out);
+    check_launch("mse");
+}
+
+uint64_t sum_rows_scratch_floats(uint64_t rows, uint64_t h) { return sum_rows_chunks(rows) * h; }
+
+void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out) {
+    if (h == 0) return;
+    uint32_t chunks = sum_rows_chunks(rows);
+    uint32_t rows_per_chunk = static_cast<uint32_t>((rows + chunks - 1) / chunks);
+    dim3 grid(static_cast<uint32_t>((h + 31) / 32), chunks);
+    sum_rows_stage1<<<grid, dim3(32, 8), 0, s>>>(g, static_cast<uint32_t>(rows), static_cast<uint32_t>(h),
+                                                 rows_per_chunk, chunks == 1 ? out : scratch);
+    check_launch("sum_rows");
+    if (chunks > 1) {
+        sum_rows_stage2<<<static_cast<uint32_t>((h + 127) / 128), 128, 0, s>>>(scratch, chunks,
+                                                                                static_cast<uint32_t>(h), out);
+        check_launch("sum_rows");
+    }
+}
+
+}  // namespace k
+}  // namespace msx

@@ -1,0 +1,323 @@
+// Row kernels: layer_norm and its two gradients, softmax and its gradient, cross_entropy and its
+// gradient. One warp per row for hidden-size rows, one block per row for vocabulary-size rows;
+// row reductions are warp-shuffle trees, so sums round in another order than the reference's
+// ascending-column loops (crates/modelspec-runtime/src/cpu/interpreter.rs:970-1034, :1172-1233,
+// :1513-1527): tolerance class, deterministic. The per-element formulas keep the reference's
+// operation order. All are HBM-bound; a row is read from L1/L2 on its second and third pass.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace msx {
+namespace k {
+
+uint32_t sum_rows_chunks(uint64_t rows);
+
+namespace {
+
+constexpr float kLayerNormEps = 1e-12f;
+constexpr int kWarpsPerBlock = 8;
+
+__device__ __forceinline__ void row_moments(const float* __restrict__ row, uint32_t h, int lane,
+                                            float* mean, float* rstd) {
+    float s = 0.0f;
+    for (uint32_t j = lane; j < h; j += 32) s += row[j];
+    float m = warp_sum(s) / static_cast<float>(h);
+    float q = 0.0f;
+    for (uint32_t j = lane; j < h; j += 32) {
+        float d = row[j] - m;
+        q = fmaf(d, d, q);
+    }
+    float variance = warp_sum(q) / static_cast<float>(h);
+    *mean = m;
+    *rstd = 1.0f / sqrtf(variance + kLayerNormEps);
+}
+
+__global__ void layer_norm_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                  const float* __restrict__ beta, float* __restrict__ out, uint32_t rows,
+                                  uint32_t h) {
+    int lane = threadIdx.x & 31;
+    uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const float* row = x + static_cast<uint64_t>(r) * h;
+    float mean, rstd;
+    row_moments(row, h, lane, &mean, &rstd);
+    float* o = out + static_cast<uint64_t>(r) * h;
+    for (uint32_t j = lane; j < h; j += 32) o[j] = (row[j] - mean) * rstd * gamma[j] + beta[j];
+}
+
+__global__ void layer_norm_grad_x_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                         const float* __restrict__ g, float* __restrict__ out, uint32_t rows,
+                                         uint32_t h) {
+    int lane = threadIdx.x & 31;
+    uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const float* row = x + static_cast<uint64_t>(r) * h;
+    const float* grow = g + static_cast<uint64_t>(r) * h;
+    float mean, rstd;
+    row_moments(row, h, lane, &mean, &rstd);
+    float s1 = 0.0f, s2 = 0.0f;
+    for (uint32_t j = lane; j < h; j += 32) {
+        float gx = grow[j] * gamma[j];
+        float xhat = (row[j] - mean) * rstd;
+        s1 += gx;
+        s2 = fmaf(gx, xhat, s2);
+    }
+    float width = static_cast<float>(h);
+    float mean_gx = warp_sum(s1) / width, mean_gx_xhat = warp_sum(s2) / width;
+    float* o = out + static_cast<uint64_t>(r) * h;
+    for (uint32_t j = lane; j < h; j += 32) {
+        float gx = grow[j] * gamma[j];
+        float xhat = (row[j] - mean) * rstd;
+        o[j] = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
+    }
+}
+
+__global__ void row_stats_kernel(const float* __restrict__ x, float* __restrict__ stats, uint32_t rows,
+                                 uint32_t h) {
+    int lane = threadIdx.x & 31;
+    uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    float mean, rstd;
+    row_moments(x + static_cast<uint64_t>(r) * h, h, lane, &mean, &rstd);
+    if (lane == 0) {
+        stats[2 * r] = mean;
+        stats[2 * r + 1] = rstd;
+    }
+}
+
+// Block (32, 8) over a 32-column tile and a chunk of rows: partial column sums of g * xhat and,
+// when wanted, of g.
+__global__ void grad_gamma_stage1(const float* __restrict__ x, const float* __restrict__ g,
+                                  const float* __restrict__ stats, uint32_t rows, uint32_t h,
+                                  uint32_t rows_per_chunk, float* __restrict__ partial_gamma,
+                                  float* __restrict__ partial_beta) {
+    __shared__ float sg[8][32], sb[8][32];
+    uint32_t c = blockIdx.x * 32 + threadIdx.x;
+    uint32_t r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+    float acc_g = 0.0f, acc_b = 0.0f;
+    if (c < h)
+        for (uint32_t r = r0 + threadIdx.y; r < r1; r += 8) {
+            float gv = g[static_cast<uint64_t>(r) * h + c];
+            float xhat = (x[static_cast<uint64_t>(r) * h + c] - stats[2 * r]) * stats[2 * r + 1];
+            acc_g = fmaf(gv, xhat, acc_g);
+            acc_b += gv;
+        }
+    sg[threadIdx.y][threadIdx.x] = acc_g;
+    sb[threadIdx.y][threadIdx.x] = acc_b;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < h) {
+        float tg = sg[0][threadIdx.x], tb = sb[0][threadIdx.x];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) {
+            tg += sg[w][threadIdx.x];
+            tb += sb[w][threadIdx.x];
+        }
+        partial_gamma[static_cast<uint64_t>(blockIdx.y) * h + c] = tg;
+        if (partial_beta) partial_beta[static_cast<uint64_t>(blockIdx.y) * h + c] = tb;
+    }
+}
+
+__global__ void grad_gamma_stage2(const float* __restrict__ partial_gamma, const float* __restrict__ partial_beta,
+                                  uint32_t chunks, uint32_t h, float* __restrict__ dgamma,
+                                  float* __restrict__ dbeta) {
+    uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= h) return;
+    float tg = partial_gamma[c];
+    for (uint32_t k = 1; k < chunks; ++k) tg += partial_gamma[static_cast<uint64_t>(k) * h + c];
+    dgamma[c] = tg;
+    if (dbeta) {
+        float tb = partial_beta[c];
+        for (uint32_t k = 1; k < chunks; ++k) tb += partial_beta[static_cast<uint64_t>(k) * h + c];
+        dbeta[c] = tb;
+    }
+}
+
+constexpr int kRowThreads = 256;
+
+// Max of the row (the first element, replaced only by a greater one: NaN never wins) and the sum
+// of exp(x - max), by a block.
+__device__ __forceinline__ void block_row_softmax(const float* __restrict__ row, uint32_t v, float* shared,
+                                                  float* max, float* total) {
+    float m = -INFINITY;
+    for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) {
+        float x = row[c];
+        if (x > m) m = x;
+    }
+    m = block_max(m, shared);
+    float s = 0.0f;
+    for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) s += expf(row[c] - m);
+    *max = m;
+    *total = block_sum(s, shared);
+}
+
+__global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ out, uint32_t k) {
+    __shared__ float shared[33];
+    const float* row = x + static_cast<uint64_t>(blockIdx.x) * k;
+    float max, total;
+    block_row_softmax(row, k, shared, &max, &total);
+    float* o = out + static_cast<uint64_t>(blockIdx.x) * k;
+    for (uint32_t c = threadIdx.x; c < k; c += blockDim.x) o[c] = expf(row[c] - max) / total;
+}
+
+__global__ void softmax_grad_kernel(const float* __restrict__ y, const float* __restrict__ g,
+                                    float* __restrict__ out, uint32_t k) {
+    __shared__ float shared[33];
+    const float* yr = y + static_cast<uint64_t>(blockIdx.x) * k;
+    const float* gr = g + static_cast<uint64_t>(blockIdx.x) * k;
+    float acc = 0.0f;
+    for (uint32_t c = threadIdx.x; c < k; c += blockDim.x) acc = fmaf(gr[c], yr[c], acc);
+    float d = block_sum(acc, shared);
+    float* o = out + static_cast<uint64_t>(blockIdx.x) * k;
+    for (uint32_t c = threadIdx.x; c < k; c += blockDim.x) o[c] = yr[c] * (gr[c] - d);
+}
+
+__global__ void cross_entropy_rows_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+                                          const float* __restrict__ weights, float* __restrict__ row_loss,
+                                          uint32_t v) {
+    __shared__ float shared[33];
+    uint32_t r = blockIdx.x;
+    // A row of weight 0 adds w * l = 0 to the loss whatever its logits: skip its passes.
+    if (weights[r] == 0.0f) {
+        if (threadIdx.x == 0) row_loss[r] = 0.0f;
+        return;
+    }
+    const float* row = logits + static_cast<uint64_t>(r) * v;
+    float max, total;
+    block_row_softmax(row, v, shared, &max, &total);
+    if (threadIdx.x == 0) {
+        int32_t label = labels[r];
+        float picked = (label >= 0 && static_cast<uint32_t>(label) < v) ? row[label] : 0.0f;
+        row_loss[r] = max + logf(total) - picked;
+    }
+}
+
+// loss = sum_n w[n] l[n] / sum_n w[n], both sums in f64 (a tree over the block), one rounding.
+__global__ void cross_entropy_loss_kernel(const float* __restrict__ row_loss, const float* __restrict__ weights,
+                                          uint32_t rows, float* __restrict__ loss) {
+    __shared__ double shared[33];
+    double num = 0.0, den = 0.0;
+    for (uint32_t r = threadIdx.x; r < rows; r += blockDim.x) {
+        double w = static_cast<double>(weights[r]);
+        num = fma(w, static_cast<double>(row_loss[r]), num);
+        den += w;
+    }
+    num = block_sum(num, shared);
+    den = block_sum(den, shared);
+    if (threadIdx.x == 0) loss[0] = den == 0.0 ? 0.0f : static_cast<float>(num / den);
+}
+
+__global__ void weight_sum_kernel(const float* __restrict__ weights, uint32_t rows, float* __restrict__ out) {
+    __shared__ double shared[33];
+    double den = 0.0;
+    for (uint32_t r = threadIdx.x; r < rows; r += blockDim.x) den += static_cast<double>(weights[r]);
+    den = block_sum(den, shared);
+    if (threadIdx.x == 0) out[0] = static_cast<float>(den);
+}
+
+__global__ void cross_entropy_grad_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+                                          const float* __restrict__ weights, const float* __restrict__ g,
+                                          const float* __restrict__ denominator, float* __restrict__ out,
+                                          uint32_t v) {
+    __shared__ float shared[33];
+    uint32_t r = blockIdx.x;
+    float* o = out + static_cast<uint64_t>(r) * v;
+    float den = denominator[0], w = weights[r];
+    if (den == 0.0f || w == 0.0f) {
+        for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) o[c] = 0.0f;
+        return;
+    }
+    const float* row = logits + static_cast<uint64_t>(r) * v;
+    float max, total;
+    block_row_softmax(row, v, shared, &max, &total);
+    float scale = g[0] * w / den;
+    uint32_t label = static_cast<uint32_t>(labels[r]);
+    for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) {
+        float target = c == label ? 1.0f : 0.0f;
+        o[c] = scale * (expf(row[c] - max) / total - target);
+    }
+}
+
+inline uint32_t warp_row_blocks(uint64_t rows) { return static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock); }
+
+}  // namespace
+
+void layer_norm(cudaStream_t s, const float* x, const float* gamma, const float* beta, float* out,
+                uint64_t rows, uint64_t h) {
+    if (rows == 0) return;
+    layer_norm_kernel<<<warp_row_blocks(rows), kWarpsPerBlock * 32, 0, s>>>(x, gamma, beta, out,
+                                                                            static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
+    check_launch("layer_norm");
+}
+
+void layer_norm_grad_x(cudaStream_t s, const float* x, const float* gamma, const float* g, float* out,
+                       uint64_t rows, uint64_t h) {
+    if (rows == 0) return;
+    layer_norm_grad_x_kernel<<<warp_row_blocks(rows), kWarpsPerBlock * 32, 0, s>>>(
+        x, gamma, g, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
+    check_launch("layer_norm_grad_x");
+}
+
+uint64_t layer_norm_grad_gamma_scratch_floats(uint64_t rows, uint64_t h) {
+    return 2 * rows + 2 * sum_rows_chunks(rows) * h;
+}
+
+void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float* scratch, float* dgamma,
+                           float* dbeta, uint64_t rows, uint64_t h) {
+    if (h == 0) return;
+    uint32_t chunks = sum_rows_chunks(rows);
+    uint32_t rows_per_chunk = static_cast<uint32_t>((rows + chunks - 1) / chunks);
+    float* stats = scratch;
+    float* partial_gamma = scratch + 2 * rows;
+    float* partial_beta = partial_gamma + static_cast<uint64_t>(chunks) * h;
+    if (rows > 0) {
+        row_stats_kernel<<<warp_row_blocks(rows), kWarpsPerBlock * 32, 0, s>>>(x, stats, static_cast<uint32_t>(rows),
+                                                                                static_cast<uint32_t>(h));
+        check_launch("layer_norm_grad_gamma");
+    }
+    dim3 grid(static_cast<uint32_t>((h + 31) / 32), chunks);
+    grad_gamma_stage1<<<grid, dim3(32, 8), 0, s>>>(x, g, stats, static_cast<uint32_t>(rows), static_cast<uint32_t>(h),
+                                                   rows_per_chunk, partial_gamma, dbeta ? partial_beta : nullptr);
+    check_launch("layer_norm_grad_gamma");
+    grad_gamma_stage2<<<static_cast<uint32_t>((h + 127) / 128), 128, 0, s>>>(partial_gamma, partial_beta, chunks,
+                                                                              static_cast<uint32_t>(h), dgamma, dbeta);
+    check_launch("layer_norm_grad_gamma");
+}
+
+void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t k) {
+    if (rows == 0) return;
+    softmax_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(x, out, static_cast<uint32_t>(k));
+    check_launch("softmax");
+}
+
+void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, uint64_t rows, uint64_t k) {
+    if (rows == 0) return;
+    softmax_grad_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(y, g, out, static_cast<uint32_t>(k));
+    check_launch("softmax_grad");
+}
+
+void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
+                   float* row_loss, double* scratch, float* loss, uint64_t rows, uint64_t v) {
+    (void)scratch;
+    if (rows > 0) {
+        cross_entropy_rows_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, row_loss,
+                                                                                      static_cast<uint32_t>(v));
+        check_launch("cross_entropy");
+    }
+    cross_entropy_loss_kernel<<<1, 1024, 0, s>>>(row_loss, weights, static_cast<uint32_t>(rows), loss);
+    check_launch("cross_entropy");
+}
+
+void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
+                        const float* g, double* scratch, float* denominator, float* out, uint64_t rows,
+                        uint64_t v) {
+    (void)scratch;
+    if (rows == 0) return;
+    weight_sum_kernel<<<1, 1024, 0, s>>>(weights, static_cast<uint32_t>(rows), denominator);
+    check_launch("cross_entropy_grad");
+    cross_entropy_grad_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, g, denominator,
+                                                                                  out, static_cast<uint32_t>(v));
+    check_launch("cross_entropy_grad");
+}
+
+}  // namespace k
+}  // namespace msx

@@ -1,0 +1,1482 @@
+// The msx C ABI (include/msx.h): devices, plans, transfers and step submission.
+//
+// A plan is built once from the text of a Tensor IR program: the scheduler below walks the live
+// nodes in definition order and emits kernel launches (plan.hpp lists the fusions), a linear-scan
+// allocator places every intermediate in one arena by liveness, and the launches are captured
+// into one CUDA graph at the first step. A step is then one host-to-device copy of the staged
+// inputs, one graph launch and one 4-byte read-back of the loss, all on the plan's stream; the
+// host never waits inside msx_run unless all of its staging slots are still in flight.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <set>
+#include <thread>
+
+#include "../../../include/msx.h"
+#include "../core/frontend.hpp"
+#include "../core/rng.hpp"
+#include "common.cuh"
+#include "kernels.cuh"
+#include "plan.hpp"
+
+using msx::Launch;
+using msx::Node;
+using msx::Op;
+using msx::Program;
+using msx::Role;
+using msx::Slot;
+namespace k = msx::k;
+
+namespace {
+
+constexpr uint64_t kAlign = 256;
+constexpr int kStagingSlots = 8;  // steps in flight before msx_run waits (the reference's SUBMIT_STEPS)
+
+uint64_t align_up(uint64_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
+
+thread_local std::string g_open_error;
+
+struct StatusError : std::runtime_error {
+    int status;
+    StatusError(int s, const std::string& what) : std::runtime_error(what), status(s) {}
+};
+
+}  // namespace
+
+struct msx_device {
+    int ordinal = 0;
+    std::string error;
+};
+
+struct InputCheck {
+    enum Kind { Ids, Labels, KeyMask, Weights } kind;
+    uint64_t bound = 0;  // Ids: table rows; Labels: classes; KeyMask: keys per sequence
+};
+
+struct HostInput {
+    std::string name;
+    uint32_t pos = 0;  // node position
+    uint64_t bytes = 0, offset = 0;
+    bool i32 = false;
+    std::vector<InputCheck> checks;
+};
+
+struct msx_plan {
+    msx_device* device = nullptr;
+    Program program;
+    uint64_t seed = 0;
+    uint32_t flags = 0;
+    msx_plan* shares = nullptr;
+
+    std::vector<Slot> slots;  // one per node, then scratch slots
+    std::vector<Launch> launches;
+    std::vector<HostInput> inputs;
+
+    cudaStream_t stream = nullptr;
+    char* arena = nullptr;
+    uint64_t arena_bytes = 0, unshared_bytes = 0;
+    std::vector<float*> params, m, v;  // by parameter index; null when the program has none
+    std::vector<char> owns_param;
+    char* d_inputs = nullptr;
+    uint64_t input_bytes = 0;
+    std::vector<char> blob;  // the staged inputs, host side
+    bool blob_dirty = true;  // staged since the last upload
+    char* pinned[kStagingSlots] = {};
+    float* pinned_loss = nullptr;  // kStagingSlots floats
+    cudaEvent_t slot_done[kStagingSlots] = {};
+    bool slot_used[kStagingSlots] = {};
+    std::vector<float> consts;
+    float* d_consts = nullptr;
+    uint32_t* d_status = nullptr;
+    uint32_t* pinned_status = nullptr;
+    void* d_update_tables = nullptr;
+
+    int loss_pos = -1;
+    uint64_t steps = 0;
+    uint64_t shard_rows_before = 0;
+
+    cudaGraphExec_t graph = nullptr;
+    cudaEvent_t clock_start = nullptr, clock_stop = nullptr;
+    uint64_t clock_steps = 0;
+
+    uint64_t live_nodes = 0, param_bytes = 0;
+
+    void* ptr(uint32_t pos) const {
+        const Slot& s = slots[pos];
+        switch (s.kind) {
+            case Slot::Arena: return arena + s.offset;
+            case Slot::Param: return params[s.index];
+            case Slot::Moment: return (s.moment == 'm' ? m : v)[s.index];
+            case Slot::Input: return d_inputs + s.offset;
+            case Slot::Const: return d_consts + s.offset;
+            case Slot::View: return ptr(s.index);
+            default: return nullptr;
+        }
+    }
+    float* f(uint32_t pos) const { return static_cast<float*>(ptr(pos)); }
+    int32_t* i(uint32_t pos) const { return static_cast<int32_t*>(ptr(pos)); }
+    bool transposed(uint32_t pos) const {
+        const Slot& s = slots[pos];
+        return s.kind == Slot::View ? !transposed(s.index) : false;
+    }
+};
+
+namespace {
+
+void cuda_ok(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return;
+    int status = e == cudaErrorMemoryAllocation ? MSX_OUT_OF_MEMORY : MSX_LAUNCH_FAILED;
+    throw StatusError(status, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The scheduler.
+
+struct Scheduler {
+    msx_plan* P;
+    const Program& prog;
+    std::vector<char> live, handled;
+    std::vector<std::vector<uint32_t>> users;  // live consumers of each node position
+
+    explicit Scheduler(msx_plan* plan) : P(plan), prog(plan->program) {}
+
+    uint32_t pos(uint32_t id) const {
+        int at = prog.position(id);
+        if (at < 0) throw StatusError(MSX_UNSUPPORTED, "value %" + std::to_string(id) + " is not defined");
+        return static_cast<uint32_t>(at);
+    }
+    const Node& node(uint32_t position) const { return prog.nodes[position]; }
+    [[noreturn]] void unsupported(const Node& n, const std::string& why) const {
+        throw StatusError(MSX_UNSUPPORTED, "E-TARGET-011: %" + std::to_string(n.id) + " " + msx::op_name(n.op) +
+                                               " has no CUDA kernel: " + why);
+    }
+
+    uint32_t scratch(uint64_t bytes) {
+        Slot s;
+        s.kind = Slot::Arena;
+        s.bytes = std::max<uint64_t>(bytes, 4);
+        P->slots.push_back(s);
+        return static_cast<uint32_t>(P->slots.size() - 1);
+    }
+
+    Launch& emit(const char* kernel, const Node& n, std::vector<uint32_t> reads, std::vector<uint32_t> writes,
+                 std::function<void(cudaStream_t)> run) {
+        Launch l;
+        l.kernel = kernel;
+        l.value = n.id;
+        // A folded Transpose is read through its source.
+        for (uint32_t& r : reads)
+            while (P->slots[r].kind == Slot::View) r = P->slots[r].index;
+        l.reads = std::move(reads);
+        l.writes = std::move(writes);
+        l.run = std::move(run);
+        P->launches.push_back(std::move(l));
+        return P->launches.back();
+    }
+
+    bool is_scalar_operand(uint32_t operand_pos, const Node& result) const {
+        return node(operand_pos).ty.rank() == 0 && result.ty.rank() > 0;
+    }
+
+    void run() {
+        const size_t n = prog.nodes.size();
+        P->slots.assign(n, Slot{});
+        live.assign(n, 0);
+        handled.assign(n, 0);
+        users.assign(n, {});
+        for (const msx::Output& o : prog.outputs) live[pos(o.value)] = 1;
+        for (size_t at = n; at-- > 0;)
+            if (live[at])
+                for (uint32_t o : node(static_cast<uint32_t>(at)).operands) live[pos(o)] = 1;
+        for (size_t at = 0; at < n; ++at)
+            if (live[at]) {
+                ++P->live_nodes;
+                for (uint32_t o : node(static_cast<uint32_t>(at)).operands) users[pos(o)].push_back(static_cast<uint32_t>(at));
+            }
+        place_leaves();
+        fold_constants();
+        plan_optimizer();
+        fold_transposes();
+        for (uint32_t at = 0; at < n; ++at)
+            if (live[at] && !handled[at]) schedule(at);
+        emit_optimizer();
+        for (const msx::Output& o : prog.outputs) {
+            Slot& s = P->slots[pos(o.value)];
+            s.keep = true;
+        }
+        if (!prog.outputs.empty()) {
+            const msx::Output* loss = nullptr;
+            for (const msx::Output& o : prog.outputs)
+                if (o.role == Role::Loss) loss = &o;
+            if (!loss && node(pos(prog.outputs[0].value)).ty.rank() == 0) loss = &prog.outputs[0];
+            if (loss) P->loss_pos = static_cast<int>(pos(loss->value));
+        }
+    }
+
+    // Parameters, host inputs and moments get their storage class; inputs are laid out in the
+    // upload region in node order.
+    void place_leaves() {
+        const size_t np = prog.params.size();
+        P->params.assign(np, nullptr);
+        P->m.assign(np, nullptr);
+        P->v.assign(np, nullptr);
+        P->owns_param.assign(np, 0);
+        uint64_t offset = 0;
+        for (uint32_t at = 0; at < prog.nodes.size(); ++at) {
+            const Node& nd = node(at);
+            Slot& s = P->slots[at];
+            s.bytes = nd.ty.count() * 4;
+            if (nd.op == Op::ParamRead) {
+                s.kind = Slot::Param;
+                s.index = nd.param;
+                handled[at] = 1;
+            } else if (nd.op == Op::Input) {
+                handled[at] = 1;
+                bool moment = false;
+                for (char which : {'m', 'v'}) {
+                    std::string prefix = std::string("optimizer.") + which + "@";
+                    if (nd.name.compare(0, prefix.size(), prefix) == 0) {
+                        int param = prog.param_index(nd.name.substr(prefix.size()));
+                        if (param < 0) throw StatusError(MSX_UNSUPPORTED, "moment input of an unknown parameter: " + nd.name);
+                        s.kind = Slot::Moment;
+                        s.index = static_cast<uint32_t>(param);
+                        s.moment = which;
+                        moment = true;
+                    }
+                }
+                if (moment || !live[at]) continue;
+                s.kind = Slot::Input;
+                s.offset = offset;
+                HostInput in;
+                in.name = nd.name;
+                in.pos = at;
+                in.bytes = s.bytes;
+                in.offset = offset;
+                in.i32 = nd.ty.i32;
+                P->inputs.push_back(in);
+                offset += align_up(s.bytes);
+            }
+        }
+        P->input_bytes = offset;
+        // What the reference's interpreter checks before a run, by how each input is read.
+        for (HostInput& in : P->inputs)
+            for (uint32_t u : users[in.pos]) {
+                const Node& user = node(u);
+                auto operand_is = [&](size_t kth) { return user.operands.size() > kth && pos(user.operands[kth]) == in.pos; };
+                if (user.op == Op::Embedding && operand_is(1))
+                    in.checks.push_back({InputCheck::Ids, node(pos(user.operands[0])).ty.shape[0]});
+                if (user.op == Op::EmbeddingGrad && operand_is(0)) in.checks.push_back({InputCheck::Ids, user.rows});
+                if ((user.op == Op::CrossEntropy || user.op == Op::CrossEntropyGrad) && operand_is(1))
+                    in.checks.push_back({InputCheck::Labels, node(pos(user.operands[0])).ty.shape[1]});
+                if ((user.op == Op::CrossEntropy || user.op == Op::CrossEntropyGrad) && operand_is(2))
+                    in.checks.push_back({InputCheck::Weights, 0});
+                if ((user.op == Op::Attention || user.op == Op::AttentionGradQ || user.op == Op::AttentionGradK ||
+                     user.op == Op::AttentionGradV) && operand_is(3))
+                    in.checks.push_back({InputCheck::KeyMask, in.bytes / 4 / std::max<uint64_t>(1, node(in.pos).ty.shape[0])});
+            }
+    }
+
+    void set_const(uint32_t at, float value) {
+        Slot& s = P->slots[at];
+        s.kind = Slot::Const;
+        s.constant = value;
+        s.offset = P->consts.size() * sizeof(float);
+        s.bytes = 4;
+        P->consts.push_back(value);
+        handled[at] = 1;
+    }
+
+    // Rank-0 expressions over constants, each one rounded f32 operation as on the device.
+    void fold_constants() {
+        for (uint32_t at = 0; at < prog.nodes.size(); ++at) {
+            const Node& nd = node(at);
+            if (!live[at] || nd.ty.rank() != 0 || nd.ty.i32) continue;
+            if (nd.op == Op::Scalar) {
+                set_const(at, nd.scalar);
+                continue;
+            }
+            bool all_const = !nd.operands.empty();
+            for (uint32_t o : nd.operands) all_const = all_const && P->slots[pos(o)].kind == Slot::Const;
+            if (!all_const) continue;
+            auto c = [&](size_t kth) { return P->slots[pos(nd.operands[kth])].constant; };
+            volatile float r;
+            switch (nd.op) {
+                case Op::Add: r = c(0) + c(1); break;
+                case Op::Sub: r = c(0) - c(1); break;
+                case Op::Mul: r = c(0) * c(1); break;
+                case Op::Div: r = c(0) / c(1); break;
+                case Op::Sqrt: r = std::sqrt(c(0)); break;
+                case Op::StopGradient: r = c(0); break;
+                default: continue;
+            }
+            set_const(at, r);
+        }
+    }
+
+    // ---- the optimizer subgraph ------------------------------------------------------------
+    struct Update {
+        uint32_t param, grad_pos;
+    };
+    std::vector<Update> updates;
+
+    void plan_optimizer() {
+        if (prog.optimizer.rule == msx::Rule::None) return;
+        std::map<uint32_t, uint32_t> grad_of;  // param -> gradient position
+        std::set<uint32_t> stops;
+        for (const msx::Output& o : prog.outputs)
+            if (o.role == Role::Gradient) {
+                grad_of[o.param] = pos(o.value);
+                stops.insert(pos(o.value));
+            }
+        // Everything between the gradients and the update / next-moment outputs is the update
+        // subgraph: it runs as one multi-tensor launch and its nodes get no storage.
+        std::vector<uint32_t> work;
+        for (const msx::Output& o : prog.outputs) {
+            if (o.role != Role::Update && o.role != Role::Moment) continue;
+            uint32_t at = pos(o.value);
+            if (o.role == Role::Update) {
+                const Node& nd = node(at);
+                bool shape = nd.op == Op::Sub && nd.operands.size() == 2 && node(pos(nd.operands[0])).op == Op::ParamRead &&
+                             node(pos(nd.operands[0])).param == o.param;
+                if (!shape || !grad_of.count(o.param))
+                    throw StatusError(MSX_UNSUPPORTED, "the update of @" + prog.params[o.param].path +
+                                                           " is not `p - rate * step` over its gradient");
+                updates.push_back({o.param, grad_of[o.param]});
+                P->slots[at].kind = Slot::Param;
+                P->slots[at].index = o.param;
+            } else {
+                P->slots[at].kind = Slot::Moment;
+                P->slots[at].index = o.param;
+                P->slots[at].moment = o.moment;
+            }
+            work.push_back(at);
+        }
+        while (!work.empty()) {
+            uint32_t at = work.back();
+            work.pop_back();
+            if (handled[at] || stops.count(at)) continue;
+            const Node& nd = node(at);
+            if (nd.op == Op::ParamRead || nd.op == Op::Input || P->slots[at].kind == Slot::Const) continue;
+            handled[at] = 1;
+            for (uint32_t o : nd.operands) work.push_back(pos(o));
+        }
+        if (prog.optimizer.rule == msx::Rule::AdamW)
+            for (const Update& u : updates) {
+                bool has_m = false, has_v = false;
+                for (const msx::Output& o : prog.outputs)
+                    if (o.role == Role::Moment && o.param == u.param) (o.moment == 'm' ? has_m : has_v) = true;
+                if (!has_m || !has_v)
+                    throw StatusError(MSX_UNSUPPORTED, "an adamw step without both next moments of @" + prog.params[u.param].path);
+            }
+    }
+
+    void emit_optimizer() {
+        if (updates.empty()) return;
+        msx_plan* plan = P;
+        // Device tables: tensors, then the chunk -> (tensor, start) map.
+        std::vector<uint32_t> chunk_tensor, chunk_start;
+        for (uint32_t t = 0; t < updates.size(); ++t) {
+            uint64_t count = prog.params[updates[t].param].ty.count();
+            for (uint64_t c = 0; c * k::kUpdateChunk < count; ++c) {
+                chunk_tensor.push_back(t);
+                chunk_start.push_back(static_cast<uint32_t>(c));
+            }
+        }
+        uint32_t chunks = static_cast<uint32_t>(chunk_tensor.size());
+        const size_t n_updates = updates.size();
+        update_chunk_tensor = chunk_tensor;
+        update_chunk_start = chunk_start;
+        std::vector<uint32_t> reads, writes;
+        uint64_t elements = 0;
+        for (const Update& u : updates) {
+            reads.push_back(u.grad_pos);
+            elements += prog.params[u.param].ty.count();
+        }
+        Node pseudo;
+        pseudo.id = node(updates[0].grad_pos).id;
+        bool adamw = prog.optimizer.rule == msx::Rule::AdamW;
+        const msx::OptimizerInfo& o = prog.optimizer;
+        if (adamw) {
+            msx::AdamW a{o.weight_decay, o.beta1, o.beta2, o.eps, o.warmup_steps};
+            std::vector<float> c = a.constants();
+            k::AdamWConstants constants{c[0], c[1], c[2], c[3], c[4], c[5]};
+            int lr_t = -1, c1 = -1, c2 = -1;
+            for (uint32_t at = 0; at < prog.nodes.size(); ++at) {
+                const Node& nd = node(at);
+                if (nd.op != Op::Input) continue;
+                if (nd.name == "optimizer.lr_t") lr_t = static_cast<int>(at);
+                if (nd.name == "optimizer.c1") c1 = static_cast<int>(at);
+                if (nd.name == "optimizer.c2") c2 = static_cast<int>(at);
+            }
+            if (lr_t < 0 || c1 < 0 || c2 < 0) throw StatusError(MSX_UNSUPPORTED, "an adamw step without its lr_t, c1, c2 inputs");
+            reads.push_back(static_cast<uint32_t>(lr_t));
+            reads.push_back(static_cast<uint32_t>(c1));
+            reads.push_back(static_cast<uint32_t>(c2));
+            Launch& l = emit("adamw_multi_tensor", pseudo, reads, writes, [=](cudaStream_t s) {
+                auto* tensors = static_cast<k::UpdateTensor*>(plan->d_update_tables);
+                auto* ct = reinterpret_cast<uint32_t*>(tensors + n_updates);
+                k::adamw(s, tensors, ct, ct + chunks, chunks, constants, plan->f(static_cast<uint32_t>(lr_t)),
+                         plan->f(static_cast<uint32_t>(c1)), plan->f(static_cast<uint32_t>(c2)));
+            });
+            l.flop = 16 * elements;
+            optimizer_bytes = 28 * elements;
+        } else {
+            // The rate is the folded Scalar the update multiplies the gradient by.
+            const Node& sub = node(update_node(updates[0].param));
+            const Node& scaled = node(pos(sub.operands[1]));
+            uint32_t rate = pos(scaled.operands[0]);
+            if (scaled.op != Op::Mul || P->slots[rate].kind != Slot::Const)
+                throw StatusError(MSX_UNSUPPORTED, "the sgd update is not `p - lr * g` with a constant rate");
+            reads.push_back(rate);
+            Launch& l = emit("sgd_multi_tensor", pseudo, reads, writes, [=](cudaStream_t s) {
+                auto* tensors = static_cast<k::UpdateTensor*>(plan->d_update_tables);
+                auto* ct = reinterpret_cast<uint32_t*>(tensors + n_updates);
+                k::sgd(s, tensors, ct, ct + chunks, chunks, plan->f(rate));
+            });
+            l.flop = 2 * elements;
+            optimizer_bytes = 12 * elements;
+        }
+    }
+    std::vector<uint32_t> update_chunk_tensor, update_chunk_start;
+    uint64_t optimizer_bytes = 0;
+    uint32_t update_node(uint32_t param) const {
+        for (const msx::Output& o : prog.outputs)
+            if (o.role == Role::Update && o.param == param) return pos(o.value);
+        throw StatusError(MSX_UNSUPPORTED, "no update");
+    }
+
+    // ---- transposes ------------------------------------------------------------------------
+    // matmul_of[t] = position of the matmul a Transpose node t absorbs (its operands swapped).
+    std::map<uint32_t, uint32_t> absorbed_matmul;
+
+    // Whether the Transpose at `at` can be read in place by everything that reads it: matmuls,
+    // and transposes that can themselves be read in place.
+    bool folds(uint32_t at, std::map<uint32_t, bool>& memo) {
+        auto known = memo.find(at);
+        if (known != memo.end()) return known->second;
+        bool ok = !users[at].empty();
+        for (const msx::Output& o : prog.outputs) ok = ok && pos(o.value) != at;
+        for (uint32_t u : users[at]) {
+            if (!ok) break;
+            const Node& user = node(u);
+            if (handled[u]) ok = false;
+            else if (user.op == Op::MatMul) continue;
+            else if (user.op == Op::Transpose) ok = folds(u, memo);
+            else ok = false;
+        }
+        memo[at] = ok;
+        return ok;
+    }
+
+    void fold_transposes() {
+        std::map<uint32_t, bool> memo;
+        for (uint32_t at = 0; at < prog.nodes.size(); ++at) {
+            const Node& nd = node(at);
+            if (!live[at] || handled[at] || nd.op != Op::Transpose) continue;
+            if (folds(at, memo)) {
+                Slot& s = P->slots[at];
+                s.kind = Slot::View;
+                s.index = pos(nd.operands[0]);
+                handled[at] = 1;
+                continue;
+            }
+            uint32_t src = pos(nd.operands[0]);
+            bool src_output = false;
+            for (const msx::Output& o : prog.outputs) src_output = src_output || pos(o.value) == src;
+            if (node(src).op == Op::MatMul && users[src].size() == 1 && !src_output && !handled[src]) {
+                absorbed_matmul[at] = src;
+                handled[src] = 1;  // never materialised
+            }
+        }
+    }
+
+    // ---- one node --------------------------------------------------------------------------
+    void schedule(uint32_t at) {
+        const Node& nd = node(at);
+        msx_plan* plan = P;
+        Slot& out = P->slots[at];
+        out.kind = Slot::Arena;
+        out.bytes = std::max<uint64_t>(nd.ty.count() * 4, 4);
+        std::vector<uint32_t> in;
+        for (uint32_t o : nd.operands) in.push_back(pos(o));
+        const uint64_t count = nd.ty.count();
+        auto rows_of = [&](uint32_t p) { return node(p).ty.shape.at(0); };
+        auto cols_of = [&](uint32_t p) { return node(p).ty.shape.at(1); };
+        switch (nd.op) {
+            case Op::Add:
+            case Op::Sub:
+            case Op::Mul:
+            case Op::Div: {
+                k::Binary op = nd.op == Op::Add ? k::Binary::Add : nd.op == Op::Sub ? k::Binary::Sub
+                               : nd.op == Op::Mul ? k::Binary::Mul : k::Binary::Div;
+                bool sa = is_scalar_operand(in[0], nd), sb = is_scalar_operand(in[1], nd);
+                uint32_t a = in[0], b = in[1];
+                emit("binary", nd, in, {at}, [=](cudaStream_t s) { k::binary(s, op, plan->f(a), sa, plan->f(b), sb, plan->f(at), count); });
+                break;
+            }
+            case Op::Relu:
+            case Op::Sqrt:
+            case Op::Gelu:
+            case Op::StopGradient: {
+                k::Unary op = nd.op == Op::Relu ? k::Unary::Relu : nd.op == Op::Sqrt ? k::Unary::Sqrt
+                              : nd.op == Op::Gelu ? k::Unary::Gelu : k::Unary::Copy;
+                uint32_t a = in[0];
+                emit(nd.op == Op::Gelu ? "gelu" : "unary", nd, in, {at}, [=](cudaStream_t s) { k::unary(s, op, plan->f(a), plan->f(at), count); });
+                break;
+            }
+            case Op::ReluGrad:
+            case Op::GeluGrad: {
+                bool gelu = nd.op == Op::GeluGrad;
+                uint32_t a = in[0], g = in[1];
+                emit(gelu ? "gelu_grad" : "relu_grad", nd, in, {at}, [=](cudaStream_t s) {
+                    if (gelu) k::gelu_grad(s, plan->f(a), plan->f(g), plan->f(at), count);
+                    else k::relu_grad(s, plan->f(a), plan->f(g), plan->f(at), count);
+                });
+                break;
+            }
+            case Op::BroadcastScalar: {
+                uint32_t a = in[0];
+                emit("fill", nd, in, {at}, [=](cudaStream_t s) { k::fill_from_scalar(s, plan->f(a), plan->f(at), count); });
+                break;
+            }
+            case Op::MatMul: {
+                uint32_t a = in[0], b = in[1];
+                uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(a);
+                Launch& l = emit("matmul", nd, in, {at}, [=](cudaStream_t s) {
+                    k::matmul(s, plan->f(a), plan->transposed(a), plan->f(b), plan->transposed(b), plan->f(at), m, n, kk);
+                });
+                l.flop = 2 * m * n * kk;
+                break;
+            }
+            case Op::Transpose: {
+                auto absorbed = absorbed_matmul.find(at);
+                if (absorbed != absorbed_matmul.end()) {
+                    // (A x B)^T = B^T x A^T: the same products summed over the same ascending k.
+                    const Node& mm = node(absorbed->second);
+                    uint32_t a = pos(mm.operands[0]), b = pos(mm.operands[1]);
+                    uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(a);
+                    Launch& l = emit("matmul", nd, {b, a}, {at}, [=](cudaStream_t s) {
+                        k::matmul(s, plan->f(b), !plan->transposed(b), plan->f(a), !plan->transposed(a), plan->f(at), m, n, kk);
+                    });
+                    l.flop = 2 * m * n * kk;
+                } else {
+                    uint32_t a = in[0];
+                    uint64_t r = rows_of(a), c = cols_of(a);
+                    if (P->slots[a].kind == Slot::View) unsupported(nd, "a transpose of a folded transpose that is not a matmul operand");
+                    emit("transpose", nd, in, {at}, [=](cudaStream_t s) { k::transpose(s, plan->f(a), plan->f(at), r, c); });
+                }
+                break;
+            }
+            case Op::ReduceSum:
+            case Op::ReduceMean: {
+                uint32_t a = in[0], tmp = scratch(k::reduce_scratch_doubles() * 8);
+                bool mean = nd.op == Op::ReduceMean;
+                uint64_t n = node(a).ty.count();
+                emit("reduce", nd, in, {at, tmp}, [=](cudaStream_t s) {
+                    k::reduce_sum(s, plan->f(a), n, mean, static_cast<double*>(plan->ptr(tmp)), plan->f(at));
+                });
+                break;
+            }
+            case Op::Mse: {
+                uint32_t a = in[0], b = in[1], tmp = scratch(k::reduce_scratch_doubles() * 8);
+                uint64_t n = node(a).ty.count();
+                emit("mse", nd, in, {at, tmp}, [=](cudaStream_t s) {
+                    k::mse(s, plan->f(a), plan->f(b), n, static_cast<double*>(plan->ptr(tmp)), plan->f(at));
+                });
+                break;
+            }
+            case Op::Embedding: {
+                uint32_t table = in[0], ids = in[1];
+                uint64_t n = rows_of(ids), rows = rows_of(table), h = cols_of(table);
+                emit("embedding", nd, in, {at}, [=](cudaStream_t s) {
+                    k::embedding(s, plan->f(table), plan->i(ids), plan->f(at), n, rows, h, plan->d_status);
+                });
+                break;
+            }
+            case Op::EmbeddingGrad: {
+                uint32_t ids = in[0], g = in[1];
+                uint64_t n = rows_of(ids), rows = nd.rows, h = cols_of(g);
+                uint32_t tmp = scratch(k::embedding_grad_scratch_ints(n, rows) * 4);
+                emit("embedding_grad", nd, in, {at, tmp}, [=](cudaStream_t s) {
+                    k::embedding_grad(s, plan->i(ids), plan->f(g), plan->f(at), n, rows, h, plan->i(tmp), plan->d_status);
+                });
+                break;
+            }
+            case Op::AddRows: {
+                uint32_t x = in[0], b = in[1];
+                uint64_t r = rows_of(x), h = cols_of(x);
+                emit("add_rows", nd, in, {at}, [=](cudaStream_t s) { k::add_rows(s, plan->f(x), plan->f(b), plan->f(at), r, h); });
+                break;
+            }
+            case Op::SumRows: {
+                uint32_t g = in[0];
+                uint64_t r = rows_of(g), h = cols_of(g);
+                uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4);
+                emit("sum_rows", nd, in, {at, tmp}, [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), plan->f(at)); });
+                break;
+            }
+            case Op::LayerNorm: {
+                uint32_t x = in[0], gamma = in[1], beta = in[2];
+                uint64_t r = rows_of(x), h = cols_of(x);
+                emit("layer_norm", nd, in, {at}, [=](cudaStream_t s) {
+                    k::layer_norm(s, plan->f(x), plan->f(gamma), plan->f(beta), plan->f(at), r, h);
+                });
+                break;
+            }
+            case Op::LayerNormGradX: {
+                uint32_t x = in[0], gamma = in[1], g = in[2];
+                uint64_t r = rows_of(x), h = cols_of(x);
+                emit("layer_norm_grad_x", nd, in, {at}, [=](cudaStream_t s) {
+                    k::layer_norm_grad_x(s, plan->f(x), plan->f(gamma), plan->f(g), plan->f(at), r, h);
+                });
+                break;
+            }
+            case Op::LayerNormGradGamma: {
+                uint32_t x = in[0], g = in[1];
+                uint64_t r = rows_of(x), h = cols_of(x);
+                // The beta gradient is the SumRows of the same adjoint: one pass gives both.
+                int beta = -1;
+                for (uint32_t u : users[g])
+                    if (u > at && node(u).op == Op::SumRows && !handled[u]) { beta = static_cast<int>(u); break; }
+                std::vector<uint32_t> writes = {at};
+                if (beta >= 0) {
+                    handled[static_cast<size_t>(beta)] = 1;
+                    Slot& b = P->slots[static_cast<size_t>(beta)];
+                    b.kind = Slot::Arena;
+                    b.bytes = h * 4;
+                    writes.push_back(static_cast<uint32_t>(beta));
+                }
+                uint32_t tmp = scratch(k::layer_norm_grad_gamma_scratch_floats(r, h) * 4);
+                writes.push_back(tmp);
+                emit("layer_norm_grad_gamma", nd, in, writes, [=](cudaStream_t s) {
+                    k::layer_norm_grad_gamma(s, plan->f(x), plan->f(g), plan->f(tmp), plan->f(at),
+                                             beta >= 0 ? plan->f(static_cast<uint32_t>(beta)) : nullptr, r, h);
+                });
+                break;
+            }
+            case Op::Softmax: {
+                uint32_t x = in[0];
+                uint64_t r = rows_of(x), c = cols_of(x);
+                emit("softmax", nd, in, {at}, [=](cudaStream_t s) { k::softmax(s, plan->f(x), plan->f(at), r, c); });
+                break;
+            }
+            case Op::SoftmaxGrad: {
+                uint32_t y = in[0], g = in[1];
+                uint64_t r = rows_of(y), c = cols_of(y);
+                emit("softmax_grad", nd, in, {at}, [=](cudaStream_t s) { k::softmax_grad(s, plan->f(y), plan->f(g), plan->f(at), r, c); });
+                break;
+            }
+            case Op::Attention:
+            case Op::AttentionGradQ:
+            case Op::AttentionGradK:
+            case Op::AttentionGradV: schedule_attention(at); break;
+            case Op::CrossEntropy: {
+                uint32_t logits = in[0], labels = in[1], weights = in[2];
+                uint64_t r = rows_of(logits), v = cols_of(logits);
+                uint32_t row_loss = scratch(std::max<uint64_t>(r, 1) * 4);
+                emit("cross_entropy", nd, in, {at, row_loss}, [=](cudaStream_t s) {
+                    k::cross_entropy(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(row_loss), nullptr, plan->f(at), r, v);
+                });
+                break;
+            }
+            case Op::CrossEntropyGrad: {
+                uint32_t logits = in[0], labels = in[1], weights = in[2], g = in[3];
+                uint64_t r = rows_of(logits), v = cols_of(logits);
+                uint32_t den = scratch(4);
+                emit("cross_entropy_grad", nd, in, {at, den}, [=](cudaStream_t s) {
+                    k::cross_entropy_grad(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(g), nullptr, plan->f(den),
+                                          plan->f(at), r, v);
+                });
+                break;
+            }
+            case Op::Dropout:
+            case Op::DropoutGrad: {
+                uint32_t x = nd.op == Op::Dropout ? in[0] : in[1], token = nd.op == Op::Dropout ? in[1] : in[0];
+                if (nd.ty.count() > (1ull << 32)) unsupported(nd, "a dropout draw addresses at most 2^32 elements");
+                uint32_t threshold = static_cast<uint32_t>(msx::dropout_keep_threshold(nd.p));
+                float scale = 1.0f / (1.0f - nd.p);
+                uint64_t row_width = nd.ty.rank() > 0 && nd.ty.shape[0] > 0 ? count / nd.ty.shape[0] : 1;
+                emit("dropout", nd, in, {at}, [=](cudaStream_t s) {
+                    k::dropout(s, plan->f(x), plan->i(token), plan->seed, threshold, scale, plan->shard_rows_before * row_width,
+                               plan->f(at), count);
+                });
+                break;
+            }
+            default: unsupported(nd, "no kernel is written for it");
+        }
+    }
+
+    void schedule_attention(uint32_t at) {
+        const Node& nd = node(at);
+        msx_plan* plan = P;
+        uint32_t q = pos(nd.operands[0]), kk = pos(nd.operands[1]), v = pos(nd.operands[2]), mask = pos(nd.operands[3]);
+        const msx::Type& qt = node(q).ty;
+        const msx::Type& mt = node(mask).ty;
+        k::AttentionShape shape;
+        shape.batch = static_cast<uint32_t>(mt.shape[0]);
+        shape.k_len = static_cast<uint32_t>(mt.shape[1]);
+        shape.q_len = static_cast<uint32_t>(qt.shape[0] / mt.shape[0]);
+        shape.heads = static_cast<uint32_t>(nd.heads);
+        shape.head_dim = static_cast<uint32_t>(qt.shape[1] / nd.heads);
+        if (shape.k_len > 512) unsupported(nd, "more than 512 keys per sequence");
+        if (shape.head_dim > 128) unsupported(nd, "a head wider than 128");
+        if (nd.op == Op::Attention) {
+            Launch& l = emit("attention_forward", nd, {q, kk, v, mask}, {at}, [=](cudaStream_t s) {
+                k::attention_forward(s, plan->f(q), plan->f(kk), plan->f(v), plan->f(mask), plan->f(at), shape);
+            });
+            l.flop = 4ull * shape.batch * shape.q_len * shape.k_len * shape.heads * shape.head_dim;
+            return;
+        }
+        // The gradient ops of one attention read the same five operands: one statistics pass
+        // (inside grad-q) serves all three.
+        uint32_t g = pos(nd.operands[4]);
+        int dq = -1, dk = -1, dv = -1;
+        for (uint32_t u : users[g]) {
+            const Node& other = node(u);
+            if (handled[u] && u != at) continue;
+            if (other.op != Op::AttentionGradQ && other.op != Op::AttentionGradK && other.op != Op::AttentionGradV) continue;
+            if (other.operands != nd.operands || other.heads != nd.heads) continue;
+            int& target = other.op == Op::AttentionGradQ ? dq : other.op == Op::AttentionGradK ? dk : dv;
+            if (target < 0) target = static_cast<int>(u);
+        }
+        for (int t : {dq, dk, dv})
+            if (t >= 0) {
+                handled[static_cast<size_t>(t)] = 1;
+                Slot& s = P->slots[static_cast<size_t>(t)];
+                s.kind = Slot::Arena;
+                s.bytes = node(static_cast<uint32_t>(t)).ty.count() * 4;
+            }
+        uint32_t stats = scratch(k::attention_stats_floats(shape) * 4);
+        std::vector<uint32_t> reads = {q, kk, v, mask, g};
+        uint64_t pair_flop = 2ull * shape.batch * shape.q_len * shape.k_len * shape.heads * shape.head_dim;
+        {
+            std::vector<uint32_t> writes = {stats};
+            if (dq >= 0) writes.push_back(static_cast<uint32_t>(dq));
+            Launch& l = emit("attention_grad_q", nd, reads, writes, [=](cudaStream_t s) {
+                k::attention_grad_q(s, plan->f(q), plan->f(kk), plan->f(v), plan->f(mask), plan->f(g), plan->f(stats),
+                                    dq >= 0 ? plan->f(static_cast<uint32_t>(dq)) : nullptr, shape);
+            });
+            l.flop = pair_flop * (dq >= 0 ? 3 : 2);
+        }
+        if (dk >= 0 || dv >= 0) {
+            std::vector<uint32_t> kv_reads = reads, writes;
+            kv_reads.push_back(stats);
+            if (dk >= 0) writes.push_back(static_cast<uint32_t>(dk));
+            if (dv >= 0) writes.push_back(static_cast<uint32_t>(dv));
+            Launch& l = emit("attention_grad_kv", nd, kv_reads, writes, [=](cudaStream_t s) {
+                k::attention_grad_kv(s, plan->f(q), plan->f(kk), plan->f(v), plan->f(mask), plan->f(g), plan->f(stats),
+                                     dk >= 0 ? plan->f(static_cast<uint32_t>(dk)) : nullptr,
+                                     dv >= 0 ? plan->f(static_cast<uint32_t>(dv)) : nullptr, shape);
+            });
+            l.flop = pair_flop * 4;
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Arena placement by liveness: launches run in order on one stream, so a value's storage is free
+// after the last launch that reads it.
+
+struct FreeList {
+    std::vector<std::pair<uint64_t, uint64_t>> blocks;  // (offset, size), sorted by offset
+    uint64_t end = 0;
+
+    uint64_t take(uint64_t bytes) {
+        bytes = align_up(bytes);
+        for (size_t b = 0; b < blocks.size(); ++b)
+            if (blocks[b].second >= bytes) {
+                uint64_t at = blocks[b].first;
+                blocks[b].first += bytes;
+                blocks[b].second -= bytes;
+                if (blocks[b].second == 0) blocks.erase(blocks.begin() + static_cast<long>(b));
+                return at;
+            }
+        // Grow: extend a free block that touches the end, else append.
+        if (!blocks.empty() && blocks.back().first + blocks.back().second == end) {
+            uint64_t at = blocks.back().first;
+            end = at + bytes;
+            blocks.pop_back();
+            return at;
+        }
+        uint64_t at = end;
+        end += bytes;
+        return at;
+    }
+    void give(uint64_t offset, uint64_t bytes) {
+        bytes = align_up(bytes);
+        auto it = std::lower_bound(blocks.begin(), blocks.end(), std::make_pair(offset, uint64_t{0}));
+        it = blocks.insert(it, {offset, bytes});
+        if (it + 1 != blocks.end() && it->first + it->second == (it + 1)->first) {
+            it->second += (it + 1)->second;
+            blocks.erase(it + 1);
+        }
+        if (it != blocks.begin() && (it - 1)->first + (it - 1)->second == it->first) {
+            (it - 1)->second += it->second;
+            blocks.erase(it);
+        }
+    }
+};
+
+void place_arena(msx_plan* P) {
+    std::vector<Slot>& slots = P->slots;
+    for (size_t l = 0; l < P->launches.size(); ++l) {
+        const Launch& launch = P->launches[l];
+        for (uint32_t w : launch.writes)
+            if (slots[w].kind == Slot::Arena) {
+                if (slots[w].first < 0) slots[w].first = static_cast<int>(l);
+                slots[w].last = std::max(slots[w].last, static_cast<int>(l));
+            }
+        for (uint32_t r : launch.reads)
+            if (slots[r].kind == Slot::Arena) {
+                if (slots[r].first < 0)
+                    throw StatusError(MSX_UNSUPPORTED, "scheduling bug: launch " + std::to_string(l) + " (" + launch.kernel +
+                                                           ") reads a value no earlier launch wrote");
+                slots[r].last = std::max(slots[r].last, static_cast<int>(l));
+            }
+    }
+    std::vector<std::vector<uint32_t>> starts(P->launches.size()), ends(P->launches.size());
+    for (uint32_t s = 0; s < slots.size(); ++s)
+        if (slots[s].kind == Slot::Arena && slots[s].first >= 0) {
+            starts[static_cast<size_t>(slots[s].first)].push_back(s);
+            if (!slots[s].keep) ends[static_cast<size_t>(slots[s].last)].push_back(s);
+            P->unshared_bytes += align_up(slots[s].bytes);
+        }
+    FreeList free;
+    for (size_t l = 0; l < P->launches.size(); ++l) {
+        for (uint32_t s : starts[l]) slots[s].offset = free.take(slots[s].bytes);
+        for (uint32_t s : ends[l]) free.give(slots[s].offset, slots[s].bytes);
+    }
+    P->arena_bytes = std::max<uint64_t>(free.end, kAlign);
+}
+
+void allocate(msx_plan* P, const Scheduler& sched) {
+    const Program& prog = P->program;
+    cuda_ok(cudaStreamCreateWithFlags(&P->stream, cudaStreamNonBlocking), "cudaStreamCreate");
+    cuda_ok(cudaMalloc(&P->arena, P->arena_bytes), "cudaMalloc(arena)");
+    std::vector<char> param_used(prog.params.size(), 0), moment_used(prog.params.size(), 0);
+    for (const Slot& s : P->slots) {
+        if (s.kind == Slot::Param) param_used[s.index] = 1;
+        if (s.kind == Slot::Moment) moment_used[s.index] = 1;
+    }
+    for (size_t p = 0; p < prog.params.size(); ++p) {
+        uint64_t bytes = std::max<uint64_t>(prog.params[p].ty.count() * 4, 4);
+        if (param_used[p]) {
+            float* shared = nullptr;
+            if (P->shares) {
+                int at = P->shares->program.param_index(prog.params[p].path);
+                if (at >= 0 && P->shares->program.params[static_cast<size_t>(at)].ty == prog.params[p].ty)
+                    shared = P->shares->params[static_cast<size_t>(at)];
+            }
+            if (shared) {
+                P->params[p] = shared;
+            } else {
+                cuda_ok(cudaMalloc(&P->params[p], bytes), "cudaMalloc(parameter)");
+                cuda_ok(cudaMemset(P->params[p], 0, bytes), "cudaMemset(parameter)");
+                P->owns_param[p] = 1;
+                P->param_bytes += bytes;
+            }
+        }
+        if (moment_used[p]) {
+            cuda_ok(cudaMalloc(&P->m[p], bytes), "cudaMalloc(moment)");
+            cuda_ok(cudaMalloc(&P->v[p], bytes), "cudaMalloc(moment)");
+            cuda_ok(cudaMemset(P->m[p], 0, bytes), "cudaMemset(moment)");
+            cuda_ok(cudaMemset(P->v[p], 0, bytes), "cudaMemset(moment)");
+            P->param_bytes += 2 * bytes;
+        }
+    }
+    uint64_t in_bytes = std::max<uint64_t>(P->input_bytes, kAlign);
+    cuda_ok(cudaMalloc(&P->d_inputs, in_bytes), "cudaMalloc(inputs)");
+    cuda_ok(cudaMemset(P->d_inputs, 0, in_bytes), "cudaMemset(inputs)");
+    P->blob.assign(in_bytes, 0);
+    for (int s = 0; s < kStagingSlots; ++s) {
+        cuda_ok(cudaMallocHost(&P->pinned[s], in_bytes), "cudaMallocHost(staging)");
+        cuda_ok(cudaEventCreateWithFlags(&P->slot_done[s], cudaEventDisableTiming), "cudaEventCreate");
+    }
+    cuda_ok(cudaMallocHost(&P->pinned_loss, kStagingSlots * sizeof(float)), "cudaMallocHost(loss)");
+    cuda_ok(cudaMallocHost(&P->pinned_status, sizeof(uint32_t)), "cudaMallocHost(status)");
+    *P->pinned_status = 0;
+    uint64_t const_bytes = std::max<uint64_t>(P->consts.size() * 4, 4);
+    cuda_ok(cudaMalloc(&P->d_consts, const_bytes), "cudaMalloc(constants)");
+    if (!P->consts.empty())
+        cuda_ok(cudaMemcpy(P->d_consts, P->consts.data(), P->consts.size() * 4, cudaMemcpyHostToDevice), "cudaMemcpy(constants)");
+    cuda_ok(cudaMalloc(&P->d_status, 4), "cudaMalloc(status)");
+    cuda_ok(cudaMemset(P->d_status, 0, 4), "cudaMemset(status)");
+    cuda_ok(cudaEventCreate(&P->clock_start), "cudaEventCreate");
+    cuda_ok(cudaEventCreate(&P->clock_stop), "cudaEventCreate");
+    if (!sched.updates.empty()) {
+        std::vector<k::UpdateTensor> tensors;
+        for (const Scheduler::Update& u : sched.updates) {
+            k::UpdateTensor t;
+            t.p = P->params[u.param];
+            t.g = static_cast<const float*>(P->ptr(u.grad_pos));
+            t.m = P->m[u.param];
+            t.v = P->v[u.param];
+            t.count = prog.params[u.param].ty.count();
+            tensors.push_back(t);
+        }
+        size_t table_bytes = tensors.size() * sizeof(k::UpdateTensor);
+        size_t chunk_bytes = sched.update_chunk_tensor.size() * 4;
+        cuda_ok(cudaMalloc(&P->d_update_tables, table_bytes + 2 * chunk_bytes), "cudaMalloc(update tables)");
+        char* base = static_cast<char*>(P->d_update_tables);
+        cuda_ok(cudaMemcpy(base, tensors.data(), table_bytes, cudaMemcpyHostToDevice), "cudaMemcpy(update tables)");
+        cuda_ok(cudaMemcpy(base + table_bytes, sched.update_chunk_tensor.data(), chunk_bytes, cudaMemcpyHostToDevice), "cudaMemcpy");
+        cuda_ok(cudaMemcpy(base + table_bytes + chunk_bytes, sched.update_chunk_start.data(), chunk_bytes, cudaMemcpyHostToDevice), "cudaMemcpy");
+    }
+}
+
+void release(msx_plan* P) {
+    if (!P) return;
+    cudaSetDevice(P->device->ordinal);
+    if (P->stream) cudaStreamSynchronize(P->stream);
+    if (P->graph) cudaGraphExecDestroy(P->graph);
+    cudaFree(P->arena);
+    for (size_t p = 0; p < P->params.size(); ++p) {
+        if (P->owns_param[p]) cudaFree(P->params[p]);
+        cudaFree(P->m[p]);
+        cudaFree(P->v[p]);
+    }
+    cudaFree(P->d_inputs);
+    cudaFree(P->d_consts);
+    cudaFree(P->d_status);
+    cudaFree(P->d_update_tables);
+    for (int s = 0; s < kStagingSlots; ++s) {
+        if (P->pinned[s]) cudaFreeHost(P->pinned[s]);
+        if (P->slot_done[s]) cudaEventDestroy(P->slot_done[s]);
+    }
+    if (P->pinned_loss) cudaFreeHost(P->pinned_loss);
+    if (P->pinned_status) cudaFreeHost(P->pinned_status);
+    if (P->clock_start) cudaEventDestroy(P->clock_start);
+    if (P->clock_stop) cudaEventDestroy(P->clock_stop);
+    if (P->stream) cudaStreamDestroy(P->stream);
+    delete P;
+}
+
+void enqueue_all(msx_plan* P) {
+    for (const Launch& l : P->launches) l.run(P->stream);
+}
+
+// Waits for `event` at most `timeout_ms`, polling: never an unbounded wait.
+int wait_event(cudaEvent_t event, uint32_t timeout_ms) {
+    auto start = std::chrono::steady_clock::now();
+    for (;;) {
+        cudaError_t e = cudaEventQuery(event);
+        if (e == cudaSuccess) return MSX_OK;
+        if (e != cudaErrorNotReady) cuda_ok(e, "cudaEventQuery");
+        auto waited = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - start).count();
+        if (timeout_ms != 0 && waited >= static_cast<long long>(timeout_ms)) return MSX_TIMEOUT;
+        if (waited > 2) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
+int wait_all(msx_plan* P, uint32_t timeout_ms) {
+    if (P->steps == 0) {
+        cuda_ok(cudaStreamSynchronize(P->stream), "cudaStreamSynchronize");
+        return MSX_OK;
+    }
+    int slot = static_cast<int>((P->steps - 1) % kStagingSlots);
+    int rc = wait_event(P->slot_done[slot], timeout_ms == 0 ? 600000u : timeout_ms);
+    if (rc != MSX_OK) return rc;
+    if (*P->pinned_status & 1u) {
+        *P->pinned_status = 0;
+        cuda_ok(cudaMemsetAsync(P->d_status, 0, 4, P->stream), "cudaMemsetAsync");
+        throw StatusError(MSX_BAD_INPUT, "an embedding id computed on the device is outside its table");
+    }
+    return MSX_OK;
+}
+
+template <class F> int guarded(msx_device* device, F body) {
+    try {
+        return body();
+    } catch (const StatusError& e) {
+        if (device) device->error = e.what();
+        else g_open_error = e.what();
+        return e.status;
+    } catch (const k::CudaError& e) {
+        if (device) device->error = e.what();
+        else g_open_error = e.what();
+        return e.code == cudaErrorMemoryAllocation ? MSX_OUT_OF_MEMORY : MSX_LAUNCH_FAILED;
+    } catch (const std::exception& e) {
+        if (device) device->error = e.what();
+        else g_open_error = e.what();
+        return MSX_UNSUPPORTED;
+    }
+}
+
+int check_input(const HostInput& in, const void* host, std::string* why) {
+    const uint64_t n = in.bytes / 4;
+    for (const InputCheck& c : in.checks) {
+        if (c.kind == InputCheck::Ids || c.kind == InputCheck::Labels) {
+            const int32_t* v = static_cast<const int32_t*>(host);
+            for (uint64_t e = 0; e < n; ++e)
+                if (v[e] < 0 || static_cast<uint64_t>(v[e]) >= c.bound) {
+                    *why = "`" + in.name + "`[" + std::to_string(e) + "] = " + std::to_string(v[e]) + " is outside [0, " +
+                           std::to_string(c.bound) + ")";
+                    return MSX_BAD_INPUT;
+                }
+        } else if (c.kind == InputCheck::Weights) {
+            const float* v = static_cast<const float*>(host);
+            for (uint64_t e = 0; e < n; ++e)
+                if (!(v[e] * 0.0f == 0.0f) || v[e] < 0.0f) {
+                    *why = "`" + in.name + "`[" + std::to_string(e) + "] is negative or not finite";
+                    return MSX_BAD_INPUT;
+                }
+        } else {
+            const float* v = static_cast<const float*>(host);
+            for (uint64_t seq = 0; seq * c.bound < n; ++seq) {
+                bool any = false;
+                for (uint64_t j = 0; j < c.bound; ++j) {
+                    float mk = v[seq * c.bound + j];
+                    if (mk != 0.0f && mk != 1.0f) {
+                        *why = "`" + in.name + "`: sequence " + std::to_string(seq) + " key " + std::to_string(j) + " is neither 0 nor 1";
+                        return MSX_BAD_INPUT;
+                    }
+                    any = any || mk == 1.0f;
+                }
+                if (!any) {
+                    *why = "`" + in.name + "`: sequence " + std::to_string(seq) + " has no unmasked key";
+                    return MSX_BAD_INPUT;
+                }
+            }
+        }
+    }
+    return MSX_OK;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+
+extern "C" {
+
+int msx_open(int ordinal, msx_device** out) {
+    return guarded(nullptr, [&]() -> int {
+        if (!out) throw StatusError(MSX_BAD_ARGUMENT, "msx_open: null output");
+        *out = nullptr;
+        int count = 0;
+        cudaError_t e = cudaGetDeviceCount(&count);
+        if (e != cudaSuccess || count == 0) throw StatusError(MSX_NO_DEVICE, std::string("no CUDA device: ") + cudaGetErrorString(e));
+        if (ordinal < 0 || ordinal >= count)
+            throw StatusError(MSX_NO_DEVICE, "no CUDA device " + std::to_string(ordinal) + " (" + std::to_string(count) + " present)");
+        cudaDeviceProp prop;
+        cuda_ok(cudaGetDeviceProperties(&prop, ordinal), "cudaGetDeviceProperties");
+        if (prop.major != 10)
+            throw StatusError(MSX_NO_DEVICE, std::string("device ") + prop.name + " is sm_" + std::to_string(prop.major * 10 + prop.minor) +
+                                                 "; the kernels are built for sm_100a only");
+        cuda_ok(cudaSetDevice(ordinal), "cudaSetDevice");
+        msx_device* d = new msx_device;
+        d->ordinal = ordinal;
+        *out = d;
+        return MSX_OK;
+    });
+}
+
+void msx_close(msx_device* device) { delete device; }
+
+const char* msx_last_error(const msx_device* device) { return device ? device->error.c_str() : g_open_error.c_str(); }
+
+// For the host loop above this file, which reports its own failures through the device handle.
+void msx_internal_set_error(msx_device* device, const char* message) {
+    if (device) device->error = message ? message : "";
+    else g_open_error = message ? message : "";
+}
+
+int msx_plan_create(msx_device* device, const char* ir_text, uint64_t seed, uint32_t flags, msx_plan* shares,
+                    msx_plan** out) {
+    if (!device || !ir_text || !out) return MSX_BAD_ARGUMENT;
+    *out = nullptr;
+    msx_plan* P = new msx_plan;
+    int rc = guarded(device, [&]() -> int {
+        cuda_ok(cudaSetDevice(device->ordinal), "cudaSetDevice");
+        P->device = device;
+        P->seed = seed;
+        P->flags = flags;
+        P->shares = shares;
+        try {
+            P->program = msx::parse_program(ir_text);
+        } catch (const msx::Error& e) {
+            throw StatusError(MSX_UNSUPPORTED, e.what());
+        }
+        if (P->program.outputs.empty()) throw StatusError(MSX_UNSUPPORTED, "the program has no output");
+        Scheduler sched(P);
+        sched.run();
+        place_arena(P);
+        allocate(P, sched);
+        return MSX_OK;
+    });
+    if (rc != MSX_OK) {
+        std::string keep = device->error;
+        release(P);
+        device->error = keep;
+        return rc;
+    }
+    *out = P;
+    return MSX_OK;
+}
+
+void msx_plan_destroy(msx_plan* plan) { release(plan); }
+
+uint32_t msx_plan_input_count(const msx_plan* plan) { return plan ? static_cast<uint32_t>(plan->inputs.size()) : 0; }
+const char* msx_plan_input_name(const msx_plan* plan, uint32_t index) {
+    return plan && index < plan->inputs.size() ? plan->inputs[index].name.c_str() : nullptr;
+}
+uint64_t msx_plan_input_bytes(const msx_plan* plan, uint32_t index) {
+    return plan && index < plan->inputs.size() ? plan->inputs[index].bytes : 0;
+}
+int msx_plan_input_is_i32(const msx_plan* plan, uint32_t index) {
+    return plan && index < plan->inputs.size() && plan->inputs[index].i32 ? 1 : 0;
+}
+uint32_t msx_plan_param_count(const msx_plan* plan) { return plan ? static_cast<uint32_t>(plan->program.params.size()) : 0; }
+const char* msx_plan_param_path(const msx_plan* plan, uint32_t index) {
+    return plan && index < plan->program.params.size() ? plan->program.params[index].path.c_str() : nullptr;
+}
+uint64_t msx_plan_param_bytes(const msx_plan* plan, uint32_t index) {
+    return plan && index < plan->program.params.size() ? plan->program.params[index].ty.count() * 4 : 0;
+}
+
+static int transfer(msx_plan* plan, float* device_ptr, uint64_t expect, void* host, uint64_t bytes, bool upload, const char* what) {
+    if (!plan || !host) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        if (!device_ptr) throw StatusError(MSX_BAD_ARGUMENT, std::string(what) + ": the plan holds no such buffer");
+        if (bytes != expect)
+            throw StatusError(MSX_BAD_ARGUMENT, std::string(what) + ": " + std::to_string(bytes) + " bytes given, " + std::to_string(expect) + " expected");
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        if (upload) cuda_ok(cudaMemcpyAsync(device_ptr, host, bytes, cudaMemcpyHostToDevice, plan->stream), what);
+        else cuda_ok(cudaMemcpyAsync(host, device_ptr, bytes, cudaMemcpyDeviceToHost, plan->stream), what);
+        cuda_ok(cudaStreamSynchronize(plan->stream), what);
+        return MSX_OK;
+    });
+}
+
+int msx_param_upload(msx_plan* plan, uint32_t index, const void* host, uint64_t bytes) {
+    if (!plan || index >= plan->program.params.size()) return MSX_BAD_ARGUMENT;
+    return transfer(plan, plan->params[index], msx_plan_param_bytes(plan, index), const_cast<void*>(host), bytes, true, "msx_param_upload");
+}
+int msx_param_download(msx_plan* plan, uint32_t index, void* host, uint64_t bytes) {
+    if (!plan || index >= plan->program.params.size()) return MSX_BAD_ARGUMENT;
+    return transfer(plan, plan->params[index], msx_plan_param_bytes(plan, index), host, bytes, false, "msx_param_download");
+}
+int msx_moment_upload(msx_plan* plan, uint32_t index, char which, const void* host, uint64_t bytes) {
+    if (!plan || index >= plan->program.params.size() || (which != 'm' && which != 'v')) return MSX_BAD_ARGUMENT;
+    return transfer(plan, (which == 'm' ? plan->m : plan->v)[index], msx_plan_param_bytes(plan, index), const_cast<void*>(host), bytes, true,
+                    "msx_moment_upload");
+}
+int msx_moment_download(msx_plan* plan, uint32_t index, char which, void* host, uint64_t bytes) {
+    if (!plan || index >= plan->program.params.size() || (which != 'm' && which != 'v')) return MSX_BAD_ARGUMENT;
+    return transfer(plan, (which == 'm' ? plan->m : plan->v)[index], msx_plan_param_bytes(plan, index), host, bytes, false,
+                    "msx_moment_download");
+}
+
+int msx_set_input(msx_plan* plan, const char* name, const void* host, uint64_t bytes) {
+    if (!plan || !name || !host) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        for (const HostInput& in : plan->inputs) {
+            if (in.name != name) continue;
+            if (bytes != in.bytes)
+                throw StatusError(MSX_BAD_ARGUMENT, "msx_set_input: `" + in.name + "` takes " + std::to_string(in.bytes) + " bytes, " +
+                                                        std::to_string(bytes) + " given");
+            std::string why;
+            int rc = check_input(in, host, &why);
+            if (rc != MSX_OK) throw StatusError(rc, why);
+            std::memcpy(plan->blob.data() + in.offset, host, bytes);
+            plan->blob_dirty = true;
+            return MSX_OK;
+        }
+        throw StatusError(MSX_BAD_ARGUMENT, std::string("msx_set_input: the step reads no input `") + name + "`");
+    });
+}
+
+int msx_set_shard(msx_plan* plan, uint64_t rows_before, uint64_t global_rows) {
+    if (!plan) return MSX_BAD_ARGUMENT;
+    (void)global_rows;
+    return guarded(plan->device, [&]() -> int {
+        if (plan->shard_rows_before != rows_before && plan->graph) {
+            cuda_ok(cudaStreamSynchronize(plan->stream), "cudaStreamSynchronize");
+            cuda_ok(cudaGraphExecDestroy(plan->graph), "cudaGraphExecDestroy");
+            plan->graph = nullptr;
+        }
+        plan->shard_rows_before = rows_before;
+        return MSX_OK;
+    });
+}
+
+int msx_run(msx_plan* plan) {
+    if (!plan) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        int slot = static_cast<int>(plan->steps % kStagingSlots);
+        if (plan->slot_used[slot]) {
+            int rc = wait_event(plan->slot_done[slot], 600000u);
+            if (rc != MSX_OK) throw StatusError(rc, "msx_run: a step submitted " + std::to_string(kStagingSlots) + " steps ago has not finished");
+        }
+        if (plan->clock_steps == 0) cuda_ok(cudaEventRecord(plan->clock_start, plan->stream), "cudaEventRecord");
+        if (plan->input_bytes && plan->blob_dirty) {
+            plan->blob_dirty = false;
+            std::memcpy(plan->pinned[slot], plan->blob.data(), plan->input_bytes);
+            cuda_ok(cudaMemcpyAsync(plan->d_inputs, plan->pinned[slot], plan->input_bytes, cudaMemcpyHostToDevice, plan->stream),
+                    "cudaMemcpyAsync(inputs)");
+        }
+        if (plan->flags & MSX_PLAN_NO_GRAPH) {
+            enqueue_all(plan);
+        } else {
+            if (!plan->graph) {
+                cudaGraph_t graph = nullptr;
+                cuda_ok(cudaStreamBeginCapture(plan->stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+                try {
+                    enqueue_all(plan);
+                } catch (...) {
+                    cudaStreamEndCapture(plan->stream, &graph);
+                    if (graph) cudaGraphDestroy(graph);
+                    throw;
+                }
+                cuda_ok(cudaStreamEndCapture(plan->stream, &graph), "cudaStreamEndCapture");
+                cudaError_t e = cudaGraphInstantiate(&plan->graph, graph, 0);
+                cudaGraphDestroy(graph);
+                cuda_ok(e, "cudaGraphInstantiate");
+            }
+            cuda_ok(cudaGraphLaunch(plan->graph, plan->stream), "cudaGraphLaunch");
+        }
+        if (plan->loss_pos >= 0)
+            cuda_ok(cudaMemcpyAsync(plan->pinned_loss + slot, plan->ptr(static_cast<uint32_t>(plan->loss_pos)), 4, cudaMemcpyDeviceToHost,
+                                    plan->stream),
+                    "cudaMemcpyAsync(loss)");
+        cuda_ok(cudaMemcpyAsync(plan->pinned_status, plan->d_status, 4, cudaMemcpyDeviceToHost, plan->stream), "cudaMemcpyAsync(status)");
+        cuda_ok(cudaEventRecord(plan->clock_stop, plan->stream), "cudaEventRecord");
+        cuda_ok(cudaEventRecord(plan->slot_done[slot], plan->stream), "cudaEventRecord");
+        plan->slot_used[slot] = true;
+        ++plan->steps;
+        ++plan->clock_steps;
+        return MSX_OK;
+    });
+}
+
+int msx_sync(msx_plan* plan, uint32_t timeout_ms) {
+    if (!plan) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int { return wait_all(plan, timeout_ms); });
+}
+
+int msx_loss(msx_plan* plan, float* loss, uint32_t timeout_ms) {
+    if (!plan || !loss) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        if (plan->steps == 0) throw StatusError(MSX_BAD_ARGUMENT, "msx_loss: no step has run");
+        if (plan->loss_pos < 0) throw StatusError(MSX_BAD_ARGUMENT, "msx_loss: the program has no rank-0 loss");
+        int rc = wait_all(plan, timeout_ms);
+        if (rc != MSX_OK) return rc;
+        *loss = plan->pinned_loss[(plan->steps - 1) % kStagingSlots];
+        return MSX_OK;
+    });
+}
+
+int msx_loss_of(msx_plan* plan, uint64_t step_number, float* loss, uint32_t timeout_ms) {
+    if (!plan || !loss) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        if (step_number >= plan->steps || step_number + kStagingSlots < plan->steps)
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_loss_of: only the last " + std::to_string(kStagingSlots) + " submitted steps keep their loss");
+        if (plan->loss_pos < 0) throw StatusError(MSX_BAD_ARGUMENT, "msx_loss_of: the program has no rank-0 loss");
+        int slot = static_cast<int>(step_number % kStagingSlots);
+        int rc = wait_event(plan->slot_done[slot], timeout_ms == 0 ? 600000u : timeout_ms);
+        if (rc != MSX_OK) return rc;
+        *loss = plan->pinned_loss[slot];
+        return MSX_OK;
+    });
+}
+
+uint64_t msx_steps_submitted(const msx_plan* plan) { return plan ? plan->steps : 0; }
+
+int msx_profile_step(msx_plan* plan, float* launch_ms, uint32_t capacity) {
+    if (!plan || !launch_ms) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        if (capacity < plan->launches.size()) throw StatusError(MSX_BAD_ARGUMENT, "msx_profile_step: room for every launch is needed");
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        int rc = wait_all(plan, 0);
+        if (rc != MSX_OK) return rc;
+        std::vector<cudaEvent_t> events(plan->launches.size() + 1);
+        for (cudaEvent_t& e : events) cuda_ok(cudaEventCreate(&e), "cudaEventCreate");
+        if (plan->input_bytes) {
+            std::memcpy(plan->pinned[0], plan->blob.data(), plan->input_bytes);
+            cuda_ok(cudaMemcpyAsync(plan->d_inputs, plan->pinned[0], plan->input_bytes, cudaMemcpyHostToDevice, plan->stream), "cudaMemcpyAsync");
+        }
+        cuda_ok(cudaEventRecord(events[0], plan->stream), "cudaEventRecord");
+        for (size_t l = 0; l < plan->launches.size(); ++l) {
+            plan->launches[l].run(plan->stream);
+            cuda_ok(cudaEventRecord(events[l + 1], plan->stream), "cudaEventRecord");
+        }
+        cuda_ok(cudaStreamSynchronize(plan->stream), "cudaStreamSynchronize");
+        for (size_t l = 0; l < plan->launches.size(); ++l)
+            cuda_ok(cudaEventElapsedTime(&launch_ms[l], events[l], events[l + 1]), "cudaEventElapsedTime");
+        for (cudaEvent_t e : events) cudaEventDestroy(e);
+        return MSX_OK;
+    });
+}
+
+uint64_t msx_launch_bytes(const msx_plan* plan, uint32_t launch) {
+    if (!plan || launch >= plan->launches.size()) return 0;
+    const Launch& l = plan->launches[launch];
+    uint64_t bytes = 0;
+    for (uint32_t r : l.reads) bytes += plan->slots[r].bytes;
+    for (uint32_t w : l.writes) bytes += plan->slots[w].bytes;
+    if (l.kernel == "adamw_multi_tensor") bytes += l.flop / 16 * 24;
+    if (l.kernel == "sgd_multi_tensor") bytes += l.flop / 2 * 8;
+    return bytes;
+}
+
+uint64_t msx_launch_flop(const msx_plan* plan, uint32_t launch) {
+    return plan && launch < plan->launches.size() ? plan->launches[launch].flop : 0;
+}
+
+const char* msx_launch_kernel(const msx_plan* plan, uint32_t launch) {
+    return plan && launch < plan->launches.size() ? plan->launches[launch].kernel.c_str() : nullptr;
+}
+
+int msx_value_download(msx_plan* plan, uint32_t value_id, void* host, uint64_t bytes) {
+    if (!plan || !host) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        int at = plan->program.position(value_id);
+        if (at < 0) throw StatusError(MSX_BAD_ARGUMENT, "msx_value_download: %" + std::to_string(value_id) + " is not defined");
+        const Slot& s = plan->slots[static_cast<size_t>(at)];
+        bool readable = s.keep || s.kind == Slot::Param || s.kind == Slot::Moment || s.kind == Slot::Input || s.kind == Slot::Const;
+        if (!readable || s.kind == Slot::Dead || s.kind == Slot::View)
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_value_download: %" + std::to_string(value_id) + " is not an output; its storage is reused");
+        uint64_t expect = plan->program.nodes[static_cast<size_t>(at)].ty.count() * 4;
+        if (bytes != expect) throw StatusError(MSX_BAD_ARGUMENT, "msx_value_download: " + std::to_string(expect) + " bytes expected");
+        int rc = wait_all(plan, 0);
+        if (rc != MSX_OK) return rc;
+        cuda_ok(cudaMemcpyAsync(host, plan->ptr(static_cast<uint32_t>(at)), bytes, cudaMemcpyDeviceToHost, plan->stream), "cudaMemcpyAsync");
+        cuda_ok(cudaStreamSynchronize(plan->stream), "cudaStreamSynchronize");
+        return MSX_OK;
+    });
+}
+
+int msx_plan_stats(const msx_plan* plan, msx_stats* out) {
+    if (!plan || !out) return MSX_BAD_ARGUMENT;
+    std::memset(out, 0, sizeof *out);
+    out->launches_per_step = plan->launches.size();
+    out->nodes = plan->program.nodes.size();
+    out->live_nodes = plan->live_nodes;
+    out->arena_bytes = plan->arena_bytes;
+    out->unshared_bytes = plan->unshared_bytes;
+    out->param_bytes = plan->param_bytes;
+    out->upload_bytes_per_step = plan->input_bytes;
+    out->steps_run = plan->steps;
+    for (const Launch& l : plan->launches) {
+        for (uint32_t r : l.reads) out->algorithmic_bytes_per_step += plan->slots[r].bytes;
+        for (uint32_t w : l.writes) out->algorithmic_bytes_per_step += plan->slots[w].bytes;
+        if (l.kernel == "matmul") out->matmul_flop_per_step += l.flop;
+        if (l.kernel == "adamw_multi_tensor") out->algorithmic_bytes_per_step += l.flop / 16 * 24;  // p, m, v read and written
+        if (l.kernel == "sgd_multi_tensor") out->algorithmic_bytes_per_step += l.flop / 2 * 8;
+    }
+    return MSX_OK;
+}
+
+uint64_t msx_plan_describe(const msx_plan* plan, char* out, uint64_t capacity) {
+    if (!plan) return 0;
+    std::string text;
+    auto name = [&](uint32_t slot) {
+        if (slot < plan->program.nodes.size()) return "%" + std::to_string(plan->program.nodes[slot].id);
+        return "scratch" + std::to_string(slot - plan->program.nodes.size());
+    };
+    for (size_t l = 0; l < plan->launches.size(); ++l) {
+        const Launch& launch = plan->launches[l];
+        text += std::to_string(l) + ": " + launch.kernel + " %" + std::to_string(launch.value) + " reads";
+        for (uint32_t r : launch.reads) text += " " + name(r);
+        text += " writes";
+        for (uint32_t w : launch.writes) text += " " + name(w);
+        if (launch.flop) text += " flop " + std::to_string(launch.flop);
+        text += "\n";
+    }
+    if (out && capacity) {
+        size_t n = std::min<size_t>(capacity - 1, text.size());
+        std::memcpy(out, text.data(), n);
+        out[n] = 0;
+    }
+    return text.size() + 1;
+}
+
+int msx_elapsed_ms(msx_plan* plan, double* total_ms, uint64_t* steps) {
+    if (!plan || !total_ms || !steps) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        *total_ms = 0.0;
+        *steps = plan->clock_steps;
+        if (plan->clock_steps == 0) return MSX_OK;
+        int rc = wait_all(plan, 0);
+        if (rc != MSX_OK) return rc;
+        cuda_ok(cudaEventSynchronize(plan->clock_stop), "cudaEventSynchronize");
+        float ms = 0.0f;
+        cuda_ok(cudaEventElapsedTime(&ms, plan->clock_start, plan->clock_stop), "cudaEventElapsedTime");
+        *total_ms = ms;
+        plan->clock_steps = 0;
+        return MSX_OK;
+    });
+}
+
+uint64_t msx_schedule_describe(const char* ir_text, char* out, uint64_t capacity) {
+    if (!ir_text) return 0;
+    msx_plan* P = new msx_plan;
+    std::string text;
+    int rc = guarded(nullptr, [&]() -> int {
+        try {
+            P->program = msx::parse_program(ir_text);
+        } catch (const msx::Error& e) {
+            throw StatusError(MSX_UNSUPPORTED, e.what());
+        }
+        if (P->program.outputs.empty()) throw StatusError(MSX_UNSUPPORTED, "the program has no output");
+        Scheduler sched(P);
+        sched.run();
+        place_arena(P);
+        uint64_t need = msx_plan_describe(P, nullptr, 0);
+        text.resize(need);
+        msx_plan_describe(P, &text[0], need);
+        text.resize(need - 1);
+        text += "arena " + std::to_string(P->arena_bytes) + " bytes, unshared " + std::to_string(P->unshared_bytes) +
+                " bytes, inputs " + std::to_string(P->input_bytes) + " bytes, launches " + std::to_string(P->launches.size()) + "\n";
+        return MSX_OK;
+    });
+    delete P;
+    if (rc != MSX_OK) return 0;
+    if (out && capacity) {
+        size_t n = std::min<size_t>(capacity - 1, text.size());
+        std::memcpy(out, text.data(), n);
+        out[n] = 0;
+    }
+    return text.size() + 1;
+}
+
+int msx_comm_unique_id(void* unique_id_128) {
+    (void)unique_id_128;
+    g_open_error = "data-parallel communication is not built into this library";
+    return MSX_UNSUPPORTED;
+}
+
+int msx_comm_init(msx_plan* plan, int rank, int world, const void* unique_id_128) {
+    (void)rank; (void)world; (void)unique_id_128;
+    if (!plan) return MSX_BAD_ARGUMENT;
+    plan->device->error = "data-parallel communication is not built into this library";
+    return MSX_UNSUPPORTED;
+}
+
+uint64_t msx_compile(const char* source, const char* which, uint64_t masked_rows, char* out, uint64_t capacity) {
+    if (!source || !which) return 0;
+    std::string text;
+    try {
+        msx::Compiled c = msx::compile_training(source, masked_rows);
+        std::string w = which;
+        if (w == "step") text = msx::print_program(c.step);
+        else if (w == "forward") text = msx::print_program(c.forward);
+        else if (w == "tensor") text = msx::print_program(c.forward_with_dropout);
+        else throw msx::Error("msx_compile: `which` is step, forward or tensor");
+    } catch (const std::exception& e) {
+        g_open_error = e.what();
+        return 0;
+    }
+    if (out && capacity) {
+        size_t n = std::min<size_t>(capacity - 1, text.size());
+        std::memcpy(out, text.data(), n);
+        out[n] = 0;
+    }
+    return text.size() + 1;
+}
+
+}  // extern "C"

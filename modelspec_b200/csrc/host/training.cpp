@@ -1,0 +1,330 @@
+// The host loop of a training run, written against the msx C ABI alone (no CUDA call here): the
+// counterpart of the reference's device runner vulkan::stepwise::train_stepwise_on_device
+// (crates/modelspec-runtime/src/vulkan/stepwise.rs:289-296, :400-) and of the CPU loop
+// train::runner::run_checked (crates/modelspec-runtime/src/train/runner.rs:365-512).
+//
+// Per step the host supplies what the reference's host supplies (stepwise.rs:475-543): the AdamW
+// scalars of t = step + 1, the dropout token of every site at this step, the masked-row gather of
+// the batch, and the batch itself. Parameters start from their initializers on Philox stream 0.
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <set>
+
+#include "../../../include/msx.h"
+#include "../core/frontend.hpp"
+#include "../core/init.hpp"
+
+// Defined beside msx_last_error: records a message on the device handle.
+extern "C" void msx_internal_set_error(msx_device* device, const char* message);
+
+struct msx_training {
+    msx_device* device = nullptr;
+    msx::Compiled compiled;
+    msx_plan* step = nullptr;
+    msx_plan* forward = nullptr;
+    std::string error;
+    std::map<std::string, std::vector<char>> batch;  // declared inputs and targets, by name
+    std::vector<std::string> sites;                  // dropout token inputs of the step
+    std::set<std::string> step_inputs, forward_inputs;
+    bool submitted = false;
+    std::map<uint64_t, uint64_t> submitted_as;  // run step -> submission number on the step plan
+};
+
+namespace {
+
+struct Fail {
+    int status;
+    std::string what;
+};
+
+void ok(msx_training* t, int rc) {
+    if (rc != MSX_OK) throw Fail{rc, msx_last_error(t->device)};
+}
+
+template <class F> int guarded(msx_training* t, F body) {
+    try {
+        body();
+        return MSX_OK;
+    } catch (const Fail& f) {
+        t->error = f.what;
+        return f.status;
+    } catch (const std::exception& e) {
+        t->error = e.what();
+        return MSX_UNSUPPORTED;
+    }
+}
+
+std::set<std::string> input_names(const msx_plan* plan) {
+    std::set<std::string> out;
+    for (uint32_t i = 0; i < msx_plan_input_count(plan); ++i) out.insert(msx_plan_input_name(plan, i));
+    return out;
+}
+
+const msx::DataDecl* declared(const msx_training* t, const std::string& name) {
+    for (const msx::DataDecl& d : t->compiled.config.data)
+        if (d.name == name) return &d;
+    return nullptr;
+}
+
+// The host side of the masked-row gather (crates/modelspec-runtime/src/train/masked.rs:88-128):
+// the rows of non-zero weight in ascending order with their labels and weights, then padding
+// rows of row 0, label 0 and weight +0.0; more selected rows than the capacity is refused.
+void gather_masked(msx_training* t, uint64_t step, bool stage) {
+    const msx::Compiled& c = t->compiled;
+    if (!c.masked_rows) return;
+    auto w = t->batch.find(c.masked_weights), l = t->batch.find(c.masked_labels);
+    if (w == t->batch.end() || l == t->batch.end())
+        throw Fail{MSX_BAD_INPUT, "E-DATA-012: the batch of step " + std::to_string(step) + " holds no `" +
+                                      (w == t->batch.end() ? c.masked_weights : c.masked_labels) + "` to gather the masked rows from"};
+    const float* weights = reinterpret_cast<const float*>(w->second.data());
+    const int32_t* labels = reinterpret_cast<const int32_t*>(l->second.data());
+    size_t rows = w->second.size() / 4, capacity = c.masked_rows;
+    std::vector<int32_t> ids, lab;
+    std::vector<float> wt;
+    for (size_t r = 0; r < rows; ++r)
+        if (weights[r] != 0.0f) {
+            ids.push_back(static_cast<int32_t>(r));
+            lab.push_back(r < l->second.size() / 4 ? labels[r] : 0);
+            wt.push_back(weights[r]);
+        }
+    if (ids.size() > capacity)
+        throw Fail{MSX_BAD_INPUT, "E-DATA-012: the batch of step " + std::to_string(step) + " has " + std::to_string(ids.size()) +
+                                      " rows of non-zero `" + c.masked_weights + "`, more than the " + std::to_string(capacity) +
+                                      " rows the masked-row gather holds"};
+    if (!stage) return;
+    ids.resize(capacity, 0);
+    lab.resize(capacity, 0);
+    wt.resize(capacity, 0.0f);
+    ok(t, msx_set_input(t->step, "masked.rows", ids.data(), capacity * 4));
+    ok(t, msx_set_input(t->step, ("masked.labels." + c.masked_labels).c_str(), lab.data(), capacity * 4));
+    ok(t, msx_set_input(t->step, ("masked.weights." + c.masked_weights).c_str(), wt.data(), capacity * 4));
+}
+
+void stage_batch(msx_training* t, msx_plan* plan, const std::set<std::string>& reads) {
+    for (const auto& [name, bytes] : t->batch)
+        if (reads.count(name)) ok(t, msx_set_input(plan, name.c_str(), bytes.data(), bytes.size()));
+}
+
+}  // namespace
+
+extern "C" {
+
+int msx_training_create(msx_device* device, const char* source, uint64_t masked_rows, uint32_t flags,
+                        msx_training** out) {
+    if (!device || !source || !out) return MSX_BAD_ARGUMENT;
+    *out = nullptr;
+    msx_training* t = new msx_training;
+    t->device = device;
+    int rc = guarded(t, [&] {
+        try {
+            t->compiled = msx::compile_training(source, masked_rows);
+        } catch (const msx::Error& e) {
+            throw Fail{MSX_UNSUPPORTED, e.what()};
+        }
+        const msx::Compiled& c = t->compiled;
+        if (c.config.rule == msx::Rule::AdamW && c.config.steps > 0 && c.config.adamw.warmup_steps >= c.config.steps)
+            throw Fail{MSX_BAD_ARGUMENT, "warmup_steps " + std::to_string(c.config.adamw.warmup_steps) +
+                                             " is not below the run's " + std::to_string(c.config.steps) + " steps"};
+        std::string step_ir = msx::print_program(c.step), forward_ir = msx::print_program(c.forward);
+        ok(t, msx_plan_create(device, step_ir.c_str(), c.config.seed, flags, nullptr, &t->step));
+        ok(t, msx_plan_create(device, forward_ir.c_str(), c.config.seed, flags, t->step, &t->forward));
+        t->step_inputs = input_names(t->step);
+        t->forward_inputs = input_names(t->forward);
+        for (const std::string& name : t->step_inputs)
+            if (name.find(".dropout#") != std::string::npos) t->sites.push_back(name);
+        // A parameter the step does not hold (the loss does not reach it) lives in the forward
+        // plan alone; both are initialised.
+        for (uint32_t p = 0; p < c.step.params.size(); ++p) {
+            std::vector<float> value = msx::initial_parameter(c.step.params[p], c.config.seed, msx::kStreamInit);
+            int rs = msx_param_upload(t->step, p, value.data(), value.size() * 4);
+            int rf = msx_param_upload(t->forward, p, value.data(), value.size() * 4);
+            if (rs != MSX_OK && rf != MSX_OK) throw Fail{rs, msx_last_error(device)};
+        }
+    });
+    if (rc != MSX_OK) {
+        std::string why = t->error;
+        msx_training_destroy(t);
+        msx_internal_set_error(device, why.c_str());  // where msx_last_error(device) finds it
+        return rc;
+    }
+    *out = t;
+    return MSX_OK;
+}
+
+void msx_training_destroy(msx_training* t) {
+    if (!t) return;
+    if (t->forward) msx_plan_destroy(t->forward);
+    if (t->step) msx_plan_destroy(t->step);
+    delete t;
+}
+
+msx_plan* msx_training_step_plan(msx_training* t) { return t ? t->step : nullptr; }
+msx_plan* msx_training_forward_plan(msx_training* t) { return t ? t->forward : nullptr; }
+uint64_t msx_training_steps(const msx_training* t) { return t ? t->compiled.config.steps : 0; }
+uint64_t msx_training_seed(const msx_training* t) { return t ? t->compiled.config.seed : 0; }
+const char* msx_training_last_error(const msx_training* t) { return t ? t->error.c_str() : ""; }
+
+int msx_training_set_input(msx_training* t, const char* name, const void* host, uint64_t bytes) {
+    if (!t || !name || !host) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::DataDecl* d = declared(t, name);
+        if (!d) throw Fail{MSX_BAD_ARGUMENT, std::string("the train block declares no `") + name + "`"};
+        if (bytes != d->ty.count() * 4)
+            throw Fail{MSX_BAD_ARGUMENT, std::string("`") + name + "` is " + d->ty.str() + ": " + std::to_string(d->ty.count() * 4) + " bytes"};
+        const char* b = static_cast<const char*>(host);
+        t->batch[name].assign(b, b + bytes);
+    });
+}
+
+int msx_training_get_input(msx_training* t, const char* name, void* host, uint64_t bytes) {
+    if (!t || !name || !host) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        auto it = t->batch.find(name);
+        if (it == t->batch.end() || it->second.size() != bytes) throw Fail{MSX_BAD_ARGUMENT, std::string("no batch input `") + name + "` of that size"};
+        std::memcpy(host, it->second.data(), bytes);
+    });
+}
+
+int msx_training_synthetic(msx_training* t) {
+    if (!t) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        const msx::Program& fwd = c.forward;
+        // Key masks: f32 inputs read only as the fourth operand of attention (data.rs:214-245).
+        std::set<std::string> masks;
+        for (uint32_t in : fwd.inputs) {
+            const msx::Node& n = fwd.node(in);
+            if (n.ty.i32) continue;
+            bool any = false, only = true;
+            for (const msx::Node& user : fwd.nodes)
+                for (size_t k = 0; k < user.operands.size(); ++k)
+                    if (user.operands[k] == in) {
+                        any = true;
+                        only = only && user.op == msx::Op::Attention && k == 3;
+                    }
+            if (any && only) masks.insert(n.name);
+        }
+        const msx::DataDecl *input = nullptr, *target = nullptr;
+        int inputs = 0, targets = 0;
+        for (const msx::DataDecl& d : c.config.data) {
+            if (masks.count(d.name)) continue;
+            if (d.target) { target = &d; ++targets; }
+            else { input = &d; ++inputs; }
+        }
+        if (inputs != 1 || targets != 1)
+            throw Fail{MSX_BAD_INPUT, "E-DATA-001: M0 synthetic data takes one input besides key masks and one target"};
+        if (input->ty.i32 || target->ty.i32) throw Fail{MSX_BAD_INPUT, "E-DATA-004: M0 synthetic data cannot draw an i32 tensor"};
+        if (target->ty != fwd.node(c.prediction).ty) throw Fail{MSX_BAD_INPUT, "E-DATA-002: the target has not the type of the prediction"};
+        std::vector<float> x = msx::standard_normal_draw(c.config.seed, msx::kStreamData, input->name, input->ty.count());
+        t->batch[input->name].assign(reinterpret_cast<char*>(x.data()), reinterpret_cast<char*>(x.data()) + x.size() * 4);
+        for (const msx::DataDecl& d : c.config.data)
+            if (masks.count(d.name)) {
+                std::vector<float> ones(d.ty.count(), 1.0f);
+                t->batch[d.name].assign(reinterpret_cast<char*>(ones.data()), reinterpret_cast<char*>(ones.data()) + ones.size() * 4);
+            }
+        // The teacher: the forward program up to the prediction, its own parameters drawn on the
+        // teacher stream.
+        msx::Program predict = fwd;
+        predict.outputs = {msx::Output{c.prediction, msx::Role::Plain, 0, 0}};
+        predict = msx::dce(std::move(predict));
+        std::string ir = msx::print_program(predict);
+        msx_plan* teacher = nullptr;
+        ok(t, msx_plan_create(t->device, ir.c_str(), c.config.seed, MSX_PLAN_NO_GRAPH, nullptr, &teacher));
+        try {
+            for (uint32_t p = 0; p < predict.params.size(); ++p) {
+                std::vector<float> value = msx::initial_parameter(predict.params[p], c.config.seed, msx::kStreamTeacher);
+                int rc = msx_param_upload(teacher, p, value.data(), value.size() * 4);
+                (void)rc;  // a parameter the prediction does not read has no buffer
+            }
+            stage_batch(t, teacher, input_names(teacher));
+            ok(t, msx_run(teacher));
+            std::vector<char> y(target->ty.count() * 4);
+            ok(t, msx_value_download(teacher, c.prediction, y.data(), y.size()));
+            t->batch[target->name] = std::move(y);
+        } catch (...) {
+            msx_plan_destroy(teacher);
+            throw;
+        }
+        msx_plan_destroy(teacher);
+    });
+}
+
+int msx_training_step(msx_training* t, uint64_t step, uint64_t end) {
+    if (!t) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        if (c.config.rule == msx::Rule::AdamW) {
+            msx::StepScalars s = msx::adamw_scalars(c.config.adamw, c.config.lr, step + 1, end);
+            if (t->step_inputs.count("optimizer.lr_t")) {
+                ok(t, msx_set_input(t->step, "optimizer.lr_t", &s.lr_t, 4));
+                ok(t, msx_set_input(t->step, "optimizer.c1", &s.c1, 4));
+                ok(t, msx_set_input(t->step, "optimizer.c2", &s.c2, 4));
+            }
+        }
+        stage_batch(t, t->step, t->step_inputs);
+        gather_masked(t, step, true);
+        for (const std::string& site : t->sites) {
+            int32_t token[2];
+            msx::dropout_token(site, step, token);
+            ok(t, msx_set_input(t->step, site.c_str(), token, 8));
+        }
+        t->submitted_as[step] = msx_steps_submitted(t->step);
+        if (t->submitted_as.size() > 64) t->submitted_as.erase(t->submitted_as.begin());
+        ok(t, msx_run(t->step));
+        t->submitted = true;
+    });
+}
+
+int msx_training_loss_of(msx_training* t, uint64_t step, float* loss) {
+    if (!t || !loss) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        auto it = t->submitted_as.find(step);
+        if (it == t->submitted_as.end()) throw Fail{MSX_BAD_ARGUMENT, "step " + std::to_string(step) + " was not submitted recently"};
+        ok(t, msx_loss_of(t->step, it->second, loss, 0));
+        if (!std::isfinite(*loss)) throw Fail{MSX_NON_FINITE, "E-TRAIN-001: the loss of step " + std::to_string(step) + " is not finite"};
+    });
+}
+
+int msx_training_loss(msx_training* t, float* loss) {
+    if (!t || !loss) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        ok(t, msx_loss(t->step, loss, 0));
+        if (!std::isfinite(*loss)) throw Fail{MSX_NON_FINITE, "E-TRAIN-001: the loss is not finite"};
+    });
+}
+
+int msx_training_final_loss(msx_training* t, float* loss) {
+    if (!t || !loss) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        // The forward plan runs on its own stream: wait for the submitted updates first.
+        ok(t, msx_sync(t->step, 0));
+        // The final batch is held to the gather as every trained batch is (runner.rs:467-471).
+        gather_masked(t, t->compiled.config.steps, false);
+        stage_batch(t, t->forward, t->forward_inputs);
+        ok(t, msx_run(t->forward));
+        ok(t, msx_loss(t->forward, loss, 0));
+    });
+}
+
+int msx_training_check_finite(msx_training* t) {
+    if (!t) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Program& p = t->compiled.step;
+        std::vector<float> host;
+        for (uint32_t i = 0; i < p.params.size(); ++i) {
+            host.resize(p.params[i].ty.count());
+            for (int which = 0; which < 3; ++which) {
+                int rc = which == 0 ? msx_param_download(t->step, i, host.data(), host.size() * 4)
+                                    : msx_moment_download(t->step, i, which == 1 ? 'm' : 'v', host.data(), host.size() * 4);
+                if (rc != MSX_OK) continue;  // the step holds no such buffer
+                for (float x : host)
+                    if (!std::isfinite(x))
+                        throw Fail{MSX_NON_FINITE, std::string("E-TRAIN-001: ") + (which == 0 ? "parameter" : which == 1 ? "moment m of" : "moment v of") +
+                                                       " `" + p.params[i].path + "` is not finite"};
+            }
+        }
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,102 @@
+"""The `.mspec` front door, autodiff and optimizer attachment against the reference's printed
+IR, and the scheduler's launch list. No GPU."""
+import os
+
+import pytest
+
+import modelspec_b200 as M
+from modelspec_b200 import models
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def golden(name):
+    return open(os.path.join(GOLDEN, name)).read()
+
+
+def test_linear_regression_ir_is_the_reference_text():
+    assert M.compile_mspec(models.linear_regression(), "tensor") == golden("linear_regression.tensor.ir")
+    assert M.compile_mspec(models.linear_regression(), "step") == golden("linear_regression.training.ir")
+
+
+def test_mnist_mlp_training_ir_is_the_reference_text():
+    """Autodiff order, subgraph tags, folded constants and SGD effects of a two-layer relu net."""
+    assert M.compile_mspec(models.mnist_mlp(), "step") == golden("mnist_mlp.training.ir")
+
+
+def test_bert_tiny_lowers_to_the_documented_program():
+    """All 104 nodes of the reference's BERT-tiny example at vocabulary 8,192, dropout sites and
+    tied decoder included (website/docs/examples/bert-tiny.md of the reference)."""
+    source = models.bert(vocab=8192, warmup_steps=1000, steps=10000)
+    assert M.compile_mspec(source, "tensor") == golden("bert_tiny.tensor.ir")
+
+
+def test_adamw_step_has_the_documented_shape():
+    text = M.compile_mspec(models.bert(hidden=32, heads=2, ffn=64, vocab=300, seq=16, batch=2), "step")
+    lines = text.splitlines()
+    assert ("optimizer adamw lr = 0.0001 weight_decay = 0.01 beta1 = 0.9 beta2 = 0.999 eps = 1e-6 warmup_steps = 10") in lines
+    for name in ("lr_t", "c1", "c2"):
+        assert any(': Tensor<f32, []> = Input "optimizer.%s"' % name in l for l in lines)
+    assert any('= Input "optimizer.m@BertTiny.tok_table" {' in l and " read m@BertTiny.tok_table v0}" in l for l in lines)
+    assert sum(l.startswith("output ") and " moment " in l for l in lines) == 2 * 41
+    ops = [l.split(" = ")[1].split()[0] for l in lines if l.startswith("optimizer %")]
+    per_param = ["Input", "Input", "Mul", "Mul", "Add", "Mul", "Mul", "Mul", "Add", "Mul", "Mul", "Sqrt", "Add", "Div",
+                 "Mul", "Add", "Mul", "Sub"]
+    assert ops[9:9 + len(per_param)] == per_param
+
+
+def test_the_masked_row_gather_reads_the_frontier_through_an_embedding():
+    text = M.compile_mspec(models.bert(), "step", masked_rows=832)
+    assert 'Tensor<i32, [832]> = Input "masked.rows"' in text
+    assert 'Input "masked.labels.labels"' in text and 'Input "masked.weights.weights"' in text
+    assert "Tensor<f32, [832, 30522]> = CrossEntropyGrad" in text
+    assert "EmbeddingGrad [4096]" in text
+    assert M.compile_mspec(models.bert(), "step", masked_rows=4096) == M.compile_mspec(models.bert(), "step")
+    assert models.default_masked_rows(4096) == 832
+
+
+def test_the_forward_program_has_no_dropout_and_no_gather():
+    text = M.compile_mspec(models.bert(), "forward", masked_rows=832)
+    assert "Dropout" not in text and "masked." not in text and "dropout#" not in text
+
+
+def test_a_step_is_read_back_from_its_own_text():
+    import oracle_lib
+    text = M.compile_mspec(models.bert(hidden=32, heads=2, ffn=64, vocab=300, seq=16, batch=2), "step", 8)
+    # The oracle parses and reprints through the same reader the backend uses.
+    t = oracle_lib.Trainer(models.bert(hidden=32, heads=2, ffn=64, vocab=300, seq=16, batch=2), 8)
+    assert t.ir("step") == text
+
+
+def test_bad_source_is_refused_with_a_message():
+    with pytest.raises(M.MsxError) as err:
+        M.compile_mspec("model M { param w: Tensor<f32, [2]> = xavier_uniform(); }")
+    assert "rank 2" in str(err.value)
+    with pytest.raises(M.MsxError) as err:
+        M.compile_mspec(models.linear_regression().replace("matmul(x, w)", "sigreg(x, slices = 2)"))
+    assert "sigreg" in str(err.value)
+
+
+def test_bert_tiny_step_schedule():
+    """What the backend launches for BERT-tiny with the gather: the ungathered head is not run,
+    every transpose is folded into a matmul, the three attention gradients share a launch pair,
+    and the 41 AdamW updates are one launch."""
+    listing = M.schedule_describe(M.compile_mspec(models.bert(), "step", masked_rows=832))
+    kernels = [l.split()[1] for l in listing.strip().splitlines()[:-1]]
+    assert kernels.count("adamw_multi_tensor") == 1 and kernels[-1] == "adamw_multi_tensor"
+    assert "transpose" not in kernels
+    assert kernels.count("attention_forward") == 2 and kernels.count("attention_grad_q") == 2 and kernels.count("attention_grad_kv") == 2
+    assert kernels.count("matmul") == 42
+    assert "[4096, 30522]" not in listing
+    assert len(kernels) < 140
+    totals = listing.strip().splitlines()[-1]
+    arena, unshared = int(totals.split()[1]), int(totals.split()[4])
+    assert arena < unshared
+
+
+def test_unschedulable_programs_are_refused():
+    with pytest.raises(M.MsxError) as err:
+        M.schedule_describe('%0: Tensor<f32, [4, 3]> = Input "p"\n%1: Tensor<f32, [3]> = SigregColumns %0\noutput %1\n')
+    assert "SigregColumns" in str(err.value)
+    with pytest.raises(M.MsxError):
+        M.schedule_describe("optimizer muon lr = 0.1 momentum = 0.9\n")

@@ -1,0 +1,307 @@
+"""Op-level parity on the GPU: each Tensor IR op as a one-node program through the C ABI,
+against the CPU oracle on the same seeded inputs. Integer-addressed work (gathers, ordered
+scatter-adds, dropout masks) and single-rounding arithmetic must match in bits; reductions and
+transcendental ops within the reference's kernel tolerance 1e-5 + 1e-4 r."""
+import numpy as np
+import pytest
+
+import modelspec_b200 as M
+from helpers import ProgramText, assert_bits_equal, assert_kernel_close, run_both
+
+pytestmark = pytest.mark.gpu
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+def values(r, *shape):
+    """Seeded f32 values with a signed zero every 7th element, as the reference's device tests
+    draw them (tests/common/mod.rs:124-161)."""
+    x = r.standard_normal(shape).astype(np.float32)
+    flat = x.reshape(-1)
+    flat[::7] = 0.0
+    flat[::14] = -0.0
+    return x
+
+
+@pytest.mark.parametrize("m,k,n", [(8, 4, 1), (64, 784, 128), (100, 37, 10), (130, 129, 67), (1, 1, 1), (5, 300, 3)])
+@pytest.mark.parametrize("form", ["nn", "tn", "nt"])
+def test_matmul_is_the_ascending_k_fma_chain_bit_for_bit(device, m, k, n, form):
+    r = rng(m * 1000 + k * 10 + n)
+    p = ProgramText()
+    if form == "nn":
+        a = p.input("a", "f32", [m, k]); b = p.input("b", "f32", [k, n])
+        out = p.op("MatMul", [m, n], [a, b])
+        feed = {"a": values(r, m, k), "b": values(r, k, n)}
+    elif form == "tn":  # X^T x G: the weight gradient
+        a = p.input("a", "f32", [k, m]); b = p.input("b", "f32", [k, n])
+        at = p.op("Transpose", [m, k], [a])
+        out = p.op("MatMul", [m, n], [at, b])
+        feed = {"a": values(r, k, m), "b": values(r, k, n)}
+    else:  # G x W^T: the input adjoint
+        a = p.input("a", "f32", [m, k]); b = p.input("b", "f32", [n, k])
+        bt = p.op("Transpose", [k, n], [b])
+        out = p.op("MatMul", [m, n], [a, bt])
+        feed = {"a": values(r, m, k), "b": values(r, n, k)}
+    p.output(out)
+    [(cpu, gpu)] = run_both(device, p.text(), feed, outputs=[(out, m * n)])
+    assert_bits_equal(gpu, cpu, "matmul %s %dx%dx%d" % (form, m, k, n))
+
+
+def test_transposed_matmul_result_is_the_swapped_matmul(device):
+    """Transpose(MatMul(A^T, G)) is scheduled as one matmul with its operands swapped."""
+    r = rng(5)
+    p = ProgramText()
+    a = p.input("a", "f32", [50, 12]); g = p.input("g", "f32", [50, 33])
+    at = p.op("Transpose", [12, 50], [a])
+    mm = p.op("MatMul", [12, 33], [at, g])
+    out = p.op("Transpose", [33, 12], [mm])
+    p.output(out)
+    text = p.text()
+    assert "transpose" not in M.schedule_describe(text)
+    [(cpu, gpu)] = run_both(device, text, {"a": values(r, 50, 12), "g": values(r, 50, 33)}, outputs=[(out, 33 * 12)])
+    assert_bits_equal(gpu, cpu)
+
+
+@pytest.mark.parametrize("op", ["Add", "Sub", "Mul", "Div"])
+@pytest.mark.parametrize("form", ["same", "scalar_right", "scalar_left"])
+def test_elementwise_ops_round_once_like_the_cpu(device, op, form):
+    r = rng(11)
+    n = 1003
+    p = ProgramText()
+    a = p.input("a", "f32", [] if form == "scalar_left" else [n])
+    b = p.input("b", "f32", [] if form == "scalar_right" else [n])
+    out = p.op(op, [n], [a, b])
+    p.output(out)
+    av = r.standard_normal(1 if form == "scalar_left" else n).astype(np.float32)
+    bv = (r.standard_normal(1 if form == "scalar_right" else n).astype(np.float32) + np.float32(3.0))
+    [(cpu, gpu)] = run_both(device, p.text(), {"a": av, "b": bv}, outputs=[(out, n)])
+    assert_bits_equal(gpu, cpu, op)
+
+
+def test_relu_and_its_gradient_are_exact_and_zero_at_zero(device):
+    r = rng(2)
+    p = ProgramText()
+    a = p.input("a", "f32", [777]); g = p.input("g", "f32", [777])
+    y = p.op("Relu", [777], [a]); d = p.op("ReluGrad", [777], [a, g]); s = p.op("Sqrt", [777], [y])
+    for v in (y, d, s):
+        p.output(v)
+    res = run_both(device, p.text(), {"a": values(r, 777), "g": values(r, 777)}, outputs=[(y, 777), (d, 777), (s, 777)])
+    for cpu, gpu in res:
+        assert_bits_equal(gpu, cpu)
+
+
+def test_gelu_and_its_gradient_within_tolerance(device):
+    r = rng(3)
+    n = 4096
+    p = ProgramText()
+    a = p.input("a", "f32", [n]); g = p.input("g", "f32", [n])
+    y = p.op("Gelu", [n], [a]); d = p.op("GeluGrad", [n], [a, g])
+    p.output(y); p.output(d)
+    x = (r.standard_normal(n) * 3).astype(np.float32)
+    x[:8] = [-20, -10, -3, -0.0, 0.0, 3, 10, 20]
+    res = run_both(device, p.text(), {"a": x, "g": values(r, n)}, outputs=[(y, n), (d, n)])
+    for cpu, gpu in res:
+        assert_kernel_close(gpu, cpu, what="gelu")
+        assert np.abs(gpu - cpu).max() <= 4e-6 * max(1.0, np.abs(cpu).max())
+
+
+def test_add_rows_transpose_and_broadcast_are_exact(device):
+    r = rng(4)
+    p = ProgramText()
+    x = p.input("x", "f32", [37, 130]); b = p.input("b", "f32", [130]); s = p.input("s", "f32", [])
+    y = p.op("AddRows", [37, 130], [x, b]); t = p.op("Transpose", [130, 37], [x])
+    f = p.op("BroadcastScalar", [5, 9], [s], attr="[5, 9]")
+    for v in (y, t, f):
+        p.output(v)
+    res = run_both(device, p.text(), {"x": values(r, 37, 130), "b": values(r, 130), "s": np.float32([2.5])},
+                   outputs=[(y, 37 * 130), (t, 37 * 130), (f, 45)])
+    for cpu, gpu in res:
+        assert_bits_equal(gpu, cpu)
+
+
+@pytest.mark.parametrize("rows,h", [(1, 5), (64, 128), (4096, 128), (833, 30), (300, 513)])
+def test_sum_rows_within_tolerance(device, rows, h):
+    r = rng(rows + h)
+    p = ProgramText()
+    g = p.input("g", "f32", [rows, h])
+    out = p.op("SumRows", [h], [g])
+    p.output(out)
+    gv = values(r, rows, h)
+    [(cpu, gpu)] = run_both(device, p.text(), {"g": gv}, outputs=[(out, h)])
+    assert_kernel_close(gpu, cpu, scale=np.abs(gv).sum(axis=0), what="sum_rows")
+
+
+def test_whole_tensor_sums_round_once_from_f64(device):
+    r = rng(6)
+    n = 70001
+    p = ProgramText()
+    a = p.input("a", "f32", [n]); b = p.input("b", "f32", [n])
+    s = p.op("ReduceSum", [], [a]); m = p.op("ReduceMean", [], [a]); e = p.op("Mse", [], [a, b])
+    for v in (s, m, e):
+        p.output(v)
+    res = run_both(device, p.text(), {"a": values(r, n), "b": values(r, n)}, outputs=[(s, 1), (m, 1), (e, 1)])
+    for cpu, gpu in res:
+        # f64 partial sums in another order: at most the last f32 bit moves.
+        assert abs(float(gpu[0]) - float(cpu[0])) <= 1.2e-7 * abs(float(cpu[0])) + 1e-30
+
+
+def test_embedding_gathers_rows_exactly_and_its_gradient_adds_in_ascending_order(device):
+    r = rng(7)
+    rows, h, n = 50, 24, 400
+    ids = r.integers(0, rows, size=n).astype(np.int32)
+    ids[:40] = 3  # one row hit many times: the order of the adds shows
+    ids[ids == 17] = 18  # a row never read stays exactly zero
+    p = ProgramText()
+    table = p.input("table", "f32", [rows, h]); i = p.input("ids", "i32", [n]); g = p.input("g", "f32", [n, h])
+    e = p.op("Embedding", [n, h], [table, i])
+    d = p.op("EmbeddingGrad", [rows, h], [i, g], attr="[%d]" % rows)
+    p.output(e); p.output(d)
+    res = run_both(device, p.text(), {"table": values(r, rows, h), "ids": ids, "g": values(r, n, h)},
+                   outputs=[(e, n * h), (d, rows * h)])
+    for cpu, gpu in res:
+        assert_bits_equal(gpu, cpu)
+    assert not res[1][1].reshape(rows, h)[17].any()
+
+
+@pytest.mark.parametrize("rows,h", [(4, 8), (37, 128), (512, 768), (65, 33)])
+def test_layer_norm_and_its_gradients(device, rows, h):
+    r = rng(rows * h)
+    p = ProgramText()
+    x = p.input("x", "f32", [rows, h]); gamma = p.input("gamma", "f32", [h]); beta = p.input("beta", "f32", [h])
+    g = p.input("g", "f32", [rows, h])
+    y = p.op("LayerNorm", [rows, h], [x, gamma, beta])
+    dx = p.op("LayerNormGradX", [rows, h], [x, gamma, g])
+    dg = p.op("LayerNormGradGamma", [h], [x, g])
+    db = p.op("SumRows", [h], [g])
+    for v in (y, dx, dg, db):
+        p.output(v)
+    feed = {"x": values(r, rows, h) * 2 + 0.5, "gamma": values(r, h) + 1, "beta": values(r, h), "g": values(r, rows, h)}
+    text = p.text()
+    assert M.schedule_describe(text).count("sum_rows") == 0, "the beta gradient rides with the gamma gradient"
+    res = run_both(device, text, feed, outputs=[(y, rows * h), (dx, rows * h), (dg, h), (db, h)])
+    assert_kernel_close(res[0][1], res[0][0], what="layer_norm")
+    assert_kernel_close(res[1][1], res[1][0], scale=np.abs(res[1][0]).max(), what="layer_norm_grad_x")
+    scale = np.abs(feed["g"]).sum(axis=0) * 3
+    assert_kernel_close(res[2][1], res[2][0], scale=scale, what="layer_norm_grad_gamma")
+    assert_kernel_close(res[3][1], res[3][0], scale=scale, what="beta gradient")
+
+
+def test_softmax_and_its_gradient(device):
+    r = rng(9)
+    rows, k = 19, 301
+    p = ProgramText()
+    x = p.input("x", "f32", [rows, k]); g = p.input("g", "f32", [rows, k])
+    y = p.op("Softmax", [rows, k], [x]); d = p.op("SoftmaxGrad", [rows, k], [y, g])
+    p.output(y); p.output(d)
+    res = run_both(device, p.text(), {"x": values(r, rows, k) * 4, "g": values(r, rows, k)}, outputs=[(y, rows * k), (d, rows * k)])
+    for cpu, gpu in res:
+        assert_kernel_close(gpu, cpu, scale=1.0 / k, what="softmax")
+
+
+@pytest.mark.parametrize("batch,q_len,k_len,heads,d", [(3, 40, 40, 2, 16), (2, 128, 128, 2, 64), (2, 7, 33, 1, 8), (1, 512, 512, 1, 64)])
+def test_attention_and_its_three_gradients(device, batch, q_len, k_len, heads, d):
+    r = rng(batch * q_len + d)
+    h = heads * d
+    p = ProgramText()
+    q = p.input("q", "f32", [batch * q_len, h]); k = p.input("k", "f32", [batch * k_len, h])
+    v = p.input("v", "f32", [batch * k_len, h]); mask = p.input("mask", "f32", [batch, k_len])
+    g = p.input("g", "f32", [batch * q_len, h])
+    attr = "[heads = %d]" % heads
+    out = p.op("Attention", [batch * q_len, h], [q, k, v, mask], attr=attr)
+    dq = p.op("AttentionGradQ", [batch * q_len, h], [q, k, v, mask, g], attr=attr)
+    dk = p.op("AttentionGradK", [batch * k_len, h], [q, k, v, mask, g], attr=attr)
+    dv = p.op("AttentionGradV", [batch * k_len, h], [q, k, v, mask, g], attr=attr)
+    for val in (out, dq, dk, dv):
+        p.output(val)
+    m = np.ones((batch, k_len), dtype=np.float32)
+    m[:, 1::3] = 0.0  # masked keys: exact zero rows in dK and dV
+    m[0, :] = 0.0
+    m[0, k_len - 1] = 1.0  # a sequence with one unmasked key
+    feed = {"q": values(r, batch * q_len, h), "k": values(r, batch * k_len, h), "v": values(r, batch * k_len, h),
+            "mask": m, "g": values(r, batch * q_len, h)}
+    text = p.text()
+    listing = M.schedule_describe(text)
+    assert listing.count("attention_grad_q") == 1 and listing.count("attention_grad_kv") == 1
+    res = run_both(device, text, feed, outputs=[(out, batch * q_len * h), (dq, batch * q_len * h),
+                                                 (dk, batch * k_len * h), (dv, batch * k_len * h)])
+    for (cpu, gpu), name in zip(res, ["attention", "grad_q", "grad_k", "grad_v"]):
+        assert_kernel_close(gpu, cpu, scale=np.abs(cpu).max(), what=name)
+    masked_rows = np.repeat(m.reshape(-1) == 0.0, h).reshape(-1)
+    for cpu, gpu in res[2:]:
+        assert not gpu[masked_rows].any() and not np.signbit(gpu[masked_rows]).any(), "a masked key's row is +0"
+
+
+@pytest.mark.parametrize("rows,v", [(5, 11), (64, 1000), (33, 30522)])
+def test_cross_entropy_and_its_gradient(device, rows, v):
+    r = rng(rows + v)
+    p = ProgramText()
+    x = p.input("x", "f32", [rows, v]); labels = p.input("labels", "i32", [rows]); w = p.input("w", "f32", [rows])
+    one = p.node("Tensor<f32, []>", "Scalar 1.0")
+    loss = p.op("CrossEntropy", [], [x, labels, w]); d = p.op("CrossEntropyGrad", [rows, v], [x, labels, w, one])
+    p.output(loss); p.output(d)
+    wv = (r.random(rows) < 0.6).astype(np.float32)
+    wv[0] = 1.0
+    feed = {"x": values(r, rows, v) * 3, "labels": r.integers(0, v, size=rows).astype(np.int32), "w": wv}
+    res = run_both(device, p.text(), feed, outputs=[(loss, 1), (d, rows * v)])
+    assert_kernel_close(res[0][1], res[0][0], what="cross_entropy")
+    assert_kernel_close(res[1][1], res[1][0], scale=1.0 / wv.sum(), what="cross_entropy_grad")
+    zero_rows = np.repeat(wv == 0.0, v)
+    assert not res[1][1][zero_rows].any()
+
+
+def test_cross_entropy_with_no_weight_is_zero_loss_and_zero_gradient(device):
+    p = ProgramText()
+    x = p.input("x", "f32", [4, 9]); labels = p.input("labels", "i32", [4]); w = p.input("w", "f32", [4])
+    one = p.node("Tensor<f32, []>", "Scalar 1.0")
+    loss = p.op("CrossEntropy", [], [x, labels, w]); d = p.op("CrossEntropyGrad", [4, 9], [x, labels, w, one])
+    p.output(loss); p.output(d)
+    res = run_both(device, p.text(), {"x": values(rng(1), 4, 9), "labels": np.zeros(4, np.int32), "w": np.zeros(4, np.float32)},
+                   outputs=[(loss, 1), (d, 36)])
+    assert res[0][1][0] == 0.0 and not res[1][1].any()
+
+
+@pytest.mark.parametrize("p_drop", [0.1, 0.5, 0.999])
+def test_dropout_mask_and_values_match_the_cpu_in_bits(device, p_drop):
+    r = rng(13)
+    n = 128 * 1031
+    p = ProgramText()
+    x = p.input("x", "f32", [128, 1031]); token = p.input("M.forward.dropout#0", "i32", [2]); g = p.input("g", "f32", [128, 1031])
+    y = p.op("Dropout", [128, 1031], [x, token], attr="[p = %r, site = M.forward.dropout#0]" % p_drop)
+    d = p.op("DropoutGrad", [128, 1031], [token, g], attr="[p = %r, site = M.forward.dropout#0]" % p_drop)
+    p.output(y); p.output(d)
+    tok = np.array([0x12345678, -5], dtype=np.int32)
+    feed = {"x": values(r, 128, 1031) + 1, "M.forward.dropout#0": tok, "g": values(r, 128, 1031) + 1}
+    res = run_both(device, p.text(), feed, outputs=[(y, n), (d, n)], seed=0x0123456789abcdef)
+    for cpu, gpu in res:
+        assert_bits_equal(gpu, cpu, "dropout p=%r" % p_drop)
+    kept = (res[0][1] != 0).mean()
+    assert abs(kept - (1 - p_drop)) < 0.01
+
+
+def test_bad_inputs_are_refused_like_the_interpreter_refuses_them(device):
+    p = ProgramText()
+    table = p.input("table", "f32", [5, 4]); ids = p.input("ids", "i32", [3])
+    e = p.op("Embedding", [3, 4], [table, ids])
+    p.output(e)
+    plan = M.Plan(device, p.text())
+    try:
+        with pytest.raises(M.MsxError) as err:
+            plan.set_input("ids", np.array([0, 5, 1], dtype=np.int32))
+        assert err.value.status == M.BAD_INPUT and "[1] = 5" in str(err.value)
+        with pytest.raises(M.MsxError) as err:
+            plan.set_input("nope", np.zeros(3, dtype=np.int32))
+        assert err.value.status == M.BAD_ARGUMENT
+        with pytest.raises(M.MsxError) as err:
+            plan.set_input("ids", np.zeros(4, dtype=np.int32))
+        assert err.value.status == M.BAD_ARGUMENT
+    finally:
+        plan.destroy()
+
+
+def test_an_op_without_a_kernel_is_refused_at_plan_creation(device):
+    text = '%0: Tensor<f32, [4, 3]> = Input "p"\n%1: Tensor<f32, [3]> = SigregColumns %0\noutput %1\n'
+    with pytest.raises(M.MsxError) as err:
+        M.Plan(device, text)
+    assert err.value.status == M.UNSUPPORTED and "SigregColumns" in str(err.value)

@@ -1,0 +1,167 @@
+"""Run-level parity on the GPU: whole training runs through the C ABI against the CPU oracle on
+the same seed and the same batches, held to the reference's run tolerance
+|g - c| <= 1e-4 + 1e-3 |c| for every loss and every parameter element
+(crates/modelspec-cli/tests/common/mod.rs:24-43 of the reference), and against the reference's
+recorded outputs where it has some."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import modelspec_b200 as M
+from modelspec_b200 import models, synthetic
+from helpers import assert_run_close, train_both
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def check_run(out, what, key_bias_atol=None):
+    assert np.isfinite(out["gpu_losses"]).all()
+    assert_run_close(out["gpu_losses"], out["cpu_losses"], what + " losses")
+    for path, g, c in zip(out["paths"], out["gpu_params"], out["cpu_params"]):
+        # The exact gradient of an attention key bias is 0; what is left is rounding, so the
+        # reference bounds it by the steps taken (tests/common/mod.rs:33-43).
+        atol = key_bias_atol if key_bias_atol and path.endswith("_bk") else 1e-4
+        assert_run_close(g, c, "%s parameter %s" % (what, path), atol=atol)
+
+
+def test_linear_regression_run_matches_the_recorded_log(device):
+    golden = json.load(open(os.path.join(GOLDEN, "linear_regression.losses.json")))
+    out = train_both(device, models.linear_regression(), 500, synthetic=True)
+    recorded = np.array(golden["losses"], dtype=np.float32)
+    assert_run_close(out["gpu_losses"], recorded, "recorded losses")
+    # The matmuls are the same fused chains and SGD the same two roundings: only the f64 tree of
+    # the mse can move a last bit.
+    assert np.abs(out["gpu_losses"][:50] - recorded[:50]).max() <= 1e-6 * recorded[:50].max()
+    assert_run_close(out["gpu_params"][0], np.array(golden["final_param"], dtype=np.float32), "final parameter")
+    check_run(out, "linear regression")
+
+
+def test_two_layer_relu_run_matches_the_recorded_losses(device):
+    golden = json.load(open(os.path.join(GOLDEN, "two_layer_relu.losses.json")))
+    out = train_both(device, models.two_layer_relu(), 200, synthetic=True)
+    assert_run_close(out["gpu_losses"], np.array(golden["losses"], dtype=np.float32), "recorded losses")
+    check_run(out, "two layer relu")
+
+
+def test_the_device_draws_the_same_synthetic_batch_as_the_cpu(device):
+    import oracle_lib
+    source = models.transformer_block(batch=2, seq=16, hidden=32, heads=2, ffn=64, layers=1)
+    cpu = oracle_lib.Trainer(source)
+    cpu.synthetic()
+    gpu = M.Training(device, source)
+    try:
+        gpu.synthetic()
+        n = 2 * 16 * 32
+        assert np.array_equal(gpu.get_input("x", n), cpu.get_input("x", n)), "the drawn input is the same bits"
+        assert np.array_equal(gpu.get_input("key_mask", 32), np.ones(32, dtype=np.float32))
+        assert_run_close(gpu.get_input("y", n), cpu.get_input("y", n), "teacher target")
+    finally:
+        gpu.destroy()
+
+
+def test_transformer_block_first_loss_is_the_recorded_one(device):
+    """The reference records `step 0 loss 0.74829835` for its transformer-block example on the
+    CPU (benchmarks/raw/2026-10-27-transformer-block/loss-cpu.txt)."""
+    out = train_both(device, models.transformer_block(), 3, synthetic=True)
+    assert abs(float(out["gpu_losses"][0]) - 0.74829835) <= 1e-4 + 1e-3 * 0.74829835
+    check_run(out, "transformer block")
+
+
+def test_mlp_classifier_run(device):
+    batch = synthetic.classifier_batch()
+    out = train_both(device, models.mlp_classifier(steps=60), 60, feed=lambda k: batch)
+    check_run(out, "mlp classifier")
+    assert out["gpu_losses"][-1] < out["gpu_losses"][0]
+
+
+def test_encoder_block_with_dropout_and_adamw_over_100_steps(device):
+    """The small twin of the encoder-block configuration: dropout, attention, layer norm, gelu,
+    mse and AdamW over 100 steps, the length the tolerance is stated for."""
+    source = models.CONFIGS["encoder_block"]["source"](batch=2, seq=16, hidden=32, heads=2, ffn=64, steps=100)
+    n = 2 * 16 * 32
+    x = synthetic.normal_batch(1, n)
+    y = synthetic.normal_batch(2, n)
+    feed = {"x": x, "y": y, "key_mask": np.ones(32, dtype=np.float32)}
+    out = train_both(device, source, 100, feed=lambda k: feed)
+    check_run(out, "encoder block twin", key_bias_atol=1e-4 + 100 * 1e-3 * 1e-3)
+
+
+def test_encoder_block_at_full_size(device):
+    source = models.CONFIGS["encoder_block"]["source"](steps=3)
+    n = 4096 * 128
+    feed = {"x": synthetic.normal_batch(1, n), "y": synthetic.normal_batch(2, n), "key_mask": np.ones(4096, dtype=np.float32)}
+    out = train_both(device, source, 3, feed=lambda k: feed)
+    check_run(out, "encoder block", key_bias_atol=1e-4 + 3 * 1e-3 * 1e-3)
+
+
+def bert_feed(vocab, seq, batch):
+    return lambda k: synthetic.mlm_batch(k, vocab=vocab, seq=seq, batch=batch, mask_id=min(103, vocab - 1))
+
+
+@pytest.mark.parametrize("masked_rows", [0, 64])
+def test_bert_twin_over_100_steps(device, masked_rows):
+    """The hidden-32 twin of BERT-tiny (the reference trains the same twin on its CPU,
+    crates/modelspec-cli/tests/fixtures/bert_cpu.mspec): embeddings, tied decoder, dropout,
+    weighted cross-entropy, AdamW with warm-up, with and without the masked-row gather."""
+    source = models.bert(name="BertTiny", hidden=32, heads=2, ffn=64, vocab=300, seq=16, batch=8, lr=3e-3,
+                         warmup_steps=10, steps=100)
+    out = train_both(device, source, 100, masked_rows=masked_rows, feed=bert_feed(300, 16, 8))
+    check_run(out, "bert twin", key_bias_atol=1e-4 + 100 * 3e-3 * 1e-3)
+    assert out["gpu_losses"][-1] < out["gpu_losses"][0]
+
+
+def test_bert_tiny_at_full_size_with_the_masked_row_gather(device):
+    """BERT-tiny at vocabulary 30,522 with the default gather capacity (832 rows of 4,096): the
+    benchmark's workload, two steps and the final loss."""
+    source = models.bert(steps=2, warmup_steps=1)
+    out = train_both(device, source, 2, masked_rows=models.default_masked_rows(4096), feed=bert_feed(30522, 128, 32))
+    check_run(out, "bert tiny", key_bias_atol=1e-4 + 2 * 1e-4 * 1e-3)
+    stats = out["stats"]
+    assert stats["arena_bytes"] < stats["unshared_bytes"], "values share storage by liveness"
+    assert stats["launches_per_step"] < 200
+
+
+def test_graph_and_direct_launches_agree_in_bits(device):
+    source = models.bert(name="BertTiny", hidden=32, heads=2, ffn=64, vocab=300, seq=16, batch=8, steps=5, warmup_steps=1)
+    runs = [train_both(device, source, 5, masked_rows=64, feed=bert_feed(300, 16, 8), flags=flags)
+            for flags in (M.PLAN_DEFAULT, M.PLAN_NO_GRAPH)]
+    assert np.array_equal(runs[0]["gpu_losses"], runs[1]["gpu_losses"])
+    for a, b in zip(runs[0]["gpu_params"], runs[1]["gpu_params"]):
+        assert np.array_equal(a, b)
+
+
+def test_more_selected_rows_than_the_gather_holds_is_refused(device):
+    source = models.bert(name="BertTiny", hidden=32, heads=2, ffn=64, vocab=300, seq=16, batch=8, steps=5, warmup_steps=1)
+    t = M.Training(device, source, masked_rows=8)
+    try:
+        for name, value in bert_feed(300, 16, 8)(0).items():
+            t.set_input(name, value)
+        with pytest.raises(M.MsxError) as err:
+            t.step(0, 5)
+        assert err.value.status == M.BAD_INPUT and "E-DATA-012" in str(err.value)
+    finally:
+        t.destroy()
+
+
+def test_a_non_finite_loss_is_reported_not_trained_through(device):
+    source = models.mlp_classifier(steps=3)
+    batch = dict(synthetic.classifier_batch())
+    batch["x"] = batch["x"].copy()
+    batch["x"][5] = np.nan
+    t = M.Training(device, source)
+    try:
+        for name, value in batch.items():
+            t.set_input(name, value)
+        t.step(0, 3)
+        with pytest.raises(M.MsxError) as err:
+            t.loss()
+        assert err.value.status == M.NON_FINITE and "E-TRAIN-001" in str(err.value)
+        t.step(1, 3)
+        with pytest.raises(M.MsxError) as err:
+            t.check_finite()
+        assert err.value.status == M.NON_FINITE
+    finally:
+        t.destroy()
