@@ -112,7 +112,7 @@ struct msx_plan {
             case Slot::Param: return params[s.index];
             case Slot::Moment: return (s.moment == 'm' ? m : v)[s.index];
             case Slot::Input: return d_inputs + s.offset;
-            case Slot::Const: return d_consts + s.offset;
+            case Slot::Const: return reinterpret_cast<char*>(d_consts) + s.offset;
             case Slot::View: return ptr(s.index);
             default: return nullptr;
         }

@@ -232,7 +232,7 @@ def default_masked_rows(rows, rate=0.15):
 CONFIGS = {
     "mlp": dict(kind="mlp", source=lambda **kw: mlp_classifier(**kw), rows=64),
     "encoder_block": dict(kind="block", source=lambda **kw: transformer_block(
-        **{**dict(batch=32, layers=1, dropout=0.1, optimizer="adamw", lr=1e-3, weight_decay=0.01, eps=1e-8,
+        **{**dict(batch=32, layers=1, dropout=0.1, optimizer="adamw", lr=1e-3, weight_decay=0.01, eps=1e-6,
                   warmup_steps=0), **kw}), rows=4096),
     "bert_tiny": dict(kind="bert", source=lambda **kw: bert(**kw), rows=4096, seq=128, batch=32, vocab=30522),
     "bert_mini": dict(kind="bert", source=lambda **kw: bert(**{**dict(name="BertMini", layers=4, hidden=256, heads=4, ffn=1024), **kw}),
