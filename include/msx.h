@@ -225,6 +225,27 @@ int msx_training_final_loss(msx_training* training, float* loss);
  * NaN or an infinity. Reads every parameter back; call it at the cadence the host can afford. */
 int msx_training_check_finite(msx_training* training);
 
+/* Column sums without any allocation: out[c] = sum over rows of g[r, c] for a row-major
+ * [rows, columns] device matrix, the `SumRows` of a bias gradient. This function has no
+ * counterpart in the reference. It exists for hosts that cannot allocate device memory once they
+ * run (all memory handed to their own pool, a loop that may not enter the allocator, a host
+ * application that forbids it): it calls no cudaMalloc, cudaFree or allocating library routine.
+ * Its partial sums live in a 1 MiB device array that is part of the library image on every GPU
+ * that loads the library, until the process exits.
+ *   - `device_g` and `device_out` are the caller's device buffers; `stream` is a cudaStream_t
+ *     (null for the default stream). The call enqueues two kernels and returns.
+ *   - `columns` must be between 1 and 4096; more is MSX_BAD_ARGUMENT, as are null pointers.
+ *     The message is msx_static_last_error().
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array. Calls whose kernels can overlap on the GPU
+ *     (different streams without an ordering between them) race on it: order them. Nothing in
+ *     the array has to be cleared between calls, since each call writes every partial sum it
+ *     later reads.
+ * The result has the bits of the plan's own `sum_rows` launch (same kernels). */
+int msx_sum_rows_static(const float* device_g, uint64_t rows, uint64_t columns, float* device_out, void* stream);
+const char* msx_static_last_error(void);
+
 /* The `.mspec` front door, for hosts without the reference's compiler: lowers the train block
  * of `source`, differentiates it and attaches its optimizer. `which` is "step", "forward" (the
  * dropout-free program of the final loss line) or "tensor". `masked_rows` is the capacity of

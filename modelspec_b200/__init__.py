@@ -86,6 +86,8 @@ SIGNATURES = {
     "msx_training_loss": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "msx_training_final_loss": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "msx_training_check_finite": (C.c_int, [_P]),
+    "msx_sum_rows_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, _P, _P]),
+    "msx_static_last_error": (C.c_char_p, []),
     "msx_compile": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_uint64, C.c_char_p, C.c_uint64]),
 }
 
