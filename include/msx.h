@@ -41,7 +41,9 @@ enum {
 /* Plan flags. */
 enum {
     MSX_PLAN_DEFAULT = 0,
-    MSX_PLAN_NO_GRAPH = 1   /* launch kernels one by one instead of through one CUDA graph */
+    MSX_PLAN_NO_GRAPH = 1,  /* launch kernels one by one instead of through one CUDA graph */
+    MSX_PLAN_EXACT_MATMUL = 2 /* matmuls as f32 fused chains in ascending k, the bits of the
+                                 reference's CPU loop, instead of 3xTF32 on the tensor cores */
 };
 
 typedef struct msx_stats {
@@ -224,6 +226,18 @@ int msx_training_final_loss(msx_training* training, float* loss);
 /* E-TRAIN-001 over the state: MSX_NON_FINITE naming the first parameter or moment that holds a
  * NaN or an infinity. Reads every parameter back; call it at the cadence the host can afford. */
 int msx_training_check_finite(msx_training* training);
+
+/* One matmul on the caller's device buffers, outside any plan: C[m, n] = op(A) x op(B) with
+ * `a_transposed` meaning A is stored [k, m] and `b_transposed` meaning B is stored [n, k]
+ * (the operand flags of the reference's matmul kernel, ir/kernel.rs:1013-1046). `exact` selects
+ * the f32 fused-chain kernel; otherwise the tensor-core kernel runs, which needs
+ * msx_op_matmul_workspace(m, n, k) floats of device scratch (0 when k is not split) and a device
+ * status word (bit 1 is raised if a bounded wait inside the kernel runs out). Enqueues on
+ * `stream` (a cudaStream_t) and returns. For profiling a single kernel on a small case and for
+ * hosts that schedule themselves. */
+int msx_op_matmul(const float* a, int a_transposed, const float* b, int b_transposed, float* c, uint64_t m, uint64_t n,
+                  uint64_t k, float* workspace, uint64_t workspace_floats, uint32_t* status, void* stream, int exact);
+uint64_t msx_op_matmul_workspace(uint64_t m, uint64_t n, uint64_t k);
 
 /* Column sums without any allocation: out[c] = sum over rows of g[r, c] for a row-major
  * [rows, columns] device matrix, the `SumRows` of a bias gradient. This function has no

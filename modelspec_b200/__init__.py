@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libmsx.so")
 
 OK, BAD_ARGUMENT, NO_DEVICE, OUT_OF_MEMORY, UNSUPPORTED, LAUNCH_FAILED, NON_FINITE, TIMEOUT, BAD_INPUT = range(9)
-PLAN_DEFAULT, PLAN_NO_GRAPH = 0, 1
+PLAN_DEFAULT, PLAN_NO_GRAPH, PLAN_EXACT_MATMUL = 0, 1, 2
 
 STATUS_NAMES = ["MSX_OK", "MSX_BAD_ARGUMENT", "MSX_NO_DEVICE", "MSX_OUT_OF_MEMORY", "MSX_UNSUPPORTED",
                 "MSX_LAUNCH_FAILED", "MSX_NON_FINITE", "MSX_TIMEOUT", "MSX_BAD_INPUT"]
@@ -86,6 +86,8 @@ SIGNATURES = {
     "msx_training_loss": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "msx_training_final_loss": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "msx_training_check_finite": (C.c_int, [_P]),
+    "msx_op_matmul": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_uint64, C.c_uint64, C.c_uint64, _P, C.c_uint64, _P, _P, C.c_int]),
+    "msx_op_matmul_workspace": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
     "msx_sum_rows_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, _P, _P]),
     "msx_static_last_error": (C.c_char_p, []),
     "msx_compile": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_uint64, C.c_char_p, C.c_uint64]),

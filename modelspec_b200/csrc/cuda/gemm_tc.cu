@@ -1,0 +1,446 @@
+// matmul on the 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory,
+// f32 operands as a 3xTF32 split (tolerance class).
+//
+// Each f32 operand x is split into hi = tf32(x) and lo = tf32(x - hi) (both round-to-nearest,
+// cvt.rna), and a product is summed as lo*hi + hi*lo + hi*hi in the f32 accumulator; the dropped
+// lo*lo term and the two roundings leave about 2^-21 of each |a||b| term, three orders below the
+// kernel tolerance 1e-5 + 1e-4 r. The exact kernel (gemm.cu) stays for bit-level parity runs.
+//
+// One CTA computes a 128 x BN tile (BN = 64 or 128) over a range of 32-deep k blocks:
+//   warps 0-7  load the A and B blocks from global memory, split them and store hi and lo in the
+//              128-byte-swizzled shared-memory layouts tcgen05 reads (K-major or MN-major by how
+//              the operand is stored, so NN, TN and NT need no transposed copy), then drain the
+//              accumulator: tcgen05.ld, bounds-checked stores to C or to the split-K workspace;
+//   warp 8     allocates tensor memory, issues 12 MMAs per k block (4 k-slices x 3 products) from
+//              one thread, and releases each shared-memory stage with tcgen05.commit.
+// The split happens on the way from global to shared memory rather than after a TMA copy: a TMA
+// tile would be written, read back and written twice more, and shared-memory bandwidth is what
+// bounds 3xTF32 from shared operands (per k block 96 KB of MMA operand reads against 64 KB of
+// split stores here, 128 KB with a TMA staging copy). Operands whose row pitch is not a multiple
+// of 16 bytes (a 30,522-wide logits matrix) could not be TMA sources in any case.
+//
+// Three stages of 64 KB. Stage hand-off is by mbarriers; every wait is bounded and, when it runs
+// out, raises bit 1 of the status word, makes every role leave its loop, frees the tensor memory
+// and returns. A k range split across CTAs (grid.z) writes partial tiles that
+// `splitk_reduce_kernel` adds in ascending split order (deterministic).
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace msx {
+namespace k {
+
+namespace {
+
+constexpr int BM = 128, BK = 32, STAGES = 3;
+constexpr int LOADER_THREADS = 256, THREADS = LOADER_THREADS + 32;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives up
+
+template <int BN> struct Smem {
+    static constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
+    static constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;  // a_hi, a_lo, b_hi, b_lo
+    static constexpr uint32_t TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+struct TcArgs {
+    const float* a;
+    const float* b;
+    float* c;          // C, or the split-K workspace [splits][m][n]
+    uint32_t m, n, k;
+    uint32_t lda, ldb, ldc;        // row pitch, in elements, of each matrix as stored
+    uint32_t kblocks_per_split;
+    uint32_t a_vec, b_vec, c_vec;  // 16-byte accesses are aligned for this operand
+    // Batched products: grid.z = batch index z, split as (z / inner, z % inner); each matrix of
+    // problem z starts at outer * stride_outer + inner * stride_inner elements. inner = 0: not batched.
+    uint32_t batch_inner;
+    uint64_t a_outer, a_inner, b_outer, b_inner, c_outer, c_inner;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for `parity` of `bar`; false when the wait ran out or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
+    for (uint32_t spin = 0; spin < WAIT_LIMIT; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicOr(status, 2u);
+    return false;
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// The shared-memory matrix descriptor of tcgen05 (version 1): start address, leading and stride
+// byte offsets in 16-byte units, and the swizzle of the tile: 2 = 128-byte swizzle of 16-byte
+// chunks (K-major tiles), 1 = 128-byte swizzle of 32-byte chunks, the one layout the tensor core
+// reads MN-major 32-bit operands from.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
+    uint64_t d = static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;  // descriptor version of sm_100
+    d |= static_cast<uint64_t>(layout_type) << 61;
+    return d;
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Byte offset of the 16-byte chunk holding elements (row, 4 c16 .. 4 c16 + 3) of a K-major tile:
+// 128-byte rows, 8-row groups of 1024 bytes, chunk index xor-ed with the row within its group.
+__device__ __forceinline__ uint32_t k_major_offset(uint32_t row, uint32_t c16) {
+    return (row >> 3) * 1024u + (row & 7u) * 128u + ((c16 ^ (row & 7u)) << 4);
+}
+// The same for an MN-major tile: for each k a 128-byte row of 32 consecutive MN elements, the
+// 32 k rows of a block forming one 4096-byte panel per 32 MN elements; within a row the 32-byte
+// chunk index is xor-ed with the k row modulo 4 (groups of 4 rows, 512 bytes). `c` counts 16-byte
+// chunks along MN.
+__device__ __forceinline__ uint32_t mn_major_offset(uint32_t krow, uint32_t c) {
+    uint32_t in_panel = c & 7u;
+    return (c >> 3) * (BK * 128u) + krow * 128u + (((in_panel >> 1) ^ (krow & 3u)) << 5) + ((in_panel & 1u) << 4);
+}
+
+__device__ __forceinline__ float4 load4(const float* __restrict__ p, uint64_t index, uint32_t valid, bool vec) {
+    // `valid` = how many of the 4 elements from `index` are inside the matrix (0..4).
+    if (valid == 4 && vec) return *reinterpret_cast<const float4*>(p + index);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (valid > 0) v.x = p[index];
+    if (valid > 1) v.y = p[index + 1];
+    if (valid > 2) v.z = p[index + 2];
+    if (valid > 3) v.w = p[index + 3];
+    return v;
+}
+
+__device__ __forceinline__ void store_split(char* hi, char* lo, uint32_t offset, float4 v) {
+    float4 h, l;
+    h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
+    l.x = to_tf32(v.x - h.x); l.y = to_tf32(v.y - h.y); l.z = to_tf32(v.z - h.z); l.w = to_tf32(v.w - h.w);
+    *reinterpret_cast<float4*>(hi + offset) = h;
+    *reinterpret_cast<float4*>(lo + offset) = l;
+}
+
+__device__ __forceinline__ uint32_t in_range(uint32_t start, uint32_t limit) {
+    return start >= limit ? 0u : (limit - start >= 4u ? 4u : limit - start);
+}
+
+template <int BN, bool A_T, bool B_T>
+__global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
+    extern __shared__ char smem_raw[];
+    // Tiles need 1024-byte alignment for the swizzle pattern to line up with address bits.
+    char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * Smem<BN>::STAGE_BYTES);
+    // bars[0..2] full, bars[3..5] empty, bars[6] accumulator ready; then the TMEM address and the abort flag.
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 9);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const uint32_t kblocks_total = (args.k + BK - 1) / BK;
+    const bool batched = args.batch_inner != 0;
+    const uint32_t z_outer = batched ? blockIdx.z / args.batch_inner : 0, z_inner = batched ? blockIdx.z % args.batch_inner : 0;
+    const uint32_t kb_begin = batched ? 0 : blockIdx.z * args.kblocks_per_split;
+    const uint32_t kb_end = min(kblocks_total, kb_begin + args.kblocks_per_split);
+    const uint32_t kblocks = kb_end > kb_begin ? kb_end - kb_begin : 0;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars[s]), LOADER_THREADS);
+            mbar_init(smem_u32(&bars[STAGES + s]), 1);
+        }
+        mbar_init(smem_u32(&bars[2 * STAGES]), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(static_cast<uint32_t>(BN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 8) {
+        // ---- loaders: global -> (hi, lo) -> swizzled shared memory ---------------------------
+        const float* __restrict__ a = args.a + z_outer * args.a_outer + z_inner * args.a_inner;
+        const float* __restrict__ b = args.b + z_outer * args.b_outer + z_inner * args.b_inner;
+        bool alive = true;
+        for (uint32_t kb = 0; kb < kblocks && alive; ++kb) {
+            const uint32_t stage = kb % STAGES, round = kb / STAGES;
+            const uint32_t k0 = (kb_begin + kb) * BK;
+            char* a_hi = tiles + stage * Smem<BN>::STAGE_BYTES;
+            char* a_lo = a_hi + Smem<BN>::A_BYTES;
+            char* b_hi = a_lo + Smem<BN>::A_BYTES;
+            char* b_lo = b_hi + Smem<BN>::B_BYTES;
+            constexpr int A_CHUNKS = BM * BK / 4 / LOADER_THREADS, B_CHUNKS = BN * BK / 4 / LOADER_THREADS;
+            float4 av[A_CHUNKS], bv[B_CHUNKS];
+            uint32_t aoff[A_CHUNKS], boff[B_CHUNKS];
+#pragma unroll
+            for (int i = 0; i < A_CHUNKS; ++i) {
+                uint32_t q = tid + i * LOADER_THREADS;
+                if (A_T) {  // stored [k, m]: 32 chunks of 4 consecutive m per k row
+                    uint32_t krow = q >> 5, c = q & 31u, gk = k0 + krow, gm = m0 + c * 4;
+                    uint32_t valid = gk < args.k ? in_range(gm, args.m) : 0u;
+                    av[i] = load4(a, static_cast<uint64_t>(gk) * args.lda + gm, valid, args.a_vec);
+                    aoff[i] = mn_major_offset(krow, c);
+                } else {    // stored [m, k]: 8 chunks of 4 consecutive k per row
+                    uint32_t row = q >> 3, c16 = q & 7u, gm = m0 + row, gk = k0 + c16 * 4;
+                    uint32_t valid = gm < args.m ? in_range(gk, args.k) : 0u;
+                    av[i] = load4(a, static_cast<uint64_t>(gm) * args.lda + gk, valid, args.a_vec);
+                    aoff[i] = k_major_offset(row, c16);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < B_CHUNKS; ++i) {
+                uint32_t q = tid + i * LOADER_THREADS;
+                if (B_T) {  // stored [n, k]
+                    uint32_t row = q >> 3, c16 = q & 7u, gn = n0 + row, gk = k0 + c16 * 4;
+                    uint32_t valid = gn < args.n ? in_range(gk, args.k) : 0u;
+                    bv[i] = load4(b, static_cast<uint64_t>(gn) * args.ldb + gk, valid, args.b_vec);
+                    boff[i] = k_major_offset(row, c16);
+                } else {    // stored [k, n]
+                    uint32_t krow = q / (BN / 4), c = q % (BN / 4), gk = k0 + krow, gn = n0 + c * 4;
+                    uint32_t valid = gk < args.k ? in_range(gn, args.n) : 0u;
+                    bv[i] = load4(b, static_cast<uint64_t>(gk) * args.ldb + gn, valid, args.b_vec);
+                    boff[i] = mn_major_offset(krow, c);
+                }
+            }
+            // The stage is free once the MMAs that read its previous contents have completed.
+            alive = mbar_wait(smem_u32(&bars[STAGES + stage]), (round & 1u) ^ 1u, abort_flag, args.status);
+            if (!alive) break;
+#pragma unroll
+            for (int i = 0; i < A_CHUNKS; ++i) store_split(a_hi, a_lo, aoff[i], av[i]);
+#pragma unroll
+            for (int i = 0; i < B_CHUNKS; ++i) store_split(b_hi, b_lo, boff[i], bv[i]);
+            // Make the generic-proxy stores visible to the tensor core's async-proxy reads.
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(&bars[stage]));
+        }
+        // ---- epilogue: tensor memory -> registers -> global -----------------------------------
+        if (alive && kblocks > 0) alive = mbar_wait(smem_u32(&bars[2 * STAGES]), 0, abort_flag, args.status);
+        alive = __all_sync(0xffffffffu, alive);  // tcgen05.ld is warp-wide: decide as a warp
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t row = (warp & 3u) * 32 + lane, gm = m0 + row;
+        const uint32_t col_half = warp >> 2;  // warps 0-3: first half of the columns, 4-7: second
+        float* __restrict__ out = batched ? args.c + z_outer * args.c_outer + z_inner * args.c_inner
+                                          : args.c + static_cast<uint64_t>(blockIdx.z) * args.m * args.ldc;
+#pragma unroll
+        for (int part = 0; part < BN / 64; ++part) {
+            const uint32_t col = col_half * (BN / 2) + part * 32;
+            uint32_t r[32];
+            if (alive && kblocks > 0) {
+                uint32_t taddr = tmem_base + (((warp & 3u) * 32u) << 16) + col;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;  // an empty k range contributes zeros
+            }
+            if (gm < args.m) {
+                float* dst = out + static_cast<uint64_t>(gm) * args.ldc + n0 + col;
+                if (args.c_vec && n0 + col + 32 <= args.n) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]) + 0.0f, __uint_as_float(r[j + 1]) + 0.0f,
+                                                                            __uint_as_float(r[j + 2]) + 0.0f, __uint_as_float(r[j + 3]) + 0.0f);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (n0 + col + j < args.n) dst[j] = __uint_as_float(r[j]) + 0.0f;
+                }
+            }
+        }
+    } else {
+        // ---- the MMA warp: one thread issues, the tensor core runs asynchronously ---------------
+        // Instruction descriptor: f32 accumulator, tf32 A and B, their majors, N >> 3, M >> 4.
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_T ? 1u : 0u) << 15) | ((B_T ? 0u : 1u) << 16) |
+                               (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+        bool alive = true;
+        for (uint32_t kb = 0; kb < kblocks && alive; ++kb) {
+            const uint32_t stage = kb % STAGES, round = kb / STAGES;
+            alive = mbar_wait(smem_u32(&bars[stage]), round & 1u, abort_flag, args.status);
+            if (!alive) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0) {
+                const uint32_t a_hi = smem_u32(tiles + stage * Smem<BN>::STAGE_BYTES);
+                const uint32_t a_lo = a_hi + Smem<BN>::A_BYTES;
+                const uint32_t b_hi = a_lo + Smem<BN>::A_BYTES;
+                const uint32_t b_lo = b_hi + Smem<BN>::B_BYTES;
+#pragma unroll
+                for (uint32_t ks = 0; ks < BK / 8; ++ks) {
+                    // One MMA covers k = 8: 32 bytes along a K-major row (8-row groups 1024 bytes
+                    // apart), or 8 rows of an MN-major panel (4-row groups 512 bytes apart, panels
+                    // of 32 MN elements 4096 bytes apart).
+                    const uint32_t a_step = A_T ? ks * 1024u : ks * 32u;
+                    const uint32_t b_step = B_T ? ks * 32u : ks * 1024u;
+                    const uint32_t a_lbo = A_T ? BK * 128u : 16u, b_lbo = B_T ? 16u : BK * 128u;
+                    const uint32_t a_sbo = A_T ? 512u : 1024u, b_sbo = B_T ? 1024u : 512u;
+                    const uint32_t a_type = A_T ? 1u : 2u, b_type = B_T ? 2u : 1u;
+                    const uint64_t da_hi = smem_desc(a_hi + a_step, a_lbo, a_sbo, a_type), da_lo = smem_desc(a_lo + a_step, a_lbo, a_sbo, a_type);
+                    const uint64_t db_hi = smem_desc(b_hi + b_step, b_lbo, b_sbo, b_type), db_lo = smem_desc(b_lo + b_step, b_lbo, b_sbo, b_type);
+                    mma_tf32(tmem_base, da_lo, db_hi, idesc, (kb | ks) != 0u);
+                    mma_tf32(tmem_base, da_hi, db_lo, idesc, 1u);
+                    mma_tf32(tmem_base, da_hi, db_hi, idesc, 1u);
+                }
+                mma_commit(smem_u32(&bars[STAGES + stage]));                   // frees the stage when they finish
+                if (kb + 1 == kblocks) mma_commit(smem_u32(&bars[2 * STAGES]));  // and, at the end, the accumulator
+            }
+            __syncwarp();
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(static_cast<uint32_t>(BN)) : "memory");
+    }
+}
+
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ c, uint64_t count, uint32_t splits) {
+    uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float acc = ws[i];
+        for (uint32_t s = 1; s < splits; ++s) acc += ws[static_cast<uint64_t>(s) * count + i];
+        c[i] = acc;
+    }
+}
+
+template <int BN, bool A_T, bool B_T> void launch(cudaStream_t s, const TcArgs& args, dim3 grid) {
+    auto kernel = matmul_tc_kernel<BN, A_T, B_T>;
+    check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Smem<BN>::TOTAL)), "matmul_tc shared memory");
+    kernel<<<grid, THREADS, Smem<BN>::TOTAL, s>>>(args);
+    check_launch("matmul_tc");
+}
+
+template <int BN> void launch_forms(cudaStream_t s, const TcArgs& args, dim3 grid, bool a_t, bool b_t) {
+    if (a_t && b_t) launch<BN, true, true>(s, args, grid);
+    else if (a_t) launch<BN, true, false>(s, args, grid);
+    else if (b_t) launch<BN, false, true>(s, args, grid);
+    else launch<BN, false, false>(s, args, grid);
+}
+
+bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+}  // namespace
+
+MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k) {
+    MatmulTcPlan p;
+    p.bn = n <= 64 ? 64 : 128;
+    uint64_t tiles = ((m + BM - 1) / BM) * ((n + p.bn - 1) / p.bn);
+    uint64_t kblocks = (k + BK - 1) / BK;
+    // Split k until about one wave of CTAs exists, keeping at least 4 k blocks per split.
+    uint64_t want = tiles >= 148 ? 1 : (148 + tiles - 1) / tiles;
+    uint64_t most = kblocks / 4 > 0 ? kblocks / 4 : 1;
+    uint64_t splits = want < most ? want : most;
+    if (splits < 1) splits = 1;
+    p.kblocks_per_split = static_cast<uint32_t>((kblocks + splits - 1) / splits);
+    if (p.kblocks_per_split == 0) p.kblocks_per_split = 1;
+    p.splits = static_cast<uint32_t>(kblocks == 0 ? 1 : (kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split);
+    p.workspace_floats = p.splits > 1 ? p.splits * m * n : 0;
+    return p;
+}
+
+void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m, uint64_t n,
+               uint64_t k, float* workspace, uint32_t* status) {
+    if (m == 0 || n == 0) return;
+    MatmulTcPlan p = matmul_tc_plan(m, n, k);
+    TcArgs args = {};
+    args.a = a;
+    args.b = b;
+    args.c = p.splits > 1 ? workspace : c;
+    args.m = static_cast<uint32_t>(m);
+    args.n = static_cast<uint32_t>(n);
+    args.k = static_cast<uint32_t>(k);
+    args.lda = static_cast<uint32_t>(a_t ? m : k);
+    args.ldb = static_cast<uint32_t>(b_t ? k : n);
+    args.ldc = static_cast<uint32_t>(n);
+    args.kblocks_per_split = p.kblocks_per_split;
+    // A float4 read starts at a multiple of 4 elements within a row, so rows must keep that phase.
+    args.a_vec = aligned16(a) && args.lda % 4 == 0;
+    args.b_vec = aligned16(b) && args.ldb % 4 == 0;
+    args.c_vec = aligned16(args.c) && n % 4 == 0;
+    args.status = status;
+    dim3 grid(static_cast<uint32_t>((n + p.bn - 1) / p.bn), static_cast<uint32_t>((m + BM - 1) / BM), p.splits);
+    if (p.bn == 64) launch_forms<64>(s, args, grid, a_t, b_t);
+    else launch_forms<128>(s, args, grid, a_t, b_t);
+    if (p.splits > 1) {
+        uint64_t count = m * n;
+        uint64_t blocks = (count + 255) / 256;
+        splitk_reduce_kernel<<<static_cast<uint32_t>(blocks > 148 * 8 ? 148 * 8 : blocks), 256, 0, s>>>(workspace, c, count, p.splits);
+        check_launch("splitk_reduce");
+    }
+}
+
+void matmul_tc_batched(cudaStream_t s, const BatchedOperand& a, const BatchedOperand& b, const BatchedOperand& c, uint64_t m,
+                       uint64_t n, uint64_t k, uint32_t outer, uint32_t inner, uint32_t* status) {
+    if (m == 0 || n == 0 || outer == 0 || inner == 0) return;
+    TcArgs args = {};
+    args.a = a.base;
+    args.b = b.base;
+    args.c = const_cast<float*>(c.base);
+    args.m = static_cast<uint32_t>(m);
+    args.n = static_cast<uint32_t>(n);
+    args.k = static_cast<uint32_t>(k);
+    args.lda = a.pitch;
+    args.ldb = b.pitch;
+    args.ldc = c.pitch;
+    args.kblocks_per_split = static_cast<uint32_t>((k + BK - 1) / BK) + 1;
+    auto vec = [](const BatchedOperand& o) {
+        return aligned16(o.base) && o.pitch % 4 == 0 && o.stride_outer % 4 == 0 && o.stride_inner % 4 == 0;
+    };
+    args.a_vec = vec(a);
+    args.b_vec = vec(b);
+    args.c_vec = vec(c);
+    args.batch_inner = inner;
+    args.a_outer = a.stride_outer; args.a_inner = a.stride_inner;
+    args.b_outer = b.stride_outer; args.b_inner = b.stride_inner;
+    args.c_outer = c.stride_outer; args.c_inner = c.stride_inner;
+    args.status = status;
+    uint32_t bn = n <= 64 ? 64 : 128;
+    dim3 grid(static_cast<uint32_t>((n + bn - 1) / bn), static_cast<uint32_t>((m + BM - 1) / BM), outer * inner);
+    if (bn == 64) launch_forms<64>(s, args, grid, a.transposed, b.transposed);
+    else launch_forms<128>(s, args, grid, a.transposed, b.transposed);
+}
+
+}  // namespace k
+}  // namespace msx

@@ -84,6 +84,32 @@ void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* o
 void matmul(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c,
             uint64_t m, uint64_t n, uint64_t k);
 
+// ---- matmul on tensor cores (gemm_tc.cu) ------------------------------------------------------
+// The same product by tcgen05.mma with a 3xTF32 operand split and f32 accumulation in tensor
+// memory: tolerance class (about 2^-21 of each |a||b| term). `workspace` holds
+// matmul_tc_plan(m, n, k).workspace_floats floats (split-K partial tiles; 0 when k is not split).
+// A wait that runs out inside the kernel raises bit 1 of *status instead of hanging.
+struct MatmulTcPlan {
+    uint32_t bn, splits, kblocks_per_split;
+    uint64_t workspace_floats;
+};
+MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k);
+void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m,
+               uint64_t n, uint64_t k, float* workspace, uint32_t* status);
+
+// outer x inner independent products through one launch (grid.z = problem): matrix z of an
+// operand starts at base + (z / inner) * stride_outer + (z % inner) * stride_inner elements and
+// has `pitch` elements between rows as stored; `transposed` as in matmul (A stored [k, m], B
+// stored [n, k]). k is not split.
+struct BatchedOperand {
+    const float* base;
+    uint32_t pitch;
+    uint64_t stride_outer, stride_inner;
+    bool transposed;
+};
+void matmul_tc_batched(cudaStream_t s, const BatchedOperand& a, const BatchedOperand& b, const BatchedOperand& c,
+                       uint64_t m, uint64_t n, uint64_t k, uint32_t outer, uint32_t inner, uint32_t* status);
+
 // ---- attention (attention.cu) -----------------------------------------------------------------
 struct AttentionShape {
     uint32_t batch, q_len, k_len, heads, head_dim;  // q rows = batch * q_len, k rows = batch * k_len
@@ -99,6 +125,16 @@ void attention_grad_q(cudaStream_t s, const float* q, const float* k, const floa
 // Reads the `stats` attention_grad_q wrote for the same operands; dk and dv may each be null.
 void attention_grad_kv(cudaStream_t s, const float* q, const float* k, const float* v, const float* mask,
                        const float* g, const float* stats, float* dk, float* dv, AttentionShape shape);
+
+// The same ops as batched tensor-core matmuls with row kernels between them (attention_tc.cu):
+// tolerance class. `p` and `dp` each hold attention_tc_scratch_floats(shape) floats.
+uint64_t attention_tc_scratch_floats(AttentionShape shape);
+void attention_tc_forward(cudaStream_t s, const float* q, const float* k, const float* v, const float* mask,
+                          float* out, float* p, AttentionShape shape, uint32_t* status);
+// dq, dk and dv may each be null.
+void attention_tc_backward(cudaStream_t s, const float* q, const float* k, const float* v, const float* mask,
+                           const float* g, float* dq, float* dk, float* dv, float* p, float* dp,
+                           AttentionShape shape, uint32_t* status);
 
 // ---- optimizer (optimizer.cu) -----------------------------------------------------------------
 struct UpdateTensor {

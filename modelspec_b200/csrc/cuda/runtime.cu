@@ -546,10 +546,7 @@ struct Scheduler {
             case Op::MatMul: {
                 uint32_t a = in[0], b = in[1];
                 uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(a);
-                Launch& l = emit("matmul", nd, in, {at}, [=](cudaStream_t s) {
-                    k::matmul(s, plan->f(a), plan->transposed(a), plan->f(b), plan->transposed(b), plan->f(at), m, n, kk);
-                });
-                l.flop = 2 * m * n * kk;
+                emit_matmul(nd, at, a, false, b, false, m, n, kk);
                 break;
             }
             case Op::Transpose: {
@@ -559,10 +556,7 @@ struct Scheduler {
                     const Node& mm = node(absorbed->second);
                     uint32_t a = pos(mm.operands[0]), b = pos(mm.operands[1]);
                     uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(a);
-                    Launch& l = emit("matmul", nd, {b, a}, {at}, [=](cudaStream_t s) {
-                        k::matmul(s, plan->f(b), !plan->transposed(b), plan->f(a), !plan->transposed(a), plan->f(at), m, n, kk);
-                    });
-                    l.flop = 2 * m * n * kk;
+                    emit_matmul(nd, at, b, true, a, true, m, n, kk);
                 } else {
                     uint32_t a = in[0];
                     uint64_t r = rows_of(a), c = cols_of(a);
@@ -710,6 +704,32 @@ struct Scheduler {
         }
     }
 
+    // C[m, n] = op(a) x op(b); `flip_*` reads the operand as the transpose of what its slot says.
+    // The exact f32 chain kernel under MSX_PLAN_EXACT_MATMUL, else the tensor cores.
+    void emit_matmul(const Node& nd, uint32_t at, uint32_t a, bool flip_a, uint32_t b, bool flip_b, uint64_t m, uint64_t n,
+                     uint64_t kk) {
+        msx_plan* plan = P;
+        if (P->flags & MSX_PLAN_EXACT_MATMUL) {
+            Launch& l = emit("matmul", nd, {a, b}, {at}, [=](cudaStream_t s) {
+                k::matmul(s, plan->f(a), plan->transposed(a) != flip_a, plan->f(b), plan->transposed(b) != flip_b, plan->f(at), m, n, kk);
+            });
+            l.flop = 2 * m * n * kk;
+            return;
+        }
+        uint64_t floats = k::matmul_tc_plan(m, n, kk).workspace_floats;
+        std::vector<uint32_t> writes = {at};
+        int ws = -1;
+        if (floats) {
+            ws = static_cast<int>(scratch(floats * 4));
+            writes.push_back(static_cast<uint32_t>(ws));
+        }
+        Launch& l = emit("matmul", nd, {a, b}, writes, [=](cudaStream_t s) {
+            k::matmul_tc(s, plan->f(a), plan->transposed(a) != flip_a, plan->f(b), plan->transposed(b) != flip_b, plan->f(at), m, n, kk,
+                         ws >= 0 ? plan->f(static_cast<uint32_t>(ws)) : nullptr, plan->d_status);
+        });
+        l.flop = 2 * m * n * kk;
+    }
+
     void schedule_attention(uint32_t at) {
         const Node& nd = node(at);
         msx_plan* plan = P;
@@ -724,15 +744,26 @@ struct Scheduler {
         shape.head_dim = static_cast<uint32_t>(qt.shape[1] / nd.heads);
         if (shape.k_len > 512) unsupported(nd, "more than 512 keys per sequence");
         if (shape.head_dim > 128) unsupported(nd, "a head wider than 128");
+        const bool simt = (P->flags & MSX_PLAN_EXACT_MATMUL) != 0;
+        const uint64_t pair_flop = 2ull * shape.batch * shape.q_len * shape.k_len * shape.heads * shape.head_dim;
         if (nd.op == Op::Attention) {
-            Launch& l = emit("attention_forward", nd, {q, kk, v, mask}, {at}, [=](cudaStream_t s) {
-                k::attention_forward(s, plan->f(q), plan->f(kk), plan->f(v), plan->f(mask), plan->f(at), shape);
-            });
-            l.flop = 4ull * shape.batch * shape.q_len * shape.k_len * shape.heads * shape.head_dim;
+            if (simt) {
+                Launch& l = emit("attention_forward", nd, {q, kk, v, mask}, {at}, [=](cudaStream_t s) {
+                    k::attention_forward(s, plan->f(q), plan->f(kk), plan->f(v), plan->f(mask), plan->f(at), shape);
+                });
+                l.flop = 2 * pair_flop;
+            } else {
+                uint32_t probs = scratch(k::attention_tc_scratch_floats(shape) * 4);
+                Launch& l = emit("attention_forward", nd, {q, kk, v, mask}, {at, probs}, [=](cudaStream_t s) {
+                    k::attention_tc_forward(s, plan->f(q), plan->f(kk), plan->f(v), plan->f(mask), plan->f(at), plan->f(probs), shape,
+                                            plan->d_status);
+                });
+                l.flop = 2 * pair_flop;
+            }
             return;
         }
-        // The gradient ops of one attention read the same five operands: one statistics pass
-        // (inside grad-q) serves all three.
+        // The gradient ops of one attention read the same five operands: one launch group
+        // recomputes the probabilities once for all three.
         uint32_t g = pos(nd.operands[4]);
         int dq = -1, dk = -1, dv = -1;
         for (uint32_t u : users[g]) {
@@ -750,9 +781,24 @@ struct Scheduler {
                 s.kind = Slot::Arena;
                 s.bytes = node(static_cast<uint32_t>(t)).ty.count() * 4;
             }
-        uint32_t stats = scratch(k::attention_stats_floats(shape) * 4);
         std::vector<uint32_t> reads = {q, kk, v, mask, g};
-        uint64_t pair_flop = 2ull * shape.batch * shape.q_len * shape.k_len * shape.heads * shape.head_dim;
+        if (!simt) {
+            uint32_t probs = scratch(k::attention_tc_scratch_floats(shape) * 4);
+            uint32_t dprobs = scratch(k::attention_tc_scratch_floats(shape) * 4);
+            std::vector<uint32_t> writes = {probs, dprobs};
+            for (int t : {dq, dk, dv})
+                if (t >= 0) writes.push_back(static_cast<uint32_t>(t));
+            Launch& l = emit("attention_backward", nd, reads, writes, [=](cudaStream_t s) {
+                k::attention_tc_backward(s, plan->f(q), plan->f(kk), plan->f(v), plan->f(mask), plan->f(g),
+                                         dq >= 0 ? plan->f(static_cast<uint32_t>(dq)) : nullptr,
+                                         dk >= 0 ? plan->f(static_cast<uint32_t>(dk)) : nullptr,
+                                         dv >= 0 ? plan->f(static_cast<uint32_t>(dv)) : nullptr, plan->f(probs), plan->f(dprobs), shape,
+                                         plan->d_status);
+            });
+            l.flop = pair_flop * (1 + (dv >= 0) + ((dq >= 0 || dk >= 0) ? 1 : 0) + (dq >= 0) + (dk >= 0));
+            return;
+        }
+        uint32_t stats = scratch(k::attention_stats_floats(shape) * 4);
         {
             std::vector<uint32_t> writes = {stats};
             if (dq >= 0) writes.push_back(static_cast<uint32_t>(dq));
@@ -980,9 +1026,11 @@ int wait_all(msx_plan* P, uint32_t timeout_ms) {
     int slot = static_cast<int>((P->steps - 1) % kStagingSlots);
     int rc = wait_event(P->slot_done[slot], timeout_ms == 0 ? 600000u : timeout_ms);
     if (rc != MSX_OK) return rc;
-    if (*P->pinned_status & 1u) {
+    if (*P->pinned_status) {
+        uint32_t bits = *P->pinned_status;
         *P->pinned_status = 0;
         cuda_ok(cudaMemsetAsync(P->d_status, 0, 4, P->stream), "cudaMemsetAsync");
+        if (bits & 2u) throw StatusError(MSX_TIMEOUT, "a bounded wait inside the tensor-core matmul ran out; the step's results are not valid");
         throw StatusError(MSX_BAD_INPUT, "an embedding id computed on the device is outside its table");
     }
     return MSX_OK;
@@ -1411,6 +1459,26 @@ int msx_elapsed_ms(msx_plan* plan, double* total_ms, uint64_t* steps) {
         return MSX_OK;
     });
 }
+
+int msx_op_matmul(const float* a, int a_transposed, const float* b, int b_transposed, float* c, uint64_t m, uint64_t n, uint64_t k,
+                  float* workspace, uint64_t workspace_floats, uint32_t* status, void* stream, int exact) {
+    if (!a || !b || !c) return MSX_BAD_ARGUMENT;
+    return guarded(nullptr, [&]() -> int {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        if (exact) {
+            k::matmul(s, a, a_transposed != 0, b, b_transposed != 0, c, m, n, k);
+            return MSX_OK;
+        }
+        uint64_t need = k::matmul_tc_plan(m, n, k).workspace_floats;
+        if (need > workspace_floats || (need && !workspace) || !status)
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_op_matmul: the tensor-core kernel needs " + std::to_string(need) +
+                                                    " workspace floats and a status word");
+        k::matmul_tc(s, a, a_transposed != 0, b, b_transposed != 0, c, m, n, k, workspace, status);
+        return MSX_OK;
+    });
+}
+
+uint64_t msx_op_matmul_workspace(uint64_t m, uint64_t n, uint64_t k) { return k::matmul_tc_plan(m, n, k).workspace_floats; }
 
 uint64_t msx_schedule_describe(const char* ir_text, char* out, uint64_t capacity) {
     if (!ir_text) return 0;

@@ -45,11 +45,11 @@ class ProgramText:
         return "\n".join(self.params + self.lines + self.outputs) + "\n"
 
 
-def run_both(device, text, inputs, params=(), outputs=(), seed=None):
+def run_both(device, text, inputs, params=(), outputs=(), seed=None, flags=M.PLAN_NO_GRAPH | M.PLAN_EXACT_MATMUL):
     """Evaluates `text` on the oracle and on the GPU; returns [(oracle, gpu)] per output id,
     `outputs` being (value id, element count) pairs."""
     session = oracle_lib.Session(text)
-    plan = M.Plan(device, text, seed=seed or 0, flags=M.PLAN_NO_GRAPH)
+    plan = M.Plan(device, text, seed=seed or 0, flags=flags)
     try:
         for name, value in inputs.items():
             session.set_input(name, value)

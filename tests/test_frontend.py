@@ -85,7 +85,7 @@ def test_bert_tiny_step_schedule():
     kernels = [l.split()[1] for l in listing.strip().splitlines()[:-1]]
     assert kernels.count("adamw_multi_tensor") == 1 and kernels[-1] == "adamw_multi_tensor"
     assert "transpose" not in kernels
-    assert kernels.count("attention_forward") == 2 and kernels.count("attention_grad_q") == 2 and kernels.count("attention_grad_kv") == 2
+    assert kernels.count("attention_forward") == 2 and kernels.count("attention_backward") == 2
     assert kernels.count("matmul") == 42
     assert "[4096, 30522]" not in listing
     assert len(kernels) < 140

@@ -49,6 +49,50 @@ def test_matmul_is_the_ascending_k_fma_chain_bit_for_bit(device, m, k, n, form):
     assert_bits_equal(gpu, cpu, "matmul %s %dx%dx%d" % (form, m, k, n))
 
 
+def matmul_program(form, m, k, n, r):
+    p = ProgramText()
+    if form == "nn":
+        a = p.input("a", "f32", [m, k]); b = p.input("b", "f32", [k, n])
+        out = p.op("MatMul", [m, n], [a, b])
+        feed = {"a": values(r, m, k), "b": values(r, k, n)}
+        am, bm = feed["a"], feed["b"]
+    elif form == "tn":
+        a = p.input("a", "f32", [k, m]); b = p.input("b", "f32", [k, n])
+        at = p.op("Transpose", [m, k], [a])
+        out = p.op("MatMul", [m, n], [at, b])
+        feed = {"a": values(r, k, m), "b": values(r, k, n)}
+        am, bm = feed["a"].T, feed["b"]
+    elif form == "nt":
+        a = p.input("a", "f32", [m, k]); b = p.input("b", "f32", [n, k])
+        bt = p.op("Transpose", [k, n], [b])
+        out = p.op("MatMul", [m, n], [a, bt])
+        feed = {"a": values(r, m, k), "b": values(r, n, k)}
+        am, bm = feed["a"], feed["b"].T
+    else:  # tt
+        a = p.input("a", "f32", [k, m]); b = p.input("b", "f32", [n, k])
+        at = p.op("Transpose", [m, k], [a]); bt = p.op("Transpose", [k, n], [b])
+        out = p.op("MatMul", [m, n], [at, bt])
+        feed = {"a": values(r, k, m), "b": values(r, n, k)}
+        am, bm = feed["a"].T, feed["b"].T
+    p.output(out)
+    return p.text(), feed, out, am, bm
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 32, 128), (128, 64, 64), (8, 4, 1), (64, 784, 128), (130, 129, 67), (300, 1000, 40),
+                                   (832, 128, 1002), (256, 4096, 128), (70, 3003, 130), (1, 1, 1)])
+@pytest.mark.parametrize("form", ["nn", "tn", "nt", "tt"])
+def test_tensor_core_matmul_within_the_kernel_tolerance(device, m, k, n, form):
+    """3xTF32 on tcgen05: every storage form, tile tails in m, n and k, unaligned rows (no
+    16-byte loads), and k split across CTAs; |g - c| <= 1e-5 + 1e-4 r with r = sum |a||b|."""
+    r = rng(m * 7 + k * 3 + n)
+    text, feed, out, am, bm = matmul_program(form, m, k, n, r)
+    [(cpu, gpu)] = run_both(device, text, feed, outputs=[(out, m * n)], flags=M.PLAN_NO_GRAPH)
+    terms = (np.abs(am.astype(np.float64)) @ np.abs(bm.astype(np.float64))).reshape(-1)
+    assert_kernel_close(gpu, cpu, scale=terms, what="matmul_tc %s %dx%dx%d" % (form, m, k, n))
+    # 3xTF32 keeps about 21 bits of every product: far inside the tolerance.
+    assert np.abs(gpu.astype(np.float64) - cpu).max() <= 4e-6 * max(terms.max(), 1e-30)
+
+
 def test_transposed_matmul_result_is_the_swapped_matmul(device):
     """Transpose(MatMul(A^T, G)) is scheduled as one matmul with its operands swapped."""
     r = rng(5)
@@ -200,8 +244,9 @@ def test_softmax_and_its_gradient(device):
         assert_kernel_close(gpu, cpu, scale=1.0 / k, what="softmax")
 
 
+@pytest.mark.parametrize("tensor_cores", [False, True])
 @pytest.mark.parametrize("batch,q_len,k_len,heads,d", [(3, 40, 40, 2, 16), (2, 128, 128, 2, 64), (2, 7, 33, 1, 8), (1, 512, 512, 1, 64)])
-def test_attention_and_its_three_gradients(device, batch, q_len, k_len, heads, d):
+def test_attention_and_its_three_gradients(device, batch, q_len, k_len, heads, d, tensor_cores):
     r = rng(batch * q_len + d)
     h = heads * d
     p = ProgramText()
@@ -223,9 +268,10 @@ def test_attention_and_its_three_gradients(device, batch, q_len, k_len, heads, d
             "mask": m, "g": values(r, batch * q_len, h)}
     text = p.text()
     listing = M.schedule_describe(text)
-    assert listing.count("attention_grad_q") == 1 and listing.count("attention_grad_kv") == 1
+    assert listing.count("attention_forward") == 1 and listing.count("attention_backward") == 1
+    flags = M.PLAN_NO_GRAPH | (0 if tensor_cores else M.PLAN_EXACT_MATMUL)
     res = run_both(device, text, feed, outputs=[(out, batch * q_len * h), (dq, batch * q_len * h),
-                                                 (dk, batch * k_len * h), (dv, batch * k_len * h)])
+                                                 (dk, batch * k_len * h), (dv, batch * k_len * h)], flags=flags)
     for (cpu, gpu), name in zip(res, ["attention", "grad_q", "grad_k", "grad_v"]):
         assert_kernel_close(gpu, cpu, scale=np.abs(cpu).max(), what=name)
     masked_rows = np.repeat(m.reshape(-1) == 0.0, h).reshape(-1)
