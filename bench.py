@@ -163,6 +163,12 @@ def main():
     device = M.Device(local)
     run = M.Training(device, source, masked)
     plan = run.step_plan
+    if world > 1:
+        # torch.distributed carries the communicator id and the barriers; the gradient
+        # all-reduces are the library's own NCCL calls.
+        ids = [M.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        run.comm_init(rank, world, ids[0], cfg["rows"])
     stats = plan.stats()
     batch_of = lambda k: synthetic.mlm_batch(k, vocab=cfg["vocab"], seq=cfg["seq"], batch=cfg["batch"],
                                              row_offset=rank * cfg["rows"])
@@ -262,6 +268,7 @@ def main():
             "tokens_per_sec": world * cfg["rows"] * 1e3 / resident_ms,
             "config": {"workload": args.config, "global_batch": cfg["batch"] * world, "seq_len": cfg["seq"], "vocab": cfg["vocab"],
                        "masked_rows": masked, "parallelism": "dp%d" % world,
+                       "gradient_buckets": int(M.lib().msx_comm_bucket_count(plan.h)),
                        "l2": "each step streams %.0f MB of intermediates (> 126 MB L2)" % (stats["algorithmic_bytes_per_step"] / 1e6)},
             "clocks": clocks,
             "e2e": {"value": world * 1e3 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,

@@ -168,6 +168,11 @@ int msx_elapsed_ms(msx_plan* plan, double* total_ms, uint64_t* steps);
  * the caller. */
 int msx_comm_unique_id(void* unique_id_128);
 int msx_comm_init(msx_plan* plan, int rank, int world, const void* unique_id_128);
+/* Lets `plan` (a forward plan) use the communicator of `owner` for its loss reductions; `owner`
+ * must outlive it, and the two must not run concurrently. */
+int msx_comm_share(msx_plan* plan, msx_plan* owner);
+/* How many all-reduces one step issues for its gradients (about 25 MB each). */
+uint32_t msx_comm_bucket_count(const msx_plan* plan);
 
 /* ---- The training run above the plan -------------------------------------------------------
  *
@@ -192,6 +197,13 @@ uint64_t msx_training_steps(const msx_training* training);   /* `steps` of the t
 uint64_t msx_training_seed(const msx_training* training);
 /* The message of the last failure of a msx_training_* call on `training`. */
 const char* msx_training_last_error(const msx_training* training);
+
+/* Makes the run one rank of a data-parallel job: joins the step plan to the communicator
+ * (msx_comm_init), lets the forward plan use it, and offsets the dropout element indices by the
+ * rows of the lower ranks (`rows_per_rank` rows of the leading dimension each), so that the
+ * masks are those of one device running the whole batch. Call before the first step. */
+int msx_training_comm_init(msx_training* training, int rank, int world, const void* unique_id_128,
+                           uint64_t rows_per_rank);
 
 /* Sets one declared `input` or `target` of the batch for the steps that follow (the dense feed
  * of train/data.rs:14-35; block k of a `--data` file is what the caller passes before step k). */

@@ -72,6 +72,9 @@ SIGNATURES = {
     "msx_elapsed_ms": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "msx_comm_unique_id": (C.c_int, [_P]),
     "msx_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P]),
+    "msx_comm_bucket_count": (C.c_uint32, [_P]),
+    "msx_comm_share": (C.c_int, [_P, _P]),
+    "msx_training_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_uint64]),
     "msx_training_create": (C.c_int, [_P, C.c_char_p, C.c_uint64, C.c_uint32, C.POINTER(_P)]),
     "msx_training_destroy": (None, [_P]),
     "msx_training_step_plan": (_P, [_P]),
@@ -132,6 +135,15 @@ def compile_mspec(source, which="step", masked_rows=0):
 def schedule_describe(ir_text):
     """The kernel launches the backend schedules for a program, one per line; needs no GPU."""
     return _text(lambda buf, cap: lib().msx_schedule_describe(ir_text.encode(), buf, cap))
+
+
+def comm_unique_id():
+    """128 bytes that name a new data-parallel job; rank 0 makes them, every rank passes them on."""
+    buf = C.create_string_buffer(128)
+    rc = lib().msx_comm_unique_id(buf)
+    if rc != OK:
+        raise MsxError(rc, lib().msx_last_error(None).decode())
+    return buf.raw
 
 
 def _host(array):
@@ -216,6 +228,11 @@ class Plan:
     def set_shard(self, rows_before, global_rows):
         self.device.check(lib().msx_set_shard(self.h, rows_before, global_rows))
 
+    def comm_init(self, rank, world, unique_id):
+        """Joins this plan to a data-parallel job; `unique_id` is the 128 bytes of comm_unique_id()."""
+        buf = C.create_string_buffer(bytes(unique_id), 128)
+        self.device.check(lib().msx_comm_init(self.h, rank, world, buf))
+
     def run(self):
         self.device.check(lib().msx_run(self.h))
 
@@ -276,6 +293,10 @@ class Training:
         if self.h:
             lib().msx_training_destroy(self.h)
             self.h = None
+
+    def comm_init(self, rank, world, unique_id, rows_per_rank):
+        buf = C.create_string_buffer(bytes(unique_id), 128)
+        self.check(lib().msx_training_comm_init(self.h, rank, world, buf, rows_per_rank))
 
     def set_input(self, name, array):
         a = _host(array)

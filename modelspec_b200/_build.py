@@ -13,6 +13,8 @@ SOURCES = ["cuda/pointwise.cu", "cuda/reduce.cu", "cuda/rowwise.cu", "cuda/embed
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-fmad=false", "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function"]
+# Extra defines for tuning builds, e.g. MSX_NVCC_DEFINES="-DMSX_TC_TRACE".
+NVCC_FLAGS += os.environ.get("MSX_NVCC_DEFINES", "").split()
 
 
 def _obj(src):

@@ -1,10 +1,10 @@
 // matmul on the 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory,
 // f32 operands as a 3xTF32 split (tolerance class).
 //
-// Each f32 operand x is split into hi = tf32(x) and lo = tf32(x - hi) (both round-to-nearest,
-// cvt.rna), and a product is summed as lo*hi + hi*lo + hi*hi in the f32 accumulator; the dropped
-// lo*lo term and the two roundings leave about 2^-21 of each |a||b| term, three orders below the
-// kernel tolerance 1e-5 + 1e-4 r. The exact kernel (gemm.cu) stays for bit-level parity runs.
+// Each f32 operand x is split into hi (its top 11 significant bits) and lo = x - hi, and a
+// product is summed as lo*hi + hi*lo + hi*hi in the f32 accumulator; the dropped lo*lo term and
+// the bits of lo below tf32 leave about 2^-20 of each |a||b| term, two orders below the kernel
+// tolerance 1e-5 + 1e-4 r. The exact kernel (gemm.cu) stays for bit-level parity runs.
 //
 // One CTA computes a 128 x BN tile (BN = 64 or 128) over a range of 32-deep k blocks:
 //   warps 0-7  load the A and B blocks from global memory, split them and store hi and lo in the
@@ -56,6 +56,15 @@ struct TcArgs {
     uint32_t* status;
 };
 
+#ifdef MSX_TC_TRACE
+// Phase timestamps of the first 16 CTAs, for tuning builds only.
+__device__ long long g_trace[16][16];
+#define TRACE(slot) do { if (blockIdx.x + blockIdx.y * gridDim.x + blockIdx.z * gridDim.x * gridDim.y < 16) \
+    g_trace[blockIdx.x + blockIdx.y * gridDim.x + blockIdx.z * gridDim.x * gridDim.y][slot] = clock64(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -84,12 +93,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     atomicOr(status, 2u);
     return false;
-}
-
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
 }
 
 // The shared-memory matrix descriptor of tcgen05 (version 1): start address, leading and stride
@@ -134,19 +137,32 @@ __device__ __forceinline__ uint32_t mn_major_offset(uint32_t krow, uint32_t c) {
 
 __device__ __forceinline__ float4 load4(const float* __restrict__ p, uint64_t index, uint32_t valid, bool vec) {
     // `valid` = how many of the 4 elements from `index` are inside the matrix (0..4).
-    if (valid == 4 && vec) return *reinterpret_cast<const float4*>(p + index);
+    // Volatile asm keeps every load where it is written: the prefetch depth is the point, and
+    // the compiler otherwise sinks the loads to their first use.
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (valid > 0) v.x = p[index];
-    if (valid > 1) v.y = p[index + 1];
-    if (valid > 2) v.z = p[index + 2];
-    if (valid > 3) v.w = p[index + 3];
+    const float* at = p + index;
+    if (valid == 4 && vec) {
+        asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(at));
+        return v;
+    }
+    if (valid > 0) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v.x) : "l"(at));
+    if (valid > 1) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v.y) : "l"(at + 1));
+    if (valid > 2) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v.z) : "l"(at + 2));
+    if (valid > 3) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v.w) : "l"(at + 3));
     return v;
 }
 
+// hi = x with the 13 mantissa bits below tf32 cleared (an exact tf32, whatever rounding the tensor
+// core would apply to a wider value), lo = x - hi exactly (at most 13 significant bits, below
+// 2^-10 |x|). The tensor core keeps 11 significant bits of lo, so x is represented to about
+// 2^-21 |x|. One logic op and one subtraction per element: the split must not cost more than
+// the MMAs it feeds.
+__device__ __forceinline__ float top_tf32(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+
 __device__ __forceinline__ void store_split(char* hi, char* lo, uint32_t offset, float4 v) {
     float4 h, l;
-    h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
-    l.x = to_tf32(v.x - h.x); l.y = to_tf32(v.y - h.y); l.z = to_tf32(v.z - h.z); l.w = to_tf32(v.w - h.w);
+    h.x = top_tf32(v.x); h.y = top_tf32(v.y); h.z = top_tf32(v.z); h.w = top_tf32(v.w);
+    l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
     *reinterpret_cast<float4*>(hi + offset) = h;
     *reinterpret_cast<float4*>(lo + offset) = l;
 }
@@ -166,6 +182,7 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 9);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) TRACE(0);
     const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const uint32_t kblocks_total = (args.k + BK - 1) / BK;
     const bool batched = args.batch_inner != 0;
@@ -191,55 +208,64 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    if (tid == 0) TRACE(1);
 
     if (warp < 8) {
         // ---- loaders: global -> (hi, lo) -> swizzled shared memory ---------------------------
         const float* __restrict__ a = args.a + z_outer * args.a_outer + z_inner * args.a_inner;
         const float* __restrict__ b = args.b + z_outer * args.b_outer + z_inner * args.b_inner;
         bool alive = true;
-        for (uint32_t kb = 0; kb < kblocks && alive; ++kb) {
-            const uint32_t stage = kb % STAGES, round = kb / STAGES;
+        constexpr int A_CHUNKS = BM * BK / 4 / LOADER_THREADS, B_CHUNKS = BN * BK / 4 / LOADER_THREADS;
+        // Where this thread's chunks sit in a block does not depend on the block: the tile
+        // coordinates and the shared-memory offsets are computed once.
+        uint32_t a_row[A_CHUNKS], a_col[A_CHUNKS], aoff[A_CHUNKS], b_row[B_CHUNKS], b_col[B_CHUNKS], boff[B_CHUNKS];
+#pragma unroll
+        for (int i = 0; i < A_CHUNKS; ++i) {
+            uint32_t q = tid + i * LOADER_THREADS;
+            if (A_T) { a_row[i] = q >> 5; a_col[i] = (q & 31u) * 4; aoff[i] = mn_major_offset(q >> 5, q & 31u); }      // (k, m)
+            else     { a_row[i] = q >> 3; a_col[i] = (q & 7u) * 4;  aoff[i] = k_major_offset(q >> 3, q & 7u); }        // (m, k)
+        }
+#pragma unroll
+        for (int i = 0; i < B_CHUNKS; ++i) {
+            uint32_t q = tid + i * LOADER_THREADS;
+            if (B_T) { b_row[i] = q >> 3; b_col[i] = (q & 7u) * 4; boff[i] = k_major_offset(q >> 3, q & 7u); }         // (n, k)
+            else     { b_row[i] = q / (BN / 4); b_col[i] = (q % (BN / 4)) * 4; boff[i] = mn_major_offset(q / (BN / 4), q % (BN / 4)); }  // (k, n)
+        }
+        auto fetch = [&](uint32_t kb, float4 (&av)[A_CHUNKS], float4 (&bv)[B_CHUNKS]) {
             const uint32_t k0 = (kb_begin + kb) * BK;
-            char* a_hi = tiles + stage * Smem<BN>::STAGE_BYTES;
-            char* a_lo = a_hi + Smem<BN>::A_BYTES;
-            char* b_hi = a_lo + Smem<BN>::A_BYTES;
-            char* b_lo = b_hi + Smem<BN>::B_BYTES;
-            constexpr int A_CHUNKS = BM * BK / 4 / LOADER_THREADS, B_CHUNKS = BN * BK / 4 / LOADER_THREADS;
-            float4 av[A_CHUNKS], bv[B_CHUNKS];
-            uint32_t aoff[A_CHUNKS], boff[B_CHUNKS];
 #pragma unroll
             for (int i = 0; i < A_CHUNKS; ++i) {
-                uint32_t q = tid + i * LOADER_THREADS;
-                if (A_T) {  // stored [k, m]: 32 chunks of 4 consecutive m per k row
-                    uint32_t krow = q >> 5, c = q & 31u, gk = k0 + krow, gm = m0 + c * 4;
+                if (A_T) {  // stored [k, m]: 4 consecutive m of one k row
+                    uint32_t gk = k0 + a_row[i], gm = m0 + a_col[i];
                     uint32_t valid = gk < args.k ? in_range(gm, args.m) : 0u;
                     av[i] = load4(a, static_cast<uint64_t>(gk) * args.lda + gm, valid, args.a_vec);
-                    aoff[i] = mn_major_offset(krow, c);
-                } else {    // stored [m, k]: 8 chunks of 4 consecutive k per row
-                    uint32_t row = q >> 3, c16 = q & 7u, gm = m0 + row, gk = k0 + c16 * 4;
+                } else {    // stored [m, k]: 4 consecutive k of one row
+                    uint32_t gm = m0 + a_row[i], gk = k0 + a_col[i];
                     uint32_t valid = gm < args.m ? in_range(gk, args.k) : 0u;
                     av[i] = load4(a, static_cast<uint64_t>(gm) * args.lda + gk, valid, args.a_vec);
-                    aoff[i] = k_major_offset(row, c16);
                 }
             }
 #pragma unroll
             for (int i = 0; i < B_CHUNKS; ++i) {
-                uint32_t q = tid + i * LOADER_THREADS;
                 if (B_T) {  // stored [n, k]
-                    uint32_t row = q >> 3, c16 = q & 7u, gn = n0 + row, gk = k0 + c16 * 4;
+                    uint32_t gn = n0 + b_row[i], gk = k0 + b_col[i];
                     uint32_t valid = gn < args.n ? in_range(gk, args.k) : 0u;
                     bv[i] = load4(b, static_cast<uint64_t>(gn) * args.ldb + gk, valid, args.b_vec);
-                    boff[i] = k_major_offset(row, c16);
                 } else {    // stored [k, n]
-                    uint32_t krow = q / (BN / 4), c = q % (BN / 4), gk = k0 + krow, gn = n0 + c * 4;
+                    uint32_t gk = k0 + b_row[i], gn = n0 + b_col[i];
                     uint32_t valid = gk < args.k ? in_range(gn, args.n) : 0u;
                     bv[i] = load4(b, static_cast<uint64_t>(gk) * args.ldb + gn, valid, args.b_vec);
-                    boff[i] = mn_major_offset(krow, c);
                 }
             }
+        };
+        auto deposit = [&](uint32_t kb, const float4 (&av)[A_CHUNKS], const float4 (&bv)[B_CHUNKS]) -> bool {
+            const uint32_t stage = kb % STAGES, round = kb / STAGES;
+            char* a_hi = tiles + stage * Smem<BN>::STAGE_BYTES;
+            char* a_lo = a_hi + Smem<BN>::A_BYTES;
+            char* b_hi = a_lo + Smem<BN>::A_BYTES;
+            char* b_lo = b_hi + Smem<BN>::B_BYTES;
             // The stage is free once the MMAs that read its previous contents have completed.
-            alive = mbar_wait(smem_u32(&bars[STAGES + stage]), (round & 1u) ^ 1u, abort_flag, args.status);
-            if (!alive) break;
+            if (!mbar_wait(smem_u32(&bars[STAGES + stage]), (round & 1u) ^ 1u, abort_flag, args.status)) return false;
 #pragma unroll
             for (int i = 0; i < A_CHUNKS; ++i) store_split(a_hi, a_lo, aoff[i], av[i]);
 #pragma unroll
@@ -247,13 +273,32 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
             // Make the generic-proxy stores visible to the tensor core's async-proxy reads.
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(smem_u32(&bars[stage]));
+            if (tid == 0 && kb < 4) TRACE(2 + kb);
+            return true;
+        };
+        // Three register sets: the loads of blocks kb + 1 and kb + 2 are in flight while block kb is
+        // split and stored. A global load takes about 2,500 cycles to come back here and a block
+        // about 1,000 to deposit, so two blocks of prefetch cover it.
+        float4 av0[A_CHUNKS], bv0[B_CHUNKS], av1[A_CHUNKS], bv1[B_CHUNKS], av2[A_CHUNKS], bv2[B_CHUNKS];
+        if (kblocks > 0) fetch(0, av0, bv0);
+        if (kblocks > 1) fetch(1, av1, bv1);
+        for (uint32_t kb = 0; kb < kblocks && alive; kb += 3) {
+            if (kb + 2 < kblocks) fetch(kb + 2, av2, bv2);
+            alive = deposit(kb, av0, bv0);
+            if (!alive || kb + 1 >= kblocks) break;
+            if (kb + 3 < kblocks) fetch(kb + 3, av0, bv0);
+            alive = deposit(kb + 1, av1, bv1);
+            if (!alive || kb + 2 >= kblocks) break;
+            if (kb + 4 < kblocks) fetch(kb + 4, av1, bv1);
+            alive = deposit(kb + 2, av2, bv2);
         }
         // ---- epilogue: tensor memory -> registers -> global -----------------------------------
         if (alive && kblocks > 0) alive = mbar_wait(smem_u32(&bars[2 * STAGES]), 0, abort_flag, args.status);
         alive = __all_sync(0xffffffffu, alive);  // tcgen05.ld is warp-wide: decide as a warp
+        if (tid == 0) TRACE(6);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t row = (warp & 3u) * 32 + lane, gm = m0 + row;
         const uint32_t col_half = warp >> 2;  // warps 0-3: first half of the columns, 4-7: second
+        float* staging = reinterpret_cast<float*>(tiles) + warp * (32 * 33);
         float* __restrict__ out = batched ? args.c + z_outer * args.c_outer + z_inner * args.c_inner
                                           : args.c + static_cast<uint64_t>(blockIdx.z) * args.m * args.ldc;
 #pragma unroll
@@ -277,19 +322,20 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = 0u;  // an empty k range contributes zeros
             }
-            if (gm < args.m) {
-                float* dst = out + static_cast<uint64_t>(gm) * args.ldc + n0 + col;
-                if (args.c_vec && n0 + col + 32 <= args.n) {
+            // Through shared memory (the stages are free once the accumulator is ready), so that
+            // a warp writes whole rows: 32 consecutive columns per store, whatever the row pitch.
+            // Lane = row on the way in, lane = column on the way out; pitch 33 keeps both
+            // conflict-free. `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]) + 0.0f, __uint_as_float(r[j + 1]) + 0.0f,
-                                                                            __uint_as_float(r[j + 2]) + 0.0f, __uint_as_float(r[j + 3]) + 0.0f);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (n0 + col + j < args.n) dst[j] = __uint_as_float(r[j]) + 0.0f;
-                }
+            for (int j = 0; j < 32; ++j) staging[lane * 33 + j] = __uint_as_float(r[j]) + 0.0f;
+            __syncwarp();
+            const uint32_t gn = n0 + col + lane;
+            if (gn < args.n) {
+                float* dst = out + static_cast<uint64_t>(m0 + (warp & 3u) * 32) * args.ldc + gn;
+                const uint32_t rows_here = m0 + (warp & 3u) * 32 < args.m ? min(32u, args.m - (m0 + (warp & 3u) * 32)) : 0u;
+                for (uint32_t rr = 0; rr < rows_here; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = staging[rr * 33 + lane];
             }
+            __syncwarp();
         }
     } else {
         // ---- the MMA warp: one thread issues, the tensor core runs asynchronously ---------------
@@ -324,13 +370,16 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
                     mma_tf32(tmem_base, da_hi, db_hi, idesc, 1u);
                 }
                 mma_commit(smem_u32(&bars[STAGES + stage]));                   // frees the stage when they finish
+                if (kb < 4) TRACE(8 + kb);
                 if (kb + 1 == kblocks) mma_commit(smem_u32(&bars[2 * STAGES]));  // and, at the end, the accumulator
             }
             __syncwarp();
         }
     }
+    if (tid == 0) TRACE(7);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (tid == 0) TRACE(12);
     if (warp == 8) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(static_cast<uint32_t>(BN)) : "memory");
     }
@@ -358,6 +407,12 @@ template <int BN> void launch_forms(cudaStream_t s, const TcArgs& args, dim3 gri
     else if (b_t) launch<BN, false, true>(s, args, grid);
     else launch<BN, false, false>(s, args, grid);
 }
+
+#ifdef MSX_TC_TRACE
+}  // namespace
+extern "C" void msx_tc_trace_read(long long* out) { cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 256); }
+namespace {
+#endif
 
 bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 

@@ -60,12 +60,17 @@ void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t
 void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, uint64_t rows, uint64_t k);
 // Row losses max + ln(sum exp(x - max)) - x[label] into row_loss[rows], then
 // loss = sum w * l / sum w (f64 sums, one rounding; 0 when the weights sum to 0).
+// `global_den`, when not null, is a device float that replaces the weight sum in the division:
+// a data-parallel shard divides its own numerator by the weight sum of the whole batch.
 void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
-                   float* row_loss, double* scratch, float* loss, uint64_t rows, uint64_t v);
+                   float* row_loss, const float* global_den, float* loss, uint64_t rows, uint64_t v);
+// out[0] = f32(sum of the weights in f64).
+void weight_sum(cudaStream_t s, const float* weights, uint64_t rows, float* out);
 // out[n, c] = g * w[n] / f32(sum w) * (softmax(logits[n])[c] - [c == labels[n]]); all 0 when the
-// weights sum to 0. `denominator` is a one-float scratch.
+// weights sum to 0. `denominator` is a one-float scratch the launcher fills with the weight sum,
+// unless `denominator_ready` says the caller already put the (whole-batch) sum there.
 void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
-                        const float* g, double* scratch, float* denominator, float* out, uint64_t rows,
+                        const float* g, bool denominator_ready, float* denominator, float* out, uint64_t rows,
                         uint64_t v);
 
 // ---- embedding (embedding.cu) -----------------------------------------------------------------

@@ -193,7 +193,7 @@ __global__ void cross_entropy_rows_kernel(const float* __restrict__ logits, cons
 
 // loss = sum_n w[n] l[n] / sum_n w[n], both sums in f64 (a tree over the block), one rounding.
 __global__ void cross_entropy_loss_kernel(const float* __restrict__ row_loss, const float* __restrict__ weights,
-                                          uint32_t rows, float* __restrict__ loss) {
+                                          uint32_t rows, const float* __restrict__ global_den, float* __restrict__ loss) {
     __shared__ double shared[33];
     double num = 0.0, den = 0.0;
     for (uint32_t r = threadIdx.x; r < rows; r += blockDim.x) {
@@ -203,6 +203,8 @@ __global__ void cross_entropy_loss_kernel(const float* __restrict__ row_loss, co
     }
     num = block_sum(num, shared);
     den = block_sum(den, shared);
+    // Data parallel: the numerator of this shard over the weight sum of the whole batch.
+    if (global_den) den = static_cast<double>(global_den[0]);
     if (threadIdx.x == 0) loss[0] = den == 0.0 ? 0.0f : static_cast<float>(num / den);
 }
 
@@ -295,25 +297,30 @@ void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, ui
     check_launch("softmax_grad");
 }
 
+void weight_sum(cudaStream_t s, const float* weights, uint64_t rows, float* out) {
+    weight_sum_kernel<<<1, 1024, 0, s>>>(weights, static_cast<uint32_t>(rows), out);
+    check_launch("weight_sum");
+}
+
 void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
-                   float* row_loss, double* scratch, float* loss, uint64_t rows, uint64_t v) {
-    (void)scratch;
+                   float* row_loss, const float* global_den, float* loss, uint64_t rows, uint64_t v) {
     if (rows > 0) {
         cross_entropy_rows_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, row_loss,
                                                                                       static_cast<uint32_t>(v));
         check_launch("cross_entropy");
     }
-    cross_entropy_loss_kernel<<<1, 1024, 0, s>>>(row_loss, weights, static_cast<uint32_t>(rows), loss);
+    cross_entropy_loss_kernel<<<1, 1024, 0, s>>>(row_loss, weights, static_cast<uint32_t>(rows), global_den, loss);
     check_launch("cross_entropy");
 }
 
 void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
-                        const float* g, double* scratch, float* denominator, float* out, uint64_t rows,
+                        const float* g, bool denominator_ready, float* denominator, float* out, uint64_t rows,
                         uint64_t v) {
-    (void)scratch;
     if (rows == 0) return;
-    weight_sum_kernel<<<1, 1024, 0, s>>>(weights, static_cast<uint32_t>(rows), denominator);
-    check_launch("cross_entropy_grad");
+    if (!denominator_ready) {
+        weight_sum_kernel<<<1, 1024, 0, s>>>(weights, static_cast<uint32_t>(rows), denominator);
+        check_launch("cross_entropy_grad");
+    }
     cross_entropy_grad_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, g, denominator,
                                                                                   out, static_cast<uint32_t>(v));
     check_launch("cross_entropy_grad");

@@ -7,6 +7,8 @@
 // inputs, one graph launch and one 4-byte read-back of the loss, all on the plan's stream; the
 // host never waits inside msx_run unless all of its staging slots are still in flight.
 #include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
 
 #include <algorithm>
 #include <chrono>
@@ -46,6 +48,52 @@ struct StatusError : std::runtime_error {
 };
 
 }  // namespace
+
+// NCCL, loaded on first use so that the library has no link-time dependency on it: a
+// single-GPU host never needs it.
+struct NcclApi {
+    void* handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    std::string error;
+
+    bool load() {
+        if (handle) return true;
+        for (const char* name : {"libnccl.so.2", "libnccl.so"}) {
+            handle = dlopen(name, RTLD_NOW | RTLD_LOCAL);
+            if (handle) break;
+        }
+        if (!handle) {
+            error = std::string("cannot load libnccl.so.2: ") + dlerror();
+            return false;
+        }
+        auto sym = [&](const char* n) { return dlsym(handle, n); };
+        GetUniqueId = reinterpret_cast<decltype(GetUniqueId)>(sym("ncclGetUniqueId"));
+        CommInitRank = reinterpret_cast<decltype(CommInitRank)>(sym("ncclCommInitRank"));
+        CommDestroy = reinterpret_cast<decltype(CommDestroy)>(sym("ncclCommDestroy"));
+        AllReduce = reinterpret_cast<decltype(AllReduce)>(sym("ncclAllReduce"));
+        GetErrorString = reinterpret_cast<decltype(GetErrorString)>(sym("ncclGetErrorString"));
+        if (!GetUniqueId || !CommInitRank || !CommDestroy || !AllReduce || !GetErrorString) {
+            error = "libnccl.so.2 lacks an expected symbol";
+            dlclose(handle);
+            handle = nullptr;
+            return false;
+        }
+        return true;
+    }
+};
+static NcclApi g_nccl;
+
+// A contiguous run of gradient bytes that is summed across ranks by one all-reduce, issued on
+// the side stream as soon as the launch that writes its last gradient has been enqueued.
+struct Bucket {
+    uint64_t offset = 0, bytes = 0;  // within the arena
+    int after_launch = -1;
+    cudaEvent_t ready = nullptr, done = nullptr;
+};
 
 struct msx_device {
     int ordinal = 0;
@@ -105,6 +153,21 @@ struct msx_plan {
 
     uint64_t live_nodes = 0, param_bytes = 0;
 
+    // Data parallel (msx_comm_init): rank and size of the job, the communicator, the side stream
+    // the gradient buckets are reduced on, and how gradients combine: summed when the loss divides
+    // by a whole-batch weight sum (cross_entropy), averaged when it divides by a shard's element
+    // count (mse).
+    ncclComm_t comm = nullptr;
+    bool owns_comm = false;
+    int rank = 0, world = 1;
+    cudaStream_t comm_stream = nullptr;
+    std::vector<Bucket> buckets;
+    uint64_t gradient_region_offset = 0, gradient_region_bytes = 0;
+    std::vector<uint32_t> gradient_slots;  // in production order
+    int optimizer_launch = -1;
+    bool average_gradients = false;
+    uint64_t bucket_bytes = 25u << 20;
+
     void* ptr(uint32_t pos) const {
         const Slot& s = slots[pos];
         switch (s.kind) {
@@ -132,6 +195,8 @@ void cuda_ok(cudaError_t e, const char* what) {
     int status = e == cudaErrorMemoryAllocation ? MSX_OUT_OF_MEMORY : MSX_LAUNCH_FAILED;
     throw StatusError(status, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
 }
+
+void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // The scheduler.
@@ -580,6 +645,7 @@ struct Scheduler {
                 uint64_t n = node(a).ty.count();
                 emit("mse", nd, in, {at, tmp}, [=](cudaStream_t s) {
                     k::mse(s, plan->f(a), plan->f(b), n, static_cast<double*>(plan->ptr(tmp)), plan->f(at));
+                    all_reduce(plan, plan->f(at), 1, true, s);  // the mean over equal shards
                 });
                 break;
             }
@@ -671,9 +737,16 @@ struct Scheduler {
             case Op::CrossEntropy: {
                 uint32_t logits = in[0], labels = in[1], weights = in[2];
                 uint64_t r = rows_of(logits), v = cols_of(logits);
-                uint32_t row_loss = scratch(std::max<uint64_t>(r, 1) * 4);
-                emit("cross_entropy", nd, in, {at, row_loss}, [=](cudaStream_t s) {
-                    k::cross_entropy(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(row_loss), nullptr, plan->f(at), r, v);
+                uint32_t row_loss = scratch(std::max<uint64_t>(r, 1) * 4), den = scratch(4);
+                emit("cross_entropy", nd, in, {at, row_loss, den}, [=](cudaStream_t s) {
+                    if (plan->comm) {
+                        // The shard's numerator over the whole batch's weight sum, then summed.
+                        k::weight_sum(s, plan->f(weights), r, plan->f(den));
+                        all_reduce(plan, plan->f(den), 1, false, s);
+                    }
+                    k::cross_entropy(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(row_loss),
+                                     plan->comm ? plan->f(den) : nullptr, plan->f(at), r, v);
+                    all_reduce(plan, plan->f(at), 1, false, s);
                 });
                 break;
             }
@@ -682,8 +755,12 @@ struct Scheduler {
                 uint64_t r = rows_of(logits), v = cols_of(logits);
                 uint32_t den = scratch(4);
                 emit("cross_entropy_grad", nd, in, {at, den}, [=](cudaStream_t s) {
-                    k::cross_entropy_grad(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(g), nullptr, plan->f(den),
-                                          plan->f(at), r, v);
+                    if (plan->comm) {
+                        k::weight_sum(s, plan->f(weights), r, plan->f(den));
+                        all_reduce(plan, plan->f(den), 1, false, s);
+                    }
+                    k::cross_entropy_grad(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(g), plan->comm != nullptr,
+                                          plan->f(den), plan->f(at), r, v);
                 });
                 break;
             }
@@ -884,9 +961,24 @@ void place_arena(msx_plan* P) {
                 slots[r].last = std::max(slots[r].last, static_cast<int>(l));
             }
     }
+    // Gradients live side by side, in the order the step produces them, so that a bucket of
+    // consecutive gradients is one contiguous all-reduce.
+    std::vector<char> is_gradient(slots.size(), 0);
+    P->gradient_slots.clear();
+    for (const msx::Output& o : P->program.outputs)
+        if (o.role == Role::Gradient) {
+            int at = P->program.position(o.value);
+            if (at >= 0 && slots[static_cast<size_t>(at)].kind == Slot::Arena && slots[static_cast<size_t>(at)].first >= 0 &&
+                !is_gradient[static_cast<size_t>(at)]) {
+                is_gradient[static_cast<size_t>(at)] = 1;
+                P->gradient_slots.push_back(static_cast<uint32_t>(at));
+            }
+        }
+    std::stable_sort(P->gradient_slots.begin(), P->gradient_slots.end(),
+                     [&](uint32_t a, uint32_t b) { return slots[a].first < slots[b].first; });
     std::vector<std::vector<uint32_t>> starts(P->launches.size()), ends(P->launches.size());
     for (uint32_t s = 0; s < slots.size(); ++s)
-        if (slots[s].kind == Slot::Arena && slots[s].first >= 0) {
+        if (slots[s].kind == Slot::Arena && slots[s].first >= 0 && !is_gradient[s]) {
             starts[static_cast<size_t>(slots[s].first)].push_back(s);
             if (!slots[s].keep) ends[static_cast<size_t>(slots[s].last)].push_back(s);
             P->unshared_bytes += align_up(slots[s].bytes);
@@ -896,13 +988,49 @@ void place_arena(msx_plan* P) {
         for (uint32_t s : starts[l]) slots[s].offset = free.take(slots[s].bytes);
         for (uint32_t s : ends[l]) free.give(slots[s].offset, slots[s].bytes);
     }
-    P->arena_bytes = std::max<uint64_t>(free.end, kAlign);
+    P->gradient_region_offset = align_up(free.end);
+    uint64_t at = P->gradient_region_offset;
+    for (uint32_t g : P->gradient_slots) {
+        slots[g].offset = at;
+        at += align_up(slots[g].bytes);
+        P->unshared_bytes += align_up(slots[g].bytes);
+    }
+    P->gradient_region_bytes = at - P->gradient_region_offset;
+    P->arena_bytes = std::max<uint64_t>(at, kAlign);
+    for (size_t l = 0; l < P->launches.size(); ++l)
+        if (P->launches[l].kernel == "adamw_multi_tensor" || P->launches[l].kernel == "sgd_multi_tensor") P->optimizer_launch = static_cast<int>(l);
+}
+
+// Cuts the gradient region into buckets of about `bucket_bytes`, each closed by the launch that
+// writes its last gradient.
+void plan_buckets(msx_plan* P) {
+    P->buckets.clear();
+    Bucket open;
+    bool any = false;
+    for (uint32_t g : P->gradient_slots) {
+        const Slot& s = P->slots[g];
+        if (!any) {
+            open = Bucket{};
+            open.offset = s.offset;
+            any = true;
+        }
+        open.bytes = s.offset + align_up(s.bytes) - open.offset;
+        open.after_launch = std::max(open.after_launch, s.first);
+        if (open.bytes >= P->bucket_bytes) {
+            P->buckets.push_back(open);
+            any = false;
+        }
+    }
+    if (any) P->buckets.push_back(open);
 }
 
 void allocate(msx_plan* P, const Scheduler& sched) {
     const Program& prog = P->program;
     cuda_ok(cudaStreamCreateWithFlags(&P->stream, cudaStreamNonBlocking), "cudaStreamCreate");
     cuda_ok(cudaMalloc(&P->arena, P->arena_bytes), "cudaMalloc(arena)");
+    // The gaps between gradients are summed with them across ranks: keep them finite.
+    if (P->gradient_region_bytes)
+        cuda_ok(cudaMemset(P->arena + P->gradient_region_offset, 0, P->gradient_region_bytes), "cudaMemset(gradients)");
     std::vector<char> param_used(prog.params.size(), 0), moment_used(prog.params.size(), 0);
     for (const Slot& s : P->slots) {
         if (s.kind == Slot::Param) param_used[s.index] = 1;
@@ -979,6 +1107,13 @@ void release(msx_plan* P) {
     cudaSetDevice(P->device->ordinal);
     if (P->stream) cudaStreamSynchronize(P->stream);
     if (P->graph) cudaGraphExecDestroy(P->graph);
+    if (P->comm_stream) cudaStreamSynchronize(P->comm_stream);
+    for (Bucket& b : P->buckets) {
+        if (b.ready) cudaEventDestroy(b.ready);
+        if (b.done) cudaEventDestroy(b.done);
+    }
+    if (P->comm && P->owns_comm) g_nccl.CommDestroy(P->comm);
+    if (P->comm_stream) cudaStreamDestroy(P->comm_stream);
     cudaFree(P->arena);
     for (size_t p = 0; p < P->params.size(); ++p) {
         if (P->owns_param[p]) cudaFree(P->params[p]);
@@ -1001,8 +1136,33 @@ void release(msx_plan* P) {
     delete P;
 }
 
+void nccl_ok(ncclResult_t r, const char* what) {
+    if (r != ncclSuccess) throw StatusError(MSX_LAUNCH_FAILED, std::string(what) + ": " + g_nccl.GetErrorString(r));
+}
+
+// Sums (or averages) `count` floats in place across the ranks, on `stream`. A no-op for a plan
+// that is not data parallel.
+void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream_t stream) {
+    if (!P->comm) return;
+    nccl_ok(g_nccl.AllReduce(data, data, count, ncclFloat, average ? ncclAvg : ncclSum, P->comm, stream), "ncclAllReduce");
+}
+
 void enqueue_all(msx_plan* P) {
-    for (const Launch& l : P->launches) l.run(P->stream);
+    for (size_t l = 0; l < P->launches.size(); ++l) {
+        if (P->comm && static_cast<int>(l) == P->optimizer_launch)
+            for (Bucket& b : P->buckets) cuda_ok(cudaStreamWaitEvent(P->stream, b.done, 0), "cudaStreamWaitEvent");
+        P->launches[l].run(P->stream);
+        if (!P->comm) continue;
+        for (Bucket& b : P->buckets) {
+            if (b.after_launch != static_cast<int>(l)) continue;
+            // The bucket's gradients are complete in stream order: reduce them on the side stream
+            // while the rest of backward runs.
+            cuda_ok(cudaEventRecord(b.ready, P->stream), "cudaEventRecord");
+            cuda_ok(cudaStreamWaitEvent(P->comm_stream, b.ready, 0), "cudaStreamWaitEvent");
+            all_reduce(P, reinterpret_cast<float*>(P->arena + b.offset), b.bytes / 4, P->average_gradients, P->comm_stream);
+            cuda_ok(cudaEventRecord(b.done, P->comm_stream), "cudaEventRecord");
+        }
+    }
 }
 
 // Waits for `event` at most `timeout_ms`, polling: never an unbounded wait.
@@ -1513,17 +1673,59 @@ uint64_t msx_schedule_describe(const char* ir_text, char* out, uint64_t capacity
 }
 
 int msx_comm_unique_id(void* unique_id_128) {
-    (void)unique_id_128;
-    g_open_error = "data-parallel communication is not built into this library";
-    return MSX_UNSUPPORTED;
+    if (!unique_id_128) return MSX_BAD_ARGUMENT;
+    return guarded(nullptr, [&]() -> int {
+        static_assert(sizeof(ncclUniqueId) == 128, "the ABI hands a 128-byte id around");
+        if (!g_nccl.load()) throw StatusError(MSX_UNSUPPORTED, g_nccl.error);
+        ncclUniqueId id;
+        nccl_ok(g_nccl.GetUniqueId(&id), "ncclGetUniqueId");
+        std::memcpy(unique_id_128, &id, sizeof id);
+        return MSX_OK;
+    });
 }
 
 int msx_comm_init(msx_plan* plan, int rank, int world, const void* unique_id_128) {
-    (void)rank; (void)world; (void)unique_id_128;
-    if (!plan) return MSX_BAD_ARGUMENT;
-    plan->device->error = "data-parallel communication is not built into this library";
-    return MSX_UNSUPPORTED;
+    if (!plan || !unique_id_128 || world < 1 || rank < 0 || rank >= world) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        if (plan->comm) throw StatusError(MSX_BAD_ARGUMENT, "msx_comm_init: the plan already has a communicator");
+        if (plan->steps) throw StatusError(MSX_BAD_ARGUMENT, "msx_comm_init: call it before the first step");
+        if (!g_nccl.load()) throw StatusError(MSX_UNSUPPORTED, g_nccl.error);
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        ncclUniqueId id;
+        std::memcpy(&id, unique_id_128, sizeof id);
+        nccl_ok(g_nccl.CommInitRank(&plan->comm, world, id, rank), "ncclCommInitRank");
+        plan->owns_comm = true;
+        plan->rank = rank;
+        plan->world = world;
+        cuda_ok(cudaStreamCreateWithFlags(&plan->comm_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        // An mse-style loss divides by the shard's own element count, so gradients are averaged;
+        // a weighted cross_entropy divides by the whole batch's weight sum, so they are summed.
+        plan->average_gradients = true;
+        for (const Node& n : plan->program.nodes)
+            if (n.op == Op::CrossEntropy) plan->average_gradients = false;
+        plan_buckets(plan);
+        for (Bucket& b : plan->buckets) {
+            cuda_ok(cudaEventCreateWithFlags(&b.ready, cudaEventDisableTiming), "cudaEventCreate");
+            cuda_ok(cudaEventCreateWithFlags(&b.done, cudaEventDisableTiming), "cudaEventCreate");
+        }
+        return MSX_OK;
+    });
 }
+
+int msx_comm_share(msx_plan* plan, msx_plan* owner) {
+    if (!plan || !owner) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        if (!owner->comm) throw StatusError(MSX_BAD_ARGUMENT, "msx_comm_share: the other plan has no communicator");
+        if (plan->comm || plan->steps) throw StatusError(MSX_BAD_ARGUMENT, "msx_comm_share: call it once, before the first step");
+        plan->comm = owner->comm;
+        plan->rank = owner->rank;
+        plan->world = owner->world;
+        plan->average_gradients = owner->average_gradients;
+        return MSX_OK;
+    });
+}
+
+uint32_t msx_comm_bucket_count(const msx_plan* plan) { return plan ? static_cast<uint32_t>(plan->buckets.size()) : 0; }
 
 uint64_t msx_compile(const char* source, const char* which, uint64_t masked_rows, char* out, uint64_t capacity) {
     if (!source || !which) return 0;

@@ -165,6 +165,15 @@ uint64_t msx_training_steps(const msx_training* t) { return t ? t->compiled.conf
 uint64_t msx_training_seed(const msx_training* t) { return t ? t->compiled.config.seed : 0; }
 const char* msx_training_last_error(const msx_training* t) { return t ? t->error.c_str() : ""; }
 
+int msx_training_comm_init(msx_training* t, int rank, int world, const void* unique_id_128, uint64_t rows_per_rank) {
+    if (!t || !unique_id_128) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        ok(t, msx_comm_init(t->step, rank, world, unique_id_128));
+        ok(t, msx_comm_share(t->forward, t->step));
+        ok(t, msx_set_shard(t->step, static_cast<uint64_t>(rank) * rows_per_rank, static_cast<uint64_t>(world) * rows_per_rank));
+    });
+}
+
 int msx_training_set_input(msx_training* t, const char* name, const void* host, uint64_t bytes) {
     if (!t || !name || !host) return MSX_BAD_ARGUMENT;
     return guarded(t, [&] {
