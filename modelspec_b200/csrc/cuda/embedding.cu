@@ -42,17 +42,19 @@ __global__ void embedding_kernel(const float* __restrict__ table, const int32_t*
     }
 }
 
-// rank[n] = how many earlier n' hold the same id; count[id] = occurrences of id. One thread per
-// n; the ids before it are staged through shared memory in tiles of 1024.
+// rank[n] = how many earlier n' hold the same id; count[id] = occurrences of id. Four lanes per
+// n, each scanning a quarter of every 1024-id tile of the ids before it, staged through shared
+// memory.
 __global__ void rank_kernel(const int32_t* __restrict__ ids, uint32_t n, uint32_t rows, int32_t* __restrict__ rank,
                             int32_t* __restrict__ count, uint32_t* __restrict__ status) {
     __shared__ int32_t tile[1024];
-    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t per_block = blockDim.x / 4;
+    uint32_t i = blockIdx.x * per_block + threadIdx.x / 4, part = threadIdx.x & 3u;
     int32_t mine = i < n ? ids[i] : -1;
     bool valid = i < n && mine >= 0 && static_cast<uint32_t>(mine) < rows;
-    if (i < n && !valid) atomicOr(status, 1u);
-    // Only ids before the block's last thread matter to anyone in the block.
-    uint32_t block_last = min(n, (blockIdx.x + 1) * blockDim.x);
+    if (i < n && !valid && part == 0) atomicOr(status, 1u);
+    // Only ids before the block's last n matter to anyone in the block.
+    uint32_t block_last = min(n, (blockIdx.x + 1) * per_block);
     int32_t earlier = 0;
     for (uint32_t t0 = 0; t0 < block_last; t0 += 1024) {
         __syncthreads();
@@ -60,8 +62,12 @@ __global__ void rank_kernel(const int32_t* __restrict__ ids, uint32_t n, uint32_
         __syncthreads();
         if (!valid || t0 >= i) continue;
         uint32_t stop = min(i, t0 + 1024u) - t0;
-        for (uint32_t j = 0; j < stop; ++j) earlier += tile[j] == mine ? 1 : 0;
+        // Interleaved quarters keep the four lanes on different banks.
+        for (uint32_t j = part; j < stop; j += 4) earlier += tile[j] == mine ? 1 : 0;
     }
+    earlier += __shfl_xor_sync(0xffffffffu, earlier, 1);
+    earlier += __shfl_xor_sync(0xffffffffu, earlier, 2);
+    if (part != 0) return;
     if (valid) {
         rank[i] = earlier;
         atomicAdd(&count[mine], 1);  // integer: the total does not depend on the order
@@ -70,26 +76,40 @@ __global__ void rank_kernel(const int32_t* __restrict__ ids, uint32_t n, uint32_
     }
 }
 
-// offset[r] = sum of count[0 .. r): one CTA, each thread a contiguous run of rows.
+// offset[r] = sum of count[0 .. r): one CTA of 1024 threads walks the rows 1024 at a time with
+// coalesced loads, a warp-shuffle scan inside each warp and a scan of the 32 warp totals.
 __global__ void offsets_kernel(const int32_t* __restrict__ count, uint32_t rows, int32_t* __restrict__ offset) {
-    __shared__ int32_t sums[1024];
-    uint32_t per = (rows + blockDim.x - 1) / blockDim.x;
-    uint32_t begin = min(rows, threadIdx.x * per), end = min(rows, begin + per);
-    int32_t local = 0;
-    for (uint32_t r = begin; r < end; ++r) local += count[r];
-    sums[threadIdx.x] = local;
+    __shared__ int32_t warp_total[32], warp_prefix[32];
+    __shared__ int32_t carry, chunk_total;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry = 0;
     __syncthreads();
-    // Hillis-Steele inclusive scan over the per-thread sums.
-    for (uint32_t d = 1; d < blockDim.x; d <<= 1) {
-        int32_t add = threadIdx.x >= d ? sums[threadIdx.x - d] : 0;
+    for (uint32_t base = 0; base < rows; base += 1024) {
+        uint32_t r = base + threadIdx.x;
+        int32_t c = r < rows ? count[r] : 0;
+        int32_t inclusive = c;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int32_t up = __shfl_up_sync(0xffffffffu, inclusive, d);
+            if (lane >= static_cast<uint32_t>(d)) inclusive += up;
+        }
+        if (lane == 31) warp_total[warp] = inclusive;
         __syncthreads();
-        sums[threadIdx.x] += add;
+        if (warp == 0) {
+            int32_t t = warp_total[lane], scan = t;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                int32_t up = __shfl_up_sync(0xffffffffu, scan, d);
+                if (lane >= static_cast<uint32_t>(d)) scan += up;
+            }
+            warp_prefix[lane] = scan - t;
+            if (lane == 31) chunk_total = scan;
+        }
         __syncthreads();
-    }
-    int32_t running = sums[threadIdx.x] - local;
-    for (uint32_t r = begin; r < end; ++r) {
-        offset[r] = running;
-        running += count[r];
+        if (r < rows) offset[r] = carry + warp_prefix[warp] + inclusive - c;
+        __syncthreads();
+        if (threadIdx.x == 0) carry += chunk_total;
+        __syncthreads();
     }
 }
 
@@ -100,51 +120,38 @@ __global__ void list_kernel(const int32_t* __restrict__ ids, uint32_t n, const i
     if (i < n && rank[i] >= 0) list[offset[ids[i]] + rank[i]] = static_cast<int32_t>(i);
 }
 
-// One warp per table row: 0 + g[n0] + g[n1] + ... over the row's occurrences in ascending n, the
-// additions in order, the loads ahead of them.
+// One warp per (table row, group of 32 columns), lane = column: 0 + g[n0] + g[n1] + ... over the
+// row's occurrences in ascending n. The additions stay in order; the loads of up to 32
+// occurrences are issued together, so a row hit hundreds of times costs a few memory round
+// trips, not one per occurrence.
 __global__ void scatter_kernel(const float* __restrict__ g, const int32_t* __restrict__ list,
                                const int32_t* __restrict__ offset, const int32_t* __restrict__ count,
                                float* __restrict__ out, uint32_t rows, uint32_t h) {
-    uint64_t row = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    int lane = threadIdx.x & 31;
-    uint64_t warps = (static_cast<uint64_t>(gridDim.x) * blockDim.x) >> 5;
-    for (; row < rows; row += warps) {
-        int32_t c = count[row];
+    const uint32_t groups = (h + 31) / 32;
+    const uint64_t items = static_cast<uint64_t>(rows) * groups;
+    uint64_t item = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * blockDim.x) >> 5;
+    for (; item < items; item += warps) {
+        const uint32_t row = static_cast<uint32_t>(item / groups), col = static_cast<uint32_t>(item % groups) * 32 + lane;
+        const int32_t c = count[row];
         const int32_t* mine = list + offset[row];
-        float* dst = out + row * h;
-        for (uint32_t j0 = 0; j0 < h; j0 += 128) {
-            // Up to four columns per lane at a time, so one pass over the list serves 128 columns.
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            int32_t i = 0;
-            for (; i + 4 <= c; i += 4) {
-                int32_t n0 = mine[i], n1 = mine[i + 1], n2 = mine[i + 2], n3 = mine[i + 3];
-                float v[4][4];
+        const bool in = col < h;
+        float acc = 0.0f;
+        for (int32_t i0 = 0; i0 < c; i0 += 32) {
+            const int32_t entry = i0 + static_cast<int32_t>(lane) < c ? mine[i0 + lane] : 0;
+            const int32_t here = min(32, c - i0);
+            float v[32];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t j = j0 + q * 32 + lane;
-                    bool in = j < h;
-                    v[0][q] = in ? g[static_cast<uint64_t>(n0) * h + j] : 0.0f;
-                    v[1][q] = in ? g[static_cast<uint64_t>(n1) * h + j] : 0.0f;
-                    v[2][q] = in ? g[static_cast<uint64_t>(n2) * h + j] : 0.0f;
-                    v[3][q] = in ? g[static_cast<uint64_t>(n3) * h + j] : 0.0f;
-                }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) acc[q] = (((acc[q] + v[0][q]) + v[1][q]) + v[2][q]) + v[3][q];
-            }
-            for (; i < c; ++i) {
-                int32_t n = mine[i];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t j = j0 + q * 32 + lane;
-                    if (j < h) acc[q] = acc[q] + g[static_cast<uint64_t>(n) * h + j];
-                }
+            for (int e = 0; e < 32; ++e) {
+                const int32_t n = __shfl_sync(0xffffffffu, entry, e);
+                v[e] = (e < here && in) ? g[static_cast<uint64_t>(n) * h + col] : 0.0f;
             }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint32_t j = j0 + q * 32 + lane;
-                if (j < h) dst[j] = acc[q];
-            }
+            for (int e = 0; e < 32; ++e)
+                if (e < here) acc = acc + v[e];
         }
+        if (in) out[static_cast<uint64_t>(row) * h + col] = acc;
     }
 }
 
@@ -171,15 +178,15 @@ void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* o
     check(cudaMemsetAsync(count, 0, rows * sizeof(int32_t), s), "embedding_grad memset");
     if (n > 0) {
         uint32_t blocks = static_cast<uint32_t>((n + 255) / 256);
-        rank_kernel<<<blocks, 256, 0, s>>>(ids, static_cast<uint32_t>(n), static_cast<uint32_t>(rows), rank, count, status);
+        rank_kernel<<<static_cast<uint32_t>((n + 63) / 64), 256, 0, s>>>(ids, static_cast<uint32_t>(n), static_cast<uint32_t>(rows), rank, count, status);
         check_launch("embedding_grad");
         offsets_kernel<<<1, 1024, 0, s>>>(count, static_cast<uint32_t>(rows), offset);
         check_launch("embedding_grad");
         list_kernel<<<blocks, 256, 0, s>>>(ids, static_cast<uint32_t>(n), rank, offset, list);
         check_launch("embedding_grad");
     }
-    uint64_t blocks = (rows * 32 + 255) / 256;
-    uint32_t grid = static_cast<uint32_t>(blocks > 148 * 16 ? 148 * 16 : blocks);
+    uint64_t blocks = (rows * ((h + 31) / 32) * 32 + 255) / 256;
+    uint32_t grid = static_cast<uint32_t>(blocks > 148 * 32 ? 148 * 32 : blocks);
     scatter_kernel<<<grid, 256, 0, s>>>(g, list, offset, count, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
     check_launch("embedding_grad");
 }

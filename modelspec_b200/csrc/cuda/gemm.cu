@@ -20,7 +20,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 template <bool A_T, bool B_T>
 __global__ void __launch_bounds__(256) matmul_kernel(const float* __restrict__ a, const float* __restrict__ b,
-                                                     float* __restrict__ c, uint32_t m, uint32_t n, uint32_t k) {
+                                                     float* __restrict__ c, uint32_t m, uint32_t n, uint32_t k,
+                                                     const float* __restrict__ bias) {
     __shared__ float as[BK][BM + 4];
     __shared__ float bs[BK][BN + 4];
     const uint32_t tid = threadIdx.x;
@@ -91,7 +92,10 @@ __global__ void __launch_bounds__(256) matmul_kernel(const float* __restrict__ a
         for (int j = 0; j < TN; ++j) {
             uint32_t gn = n0 + tx * TN + j;
             // k = 0 leaves the -0.0 start; the reference writes +0 then.
-            if (gn < n) c[static_cast<uint64_t>(gm) * n + gn] = k == 0 ? 0.0f : acc[i][j];
+            if (gn < n) {
+                float value = k == 0 ? 0.0f : acc[i][j];
+                c[static_cast<uint64_t>(gm) * n + gn] = bias ? value + bias[gn] : value;
+            }
         }
     }
 }
@@ -99,14 +103,14 @@ __global__ void __launch_bounds__(256) matmul_kernel(const float* __restrict__ a
 }  // namespace
 
 void matmul(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c,
-            uint64_t m, uint64_t n, uint64_t k) {
+            uint64_t m, uint64_t n, uint64_t k, const float* bias) {
     if (m == 0 || n == 0) return;
     dim3 grid(static_cast<uint32_t>((n + BN - 1) / BN), static_cast<uint32_t>((m + BM - 1) / BM));
     uint32_t mm = static_cast<uint32_t>(m), nn = static_cast<uint32_t>(n), kk = static_cast<uint32_t>(k);
-    if (a_t && b_t) matmul_kernel<true, true><<<grid, 256, 0, s>>>(a, b, c, mm, nn, kk);
-    else if (a_t) matmul_kernel<true, false><<<grid, 256, 0, s>>>(a, b, c, mm, nn, kk);
-    else if (b_t) matmul_kernel<false, true><<<grid, 256, 0, s>>>(a, b, c, mm, nn, kk);
-    else matmul_kernel<false, false><<<grid, 256, 0, s>>>(a, b, c, mm, nn, kk);
+    if (a_t && b_t) matmul_kernel<true, true><<<grid, 256, 0, s>>>(a, b, c, mm, nn, kk, bias);
+    else if (a_t) matmul_kernel<true, false><<<grid, 256, 0, s>>>(a, b, c, mm, nn, kk, bias);
+    else if (b_t) matmul_kernel<false, true><<<grid, 256, 0, s>>>(a, b, c, mm, nn, kk, bias);
+    else matmul_kernel<false, false><<<grid, 256, 0, s>>>(a, b, c, mm, nn, kk, bias);
     check_launch("matmul");
 }
 

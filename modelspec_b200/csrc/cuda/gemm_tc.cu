@@ -45,6 +45,7 @@ struct TcArgs {
     const float* a;
     const float* b;
     float* c;          // C, or the split-K workspace [splits][m][n]
+    const float* bias; // added to every row of C by the CTA that writes C; null for none
     uint32_t m, n, k;
     uint32_t lda, ldb, ldc;        // row pitch, in elements, of each matrix as stored
     uint32_t kblocks_per_split;
@@ -331,9 +332,10 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
             __syncwarp();
             const uint32_t gn = n0 + col + lane;
             if (gn < args.n) {
+                const float bias = args.bias ? args.bias[gn] : 0.0f;
                 float* dst = out + static_cast<uint64_t>(m0 + (warp & 3u) * 32) * args.ldc + gn;
                 const uint32_t rows_here = m0 + (warp & 3u) * 32 < args.m ? min(32u, args.m - (m0 + (warp & 3u) * 32)) : 0u;
-                for (uint32_t rr = 0; rr < rows_here; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = staging[rr * 33 + lane];
+                for (uint32_t rr = 0; rr < rows_here; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = staging[rr * 33 + lane] + bias;
             }
             __syncwarp();
         }
@@ -385,12 +387,13 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
     }
 }
 
-__global__ void splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ c, uint64_t count, uint32_t splits) {
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ c, uint64_t count, uint32_t splits,
+                                     const float* __restrict__ bias, uint32_t n) {
     uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
         float acc = ws[i];
         for (uint32_t s = 1; s < splits; ++s) acc += ws[static_cast<uint64_t>(s) * count + i];
-        c[i] = acc;
+        c[i] = bias ? acc + bias[i % n] : acc;
     }
 }
 
@@ -436,13 +439,14 @@ MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k) {
 }
 
 void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m, uint64_t n,
-               uint64_t k, float* workspace, uint32_t* status) {
+               uint64_t k, float* workspace, uint32_t* status, const float* bias) {
     if (m == 0 || n == 0) return;
     MatmulTcPlan p = matmul_tc_plan(m, n, k);
     TcArgs args = {};
     args.a = a;
     args.b = b;
     args.c = p.splits > 1 ? workspace : c;
+    args.bias = p.splits > 1 ? nullptr : bias;
     args.m = static_cast<uint32_t>(m);
     args.n = static_cast<uint32_t>(n);
     args.k = static_cast<uint32_t>(k);
@@ -461,7 +465,8 @@ void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_
     if (p.splits > 1) {
         uint64_t count = m * n;
         uint64_t blocks = (count + 255) / 256;
-        splitk_reduce_kernel<<<static_cast<uint32_t>(blocks > 148 * 8 ? 148 * 8 : blocks), 256, 0, s>>>(workspace, c, count, p.splits);
+        splitk_reduce_kernel<<<static_cast<uint32_t>(blocks > 148 * 8 ? 148 * 8 : blocks), 256, 0, s>>>(workspace, c, count, p.splits, bias,
+                                                                                                                  static_cast<uint32_t>(n));
         check_launch("splitk_reduce");
     }
 }

@@ -73,6 +73,13 @@ void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labe
                         const float* g, bool denominator_ready, float* denominator, float* out, uint64_t rows,
                         uint64_t v);
 
+// Both at once, one visit of each logits row: `loss` as cross_entropy gives it, `grad` as
+// cross_entropy_grad gives it. `denominator` as in cross_entropy_grad; when it is ready (data
+// parallel) the loss divides by it too.
+void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
+                             const float* g, bool denominator_ready, float* denominator, float* row_loss, float* loss,
+                             float* grad, uint64_t rows, uint64_t v);
+
 // ---- embedding (embedding.cu) -----------------------------------------------------------------
 // out[n, :] = table[ids[n], :]; an id outside [0, rows) writes zeros and raises bit 0 of *status.
 void embedding(cudaStream_t s, const float* table, const int32_t* ids, float* out, uint64_t n,
@@ -86,8 +93,10 @@ void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* o
 // ---- matmul (gemm.cu) -------------------------------------------------------------------------
 // C[m, n] = op(A) x op(B) (+ bias[n]) with each element one ascending-k fused chain starting
 // from its first product. `a_t`: A is stored [k, m] and read transposed; `b_t`: B stored [n, k].
+// `bias`, when not null, is a row of n floats added to every row of the product (one more
+// rounding per element, the add_rows the reference runs as its own kernel).
 void matmul(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c,
-            uint64_t m, uint64_t n, uint64_t k);
+            uint64_t m, uint64_t n, uint64_t k, const float* bias = nullptr);
 
 // ---- matmul on tensor cores (gemm_tc.cu) ------------------------------------------------------
 // The same product by tcgen05.mma with a 3xTF32 operand split and f32 accumulation in tensor
@@ -100,7 +109,7 @@ struct MatmulTcPlan {
 };
 MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k);
 void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m,
-               uint64_t n, uint64_t k, float* workspace, uint32_t* status);
+               uint64_t n, uint64_t k, float* workspace, uint32_t* status, const float* bias = nullptr);
 
 // outer x inner independent products through one launch (grid.z = problem): matrix z of an
 // operand starts at base + (z / inner) * stride_outer + (z % inner) * stride_inner elements and

@@ -239,6 +239,38 @@ __global__ void cross_entropy_grad_kernel(const float* __restrict__ logits, cons
     }
 }
 
+// Loss row and gradient row in one visit of the logits row: max, sum of exp, then
+// scale * (p - onehot) while the row is still in cache. The same formulas, in the same order, as
+// the two separate kernels.
+__global__ void cross_entropy_fused_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+                                           const float* __restrict__ weights, const float* __restrict__ g,
+                                           const float* __restrict__ denominator, float* __restrict__ row_loss,
+                                           float* __restrict__ out, uint32_t v) {
+    __shared__ float shared[33];
+    uint32_t r = blockIdx.x;
+    float* o = out + static_cast<uint64_t>(r) * v;
+    float den = denominator[0], w = weights[r];
+    if (w == 0.0f) {
+        if (threadIdx.x == 0) row_loss[r] = 0.0f;
+        for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) o[c] = 0.0f;
+        return;
+    }
+    const float* row = logits + static_cast<uint64_t>(r) * v;
+    float max, total;
+    block_row_softmax(row, v, shared, &max, &total);
+    uint32_t label = static_cast<uint32_t>(labels[r]);
+    if (threadIdx.x == 0) row_loss[r] = max + logf(total) - (label < v ? row[label] : 0.0f);
+    if (den == 0.0f) {
+        for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) o[c] = 0.0f;
+        return;
+    }
+    float scale = g[0] * w / den;
+    for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) {
+        float target = c == label ? 1.0f : 0.0f;
+        o[c] = scale * (expf(row[c] - max) / total - target);
+    }
+}
+
 inline uint32_t warp_row_blocks(uint64_t rows) { return static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock); }
 
 }  // namespace
@@ -311,6 +343,22 @@ void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, c
     }
     cross_entropy_loss_kernel<<<1, 1024, 0, s>>>(row_loss, weights, static_cast<uint32_t>(rows), global_den, loss);
     check_launch("cross_entropy");
+}
+
+void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
+                             const float* g, bool denominator_ready, float* denominator, float* row_loss, float* loss,
+                             float* grad, uint64_t rows, uint64_t v) {
+    if (!denominator_ready) {
+        weight_sum_kernel<<<1, 1024, 0, s>>>(weights, static_cast<uint32_t>(rows), denominator);
+        check_launch("cross_entropy_with_grad");
+    }
+    if (rows > 0) {
+        cross_entropy_fused_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, g, denominator, row_loss,
+                                                                                       grad, static_cast<uint32_t>(v));
+        check_launch("cross_entropy_with_grad");
+    }
+    cross_entropy_loss_kernel<<<1, 1024, 0, s>>>(row_loss, weights, static_cast<uint32_t>(rows), denominator_ready ? denominator : nullptr, loss);
+    check_launch("cross_entropy_with_grad");
 }
 
 void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,

@@ -611,7 +611,26 @@ struct Scheduler {
             case Op::MatMul: {
                 uint32_t a = in[0], b = in[1];
                 uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(a);
-                emit_matmul(nd, at, a, false, b, false, m, n, kk);
+                // add_rows(matmul(x, w), b) with nothing else reading the product: the bias rides
+                // in the matmul's epilogue and the product itself is never stored.
+                int bias = -1;
+                uint32_t result = at;
+                bool is_output = false;
+                for (const msx::Output& o : prog.outputs) is_output = is_output || pos(o.value) == at;
+                if (!is_output && users[at].size() == 1) {
+                    uint32_t u = users[at][0];
+                    const Node& add = node(u);
+                    if (add.op == Op::AddRows && !handled[u] && pos(add.operands[0]) == at && pos(add.operands[1]) < at) {
+                        bias = static_cast<int>(pos(add.operands[1]));
+                        result = u;
+                        handled[u] = 1;
+                        out.kind = Slot::Dead;
+                        Slot& r = P->slots[u];
+                        r.kind = Slot::Arena;
+                        r.bytes = std::max<uint64_t>(add.ty.count() * 4, 4);
+                    }
+                }
+                emit_matmul(nd, result, a, false, b, false, m, n, kk, bias);
                 break;
             }
             case Op::Transpose: {
@@ -738,6 +757,34 @@ struct Scheduler {
                 uint32_t logits = in[0], labels = in[1], weights = in[2];
                 uint64_t r = rows_of(logits), v = cols_of(logits);
                 uint32_t row_loss = scratch(std::max<uint64_t>(r, 1) * 4), den = scratch(4);
+                // The gradient op of the same loss reads the same row maxima and sums: when its
+                // incoming adjoint is a constant (the seed), one pass over the logits gives both.
+                int grad = -1;
+                for (uint32_t u : users[logits]) {
+                    const Node& other = node(u);
+                    if (other.op != Op::CrossEntropyGrad || handled[u] || u < at) continue;
+                    if (pos(other.operands[0]) != logits || pos(other.operands[1]) != labels || pos(other.operands[2]) != weights) continue;
+                    if (P->slots[pos(other.operands[3])].kind != Slot::Const) continue;
+                    grad = static_cast<int>(u);
+                    break;
+                }
+                if (grad >= 0) {
+                    uint32_t gpos = static_cast<uint32_t>(grad), seed = pos(node(gpos).operands[3]);
+                    handled[gpos] = 1;
+                    Slot& gs = P->slots[gpos];
+                    gs.kind = Slot::Arena;
+                    gs.bytes = std::max<uint64_t>(node(gpos).ty.count() * 4, 4);
+                    emit("cross_entropy_with_grad", nd, {logits, labels, weights, seed}, {at, gpos, row_loss, den}, [=](cudaStream_t s) {
+                        if (plan->comm) {
+                            k::weight_sum(s, plan->f(weights), r, plan->f(den));
+                            all_reduce(plan, plan->f(den), 1, false, s);
+                        }
+                        k::cross_entropy_with_grad(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(seed), plan->comm != nullptr,
+                                                   plan->f(den), plan->f(row_loss), plan->f(at), plan->f(gpos), r, v);
+                        all_reduce(plan, plan->f(at), 1, false, s);
+                    });
+                    break;
+                }
                 emit("cross_entropy", nd, in, {at, row_loss, den}, [=](cudaStream_t s) {
                     if (plan->comm) {
                         // The shard's numerator over the whole batch's weight sum, then summed.
@@ -784,11 +831,15 @@ struct Scheduler {
     // C[m, n] = op(a) x op(b); `flip_*` reads the operand as the transpose of what its slot says.
     // The exact f32 chain kernel under MSX_PLAN_EXACT_MATMUL, else the tensor cores.
     void emit_matmul(const Node& nd, uint32_t at, uint32_t a, bool flip_a, uint32_t b, bool flip_b, uint64_t m, uint64_t n,
-                     uint64_t kk) {
+                     uint64_t kk, int bias = -1) {
         msx_plan* plan = P;
+        std::vector<uint32_t> reads = {a, b};
+        if (bias >= 0) reads.push_back(static_cast<uint32_t>(bias));
+        auto bias_of = [=]() -> const float* { return bias >= 0 ? plan->f(static_cast<uint32_t>(bias)) : nullptr; };
         if (P->flags & MSX_PLAN_EXACT_MATMUL) {
-            Launch& l = emit("matmul", nd, {a, b}, {at}, [=](cudaStream_t s) {
-                k::matmul(s, plan->f(a), plan->transposed(a) != flip_a, plan->f(b), plan->transposed(b) != flip_b, plan->f(at), m, n, kk);
+            Launch& l = emit("matmul", nd, reads, {at}, [=](cudaStream_t s) {
+                k::matmul(s, plan->f(a), plan->transposed(a) != flip_a, plan->f(b), plan->transposed(b) != flip_b, plan->f(at), m, n, kk,
+                          bias_of());
             });
             l.flop = 2 * m * n * kk;
             return;
@@ -800,9 +851,9 @@ struct Scheduler {
             ws = static_cast<int>(scratch(floats * 4));
             writes.push_back(static_cast<uint32_t>(ws));
         }
-        Launch& l = emit("matmul", nd, {a, b}, writes, [=](cudaStream_t s) {
+        Launch& l = emit("matmul", nd, reads, writes, [=](cudaStream_t s) {
             k::matmul_tc(s, plan->f(a), plan->transposed(a) != flip_a, plan->f(b), plan->transposed(b) != flip_b, plan->f(at), m, n, kk,
-                         ws >= 0 ? plan->f(static_cast<uint32_t>(ws)) : nullptr, plan->d_status);
+                         ws >= 0 ? plan->f(static_cast<uint32_t>(ws)) : nullptr, plan->d_status, bias_of());
         });
         l.flop = 2 * m * n * kk;
     }
