@@ -110,5 +110,24 @@ __device__ __forceinline__ float block_max(float v, float* shared) {
     return shared[32];
 }
 
+// One-launch two-stage reductions: every block publishes its partial result, then calls this; the
+// block that arrives last at `counter` (true for all its threads) sees every block's partials and
+// finishes the job. The counter goes back to 0 for the next launch. Partials written by other
+// blocks must be read with __ldcg (they may sit in another SM's path, never in this SM's L1).
+__device__ __forceinline__ bool last_block_arrives(uint32_t* counter, uint32_t expected, bool* shared_flag) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+        uint32_t before = atomicAdd(counter, 1u);
+        bool last = before + 1u == expected;
+        if (last) *counter = 0u;
+        *shared_flag = last;
+    }
+    __syncthreads();
+    bool last = *shared_flag;
+    if (last) __threadfence();
+    return last;
+}
+
 }  // namespace k
 }  // namespace msx

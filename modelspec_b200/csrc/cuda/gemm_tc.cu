@@ -335,7 +335,16 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
                 const float bias = args.bias ? args.bias[gn] : 0.0f;
                 float* dst = out + static_cast<uint64_t>(m0 + (warp & 3u) * 32) * args.ldc + gn;
                 const uint32_t rows_here = m0 + (warp & 3u) * 32 < args.m ? min(32u, args.m - (m0 + (warp & 3u) * 32)) : 0u;
-                for (uint32_t rr = 0; rr < rows_here; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = staging[rr * 33 + lane] + bias;
+                if (rows_here == 32) {
+                    // All the shared-memory reads first: the stores then leave back to back.
+                    float v[32];
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr) v[rr] = staging[rr * 33 + lane] + bias;
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = v[rr];
+                } else {
+                    for (uint32_t rr = 0; rr < rows_here; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = staging[rr * 33 + lane] + bias;
+                }
             }
             __syncwarp();
         }

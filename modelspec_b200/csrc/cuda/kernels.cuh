@@ -44,7 +44,12 @@ void mse(cudaStream_t s, const float* a, const float* b, uint64_t n, double* scr
 // out[c] = sum over rows of g[r, c]. `scratch` holds sum_rows_scratch_floats(rows, h) floats.
 uint32_t sum_rows_chunks(uint64_t rows);
 uint64_t sum_rows_scratch_floats(uint64_t rows, uint64_t h);
-void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out);
+// `counters`, when not null, is sum_rows_counters(h) words that are zero before the first launch
+// and left zero by every launch: the chunk sums are then combined by the same launch (same order,
+// same result) instead of a second one.
+uint64_t sum_rows_counters(uint64_t h);
+void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out,
+              uint32_t* counters = nullptr);
 
 // ---- row kernels (rowwise.cu) -----------------------------------------------------------------
 void layer_norm(cudaStream_t s, const float* x, const float* gamma, const float* beta, float* out,
@@ -56,6 +61,14 @@ void layer_norm_grad_x(cudaStream_t s, const float* x, const float* gamma, const
 uint64_t layer_norm_grad_gamma_scratch_floats(uint64_t rows, uint64_t h);
 void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float* scratch,
                            float* dgamma, float* dbeta, uint64_t rows, uint64_t h);
+// layer_norm_grad_x (into dx, with gamma), layer_norm_grad_gamma (dgamma) and the column sums of g
+// (dbeta) in one launch, for rows of up to 1,024 elements. dx, dgamma and dbeta may each be null.
+// `scratch` holds layer_norm_backward_scratch_floats(rows, h) floats; `counter` is one word that
+// is zero before the first launch and left zero by every launch.
+bool layer_norm_backward_supported(uint64_t h);
+uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h);
+void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
+                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h);
 void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t k);
 void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, uint64_t rows, uint64_t k);
 // Row losses max + ln(sum exp(x - max)) - x[label] into row_loss[rows], then
@@ -75,10 +88,12 @@ void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labe
 
 // Both at once, one visit of each logits row: `loss` as cross_entropy gives it, `grad` as
 // cross_entropy_grad gives it. `denominator` as in cross_entropy_grad; when it is ready (data
-// parallel) the loss divides by it too.
+// parallel) the loss divides by it too. `counter`, when not null, is one word that is zero before
+// the first launch and left zero by every launch: rows of up to 32,768 logits then take one
+// launch in all (weight sum and final loss included) and one read of the logits from memory.
 void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
                              const float* g, bool denominator_ready, float* denominator, float* row_loss, float* loss,
-                             float* grad, uint64_t rows, uint64_t v);
+                             float* grad, uint64_t rows, uint64_t v, uint32_t* counter = nullptr);
 
 // ---- embedding (embedding.cu) -----------------------------------------------------------------
 // out[n, :] = table[ids[n], :]; an id outside [0, rows) writes zeros and raises bit 0 of *status.

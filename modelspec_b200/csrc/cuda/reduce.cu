@@ -54,9 +54,13 @@ uint32_t whole_blocks(uint64_t n) {
 
 // Block (32, 8): lane = column of a 32-column tile, each of the 8 warps takes every 8th row of
 // the block's row chunk.
+// `counters`, when not null, holds one zeroed word per column block: the last chunk block of a
+// column block to finish adds the chunk sums in ascending chunk order (what sum_rows_stage2 does
+// as a second launch) and writes `out`.
 __global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint32_t h, uint32_t rows_per_chunk,
-                                float* __restrict__ partial) {
+                                float* __restrict__ partial, uint32_t* __restrict__ counters, float* __restrict__ out) {
     __shared__ float shared[8][32];
+    __shared__ bool is_last;
     uint32_t c = blockIdx.x * 32 + threadIdx.x;
     uint32_t r0 = blockIdx.y * rows_per_chunk;
     uint32_t r1 = min(rows, r0 + rows_per_chunk);
@@ -70,6 +74,13 @@ __global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint
 #pragma unroll
         for (int w = 1; w < 8; ++w) total += shared[w][threadIdx.x];
         partial[static_cast<uint64_t>(blockIdx.y) * h + c] = total;
+    }
+    if (counters == nullptr) return;
+    if (!last_block_arrives(counters + blockIdx.x, gridDim.y, &is_last)) return;
+    if (threadIdx.y == 0 && c < h) {
+        float total = __ldcg(partial + c);
+        for (uint32_t k = 1; k < gridDim.y; ++k) total += __ldcg(partial + static_cast<uint64_t>(k) * h + c);
+        out[c] = total;
     }
 }
 
@@ -109,15 +120,17 @@ void mse(cudaStream_t s, const float* a, const float* b, uint64_t n, double* scr
 
 uint64_t sum_rows_scratch_floats(uint64_t rows, uint64_t h) { return sum_rows_chunks(rows) * h; }
 
-void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out) {
+uint64_t sum_rows_counters(uint64_t h) { return (h + 31) / 32; }
+
+void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out, uint32_t* counters) {
     if (h == 0) return;
     uint32_t chunks = sum_rows_chunks(rows);
     uint32_t rows_per_chunk = static_cast<uint32_t>((rows + chunks - 1) / chunks);
     dim3 grid(static_cast<uint32_t>((h + 31) / 32), chunks);
     sum_rows_stage1<<<grid, dim3(32, 8), 0, s>>>(g, static_cast<uint32_t>(rows), static_cast<uint32_t>(h),
-                                                 rows_per_chunk, chunks == 1 ? out : scratch);
+                                                 rows_per_chunk, chunks == 1 ? out : scratch, chunks > 1 ? counters : nullptr, out);
     check_launch("sum_rows");
-    if (chunks > 1) {
+    if (chunks > 1 && counters == nullptr) {
         sum_rows_stage2<<<static_cast<uint32_t>((h + 127) / 128), 128, 0, s>>>(scratch, chunks,
                                                                                 static_cast<uint32_t>(h), out);
         check_launch("sum_rows");

@@ -271,7 +271,207 @@ __global__ void cross_entropy_fused_kernel(const float* __restrict__ logits, con
     }
 }
 
+// The same, for rows of up to 32 * 1024 logits, with the row held in registers: one read of the
+// logits from memory (every load of the row in flight at once), one write of the gradient, and
+// each exp computed once.
+constexpr int kWideThreads = 1024, kWideItems = 32;
+__global__ void __launch_bounds__(kWideThreads, 1)
+cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+                                const float* __restrict__ weights, const float* __restrict__ g,
+                                const float* __restrict__ denominator, float* __restrict__ row_loss,
+                                float* __restrict__ out, uint32_t v, uint32_t* __restrict__ counter,
+                                float* __restrict__ loss) {
+    __shared__ float shared[33];
+    __shared__ double shared64[33];
+    __shared__ bool is_last;
+    const uint32_t r = blockIdx.x, tid = threadIdx.x, rows = gridDim.x;
+    float* o = out + static_cast<uint64_t>(r) * v;
+    // The weight sum: given (the whole batch's, data parallel), or summed here by every block in
+    // the same order (f64 over the block, one rounding), so that no launch has to precede this one.
+    float den;
+    if (denominator != nullptr) {
+        den = denominator[0];
+    } else {
+        double sum = 0.0;
+        for (uint32_t j = tid; j < rows; j += kWideThreads) sum += static_cast<double>(weights[j]);
+        den = static_cast<float>(block_sum(sum, shared64));
+    }
+    const float w = weights[r];
+    if (w == 0.0f) {
+        if (tid == 0) row_loss[r] = 0.0f;
+        for (uint32_t c = tid; c < v; c += kWideThreads) o[c] = 0.0f;
+    } else {
+    const float* row = logits + static_cast<uint64_t>(r) * v;
+    float x[kWideItems];
+#pragma unroll
+    for (int i = 0; i < kWideItems; ++i) {
+        uint32_t c = i * kWideThreads + tid;
+        x[i] = c < v ? __ldg(row + c) : -INFINITY;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kWideItems; ++i)
+        if (x[i] > m) m = x[i];
+    m = block_max(m, shared);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kWideItems; ++i) {
+        uint32_t c = i * kWideThreads + tid;
+        if (c < v) {
+            x[i] = expf(x[i] - m);
+            sum += x[i];
+        }
+    }
+    const float total = block_sum(sum, shared);
+    const uint32_t label = static_cast<uint32_t>(labels[r]);
+    if (tid == 0) row_loss[r] = m + logf(total) - (label < v ? row[label] : 0.0f);
+    const bool zero = den == 0.0f;
+    const float scale = zero ? 0.0f : g[0] * w / den;
+#pragma unroll
+    for (int i = 0; i < kWideItems; ++i) {
+        uint32_t c = i * kWideThreads + tid;
+        if (c < v) {
+            float target = c == label ? 1.0f : 0.0f;
+            o[c] = zero ? 0.0f : scale * (x[i] / total - target);
+        }
+    }
+    }
+    // The loss, by the last block to finish: sum of w * l over sum of w, f64 sums, one rounding.
+    if (!last_block_arrives(counter, rows, &is_last)) return;
+    double num = 0.0, den64 = 0.0;
+    for (uint32_t j = tid; j < rows; j += kWideThreads) {
+        double wj = static_cast<double>(weights[j]);
+        num = fma(wj, static_cast<double>(__ldcg(row_loss + j)), num);
+        den64 += wj;
+    }
+    num = block_sum(num, shared64);
+    den64 = block_sum(den64, shared64);
+    if (denominator != nullptr) den64 = static_cast<double>(denominator[0]);
+    if (tid == 0) loss[0] = den64 == 0.0 ? 0.0f : static_cast<float>(num / den64);
+}
+
 inline uint32_t warp_row_blocks(uint64_t rows) { return static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock); }
+
+// layer_norm_grad_x, layer_norm_grad_gamma and the beta gradient in one launch. A block takes a
+// chunk of rows, a warp one row at a time with the row of x and of g in registers (ITEMS values
+// per lane): row moments, then the dx row, then this row's terms of the column sums. Warp sums of
+// a chunk are added in warp order, chunk sums by the last block to finish: thread (lane, w) adds
+// chunks w, w + 8, ... in ascending order and the eight sums are added in ascending w. Every
+// output is a fixed expression of the inputs: deterministic, tolerance class against a
+// sequential column sum. dx (with gamma), dgamma and dbeta may each be null.
+template <int ITEMS>
+__global__ void __launch_bounds__(256) layer_norm_backward_kernel(
+    const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ g, float* __restrict__ dx,
+    float* __restrict__ partial, uint32_t* __restrict__ counter, float* __restrict__ dgamma, float* __restrict__ dbeta,
+    uint32_t rows, uint32_t h, uint32_t rows_per_chunk) {
+    __shared__ float buf[8 * 32 * ITEMS];
+    __shared__ bool is_last;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, chunks = gridDim.x;
+    const uint32_t r0 = blockIdx.x * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+    const float width = static_cast<float>(h);
+    float acc_g[ITEMS], acc_b[ITEMS], gam[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        acc_g[i] = 0.0f;
+        acc_b[i] = 0.0f;
+        uint32_t c = i * 32 + lane;
+        gam[i] = (dx != nullptr && c < h) ? gamma[c] : 0.0f;
+    }
+    for (uint32_t r = r0 + warp; r < r1; r += 8) {
+        const float* xr = x + static_cast<uint64_t>(r) * h;
+        const float* gr = g + static_cast<uint64_t>(r) * h;
+        float xv[ITEMS], gv[ITEMS];
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            uint32_t c = i * 32 + lane;
+            xv[i] = c < h ? xr[c] : 0.0f;
+            gv[i] = c < h ? gr[c] : 0.0f;
+        }
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i)
+            if (i * 32 + lane < h) sum += xv[i];
+        const float mean = warp_sum(sum) / width;
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i)
+            if (i * 32 + lane < h) {
+                float d = xv[i] - mean;
+                q = fmaf(d, d, q);
+            }
+        const float rstd = 1.0f / sqrtf(warp_sum(q) / width + kLayerNormEps);
+        float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i)
+            if (i * 32 + lane < h) {
+                float xhat = (xv[i] - mean) * rstd;
+                acc_g[i] = fmaf(gv[i], xhat, acc_g[i]);
+                acc_b[i] += gv[i];
+                float gx = gv[i] * gam[i];
+                s1 += gx;
+                s2 = fmaf(gx, xhat, s2);
+            }
+        if (dx != nullptr) {
+            const float mean_gx = warp_sum(s1) / width, mean_gx_xhat = warp_sum(s2) / width;
+            float* o = dx + static_cast<uint64_t>(r) * h;
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+                uint32_t c = i * 32 + lane;
+                if (c < h) {
+                    float gx = gv[i] * gam[i];
+                    float xhat = (xv[i] - mean) * rstd;
+                    o[c] = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
+                }
+            }
+        }
+    }
+    if (dgamma == nullptr && dbeta == nullptr) return;
+    float* partial_gamma = partial + static_cast<uint64_t>(blockIdx.x) * h;
+    float* partial_beta = partial + static_cast<uint64_t>(chunks + blockIdx.x) * h;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+        if (pass == 0 ? dgamma == nullptr : dbeta == nullptr) continue;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) buf[(warp * ITEMS + i) * 32 + lane] = pass == 0 ? acc_g[i] : acc_b[i];
+        __syncthreads();
+        for (uint32_t c = threadIdx.x; c < h; c += 256) {
+            uint32_t i = c >> 5, l = c & 31;
+            float total = buf[i * 32 + l];
+#pragma unroll
+            for (int w = 1; w < 8; ++w) total += buf[(w * ITEMS + i) * 32 + l];
+            (pass == 0 ? partial_gamma : partial_beta)[c] = total;
+        }
+    }
+    if (!last_block_arrives(counter, chunks, &is_last)) return;
+    for (int pass = 0; pass < 2; ++pass) {
+        float* out = pass == 0 ? dgamma : dbeta;
+        if (out == nullptr) continue;
+        const float* from = partial + static_cast<uint64_t>(pass) * chunks * h;
+        for (uint32_t c0 = 0; c0 < h; c0 += 32) {
+            uint32_t c = c0 + lane;
+            float total = 0.0f;
+            if (c < h)
+                for (uint32_t k = warp; k < chunks; k += 8) total += __ldcg(from + static_cast<uint64_t>(k) * h + c);
+            __syncthreads();
+            buf[warp * 32 + lane] = total;
+            __syncthreads();
+            if (warp == 0 && c < h) {
+                float t = buf[lane];
+#pragma unroll
+                for (int w = 1; w < 8; ++w) t += buf[w * 32 + lane];
+                out[c] = t;
+            }
+        }
+    }
+}
+
+uint32_t backward_chunks(uint64_t rows) {
+    uint64_t per = (rows + 147) / 148;
+    if (per < 8) per = 8;
+    uint64_t chunks = (rows + per - 1) / per;
+    return static_cast<uint32_t>(chunks < 1 ? 1 : chunks);
+}
 
 }  // namespace
 
@@ -317,6 +517,28 @@ void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float
     check_launch("layer_norm_grad_gamma");
 }
 
+bool layer_norm_backward_supported(uint64_t h) { return h >= 1 && h <= 1024; }
+uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h) { return 2ull * backward_chunks(rows) * h; }
+
+void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
+                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h) {
+    if (h == 0) return;
+    uint32_t chunks = backward_chunks(rows);
+    uint32_t per = static_cast<uint32_t>((rows + chunks - 1) / chunks);
+    uint32_t items = static_cast<uint32_t>((h + 31) / 32);
+    uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
+#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, dx, scratch, counter, dgamma, dbeta, r, hh, per)
+    if (items <= 1) MSX_LN_BACKWARD(1);
+    else if (items <= 2) MSX_LN_BACKWARD(2);
+    else if (items <= 4) MSX_LN_BACKWARD(4);
+    else if (items <= 8) MSX_LN_BACKWARD(8);
+    else if (items <= 16) MSX_LN_BACKWARD(16);
+    else if (items <= 24) MSX_LN_BACKWARD(24);
+    else MSX_LN_BACKWARD(32);
+#undef MSX_LN_BACKWARD
+    check_launch("layer_norm_backward");
+}
+
 void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t k) {
     if (rows == 0) return;
     softmax_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(x, out, static_cast<uint32_t>(k));
@@ -347,7 +569,13 @@ void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, c
 
 void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
                              const float* g, bool denominator_ready, float* denominator, float* row_loss, float* loss,
-                             float* grad, uint64_t rows, uint64_t v) {
+                             float* grad, uint64_t rows, uint64_t v, uint32_t* counter) {
+    if (rows > 0 && counter != nullptr && v <= static_cast<uint64_t>(kWideThreads) * kWideItems) {
+        cross_entropy_fused_wide_kernel<<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(
+            logits, labels, weights, g, denominator_ready ? denominator : nullptr, row_loss, grad, static_cast<uint32_t>(v), counter, loss);
+        check_launch("cross_entropy_with_grad");
+        return;
+    }
     if (!denominator_ready) {
         weight_sum_kernel<<<1, 1024, 0, s>>>(weights, static_cast<uint32_t>(rows), denominator);
         check_launch("cross_entropy_with_grad");

@@ -141,6 +141,10 @@ struct msx_plan {
     float* d_consts = nullptr;
     uint32_t* d_status = nullptr;
     uint32_t* pinned_status = nullptr;
+    // Arrival counters of the one-launch two-stage reductions: zero between launches.
+    uint32_t* d_counters = nullptr;
+    uint32_t counters_used = 0;
+    uint32_t* counter(uint32_t index) const { return d_counters + index; }
     void* d_update_tables = nullptr;
 
     int loss_pos = -1;
@@ -218,6 +222,12 @@ struct Scheduler {
     [[noreturn]] void unsupported(const Node& n, const std::string& why) const {
         throw StatusError(MSX_UNSUPPORTED, "E-TARGET-011: %" + std::to_string(n.id) + " " + msx::op_name(n.op) +
                                                " has no CUDA kernel: " + why);
+    }
+
+    uint32_t counters(uint64_t n) {
+        uint32_t base = P->counters_used;
+        P->counters_used += static_cast<uint32_t>(n);
+        return base;
     }
 
     uint32_t scratch(uint64_t bytes) {
@@ -694,8 +704,9 @@ struct Scheduler {
             case Op::SumRows: {
                 uint32_t g = in[0];
                 uint64_t r = rows_of(g), h = cols_of(g);
-                uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4);
-                emit("sum_rows", nd, in, {at, tmp}, [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), plan->f(at)); });
+                uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4), ctr = counters(k::sum_rows_counters(h));
+                emit("sum_rows", nd, in, {at, tmp},
+                     [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), plan->f(at), plan->counter(ctr)); });
                 break;
             }
             case Op::LayerNorm: {
@@ -707,6 +718,7 @@ struct Scheduler {
                 break;
             }
             case Op::LayerNormGradX: {
+                if (schedule_layer_norm_backward(at)) break;
                 uint32_t x = in[0], gamma = in[1], g = in[2];
                 uint64_t r = rows_of(x), h = cols_of(x);
                 emit("layer_norm_grad_x", nd, in, {at}, [=](cudaStream_t s) {
@@ -715,6 +727,7 @@ struct Scheduler {
                 break;
             }
             case Op::LayerNormGradGamma: {
+                if (schedule_layer_norm_backward(at)) break;
                 uint32_t x = in[0], g = in[1];
                 uint64_t r = rows_of(x), h = cols_of(x);
                 // The beta gradient is the SumRows of the same adjoint: one pass gives both.
@@ -774,13 +787,14 @@ struct Scheduler {
                     Slot& gs = P->slots[gpos];
                     gs.kind = Slot::Arena;
                     gs.bytes = std::max<uint64_t>(node(gpos).ty.count() * 4, 4);
+                    uint32_t ctr = counters(1);
                     emit("cross_entropy_with_grad", nd, {logits, labels, weights, seed}, {at, gpos, row_loss, den}, [=](cudaStream_t s) {
                         if (plan->comm) {
                             k::weight_sum(s, plan->f(weights), r, plan->f(den));
                             all_reduce(plan, plan->f(den), 1, false, s);
                         }
                         k::cross_entropy_with_grad(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(seed), plan->comm != nullptr,
-                                                   plan->f(den), plan->f(row_loss), plan->f(at), plan->f(gpos), r, v);
+                                                   plan->f(den), plan->f(row_loss), plan->f(at), plan->f(gpos), r, v, plan->counter(ctr));
                         all_reduce(plan, plan->f(at), 1, false, s);
                     });
                     break;
@@ -826,6 +840,53 @@ struct Scheduler {
             }
             default: unsupported(nd, "no kernel is written for it");
         }
+    }
+
+    // The gradients of one layer_norm (dx, dgamma and, as the column sums of the same adjoint,
+    // dbeta) read the same two matrices: whichever of them comes first in the program takes the
+    // others along in one launch. False when the row width has no one-launch kernel.
+    bool schedule_layer_norm_backward(uint32_t at) {
+        const Node& nd = node(at);
+        const bool from_dx = nd.op == Op::LayerNormGradX;
+        const uint32_t x = pos(nd.operands[0]), g = pos(nd.operands[from_dx ? 2 : 1]);
+        const uint64_t r = node(x).ty.shape.at(0), h = node(x).ty.shape.at(1);
+        if (!k::layer_norm_backward_supported(h)) return false;
+        int dx = from_dx ? static_cast<int>(at) : -1, dgamma = from_dx ? -1 : static_cast<int>(at), dbeta = -1;
+        int gamma = from_dx ? static_cast<int>(pos(nd.operands[1])) : -1;
+        for (uint32_t u : users[x]) {
+            if (u <= at || handled[u]) continue;
+            const Node& other = node(u);
+            if (dx < 0 && other.op == Op::LayerNormGradX && pos(other.operands[0]) == x && pos(other.operands[2]) == g &&
+                pos(other.operands[1]) < at) {
+                dx = static_cast<int>(u);
+                gamma = static_cast<int>(pos(other.operands[1]));
+            } else if (dgamma < 0 && other.op == Op::LayerNormGradGamma && pos(other.operands[0]) == x && pos(other.operands[1]) == g) {
+                dgamma = static_cast<int>(u);
+            }
+        }
+        if (dgamma >= 0)
+            for (uint32_t u : users[g])
+                if (u > at && node(u).op == Op::SumRows && !handled[u]) { dbeta = static_cast<int>(u); break; }
+        std::vector<uint32_t> reads = {x, g}, writes;
+        if (gamma >= 0) reads.push_back(static_cast<uint32_t>(gamma));
+        for (int other : {dx, dgamma, dbeta}) {
+            if (other < 0) continue;
+            uint32_t u = static_cast<uint32_t>(other);
+            handled[u] = 1;
+            Slot& slot = P->slots[u];
+            slot.kind = Slot::Arena;
+            slot.bytes = std::max<uint64_t>(node(u).ty.count() * 4, 4);
+            writes.push_back(u);
+        }
+        uint32_t tmp = scratch(k::layer_norm_backward_scratch_floats(r, h) * 4), ctr = counters(1);
+        writes.push_back(tmp);
+        msx_plan* plan = P;
+        auto at_or_null = [plan](int p) -> float* { return p >= 0 ? plan->f(static_cast<uint32_t>(p)) : nullptr; };
+        emit("layer_norm_backward", nd, reads, writes, [=](cudaStream_t s) {
+            k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(g), at_or_null(dx), plan->f(tmp), plan->counter(ctr),
+                                   at_or_null(dgamma), at_or_null(dbeta), r, h);
+        });
+        return true;
     }
 
     // C[m, n] = op(a) x op(b); `flip_*` reads the operand as the transpose of what its slot says.
@@ -1130,6 +1191,9 @@ void allocate(msx_plan* P, const Scheduler& sched) {
         cuda_ok(cudaMemcpy(P->d_consts, P->consts.data(), P->consts.size() * 4, cudaMemcpyHostToDevice), "cudaMemcpy(constants)");
     cuda_ok(cudaMalloc(&P->d_status, 4), "cudaMalloc(status)");
     cuda_ok(cudaMemset(P->d_status, 0, 4), "cudaMemset(status)");
+    uint64_t counter_bytes = std::max<uint64_t>(P->counters_used, 1) * 4;
+    cuda_ok(cudaMalloc(&P->d_counters, counter_bytes), "cudaMalloc(counters)");
+    cuda_ok(cudaMemset(P->d_counters, 0, counter_bytes), "cudaMemset(counters)");
     cuda_ok(cudaEventCreate(&P->clock_start), "cudaEventCreate");
     cuda_ok(cudaEventCreate(&P->clock_stop), "cudaEventCreate");
     if (!sched.updates.empty()) {
@@ -1174,6 +1238,7 @@ void release(msx_plan* P) {
     cudaFree(P->d_inputs);
     cudaFree(P->d_consts);
     cudaFree(P->d_status);
+    cudaFree(P->d_counters);
     cudaFree(P->d_update_tables);
     for (int s = 0; s < kStagingSlots; ++s) {
         if (P->pinned[s]) cudaFreeHost(P->pinned[s]);
