@@ -147,6 +147,12 @@ uint64_t msx_plan_describe(const msx_plan* plan, char* out, uint64_t capacity);
  * its bytes read + written and FLOP by the reference's counting rule (ir/kernel.rs:1221-1306,
  * :1562-1579). */
 int msx_profile_step(msx_plan* plan, float* launch_ms, uint32_t capacity);
+/* The same with every launch issued `repeats` times back to back between its two events and the
+ * time divided by `repeats`: a launch of a few microseconds is then timed at the rate the device
+ * runs it rather than the rate the host can issue single launches. Every kernel of a step writes
+ * a function of what it reads, so repeating it leaves the step's values unchanged; the optimizer
+ * launch, which updates in place, is issued once. */
+int msx_profile_step_repeated(msx_plan* plan, uint32_t repeats, float* launch_ms, uint32_t capacity);
 const char* msx_launch_kernel(const msx_plan* plan, uint32_t launch);
 uint64_t msx_launch_bytes(const msx_plan* plan, uint32_t launch);
 uint64_t msx_launch_flop(const msx_plan* plan, uint32_t launch);

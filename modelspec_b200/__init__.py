@@ -61,6 +61,7 @@ SIGNATURES = {
     "msx_loss_of": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_float), C.c_uint32]),
     "msx_steps_submitted": (C.c_uint64, [_P]),
     "msx_profile_step": (C.c_int, [_P, C.POINTER(C.c_float), C.c_uint32]),
+    "msx_profile_step_repeated": (C.c_int, [_P, C.c_uint32, C.POINTER(C.c_float), C.c_uint32]),
     "msx_launch_kernel": (C.c_char_p, [_P, C.c_uint32]),
     "msx_launch_bytes": (C.c_uint64, [_P, C.c_uint32]),
     "msx_launch_flop": (C.c_uint64, [_P, C.c_uint32]),
@@ -257,11 +258,12 @@ class Plan:
     def describe(self):
         return _text(lambda buf, cap: lib().msx_plan_describe(self.h, buf, cap))
 
-    def profile_step(self):
-        """Runs one step launch by launch; returns [(kernel, ms, bytes, flop)] per launch."""
+    def profile_step(self, repeats=1):
+        """Runs one step launch by launch (each launch `repeats` times back to back, its time
+        divided by `repeats`); returns [(kernel, ms, bytes, flop)] per launch."""
         n = self.stats()["launches_per_step"]
         ms = (C.c_float * n)()
-        self.device.check(lib().msx_profile_step(self.h, ms, n))
+        self.device.check(lib().msx_profile_step_repeated(self.h, repeats, ms, n))
         L = lib()
         return [(L.msx_launch_kernel(self.h, i).decode(), float(ms[i]), L.msx_launch_bytes(self.h, i),
                  L.msx_launch_flop(self.h, i)) for i in range(n)]

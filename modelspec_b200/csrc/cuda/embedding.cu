@@ -3,13 +3,15 @@
 // The gather copies rows (bit-exact). The gradient adds row g[n] to row ids[n] of a zero tensor
 // in ascending n, as the reference's sequential loop does
 // (crates/modelspec-runtime/src/cpu/interpreter.rs:923-941), without floating-point atomics: a
-// counting sort groups the occurrences of each id in ascending n (rank among earlier equal ids,
-// per-id counts by integer atomics, an exclusive scan for the group offsets), and one warp per
-// table row then adds its group's rows of g in that order, loads issued ahead of the dependent
-// additions. The result is bit-identical to the sequential loop, including `0 + g` for the first
+// sort by counting (the position of an occurrence is the number of occurrences that precede it in
+// (id, n) order) groups the occurrences of each id in ascending n, and one warp per table row
+// then finds its group by a search and adds those rows of g in that order, loads issued ahead of
+// the dependent additions. The result is bit-identical to the sequential loop, including `0 + g` for the first
 // occurrence and an exact zero row for an id never read. The reference's Vulkan path reaches the same order
 // with a rank sort of the ids (crates/modelspec-runtime/src/spirv/emit/rowwise.rs:1024-1190).
-// HBM-bound: the output is written once (rows * h * 4 bytes), g is read once.
+// HBM-bound: the output is written once (rows * h * 4 bytes), g is read once. With `base` the
+// result is base + that sum (one more rounded addition per element, the Add that follows the
+// scatter when a tied weight has a second, dense gradient).
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -42,116 +44,143 @@ __global__ void embedding_kernel(const float* __restrict__ table, const int32_t*
     }
 }
 
-// rank[n] = how many earlier n' hold the same id; count[id] = occurrences of id. Four lanes per
-// n, each scanning a quarter of every 1024-id tile of the ids before it, staged through shared
-// memory.
-__global__ void rank_kernel(const int32_t* __restrict__ ids, uint32_t n, uint32_t rows, int32_t* __restrict__ rank,
-                            int32_t* __restrict__ count, uint32_t* __restrict__ status) {
-    __shared__ int32_t tile[1024];
-    const uint32_t per_block = blockDim.x / 4;
-    uint32_t i = blockIdx.x * per_block + threadIdx.x / 4, part = threadIdx.x & 3u;
-    int32_t mine = i < n ? ids[i] : -1;
-    bool valid = i < n && mine >= 0 && static_cast<uint32_t>(mine) < rows;
-    if (i < n && !valid && part == 0) atomicOr(status, 1u);
-    // Only ids before the block's last n matter to anyone in the block.
-    uint32_t block_last = min(n, (blockIdx.x + 1) * per_block);
-    int32_t earlier = 0;
-    for (uint32_t t0 = 0; t0 < block_last; t0 += 1024) {
-        __syncthreads();
-        for (uint32_t j = threadIdx.x; j < 1024; j += blockDim.x) tile[j] = t0 + j < n ? ids[t0 + j] : -2;
-        __syncthreads();
-        if (!valid || t0 >= i) continue;
-        uint32_t stop = min(i, t0 + 1024u) - t0;
-        // Interleaved quarters keep the four lanes on different banks.
-        for (uint32_t j = part; j < stop; j += 4) earlier += tile[j] == mine ? 1 : 0;
+// Sorted position of occurrence i among all n: the number of occurrences with a smaller id, plus
+// the earlier ones with the same id. Writing (id, i) there sorts the occurrences by id, ascending
+// n within an id, without atomics. Eight lanes per occurrence each compare an eighth of every
+// 4096-id tile, read from shared memory as broadcast int4; an id outside the table sorts last and
+// is never matched by a row. n^2 / 8 comparisons per lane group: 2 M for n = 4096.
+constexpr int kOrderTile = 4096;
+__global__ void __launch_bounds__(256) order_kernel(const int32_t* __restrict__ ids, uint32_t n, uint32_t rows,
+                                                    int32_t* __restrict__ sorted_id, int32_t* __restrict__ sorted_n,
+                                                    uint32_t* __restrict__ status) {
+    __shared__ int4 tile[kOrderTile / 4];
+    const uint32_t i = blockIdx.x * 32 + threadIdx.x / 8, part = threadIdx.x & 7u;
+    int32_t mine = i < n ? ids[i] : 0;
+    const bool inside = i < n && mine >= 0 && static_cast<uint32_t>(mine) < rows;
+    if (i < n && !inside) {
+        if (part == 0) atomicOr(status, 1u);
+        mine = INT32_MAX;
     }
-    earlier += __shfl_xor_sync(0xffffffffu, earlier, 1);
-    earlier += __shfl_xor_sync(0xffffffffu, earlier, 2);
-    if (part != 0) return;
-    if (valid) {
-        rank[i] = earlier;
-        atomicAdd(&count[mine], 1);  // integer: the total does not depend on the order
-    } else if (i < n) {
-        rank[i] = -1;
-    }
-}
-
-// offset[r] = sum of count[0 .. r): one CTA of 1024 threads walks the rows 1024 at a time with
-// coalesced loads, a warp-shuffle scan inside each warp and a scan of the 32 warp totals.
-__global__ void offsets_kernel(const int32_t* __restrict__ count, uint32_t rows, int32_t* __restrict__ offset) {
-    __shared__ int32_t warp_total[32], warp_prefix[32];
-    __shared__ int32_t carry, chunk_total;
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) carry = 0;
-    __syncthreads();
-    for (uint32_t base = 0; base < rows; base += 1024) {
-        uint32_t r = base + threadIdx.x;
-        int32_t c = r < rows ? count[r] : 0;
-        int32_t inclusive = c;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            int32_t up = __shfl_up_sync(0xffffffffu, inclusive, d);
-            if (lane >= static_cast<uint32_t>(d)) inclusive += up;
-        }
-        if (lane == 31) warp_total[warp] = inclusive;
+    uint32_t before = 0;
+    for (uint32_t t0 = 0; t0 < n; t0 += kOrderTile) {
         __syncthreads();
-        if (warp == 0) {
-            int32_t t = warp_total[lane], scan = t;
+        for (uint32_t j = threadIdx.x; j < kOrderTile / 4; j += 256) {
+            int4 v;
+            int32_t* e = reinterpret_cast<int32_t*>(&v);
 #pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                int32_t up = __shfl_up_sync(0xffffffffu, scan, d);
-                if (lane >= static_cast<uint32_t>(d)) scan += up;
+            for (int q = 0; q < 4; ++q) {
+                uint32_t at = t0 + 4 * j + q;
+                int32_t id = at < n ? ids[at] : INT32_MAX;
+                e[q] = (at < n && (id < 0 || static_cast<uint32_t>(id) >= rows)) ? INT32_MAX : id;
             }
-            warp_prefix[lane] = scan - t;
-            if (lane == 31) chunk_total = scan;
+            tile[j] = v;
         }
         __syncthreads();
-        if (r < rows) offset[r] = carry + warp_prefix[warp] + inclusive - c;
-        __syncthreads();
-        if (threadIdx.x == 0) carry += chunk_total;
-        __syncthreads();
+        if (i >= n) continue;
+        const uint32_t stop = min(n - t0, static_cast<uint32_t>(kOrderTile));
+        for (uint32_t j = part; 4 * j < stop; j += 8) {
+            const int4 v = tile[j];
+            const int32_t* e = reinterpret_cast<const int32_t*>(&v);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t at = t0 + 4 * j + q;
+                // Padding past n holds INT32_MAX at an index above every i: never counted.
+                before += (e[q] < mine || (e[q] == mine && at < i)) ? 1u : 0u;
+            }
+        }
+    }
+    before += __shfl_xor_sync(0xffffffffu, before, 1);
+    before += __shfl_xor_sync(0xffffffffu, before, 2);
+    before += __shfl_xor_sync(0xffffffffu, before, 4);
+    if (part == 0 && i < n) {
+        sorted_id[before] = mine;
+        sorted_n[before] = static_cast<int32_t>(i);
     }
 }
 
-// list[offset[id] + rank] = n: the occurrences of each id, ascending.
-__global__ void list_kernel(const int32_t* __restrict__ ids, uint32_t n, const int32_t* __restrict__ rank,
-                            const int32_t* __restrict__ offset, int32_t* __restrict__ list) {
-    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n && rank[i] >= 0) list[offset[ids[i]] + rank[i]] = static_cast<int32_t>(i);
+// First position in sorted_id[0 .. n) whose id is not below `row`, by a 32-way search: each
+// round the lanes probe 32 evenly spaced positions of the remaining range.
+__device__ __forceinline__ uint32_t warp_lower_bound(const int32_t* __restrict__ sorted_id, uint32_t n, int32_t row, uint32_t lane) {
+    uint32_t lo = 0, hi = n;
+    while (lo < hi) {
+        const uint32_t step = (hi - lo + 31) / 32;
+        const uint32_t probe = lo + lane * step;
+        const bool below = probe < hi && __ldg(sorted_id + probe) < row;
+        const uint32_t count = __popc(__ballot_sync(0xffffffffu, below));
+        if (count == 0) return lo;
+        const uint32_t next_hi = min(hi, lo + count * step);
+        lo = lo + (count - 1) * step + 1;
+        hi = next_hi;
+    }
+    return lo;
 }
 
-// One warp per (table row, group of 32 columns), lane = column: 0 + g[n0] + g[n1] + ... over the
-// row's occurrences in ascending n. The additions stay in order; the loads of up to 32
-// occurrences are issued together, so a row hit hundreds of times costs a few memory round
-// trips, not one per occurrence.
-__global__ void scatter_kernel(const float* __restrict__ g, const int32_t* __restrict__ list,
-                               const int32_t* __restrict__ offset, const int32_t* __restrict__ count,
-                               float* __restrict__ out, uint32_t rows, uint32_t h) {
-    const uint32_t groups = (h + 31) / 32;
+// One warp per (table row, group of VEC * 32 columns): base + (0 + g[n0] + g[n1] + ...) over the
+// row's occurrences in ascending n. The additions stay in order; the loads of up to 8 occurrences
+// are issued together. A row nobody read gets `base` (or zero). VEC = 4 reads and writes 16 bytes
+// per lane and needs h % 4 == 0 and 16-byte aligned g, base and out.
+template <int VEC>
+__global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ g, const int32_t* __restrict__ sorted_id,
+                                                      const int32_t* __restrict__ sorted_n, uint32_t n,
+                                                      const float* __restrict__ base, float* __restrict__ out,
+                                                      uint32_t rows, uint32_t h) {
+    const uint32_t span = VEC * 32, groups = (h + span - 1) / span;
     const uint64_t items = static_cast<uint64_t>(rows) * groups;
     uint64_t item = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * blockDim.x) >> 5;
     for (; item < items; item += warps) {
-        const uint32_t row = static_cast<uint32_t>(item / groups), col = static_cast<uint32_t>(item % groups) * 32 + lane;
-        const int32_t c = count[row];
-        const int32_t* mine = list + offset[row];
+        const uint32_t row = static_cast<uint32_t>(item / groups), col = static_cast<uint32_t>(item % groups) * span + lane * VEC;
         const bool in = col < h;
-        float acc = 0.0f;
-        for (int32_t i0 = 0; i0 < c; i0 += 32) {
-            const int32_t entry = i0 + static_cast<int32_t>(lane) < c ? mine[i0 + lane] : 0;
-            const int32_t here = min(32, c - i0);
-            float v[32];
+        float acc[VEC];
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                const int32_t n = __shfl_sync(0xffffffffu, entry, e);
-                v[e] = (e < here && in) ? g[static_cast<uint64_t>(n) * h + col] : 0.0f;
+        for (int q = 0; q < VEC; ++q) acc[q] = 0.0f;
+        uint32_t at = n ? warp_lower_bound(sorted_id, n, static_cast<int32_t>(row), lane) : 0u;
+        while (at < n) {
+            // How many of the next 8 sorted entries still belong to this row.
+            const bool mine = lane < 8 && at + lane < n && __ldg(sorted_id + at + lane) == static_cast<int32_t>(row);
+            const uint32_t match = __ballot_sync(0xffffffffu, mine) & 0xffu;
+            const uint32_t here = __ffs(~match) - 1;  // entries are sorted: the matches are a prefix
+            if (here == 0) break;
+            const int32_t entry = lane < here ? __ldg(sorted_n + at + lane) : 0;
+            float v[8][VEC];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int32_t src = __shfl_sync(0xffffffffu, entry, e);
+                const float* from = g + static_cast<uint64_t>(src) * h + col;
+                if (static_cast<uint32_t>(e) < here && in) {
+                    if (VEC == 4) {
+                        const float4 f = *reinterpret_cast<const float4*>(from);
+                        v[e][0] = f.x; v[e][1 % VEC] = f.y; v[e][2 % VEC] = f.z; v[e][3 % VEC] = f.w;
+                    } else {
+                        v[e][0] = *from;
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) v[e][q] = 0.0f;
+                }
             }
 #pragma unroll
-            for (int e = 0; e < 32; ++e)
-                if (e < here) acc = acc + v[e];
+            for (int e = 0; e < 8; ++e)
+                if (static_cast<uint32_t>(e) < here) {
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) acc[q] = acc[q] + v[e][q];
+                }
+            at += here;
+            if (here < 8) break;
         }
-        if (in) out[static_cast<uint64_t>(row) * h + col] = acc;
+        if (!in) continue;
+        float* to = out + static_cast<uint64_t>(row) * h + col;
+        if (VEC == 4) {
+            float4 r = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
+            if (base) {
+                const float4 b = *reinterpret_cast<const float4*>(base + static_cast<uint64_t>(row) * h + col);
+                r.x = b.x + r.x; r.y = b.y + r.y; r.z = b.z + r.z; r.w = b.w + r.w;
+            }
+            *reinterpret_cast<float4*>(to) = r;
+        } else {
+            *to = base ? base[static_cast<uint64_t>(row) * h + col] + acc[0] : acc[0];
+        }
     }
 }
 
@@ -166,28 +195,28 @@ void embedding(cudaStream_t s, const float* table, const int32_t* ids, float* ou
     check_launch("embedding");
 }
 
-uint64_t embedding_grad_scratch_ints(uint64_t n, uint64_t rows) { return 2 * n + 2 * rows; }
+uint64_t embedding_grad_scratch_ints(uint64_t n, uint64_t rows) {
+    (void)rows;
+    return 2 * n;
+}
 
 void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* out, uint64_t n,
-                    uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status) {
+                    uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status, const float* base) {
     if (rows == 0 || h == 0) return;
-    int32_t* rank = scratch;
-    int32_t* list = scratch + n;
-    int32_t* count = scratch + 2 * n;
-    int32_t* offset = count + rows;
-    check(cudaMemsetAsync(count, 0, rows * sizeof(int32_t), s), "embedding_grad memset");
+    int32_t* sorted_id = scratch;
+    int32_t* sorted_n = scratch + n;
     if (n > 0) {
-        uint32_t blocks = static_cast<uint32_t>((n + 255) / 256);
-        rank_kernel<<<static_cast<uint32_t>((n + 63) / 64), 256, 0, s>>>(ids, static_cast<uint32_t>(n), static_cast<uint32_t>(rows), rank, count, status);
-        check_launch("embedding_grad");
-        offsets_kernel<<<1, 1024, 0, s>>>(count, static_cast<uint32_t>(rows), offset);
-        check_launch("embedding_grad");
-        list_kernel<<<blocks, 256, 0, s>>>(ids, static_cast<uint32_t>(n), rank, offset, list);
+        order_kernel<<<static_cast<uint32_t>((n + 31) / 32), 256, 0, s>>>(ids, static_cast<uint32_t>(n), static_cast<uint32_t>(rows), sorted_id,
+                                                                          sorted_n, status);
         check_launch("embedding_grad");
     }
-    uint64_t blocks = (rows * ((h + 31) / 32) * 32 + 255) / 256;
-    uint32_t grid = static_cast<uint32_t>(blocks > 148 * 32 ? 148 * 32 : blocks);
-    scatter_kernel<<<grid, 256, 0, s>>>(g, list, offset, count, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
+    auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool vec = h % 4 == 0 && aligned(g) && aligned(out) && aligned(base);
+    const uint64_t span = vec ? 128 : 32;
+    const uint64_t blocks = (rows * ((h + span - 1) / span) * 32 + 255) / 256;
+    const uint32_t grid = static_cast<uint32_t>(blocks > 148 * 32 ? 148 * 32 : blocks);
+    if (vec) scatter_kernel<4><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
+    else scatter_kernel<1><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
     check_launch("embedding_grad");
 }
 

@@ -1,28 +1,40 @@
 // matmul on the 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory,
-// f32 operands as a 3xTF32 split (tolerance class).
+// f32 operands as a split-TF32 product (tolerance class).
 //
-// Each f32 operand x is split into hi (its top 11 significant bits) and lo = x - hi, and a
-// product is summed as lo*hi + hi*lo + hi*hi in the f32 accumulator; the dropped lo*lo term and
-// the bits of lo below tf32 leave about 2^-20 of each |a||b| term, two orders below the kernel
-// tolerance 1e-5 + 1e-4 r. The exact kernel (gemm.cu) stays for bit-level parity runs.
+// Each f32 operand x is split into hi (its top 11 significant bits) and lo = x - hi, both exact
+// tf32 values (the tensor core keeps 11 significant bits of lo, so x is represented to about
+// 2^-21 |x|), and a product is summed as hi*hi + hi*lo + lo*hi + lo*lo in f32 accumulators: two
+// orders below the kernel tolerance 1e-5 + 1e-4 r. The exact kernel (gemm.cu) stays for
+// bit-level parity runs.
 //
-// One CTA computes a 128 x BN tile (BN = 64 or 128) over a range of 32-deep k blocks:
+// One tcgen05.mma of this shape costs about the same 100-130 cycles whatever its width (its 128
+// rows of A are read 32 bytes at a time), so the four partial products are not four MMAs: the hi
+// and lo halves of A are stacked along M (64 rows each of one 128-row operand) and those of B
+// along N (BN columns each of one 2 BN-wide operand). One MMA per 8-deep k slice then yields all
+// four products, in four quadrants of tensor memory that the epilogue adds.
+//
+// One CTA computes a 64 x BN tile (BN = 32, 64 or 128) over a range of 32-deep k blocks:
 //   warps 0-7  load the A and B blocks from global memory, split them and store hi and lo in the
 //              128-byte-swizzled shared-memory layouts tcgen05 reads (K-major or MN-major by how
 //              the operand is stored, so NN, TN and NT need no transposed copy), then drain the
-//              accumulator: tcgen05.ld, bounds-checked stores to C or to the split-K workspace;
-//   warp 8     allocates tensor memory, issues 12 MMAs per k block (4 k-slices x 3 products) from
-//              one thread, and releases each shared-memory stage with tcgen05.commit.
+//              accumulator: tcgen05.ld, the quadrant sums, row-wise stores to C or to the
+//              split-K workspace;
+//   warp 8     allocates tensor memory, issues 4 MMAs per k block from one thread, and releases
+//              each shared-memory stage with tcgen05.commit.
 // The split happens on the way from global to shared memory rather than after a TMA copy: a TMA
-// tile would be written, read back and written twice more, and shared-memory bandwidth is what
-// bounds 3xTF32 from shared operands (per k block 96 KB of MMA operand reads against 64 KB of
-// split stores here, 128 KB with a TMA staging copy). Operands whose row pitch is not a multiple
-// of 16 bytes (a 30,522-wide logits matrix) could not be TMA sources in any case.
+// tile would be written, read back and written twice more, and shared-memory bandwidth (split
+// stores plus the operand reads of the MMAs) is what bounds a wide tile. Operands whose row
+// pitch is not a multiple of 16 bytes (a 30,522-wide logits matrix) could not be TMA sources in
+// any case.
 //
-// Three stages of 64 KB. Stage hand-off is by mbarriers; every wait is bounded and, when it runs
-// out, raises bit 1 of the status word, makes every role leave its loop, frees the tensor memory
-// and returns. A k range split across CTAs (grid.z) writes partial tiles that
-// `splitk_reduce_kernel` adds in ascending split order (deterministic).
+// Shared memory stays under half an SM's (2 to 4 stages of 24 to 48 KB) and registers under
+// half its file, so two CTAs share an SM and one drains while the other loads. Stage hand-off is
+// by mbarriers; every wait is bounded and, when it runs out, raises bit 1 of the status word,
+// makes every role leave its loop, frees the tensor memory and returns. A k range split across
+// CTAs (grid.z) writes partial tiles that `splitk_reduce_kernel` adds in ascending split order
+// (deterministic).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -31,14 +43,28 @@ namespace k {
 
 namespace {
 
-constexpr int BM = 128, BK = 32, STAGES = 3;
+constexpr int BM = 64, BK = 32;
 constexpr int LOADER_THREADS = 256, THREADS = LOADER_THREADS + 32;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives up
 
-template <int BN> struct Smem {
-    static constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
-    static constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;  // a_hi, a_lo, b_hi, b_lo
+// The cost model of matmul_tc_plan, in SM cycles (tuning builds may override).
+#ifndef MSX_TC_FIXED
+#define MSX_TC_FIXED 5000.0
+#define MSX_TC_KB32 450.0
+#define MSX_TC_KB64 520.0
+#define MSX_TC_KB128 800.0
+#define MSX_TC_REDUCE_FIXED 8000.0
+#define MSX_TC_REDUCE_BYTES_PER_CYCLE 3000.0
+#endif
+
+template <int BN> struct Config {
+    static constexpr int STAGES = BN == 128 ? 2 : (BN == 64 ? 3 : 4);  // shared-memory stages
+    static constexpr int SETS = BN == 128 ? 2 : (BN == 64 ? 3 : 4);    // register sets of loads in flight
+    static constexpr uint32_t A_BYTES = 2 * BM * BK * 4;  // hi rows 0-63, lo rows 64-127
+    static constexpr uint32_t B_BYTES = 2 * BN * BK * 4;  // hi columns 0..BN-1, lo columns BN..2BN-1
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr uint32_t TMEM_COLUMNS = 2 * BN;
 };
 
 struct TcArgs {
@@ -49,7 +75,7 @@ struct TcArgs {
     uint32_t m, n, k;
     uint32_t lda, ldb, ldc;        // row pitch, in elements, of each matrix as stored
     uint32_t kblocks_per_split;
-    uint32_t a_vec, b_vec, c_vec;  // 16-byte accesses are aligned for this operand
+    uint32_t a_vec, b_vec;         // 16-byte loads are aligned for this operand
     // Batched products: grid.z = batch index z, split as (z / inner, z % inner); each matrix of
     // problem z starts at outer * stride_outer + inner * stride_inner elements. inner = 0: not batched.
     uint32_t batch_inner;
@@ -96,19 +122,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
-// The shared-memory matrix descriptor of tcgen05 (version 1): start address, leading and stride
-// byte offsets in 16-byte units, and the swizzle of the tile: 2 = 128-byte swizzle of 16-byte
-// chunks (K-major tiles), 1 = 128-byte swizzle of 32-byte chunks, the one layout the tensor core
-// reads MN-major 32-bit operands from.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
-    uint64_t d = static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
-    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= 1ull << 46;  // descriptor version of sm_100
-    d |= static_cast<uint64_t>(layout_type) << 61;
-    return d;
-}
-
 __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -120,6 +133,21 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint6
 
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive columns of tensor memory: r[j] = column `taddr.column + j` of this
+// thread's lane.
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
 }
 
 // Byte offset of the 16-byte chunk holding elements (row, 4 c16 .. 4 c16 + 3) of a K-major tile:
@@ -155,32 +183,38 @@ __device__ __forceinline__ float4 load4(const float* __restrict__ p, uint64_t in
 
 // hi = x with the 13 mantissa bits below tf32 cleared (an exact tf32, whatever rounding the tensor
 // core would apply to a wider value), lo = x - hi exactly (at most 13 significant bits, below
-// 2^-10 |x|). The tensor core keeps 11 significant bits of lo, so x is represented to about
-// 2^-21 |x|. One logic op and one subtraction per element: the split must not cost more than
+// 2^-10 |x|). One logic op and one subtraction per element: the split must not cost more than
 // the MMAs it feeds.
 __device__ __forceinline__ float top_tf32(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 
-__device__ __forceinline__ void store_split(char* hi, char* lo, uint32_t offset, float4 v) {
+__device__ __forceinline__ void store_split(char* tile, uint32_t hi_offset, uint32_t lo_offset, float4 v) {
     float4 h, l;
     h.x = top_tf32(v.x); h.y = top_tf32(v.y); h.z = top_tf32(v.z); h.w = top_tf32(v.w);
     l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
-    *reinterpret_cast<float4*>(hi + offset) = h;
-    *reinterpret_cast<float4*>(lo + offset) = l;
+    *reinterpret_cast<float4*>(tile + hi_offset) = h;
+    *reinterpret_cast<float4*>(tile + lo_offset) = l;
 }
 
 __device__ __forceinline__ uint32_t in_range(uint32_t start, uint32_t limit) {
     return start >= limit ? 0u : (limit - start >= 4u ? 4u : limit - start);
 }
 
+__device__ __forceinline__ void loaders_barrier(uint32_t threads) {
+    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
 template <int BN, bool A_T, bool B_T>
-__global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
+__global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
+    using Cfg = Config<BN>;
+    constexpr int STAGES = Cfg::STAGES, SETS = Cfg::SETS;
     extern __shared__ char smem_raw[];
     // Tiles need 1024-byte alignment for the swizzle pattern to line up with address bits.
     char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * Smem<BN>::STAGE_BYTES);
-    // bars[0..2] full, bars[3..5] empty, bars[6] accumulator ready; then the TMEM address and the abort flag.
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 9);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * Cfg::STAGE_BYTES);
+    // bars[0 .. STAGES) full, bars[STAGES .. 2 STAGES) empty, bars[2 STAGES] accumulator ready;
+    // then the TMEM address and the abort flag.
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 2);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) TRACE(0);
@@ -192,6 +226,63 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
     const uint32_t kb_end = min(kblocks_total, kb_begin + args.kblocks_per_split);
     const uint32_t kblocks = kb_end > kb_begin ? kb_end - kb_begin : 0;
 
+    // ---- loaders, first part: where this thread's chunks sit, and the first loads. They are issued
+    // before the barriers and the tensor memory are set up, so that the set-up hides under them.
+    const float* __restrict__ a = args.a + z_outer * args.a_outer + z_inner * args.a_inner;
+    const float* __restrict__ b = args.b + z_outer * args.b_outer + z_inner * args.b_inner;
+    constexpr int A_CHUNKS = BM * BK / 4 / LOADER_THREADS, B_CHUNKS = BN * BK / 4 / LOADER_THREADS;
+    // Where this thread's chunks sit in a block does not depend on the block: the tile coordinates
+    // and the shared-memory offsets are computed once. The lo half of an operand lies half the
+    // operand's bytes after the hi half (64 rows, BN rows, or as many 32-element panels).
+    uint32_t a_row[A_CHUNKS], a_col[A_CHUNKS], aoff[A_CHUNKS], b_row[B_CHUNKS], b_col[B_CHUNKS], boff[B_CHUNKS];
+#pragma unroll
+    for (int i = 0; i < A_CHUNKS; ++i) {
+        uint32_t q = tid + i * LOADER_THREADS;
+        if (A_T) { a_row[i] = q >> 4; a_col[i] = (q & 15u) * 4; aoff[i] = mn_major_offset(q >> 4, q & 15u); }      // (k, m)
+        else     { a_row[i] = q >> 3; a_col[i] = (q & 7u) * 4;  aoff[i] = k_major_offset(q >> 3, q & 7u); }        // (m, k)
+    }
+#pragma unroll
+    for (int i = 0; i < B_CHUNKS; ++i) {
+        uint32_t q = tid + i * LOADER_THREADS;
+        if (B_T) { b_row[i] = q >> 3; b_col[i] = (q & 7u) * 4; boff[i] = k_major_offset(q >> 3, q & 7u); }         // (n, k)
+        else     { b_row[i] = q / (BN / 4); b_col[i] = (q % (BN / 4)) * 4; boff[i] = mn_major_offset(q / (BN / 4), q % (BN / 4)); }  // (k, n)
+    }
+    auto fetch = [&](uint32_t kb, float4 (&av)[A_CHUNKS], float4 (&bv)[B_CHUNKS]) {
+        const uint32_t k0 = (kb_begin + kb) * BK;
+#pragma unroll
+        for (int i = 0; i < A_CHUNKS; ++i) {
+            if (A_T) {  // stored [k, m]: 4 consecutive m of one k row
+                uint32_t gk = k0 + a_row[i], gm = m0 + a_col[i];
+                uint32_t valid = gk < args.k ? in_range(gm, args.m) : 0u;
+                av[i] = load4(a, static_cast<uint64_t>(gk) * args.lda + gm, valid, args.a_vec);
+            } else {    // stored [m, k]: 4 consecutive k of one row
+                uint32_t gm = m0 + a_row[i], gk = k0 + a_col[i];
+                uint32_t valid = gm < args.m ? in_range(gk, args.k) : 0u;
+                av[i] = load4(a, static_cast<uint64_t>(gm) * args.lda + gk, valid, args.a_vec);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < B_CHUNKS; ++i) {
+            if (B_T) {  // stored [n, k]
+                uint32_t gn = n0 + b_row[i], gk = k0 + b_col[i];
+                uint32_t valid = gn < args.n ? in_range(gk, args.k) : 0u;
+                bv[i] = load4(b, static_cast<uint64_t>(gn) * args.ldb + gk, valid, args.b_vec);
+            } else {    // stored [k, n]
+                uint32_t gk = k0 + b_row[i], gn = n0 + b_col[i];
+                uint32_t valid = gk < args.k ? in_range(gn, args.n) : 0u;
+                bv[i] = load4(b, static_cast<uint64_t>(gk) * args.ldb + gn, valid, args.b_vec);
+            }
+        }
+    };
+    // SETS register sets: the loads of the next SETS - 1 blocks are in flight while a block is
+    // split and stored.
+    float4 av[SETS][A_CHUNKS], bv[SETS][B_CHUNKS];
+    if (warp < 8) {
+#pragma unroll
+        for (int s = 0; s < SETS - 1; ++s)
+            if (static_cast<uint32_t>(s) < kblocks) fetch(s, av[s], bv[s]);
+    }
+
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&bars[s]), LOADER_THREADS);
@@ -202,7 +293,7 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 8) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(static_cast<uint32_t>(BN)) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Cfg::TMEM_COLUMNS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -213,177 +304,142 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
 
     if (warp < 8) {
         // ---- loaders: global -> (hi, lo) -> swizzled shared memory ---------------------------
-        const float* __restrict__ a = args.a + z_outer * args.a_outer + z_inner * args.a_inner;
-        const float* __restrict__ b = args.b + z_outer * args.b_outer + z_inner * args.b_inner;
         bool alive = true;
-        constexpr int A_CHUNKS = BM * BK / 4 / LOADER_THREADS, B_CHUNKS = BN * BK / 4 / LOADER_THREADS;
-        // Where this thread's chunks sit in a block does not depend on the block: the tile
-        // coordinates and the shared-memory offsets are computed once.
-        uint32_t a_row[A_CHUNKS], a_col[A_CHUNKS], aoff[A_CHUNKS], b_row[B_CHUNKS], b_col[B_CHUNKS], boff[B_CHUNKS];
-#pragma unroll
-        for (int i = 0; i < A_CHUNKS; ++i) {
-            uint32_t q = tid + i * LOADER_THREADS;
-            if (A_T) { a_row[i] = q >> 5; a_col[i] = (q & 31u) * 4; aoff[i] = mn_major_offset(q >> 5, q & 31u); }      // (k, m)
-            else     { a_row[i] = q >> 3; a_col[i] = (q & 7u) * 4;  aoff[i] = k_major_offset(q >> 3, q & 7u); }        // (m, k)
-        }
-#pragma unroll
-        for (int i = 0; i < B_CHUNKS; ++i) {
-            uint32_t q = tid + i * LOADER_THREADS;
-            if (B_T) { b_row[i] = q >> 3; b_col[i] = (q & 7u) * 4; boff[i] = k_major_offset(q >> 3, q & 7u); }         // (n, k)
-            else     { b_row[i] = q / (BN / 4); b_col[i] = (q % (BN / 4)) * 4; boff[i] = mn_major_offset(q / (BN / 4), q % (BN / 4)); }  // (k, n)
-        }
-        auto fetch = [&](uint32_t kb, float4 (&av)[A_CHUNKS], float4 (&bv)[B_CHUNKS]) {
-            const uint32_t k0 = (kb_begin + kb) * BK;
-#pragma unroll
-            for (int i = 0; i < A_CHUNKS; ++i) {
-                if (A_T) {  // stored [k, m]: 4 consecutive m of one k row
-                    uint32_t gk = k0 + a_row[i], gm = m0 + a_col[i];
-                    uint32_t valid = gk < args.k ? in_range(gm, args.m) : 0u;
-                    av[i] = load4(a, static_cast<uint64_t>(gk) * args.lda + gm, valid, args.a_vec);
-                } else {    // stored [m, k]: 4 consecutive k of one row
-                    uint32_t gm = m0 + a_row[i], gk = k0 + a_col[i];
-                    uint32_t valid = gm < args.m ? in_range(gk, args.k) : 0u;
-                    av[i] = load4(a, static_cast<uint64_t>(gm) * args.lda + gk, valid, args.a_vec);
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < B_CHUNKS; ++i) {
-                if (B_T) {  // stored [n, k]
-                    uint32_t gn = n0 + b_row[i], gk = k0 + b_col[i];
-                    uint32_t valid = gn < args.n ? in_range(gk, args.k) : 0u;
-                    bv[i] = load4(b, static_cast<uint64_t>(gn) * args.ldb + gk, valid, args.b_vec);
-                } else {    // stored [k, n]
-                    uint32_t gk = k0 + b_row[i], gn = n0 + b_col[i];
-                    uint32_t valid = gk < args.k ? in_range(gn, args.n) : 0u;
-                    bv[i] = load4(b, static_cast<uint64_t>(gk) * args.ldb + gn, valid, args.b_vec);
-                }
-            }
-        };
-        auto deposit = [&](uint32_t kb, const float4 (&av)[A_CHUNKS], const float4 (&bv)[B_CHUNKS]) -> bool {
+        auto deposit = [&](uint32_t kb, const float4 (&a_regs)[A_CHUNKS], const float4 (&b_regs)[B_CHUNKS]) -> bool {
             const uint32_t stage = kb % STAGES, round = kb / STAGES;
-            char* a_hi = tiles + stage * Smem<BN>::STAGE_BYTES;
-            char* a_lo = a_hi + Smem<BN>::A_BYTES;
-            char* b_hi = a_lo + Smem<BN>::A_BYTES;
-            char* b_lo = b_hi + Smem<BN>::B_BYTES;
+            char* a_tile = tiles + stage * Cfg::STAGE_BYTES;
+            char* b_tile = a_tile + Cfg::A_BYTES;
             // The stage is free once the MMAs that read its previous contents have completed.
             if (!mbar_wait(smem_u32(&bars[STAGES + stage]), (round & 1u) ^ 1u, abort_flag, args.status)) return false;
 #pragma unroll
-            for (int i = 0; i < A_CHUNKS; ++i) store_split(a_hi, a_lo, aoff[i], av[i]);
+            for (int i = 0; i < A_CHUNKS; ++i) store_split(a_tile, aoff[i], aoff[i] + Cfg::A_BYTES / 2, a_regs[i]);
 #pragma unroll
-            for (int i = 0; i < B_CHUNKS; ++i) store_split(b_hi, b_lo, boff[i], bv[i]);
+            for (int i = 0; i < B_CHUNKS; ++i) store_split(b_tile, boff[i], boff[i] + Cfg::B_BYTES / 2, b_regs[i]);
             // Make the generic-proxy stores visible to the tensor core's async-proxy reads.
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(smem_u32(&bars[stage]));
             if (tid == 0 && kb < 4) TRACE(2 + kb);
             return true;
         };
-        // Three register sets: the loads of blocks kb + 1 and kb + 2 are in flight while block kb is
-        // split and stored. A global load takes about 2,500 cycles to come back here and a block
-        // about 1,000 to deposit, so two blocks of prefetch cover it.
-        float4 av0[A_CHUNKS], bv0[B_CHUNKS], av1[A_CHUNKS], bv1[B_CHUNKS], av2[A_CHUNKS], bv2[B_CHUNKS];
-        if (kblocks > 0) fetch(0, av0, bv0);
-        if (kblocks > 1) fetch(1, av1, bv1);
-        for (uint32_t kb = 0; kb < kblocks && alive; kb += 3) {
-            if (kb + 2 < kblocks) fetch(kb + 2, av2, bv2);
-            alive = deposit(kb, av0, bv0);
-            if (!alive || kb + 1 >= kblocks) break;
-            if (kb + 3 < kblocks) fetch(kb + 3, av0, bv0);
-            alive = deposit(kb + 1, av1, bv1);
-            if (!alive || kb + 2 >= kblocks) break;
-            if (kb + 4 < kblocks) fetch(kb + 4, av1, bv1);
-            alive = deposit(kb + 2, av2, bv2);
+        for (uint32_t kb0 = 0; kb0 < kblocks && alive; kb0 += SETS) {
+#pragma unroll
+            for (int s = 0; s < SETS; ++s) {
+                const uint32_t kb = kb0 + s;
+                if (kb >= kblocks || !alive) break;
+                if (kb + SETS - 1 < kblocks) fetch(kb + SETS - 1, av[(s + SETS - 1) % SETS], bv[(s + SETS - 1) % SETS]);
+                alive = deposit(kb, av[s], bv[s]);
+            }
         }
         // ---- epilogue: tensor memory -> registers -> global -----------------------------------
+        // Lanes 0-63 of tensor memory hold the A_hi rows, 64-127 the A_lo rows of the same 64 tile
+        // rows; columns [0, BN) the products with B_hi, [BN, 2 BN) those with B_lo. A warp reads
+        // its lane quarter, adds the two column halves, and the lo warps hand their sums to the hi
+        // warps of the same rows through shared memory (the stages are free by now).
         if (alive && kblocks > 0) alive = mbar_wait(smem_u32(&bars[2 * STAGES]), 0, abort_flag, args.status);
         alive = __all_sync(0xffffffffu, alive);  // tcgen05.ld is warp-wide: decide as a warp
         if (tid == 0) TRACE(6);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t col_half = warp >> 2;  // warps 0-3: first half of the columns, 4-7: second
-        float* staging = reinterpret_cast<float*>(tiles) + warp * (32 * 33);
+        const uint32_t quarter = warp & 3u, half = warp >> 2;
+        const bool holds_hi = quarter < 2;
+        const uint32_t row_block = (quarter & 1u) * 32u;
+        constexpr int PARTS = BN == 128 ? 2 : 1;
+        constexpr uint32_t EPILOGUE_THREADS = BN == 32 ? 128u : 256u;
+        const bool drains = BN != 32 || half == 0;  // a 32-column tile is one block per lane quarter
+        float* staging = reinterpret_cast<float*>(tiles);  // [warp][part][32 x 33]
         float* __restrict__ out = batched ? args.c + z_outer * args.c_outer + z_inner * args.c_inner
                                           : args.c + static_cast<uint64_t>(blockIdx.z) * args.m * args.ldc;
+        if (drains) {
 #pragma unroll
-        for (int part = 0; part < BN / 64; ++part) {
-            const uint32_t col = col_half * (BN / 2) + part * 32;
-            uint32_t r[32];
-            if (alive && kblocks > 0) {
-                uint32_t taddr = tmem_base + (((warp & 3u) * 32u) << 16) + col;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                    : "r"(taddr)
-                    : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = 0u;  // an empty k range contributes zeros
-            }
-            // Through shared memory (the stages are free once the accumulator is ready), so that
-            // a warp writes whole rows: 32 consecutive columns per store, whatever the row pitch.
-            // Lane = row on the way in, lane = column on the way out; pitch 33 keeps both
-            // conflict-free. `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
-#pragma unroll
-            for (int j = 0; j < 32; ++j) staging[lane * 33 + j] = __uint_as_float(r[j]) + 0.0f;
-            __syncwarp();
-            const uint32_t gn = n0 + col + lane;
-            if (gn < args.n) {
-                const float bias = args.bias ? args.bias[gn] : 0.0f;
-                float* dst = out + static_cast<uint64_t>(m0 + (warp & 3u) * 32) * args.ldc + gn;
-                const uint32_t rows_here = m0 + (warp & 3u) * 32 < args.m ? min(32u, args.m - (m0 + (warp & 3u) * 32)) : 0u;
-                if (rows_here == 32) {
-                    // All the shared-memory reads first: the stores then leave back to back.
-                    float v[32];
-#pragma unroll
-                    for (int rr = 0; rr < 32; ++rr) v[rr] = staging[rr * 33 + lane] + bias;
-#pragma unroll
-                    for (int rr = 0; rr < 32; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = v[rr];
+            for (int part = 0; part < PARTS; ++part) {
+                const uint32_t col = BN == 128 ? half * 64u + part * 32u : (BN == 64 ? half * 32u : 0u);
+                uint32_t r1[32], r2[32];
+                if (alive && kblocks > 0) {
+                    const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + col;
+                    tmem_load32(taddr, r1);
+                    tmem_load32(taddr + BN, r2);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 } else {
-                    for (uint32_t rr = 0; rr < rows_here; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = staging[rr * 33 + lane] + bias;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) { r1[j] = 0u; r2[j] = 0u; }  // an empty k range contributes zeros
+                }
+                float* mine = staging + (warp * PARTS + part) * (32 * 33);
+                // Lane = row on the way in, lane = column on the way out; pitch 33 keeps both
+                // conflict-free.
+                if (!holds_hi) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mine[lane * 33 + j] = __uint_as_float(r1[j]) + __uint_as_float(r2[j]);
+                }
+                loaders_barrier(EPILOGUE_THREADS);
+                if (holds_hi) {
+                    const float* other = staging + ((warp + 2) * PARTS + part) * (32 * 33);
+                    // `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        mine[lane * 33 + j] = ((__uint_as_float(r1[j]) + __uint_as_float(r2[j])) + other[lane * 33 + j]) + 0.0f;
+                    __syncwarp();
+                    // A warp writes whole rows: 32 consecutive columns per store, whatever the row pitch.
+                    const uint32_t gn = n0 + col + lane, row0 = m0 + row_block;
+                    if (gn < args.n && row0 < args.m) {
+                        const float bias = args.bias ? args.bias[gn] : 0.0f;
+                        float* dst = out + static_cast<uint64_t>(row0) * args.ldc + gn;
+                        const uint32_t rows_here = min(32u, args.m - row0);
+                        if (rows_here == 32) {
+                            // All the shared-memory reads first: the stores then leave back to back.
+                            float v[32];
+#pragma unroll
+                            for (int rr = 0; rr < 32; ++rr) v[rr] = mine[rr * 33 + lane] + bias;
+#pragma unroll
+                            for (int rr = 0; rr < 32; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = v[rr];
+                        } else {
+                            for (uint32_t rr = 0; rr < rows_here; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = mine[rr * 33 + lane] + bias;
+                        }
+                    }
                 }
             }
-            __syncwarp();
         }
     } else {
         // ---- the MMA warp: one thread issues, the tensor core runs asynchronously ---------------
-        // Instruction descriptor: f32 accumulator, tf32 A and B, their majors, N >> 3, M >> 4.
+        // Instruction descriptor: f32 accumulator, tf32 A and B, their majors, N >> 3, M >> 4, for
+        // the stacked operands: M = 128 (hi and lo rows), N = 2 BN (hi and lo columns).
         const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_T ? 1u : 0u) << 15) | ((B_T ? 0u : 1u) << 16) |
-                               (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+                               (static_cast<uint32_t>((2 * BN) >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+        // The shared-memory matrix descriptor of tcgen05 (version 1): start address (bits 0-13),
+        // leading (16-29) and stride (32-45) byte offsets, all in 16-byte units, bit 46 set (the
+        // sm_100 version), and in bits 61-63 the swizzle of the tile: 2 = 128-byte swizzle of
+        // 16-byte chunks (K-major tiles), 1 = 128-byte swizzle of 32-byte chunks, the one layout
+        // the tensor core reads MN-major 32-bit operands from. The descriptors of a k block differ
+        // only in the start address: everything else is built once.
+        constexpr uint32_t a_lbo = A_T ? BK * 128u : 16u, b_lbo = B_T ? 16u : BK * 128u;
+        constexpr uint32_t a_sbo = A_T ? 512u : 1024u, b_sbo = B_T ? 1024u : 512u;
+        constexpr uint32_t a_type = A_T ? 1u : 2u, b_type = B_T ? 2u : 1u;
+        constexpr uint32_t a_high = ((a_sbo >> 4) & 0x3FFFu) | (1u << 14) | (a_type << 29);
+        constexpr uint32_t b_high = ((b_sbo >> 4) & 0x3FFFu) | (1u << 14) | (b_type << 29);
+        constexpr uint32_t a_low = ((a_lbo >> 4) & 0x3FFFu) << 16, b_low = ((b_lbo >> 4) & 0x3FFFu) << 16;
+        const uint32_t tiles16 = (smem_u32(tiles) & 0x3FFFFu) >> 4;
+        auto desc = [](uint32_t high, uint32_t low) { return (static_cast<uint64_t>(high) << 32) | low; };
         bool alive = true;
+        uint32_t stage = 0, parity = 0;
         for (uint32_t kb = 0; kb < kblocks && alive; ++kb) {
-            const uint32_t stage = kb % STAGES, round = kb / STAGES;
-            alive = mbar_wait(smem_u32(&bars[stage]), round & 1u, abort_flag, args.status);
+            alive = mbar_wait(smem_u32(&bars[stage]), parity, abort_flag, args.status);
             if (!alive) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
-                const uint32_t a_hi = smem_u32(tiles + stage * Smem<BN>::STAGE_BYTES);
-                const uint32_t a_lo = a_hi + Smem<BN>::A_BYTES;
-                const uint32_t b_hi = a_lo + Smem<BN>::A_BYTES;
-                const uint32_t b_lo = b_hi + Smem<BN>::B_BYTES;
+                const uint32_t a16 = a_low + tiles16 + stage * (Cfg::STAGE_BYTES >> 4);
+                const uint32_t b16 = b_low + tiles16 + stage * (Cfg::STAGE_BYTES >> 4) + (Cfg::A_BYTES >> 4);
 #pragma unroll
                 for (uint32_t ks = 0; ks < BK / 8; ++ks) {
                     // One MMA covers k = 8: 32 bytes along a K-major row (8-row groups 1024 bytes
                     // apart), or 8 rows of an MN-major panel (4-row groups 512 bytes apart, panels
                     // of 32 MN elements 4096 bytes apart).
-                    const uint32_t a_step = A_T ? ks * 1024u : ks * 32u;
-                    const uint32_t b_step = B_T ? ks * 32u : ks * 1024u;
-                    const uint32_t a_lbo = A_T ? BK * 128u : 16u, b_lbo = B_T ? 16u : BK * 128u;
-                    const uint32_t a_sbo = A_T ? 512u : 1024u, b_sbo = B_T ? 1024u : 512u;
-                    const uint32_t a_type = A_T ? 1u : 2u, b_type = B_T ? 2u : 1u;
-                    const uint64_t da_hi = smem_desc(a_hi + a_step, a_lbo, a_sbo, a_type), da_lo = smem_desc(a_lo + a_step, a_lbo, a_sbo, a_type);
-                    const uint64_t db_hi = smem_desc(b_hi + b_step, b_lbo, b_sbo, b_type), db_lo = smem_desc(b_lo + b_step, b_lbo, b_sbo, b_type);
-                    mma_tf32(tmem_base, da_lo, db_hi, idesc, (kb | ks) != 0u);
-                    mma_tf32(tmem_base, da_hi, db_lo, idesc, 1u);
-                    mma_tf32(tmem_base, da_hi, db_hi, idesc, 1u);
+                    const uint32_t a_step = (A_T ? ks * 1024u : ks * 32u) >> 4;
+                    const uint32_t b_step = (B_T ? ks * 32u : ks * 1024u) >> 4;
+                    mma_tf32(tmem_base, desc(a_high, a16 + a_step), desc(b_high, b16 + b_step), idesc, (kb | ks) != 0u);
                 }
                 mma_commit(smem_u32(&bars[STAGES + stage]));                   // frees the stage when they finish
                 if (kb < 4) TRACE(8 + kb);
                 if (kb + 1 == kblocks) mma_commit(smem_u32(&bars[2 * STAGES]));  // and, at the end, the accumulator
             }
+            if (++stage == STAGES) { stage = 0; parity ^= 1u; }
             __syncwarp();
         }
     }
@@ -392,7 +448,7 @@ __global__ void __launch_bounds__(THREADS, 1) matmul_tc_kernel(TcArgs args) {
     __syncthreads();
     if (tid == 0) TRACE(12);
     if (warp == 8) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(static_cast<uint32_t>(BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLUMNS) : "memory");
     }
 }
 
@@ -408,8 +464,14 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, float* __rest
 
 template <int BN, bool A_T, bool B_T> void launch(cudaStream_t s, const TcArgs& args, dim3 grid) {
     auto kernel = matmul_tc_kernel<BN, A_T, B_T>;
-    check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Smem<BN>::TOTAL)), "matmul_tc shared memory");
-    kernel<<<grid, THREADS, Smem<BN>::TOTAL, s>>>(args);
+    static int configured_device = -1;  // the attribute is per device: set it when the device changes
+    int device = 0;
+    check(cudaGetDevice(&device), "cudaGetDevice");
+    if (device != configured_device) {
+        check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Config<BN>::TOTAL)), "matmul_tc shared memory");
+        configured_device = device;
+    }
+    kernel<<<grid, THREADS, Config<BN>::TOTAL, s>>>(args);
     check_launch("matmul_tc");
 }
 
@@ -418,6 +480,12 @@ template <int BN> void launch_forms(cudaStream_t s, const TcArgs& args, dim3 gri
     else if (a_t) launch<BN, true, false>(s, args, grid);
     else if (b_t) launch<BN, false, true>(s, args, grid);
     else launch<BN, false, false>(s, args, grid);
+}
+
+void launch_width(cudaStream_t s, const TcArgs& args, dim3 grid, uint32_t bn, bool a_t, bool b_t) {
+    if (bn == 32) launch_forms<32>(s, args, grid, a_t, b_t);
+    else if (bn == 64) launch_forms<64>(s, args, grid, a_t, b_t);
+    else launch_forms<128>(s, args, grid, a_t, b_t);
 }
 
 #ifdef MSX_TC_TRACE
@@ -430,25 +498,46 @@ bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0;
 
 }  // namespace
 
-MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k) {
-    MatmulTcPlan p;
-    p.bn = n <= 64 ? 64 : 128;
-    uint64_t tiles = ((m + BM - 1) / BM) * ((n + p.bn - 1) / p.bn);
-    uint64_t kblocks = (k + BK - 1) / BK;
-    // Split k until about one wave of CTAs exists, keeping at least 4 k blocks per split.
-    uint64_t want = tiles >= 148 ? 1 : (148 + tiles - 1) / tiles;
-    uint64_t most = kblocks / 4 > 0 ? kblocks / 4 : 1;
-    uint64_t splits = want < most ? want : most;
-    if (splits < 1) splits = 1;
-    p.kblocks_per_split = static_cast<uint32_t>((kblocks + splits - 1) / splits);
-    if (p.kblocks_per_split == 0) p.kblocks_per_split = 1;
-    p.splits = static_cast<uint32_t>(kblocks == 0 ? 1 : (kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split);
-    p.workspace_floats = p.splits > 1 ? p.splits * m * n : 0;
-    return p;
+// Tile width and k split by a cost model in SM cycles, fitted to measured phase times of this
+// kernel: a CTA costs a fixed latency (set-up, first loads, drain) once per wave of CTAs on an SM
+// plus a time per k block that shared-memory bandwidth and the MMA rate set; a split k adds the
+// reduce launch. Narrow tiles win when the problem is small (more SMs share the latency-bound
+// work), wide ones when it is large (less operand re-reading).
+MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems) {
+    static const uint32_t widths[3] = {32, 64, 128};
+    static const double per_block[3] = {MSX_TC_KB32, MSX_TC_KB64, MSX_TC_KB128};
+    const uint64_t kblocks = (k + BK - 1) / BK;
+    MatmulTcPlan best = {};
+    double best_cost = 0.0;
+    for (int w = 0; w < 3; ++w) {
+#ifdef MSX_TC_TRACE
+        if (const char* forced = std::getenv("MSX_TC_FORCE_BN"))
+            if (static_cast<uint32_t>(std::atoi(forced)) != widths[w]) continue;
+#endif
+        const uint64_t tiles = ((m + BM - 1) / BM) * ((n + widths[w] - 1) / widths[w]) * problems;
+        const uint64_t most = problems > 1 ? 1 : (kblocks / 2 > 0 ? kblocks / 2 : 1);
+        for (uint64_t splits = 1; splits <= most && splits <= 64; ++splits) {
+            const uint64_t per = (kblocks + splits - 1) / splits;
+            const uint64_t used = kblocks == 0 ? 1 : (kblocks + per - 1) / per;
+            if (used != splits) continue;  // the same partition as a smaller count
+            // CTAs an SM runs one after another (two share it, overlapping their fixed parts).
+            const uint64_t per_sm = (tiles * splits + 147) / 148;
+            double cost = MSX_TC_FIXED * static_cast<double>((per_sm + 1) / 2) + static_cast<double>(per_sm * per) * per_block[w];
+            if (splits > 1) cost += MSX_TC_REDUCE_FIXED + static_cast<double>(m * n * (splits + 1)) * 4.0 / MSX_TC_REDUCE_BYTES_PER_CYCLE;
+            if (best.bn == 0 || cost < best_cost) {
+                best_cost = cost;
+                best.bn = widths[w];
+                best.splits = static_cast<uint32_t>(splits);
+                best.kblocks_per_split = static_cast<uint32_t>(per == 0 ? 1 : per);
+            }
+        }
+    }
+    best.workspace_floats = best.splits > 1 ? best.splits * m * n : 0;
+    return best;
 }
 
 void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m, uint64_t n,
-               uint64_t k, float* workspace, uint32_t* status, const float* bias) {
+               uint64_t k, float* workspace, uint32_t* status, const float* bias, bool leave_partials) {
     if (m == 0 || n == 0) return;
     MatmulTcPlan p = matmul_tc_plan(m, n, k);
     TcArgs args = {};
@@ -466,16 +555,14 @@ void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_
     // A float4 read starts at a multiple of 4 elements within a row, so rows must keep that phase.
     args.a_vec = aligned16(a) && args.lda % 4 == 0;
     args.b_vec = aligned16(b) && args.ldb % 4 == 0;
-    args.c_vec = aligned16(args.c) && n % 4 == 0;
     args.status = status;
     dim3 grid(static_cast<uint32_t>((n + p.bn - 1) / p.bn), static_cast<uint32_t>((m + BM - 1) / BM), p.splits);
-    if (p.bn == 64) launch_forms<64>(s, args, grid, a_t, b_t);
-    else launch_forms<128>(s, args, grid, a_t, b_t);
-    if (p.splits > 1) {
+    launch_width(s, args, grid, p.bn, a_t, b_t);
+    if (p.splits > 1 && !leave_partials) {
         uint64_t count = m * n;
         uint64_t blocks = (count + 255) / 256;
         splitk_reduce_kernel<<<static_cast<uint32_t>(blocks > 148 * 8 ? 148 * 8 : blocks), 256, 0, s>>>(workspace, c, count, p.splits, bias,
-                                                                                                                  static_cast<uint32_t>(n));
+                                                                                                        static_cast<uint32_t>(n));
         check_launch("splitk_reduce");
     }
 }
@@ -499,16 +586,14 @@ void matmul_tc_batched(cudaStream_t s, const BatchedOperand& a, const BatchedOpe
     };
     args.a_vec = vec(a);
     args.b_vec = vec(b);
-    args.c_vec = vec(c);
     args.batch_inner = inner;
     args.a_outer = a.stride_outer; args.a_inner = a.stride_inner;
     args.b_outer = b.stride_outer; args.b_inner = b.stride_inner;
     args.c_outer = c.stride_outer; args.c_inner = c.stride_inner;
     args.status = status;
-    uint32_t bn = n <= 64 ? 64 : 128;
+    uint32_t bn = matmul_tc_plan(m, n, k, static_cast<uint64_t>(outer) * inner).bn;
     dim3 grid(static_cast<uint32_t>((n + bn - 1) / bn), static_cast<uint32_t>((m + BM - 1) / BM), outer * inner);
-    if (bn == 64) launch_forms<64>(s, args, grid, a.transposed, b.transposed);
-    else launch_forms<128>(s, args, grid, a.transposed, b.transposed);
+    launch_width(s, args, grid, bn, a.transposed, b.transposed);
 }
 
 }  // namespace k

@@ -47,9 +47,26 @@ uint64_t sum_rows_scratch_floats(uint64_t rows, uint64_t h);
 // `counters`, when not null, is sum_rows_counters(h) words that are zero before the first launch
 // and left zero by every launch: the chunk sums are then combined by the same launch (same order,
 // same result) instead of a second one.
+// With `out` null only the chunk sums are written, as scratch[chunk][h]: finalize_sums adds them.
 uint64_t sum_rows_counters(uint64_t h);
 void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out,
               uint32_t* counters = nullptr);
+
+// Deferred second stages. A kernel that leaves `chunks` partial results of `width` floats each,
+// stored [chunk][width], is finished by one launch over all such jobs of a step: up to 64 chunks
+// are added in ascending order; beyond that thread y of 8 adds chunks y, y + 8, ... in ascending
+// order and the eight sums are added in ascending y (deterministic; tolerance class against a
+// sequential sum). `first_block` = the blocks
+// (sum_job_blocks each) of the jobs before this one.
+struct SumJob {
+    const float* partial;
+    float* out;
+    uint32_t chunks, width, first_block, reserved;
+};
+inline uint32_t sum_job_blocks(uint32_t chunks, uint64_t width) {
+    return static_cast<uint32_t>(chunks <= 64 ? (width + 255) / 256 : (width + 31) / 32);
+}
+void finalize_sums(cudaStream_t s, const SumJob* d_jobs, uint32_t jobs, uint32_t blocks);
 
 // ---- row kernels (rowwise.cu) -----------------------------------------------------------------
 void layer_norm(cudaStream_t s, const float* x, const float* gamma, const float* beta, float* out,
@@ -65,7 +82,11 @@ void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float
 // (dbeta) in one launch, for rows of up to 1,024 elements. dx, dgamma and dbeta may each be null.
 // `scratch` holds layer_norm_backward_scratch_floats(rows, h) floats; `counter` is one word that
 // is zero before the first launch and left zero by every launch.
+// With `counter` null the chunk sums stay in `scratch` for finalize_sums: dgamma's as
+// scratch[chunk][h], dbeta's after them, layer_norm_backward_chunks(rows) chunks each; the dgamma
+// and dbeta pointers then only say which are wanted.
 bool layer_norm_backward_supported(uint64_t h);
+uint32_t layer_norm_backward_chunks(uint64_t rows);
 uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h);
 void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
                          uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h);
@@ -100,10 +121,11 @@ void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t*
 void embedding(cudaStream_t s, const float* table, const int32_t* ids, float* out, uint64_t n,
                uint64_t rows, uint64_t h, uint32_t* status);
 // out = zeros[rows, h] with g[n, :] added to row ids[n] in ascending n: bit-exact with a
-// sequential loop. `scratch` holds embedding_grad_scratch_ints(n, rows) ints.
+// sequential loop. `scratch` holds embedding_grad_scratch_ints(n, rows) ints. With `base`
+// ([rows, h]) the result is base + that tensor, element by element.
 uint64_t embedding_grad_scratch_ints(uint64_t n, uint64_t rows);
 void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* out, uint64_t n,
-                    uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status);
+                    uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status, const float* base = nullptr);
 
 // ---- matmul (gemm.cu) -------------------------------------------------------------------------
 // C[m, n] = op(A) x op(B) (+ bias[n]) with each element one ascending-k fused chain starting
@@ -117,14 +139,18 @@ void matmul(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, 
 // The same product by tcgen05.mma with a 3xTF32 operand split and f32 accumulation in tensor
 // memory: tolerance class (about 2^-21 of each |a||b| term). `workspace` holds
 // matmul_tc_plan(m, n, k).workspace_floats floats (split-K partial tiles; 0 when k is not split).
-// A wait that runs out inside the kernel raises bit 1 of *status instead of hanging.
+// A wait that runs out inside the kernel raises bit 1 of *status instead of hanging. With
+// `leave_partials` a split k stops at the partial tiles, workspace[split][m][n], for
+// finalize_sums (no bias then).
 struct MatmulTcPlan {
     uint32_t bn, splits, kblocks_per_split;
     uint64_t workspace_floats;
 };
-MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k);
+// `problems` > 1: that many independent products in one launch (k is then not split).
+MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems = 1);
 void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m,
-               uint64_t n, uint64_t k, float* workspace, uint32_t* status, const float* bias = nullptr);
+               uint64_t n, uint64_t k, float* workspace, uint32_t* status, const float* bias = nullptr,
+               bool leave_partials = false);
 
 // outer x inner independent products through one launch (grid.z = problem): matrix z of an
 // operand starts at base + (z / inner) * stride_outer + (z % inner) * stride_inner elements and

@@ -93,7 +93,51 @@ __global__ void sum_rows_stage2(const float* __restrict__ partial, uint32_t chun
     out[c] = total;
 }
 
+__global__ void finalize_sums_kernel(const SumJob* __restrict__ jobs, uint32_t count) {
+    __shared__ float shared[8][32];
+    __shared__ uint32_t which;
+    if (threadIdx.x == 0 && threadIdx.y == 0) {
+        uint32_t j = 0;
+        while (j + 1 < count && jobs[j + 1].first_block <= blockIdx.x) ++j;
+        which = j;
+    }
+    __syncthreads();
+    const SumJob job = jobs[which];
+    const uint32_t block = blockIdx.x - job.first_block;
+    if (job.chunks <= 64) {
+        // Plain ascending order, one thread per column (what the two-launch forms of sum_rows and
+        // the split-K reduction do).
+        const uint32_t c = block * 256 + threadIdx.y * 32 + threadIdx.x;
+        if (c >= job.width) return;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (uint32_t k = 0; k < job.chunks; ++k) acc += job.partial[static_cast<uint64_t>(k) * job.width + c];
+        job.out[c] = acc;
+        return;
+    }
+    const uint32_t c = block * 32 + threadIdx.x;
+    float acc = 0.0f;
+    if (c < job.width) {
+#pragma unroll 4
+        for (uint32_t k = threadIdx.y; k < job.chunks; k += 8) acc += job.partial[static_cast<uint64_t>(k) * job.width + c];
+    }
+    shared[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < job.width) {
+        float total = shared[0][threadIdx.x];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) total += shared[w][threadIdx.x];
+        job.out[c] = total;
+    }
+}
+
 }  // namespace
+
+void finalize_sums(cudaStream_t s, const SumJob* d_jobs, uint32_t jobs, uint32_t blocks) {
+    if (jobs == 0 || blocks == 0) return;
+    finalize_sums_kernel<<<blocks, dim3(32, 8), 0, s>>>(d_jobs, jobs);
+    check_launch("finalize_sums");
+}
 
 uint32_t sum_rows_chunks(uint64_t rows) {
     uint64_t chunks = (rows + 127) / 128;
@@ -128,9 +172,10 @@ void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* 
     uint32_t rows_per_chunk = static_cast<uint32_t>((rows + chunks - 1) / chunks);
     dim3 grid(static_cast<uint32_t>((h + 31) / 32), chunks);
     sum_rows_stage1<<<grid, dim3(32, 8), 0, s>>>(g, static_cast<uint32_t>(rows), static_cast<uint32_t>(h),
-                                                 rows_per_chunk, chunks == 1 ? out : scratch, chunks > 1 ? counters : nullptr, out);
+                                                 rows_per_chunk, (chunks == 1 && out) ? out : scratch,
+                                                 (chunks > 1 && out) ? counters : nullptr, out);
     check_launch("sum_rows");
-    if (chunks > 1 && counters == nullptr) {
+    if (chunks > 1 && counters == nullptr && out != nullptr) {
         sum_rows_stage2<<<static_cast<uint32_t>((h + 127) / 128), 128, 0, s>>>(scratch, chunks,
                                                                                 static_cast<uint32_t>(h), out);
         check_launch("sum_rows");

@@ -363,7 +363,7 @@ template <int ITEMS>
 __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
     const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ g, float* __restrict__ dx,
     float* __restrict__ partial, uint32_t* __restrict__ counter, float* __restrict__ dgamma, float* __restrict__ dbeta,
-    uint32_t rows, uint32_t h, uint32_t rows_per_chunk) {
+    uint32_t want, uint32_t rows, uint32_t h, uint32_t rows_per_chunk) {
     __shared__ float buf[8 * 32 * ITEMS];
     __shared__ bool is_last;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, chunks = gridDim.x;
@@ -425,12 +425,12 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
             }
         }
     }
-    if (dgamma == nullptr && dbeta == nullptr) return;
+    if (want == 0) return;
     float* partial_gamma = partial + static_cast<uint64_t>(blockIdx.x) * h;
     float* partial_beta = partial + static_cast<uint64_t>(chunks + blockIdx.x) * h;
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
-        if (pass == 0 ? dgamma == nullptr : dbeta == nullptr) continue;
+        if ((want & (1u << pass)) == 0) continue;
         __syncthreads();
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) buf[(warp * ITEMS + i) * 32 + lane] = pass == 0 ? acc_g[i] : acc_b[i];
@@ -443,10 +443,11 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
             (pass == 0 ? partial_gamma : partial_beta)[c] = total;
         }
     }
+    if (counter == nullptr) return;  // the chunk sums are added later, by finalize_sums
     if (!last_block_arrives(counter, chunks, &is_last)) return;
     for (int pass = 0; pass < 2; ++pass) {
         float* out = pass == 0 ? dgamma : dbeta;
-        if (out == nullptr) continue;
+        if ((want & (1u << pass)) == 0) continue;
         const float* from = partial + static_cast<uint64_t>(pass) * chunks * h;
         for (uint32_t c0 = 0; c0 < h; c0 += 32) {
             uint32_t c = c0 + lane;
@@ -518,6 +519,7 @@ void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float
 }
 
 bool layer_norm_backward_supported(uint64_t h) { return h >= 1 && h <= 1024; }
+uint32_t layer_norm_backward_chunks(uint64_t rows) { return backward_chunks(rows); }
 uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h) { return 2ull * backward_chunks(rows) * h; }
 
 void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
@@ -527,7 +529,8 @@ void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, con
     uint32_t per = static_cast<uint32_t>((rows + chunks - 1) / chunks);
     uint32_t items = static_cast<uint32_t>((h + 31) / 32);
     uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
-#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, dx, scratch, counter, dgamma, dbeta, r, hh, per)
+    uint32_t want = (dgamma ? 1u : 0u) | (dbeta ? 2u : 0u);
+#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, dx, scratch, counter, dgamma, dbeta, want, r, hh, per)
     if (items <= 1) MSX_LN_BACKWARD(1);
     else if (items <= 2) MSX_LN_BACKWARD(2);
     else if (items <= 4) MSX_LN_BACKWARD(4);

@@ -146,6 +146,7 @@ struct msx_plan {
     uint32_t counters_used = 0;
     uint32_t* counter(uint32_t index) const { return d_counters + index; }
     void* d_update_tables = nullptr;
+    void* d_sum_jobs = nullptr;  // k::SumJob table of the deferred second stages
 
     int loss_pos = -1;
     uint64_t steps = 0;
@@ -224,6 +225,38 @@ struct Scheduler {
                                                " has no CUDA kernel: " + why);
     }
 
+    // Two-stage sums whose result only the optimizer (or nobody on the device) reads leave their
+    // partial results in scratch; one launch before the optimizer finishes them all.
+    struct Deferred {
+        uint32_t partial;      // scratch slot of the partial results
+        uint64_t offset;       // floats into it
+        uint32_t chunks;
+        uint64_t width;
+        uint32_t out;          // node position of the result
+    };
+    std::vector<Deferred> deferred;
+    bool deferrable(uint32_t at) const {
+        for (uint32_t u : users[at])
+            if (node(u).tag != msx::Tag::Optimizer || !handled[u]) return false;
+        return true;
+    }
+    void emit_finalize() {
+        if (deferred.empty()) return;
+        std::vector<uint32_t> reads, writes;
+        uint32_t blocks = 0;
+        for (const Deferred& d : deferred) {
+            reads.push_back(d.partial);
+            writes.push_back(d.out);
+            blocks += k::sum_job_blocks(d.chunks, d.width);
+        }
+        Node pseudo;
+        pseudo.id = node(deferred[0].out).id;
+        msx_plan* plan = P;
+        const uint32_t jobs = static_cast<uint32_t>(deferred.size());
+        emit("finalize_sums", pseudo, reads, writes,
+             [=](cudaStream_t s) { k::finalize_sums(s, static_cast<const k::SumJob*>(plan->d_sum_jobs), jobs, blocks); });
+    }
+
     uint32_t counters(uint64_t n) {
         uint32_t base = P->counters_used;
         P->counters_used += static_cast<uint32_t>(n);
@@ -278,6 +311,7 @@ struct Scheduler {
         fold_transposes();
         for (uint32_t at = 0; at < n; ++at)
             if (live[at] && !handled[at]) schedule(at);
+        emit_finalize();
         emit_optimizer();
         for (const msx::Output& o : prog.outputs) {
             Slot& s = P->slots[pos(o.value)];
@@ -690,6 +724,29 @@ struct Scheduler {
                 uint32_t ids = in[0], g = in[1];
                 uint64_t n = rows_of(ids), rows = nd.rows, h = cols_of(g);
                 uint32_t tmp = scratch(k::embedding_grad_scratch_ints(n, rows) * 4);
+                // other + embedding_grad(...) with nothing else reading the scatter (a tied weight's
+                // dense gradient plus its lookup gradient): the scatter adds `other` as it writes.
+                bool is_output = false;
+                for (const msx::Output& o : prog.outputs) is_output = is_output || pos(o.value) == at;
+                if (!is_output && users[at].size() == 1) {
+                    uint32_t u = users[at][0];
+                    const Node& add = node(u);
+                    if (add.op == Op::Add && !handled[u] && add.ty.count() == nd.ty.count()) {
+                        uint32_t other = pos(add.operands[0]) == at ? pos(add.operands[1]) : pos(add.operands[0]);
+                        if (other < at && other != at && node(other).ty.count() == nd.ty.count()) {
+                            handled[u] = 1;
+                            out.kind = Slot::Dead;
+                            Slot& sum = P->slots[u];
+                            sum.kind = Slot::Arena;
+                            sum.bytes = std::max<uint64_t>(add.ty.count() * 4, 4);
+                            emit("embedding_grad", nd, {ids, g, other}, {u, tmp}, [=](cudaStream_t s) {
+                                k::embedding_grad(s, plan->i(ids), plan->f(g), plan->f(u), n, rows, h, plan->i(tmp), plan->d_status,
+                                                  plan->f(other));
+                            });
+                            break;
+                        }
+                    }
+                }
                 emit("embedding_grad", nd, in, {at, tmp}, [=](cudaStream_t s) {
                     k::embedding_grad(s, plan->i(ids), plan->f(g), plan->f(at), n, rows, h, plan->i(tmp), plan->d_status);
                 });
@@ -704,6 +761,12 @@ struct Scheduler {
             case Op::SumRows: {
                 uint32_t g = in[0];
                 uint64_t r = rows_of(g), h = cols_of(g);
+                if (deferrable(at)) {
+                    uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4);
+                    emit("sum_rows", nd, in, {tmp}, [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), nullptr); });
+                    deferred.push_back({tmp, 0, k::sum_rows_chunks(r), h, at});
+                    break;
+                }
                 uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4), ctr = counters(k::sum_rows_counters(h));
                 emit("sum_rows", nd, in, {at, tmp},
                      [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), plan->f(at), plan->counter(ctr)); });
@@ -878,10 +941,27 @@ struct Scheduler {
             slot.bytes = std::max<uint64_t>(node(u).ty.count() * 4, 4);
             writes.push_back(u);
         }
-        uint32_t tmp = scratch(k::layer_norm_backward_scratch_floats(r, h) * 4), ctr = counters(1);
-        writes.push_back(tmp);
+        uint32_t tmp = scratch(k::layer_norm_backward_scratch_floats(r, h) * 4);
         msx_plan* plan = P;
         auto at_or_null = [plan](int p) -> float* { return p >= 0 ? plan->f(static_cast<uint32_t>(p)) : nullptr; };
+        const bool defer = (dgamma < 0 || deferrable(static_cast<uint32_t>(dgamma))) && (dbeta < 0 || deferrable(static_cast<uint32_t>(dbeta)));
+        if (defer) {
+            // dx is written here; the column sums stay as chunk sums until the finalize launch.
+            std::vector<uint32_t> now;
+            if (dx >= 0) now.push_back(static_cast<uint32_t>(dx));
+            now.push_back(tmp);
+            const uint32_t chunks = k::layer_norm_backward_chunks(r);
+            if (dgamma >= 0) deferred.push_back({tmp, 0, chunks, h, static_cast<uint32_t>(dgamma)});
+            if (dbeta >= 0) deferred.push_back({tmp, static_cast<uint64_t>(chunks) * h, chunks, h, static_cast<uint32_t>(dbeta)});
+            float* const wanted = reinterpret_cast<float*>(uintptr_t{1});  // only null or not is read
+            emit("layer_norm_backward", nd, reads, now, [=](cudaStream_t s) {
+                k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(g), at_or_null(dx), plan->f(tmp), nullptr,
+                                       dgamma >= 0 ? wanted : nullptr, dbeta >= 0 ? wanted : nullptr, r, h);
+            });
+            return true;
+        }
+        uint32_t ctr = counters(1);
+        writes.push_back(tmp);
         emit("layer_norm_backward", nd, reads, writes, [=](cudaStream_t s) {
             k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(g), at_or_null(dx), plan->f(tmp), plan->counter(ctr),
                                    at_or_null(dgamma), at_or_null(dbeta), r, h);
@@ -905,16 +985,24 @@ struct Scheduler {
             l.flop = 2 * m * n * kk;
             return;
         }
-        uint64_t floats = k::matmul_tc_plan(m, n, kk).workspace_floats;
+        const k::MatmulTcPlan tc = k::matmul_tc_plan(m, n, kk);
+        uint64_t floats = tc.workspace_floats;
         std::vector<uint32_t> writes = {at};
         int ws = -1;
         if (floats) {
             ws = static_cast<int>(scratch(floats * 4));
             writes.push_back(static_cast<uint32_t>(ws));
         }
+        // A split k whose sum only the optimizer reads (a weight gradient) stays as partial
+        // tiles: the finalize launch adds them with every other deferred sum.
+        const bool defer = floats != 0 && bias < 0 && deferrable(at);
+        if (defer) {
+            writes = {static_cast<uint32_t>(ws)};
+            deferred.push_back({static_cast<uint32_t>(ws), 0, tc.splits, m * n, at});
+        }
         Launch& l = emit("matmul", nd, reads, writes, [=](cudaStream_t s) {
             k::matmul_tc(s, plan->f(a), plan->transposed(a) != flip_a, plan->f(b), plan->transposed(b) != flip_b, plan->f(at), m, n, kk,
-                         ws >= 0 ? plan->f(static_cast<uint32_t>(ws)) : nullptr, plan->d_status, bias_of());
+                         ws >= 0 ? plan->f(static_cast<uint32_t>(ws)) : nullptr, plan->d_status, bias_of(), defer);
         });
         l.flop = 2 * m * n * kk;
     }
@@ -1196,6 +1284,22 @@ void allocate(msx_plan* P, const Scheduler& sched) {
     cuda_ok(cudaMemset(P->d_counters, 0, counter_bytes), "cudaMemset(counters)");
     cuda_ok(cudaEventCreate(&P->clock_start), "cudaEventCreate");
     cuda_ok(cudaEventCreate(&P->clock_stop), "cudaEventCreate");
+    if (!sched.deferred.empty()) {
+        std::vector<k::SumJob> jobs;
+        uint32_t first_block = 0;
+        for (const Scheduler::Deferred& d : sched.deferred) {
+            k::SumJob job = {};
+            job.partial = static_cast<const float*>(P->ptr(d.partial)) + d.offset;
+            job.out = static_cast<float*>(P->ptr(d.out));
+            job.chunks = d.chunks;
+            job.width = static_cast<uint32_t>(d.width);
+            job.first_block = first_block;
+            first_block += k::sum_job_blocks(d.chunks, d.width);
+            jobs.push_back(job);
+        }
+        cuda_ok(cudaMalloc(&P->d_sum_jobs, jobs.size() * sizeof(k::SumJob)), "cudaMalloc(sum jobs)");
+        cuda_ok(cudaMemcpy(P->d_sum_jobs, jobs.data(), jobs.size() * sizeof(k::SumJob), cudaMemcpyHostToDevice), "cudaMemcpy(sum jobs)");
+    }
     if (!sched.updates.empty()) {
         std::vector<k::UpdateTensor> tensors;
         for (const Scheduler::Update& u : sched.updates) {
@@ -1240,6 +1344,7 @@ void release(msx_plan* P) {
     cudaFree(P->d_status);
     cudaFree(P->d_counters);
     cudaFree(P->d_update_tables);
+    cudaFree(P->d_sum_jobs);
     for (int s = 0; s < kStagingSlots; ++s) {
         if (P->pinned[s]) cudaFreeHost(P->pinned[s]);
         if (P->slot_done[s]) cudaEventDestroy(P->slot_done[s]);
@@ -1611,7 +1716,11 @@ int msx_loss_of(msx_plan* plan, uint64_t step_number, float* loss, uint32_t time
 uint64_t msx_steps_submitted(const msx_plan* plan) { return plan ? plan->steps : 0; }
 
 int msx_profile_step(msx_plan* plan, float* launch_ms, uint32_t capacity) {
-    if (!plan || !launch_ms) return MSX_BAD_ARGUMENT;
+    return msx_profile_step_repeated(plan, 1, launch_ms, capacity);
+}
+
+int msx_profile_step_repeated(msx_plan* plan, uint32_t repeats, float* launch_ms, uint32_t capacity) {
+    if (!plan || !launch_ms || repeats == 0) return MSX_BAD_ARGUMENT;
     return guarded(plan->device, [&]() -> int {
         if (capacity < plan->launches.size()) throw StatusError(MSX_BAD_ARGUMENT, "msx_profile_step: room for every launch is needed");
         cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
@@ -1625,12 +1734,17 @@ int msx_profile_step(msx_plan* plan, float* launch_ms, uint32_t capacity) {
         }
         cuda_ok(cudaEventRecord(events[0], plan->stream), "cudaEventRecord");
         for (size_t l = 0; l < plan->launches.size(); ++l) {
-            plan->launches[l].run(plan->stream);
+            const std::string& kernel = plan->launches[l].kernel;
+            const bool in_place = kernel == "adamw_multi_tensor" || kernel == "sgd_multi_tensor";
+            for (uint32_t r = 0; r < (in_place ? 1u : repeats); ++r) plan->launches[l].run(plan->stream);
             cuda_ok(cudaEventRecord(events[l + 1], plan->stream), "cudaEventRecord");
         }
         cuda_ok(cudaStreamSynchronize(plan->stream), "cudaStreamSynchronize");
-        for (size_t l = 0; l < plan->launches.size(); ++l)
+        for (size_t l = 0; l < plan->launches.size(); ++l) {
             cuda_ok(cudaEventElapsedTime(&launch_ms[l], events[l], events[l + 1]), "cudaEventElapsedTime");
+            const std::string& kernel = plan->launches[l].kernel;
+            if (kernel != "adamw_multi_tensor" && kernel != "sgd_multi_tensor") launch_ms[l] /= static_cast<float>(repeats);
+        }
         for (cudaEvent_t e : events) cudaEventDestroy(e);
         return MSX_OK;
     });
