@@ -67,11 +67,15 @@ template <int BN> struct Config {
     static constexpr uint32_t TMEM_COLUMNS = 2 * BN;
 };
 
+constexpr int MAX_GROUP = 4;  // products of one shape that one launch can carry
+
 struct TcArgs {
-    const float* a;
-    const float* b;
-    float* c;          // C, or the split-K workspace [splits][m][n]
-    const float* bias; // added to every row of C by the CTA that writes C; null for none
+    // Per product of the group (grid.z = product * splits + split when not batched):
+    const float* a[MAX_GROUP];
+    const float* b[MAX_GROUP];
+    float* c[MAX_GROUP];           // C, or the split-K workspace [splits][m][n]
+    const float* bias[MAX_GROUP];  // added to every row of C by the CTA that writes C; null for none
+    uint32_t splits;
     uint32_t m, n, k;
     uint32_t lda, ldb, ldc;        // row pitch, in elements, of each matrix as stored
     uint32_t kblocks_per_split;
@@ -222,14 +226,15 @@ __global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
     const uint32_t kblocks_total = (args.k + BK - 1) / BK;
     const bool batched = args.batch_inner != 0;
     const uint32_t z_outer = batched ? blockIdx.z / args.batch_inner : 0, z_inner = batched ? blockIdx.z % args.batch_inner : 0;
-    const uint32_t kb_begin = batched ? 0 : blockIdx.z * args.kblocks_per_split;
+    const uint32_t product = batched ? 0 : blockIdx.z / args.splits, split = batched ? 0 : blockIdx.z % args.splits;
+    const uint32_t kb_begin = split * args.kblocks_per_split;
     const uint32_t kb_end = min(kblocks_total, kb_begin + args.kblocks_per_split);
     const uint32_t kblocks = kb_end > kb_begin ? kb_end - kb_begin : 0;
 
     // ---- loaders, first part: where this thread's chunks sit, and the first loads. They are issued
     // before the barriers and the tensor memory are set up, so that the set-up hides under them.
-    const float* __restrict__ a = args.a + z_outer * args.a_outer + z_inner * args.a_inner;
-    const float* __restrict__ b = args.b + z_outer * args.b_outer + z_inner * args.b_inner;
+    const float* __restrict__ a = args.a[product] + z_outer * args.a_outer + z_inner * args.a_inner;
+    const float* __restrict__ b = args.b[product] + z_outer * args.b_outer + z_inner * args.b_inner;
     constexpr int A_CHUNKS = BM * BK / 4 / LOADER_THREADS, B_CHUNKS = BN * BK / 4 / LOADER_THREADS;
     // Where this thread's chunks sit in a block does not depend on the block: the tile coordinates
     // and the shared-memory offsets are computed once. The lo half of an operand lies half the
@@ -346,8 +351,9 @@ __global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
         constexpr uint32_t EPILOGUE_THREADS = BN == 32 ? 128u : 256u;
         const bool drains = BN != 32 || half == 0;  // a 32-column tile is one block per lane quarter
         float* staging = reinterpret_cast<float*>(tiles);  // [warp][part][32 x 33]
-        float* __restrict__ out = batched ? args.c + z_outer * args.c_outer + z_inner * args.c_inner
-                                          : args.c + static_cast<uint64_t>(blockIdx.z) * args.m * args.ldc;
+        float* __restrict__ out = batched ? args.c[0] + z_outer * args.c_outer + z_inner * args.c_inner
+                                          : args.c[product] + static_cast<uint64_t>(split) * args.m * args.ldc;
+        const float* __restrict__ bias_row = args.bias[product];
         if (drains) {
 #pragma unroll
             for (int part = 0; part < PARTS; ++part) {
@@ -380,7 +386,7 @@ __global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
                     // A warp writes whole rows: 32 consecutive columns per store, whatever the row pitch.
                     const uint32_t gn = n0 + col + lane, row0 = m0 + row_block;
                     if (gn < args.n && row0 < args.m) {
-                        const float bias = args.bias ? args.bias[gn] : 0.0f;
+                        const float bias = bias_row ? bias_row[gn] : 0.0f;
                         float* dst = out + static_cast<uint64_t>(row0) * args.ldc + gn;
                         const uint32_t rows_here = min(32u, args.m - row0);
                         if (rows_here == 32) {
@@ -503,7 +509,7 @@ bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0;
 // plus a time per k block that shared-memory bandwidth and the MMA rate set; a split k adds the
 // reduce launch. Narrow tiles win when the problem is small (more SMs share the latency-bound
 // work), wide ones when it is large (less operand re-reading).
-MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems) {
+MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems, uint64_t group) {
     static const uint32_t widths[3] = {32, 64, 128};
     static const double per_block[3] = {MSX_TC_KB32, MSX_TC_KB64, MSX_TC_KB128};
     const uint64_t kblocks = (k + BK - 1) / BK;
@@ -514,7 +520,7 @@ MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problem
         if (const char* forced = std::getenv("MSX_TC_FORCE_BN"))
             if (static_cast<uint32_t>(std::atoi(forced)) != widths[w]) continue;
 #endif
-        const uint64_t tiles = ((m + BM - 1) / BM) * ((n + widths[w] - 1) / widths[w]) * problems;
+        const uint64_t tiles = ((m + BM - 1) / BM) * ((n + widths[w] - 1) / widths[w]) * problems * group;
         const uint64_t most = problems > 1 ? 1 : (kblocks / 2 > 0 ? kblocks / 2 : 1);
         for (uint64_t splits = 1; splits <= most && splits <= 64; ++splits) {
             const uint64_t per = (kblocks + splits - 1) / splits;
@@ -536,44 +542,59 @@ MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problem
     return best;
 }
 
-void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m, uint64_t n,
-               uint64_t k, float* workspace, uint32_t* status, const float* bias, bool leave_partials) {
-    if (m == 0 || n == 0) return;
-    MatmulTcPlan p = matmul_tc_plan(m, n, k);
+void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t count, bool a_t, bool b_t, uint64_t m, uint64_t n,
+                     uint64_t k, uint32_t* status, bool leave_partials) {
+    if (m == 0 || n == 0 || count == 0) return;
+    if (count > MAX_GROUP) throw std::invalid_argument("matmul_tc_group: more products than one launch carries");
+    MatmulTcPlan p = matmul_tc_plan(m, n, k, 1, count);
     TcArgs args = {};
-    args.a = a;
-    args.b = b;
-    args.c = p.splits > 1 ? workspace : c;
-    args.bias = p.splits > 1 ? nullptr : bias;
     args.m = static_cast<uint32_t>(m);
     args.n = static_cast<uint32_t>(n);
     args.k = static_cast<uint32_t>(k);
     args.lda = static_cast<uint32_t>(a_t ? m : k);
     args.ldb = static_cast<uint32_t>(b_t ? k : n);
     args.ldc = static_cast<uint32_t>(n);
+    args.splits = p.splits;
     args.kblocks_per_split = p.kblocks_per_split;
     // A float4 read starts at a multiple of 4 elements within a row, so rows must keep that phase.
-    args.a_vec = aligned16(a) && args.lda % 4 == 0;
-    args.b_vec = aligned16(b) && args.ldb % 4 == 0;
+    args.a_vec = args.lda % 4 == 0;
+    args.b_vec = args.ldb % 4 == 0;
+    for (uint32_t g = 0; g < count; ++g) {
+        args.a[g] = products[g].a;
+        args.b[g] = products[g].b;
+        args.c[g] = p.splits > 1 ? products[g].workspace : products[g].c;
+        args.bias[g] = p.splits > 1 ? nullptr : products[g].bias;
+        args.a_vec = args.a_vec && aligned16(products[g].a);
+        args.b_vec = args.b_vec && aligned16(products[g].b);
+    }
     args.status = status;
-    dim3 grid(static_cast<uint32_t>((n + p.bn - 1) / p.bn), static_cast<uint32_t>((m + BM - 1) / BM), p.splits);
+    dim3 grid(static_cast<uint32_t>((n + p.bn - 1) / p.bn), static_cast<uint32_t>((m + BM - 1) / BM), p.splits * count);
     launch_width(s, args, grid, p.bn, a_t, b_t);
     if (p.splits > 1 && !leave_partials) {
-        uint64_t count = m * n;
-        uint64_t blocks = (count + 255) / 256;
-        splitk_reduce_kernel<<<static_cast<uint32_t>(blocks > 148 * 8 ? 148 * 8 : blocks), 256, 0, s>>>(workspace, c, count, p.splits, bias,
-                                                                                                        static_cast<uint32_t>(n));
-        check_launch("splitk_reduce");
+        uint64_t total = m * n;
+        uint64_t blocks = (total + 255) / 256;
+        for (uint32_t g = 0; g < count; ++g) {
+            splitk_reduce_kernel<<<static_cast<uint32_t>(blocks > 148 * 8 ? 148 * 8 : blocks), 256, 0, s>>>(
+                products[g].workspace, products[g].c, total, p.splits, products[g].bias, static_cast<uint32_t>(n));
+            check_launch("splitk_reduce");
+        }
     }
+}
+
+void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m, uint64_t n,
+               uint64_t k, float* workspace, uint32_t* status, const float* bias, bool leave_partials) {
+    MatmulOperands one = {a, b, c, bias, workspace};
+    matmul_tc_group(s, &one, 1, a_t, b_t, m, n, k, status, leave_partials);
 }
 
 void matmul_tc_batched(cudaStream_t s, const BatchedOperand& a, const BatchedOperand& b, const BatchedOperand& c, uint64_t m,
                        uint64_t n, uint64_t k, uint32_t outer, uint32_t inner, uint32_t* status) {
     if (m == 0 || n == 0 || outer == 0 || inner == 0) return;
     TcArgs args = {};
-    args.a = a.base;
-    args.b = b.base;
-    args.c = const_cast<float*>(c.base);
+    args.a[0] = a.base;
+    args.b[0] = b.base;
+    args.c[0] = const_cast<float*>(c.base);
+    args.splits = 1;
     args.m = static_cast<uint32_t>(m);
     args.n = static_cast<uint32_t>(n);
     args.k = static_cast<uint32_t>(k);

@@ -146,11 +146,26 @@ struct MatmulTcPlan {
     uint32_t bn, splits, kblocks_per_split;
     uint64_t workspace_floats;
 };
-// `problems` > 1: that many independent products in one launch (k is then not split).
-MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems = 1);
+// `problems` > 1: that many independent batched products in one launch (k is then not split);
+// `group` > 1: that many products of this shape in one launch of matmul_tc_group (the workspace
+// size is per product).
+MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems = 1, uint64_t group = 1);
 void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m,
                uint64_t n, uint64_t k, float* workspace, uint32_t* status, const float* bias = nullptr,
                bool leave_partials = false);
+
+// Up to 4 products of one shape and one storage form in one launch (the query, key and value
+// projections of a layer, their input gradients, their weight gradients): the CTAs of all of them
+// share the SMs, where each alone fills a fraction of the device.
+struct MatmulOperands {
+    const float* a;
+    const float* b;
+    float* c;
+    const float* bias;   // may be null
+    float* workspace;    // matmul_tc_plan(m, n, k, 1, count).workspace_floats floats, or null when that is 0
+};
+void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t count, bool a_t, bool b_t, uint64_t m, uint64_t n,
+                     uint64_t k, uint32_t* status, bool leave_partials = false);
 
 // outer x inner independent products through one launch (grid.z = problem): matrix z of an
 // operand starts at base + (z / inner) * stride_outer + (z % inner) * stride_inner elements and

@@ -653,28 +653,14 @@ struct Scheduler {
                 break;
             }
             case Op::MatMul: {
-                uint32_t a = in[0], b = in[1];
-                uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(a);
-                // add_rows(matmul(x, w), b) with nothing else reading the product: the bias rides
-                // in the matmul's epilogue and the product itself is never stored.
-                int bias = -1;
-                uint32_t result = at;
-                bool is_output = false;
-                for (const msx::Output& o : prog.outputs) is_output = is_output || pos(o.value) == at;
-                if (!is_output && users[at].size() == 1) {
-                    uint32_t u = users[at][0];
-                    const Node& add = node(u);
-                    if (add.op == Op::AddRows && !handled[u] && pos(add.operands[0]) == at && pos(add.operands[1]) < at) {
-                        bias = static_cast<int>(pos(add.operands[1]));
-                        result = u;
-                        handled[u] = 1;
-                        out.kind = Slot::Dead;
-                        Slot& r = P->slots[u];
-                        r.kind = Slot::Arena;
-                        r.bytes = std::max<uint64_t>(add.ty.count() * 4, 4);
-                    }
-                }
-                emit_matmul(nd, result, a, false, b, false, m, n, kk, bias);
+                uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(in[0]);
+                std::vector<Product> group = {claim_product(at)};
+                // Later matmuls of the same shape and storage form whose operands already exist
+                // (the three projections of an attention layer, their gradients) join the launch.
+                if (!(P->flags & MSX_PLAN_EXACT_MATMUL))
+                    for (uint32_t later = at + 1; later < prog.nodes.size() && later < at + 64 && group.size() < 4; ++later)
+                        if (joins(later, group[0], at, m, n, kk)) group.push_back(claim_product(later));
+                emit_matmul(nd, group, m, n, kk);
                 break;
             }
             case Op::Transpose: {
@@ -684,7 +670,8 @@ struct Scheduler {
                     const Node& mm = node(absorbed->second);
                     uint32_t a = pos(mm.operands[0]), b = pos(mm.operands[1]);
                     uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(a);
-                    emit_matmul(nd, at, b, true, a, true, m, n, kk);
+                    std::vector<Product> one = {{at, at, b, a, true, true, -1}};
+                    emit_matmul(nd, one, m, n, kk);
                 } else {
                     uint32_t a = in[0];
                     uint64_t r = rows_of(a), c = cols_of(a);
@@ -969,42 +956,118 @@ struct Scheduler {
         return true;
     }
 
-    // C[m, n] = op(a) x op(b); `flip_*` reads the operand as the transpose of what its slot says.
-    // The exact f32 chain kernel under MSX_PLAN_EXACT_MATMUL, else the tensor cores.
-    void emit_matmul(const Node& nd, uint32_t at, uint32_t a, bool flip_a, uint32_t b, bool flip_b, uint64_t m, uint64_t n,
-                     uint64_t kk, int bias = -1) {
+    // One product of a matmul launch: `result` = the node whose slot receives it (the AddRows node
+    // when the bias rides in the epilogue), `flip_*` reads the operand as the transpose of what its
+    // slot says.
+    struct Product {
+        uint32_t node, result, a, b;
+        bool flip_a, flip_b;
+        int bias;
+    };
+
+    // The product of MatMul node `at`, with add_rows(matmul(x, w), b) folded when nothing else
+    // reads the product: the bias rides in the matmul's epilogue and the product is never stored.
+    Product describe_product(uint32_t at) const {
+        const Node& nd = node(at);
+        Product p = {at, at, pos(nd.operands[0]), pos(nd.operands[1]), false, false, -1};
+        bool is_output = false;
+        for (const msx::Output& o : prog.outputs) is_output = is_output || pos(o.value) == at;
+        if (!is_output && users[at].size() == 1) {
+            uint32_t u = users[at][0];
+            const Node& add = node(u);
+            if (add.op == Op::AddRows && !handled[u] && pos(add.operands[0]) == at && pos(add.operands[1]) < at) {
+                p.bias = static_cast<int>(pos(add.operands[1]));
+                p.result = u;
+            }
+        }
+        return p;
+    }
+    Product claim_product(uint32_t at) {
+        Product p = describe_product(at);
+        handled[at] = 1;
+        Slot& own = P->slots[at];
+        own.kind = Slot::Arena;
+        own.bytes = std::max<uint64_t>(node(at).ty.count() * 4, 4);
+        if (p.result != at) {
+            handled[p.result] = 1;
+            own.kind = Slot::Dead;
+            Slot& r = P->slots[p.result];
+            r.kind = Slot::Arena;
+            r.bytes = std::max<uint64_t>(node(p.result).ty.count() * 4, 4);
+        }
+        return p;
+    }
+    // Whether the storage behind operand position `p` exists before node `before` is scheduled.
+    bool ready_before(uint32_t p, uint32_t before) const {
+        const Slot& s = P->slots[p];
+        if (s.kind == Slot::View) return ready_before(s.index, before);
+        return p < before;
+    }
+    bool joins(uint32_t later, const Product& first, uint32_t at, uint64_t m, uint64_t n, uint64_t kk) const {
+        const Node& nd = node(later);
+        if (!live[later] || handled[later] || nd.op != Op::MatMul) return false;
+        if (nd.ty.shape[0] != m || nd.ty.shape[1] != n || node(pos(nd.operands[0])).ty.shape.at(1) != kk) return false;
+        Product p = describe_product(later);
+        if (!ready_before(p.a, at) || !ready_before(p.b, at)) return false;
+        if (P->transposed(p.a) != P->transposed(first.a) || P->transposed(p.b) != P->transposed(first.b)) return false;
+        if ((p.bias >= 0) != (first.bias >= 0)) return false;
+        if (p.bias >= 0 && static_cast<uint32_t>(p.bias) >= at) return false;
+        // A split k is either reduced by the launch or left for the finalize launch: one rule per launch.
+        return deferrable(p.result) == deferrable(first.result);
+    }
+
+    // C[m, n] = op(a) x op(b) for every product of `group` (one shape, one storage form): the exact
+    // f32 chain kernel under MSX_PLAN_EXACT_MATMUL (one product), else the tensor cores.
+    void emit_matmul(const Node& nd, const std::vector<Product>& group, uint64_t m, uint64_t n, uint64_t kk) {
         msx_plan* plan = P;
-        std::vector<uint32_t> reads = {a, b};
-        if (bias >= 0) reads.push_back(static_cast<uint32_t>(bias));
-        auto bias_of = [=]() -> const float* { return bias >= 0 ? plan->f(static_cast<uint32_t>(bias)) : nullptr; };
+        std::vector<uint32_t> reads, writes;
+        for (const Product& p : group) {
+            reads.push_back(p.a);
+            reads.push_back(p.b);
+            if (p.bias >= 0) reads.push_back(static_cast<uint32_t>(p.bias));
+        }
+        const Product first = group[0];
+        const bool a_t_flip = first.flip_a, b_t_flip = first.flip_b;
         if (P->flags & MSX_PLAN_EXACT_MATMUL) {
+            const uint32_t a = first.a, b = first.b, at = first.result;
+            const int bias = first.bias;
             Launch& l = emit("matmul", nd, reads, {at}, [=](cudaStream_t s) {
-                k::matmul(s, plan->f(a), plan->transposed(a) != flip_a, plan->f(b), plan->transposed(b) != flip_b, plan->f(at), m, n, kk,
-                          bias_of());
+                k::matmul(s, plan->f(a), plan->transposed(a) != a_t_flip, plan->f(b), plan->transposed(b) != b_t_flip, plan->f(at), m, n, kk,
+                          bias >= 0 ? plan->f(static_cast<uint32_t>(bias)) : nullptr);
             });
             l.flop = 2 * m * n * kk;
             return;
         }
-        const k::MatmulTcPlan tc = k::matmul_tc_plan(m, n, kk);
-        uint64_t floats = tc.workspace_floats;
-        std::vector<uint32_t> writes = {at};
-        int ws = -1;
-        if (floats) {
-            ws = static_cast<int>(scratch(floats * 4));
-            writes.push_back(static_cast<uint32_t>(ws));
-        }
+        const uint32_t count = static_cast<uint32_t>(group.size());
+        const k::MatmulTcPlan tc = k::matmul_tc_plan(m, n, kk, 1, count);
         // A split k whose sum only the optimizer reads (a weight gradient) stays as partial
         // tiles: the finalize launch adds them with every other deferred sum.
-        const bool defer = floats != 0 && bias < 0 && deferrable(at);
-        if (defer) {
-            writes = {static_cast<uint32_t>(ws)};
-            deferred.push_back({static_cast<uint32_t>(ws), 0, tc.splits, m * n, at});
+        const bool defer = tc.workspace_floats != 0 && first.bias < 0 && deferrable(first.result);
+        std::vector<int> workspaces;
+        for (const Product& p : group) {
+            int ws = -1;
+            if (tc.workspace_floats) {
+                ws = static_cast<int>(scratch(tc.workspace_floats * 4));
+                writes.push_back(static_cast<uint32_t>(ws));
+            }
+            workspaces.push_back(ws);
+            if (defer) deferred.push_back({static_cast<uint32_t>(ws), 0, tc.splits, m * n, p.result});
+            else writes.push_back(p.result);
         }
         Launch& l = emit("matmul", nd, reads, writes, [=](cudaStream_t s) {
-            k::matmul_tc(s, plan->f(a), plan->transposed(a) != flip_a, plan->f(b), plan->transposed(b) != flip_b, plan->f(at), m, n, kk,
-                         ws >= 0 ? plan->f(static_cast<uint32_t>(ws)) : nullptr, plan->d_status, bias_of(), defer);
+            k::MatmulOperands operands[4];
+            for (uint32_t g = 0; g < count; ++g) {
+                const Product& p = group[g];
+                operands[g].a = plan->f(p.a);
+                operands[g].b = plan->f(p.b);
+                operands[g].c = plan->f(p.result);
+                operands[g].bias = p.bias >= 0 ? plan->f(static_cast<uint32_t>(p.bias)) : nullptr;
+                operands[g].workspace = workspaces[g] >= 0 ? plan->f(static_cast<uint32_t>(workspaces[g])) : nullptr;
+            }
+            k::matmul_tc_group(s, operands, count, plan->transposed(first.a) != a_t_flip, plan->transposed(first.b) != b_t_flip, m, n, kk,
+                               plan->d_status, defer);
         });
-        l.flop = 2 * m * n * kk;
+        l.flop = 2 * m * n * kk * count;
     }
 
     void schedule_attention(uint32_t at) {

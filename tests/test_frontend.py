@@ -80,15 +80,23 @@ def test_bad_source_is_refused_with_a_message():
 def test_bert_tiny_step_schedule():
     """What the backend launches for BERT-tiny with the gather: the ungathered head is not run,
     every transpose is folded into a matmul, the three attention gradients share a launch pair,
-    and the 41 AdamW updates are one launch."""
+    the query/key/value projections of a layer (and their input and weight gradients) share a
+    matmul launch, the second stages of every column sum and split-k weight gradient are one
+    launch, and the 41 AdamW updates are one launch."""
     listing = M.schedule_describe(M.compile_mspec(models.bert(), "step", masked_rows=832))
     kernels = [l.split()[1] for l in listing.strip().splitlines()[:-1]]
     assert kernels.count("adamw_multi_tensor") == 1 and kernels[-1] == "adamw_multi_tensor"
     assert "transpose" not in kernels
     assert kernels.count("attention_forward") == 2 and kernels.count("attention_backward") == 2
-    assert kernels.count("matmul") == 42
+    # 42 products: 6 groups of 3 (2 layers x {projections, input gradients, weight gradients}) + 24.
+    assert kernels.count("matmul") == 30
+    matmuls = [l for l in listing.strip().splitlines() if l.split()[1] == "matmul"]
+    assert sum(1 for l in matmuls if l.split("writes")[1].count("%") + l.split("writes")[1].count("scratch") >= 3) == 6
+    assert kernels.count("finalize_sums") == 1 and kernels[-2] == "finalize_sums"
+    assert "layer_norm_grad_x" not in kernels and kernels.count("layer_norm_backward") == 6
+    assert kernels.count("cross_entropy_with_grad") == 1 and "cross_entropy_grad" not in kernels
     assert "[4096, 30522]" not in listing
-    assert len(kernels) < 140
+    assert len(kernels) < 100
     totals = listing.strip().splitlines()[-1]
     arena, unshared = int(totals.split()[1]), int(totals.split()[4])
     assert arena < unshared
