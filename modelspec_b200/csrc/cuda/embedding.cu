@@ -115,71 +115,135 @@ __device__ __forceinline__ uint32_t warp_lower_bound(const int32_t* __restrict__
     return lo;
 }
 
-// One warp per (table row, group of VEC * 32 columns): base + (0 + g[n0] + g[n1] + ...) over the
-// row's occurrences in ascending n. The additions stay in order; the loads of up to 8 occurrences
-// are issued together. A row nobody read gets `base` (or zero). VEC = 4 reads and writes 16 bytes
-// per lane and needs h % 4 == 0 and 16-byte aligned g, base and out.
+// One warp per (table row, group of VEC * 32 columns), eight per block: base + (0 + g[n0] + g[n1]
+// + ...) over the row's occurrences in ascending n. The additions stay in order. A row read up to
+// 32 times is summed by its warp, the loads of 8 occurrences issued together. A hotter row (the
+// mask token, a padding position: hundreds of occurrences) would be one warp waiting on memory
+// hundreds of times: the block takes it together instead, all 256 threads streaming 64
+// occurrences at a time into shared memory while one thread per column adds the previous 64 in
+// order. A row nobody read gets `base` (or zero). VEC = 4 reads and writes 16 bytes per lane and
+// needs h % 4 == 0 and 16-byte aligned g, base and out.
+constexpr uint32_t kHotRow = 32, kHotChunk = 64;
 template <int VEC>
 __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ g, const int32_t* __restrict__ sorted_id,
                                                       const int32_t* __restrict__ sorted_n, uint32_t n,
                                                       const float* __restrict__ base, float* __restrict__ out,
                                                       uint32_t rows, uint32_t h) {
-    const uint32_t span = VEC * 32, groups = (h + span - 1) / span;
+    constexpr uint32_t span = VEC * 32;
+    constexpr int LOADS = kHotChunk * span / VEC / 256;
+    __shared__ float stage[kHotChunk][span];
+    __shared__ uint32_t hot_item[8], hot_at[8], hot_count[8], hot_rows;
+    const uint32_t groups = (h + span - 1) / span;
     const uint64_t items = static_cast<uint64_t>(rows) * groups;
-    uint64_t item = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    const uint32_t lane = threadIdx.x & 31;
-    const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * blockDim.x) >> 5;
-    for (; item < items; item += warps) {
-        const uint32_t row = static_cast<uint32_t>(item / groups), col = static_cast<uint32_t>(item % groups) * span + lane * VEC;
-        const bool in = col < h;
-        float acc[VEC];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint64_t first = static_cast<uint64_t>(blockIdx.x) * 8; first < items; first += static_cast<uint64_t>(gridDim.x) * 8) {
+        if (threadIdx.x == 0) hot_rows = 0;
+        __syncthreads();
+        const uint64_t item = first + warp;
+        if (item < items) {
+            const uint32_t row = static_cast<uint32_t>(item / groups), col = static_cast<uint32_t>(item % groups) * span + lane * VEC;
+            const bool in = col < h;
+            uint32_t at = n ? warp_lower_bound(sorted_id, n, static_cast<int32_t>(row), lane) : 0u;
+            uint32_t count = 0;
+            if (at < n && __ldg(sorted_id + at) == static_cast<int32_t>(row))
+                count = warp_lower_bound(sorted_id, n, static_cast<int32_t>(row) + 1, lane) - at;
+            if (count > kHotRow) {
+                if (lane == 0) {
+                    uint32_t slot = atomicAdd(&hot_rows, 1u);
+                    hot_item[slot] = static_cast<uint32_t>(item - first);
+                    hot_at[slot] = at;
+                    hot_count[slot] = count;
+                }
+            } else {
+                float acc[VEC];
 #pragma unroll
-        for (int q = 0; q < VEC; ++q) acc[q] = 0.0f;
-        uint32_t at = n ? warp_lower_bound(sorted_id, n, static_cast<int32_t>(row), lane) : 0u;
-        while (at < n) {
-            // How many of the next 8 sorted entries still belong to this row.
-            const bool mine = lane < 8 && at + lane < n && __ldg(sorted_id + at + lane) == static_cast<int32_t>(row);
-            const uint32_t match = __ballot_sync(0xffffffffu, mine) & 0xffu;
-            const uint32_t here = __ffs(~match) - 1;  // entries are sorted: the matches are a prefix
-            if (here == 0) break;
-            const int32_t entry = lane < here ? __ldg(sorted_n + at + lane) : 0;
-            float v[8][VEC];
+                for (int q = 0; q < VEC; ++q) acc[q] = 0.0f;
+                for (uint32_t done = 0; done < count; done += 8) {
+                    const uint32_t here = min(8u, count - done);
+                    const int32_t entry = lane < here ? __ldg(sorted_n + at + done + lane) : 0;
+                    float v[8][VEC];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int32_t src = __shfl_sync(0xffffffffu, entry, e);
-                const float* from = g + static_cast<uint64_t>(src) * h + col;
-                if (static_cast<uint32_t>(e) < here && in) {
-                    if (VEC == 4) {
-                        const float4 f = *reinterpret_cast<const float4*>(from);
-                        v[e][0] = f.x; v[e][1 % VEC] = f.y; v[e][2 % VEC] = f.z; v[e][3 % VEC] = f.w;
-                    } else {
-                        v[e][0] = *from;
+                    for (int e = 0; e < 8; ++e) {
+                        const int32_t src = __shfl_sync(0xffffffffu, entry, e);
+                        const float* from = g + static_cast<uint64_t>(src) * h + col;
+                        if (static_cast<uint32_t>(e) < here && in) {
+                            if (VEC == 4) {
+                                const float4 f = *reinterpret_cast<const float4*>(from);
+                                v[e][0] = f.x; v[e][1 % VEC] = f.y; v[e][2 % VEC] = f.z; v[e][3 % VEC] = f.w;
+                            } else {
+                                v[e][0] = *from;
+                            }
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < VEC; ++q) v[e][q] = 0.0f;
+                        }
                     }
-                } else {
 #pragma unroll
-                    for (int q = 0; q < VEC; ++q) v[e][q] = 0.0f;
+                    for (int e = 0; e < 8; ++e)
+                        if (static_cast<uint32_t>(e) < here) {
+#pragma unroll
+                            for (int q = 0; q < VEC; ++q) acc[q] = acc[q] + v[e][q];
+                        }
+                }
+                if (in) {
+                    float* to = out + static_cast<uint64_t>(row) * h + col;
+                    if (VEC == 4) {
+                        float4 r = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
+                        if (base) {
+                            const float4 b = *reinterpret_cast<const float4*>(base + static_cast<uint64_t>(row) * h + col);
+                            r.x = b.x + r.x; r.y = b.y + r.y; r.z = b.z + r.z; r.w = b.w + r.w;
+                        }
+                        *reinterpret_cast<float4*>(to) = r;
+                    } else {
+                        *to = base ? base[static_cast<uint64_t>(row) * h + col] + acc[0] : acc[0];
+                    }
                 }
             }
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-                if (static_cast<uint32_t>(e) < here) {
-#pragma unroll
-                    for (int q = 0; q < VEC; ++q) acc[q] = acc[q] + v[e][q];
-                }
-            at += here;
-            if (here < 8) break;
         }
-        if (!in) continue;
-        float* to = out + static_cast<uint64_t>(row) * h + col;
-        if (VEC == 4) {
-            float4 r = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
-            if (base) {
-                const float4 b = *reinterpret_cast<const float4*>(base + static_cast<uint64_t>(row) * h + col);
-                r.x = b.x + r.x; r.y = b.y + r.y; r.z = b.z + r.z; r.w = b.w + r.w;
+        __syncthreads();
+        // The hot rows of this round, one after another, by the whole block (in slot order: which
+        // warp took which slot does not change any sum).
+        const uint32_t hot = hot_rows;
+        for (uint32_t slot = 0; slot < hot; ++slot) {
+            const uint64_t hot_id = first + hot_item[slot];
+            const uint32_t row = static_cast<uint32_t>(hot_id / groups), col0 = static_cast<uint32_t>(hot_id % groups) * span;
+            const uint32_t at = hot_at[slot], count = hot_count[slot];
+            float4 held4[VEC == 4 ? LOADS : 1];
+            float held1[VEC == 1 ? LOADS : 1];
+            auto fetch = [&](uint32_t chunk_start) {
+#pragma unroll
+                for (int j = 0; j < LOADS; ++j) {
+                    const uint32_t f = threadIdx.x + 256 * j;
+                    const uint32_t r = f / (span / VEC), c = (f % (span / VEC)) * VEC;
+                    const bool wanted = chunk_start + r < count && col0 + c < h;
+                    const int32_t src = wanted ? __ldg(sorted_n + at + chunk_start + r) : 0;
+                    const float* from = g + static_cast<uint64_t>(src) * h + col0 + c;
+                    if (VEC == 4) held4[j % (VEC == 4 ? LOADS : 1)] = wanted ? *reinterpret_cast<const float4*>(from) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    else held1[j % (VEC == 1 ? LOADS : 1)] = wanted ? *from : 0.0f;
+                }
+            };
+            float acc = 0.0f;
+            fetch(0);
+            for (uint32_t start = 0; start < count; start += kHotChunk) {
+#pragma unroll
+                for (int j = 0; j < LOADS; ++j) {
+                    const uint32_t f = threadIdx.x + 256 * j;
+                    const uint32_t r = f / (span / VEC), c = (f % (span / VEC)) * VEC;
+                    if (VEC == 4) *reinterpret_cast<float4*>(&stage[r][c]) = held4[j % (VEC == 4 ? LOADS : 1)];
+                    else stage[r][c] = held1[j % (VEC == 1 ? LOADS : 1)];
+                }
+                __syncthreads();
+                if (start + kHotChunk < count) fetch(start + kHotChunk);  // in flight while the chain below runs
+                if (threadIdx.x < span) {
+                    const uint32_t here = min(kHotChunk, count - start);
+                    for (uint32_t r = 0; r < here; ++r) acc = acc + stage[r][threadIdx.x];
+                }
+                __syncthreads();
             }
-            *reinterpret_cast<float4*>(to) = r;
-        } else {
-            *to = base ? base[static_cast<uint64_t>(row) * h + col] + acc[0] : acc[0];
+            if (threadIdx.x < span && col0 + threadIdx.x < h) {
+                const uint64_t where = static_cast<uint64_t>(row) * h + col0 + threadIdx.x;
+                out[where] = base ? base[where] + acc : acc;
+            }
         }
     }
 }
@@ -213,7 +277,7 @@ void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* o
     auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
     const bool vec = h % 4 == 0 && aligned(g) && aligned(out) && aligned(base);
     const uint64_t span = vec ? 128 : 32;
-    const uint64_t blocks = (rows * ((h + span - 1) / span) * 32 + 255) / 256;
+    const uint64_t blocks = (rows * ((h + span - 1) / span) + 7) / 8;
     const uint32_t grid = static_cast<uint32_t>(blocks > 148 * 32 ? 148 * 32 : blocks);
     if (vec) scatter_kernel<4><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
     else scatter_kernel<1><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));

@@ -65,8 +65,18 @@ __global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint
     uint32_t r0 = blockIdx.y * rows_per_chunk;
     uint32_t r1 = min(rows, r0 + rows_per_chunk);
     float acc = 0.0f;
-    if (c < h)
-        for (uint32_t r = r0 + threadIdx.y; r < r1; r += 8) acc += g[static_cast<uint64_t>(r) * h + c];
+    if (c < h) {
+        // Eight loads in flight per thread; the additions stay in row order.
+        uint32_t r = r0 + threadIdx.y;
+        for (; r + 56 < r1; r += 64) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldg(g + static_cast<uint64_t>(r + 8 * j) * h + c);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc += v[j];
+        }
+        for (; r < r1; r += 8) acc += __ldg(g + static_cast<uint64_t>(r) * h + c);
+    }
     shared[threadIdx.y][threadIdx.x] = acc;
     __syncthreads();
     if (threadIdx.y == 0 && c < h) {

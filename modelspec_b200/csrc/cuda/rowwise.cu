@@ -273,7 +273,10 @@ __global__ void cross_entropy_fused_kernel(const float* __restrict__ logits, con
 
 // The same, for rows of up to 32 * 1024 logits, with the row held in registers: one read of the
 // logits from memory (every load of the row in flight at once), one write of the gradient, and
-// each exp computed once.
+// each exp computed once, by the hardware exponential (relative error about 2^-21, far inside the
+// tolerance class every exp-based kernel is in), with one reciprocal of the row sum instead of a
+// division per element: 30,522 exps and divisions per row are otherwise as long as the row's
+// memory traffic.
 constexpr int kWideThreads = 1024, kWideItems = 32;
 __global__ void __launch_bounds__(kWideThreads, 1)
 cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
@@ -318,11 +321,12 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
     for (int i = 0; i < kWideItems; ++i) {
         uint32_t c = i * kWideThreads + tid;
         if (c < v) {
-            x[i] = expf(x[i] - m);
+            x[i] = __expf(x[i] - m);
             sum += x[i];
         }
     }
     const float total = block_sum(sum, shared);
+    const float inverse = 1.0f / total;
     const uint32_t label = static_cast<uint32_t>(labels[r]);
     if (tid == 0) row_loss[r] = m + logf(total) - (label < v ? row[label] : 0.0f);
     const bool zero = den == 0.0f;
@@ -332,7 +336,7 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
         uint32_t c = i * kWideThreads + tid;
         if (c < v) {
             float target = c == label ? 1.0f : 0.0f;
-            o[c] = zero ? 0.0f : scale * (x[i] / total - target);
+            o[c] = zero ? 0.0f : scale * (x[i] * inverse - target);
         }
     }
     }

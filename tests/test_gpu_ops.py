@@ -209,6 +209,26 @@ def test_embedding_gathers_rows_exactly_and_its_gradient_adds_in_ascending_order
     assert not res[1][1].reshape(rows, h)[17].any()
 
 
+@pytest.mark.parametrize("rows,h,n,hot", [(300, 128, 2000, 700), (90, 33, 900, 150), (1000, 256, 3000, 65), (64, 20, 50, 0)])
+def test_embedding_gradient_of_hot_rows_and_with_a_dense_addend(device, rows, h, n, hot):
+    """A row read hundreds of times (the mask token of an MLM batch) goes through the block-wide
+    path; the sum stays the sequential one, bit for bit, alone and with the dense gradient of a
+    tied weight added by the same launch."""
+    r = rng(rows + h + n)
+    ids = r.integers(0, rows, size=n).astype(np.int32)
+    ids[r.permutation(n)[:hot]] = 5
+    p = ProgramText()
+    i = p.input("ids", "i32", [n]); g = p.input("g", "f32", [n, h]); dense = p.input("dense", "f32", [rows, h])
+    d = p.op("EmbeddingGrad", [rows, h], [i, g], attr="[%d]" % rows)
+    d2 = p.op("EmbeddingGrad", [rows, h], [i, g], attr="[%d]" % rows)
+    tied = p.op("Add", [rows, h], [dense, d2])
+    p.output(d); p.output(tied)
+    res = run_both(device, p.text(), {"ids": ids, "g": values(r, n, h), "dense": values(r, rows, h)},
+                   outputs=[(d, rows * h), (tied, rows * h)])
+    for cpu, gpu in res:
+        assert_bits_equal(gpu, cpu)
+
+
 @pytest.mark.parametrize("rows,h", [(4, 8), (37, 128), (512, 768), (65, 33)])
 def test_layer_norm_and_its_gradients(device, rows, h):
     r = rng(rows * h)
