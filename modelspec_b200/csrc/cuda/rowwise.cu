@@ -300,37 +300,66 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
         den = static_cast<float>(block_sum(sum, shared64));
     }
     const float w = weights[r];
+    float x[kWideItems];
+    float total = 0.0f;
+    uint32_t label = 0;
     if (w == 0.0f) {
         if (tid == 0) row_loss[r] = 0.0f;
-        for (uint32_t c = tid; c < v; c += kWideThreads) o[c] = 0.0f;
     } else {
-    const float* row = logits + static_cast<uint64_t>(r) * v;
-    float x[kWideItems];
+        const float* row = logits + static_cast<uint64_t>(r) * v;
 #pragma unroll
-    for (int i = 0; i < kWideItems; ++i) {
-        uint32_t c = i * kWideThreads + tid;
-        x[i] = c < v ? __ldg(row + c) : -INFINITY;
-    }
-    float m = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < kWideItems; ++i)
-        if (x[i] > m) m = x[i];
-    m = block_max(m, shared);
-    float sum = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kWideItems; ++i) {
-        uint32_t c = i * kWideThreads + tid;
-        if (c < v) {
-            x[i] = __expf(x[i] - m);
-            sum += x[i];
+        for (int i = 0; i < kWideItems; ++i) {
+            uint32_t c = i * kWideThreads + tid;
+            x[i] = c < v ? __ldg(row + c) : -INFINITY;
         }
+        float m = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kWideItems; ++i)
+            if (x[i] > m) m = x[i];
+        m = block_max(m, shared);
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kWideItems; ++i) {
+            uint32_t c = i * kWideThreads + tid;
+            if (c < v) {
+                x[i] = __expf(x[i] - m);
+                sum += x[i];
+            }
+        }
+        total = block_sum(sum, shared);
+        label = static_cast<uint32_t>(labels[r]);
+        if (tid == 0) row_loss[r] = m + logf(total) - (label < v ? row[label] : 0.0f);
     }
-    const float total = block_sum(sum, shared);
-    const float inverse = 1.0f / total;
-    const uint32_t label = static_cast<uint32_t>(labels[r]);
-    if (tid == 0) row_loss[r] = m + logf(total) - (label < v ? row[label] : 0.0f);
+    // The loss, by the last block to get here: sum of w * l over sum of w, f64 sums, one rounding.
+    // Only thread 0's row loss has to be visible to that block, so only thread 0 fences, and the
+    // gradient stores below are not waited for: they drain while the SM's next block loads.
+    if (tid == 0) {
+        __threadfence();
+        const uint32_t before = atomicAdd(counter, 1u);
+        is_last = before + 1u == rows;
+        if (is_last) *counter = 0u;
+    }
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        double num = 0.0, den64 = 0.0;
+        for (uint32_t j = tid; j < rows; j += kWideThreads) {
+            double wj = static_cast<double>(weights[j]);
+            num = fma(wj, static_cast<double>(__ldcg(row_loss + j)), num);
+            den64 += wj;
+        }
+        num = block_sum(num, shared64);
+        den64 = block_sum(den64, shared64);
+        if (denominator != nullptr) den64 = static_cast<double>(denominator[0]);
+        if (tid == 0) loss[0] = den64 == 0.0 ? 0.0f : static_cast<float>(num / den64);
+    }
+    if (w == 0.0f) {
+        for (uint32_t c = tid; c < v; c += kWideThreads) o[c] = 0.0f;
+        return;
+    }
     const bool zero = den == 0.0f;
     const float scale = zero ? 0.0f : g[0] * w / den;
+    const float inverse = 1.0f / total;
 #pragma unroll
     for (int i = 0; i < kWideItems; ++i) {
         uint32_t c = i * kWideThreads + tid;
@@ -339,19 +368,6 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
             o[c] = zero ? 0.0f : scale * (x[i] * inverse - target);
         }
     }
-    }
-    // The loss, by the last block to finish: sum of w * l over sum of w, f64 sums, one rounding.
-    if (!last_block_arrives(counter, rows, &is_last)) return;
-    double num = 0.0, den64 = 0.0;
-    for (uint32_t j = tid; j < rows; j += kWideThreads) {
-        double wj = static_cast<double>(weights[j]);
-        num = fma(wj, static_cast<double>(__ldcg(row_loss + j)), num);
-        den64 += wj;
-    }
-    num = block_sum(num, shared64);
-    den64 = block_sum(den64, shared64);
-    if (denominator != nullptr) den64 = static_cast<double>(denominator[0]);
-    if (tid == 0) loss[0] = den64 == 0.0 ? 0.0f : static_cast<float>(num / den64);
 }
 
 inline uint32_t warp_row_blocks(uint64_t rows) { return static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock); }
