@@ -543,7 +543,7 @@ MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problem
 }
 
 void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t count, bool a_t, bool b_t, uint64_t m, uint64_t n,
-                     uint64_t k, uint32_t* status, bool leave_partials) {
+                     uint64_t k, uint32_t* status, bool leave_partials, MatmulPitches pitches) {
     if (m == 0 || n == 0 || count == 0) return;
     if (count > MAX_GROUP) throw std::invalid_argument("matmul_tc_group: more products than one launch carries");
     MatmulTcPlan p = matmul_tc_plan(m, n, k, 1, count);
@@ -551,9 +551,11 @@ void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t co
     args.m = static_cast<uint32_t>(m);
     args.n = static_cast<uint32_t>(n);
     args.k = static_cast<uint32_t>(k);
-    args.lda = static_cast<uint32_t>(a_t ? m : k);
-    args.ldb = static_cast<uint32_t>(b_t ? k : n);
-    args.ldc = static_cast<uint32_t>(n);
+    args.lda = pitches.a ? pitches.a : static_cast<uint32_t>(a_t ? m : k);
+    args.ldb = pitches.b ? pitches.b : static_cast<uint32_t>(b_t ? k : n);
+    // Partial tiles of a split k are dense; the pitch of C applies to the CTAs that write C itself.
+    args.ldc = (pitches.c && p.splits == 1) ? pitches.c : static_cast<uint32_t>(n);
+    if (pitches.c && p.splits > 1) throw std::invalid_argument("matmul_tc_group: a pitched result with a split k");
     args.splits = p.splits;
     args.kblocks_per_split = p.kblocks_per_split;
     // A float4 read starts at a multiple of 4 elements within a row, so rows must keep that phase.

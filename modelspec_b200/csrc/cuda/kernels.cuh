@@ -50,7 +50,7 @@ uint64_t sum_rows_scratch_floats(uint64_t rows, uint64_t h);
 // With `out` null only the chunk sums are written, as scratch[chunk][h]: finalize_sums adds them.
 uint64_t sum_rows_counters(uint64_t h);
 void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out,
-              uint32_t* counters = nullptr);
+              uint32_t* counters = nullptr, uint64_t ld = 0);
 
 // Deferred second stages. A kernel that leaves `chunks` partial results of `width` floats each,
 // stored [chunk][width], is finished by one launch over all such jobs of a step: up to 64 chunks
@@ -69,6 +69,9 @@ inline uint32_t sum_job_blocks(uint32_t chunks, uint64_t width) {
 void finalize_sums(cudaStream_t s, const SumJob* d_jobs, uint32_t jobs, uint32_t blocks);
 
 // ---- row kernels (rowwise.cu) -----------------------------------------------------------------
+// `ld`, `ld_out`, `ld_grad`: elements between the rows of the logits and of the gradient as stored
+// (0 = the row width v). A width that is not a multiple of 4 is stored with the pitch rounded up,
+// so that rows start on 16-byte boundaries; the padding is never read as data.
 void layer_norm(cudaStream_t s, const float* x, const float* gamma, const float* beta, float* out,
                 uint64_t rows, uint64_t h);
 void layer_norm_grad_x(cudaStream_t s, const float* x, const float* gamma, const float* g, float* out,
@@ -97,7 +100,7 @@ void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, ui
 // `global_den`, when not null, is a device float that replaces the weight sum in the division:
 // a data-parallel shard divides its own numerator by the weight sum of the whole batch.
 void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
-                   float* row_loss, const float* global_den, float* loss, uint64_t rows, uint64_t v);
+                   float* row_loss, const float* global_den, float* loss, uint64_t rows, uint64_t v, uint64_t ld = 0);
 // out[0] = f32(sum of the weights in f64).
 void weight_sum(cudaStream_t s, const float* weights, uint64_t rows, float* out);
 // out[n, c] = g * w[n] / f32(sum w) * (softmax(logits[n])[c] - [c == labels[n]]); all 0 when the
@@ -105,7 +108,7 @@ void weight_sum(cudaStream_t s, const float* weights, uint64_t rows, float* out)
 // unless `denominator_ready` says the caller already put the (whole-batch) sum there.
 void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
                         const float* g, bool denominator_ready, float* denominator, float* out, uint64_t rows,
-                        uint64_t v);
+                        uint64_t v, uint64_t ld = 0, uint64_t ld_out = 0);
 
 // Both at once, one visit of each logits row: `loss` as cross_entropy gives it, `grad` as
 // cross_entropy_grad gives it. `denominator` as in cross_entropy_grad; when it is ready (data
@@ -114,7 +117,8 @@ void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labe
 // launch in all (weight sum and final loss included) and one read of the logits from memory.
 void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
                              const float* g, bool denominator_ready, float* denominator, float* row_loss, float* loss,
-                             float* grad, uint64_t rows, uint64_t v, uint32_t* counter = nullptr);
+                             float* grad, uint64_t rows, uint64_t v, uint32_t* counter = nullptr, uint64_t ld = 0,
+                             uint64_t ld_grad = 0);
 
 // ---- embedding (embedding.cu) -----------------------------------------------------------------
 // out[n, :] = table[ids[n], :]; an id outside [0, rows) writes zeros and raises bit 0 of *status.
@@ -164,8 +168,13 @@ struct MatmulOperands {
     const float* bias;   // may be null
     float* workspace;    // matmul_tc_plan(m, n, k, 1, count).workspace_floats floats, or null when that is 0
 };
+// Elements between the rows of A, B and C as stored; 0 = dense (the row width). A pitched C needs
+// an unsplit k (matmul_tc_plan(...).splits == 1).
+struct MatmulPitches {
+    uint32_t a = 0, b = 0, c = 0;
+};
 void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t count, bool a_t, bool b_t, uint64_t m, uint64_t n,
-                     uint64_t k, uint32_t* status, bool leave_partials = false);
+                     uint64_t k, uint32_t* status, bool leave_partials = false, MatmulPitches pitches = {});
 
 // outer x inner independent products through one launch (grid.z = problem): matrix z of an
 // operand starts at base + (z / inner) * stride_outer + (z % inner) * stride_inner elements and

@@ -36,6 +36,7 @@ struct Slot {
         View       // a Transpose folded away: reads its source with the transposed flag flipped
     } kind = Dead;
     uint64_t bytes = 0;
+    uint32_t pitch = 0;        // elements between rows as stored; 0 = the row width
     uint64_t offset = 0;       // Arena, Input: byte offset; Const: index into the constant table
     uint32_t index = 0;        // Param, Moment: parameter index; View: position of the source
     char moment = 0;           // Moment: 'm' or 'v'

@@ -57,7 +57,7 @@ uint32_t whole_blocks(uint64_t n) {
 // `counters`, when not null, holds one zeroed word per column block: the last chunk block of a
 // column block to finish adds the chunk sums in ascending chunk order (what sum_rows_stage2 does
 // as a second launch) and writes `out`.
-__global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint32_t h, uint32_t rows_per_chunk,
+__global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint32_t h, uint32_t ld, uint32_t rows_per_chunk,
                                 float* __restrict__ partial, uint32_t* __restrict__ counters, float* __restrict__ out) {
     __shared__ float shared[8][32];
     __shared__ bool is_last;
@@ -71,11 +71,11 @@ __global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint
         for (; r + 56 < r1; r += 64) {
             float v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __ldg(g + static_cast<uint64_t>(r + 8 * j) * h + c);
+            for (int j = 0; j < 8; ++j) v[j] = __ldg(g + static_cast<uint64_t>(r + 8 * j) * ld + c);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc += v[j];
         }
-        for (; r < r1; r += 8) acc += __ldg(g + static_cast<uint64_t>(r) * h + c);
+        for (; r < r1; r += 8) acc += __ldg(g + static_cast<uint64_t>(r) * ld + c);
     }
     shared[threadIdx.y][threadIdx.x] = acc;
     __syncthreads();
@@ -176,12 +176,14 @@ uint64_t sum_rows_scratch_floats(uint64_t rows, uint64_t h) { return sum_rows_ch
 
 uint64_t sum_rows_counters(uint64_t h) { return (h + 31) / 32; }
 
-void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out, uint32_t* counters) {
+void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out, uint32_t* counters,
+              uint64_t ld) {
     if (h == 0) return;
+    if (ld == 0) ld = h;
     uint32_t chunks = sum_rows_chunks(rows);
     uint32_t rows_per_chunk = static_cast<uint32_t>((rows + chunks - 1) / chunks);
     dim3 grid(static_cast<uint32_t>((h + 31) / 32), chunks);
-    sum_rows_stage1<<<grid, dim3(32, 8), 0, s>>>(g, static_cast<uint32_t>(rows), static_cast<uint32_t>(h),
+    sum_rows_stage1<<<grid, dim3(32, 8), 0, s>>>(g, static_cast<uint32_t>(rows), static_cast<uint32_t>(h), static_cast<uint32_t>(ld),
                                                  rows_per_chunk, (chunks == 1 && out) ? out : scratch,
                                                  (chunks > 1 && out) ? counters : nullptr, out);
     check_launch("sum_rows");

@@ -173,7 +173,7 @@ __global__ void softmax_grad_kernel(const float* __restrict__ y, const float* __
 
 __global__ void cross_entropy_rows_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
                                           const float* __restrict__ weights, float* __restrict__ row_loss,
-                                          uint32_t v) {
+                                          uint32_t v, uint32_t ld) {
     __shared__ float shared[33];
     uint32_t r = blockIdx.x;
     // A row of weight 0 adds w * l = 0 to the loss whatever its logits: skip its passes.
@@ -181,7 +181,7 @@ __global__ void cross_entropy_rows_kernel(const float* __restrict__ logits, cons
         if (threadIdx.x == 0) row_loss[r] = 0.0f;
         return;
     }
-    const float* row = logits + static_cast<uint64_t>(r) * v;
+    const float* row = logits + static_cast<uint64_t>(r) * ld;
     float max, total;
     block_row_softmax(row, v, shared, &max, &total);
     if (threadIdx.x == 0) {
@@ -219,16 +219,16 @@ __global__ void weight_sum_kernel(const float* __restrict__ weights, uint32_t ro
 __global__ void cross_entropy_grad_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
                                           const float* __restrict__ weights, const float* __restrict__ g,
                                           const float* __restrict__ denominator, float* __restrict__ out,
-                                          uint32_t v) {
+                                          uint32_t v, uint32_t ld, uint32_t ld_out) {
     __shared__ float shared[33];
     uint32_t r = blockIdx.x;
-    float* o = out + static_cast<uint64_t>(r) * v;
+    float* o = out + static_cast<uint64_t>(r) * ld_out;
     float den = denominator[0], w = weights[r];
     if (den == 0.0f || w == 0.0f) {
         for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) o[c] = 0.0f;
         return;
     }
-    const float* row = logits + static_cast<uint64_t>(r) * v;
+    const float* row = logits + static_cast<uint64_t>(r) * ld;
     float max, total;
     block_row_softmax(row, v, shared, &max, &total);
     float scale = g[0] * w / den;
@@ -245,17 +245,17 @@ __global__ void cross_entropy_grad_kernel(const float* __restrict__ logits, cons
 __global__ void cross_entropy_fused_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
                                            const float* __restrict__ weights, const float* __restrict__ g,
                                            const float* __restrict__ denominator, float* __restrict__ row_loss,
-                                           float* __restrict__ out, uint32_t v) {
+                                           float* __restrict__ out, uint32_t v, uint32_t ld, uint32_t ld_out) {
     __shared__ float shared[33];
     uint32_t r = blockIdx.x;
-    float* o = out + static_cast<uint64_t>(r) * v;
+    float* o = out + static_cast<uint64_t>(r) * ld_out;
     float den = denominator[0], w = weights[r];
     if (w == 0.0f) {
         if (threadIdx.x == 0) row_loss[r] = 0.0f;
         for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) o[c] = 0.0f;
         return;
     }
-    const float* row = logits + static_cast<uint64_t>(r) * v;
+    const float* row = logits + static_cast<uint64_t>(r) * ld;
     float max, total;
     block_row_softmax(row, v, shared, &max, &total);
     uint32_t label = static_cast<uint32_t>(labels[r]);
@@ -277,18 +277,23 @@ __global__ void cross_entropy_fused_kernel(const float* __restrict__ logits, con
 // tolerance class every exp-based kernel is in), with one reciprocal of the row sum instead of a
 // division per element: 30,522 exps and divisions per row are otherwise as long as the row's
 // memory traffic.
+// VEC = 4 reads and writes 16 bytes per thread (row pitches that are multiples of 4 floats).
 constexpr int kWideThreads = 1024, kWideItems = 32;
+template <int VEC>
 __global__ void __launch_bounds__(kWideThreads, 1)
 cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
                                 const float* __restrict__ weights, const float* __restrict__ g,
                                 const float* __restrict__ denominator, float* __restrict__ row_loss,
-                                float* __restrict__ out, uint32_t v, uint32_t* __restrict__ counter,
-                                float* __restrict__ loss) {
+                                float* __restrict__ out, uint32_t v, uint32_t ld, uint32_t ld_out,
+                                uint32_t* __restrict__ counter, float* __restrict__ loss) {
+    // Element i of this thread is column column_of(i): consecutive threads take consecutive
+    // (groups of VEC) columns.
+    auto column_of = [](int i, uint32_t tid) { return (static_cast<uint32_t>(i / VEC) * kWideThreads + tid) * VEC + i % VEC; };
     __shared__ float shared[33];
     __shared__ double shared64[33];
     __shared__ bool is_last;
     const uint32_t r = blockIdx.x, tid = threadIdx.x, rows = gridDim.x;
-    float* o = out + static_cast<uint64_t>(r) * v;
+    float* o = out + static_cast<uint64_t>(r) * ld_out;
     // The weight sum: given (the whole batch's, data parallel), or summed here by every block in
     // the same order (f64 over the block, one rounding), so that no launch has to precede this one.
     float den;
@@ -306,11 +311,24 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
     if (w == 0.0f) {
         if (tid == 0) row_loss[r] = 0.0f;
     } else {
-        const float* row = logits + static_cast<uint64_t>(r) * v;
+        const float* row = logits + static_cast<uint64_t>(r) * ld;
+        if (VEC == 4) {
 #pragma unroll
-        for (int i = 0; i < kWideItems; ++i) {
-            uint32_t c = i * kWideThreads + tid;
-            x[i] = c < v ? __ldg(row + c) : -INFINITY;
+            for (int i = 0; i < kWideItems; i += 4) {
+                const uint32_t c = column_of(i, tid);
+                float4 f = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                if (c < v) f = __ldg(reinterpret_cast<const float4*>(row + c));  // the pitch covers the whole float4
+                x[i] = f.x;
+                x[i + 1] = c + 1 < v ? f.y : -INFINITY;
+                x[i + 2] = c + 2 < v ? f.z : -INFINITY;
+                x[i + 3] = c + 3 < v ? f.w : -INFINITY;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < kWideItems; ++i) {
+                const uint32_t c = column_of(i, tid);
+                x[i] = c < v ? __ldg(row + c) : -INFINITY;
+            }
         }
         float m = -INFINITY;
 #pragma unroll
@@ -320,7 +338,7 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
         float sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < kWideItems; ++i) {
-            uint32_t c = i * kWideThreads + tid;
+            const uint32_t c = column_of(i, tid);
             if (c < v) {
                 x[i] = __expf(x[i] - m);
                 sum += x[i];
@@ -353,19 +371,27 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
         if (denominator != nullptr) den64 = static_cast<double>(denominator[0]);
         if (tid == 0) loss[0] = den64 == 0.0 ? 0.0f : static_cast<float>(num / den64);
     }
-    if (w == 0.0f) {
-        for (uint32_t c = tid; c < v; c += kWideThreads) o[c] = 0.0f;
-        return;
-    }
-    const bool zero = den == 0.0f;
+    const bool zero = den == 0.0f || w == 0.0f;
     const float scale = zero ? 0.0f : g[0] * w / den;
-    const float inverse = 1.0f / total;
+    const float inverse = zero ? 0.0f : 1.0f / total;
 #pragma unroll
     for (int i = 0; i < kWideItems; ++i) {
-        uint32_t c = i * kWideThreads + tid;
-        if (c < v) {
-            float target = c == label ? 1.0f : 0.0f;
-            o[c] = zero ? 0.0f : scale * (x[i] * inverse - target);
+        const uint32_t c = column_of(i, tid);
+        const float target = c == label ? 1.0f : 0.0f;
+        x[i] = zero ? 0.0f : scale * (x[i] * inverse - target);
+    }
+    if (VEC == 4) {
+#pragma unroll
+        for (int i = 0; i < kWideItems; i += 4) {
+            const uint32_t c = column_of(i, tid);
+            // Columns past v inside the pitch are padding nobody reads: the whole float4 is written.
+            if (c < v) *reinterpret_cast<float4*>(o + c) = make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kWideItems; ++i) {
+            const uint32_t c = column_of(i, tid);
+            if (c < v) o[c] = x[i];
         }
     }
 }
@@ -580,10 +606,11 @@ void weight_sum(cudaStream_t s, const float* weights, uint64_t rows, float* out)
 }
 
 void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
-                   float* row_loss, const float* global_den, float* loss, uint64_t rows, uint64_t v) {
+                   float* row_loss, const float* global_den, float* loss, uint64_t rows, uint64_t v, uint64_t ld) {
+    if (ld == 0) ld = v;
     if (rows > 0) {
         cross_entropy_rows_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, row_loss,
-                                                                                      static_cast<uint32_t>(v));
+                                                                                      static_cast<uint32_t>(v), static_cast<uint32_t>(ld));
         check_launch("cross_entropy");
     }
     cross_entropy_loss_kernel<<<1, 1024, 0, s>>>(row_loss, weights, static_cast<uint32_t>(rows), global_den, loss);
@@ -592,10 +619,20 @@ void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, c
 
 void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
                              const float* g, bool denominator_ready, float* denominator, float* row_loss, float* loss,
-                             float* grad, uint64_t rows, uint64_t v, uint32_t* counter) {
+                             float* grad, uint64_t rows, uint64_t v, uint32_t* counter, uint64_t ld, uint64_t ld_grad) {
+    if (ld == 0) ld = v;
+    if (ld_grad == 0) ld_grad = v;
+    const uint32_t vv = static_cast<uint32_t>(v), l1 = static_cast<uint32_t>(ld), l2 = static_cast<uint32_t>(ld_grad);
     if (rows > 0 && counter != nullptr && v <= static_cast<uint64_t>(kWideThreads) * kWideItems) {
-        cross_entropy_fused_wide_kernel<<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(
-            logits, labels, weights, g, denominator_ready ? denominator : nullptr, row_loss, grad, static_cast<uint32_t>(v), counter, loss);
+        const float* den = denominator_ready ? denominator : nullptr;
+        const bool vec = ld % 4 == 0 && ld_grad % 4 == 0 && reinterpret_cast<uintptr_t>(logits) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(grad) % 16 == 0;
+        if (vec)
+            cross_entropy_fused_wide_kernel<4><<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(logits, labels, weights, g, den, row_loss,
+                                                                                                    grad, vv, l1, l2, counter, loss);
+        else
+            cross_entropy_fused_wide_kernel<1><<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(logits, labels, weights, g, den, row_loss,
+                                                                                                    grad, vv, l1, l2, counter, loss);
         check_launch("cross_entropy_with_grad");
         return;
     }
@@ -605,7 +642,7 @@ void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t*
     }
     if (rows > 0) {
         cross_entropy_fused_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, g, denominator, row_loss,
-                                                                                       grad, static_cast<uint32_t>(v));
+                                                                                       grad, vv, l1, l2);
         check_launch("cross_entropy_with_grad");
     }
     cross_entropy_loss_kernel<<<1, 1024, 0, s>>>(row_loss, weights, static_cast<uint32_t>(rows), denominator_ready ? denominator : nullptr, loss);
@@ -614,14 +651,17 @@ void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t*
 
 void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
                         const float* g, bool denominator_ready, float* denominator, float* out, uint64_t rows,
-                        uint64_t v) {
+                        uint64_t v, uint64_t ld, uint64_t ld_out) {
     if (rows == 0) return;
+    if (ld == 0) ld = v;
+    if (ld_out == 0) ld_out = v;
     if (!denominator_ready) {
         weight_sum_kernel<<<1, 1024, 0, s>>>(weights, static_cast<uint32_t>(rows), denominator);
         check_launch("cross_entropy_grad");
     }
-    cross_entropy_grad_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, g, denominator,
-                                                                                  out, static_cast<uint32_t>(v));
+    cross_entropy_grad_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, g, denominator, out,
+                                                                                  static_cast<uint32_t>(v), static_cast<uint32_t>(ld),
+                                                                                  static_cast<uint32_t>(ld_out));
     check_launch("cross_entropy_grad");
 }
 

@@ -655,9 +655,10 @@ struct Scheduler {
             case Op::MatMul: {
                 uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(in[0]);
                 std::vector<Product> group = {claim_product(at)};
+                const bool pitched = pitch_of(group[0].a) || pitch_of(group[0].b) || pitchable(group[0].result);
                 // Later matmuls of the same shape and storage form whose operands already exist
                 // (the three projections of an attention layer, their gradients) join the launch.
-                if (!(P->flags & MSX_PLAN_EXACT_MATMUL))
+                if (!(P->flags & MSX_PLAN_EXACT_MATMUL) && !pitched)
                     for (uint32_t later = at + 1; later < prog.nodes.size() && later < at + 64 && group.size() < 4; ++later)
                         if (joins(later, group[0], at, m, n, kk)) group.push_back(claim_product(later));
                 emit_matmul(nd, group, m, n, kk);
@@ -747,16 +748,16 @@ struct Scheduler {
             }
             case Op::SumRows: {
                 uint32_t g = in[0];
-                uint64_t r = rows_of(g), h = cols_of(g);
+                uint64_t r = rows_of(g), h = cols_of(g), ld = pitch_of(g);
                 if (deferrable(at)) {
                     uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4);
-                    emit("sum_rows", nd, in, {tmp}, [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), nullptr); });
+                    emit("sum_rows", nd, in, {tmp}, [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), nullptr, nullptr, ld); });
                     deferred.push_back({tmp, 0, k::sum_rows_chunks(r), h, at});
                     break;
                 }
                 uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4), ctr = counters(k::sum_rows_counters(h));
                 emit("sum_rows", nd, in, {at, tmp},
-                     [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), plan->f(at), plan->counter(ctr)); });
+                     [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), plan->f(at), plan->counter(ctr), ld); });
                 break;
             }
             case Op::LayerNorm: {
@@ -818,7 +819,7 @@ struct Scheduler {
             case Op::AttentionGradV: schedule_attention(at); break;
             case Op::CrossEntropy: {
                 uint32_t logits = in[0], labels = in[1], weights = in[2];
-                uint64_t r = rows_of(logits), v = cols_of(logits);
+                uint64_t r = rows_of(logits), v = cols_of(logits), ld = pitch_of(logits);
                 uint32_t row_loss = scratch(std::max<uint64_t>(r, 1) * 4), den = scratch(4);
                 // The gradient op of the same loss reads the same row maxima and sums: when its
                 // incoming adjoint is a constant (the seed), one pass over the logits gives both.
@@ -837,6 +838,8 @@ struct Scheduler {
                     Slot& gs = P->slots[gpos];
                     gs.kind = Slot::Arena;
                     gs.bytes = std::max<uint64_t>(node(gpos).ty.count() * 4, 4);
+                    if (pitchable(gpos)) set_pitch(gpos);
+                    const uint64_t ld_grad = gs.pitch;
                     uint32_t ctr = counters(1);
                     emit("cross_entropy_with_grad", nd, {logits, labels, weights, seed}, {at, gpos, row_loss, den}, [=](cudaStream_t s) {
                         if (plan->comm) {
@@ -844,7 +847,8 @@ struct Scheduler {
                             all_reduce(plan, plan->f(den), 1, false, s);
                         }
                         k::cross_entropy_with_grad(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(seed), plan->comm != nullptr,
-                                                   plan->f(den), plan->f(row_loss), plan->f(at), plan->f(gpos), r, v, plan->counter(ctr));
+                                                   plan->f(den), plan->f(row_loss), plan->f(at), plan->f(gpos), r, v, plan->counter(ctr), ld,
+                                                   ld_grad);
                         all_reduce(plan, plan->f(at), 1, false, s);
                     });
                     break;
@@ -856,14 +860,16 @@ struct Scheduler {
                         all_reduce(plan, plan->f(den), 1, false, s);
                     }
                     k::cross_entropy(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(row_loss),
-                                     plan->comm ? plan->f(den) : nullptr, plan->f(at), r, v);
+                                     plan->comm ? plan->f(den) : nullptr, plan->f(at), r, v, ld);
                     all_reduce(plan, plan->f(at), 1, false, s);
                 });
                 break;
             }
             case Op::CrossEntropyGrad: {
                 uint32_t logits = in[0], labels = in[1], weights = in[2], g = in[3];
-                uint64_t r = rows_of(logits), v = cols_of(logits);
+                uint64_t r = rows_of(logits), v = cols_of(logits), ld = pitch_of(logits);
+                if (pitchable(at)) set_pitch(at);
+                const uint64_t ld_out = out.pitch;
                 uint32_t den = scratch(4);
                 emit("cross_entropy_grad", nd, in, {at, den}, [=](cudaStream_t s) {
                     if (plan->comm) {
@@ -871,7 +877,7 @@ struct Scheduler {
                         all_reduce(plan, plan->f(den), 1, false, s);
                     }
                     k::cross_entropy_grad(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(g), plan->comm != nullptr,
-                                          plan->f(den), plan->f(at), r, v);
+                                          plan->f(den), plan->f(at), r, v, ld, ld_out);
                 });
                 break;
             }
@@ -956,6 +962,40 @@ struct Scheduler {
         return true;
     }
 
+    // A matrix whose width is not a multiple of 4 floats (a 30,522-wide logits matrix) is stored
+    // with its pitch rounded up when every kernel that touches it takes a pitch: rows then start
+    // on 16-byte boundaries and are read and written 16 bytes at a time. The padding is never read
+    // as data.
+    bool pitchable(uint32_t v) const {
+        if (P->flags & MSX_PLAN_EXACT_MATMUL) return false;
+        const msx::Type& t = node(v).ty;
+        if (t.rank() != 2 || t.i32 || t.shape[1] % 4 == 0 || t.shape[1] < 8) return false;
+        for (const msx::Output& o : prog.outputs)
+            if (pos(o.value) == v) return false;
+        for (uint32_t u : users[v]) {
+            const Node& un = node(u);
+            bool ok = false;
+            if (un.op == Op::MatMul || un.op == Op::SumRows) ok = true;
+            if ((un.op == Op::CrossEntropy || un.op == Op::CrossEntropyGrad) && pos(un.operands[0]) == v) {
+                ok = true;
+                for (size_t i = 1; i < un.operands.size(); ++i) ok = ok && pos(un.operands[i]) != v;
+            }
+            if (un.op == Op::Transpose && P->slots[u].kind == Slot::View) ok = true;  // folded: read only by matmuls
+            if (!ok) return false;
+        }
+        return true;
+    }
+    void set_pitch(uint32_t v) {
+        const msx::Type& t = node(v).ty;
+        Slot& s = P->slots[v];
+        s.pitch = static_cast<uint32_t>((t.shape[1] + 3) / 4 * 4);
+        s.bytes = t.shape[0] * s.pitch * 4;
+    }
+    uint32_t pitch_of(uint32_t p) const {
+        const Slot& s = P->slots[p];
+        return s.kind == Slot::View ? pitch_of(s.index) : s.pitch;
+    }
+
     // One product of a matmul launch: `result` = the node whose slot receives it (the AddRows node
     // when the bias rides in the epilogue), `flip_*` reads the operand as the transpose of what its
     // slot says.
@@ -1009,6 +1049,7 @@ struct Scheduler {
         if (nd.ty.shape[0] != m || nd.ty.shape[1] != n || node(pos(nd.operands[0])).ty.shape.at(1) != kk) return false;
         Product p = describe_product(later);
         if (!ready_before(p.a, at) || !ready_before(p.b, at)) return false;
+        if (pitch_of(p.a) || pitch_of(p.b) || pitchable(p.result)) return false;
         if (P->transposed(p.a) != P->transposed(first.a) || P->transposed(p.b) != P->transposed(first.b)) return false;
         if ((p.bias >= 0) != (first.bias >= 0)) return false;
         if (p.bias >= 0 && static_cast<uint32_t>(p.bias) >= at) return false;
@@ -1043,6 +1084,13 @@ struct Scheduler {
         // A split k whose sum only the optimizer reads (a weight gradient) stays as partial
         // tiles: the finalize launch adds them with every other deferred sum.
         const bool defer = tc.workspace_floats != 0 && first.bias < 0 && deferrable(first.result);
+        k::MatmulPitches pitches;
+        pitches.a = pitch_of(first.a);
+        pitches.b = pitch_of(first.b);
+        if (count == 1 && tc.splits == 1 && pitchable(first.result)) {
+            set_pitch(first.result);
+            pitches.c = P->slots[first.result].pitch;
+        }
         std::vector<int> workspaces;
         for (const Product& p : group) {
             int ws = -1;
@@ -1065,7 +1113,7 @@ struct Scheduler {
                 operands[g].workspace = workspaces[g] >= 0 ? plan->f(static_cast<uint32_t>(workspaces[g])) : nullptr;
             }
             k::matmul_tc_group(s, operands, count, plan->transposed(first.a) != a_t_flip, plan->transposed(first.b) != b_t_flip, m, n, kk,
-                               plan->d_status, defer);
+                               plan->d_status, defer, pitches);
         });
         l.flop = 2 * m * n * kk * count;
     }

@@ -93,6 +93,35 @@ def test_tensor_core_matmul_within_the_kernel_tolerance(device, m, k, n, form):
     assert np.abs(gpu.astype(np.float64) - cpu).max() <= 4e-6 * max(terms.max(), 1e-30)
 
 
+@pytest.mark.parametrize("rows,h,v", [(64, 32, 50), (130, 64, 1002), (96, 128, 4099)])
+def test_a_vocabulary_head_of_odd_width_through_padded_rows(device, rows, h, v):
+    """logits = x W^T + b, cross entropy and its gradient, the bias gradient (column sums of the
+    logits gradient) and both matmuls that read it, with a width that is not a multiple of 4: on
+    the tensor-core path the logits and their gradient are stored with padded rows, which no
+    result may show."""
+    r = rng(rows + v)
+    p = ProgramText()
+    x = p.input("x", "f32", [rows, h]); w = p.input("w", "f32", [v, h]); b = p.input("b", "f32", [v])
+    labels = p.input("labels", "i32", [rows]); weights = p.input("weights", "f32", [rows]); seed = p.input("seed", "f32", [])
+    wt = p.op("Transpose", [h, v], [w])
+    raw = p.op("MatMul", [rows, v], [x, wt])
+    logits = p.op("AddRows", [rows, v], [raw, b])
+    loss = p.op("CrossEntropy", [], [logits, labels, weights])
+    dlogits = p.op("CrossEntropyGrad", [rows, v], [logits, labels, weights, seed])
+    db = p.op("SumRows", [v], [dlogits])
+    dx = p.op("MatMul", [rows, h], [dlogits, w])
+    dlt = p.op("Transpose", [v, rows], [dlogits])
+    dw = p.op("MatMul", [v, h], [dlt, x])
+    for value in (loss, db, dx, dw):
+        p.output(value)
+    feed = {"x": values(r, rows, h), "w": values(r, v, h) * 0.2, "b": values(r, v) * 0.1,
+            "labels": r.integers(0, v, size=rows).astype(np.int32), "weights": (r.random(rows) < 0.8).astype(np.float32),
+            "seed": np.float32(1.0)}
+    res = run_both(device, p.text(), feed, outputs=[(loss, 1), (db, v), (dx, rows * h), (dw, v * h)], flags=M.PLAN_NO_GRAPH)
+    for (cpu, gpu), what in zip(res, ("loss", "bias gradient", "input gradient", "weight gradient")):
+        assert_kernel_close(gpu, cpu, scale=np.full(cpu.shape, max(1.0, float(np.abs(cpu).max()))), what=what)
+
+
 def test_transposed_matmul_result_is_the_swapped_matmul(device):
     """Transpose(MatMul(A^T, G)) is scheduled as one matmul with its operands swapped."""
     r = rng(5)
