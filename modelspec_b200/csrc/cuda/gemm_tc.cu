@@ -50,6 +50,11 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives
 // The cost model of matmul_tc_plan, in SM cycles (tuning builds may override).
 #ifndef MSX_TC_FIXED
 #define MSX_TC_FIXED 5000.0
+// Per k block of one CTA, bounded by how far ahead its loads run (SETS - 1 blocks) ...
+#define MSX_TC_LATENCY32 700.0
+#define MSX_TC_LATENCY64 950.0
+#define MSX_TC_LATENCY128 2000.0
+// ... and per k block of an SM, bounded by shared-memory bandwidth, however many CTAs share it.
 #define MSX_TC_KB32 450.0
 #define MSX_TC_KB64 520.0
 #define MSX_TC_KB128 800.0
@@ -79,7 +84,8 @@ struct TcArgs {
     uint32_t m, n, k;
     uint32_t lda, ldb, ldc;        // row pitch, in elements, of each matrix as stored
     uint32_t kblocks_per_split;
-    uint32_t a_vec, b_vec;         // 16-byte loads are aligned for this operand
+    uint32_t a_vec, b_vec, c_vec;  // 16-byte accesses are aligned for this operand
+    uint32_t c_padded;             // the columns of C between n and ldc are padding that may be overwritten
     // Batched products: grid.z = batch index z, split as (z / inner, z % inner); each matrix of
     // problem z starts at outer * stride_outer + inner * stride_inner elements. inner = 0: not batched.
     uint32_t batch_inner;
@@ -335,26 +341,25 @@ __global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
                 alive = deposit(kb, av[s], bv[s]);
             }
         }
-        // ---- epilogue: tensor memory -> registers -> global -----------------------------------
+        // ---- epilogue: tensor memory -> shared memory -> global --------------------------------
         // Lanes 0-63 of tensor memory hold the A_hi rows, 64-127 the A_lo rows of the same 64 tile
         // rows; columns [0, BN) the products with B_hi, [BN, 2 BN) those with B_lo. A warp reads
-        // its lane quarter, adds the two column halves, and the lo warps hand their sums to the hi
-        // warps of the same rows through shared memory (the stages are free by now).
+        // its lane quarter, adds the two column halves and writes the sums, row-major, into one of
+        // two shared-memory tiles (hi rows, lo rows; the stages are free by now). After a barrier
+        // all eight warps add the two tiles and write C a whole tile row at a time, 16 bytes per
+        // lane where the pitch of C allows.
         if (alive && kblocks > 0) alive = mbar_wait(smem_u32(&bars[2 * STAGES]), 0, abort_flag, args.status);
         alive = __all_sync(0xffffffffu, alive);  // tcgen05.ld is warp-wide: decide as a warp
         if (tid == 0) TRACE(6);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t quarter = warp & 3u, half = warp >> 2;
-        const bool holds_hi = quarter < 2;
-        const uint32_t row_block = (quarter & 1u) * 32u;
         constexpr int PARTS = BN == 128 ? 2 : 1;
-        constexpr uint32_t EPILOGUE_THREADS = BN == 32 ? 128u : 256u;
+        constexpr uint32_t PITCH = BN + 4;  // 16-byte phases of consecutive rows fall on distinct banks
         const bool drains = BN != 32 || half == 0;  // a 32-column tile is one block per lane quarter
-        float* staging = reinterpret_cast<float*>(tiles);  // [warp][part][32 x 33]
-        float* __restrict__ out = batched ? args.c[0] + z_outer * args.c_outer + z_inner * args.c_inner
-                                          : args.c[product] + static_cast<uint64_t>(split) * args.m * args.ldc;
-        const float* __restrict__ bias_row = args.bias[product];
+        float* tile_hi = reinterpret_cast<float*>(tiles);
+        float* tile_lo = tile_hi + BM * PITCH;
         if (drains) {
+            float* to_row = (quarter < 2 ? tile_hi : tile_lo) + ((quarter & 1u) * 32u + lane) * PITCH;
 #pragma unroll
             for (int part = 0; part < PARTS; ++part) {
                 const uint32_t col = BN == 128 ? half * 64u + part * 32u : (BN == 64 ? half * 32u : 0u);
@@ -368,39 +373,45 @@ __global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) { r1[j] = 0u; r2[j] = 0u; }  // an empty k range contributes zeros
                 }
-                float* mine = staging + (warp * PARTS + part) * (32 * 33);
-                // Lane = row on the way in, lane = column on the way out; pitch 33 keeps both
-                // conflict-free.
-                if (!holds_hi) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) mine[lane * 33 + j] = __uint_as_float(r1[j]) + __uint_as_float(r2[j]);
+                for (int j = 0; j < 32; j += 4) {
+                    float4 v;
+                    v.x = __uint_as_float(r1[j]) + __uint_as_float(r2[j]);
+                    v.y = __uint_as_float(r1[j + 1]) + __uint_as_float(r2[j + 1]);
+                    v.z = __uint_as_float(r1[j + 2]) + __uint_as_float(r2[j + 2]);
+                    v.w = __uint_as_float(r1[j + 3]) + __uint_as_float(r2[j + 3]);
+                    *reinterpret_cast<float4*>(to_row + col + j) = v;
                 }
-                loaders_barrier(EPILOGUE_THREADS);
-                if (holds_hi) {
-                    const float* other = staging + ((warp + 2) * PARTS + part) * (32 * 33);
-                    // `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
+            }
+        }
+        loaders_barrier(LOADER_THREADS);
+        if (tid == 0) TRACE(13);
+        float* __restrict__ out = batched ? args.c[0] + z_outer * args.c_outer + z_inner * args.c_inner
+                                          : args.c[product] + static_cast<uint64_t>(split) * args.m * args.ldc;
+        const float* __restrict__ bias_row = args.bias[product];
+        constexpr uint32_t LANES_PER_ROW = BN / 4, ROWS_PER_PASS = 32 / LANES_PER_ROW;
+        const uint32_t c4 = (lane % LANES_PER_ROW) * 4, gn = n0 + c4;
+#pragma unroll 4
+        for (uint32_t r = warp * ROWS_PER_PASS + lane / LANES_PER_ROW; r < BM; r += 8 * ROWS_PER_PASS) {
+            const uint32_t gm = m0 + r;
+            if (gm >= args.m || gn >= args.n) continue;
+            const float4 h = *reinterpret_cast<const float4*>(tile_hi + r * PITCH + c4);
+            const float4 l = *reinterpret_cast<const float4*>(tile_lo + r * PITCH + c4);
+            // `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
+            float v[4] = {(h.x + l.x) + 0.0f, (h.y + l.y) + 0.0f, (h.z + l.z) + 0.0f, (h.w + l.w) + 0.0f};
+            if (bias_row) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        mine[lane * 33 + j] = ((__uint_as_float(r1[j]) + __uint_as_float(r2[j])) + other[lane * 33 + j]) + 0.0f;
-                    __syncwarp();
-                    // A warp writes whole rows: 32 consecutive columns per store, whatever the row pitch.
-                    const uint32_t gn = n0 + col + lane, row0 = m0 + row_block;
-                    if (gn < args.n && row0 < args.m) {
-                        const float bias = bias_row ? bias_row[gn] : 0.0f;
-                        float* dst = out + static_cast<uint64_t>(row0) * args.ldc + gn;
-                        const uint32_t rows_here = min(32u, args.m - row0);
-                        if (rows_here == 32) {
-                            // All the shared-memory reads first: the stores then leave back to back.
-                            float v[32];
+                for (int q = 0; q < 4; ++q)
+                    if (gn + q < args.n) v[q] = v[q] + bias_row[gn + q];
+            }
+            float* dst = out + static_cast<uint64_t>(gm) * args.ldc + gn;
+            // Inside the pitch a whole float4 may be written: what lies past n is padding.
+            if (args.c_vec && (gn + 4 <= args.n || (args.c_padded && gn + 4 <= args.ldc))) {
+                *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
 #pragma unroll
-                            for (int rr = 0; rr < 32; ++rr) v[rr] = mine[rr * 33 + lane] + bias;
-#pragma unroll
-                            for (int rr = 0; rr < 32; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = v[rr];
-                        } else {
-                            for (uint32_t rr = 0; rr < rows_here; ++rr) dst[static_cast<uint64_t>(rr) * args.ldc] = mine[rr * 33 + lane] + bias;
-                        }
-                    }
-                }
+                for (int q = 0; q < 4; ++q)
+                    if (gn + q < args.n) dst[q] = v[q];
             }
         }
     } else {
@@ -505,13 +516,16 @@ bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0;
 }  // namespace
 
 // Tile width and k split by a cost model in SM cycles, fitted to measured phase times of this
-// kernel: a CTA costs a fixed latency (set-up, first loads, drain) once per wave of CTAs on an SM
-// plus a time per k block that shared-memory bandwidth and the MMA rate set; a split k adds the
+// kernel. A CTA costs a fixed latency (set-up, first loads, drain) plus a latency-bound time per
+// k block; two CTAs share an SM and overlap, so an SM's CTAs run in pairs; shared-memory
+// bandwidth bounds the k blocks an SM gets through whatever the overlap; a split k adds the
 // reduce launch. Narrow tiles win when the problem is small (more SMs share the latency-bound
-// work), wide ones when it is large (less operand re-reading).
+// work) or k is long (their loads run further ahead), wide ones when the product is large (less
+// operand re-reading).
 MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems, uint64_t group) {
     static const uint32_t widths[3] = {32, 64, 128};
     static const double per_block[3] = {MSX_TC_KB32, MSX_TC_KB64, MSX_TC_KB128};
+    static const double latency[3] = {MSX_TC_LATENCY32, MSX_TC_LATENCY64, MSX_TC_LATENCY128};
     const uint64_t kblocks = (k + BK - 1) / BK;
     MatmulTcPlan best = {};
     double best_cost = 0.0;
@@ -526,9 +540,10 @@ MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problem
             const uint64_t per = (kblocks + splits - 1) / splits;
             const uint64_t used = kblocks == 0 ? 1 : (kblocks + per - 1) / per;
             if (used != splits) continue;  // the same partition as a smaller count
-            // CTAs an SM runs one after another (two share it, overlapping their fixed parts).
             const uint64_t per_sm = (tiles * splits + 147) / 148;
-            double cost = MSX_TC_FIXED * static_cast<double>((per_sm + 1) / 2) + static_cast<double>(per_sm * per) * per_block[w];
+            const double paired = static_cast<double>((per_sm + 1) / 2) * (MSX_TC_FIXED + static_cast<double>(per) * latency[w]);
+            const double streamed = static_cast<double>(per_sm * per) * per_block[w];
+            double cost = paired > streamed ? paired : streamed;
             if (splits > 1) cost += MSX_TC_REDUCE_FIXED + static_cast<double>(m * n * (splits + 1)) * 4.0 / MSX_TC_REDUCE_BYTES_PER_CYCLE;
             if (best.bn == 0 || cost < best_cost) {
                 best_cost = cost;
@@ -561,7 +576,10 @@ void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t co
     // A float4 read starts at a multiple of 4 elements within a row, so rows must keep that phase.
     args.a_vec = args.lda % 4 == 0;
     args.b_vec = args.ldb % 4 == 0;
+    args.c_vec = args.ldc % 4 == 0;
+    args.c_padded = pitches.c != 0 && p.splits == 1;
     for (uint32_t g = 0; g < count; ++g) {
+        args.c_vec = args.c_vec && aligned16(p.splits > 1 ? products[g].workspace : products[g].c);
         args.a[g] = products[g].a;
         args.b[g] = products[g].b;
         args.c[g] = p.splits > 1 ? products[g].workspace : products[g].c;
@@ -609,6 +627,7 @@ void matmul_tc_batched(cudaStream_t s, const BatchedOperand& a, const BatchedOpe
     };
     args.a_vec = vec(a);
     args.b_vec = vec(b);
+    args.c_vec = vec(c);
     args.batch_inner = inner;
     args.a_outer = a.stride_outer; args.a_inner = a.stride_inner;
     args.b_outer = b.stride_outer; args.b_inner = b.stride_inner;
