@@ -31,8 +31,8 @@
 // half its file, so two CTAs share an SM and one drains while the other loads. Stage hand-off is
 // by mbarriers; every wait is bounded and, when it runs out, raises bit 1 of the status word,
 // makes every role leave its loop, frees the tensor memory and returns. A k range split across
-// CTAs (grid.z) writes partial tiles that `splitk_reduce_kernel` adds in ascending split order
-// (deterministic).
+// CTAs (grid.z, k blocks dealt out round-robin) writes partial tiles that `splitk_reduce_kernel`
+// or the step's finalize launch adds in ascending split order (deterministic).
 #include <cstdlib>
 
 #include "common.cuh"
@@ -43,7 +43,7 @@ namespace k {
 
 namespace {
 
-constexpr int BM = 64, BK = 32;
+constexpr int BK = 32;
 constexpr int LOADER_THREADS = 256, THREADS = LOADER_THREADS + 32;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives up
 
@@ -58,14 +58,25 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives
 #define MSX_TC_KB32 450.0
 #define MSX_TC_KB64 520.0
 #define MSX_TC_KB128 800.0
+// The 128 x 128 tile: one CTA per SM, two MMAs per k slice.
+#define MSX_TC_FIXED_WIDE 9000.0
+#define MSX_TC_KB_WIDE 1300.0
+// Operand bytes all SMs together pull through the L2 per SM cycle (measured: about 3.7 TB/s).
+#define MSX_TC_BYTES_PER_CYCLE 1900.0
 #define MSX_TC_REDUCE_FIXED 8000.0
 #define MSX_TC_REDUCE_BYTES_PER_CYCLE 3000.0
 #endif
 
-template <int BN> struct Config {
-    static constexpr int STAGES = BN == 128 ? 2 : (BN == 64 ? 3 : 4);  // shared-memory stages
-    static constexpr int SETS = BN == 128 ? 2 : (BN == 64 ? 3 : 4);    // register sets of loads in flight
-    static constexpr uint32_t A_BYTES = 2 * BM * BK * 4;  // hi rows 0-63, lo rows 64-127
+// BM = 64: the tile described above, two CTAs per SM. BM = 128 (with BN = 128): a 128 x 128 tile
+// for products large enough to be bound by operand traffic: the hi and lo halves of A are two
+// 128-row operands, two MMAs per k slice add their products with the stacked B into the same
+// accumulator, and the tile reads half the A and B bytes per output of the narrow one. One CTA
+// per SM then (three 64 KB stages).
+template <int BM, int BN> struct Config {
+    static constexpr int STAGES = BM == 128 ? 3 : (BN == 128 ? 2 : (BN == 64 ? 3 : 4));  // shared-memory stages
+    static constexpr int SETS = BN == 32 ? 4 : ((BN == 128 && BM == 64) ? 2 : 3);       // register sets of loads in flight
+    static constexpr int CTAS_PER_SM = BM == 128 ? 1 : 2;
+    static constexpr uint32_t A_BYTES = 2 * 128 * BK * 4 * BM / 128;  // BM 64: hi rows 0-63, lo rows 64-127; BM 128: hi tile, lo tile
     static constexpr uint32_t B_BYTES = 2 * BN * BK * 4;  // hi columns 0..BN-1, lo columns BN..2BN-1
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -213,9 +224,10 @@ __device__ __forceinline__ void loaders_barrier(uint32_t threads) {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
 
-template <int BN, bool A_T, bool B_T>
-__global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
-    using Cfg = Config<BN>;
+template <int BM, int BN, bool A_T, bool B_T>
+__global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_tc_kernel(TcArgs args) {
+    using Cfg = Config<BM, BN>;
+    constexpr bool WIDE = BM == 128;
     constexpr int STAGES = Cfg::STAGES, SETS = Cfg::SETS;
     extern __shared__ char smem_raw[];
     // Tiles need 1024-byte alignment for the swizzle pattern to line up with address bits.
@@ -233,53 +245,96 @@ __global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
     const bool batched = args.batch_inner != 0;
     const uint32_t z_outer = batched ? blockIdx.z / args.batch_inner : 0, z_inner = batched ? blockIdx.z % args.batch_inner : 0;
     const uint32_t product = batched ? 0 : blockIdx.z / args.splits, split = batched ? 0 : blockIdx.z % args.splits;
-    const uint32_t kb_begin = split * args.kblocks_per_split;
-    const uint32_t kb_end = min(kblocks_total, kb_begin + args.kblocks_per_split);
-    const uint32_t kblocks = kb_end > kb_begin ? kb_end - kb_begin : 0;
+    // A split k is dealt out block by block: split s takes k blocks s, s + splits, ... The CTAs of
+    // the splits of one tile run side by side, so at any time they read neighbouring 128-byte
+    // pieces of the same operand rows (one DRAM page) instead of pieces a whole k range apart.
+    const uint32_t stride = batched ? 1u : args.splits;
+    const uint32_t kblocks = kblocks_total > split ? (kblocks_total - split + stride - 1) / stride : 0;
 
     // ---- loaders, first part: where this thread's chunks sit, and the first loads. They are issued
     // before the barriers and the tensor memory are set up, so that the set-up hides under them.
     const float* __restrict__ a = args.a[product] + z_outer * args.a_outer + z_inner * args.a_inner;
     const float* __restrict__ b = args.b[product] + z_outer * args.b_outer + z_inner * args.b_inner;
     constexpr int A_CHUNKS = BM * BK / 4 / LOADER_THREADS, B_CHUNKS = BN * BK / 4 / LOADER_THREADS;
-    // Where this thread's chunks sit in a block does not depend on the block: the tile coordinates
-    // and the shared-memory offsets are computed once. The lo half of an operand lies half the
-    // operand's bytes after the hi half (64 rows, BN rows, or as many 32-element panels).
-    uint32_t a_row[A_CHUNKS], a_col[A_CHUNKS], aoff[A_CHUNKS], b_row[B_CHUNKS], b_col[B_CHUNKS], boff[B_CHUNKS];
+    // Where this thread's chunks sit in a block does not depend on the block: the shared-memory
+    // offsets, the address of each chunk in the first k block and whether all four of its elements
+    // lie inside the matrix rows are computed once. A k block that lies wholly inside k then costs
+    // one pointer addition and one 16-byte load per chunk: address arithmetic and bounds checks
+    // per block would be as many instructions again as the split itself. The lo half of an operand
+    // lies half the operand's bytes after the hi half (64 rows, BN rows, or as many 32-element
+    // panels).
+    uint32_t aoff[A_CHUNKS], boff[B_CHUNKS];
+    const float* a_at[A_CHUNKS];
+    const float* b_at[B_CHUNKS];
+    bool a_whole[A_CHUNKS], b_whole[B_CHUNKS];
+    constexpr uint32_t a_per_k_row = BM / 4, b_per_k_row = BN / 4;  // 16-byte chunks of one k row of an MN-major tile
+    auto a_place = [&](int i, uint32_t* row, uint32_t* col) {
+        const uint32_t q = tid + i * LOADER_THREADS;
+        if (A_T) { *row = q / a_per_k_row; *col = (q % a_per_k_row) * 4; }  // (k, m)
+        else     { *row = q >> 3; *col = (q & 7u) * 4; }                    // (m, k)
+    };
+    auto b_place = [&](int i, uint32_t* row, uint32_t* col) {
+        const uint32_t q = tid + i * LOADER_THREADS;
+        if (B_T) { *row = q >> 3; *col = (q & 7u) * 4; }                    // (n, k)
+        else     { *row = q / b_per_k_row; *col = (q % b_per_k_row) * 4; }  // (k, n)
+    };
+    const uint32_t first_k = split * BK;
 #pragma unroll
     for (int i = 0; i < A_CHUNKS; ++i) {
-        uint32_t q = tid + i * LOADER_THREADS;
-        if (A_T) { a_row[i] = q >> 4; a_col[i] = (q & 15u) * 4; aoff[i] = mn_major_offset(q >> 4, q & 15u); }      // (k, m)
-        else     { a_row[i] = q >> 3; a_col[i] = (q & 7u) * 4;  aoff[i] = k_major_offset(q >> 3, q & 7u); }        // (m, k)
+        uint32_t row, col;
+        a_place(i, &row, &col);
+        aoff[i] = A_T ? mn_major_offset(row, col / 4) : k_major_offset(row, col / 4);
+        a_at[i] = A_T ? a + static_cast<uint64_t>(first_k + row) * args.lda + m0 + col
+                      : a + static_cast<uint64_t>(m0 + row) * args.lda + first_k + col;
+        a_whole[i] = args.a_vec && (A_T ? m0 + col + 4 <= args.m : m0 + row < args.m);
     }
 #pragma unroll
     for (int i = 0; i < B_CHUNKS; ++i) {
-        uint32_t q = tid + i * LOADER_THREADS;
-        if (B_T) { b_row[i] = q >> 3; b_col[i] = (q & 7u) * 4; boff[i] = k_major_offset(q >> 3, q & 7u); }         // (n, k)
-        else     { b_row[i] = q / (BN / 4); b_col[i] = (q % (BN / 4)) * 4; boff[i] = mn_major_offset(q / (BN / 4), q % (BN / 4)); }  // (k, n)
+        uint32_t row, col;
+        b_place(i, &row, &col);
+        boff[i] = B_T ? k_major_offset(row, col / 4) : mn_major_offset(row, col / 4);
+        b_at[i] = B_T ? b + static_cast<uint64_t>(n0 + row) * args.ldb + first_k + col
+                      : b + static_cast<uint64_t>(first_k + row) * args.ldb + n0 + col;
+        b_whole[i] = args.b_vec && (B_T ? n0 + row < args.n : n0 + col + 4 <= args.n);
     }
+    // Elements from one k block of this CTA to its next.
+    const uint64_t a_step = static_cast<uint64_t>(BK) * stride * (A_T ? args.lda : 1u);
+    const uint64_t b_step = static_cast<uint64_t>(BK) * stride * (B_T ? 1u : args.ldb);
     auto fetch = [&](uint32_t kb, float4 (&av)[A_CHUNKS], float4 (&bv)[B_CHUNKS]) {
-        const uint32_t k0 = (kb_begin + kb) * BK;
+        const uint32_t k0 = (kb * stride + split) * BK;
+        const bool inside = k0 + BK <= args.k;
 #pragma unroll
         for (int i = 0; i < A_CHUNKS; ++i) {
+            if (inside && a_whole[i]) {
+                av[i] = load4(a_at[i] + kb * a_step, 0, 4, true);
+                continue;
+            }
+            uint32_t row, col;
+            a_place(i, &row, &col);
             if (A_T) {  // stored [k, m]: 4 consecutive m of one k row
-                uint32_t gk = k0 + a_row[i], gm = m0 + a_col[i];
+                uint32_t gk = k0 + row, gm = m0 + col;
                 uint32_t valid = gk < args.k ? in_range(gm, args.m) : 0u;
                 av[i] = load4(a, static_cast<uint64_t>(gk) * args.lda + gm, valid, args.a_vec);
             } else {    // stored [m, k]: 4 consecutive k of one row
-                uint32_t gm = m0 + a_row[i], gk = k0 + a_col[i];
+                uint32_t gm = m0 + row, gk = k0 + col;
                 uint32_t valid = gm < args.m ? in_range(gk, args.k) : 0u;
                 av[i] = load4(a, static_cast<uint64_t>(gm) * args.lda + gk, valid, args.a_vec);
             }
         }
 #pragma unroll
         for (int i = 0; i < B_CHUNKS; ++i) {
+            if (inside && b_whole[i]) {
+                bv[i] = load4(b_at[i] + kb * b_step, 0, 4, true);
+                continue;
+            }
+            uint32_t row, col;
+            b_place(i, &row, &col);
             if (B_T) {  // stored [n, k]
-                uint32_t gn = n0 + b_row[i], gk = k0 + b_col[i];
+                uint32_t gn = n0 + row, gk = k0 + col;
                 uint32_t valid = gn < args.n ? in_range(gk, args.k) : 0u;
                 bv[i] = load4(b, static_cast<uint64_t>(gn) * args.ldb + gk, valid, args.b_vec);
             } else {    // stored [k, n]
-                uint32_t gk = k0 + b_row[i], gn = n0 + b_col[i];
+                uint32_t gk = k0 + row, gn = n0 + col;
                 uint32_t valid = gk < args.k ? in_range(gn, args.n) : 0u;
                 bv[i] = load4(b, static_cast<uint64_t>(gk) * args.ldb + gn, valid, args.b_vec);
             }
@@ -357,9 +412,11 @@ __global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
         constexpr uint32_t PITCH = BN + 4;  // 16-byte phases of consecutive rows fall on distinct banks
         const bool drains = BN != 32 || half == 0;  // a 32-column tile is one block per lane quarter
         float* tile_hi = reinterpret_cast<float*>(tiles);
-        float* tile_lo = tile_hi + BM * PITCH;
+        float* tile_lo = tile_hi + 64 * PITCH;  // BM 64 only: the sums of the A_lo rows
         if (drains) {
-            float* to_row = (quarter < 2 ? tile_hi : tile_lo) + ((quarter & 1u) * 32u + lane) * PITCH;
+            // BM 128: lane quarter q holds tile rows 32 q ..; BM 64: quarters 0-1 the A_hi rows, 2-3 the A_lo rows.
+            float* to_row = WIDE ? tile_hi + (quarter * 32u + lane) * PITCH
+                                 : (quarter < 2 ? tile_hi : tile_lo) + ((quarter & 1u) * 32u + lane) * PITCH;
 #pragma unroll
             for (int part = 0; part < PARTS; ++part) {
                 const uint32_t col = BN == 128 ? half * 64u + part * 32u : (BN == 64 ? half * 32u : 0u);
@@ -396,7 +453,7 @@ __global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
             const uint32_t gm = m0 + r;
             if (gm >= args.m || gn >= args.n) continue;
             const float4 h = *reinterpret_cast<const float4*>(tile_hi + r * PITCH + c4);
-            const float4 l = *reinterpret_cast<const float4*>(tile_lo + r * PITCH + c4);
+            const float4 l = WIDE ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(tile_lo + r * PITCH + c4);
             // `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
             float v[4] = {(h.x + l.x) + 0.0f, (h.y + l.y) + 0.0f, (h.z + l.z) + 0.0f, (h.w + l.w) + 0.0f};
             if (bias_row) {
@@ -451,6 +508,7 @@ __global__ void __launch_bounds__(THREADS, 2) matmul_tc_kernel(TcArgs args) {
                     const uint32_t a_step = (A_T ? ks * 1024u : ks * 32u) >> 4;
                     const uint32_t b_step = (B_T ? ks * 32u : ks * 1024u) >> 4;
                     mma_tf32(tmem_base, desc(a_high, a16 + a_step), desc(b_high, b16 + b_step), idesc, (kb | ks) != 0u);
+                    if (WIDE) mma_tf32(tmem_base, desc(a_high, a16 + (Cfg::A_BYTES >> 5) + a_step), desc(b_high, b16 + b_step), idesc, 1u);
                 }
                 mma_commit(smem_u32(&bars[STAGES + stage]));                   // frees the stage when they finish
                 if (kb < 4) TRACE(8 + kb);
@@ -479,30 +537,31 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, float* __rest
     }
 }
 
-template <int BN, bool A_T, bool B_T> void launch(cudaStream_t s, const TcArgs& args, dim3 grid) {
-    auto kernel = matmul_tc_kernel<BN, A_T, B_T>;
+template <int BM, int BN, bool A_T, bool B_T> void launch(cudaStream_t s, const TcArgs& args, dim3 grid) {
+    auto kernel = matmul_tc_kernel<BM, BN, A_T, B_T>;
     static int configured_device = -1;  // the attribute is per device: set it when the device changes
     int device = 0;
     check(cudaGetDevice(&device), "cudaGetDevice");
     if (device != configured_device) {
-        check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Config<BN>::TOTAL)), "matmul_tc shared memory");
+        check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Config<BM, BN>::TOTAL)), "matmul_tc shared memory");
         configured_device = device;
     }
-    kernel<<<grid, THREADS, Config<BN>::TOTAL, s>>>(args);
+    kernel<<<grid, THREADS, Config<BM, BN>::TOTAL, s>>>(args);
     check_launch("matmul_tc");
 }
 
-template <int BN> void launch_forms(cudaStream_t s, const TcArgs& args, dim3 grid, bool a_t, bool b_t) {
-    if (a_t && b_t) launch<BN, true, true>(s, args, grid);
-    else if (a_t) launch<BN, true, false>(s, args, grid);
-    else if (b_t) launch<BN, false, true>(s, args, grid);
-    else launch<BN, false, false>(s, args, grid);
+template <int BM, int BN> void launch_forms(cudaStream_t s, const TcArgs& args, dim3 grid, bool a_t, bool b_t) {
+    if (a_t && b_t) launch<BM, BN, true, true>(s, args, grid);
+    else if (a_t) launch<BM, BN, true, false>(s, args, grid);
+    else if (b_t) launch<BM, BN, false, true>(s, args, grid);
+    else launch<BM, BN, false, false>(s, args, grid);
 }
 
-void launch_width(cudaStream_t s, const TcArgs& args, dim3 grid, uint32_t bn, bool a_t, bool b_t) {
-    if (bn == 32) launch_forms<32>(s, args, grid, a_t, b_t);
-    else if (bn == 64) launch_forms<64>(s, args, grid, a_t, b_t);
-    else launch_forms<128>(s, args, grid, a_t, b_t);
+void launch_tile(cudaStream_t s, const TcArgs& args, dim3 grid, uint32_t bm, uint32_t bn, bool a_t, bool b_t) {
+    if (bm == 128) launch_forms<128, 128>(s, args, grid, a_t, b_t);
+    else if (bn == 32) launch_forms<64, 32>(s, args, grid, a_t, b_t);
+    else if (bn == 64) launch_forms<64, 64>(s, args, grid, a_t, b_t);
+    else launch_forms<64, 128>(s, args, grid, a_t, b_t);
 }
 
 #ifdef MSX_TC_TRACE
@@ -523,30 +582,45 @@ bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0;
 // work) or k is long (their loads run further ahead), wide ones when the product is large (less
 // operand re-reading).
 MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems, uint64_t group) {
-    static const uint32_t widths[3] = {32, 64, 128};
-    static const double per_block[3] = {MSX_TC_KB32, MSX_TC_KB64, MSX_TC_KB128};
-    static const double latency[3] = {MSX_TC_LATENCY32, MSX_TC_LATENCY64, MSX_TC_LATENCY128};
+    // Candidates: 64-row tiles of width 32, 64, 128 (two CTAs per SM) and the 128 x 128 tile.
+    static const uint32_t rows[4] = {64, 64, 64, 128}, widths[4] = {32, 64, 128, 128};
+    static const double per_block[4] = {MSX_TC_KB32, MSX_TC_KB64, MSX_TC_KB128, MSX_TC_KB_WIDE};
+    static const double latency[4] = {MSX_TC_LATENCY32, MSX_TC_LATENCY64, MSX_TC_LATENCY128, MSX_TC_KB_WIDE};
     const uint64_t kblocks = (k + BK - 1) / BK;
     MatmulTcPlan best = {};
     double best_cost = 0.0;
-    for (int w = 0; w < 3; ++w) {
+    for (int w = 0; w < 4; ++w) {
 #ifdef MSX_TC_TRACE
         if (const char* forced = std::getenv("MSX_TC_FORCE_BN"))
             if (static_cast<uint32_t>(std::atoi(forced)) != widths[w]) continue;
+        if (const char* forced = std::getenv("MSX_TC_FORCE_BM"))
+            if (static_cast<uint32_t>(std::atoi(forced)) != rows[w]) continue;
 #endif
-        const uint64_t tiles = ((m + BM - 1) / BM) * ((n + widths[w] - 1) / widths[w]) * problems * group;
+        if (rows[w] == 128 && problems > 1) continue;  // batched products stay on the narrow tiles
+        const uint64_t m_tiles = (m + rows[w] - 1) / rows[w], n_tiles = (n + widths[w] - 1) / widths[w];
+        const uint64_t tiles = m_tiles * n_tiles * problems * group;
         const uint64_t most = problems > 1 ? 1 : (kblocks / 2 > 0 ? kblocks / 2 : 1);
         for (uint64_t splits = 1; splits <= most && splits <= 64; ++splits) {
             const uint64_t per = (kblocks + splits - 1) / splits;
             const uint64_t used = kblocks == 0 ? 1 : (kblocks + per - 1) / per;
             if (used != splits) continue;  // the same partition as a smaller count
             const uint64_t per_sm = (tiles * splits + 147) / 148;
-            const double paired = static_cast<double>((per_sm + 1) / 2) * (MSX_TC_FIXED + static_cast<double>(per) * latency[w]);
+            const uint64_t together = rows[w] == 128 ? 1 : 2;  // CTAs that share an SM and overlap
+            const double fixed = rows[w] == 128 ? MSX_TC_FIXED_WIDE : MSX_TC_FIXED;
+            const double paired = static_cast<double>((per_sm + together - 1) / together) * (fixed + static_cast<double>(per) * latency[w]);
             const double streamed = static_cast<double>(per_sm * per) * per_block[w];
+            // Every tile reads its rows of A and columns of B over k; what the SMs can pull
+            // through the L2 in a cycle bounds a product with many tiles.
+            const double bytes = 4.0 * static_cast<double>(problems * group) *
+                                 (static_cast<double>(m * k * n_tiles) + static_cast<double>(n * k * m_tiles) +
+                                  static_cast<double>(m * n * (splits > 1 ? splits : 1)));
+            const double traffic = bytes / MSX_TC_BYTES_PER_CYCLE;
             double cost = paired > streamed ? paired : streamed;
+            if (traffic > cost) cost = traffic;
             if (splits > 1) cost += MSX_TC_REDUCE_FIXED + static_cast<double>(m * n * (splits + 1)) * 4.0 / MSX_TC_REDUCE_BYTES_PER_CYCLE;
             if (best.bn == 0 || cost < best_cost) {
                 best_cost = cost;
+                best.bm = rows[w];
                 best.bn = widths[w];
                 best.splits = static_cast<uint32_t>(splits);
                 best.kblocks_per_split = static_cast<uint32_t>(per == 0 ? 1 : per);
@@ -588,8 +662,8 @@ void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t co
         args.b_vec = args.b_vec && aligned16(products[g].b);
     }
     args.status = status;
-    dim3 grid(static_cast<uint32_t>((n + p.bn - 1) / p.bn), static_cast<uint32_t>((m + BM - 1) / BM), p.splits * count);
-    launch_width(s, args, grid, p.bn, a_t, b_t);
+    dim3 grid(static_cast<uint32_t>((n + p.bn - 1) / p.bn), static_cast<uint32_t>((m + p.bm - 1) / p.bm), p.splits * count);
+    launch_tile(s, args, grid, p.bm, p.bn, a_t, b_t);
     if (p.splits > 1 && !leave_partials) {
         uint64_t total = m * n;
         uint64_t blocks = (total + 255) / 256;
@@ -633,9 +707,9 @@ void matmul_tc_batched(cudaStream_t s, const BatchedOperand& a, const BatchedOpe
     args.b_outer = b.stride_outer; args.b_inner = b.stride_inner;
     args.c_outer = c.stride_outer; args.c_inner = c.stride_inner;
     args.status = status;
-    uint32_t bn = matmul_tc_plan(m, n, k, static_cast<uint64_t>(outer) * inner).bn;
-    dim3 grid(static_cast<uint32_t>((n + bn - 1) / bn), static_cast<uint32_t>((m + BM - 1) / BM), outer * inner);
-    launch_width(s, args, grid, bn, a.transposed, b.transposed);
+    const MatmulTcPlan p = matmul_tc_plan(m, n, k, static_cast<uint64_t>(outer) * inner);
+    dim3 grid(static_cast<uint32_t>((n + p.bn - 1) / p.bn), static_cast<uint32_t>((m + p.bm - 1) / p.bm), outer * inner);
+    launch_tile(s, args, grid, p.bm, p.bn, a.transposed, b.transposed);
 }
 
 }  // namespace k

@@ -147,7 +147,7 @@ void matmul(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, 
 // `leave_partials` a split k stops at the partial tiles, workspace[split][m][n], for
 // finalize_sums (no bias then).
 struct MatmulTcPlan {
-    uint32_t bn, splits, kblocks_per_split;
+    uint32_t bm, bn, splits, kblocks_per_split;  // tile rows (64 or 128) and width, k split
     uint64_t workspace_floats;
 };
 // `problems` > 1: that many independent batched products in one launch (k is then not split);
