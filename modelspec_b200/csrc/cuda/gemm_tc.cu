@@ -53,16 +53,18 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives
 // Per k block of one CTA, bounded by how far ahead its loads run (SETS - 1 blocks) ...
 #define MSX_TC_LATENCY32 700.0
 #define MSX_TC_LATENCY64 950.0
-#define MSX_TC_LATENCY128 2000.0
-// ... and per k block of an SM, bounded by shared-memory bandwidth, however many CTAs share it.
-#define MSX_TC_KB32 450.0
-#define MSX_TC_KB64 520.0
-#define MSX_TC_KB128 800.0
-// The 128 x 128 tile: one CTA per SM, two MMAs per k slice.
+#define MSX_TC_LATENCY128 1900.0
+// ... and per k block of an SM, however many CTAs share it, bounded by the tensor pipe: a tf32
+// MMA of 128 x 256 x 8 was measured at about 275 cycles (half that for 128 wide, a floor of
+// about 100 below), four of them per k block.
+#define MSX_TC_KB32 400.0
+#define MSX_TC_KB64 560.0
+#define MSX_TC_KB128 1100.0
+// The 128 x 128 tile: one CTA per SM, eight MMAs of 128 x 256 x 8 per k block.
 #define MSX_TC_FIXED_WIDE 9000.0
-#define MSX_TC_KB_WIDE 1300.0
-// Operand bytes all SMs together pull through the L2 per SM cycle (measured: about 3.7 TB/s).
-#define MSX_TC_BYTES_PER_CYCLE 1900.0
+#define MSX_TC_KB_WIDE 2200.0
+// Operand bytes all SMs together pull through the L2 per SM cycle.
+#define MSX_TC_BYTES_PER_CYCLE 3800.0
 #define MSX_TC_REDUCE_FIXED 8000.0
 #define MSX_TC_REDUCE_BYTES_PER_CYCLE 3000.0
 #endif

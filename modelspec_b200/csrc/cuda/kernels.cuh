@@ -52,6 +52,19 @@ uint64_t sum_rows_counters(uint64_t h);
 void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out,
               uint32_t* counters = nullptr, uint64_t ld = 0);
 
+// The first stages of many column sums (the bias gradients of a step) in one launch: job j sums
+// the rows of g ([rows, width], pitch ld) in sum_rows_chunks(rows) chunks into
+// partial[chunk][width], as sum_rows with a null `out` does; finalize_sums adds the chunks.
+// `first_block` = the blocks (row_sum_job_blocks each) of the jobs before this one.
+struct RowSumJob {
+    const float* g;
+    float* partial;
+    uint32_t rows, width, ld, rows_per_chunk, first_block, reserved;
+};
+RowSumJob row_sum_job(const float* g, float* partial, uint64_t rows, uint64_t h, uint64_t ld, uint32_t first_block);
+uint32_t row_sum_job_blocks(uint64_t rows, uint64_t h);
+void sum_rows_batched(cudaStream_t s, const RowSumJob* d_jobs, uint32_t jobs, uint32_t blocks);
+
 // Deferred second stages. A kernel that leaves `chunks` partial results of `width` floats each,
 // stored [chunk][width], is finished by one launch over all such jobs of a step: up to 64 chunks
 // are added in ascending order; beyond that thread y of 8 adds chunks y, y + 8, ... in ascending

@@ -94,6 +94,43 @@ __global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint
     }
 }
 
+// The first stage of many column sums in one launch: block b works on the job whose block range
+// holds it, on one 32-column block and one chunk of rows, exactly as sum_rows_stage1 does.
+__global__ void sum_rows_batched_kernel(const RowSumJob* __restrict__ jobs, uint32_t count) {
+    __shared__ float shared[8][32];
+    __shared__ uint32_t which;
+    if (threadIdx.x == 0 && threadIdx.y == 0) {
+        uint32_t j = 0;
+        while (j + 1 < count && jobs[j + 1].first_block <= blockIdx.x) ++j;
+        which = j;
+    }
+    __syncthreads();
+    const RowSumJob job = jobs[which];
+    const uint32_t local = blockIdx.x - job.first_block, column_blocks = (job.width + 31) / 32;
+    const uint32_t c = (local % column_blocks) * 32 + threadIdx.x, chunk = local / column_blocks;
+    const uint32_t r0 = chunk * job.rows_per_chunk, r1 = min(job.rows, r0 + job.rows_per_chunk);
+    float acc = 0.0f;
+    if (c < job.width) {
+        uint32_t r = r0 + threadIdx.y;
+        for (; r + 56 < r1; r += 64) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldg(job.g + static_cast<uint64_t>(r + 8 * j) * job.ld + c);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc += v[j];
+        }
+        for (; r < r1; r += 8) acc += __ldg(job.g + static_cast<uint64_t>(r) * job.ld + c);
+    }
+    shared[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < job.width) {
+        float total = shared[0][threadIdx.x];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) total += shared[w][threadIdx.x];
+        job.partial[static_cast<uint64_t>(chunk) * job.width + c] = total;
+    }
+}
+
 __global__ void sum_rows_stage2(const float* __restrict__ partial, uint32_t chunks, uint32_t h,
                                 float* __restrict__ out) {
     uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -142,6 +179,26 @@ __global__ void finalize_sums_kernel(const SumJob* __restrict__ jobs, uint32_t c
 }
 
 }  // namespace
+
+RowSumJob row_sum_job(const float* g, float* partial, uint64_t rows, uint64_t h, uint64_t ld, uint32_t first_block) {
+    RowSumJob job = {};
+    job.g = g;
+    job.partial = partial;
+    job.rows = static_cast<uint32_t>(rows);
+    job.width = static_cast<uint32_t>(h);
+    job.ld = static_cast<uint32_t>(ld ? ld : h);
+    const uint32_t chunks = sum_rows_chunks(rows);
+    job.rows_per_chunk = static_cast<uint32_t>((rows + chunks - 1) / chunks);
+    job.first_block = first_block;
+    return job;
+}
+uint32_t row_sum_job_blocks(uint64_t rows, uint64_t h) { return static_cast<uint32_t>((h + 31) / 32) * sum_rows_chunks(rows); }
+
+void sum_rows_batched(cudaStream_t s, const RowSumJob* d_jobs, uint32_t jobs, uint32_t blocks) {
+    if (jobs == 0 || blocks == 0) return;
+    sum_rows_batched_kernel<<<blocks, dim3(32, 8), 0, s>>>(d_jobs, jobs);
+    check_launch("sum_rows_batched");
+}
 
 void finalize_sums(cudaStream_t s, const SumJob* d_jobs, uint32_t jobs, uint32_t blocks) {
     if (jobs == 0 || blocks == 0) return;

@@ -147,6 +147,7 @@ struct msx_plan {
     uint32_t* counter(uint32_t index) const { return d_counters + index; }
     void* d_update_tables = nullptr;
     void* d_sum_jobs = nullptr;  // k::SumJob table of the deferred second stages
+    void* d_row_sum_jobs = nullptr;  // k::RowSumJob table of the column sums that share one launch
 
     int loss_pos = -1;
     uint64_t steps = 0;
@@ -235,12 +236,36 @@ struct Scheduler {
         uint32_t out;          // node position of the result
     };
     std::vector<Deferred> deferred;
+    // Column sums whose result only the optimizer reads wait for one launch that does the first
+    // stage of all of them (a bias gradient is a 3 us kernel of its own otherwise); the matrix
+    // they sum stays alive until then, so only matrices of a few MB wait.
+    struct DeferredRows {
+        uint32_t g, partial;
+        uint64_t rows, width, ld;
+    };
+    std::vector<DeferredRows> deferred_rows;
+    static constexpr uint64_t kDeferredRowsBytes = 16ull << 20;
     bool deferrable(uint32_t at) const {
         for (uint32_t u : users[at])
             if (node(u).tag != msx::Tag::Optimizer || !handled[u]) return false;
         return true;
     }
     void emit_finalize() {
+        if (!deferred_rows.empty()) {
+            std::vector<uint32_t> reads, writes;
+            uint32_t blocks = 0;
+            for (const DeferredRows& d : deferred_rows) {
+                reads.push_back(d.g);
+                writes.push_back(d.partial);
+                blocks += k::row_sum_job_blocks(d.rows, d.width);
+            }
+            Node pseudo;
+            pseudo.id = node(deferred_rows[0].g).id;
+            msx_plan* plan = P;
+            const uint32_t jobs = static_cast<uint32_t>(deferred_rows.size());
+            emit("sum_rows_batched", pseudo, reads, writes,
+                 [=](cudaStream_t s) { k::sum_rows_batched(s, static_cast<const k::RowSumJob*>(plan->d_row_sum_jobs), jobs, blocks); });
+        }
         if (deferred.empty()) return;
         std::vector<uint32_t> reads, writes;
         uint32_t blocks = 0;
@@ -749,6 +774,14 @@ struct Scheduler {
             case Op::SumRows: {
                 uint32_t g = in[0];
                 uint64_t r = rows_of(g), h = cols_of(g), ld = pitch_of(g);
+                if (deferrable(at) && r * std::max<uint64_t>(ld, h) * 4 <= kDeferredRowsBytes) {
+                    uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4);
+                    uint32_t source = g;
+                    while (P->slots[source].kind == Slot::View) source = P->slots[source].index;
+                    deferred_rows.push_back({source, tmp, r, h, ld});
+                    deferred.push_back({tmp, 0, k::sum_rows_chunks(r), h, at});
+                    break;
+                }
                 if (deferrable(at)) {
                     uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4);
                     emit("sum_rows", nd, in, {tmp}, [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), nullptr, nullptr, ld); });
@@ -1395,6 +1428,17 @@ void allocate(msx_plan* P, const Scheduler& sched) {
     cuda_ok(cudaMemset(P->d_counters, 0, counter_bytes), "cudaMemset(counters)");
     cuda_ok(cudaEventCreate(&P->clock_start), "cudaEventCreate");
     cuda_ok(cudaEventCreate(&P->clock_stop), "cudaEventCreate");
+    if (!sched.deferred_rows.empty()) {
+        std::vector<k::RowSumJob> jobs;
+        uint32_t first_block = 0;
+        for (const Scheduler::DeferredRows& d : sched.deferred_rows) {
+            jobs.push_back(k::row_sum_job(static_cast<const float*>(P->ptr(d.g)), static_cast<float*>(P->ptr(d.partial)), d.rows, d.width,
+                                          d.ld, first_block));
+            first_block += k::row_sum_job_blocks(d.rows, d.width);
+        }
+        cuda_ok(cudaMalloc(&P->d_row_sum_jobs, jobs.size() * sizeof(k::RowSumJob)), "cudaMalloc(row sum jobs)");
+        cuda_ok(cudaMemcpy(P->d_row_sum_jobs, jobs.data(), jobs.size() * sizeof(k::RowSumJob), cudaMemcpyHostToDevice), "cudaMemcpy(row sum jobs)");
+    }
     if (!sched.deferred.empty()) {
         std::vector<k::SumJob> jobs;
         uint32_t first_block = 0;
@@ -1456,6 +1500,7 @@ void release(msx_plan* P) {
     cudaFree(P->d_counters);
     cudaFree(P->d_update_tables);
     cudaFree(P->d_sum_jobs);
+    cudaFree(P->d_row_sum_jobs);
     for (int s = 0; s < kStagingSlots; ++s) {
         if (P->pinned[s]) cudaFreeHost(P->pinned[s]);
         if (P->slot_done[s]) cudaEventDestroy(P->slot_done[s]);
