@@ -99,10 +99,10 @@ void attention_tc_forward(cudaStream_t s, const float* q, const float* k, const 
 }
 
 void attention_tc_backward(cudaStream_t s, const float* q, const float* k, const float* v, const float* mask, const float* g,
-                           float* dq, float* dk, float* dv, float* p, float* dp, AttentionShape sh, uint32_t* status) {
+                           float* dq, float* dk, float* dv, float* p, float* dp, AttentionShape sh, uint32_t* status, bool p_ready) {
     if (sh.batch == 0 || sh.q_len == 0) return;
     Heads hd = heads_of(sh);
-    probabilities(s, q, k, mask, p, hd, status);
+    if (!p_ready) probabilities(s, q, k, mask, p, hd, status);
     // dV[j, c] = sum_i P[i, j] g[i, c]: A is P stored [k, m].
     if (dv) matmul_tc_batched(s, transposed(hd.scores(p)), hd.q(g), hd.kv(dv), hd.s, hd.d, hd.l, hd.b, hd.a, status);
     if (!dq && !dk) return;

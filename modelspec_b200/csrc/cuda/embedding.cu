@@ -105,7 +105,7 @@ __device__ __forceinline__ uint32_t warp_lower_bound(const int32_t* __restrict__
     while (lo < hi) {
         const uint32_t step = (hi - lo + 31) / 32;
         const uint32_t probe = lo + lane * step;
-        const bool below = probe < hi && __ldg(sorted_id + probe) < row;
+        const bool below = probe < hi && sorted_id[probe] < row;
         const uint32_t count = __popc(__ballot_sync(0xffffffffu, below));
         if (count == 0) return lo;
         const uint32_t next_hi = min(hi, lo + count * step);
@@ -119,11 +119,11 @@ __device__ __forceinline__ uint32_t warp_lower_bound(const int32_t* __restrict__
 // + ...) over the row's occurrences in ascending n. The additions stay in order. A row read up to
 // 32 times is summed by its warp, the loads of 8 occurrences issued together. A hotter row (the
 // mask token, a padding position: hundreds of occurrences) would be one warp waiting on memory
-// hundreds of times: the block takes it together instead, all 256 threads streaming 64
-// occurrences at a time into shared memory while one thread per column adds the previous 64 in
+// hundreds of times: the block takes it together instead, all 256 threads streaming 32
+// occurrences at a time into shared memory while one thread per column adds the previous 32 in
 // order. A row nobody read gets `base` (or zero). VEC = 4 reads and writes 16 bytes per lane and
 // needs h % 4 == 0 and 16-byte aligned g, base and out.
-constexpr uint32_t kHotRow = 32, kHotChunk = 64;
+constexpr uint32_t kHotRow = 32, kHotChunk = 32, kCachedIds = 4096;
 template <int VEC>
 __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ g, const int32_t* __restrict__ sorted_id,
                                                       const int32_t* __restrict__ sorted_n, uint32_t n,
@@ -132,7 +132,16 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
     constexpr uint32_t span = VEC * 32;
     constexpr int LOADS = kHotChunk * span / VEC / 256;
     __shared__ float stage[kHotChunk][span];
+    __shared__ int32_t cached_ids[kCachedIds];
     __shared__ uint32_t hot_item[8], hot_at[8], hot_count[8], hot_rows;
+    // Every row's warp searches the sorted ids: up to 4096 of them are copied into shared memory
+    // once per block (a block walks many rows), so that a search round is a shared-memory read.
+    const int32_t* ids = sorted_id;
+    if (n <= kCachedIds) {
+        for (uint32_t j = threadIdx.x; j < n; j += blockDim.x) cached_ids[j] = sorted_id[j];
+        ids = cached_ids;
+        __syncthreads();
+    }
     const uint32_t groups = (h + span - 1) / span;
     const uint64_t items = static_cast<uint64_t>(rows) * groups;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -143,10 +152,10 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
         if (item < items) {
             const uint32_t row = static_cast<uint32_t>(item / groups), col = static_cast<uint32_t>(item % groups) * span + lane * VEC;
             const bool in = col < h;
-            uint32_t at = n ? warp_lower_bound(sorted_id, n, static_cast<int32_t>(row), lane) : 0u;
+            uint32_t at = n ? warp_lower_bound(ids, n, static_cast<int32_t>(row), lane) : 0u;
             uint32_t count = 0;
-            if (at < n && __ldg(sorted_id + at) == static_cast<int32_t>(row))
-                count = warp_lower_bound(sorted_id, n, static_cast<int32_t>(row) + 1, lane) - at;
+            if (at < n && ids[at] == static_cast<int32_t>(row))
+                count = warp_lower_bound(ids, n, static_cast<int32_t>(row) + 1, lane) - at;
             if (count > kHotRow) {
                 if (lane == 0) {
                     uint32_t slot = atomicAdd(&hot_rows, 1u);
@@ -278,7 +287,7 @@ void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* o
     const bool vec = h % 4 == 0 && aligned(g) && aligned(out) && aligned(base);
     const uint64_t span = vec ? 128 : 32;
     const uint64_t blocks = (rows * ((h + span - 1) / span) + 7) / 8;
-    const uint32_t grid = static_cast<uint32_t>(blocks > 148 * 32 ? 148 * 32 : blocks);
+    const uint32_t grid = static_cast<uint32_t>(blocks > 148 * 6 ? 148 * 6 : blocks);
     if (vec) scatter_kernel<4><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
     else scatter_kernel<1><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
     check_launch("embedding_grad");

@@ -223,10 +223,11 @@ void attention_grad_kv(cudaStream_t s, const float* q, const float* k, const flo
 uint64_t attention_tc_scratch_floats(AttentionShape shape);
 void attention_tc_forward(cudaStream_t s, const float* q, const float* k, const float* v, const float* mask,
                           float* out, float* p, AttentionShape shape, uint32_t* status);
-// dq, dk and dv may each be null.
+// dq, dk and dv may each be null. `p_ready`: `p` still holds what attention_tc_forward left there
+// for the same operands (the probabilities are then not computed again); it is only read.
 void attention_tc_backward(cudaStream_t s, const float* q, const float* k, const float* v, const float* mask,
                            const float* g, float* dq, float* dk, float* dv, float* p, float* dp,
-                           AttentionShape shape, uint32_t* status);
+                           AttentionShape shape, uint32_t* status, bool p_ready = false);
 
 // ---- optimizer (optimizer.cu) -----------------------------------------------------------------
 struct UpdateTensor {

@@ -94,6 +94,46 @@ __global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint
     }
 }
 
+// The same with four columns per lane (16-byte loads) for matrices whose rows start on 16-byte
+// boundaries: a block covers 128 columns. Only the chunk sums are written (the second stage is
+// the step's finalize launch or sum_rows_stage2).
+__global__ void sum_rows_stage1_wide(const float* __restrict__ g, uint32_t rows, uint32_t h, uint32_t ld, uint32_t rows_per_chunk,
+                                     float* __restrict__ partial) {
+    __shared__ float4 shared[8][32];
+    const uint32_t c = (blockIdx.x * 32 + threadIdx.x) * 4;
+    const uint32_t r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < h) {  // the pitch covers the whole float4; columns past h hold padding and are not written below
+        uint32_t r = r0 + threadIdx.y;
+        for (; r + 24 < r1; r += 32) {
+            float4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(g + static_cast<uint64_t>(r + 8 * j) * ld + c));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+        }
+        for (; r < r1; r += 8) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(g + static_cast<uint64_t>(r) * ld + c));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    }
+    shared[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < h) {
+        float4 total = shared[0][threadIdx.x];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) {
+            const float4 v = shared[w][threadIdx.x];
+            total.x += v.x; total.y += v.y; total.z += v.z; total.w += v.w;
+        }
+        float* to = partial + static_cast<uint64_t>(blockIdx.y) * h + c;
+        to[0] = total.x;
+        if (c + 1 < h) to[1] = total.y;
+        if (c + 2 < h) to[2] = total.z;
+        if (c + 3 < h) to[3] = total.w;
+    }
+}
+
 // The first stage of many column sums in one launch: block b works on the job whose block range
 // holds it, on one 32-column block and one chunk of rows, exactly as sum_rows_stage1 does.
 __global__ void sum_rows_batched_kernel(const RowSumJob* __restrict__ jobs, uint32_t count) {
@@ -239,11 +279,21 @@ void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* 
     if (ld == 0) ld = h;
     uint32_t chunks = sum_rows_chunks(rows);
     uint32_t rows_per_chunk = static_cast<uint32_t>((rows + chunks - 1) / chunks);
-    dim3 grid(static_cast<uint32_t>((h + 31) / 32), chunks);
-    sum_rows_stage1<<<grid, dim3(32, 8), 0, s>>>(g, static_cast<uint32_t>(rows), static_cast<uint32_t>(h), static_cast<uint32_t>(ld),
-                                                 rows_per_chunk, (chunks == 1 && out) ? out : scratch,
-                                                 (chunks > 1 && out) ? counters : nullptr, out);
-    check_launch("sum_rows");
+    // Wide matrices with 16-byte-aligned rows: four columns per lane, chunk sums only.
+    const bool wide = h >= 1024 && ld % 4 == 0 && reinterpret_cast<uintptr_t>(g) % 16 == 0 && (out == nullptr || counters == nullptr) &&
+                      !(chunks == 1 && out);
+    if (wide) {
+        dim3 grid(static_cast<uint32_t>((h + 127) / 128), chunks);
+        sum_rows_stage1_wide<<<grid, dim3(32, 8), 0, s>>>(g, static_cast<uint32_t>(rows), static_cast<uint32_t>(h), static_cast<uint32_t>(ld),
+                                                          rows_per_chunk, scratch);
+        check_launch("sum_rows");
+    } else {
+        dim3 grid(static_cast<uint32_t>((h + 31) / 32), chunks);
+        sum_rows_stage1<<<grid, dim3(32, 8), 0, s>>>(g, static_cast<uint32_t>(rows), static_cast<uint32_t>(h), static_cast<uint32_t>(ld),
+                                                     rows_per_chunk, (chunks == 1 && out) ? out : scratch,
+                                                     (chunks > 1 && out) ? counters : nullptr, out);
+        check_launch("sum_rows");
+    }
     if (chunks > 1 && counters == nullptr && out != nullptr) {
         sum_rows_stage2<<<static_cast<uint32_t>((h + 127) / 128), 128, 0, s>>>(scratch, chunks,
                                                                                 static_cast<uint32_t>(h), out);

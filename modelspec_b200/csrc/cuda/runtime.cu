@@ -11,6 +11,7 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <array>
 #include <chrono>
 #include <cstring>
 #include <map>
@@ -1151,6 +1152,8 @@ struct Scheduler {
         l.flop = 2 * m * n * kk * count;
     }
 
+    std::map<std::array<uint32_t, 5>, uint32_t> forward_probabilities;  // (q, k, v, mask, heads) -> scratch slot
+
     void schedule_attention(uint32_t at) {
         const Node& nd = node(at);
         msx_plan* plan = P;
@@ -1175,6 +1178,9 @@ struct Scheduler {
                 l.flop = 2 * pair_flop;
             } else {
                 uint32_t probs = scratch(k::attention_tc_scratch_floats(shape) * 4);
+                // The backward of the same attention reads these probabilities instead of
+                // computing them again: the scratch then lives until that launch.
+                forward_probabilities[{q, kk, v, mask, static_cast<uint32_t>(nd.heads)}] = probs;
                 Launch& l = emit("attention_forward", nd, {q, kk, v, mask}, {at, probs}, [=](cudaStream_t s) {
                     k::attention_tc_forward(s, plan->f(q), plan->f(kk), plan->f(v), plan->f(mask), plan->f(at), plan->f(probs), shape,
                                             plan->d_status);
@@ -1204,9 +1210,13 @@ struct Scheduler {
             }
         std::vector<uint32_t> reads = {q, kk, v, mask, g};
         if (!simt) {
-            uint32_t probs = scratch(k::attention_tc_scratch_floats(shape) * 4);
+            auto kept = forward_probabilities.find({q, kk, v, mask, static_cast<uint32_t>(nd.heads)});
+            const bool p_ready = kept != forward_probabilities.end();
+            uint32_t probs = p_ready ? kept->second : scratch(k::attention_tc_scratch_floats(shape) * 4);
             uint32_t dprobs = scratch(k::attention_tc_scratch_floats(shape) * 4);
-            std::vector<uint32_t> writes = {probs, dprobs};
+            std::vector<uint32_t> writes = {dprobs};
+            if (p_ready) reads.push_back(probs);
+            else writes.push_back(probs);
             for (int t : {dq, dk, dv})
                 if (t >= 0) writes.push_back(static_cast<uint32_t>(t));
             Launch& l = emit("attention_backward", nd, reads, writes, [=](cudaStream_t s) {
@@ -1214,7 +1224,7 @@ struct Scheduler {
                                          dq >= 0 ? plan->f(static_cast<uint32_t>(dq)) : nullptr,
                                          dk >= 0 ? plan->f(static_cast<uint32_t>(dk)) : nullptr,
                                          dv >= 0 ? plan->f(static_cast<uint32_t>(dv)) : nullptr, plan->f(probs), plan->f(dprobs), shape,
-                                         plan->d_status);
+                                         plan->d_status, p_ready);
             });
             l.flop = pair_flop * (1 + (dv >= 0) + ((dq >= 0 || dk >= 0) ? 1 : 0) + (dq >= 0) + (dk >= 0));
             return;

@@ -93,12 +93,13 @@ def test_tensor_core_matmul_within_the_kernel_tolerance(device, m, k, n, form):
     assert np.abs(gpu.astype(np.float64) - cpu).max() <= 4e-6 * max(terms.max(), 1e-30)
 
 
-@pytest.mark.parametrize("rows,h,v", [(64, 32, 50), (130, 64, 1002), (96, 128, 4099)])
+@pytest.mark.parametrize("rows,h,v", [(64, 32, 50), (130, 64, 1002), (96, 128, 4099), (333, 32, 1002), (400, 16, 40001)])
 def test_a_vocabulary_head_of_odd_width_through_padded_rows(device, rows, h, v):
     """logits = x W^T + b, cross entropy and its gradient, the bias gradient (column sums of the
     logits gradient) and both matmuls that read it, with a width that is not a multiple of 4: on
     the tensor-core path the logits and their gradient are stored with padded rows, which no
-    result may show."""
+    result may show. 40,001 logits do not fit the registers of the one-read kernel and take the
+    general one."""
     r = rng(rows + v)
     p = ProgramText()
     x = p.input("x", "f32", [rows, h]); w = p.input("w", "f32", [v, h]); b = p.input("b", "f32", [v])
