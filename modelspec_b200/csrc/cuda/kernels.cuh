@@ -104,8 +104,16 @@ void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float
 bool layer_norm_backward_supported(uint64_t h);
 uint32_t layer_norm_backward_chunks(uint64_t rows);
 uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h);
+// g1, g2, g3, when not null, are further addends of the adjoint: the kernel reads ((g + g1) + g2) + g3
+// where the program has a chain of Adds that nothing else reads.
 void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
-                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h);
+                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const float* g1 = nullptr,
+                         const float* g2 = nullptr, const float* g3 = nullptr);
+// sum_out = residual + dropout(x), out = layer_norm(sum_out, gamma, beta), rows of up to 1,024
+// elements (layer_norm_backward_supported(h)); the dropout draw is that of `dropout`.
+void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residual, const int32_t* token, uint64_t seed,
+                            uint32_t threshold, float scale, uint64_t index_base, const float* gamma, const float* beta,
+                            float* sum_out, float* out, uint64_t rows, uint64_t h);
 void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t k);
 void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, uint64_t rows, uint64_t k);
 // Row losses max + ln(sum exp(x - max)) - x[label] into row_loss[rows], then

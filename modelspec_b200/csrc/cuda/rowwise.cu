@@ -398,6 +398,53 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
 
 inline uint32_t warp_row_blocks(uint64_t rows) { return static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock); }
 
+// dropout(x) + residual, then layer_norm of the sum, one warp per row with the row in registers:
+// the three launches of a transformer sublayer's tail as one. Every element goes through the same
+// rounded operations as the separate kernels (the Philox draw of element index_base + r h + c, the
+// scaled or zeroed value, one addition, the layer norm of the stored sum).
+template <int ITEMS>
+__global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
+    const float* __restrict__ x, const float* __restrict__ residual, const int32_t* __restrict__ token, uint32_t seed_lo,
+    uint32_t seed_hi, uint32_t threshold, float scale, uint64_t index_base, const float* __restrict__ gamma,
+    const float* __restrict__ beta, float* __restrict__ sum_out, float* __restrict__ out, uint32_t rows, uint32_t h) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const uint32_t id_lo = static_cast<uint32_t>(token[0]), id_hi = static_cast<uint32_t>(token[1]);
+    const uint64_t base = static_cast<uint64_t>(r) * h;
+    float v[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const uint32_t c = i * 32 + lane;
+        v[i] = 0.0f;
+        if (c < h) {
+            const uint32_t w0 = philox_word0(static_cast<uint32_t>(index_base + base + c), 4u, id_lo, id_hi, seed_lo, seed_hi);
+            const float dropped = w0 >= threshold ? x[base + c] * scale : 0.0f;
+            v[i] = residual[base + c] + dropped;
+            sum_out[base + c] = v[i];
+        }
+    }
+    const float width = static_cast<float>(h);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i)
+        if (i * 32 + lane < h) sum += v[i];
+    const float mean = warp_sum(sum) / width;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i)
+        if (i * 32 + lane < h) {
+            float d = v[i] - mean;
+            q = fmaf(d, d, q);
+        }
+    const float rstd = 1.0f / sqrtf(warp_sum(q) / width + kLayerNormEps);
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const uint32_t c = i * 32 + lane;
+        if (c < h) out[base + c] = (v[i] - mean) * rstd * gamma[c] + beta[c];
+    }
+}
+
 // layer_norm_grad_x, layer_norm_grad_gamma and the beta gradient in one launch. A block takes a
 // chunk of rows, a warp one row at a time with the row of x and of g in registers (ITEMS values
 // per lane): row moments, then the dx row, then this row's terms of the column sums. Warp sums of
@@ -407,7 +454,8 @@ inline uint32_t warp_row_blocks(uint64_t rows) { return static_cast<uint32_t>((r
 // sequential column sum. dx (with gamma), dgamma and dbeta may each be null.
 template <int ITEMS>
 __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
-    const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ g, float* __restrict__ dx,
+    const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ g, const float* __restrict__ g1,
+    const float* __restrict__ g2, const float* __restrict__ g3, float* __restrict__ dx,
     float* __restrict__ partial, uint32_t* __restrict__ counter, float* __restrict__ dgamma, float* __restrict__ dbeta,
     uint32_t want, uint32_t rows, uint32_t h, uint32_t rows_per_chunk) {
     __shared__ float buf[8 * 32 * ITEMS];
@@ -432,6 +480,10 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
             uint32_t c = i * 32 + lane;
             xv[i] = c < h ? xr[c] : 0.0f;
             gv[i] = c < h ? gr[c] : 0.0f;
+            // The adjoint as a sum the program spells as a chain of Adds: ((g + g1) + g2) + g3.
+            if (g1 != nullptr && c < h) gv[i] = gv[i] + g1[static_cast<uint64_t>(r) * h + c];
+            if (g2 != nullptr && c < h) gv[i] = gv[i] + g2[static_cast<uint64_t>(r) * h + c];
+            if (g3 != nullptr && c < h) gv[i] = gv[i] + g3[static_cast<uint64_t>(r) * h + c];
         }
         float sum = 0.0f;
 #pragma unroll
@@ -564,19 +616,39 @@ void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float
     check_launch("layer_norm_grad_gamma");
 }
 
+void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residual, const int32_t* token, uint64_t seed,
+                            uint32_t threshold, float scale, uint64_t index_base, const float* gamma, const float* beta,
+                            float* sum_out, float* out, uint64_t rows, uint64_t h) {
+    if (rows == 0 || h == 0) return;
+    const uint32_t items = static_cast<uint32_t>((h + 31) / 32), blocks = static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    const uint32_t lo = static_cast<uint32_t>(seed), hi = static_cast<uint32_t>(seed >> 32), r = static_cast<uint32_t>(rows),
+                   hh = static_cast<uint32_t>(h);
+#define MSX_DROPOUT_LN(N) dropout_add_layer_norm_kernel<N><<<blocks, 256, 0, s>>>(x, residual, token, lo, hi, threshold, scale, index_base, gamma, beta, sum_out, out, r, hh)
+    if (items <= 1) MSX_DROPOUT_LN(1);
+    else if (items <= 2) MSX_DROPOUT_LN(2);
+    else if (items <= 4) MSX_DROPOUT_LN(4);
+    else if (items <= 8) MSX_DROPOUT_LN(8);
+    else if (items <= 16) MSX_DROPOUT_LN(16);
+    else if (items <= 24) MSX_DROPOUT_LN(24);
+    else MSX_DROPOUT_LN(32);
+#undef MSX_DROPOUT_LN
+    check_launch("dropout_add_layer_norm");
+}
+
 bool layer_norm_backward_supported(uint64_t h) { return h >= 1 && h <= 1024; }
 uint32_t layer_norm_backward_chunks(uint64_t rows) { return backward_chunks(rows); }
 uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h) { return 2ull * backward_chunks(rows) * h; }
 
 void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
-                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h) {
+                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const float* g1, const float* g2,
+                         const float* g3) {
     if (h == 0) return;
     uint32_t chunks = backward_chunks(rows);
     uint32_t per = static_cast<uint32_t>((rows + chunks - 1) / chunks);
     uint32_t items = static_cast<uint32_t>((h + 31) / 32);
     uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
     uint32_t want = (dgamma ? 1u : 0u) | (dbeta ? 2u : 0u);
-#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, dx, scratch, counter, dgamma, dbeta, want, r, hh, per)
+#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per)
     if (items <= 1) MSX_LN_BACKWARD(1);
     else if (items <= 2) MSX_LN_BACKWARD(2);
     else if (items <= 4) MSX_LN_BACKWARD(4);

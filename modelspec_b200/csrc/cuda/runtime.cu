@@ -13,6 +13,7 @@
 #include <algorithm>
 #include <array>
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -90,6 +91,10 @@ static NcclApi g_nccl;
 
 // A contiguous run of gradient bytes that is summed across ranks by one all-reduce, issued on
 // the side stream as soon as the launch that writes its last gradient has been enqueued.
+#ifndef MSX_DEFAULT_FUSIONS
+#define MSX_DEFAULT_FUSIONS 3u
+#endif
+
 struct Bucket {
     uint64_t offset = 0, bytes = 0;  // within the arena
     int after_launch = -1;
@@ -173,6 +178,15 @@ struct msx_plan {
     std::vector<uint32_t> gradient_slots;  // in production order
     int optimizer_launch = -1;
     bool average_gradients = false;
+    // The weight sum of the whole batch, which a data-parallel cross-entropy divides by, depends
+    // only on a host input: it is summed and all-reduced on the side stream from the start of the
+    // step, beside the forward pass, into a buffer of its own. The loss is all-reduced on the side
+    // stream too; nothing on the device waits for it before the end of the step.
+    int early_weights = -1;          // slot of the weights input, or -1
+    uint64_t early_rows = 0;
+    float* d_weight_total = nullptr;
+    cudaEvent_t step_begun = nullptr, weights_summed = nullptr, loss_ready = nullptr, loss_reduced = nullptr;
+    bool loss_in_flight = false;     // set while a step is being enqueued
     uint64_t bucket_bytes = 25u << 20;
 
     void* ptr(uint32_t pos) const {
@@ -207,6 +221,16 @@ void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream
 
 // ---------------------------------------------------------------------------------------------
 // The scheduler.
+
+// Tuning switch: MSX_FUSE is a bit mask of optional fusions (default: all). 1 sublayer tails
+// (dropout + residual + layer norm), 2 adjoint sums inside layer-norm backward.
+inline uint32_t fusion_mask() {
+    static const uint32_t mask = [] {
+        const char* text = std::getenv("MSX_FUSE");
+        return text ? static_cast<uint32_t>(std::strtoul(text, nullptr, 0)) : MSX_DEFAULT_FUSIONS;
+    }();
+    return mask;
+}
 
 struct Scheduler {
     msx_plan* P;
@@ -646,6 +670,18 @@ struct Scheduler {
             case Op::Sub:
             case Op::Mul:
             case Op::Div: {
+                if (nd.op == Op::Add && joins_layer_norm_adjoint(at)) {
+                    // The sum is formed inside the layer-norm backward launch that alone reads it.
+                    std::vector<uint32_t> addends;
+                    for (uint32_t operand : in) {
+                        auto inner = adjoint_sums.find(operand);
+                        if (inner != adjoint_sums.end()) addends.insert(addends.end(), inner->second.begin(), inner->second.end());
+                        else addends.push_back(operand);
+                    }
+                    adjoint_sums[at] = addends;
+                    out.kind = Slot::Dead;
+                    break;
+                }
                 k::Binary op = nd.op == Op::Add ? k::Binary::Add : nd.op == Op::Sub ? k::Binary::Sub
                                : nd.op == Op::Mul ? k::Binary::Mul : k::Binary::Div;
                 bool sa = is_scalar_operand(in[0], nd), sb = is_scalar_operand(in[1], nd);
@@ -875,15 +911,32 @@ struct Scheduler {
                     if (pitchable(gpos)) set_pitch(gpos);
                     const uint64_t ld_grad = gs.pitch;
                     uint32_t ctr = counters(1);
+                    if (P->slots[weights].kind == Slot::Input && P->early_weights < 0) {
+                        P->early_weights = static_cast<int>(weights);
+                        P->early_rows = r;
+                    }
                     emit("cross_entropy_with_grad", nd, {logits, labels, weights, seed}, {at, gpos, row_loss, den}, [=](cudaStream_t s) {
-                        if (plan->comm) {
-                            k::weight_sum(s, plan->f(weights), r, plan->f(den));
-                            all_reduce(plan, plan->f(den), 1, false, s);
+                        float* total = plan->f(den);
+                        const bool side = plan->comm && plan->comm_stream && plan->early_weights == static_cast<int>(weights);
+                        if (side) {
+                            total = plan->d_weight_total;  // summed and reduced since the start of the step
+                            cuda_ok(cudaStreamWaitEvent(s, plan->weights_summed, 0), "cudaStreamWaitEvent");
+                        } else if (plan->comm) {
+                            k::weight_sum(s, plan->f(weights), r, total);
+                            all_reduce(plan, total, 1, false, s);
                         }
                         k::cross_entropy_with_grad(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(seed), plan->comm != nullptr,
-                                                   plan->f(den), plan->f(row_loss), plan->f(at), plan->f(gpos), r, v, plan->counter(ctr), ld,
+                                                   total, plan->f(row_loss), plan->f(at), plan->f(gpos), r, v, plan->counter(ctr), ld,
                                                    ld_grad);
-                        all_reduce(plan, plan->f(at), 1, false, s);
+                        if (side) {
+                            cuda_ok(cudaEventRecord(plan->loss_ready, s), "cudaEventRecord");
+                            cuda_ok(cudaStreamWaitEvent(plan->comm_stream, plan->loss_ready, 0), "cudaStreamWaitEvent");
+                            all_reduce(plan, plan->f(at), 1, false, plan->comm_stream);
+                            cuda_ok(cudaEventRecord(plan->loss_reduced, plan->comm_stream), "cudaEventRecord");
+                            plan->loss_in_flight = true;
+                        } else {
+                            all_reduce(plan, plan->f(at), 1, false, s);
+                        }
                     });
                     break;
                 }
@@ -922,6 +975,44 @@ struct Scheduler {
                 uint32_t threshold = static_cast<uint32_t>(msx::dropout_keep_threshold(nd.p));
                 float scale = 1.0f / (1.0f - nd.p);
                 uint64_t row_width = nd.ty.rank() > 0 && nd.ty.shape[0] > 0 ? count / nd.ty.shape[0] : 1;
+                // residual + dropout(x) followed by the layer norm of that sum (the tail of every
+                // transformer sublayer): one launch writes the sum and its layer norm.
+                if ((fusion_mask() & 1u) && nd.op == Op::Dropout && nd.ty.rank() == 2 && users[at].size() == 1 &&
+                    k::layer_norm_backward_supported(nd.ty.shape[1])) {
+                    bool is_output = false;
+                    for (const msx::Output& o : prog.outputs) is_output = is_output || pos(o.value) == at;
+                    const uint32_t add_at = users[at][0];
+                    const Node& add = node(add_at);
+                    int norm = -1;
+                    if (!is_output && add.op == Op::Add && !handled[add_at] && add.ty.shape == nd.ty.shape) {
+                        const uint32_t residual = pos(add.operands[0]) == at ? pos(add.operands[1]) : pos(add.operands[0]);
+                        if (residual < at && node(residual).ty.shape == nd.ty.shape) {
+                            for (uint32_t u : users[add_at]) {
+                                const Node& ln = node(u);
+                                if (ln.op == Op::LayerNorm && !handled[u] && pos(ln.operands[0]) == add_at && pos(ln.operands[1]) < at &&
+                                    pos(ln.operands[2]) < at) { norm = static_cast<int>(u); break; }
+                            }
+                            if (norm >= 0) {
+                                const uint32_t ln_at = static_cast<uint32_t>(norm);
+                                const uint32_t gamma = pos(node(ln_at).operands[1]), beta = pos(node(ln_at).operands[2]);
+                                handled[add_at] = handled[ln_at] = 1;
+                                out.kind = Slot::Dead;
+                                for (uint32_t made : {add_at, ln_at}) {
+                                    Slot& slot = P->slots[made];
+                                    slot.kind = Slot::Arena;
+                                    slot.bytes = std::max<uint64_t>(node(made).ty.count() * 4, 4);
+                                }
+                                const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
+                                emit("dropout_add_layer_norm", nd, {x, token, residual, gamma, beta}, {add_at, ln_at}, [=](cudaStream_t s) {
+                                    k::dropout_add_layer_norm(s, plan->f(x), plan->f(residual), plan->i(token), plan->seed, threshold, scale,
+                                                              plan->shard_rows_before * row_width, plan->f(gamma), plan->f(beta),
+                                                              plan->f(add_at), plan->f(ln_at), r, h);
+                                });
+                                break;
+                            }
+                        }
+                    }
+                }
                 emit("dropout", nd, in, {at}, [=](cudaStream_t s) {
                     k::dropout(s, plan->f(x), plan->i(token), plan->seed, threshold, scale, plan->shard_rows_before * row_width,
                                plan->f(at), count);
@@ -930,6 +1021,43 @@ struct Scheduler {
             }
             default: unsupported(nd, "no kernel is written for it");
         }
+    }
+
+    // Chains of Adds that only the gradients of one layer norm read (the sum of the three input
+    // gradients of the Q, K, V projections and the residual path): the backward launch adds them
+    // as it loads its adjoint, in the program's nesting order, and the sums are never stored.
+    std::map<uint32_t, std::vector<uint32_t>> adjoint_sums;
+    size_t addend_count(uint32_t at) const {
+        size_t n = 0;
+        for (uint32_t o : node(at).operands) {
+            auto inner = adjoint_sums.find(pos(o));
+            n += inner != adjoint_sums.end() ? inner->second.size() : 1;
+        }
+        return n;
+    }
+    bool joins_layer_norm_adjoint(uint32_t at, size_t carried = 0) const {
+        const Node& nd = node(at);
+        if (!(fusion_mask() & 2u) || nd.op != Op::Add || nd.ty.rank() != 2 || nd.operands.size() != 2) return false;
+        for (uint32_t o : nd.operands)
+            if (node(pos(o)).ty.shape != nd.ty.shape) return false;
+        for (const msx::Output& o : prog.outputs)
+            if (pos(o.value) == at) return false;
+        const size_t addends = carried ? carried + 1 : addend_count(at);
+        if (addends > 4 || users[at].empty()) return false;
+        // Either the next Add of the chain ...
+        if (users[at].size() == 1 && node(users[at][0]).op == Op::Add)
+            return pos(node(users[at][0]).operands[0]) != pos(node(users[at][0]).operands[1]) && joins_layer_norm_adjoint(users[at][0], addends);
+        // ... or exactly the three gradient ops of one layer norm, which one launch will take.
+        if (!k::layer_norm_backward_supported(nd.ty.shape[1]) || users[at].size() != 3) return false;
+        int dx = -1, dgamma = -1, dbeta = -1;
+        for (uint32_t u : users[at]) {
+            const Node& un = node(u);
+            if (un.op == Op::LayerNormGradX && pos(un.operands[2]) == at && pos(un.operands[0]) != at && pos(un.operands[1]) != at) dx = static_cast<int>(u);
+            else if (un.op == Op::LayerNormGradGamma && pos(un.operands[1]) == at && pos(un.operands[0]) != at) dgamma = static_cast<int>(u);
+            else if (un.op == Op::SumRows) dbeta = static_cast<int>(u);
+        }
+        if (dx < 0 || dgamma < 0 || dbeta < 0) return false;
+        return pos(node(static_cast<uint32_t>(dx)).operands[0]) == pos(node(static_cast<uint32_t>(dgamma)).operands[0]);
     }
 
     // The gradients of one layer_norm (dx, dgamma and, as the column sums of the same adjoint,
@@ -957,7 +1085,12 @@ struct Scheduler {
         if (dgamma >= 0)
             for (uint32_t u : users[g])
                 if (u > at && node(u).op == Op::SumRows && !handled[u]) { dbeta = static_cast<int>(u); break; }
-        std::vector<uint32_t> reads = {x, g}, writes;
+        // An adjoint that is an absorbed chain of Adds is read as its addends.
+        std::vector<uint32_t> adjoint = {g};
+        auto summed = adjoint_sums.find(g);
+        if (summed != adjoint_sums.end()) adjoint = summed->second;
+        std::vector<uint32_t> reads = {x}, writes;
+        reads.insert(reads.end(), adjoint.begin(), adjoint.end());
         if (gamma >= 0) reads.push_back(static_cast<uint32_t>(gamma));
         for (int other : {dx, dgamma, dbeta}) {
             if (other < 0) continue;
@@ -982,16 +1115,20 @@ struct Scheduler {
             if (dbeta >= 0) deferred.push_back({tmp, static_cast<uint64_t>(chunks) * h, chunks, h, static_cast<uint32_t>(dbeta)});
             float* const wanted = reinterpret_cast<float*>(uintptr_t{1});  // only null or not is read
             emit("layer_norm_backward", nd, reads, now, [=](cudaStream_t s) {
-                k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(g), at_or_null(dx), plan->f(tmp), nullptr,
-                                       dgamma >= 0 ? wanted : nullptr, dbeta >= 0 ? wanted : nullptr, r, h);
+                k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(dx), plan->f(tmp), nullptr,
+                                       dgamma >= 0 ? wanted : nullptr, dbeta >= 0 ? wanted : nullptr, r, h,
+                                       adjoint.size() > 1 ? plan->f(adjoint[1]) : nullptr, adjoint.size() > 2 ? plan->f(adjoint[2]) : nullptr,
+                                       adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr);
             });
             return true;
         }
         uint32_t ctr = counters(1);
         writes.push_back(tmp);
         emit("layer_norm_backward", nd, reads, writes, [=](cudaStream_t s) {
-            k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(g), at_or_null(dx), plan->f(tmp), plan->counter(ctr),
-                                   at_or_null(dgamma), at_or_null(dbeta), r, h);
+            k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(dx), plan->f(tmp), plan->counter(ctr),
+                                   at_or_null(dgamma), at_or_null(dbeta), r, h,
+                                   adjoint.size() > 1 ? plan->f(adjoint[1]) : nullptr, adjoint.size() > 2 ? plan->f(adjoint[2]) : nullptr,
+                                   adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr);
         });
         return true;
     }
@@ -1125,8 +1262,9 @@ struct Scheduler {
             set_pitch(first.result);
             pitches.c = P->slots[first.result].pitch;
         }
+        const std::vector<Product>& products = group;
         std::vector<int> workspaces;
-        for (const Product& p : group) {
+        for (const Product& p : products) {
             int ws = -1;
             if (tc.workspace_floats) {
                 ws = static_cast<int>(scratch(tc.workspace_floats * 4));
@@ -1139,7 +1277,7 @@ struct Scheduler {
         Launch& l = emit("matmul", nd, reads, writes, [=](cudaStream_t s) {
             k::MatmulOperands operands[4];
             for (uint32_t g = 0; g < count; ++g) {
-                const Product& p = group[g];
+                const Product& p = products[g];
                 operands[g].a = plan->f(p.a);
                 operands[g].b = plan->f(p.b);
                 operands[g].c = plan->f(p.result);
@@ -1498,6 +1636,9 @@ void release(msx_plan* P) {
     }
     if (P->comm && P->owns_comm) g_nccl.CommDestroy(P->comm);
     if (P->comm_stream) cudaStreamDestroy(P->comm_stream);
+    for (cudaEvent_t e : {P->step_begun, P->weights_summed, P->loss_ready, P->loss_reduced})
+        if (e) cudaEventDestroy(e);
+    cudaFree(P->d_weight_total);
     cudaFree(P->arena);
     for (size_t p = 0; p < P->params.size(); ++p) {
         if (P->owns_param[p]) cudaFree(P->params[p]);
@@ -1535,9 +1676,25 @@ void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream
 }
 
 void enqueue_all(msx_plan* P) {
+    const bool side = P->comm && P->comm_stream;
+    P->loss_in_flight = false;
+    if (side && P->early_weights >= 0) {
+        cuda_ok(cudaEventRecord(P->step_begun, P->stream), "cudaEventRecord");
+        cuda_ok(cudaStreamWaitEvent(P->comm_stream, P->step_begun, 0), "cudaStreamWaitEvent");
+        k::weight_sum(P->comm_stream, P->f(static_cast<uint32_t>(P->early_weights)), P->early_rows, P->d_weight_total);
+        all_reduce(P, P->d_weight_total, 1, false, P->comm_stream);
+        cuda_ok(cudaEventRecord(P->weights_summed, P->comm_stream), "cudaEventRecord");
+    }
+    auto join_loss = [&]() {
+        if (!P->loss_in_flight) return;
+        cuda_ok(cudaStreamWaitEvent(P->stream, P->loss_reduced, 0), "cudaStreamWaitEvent");
+        P->loss_in_flight = false;
+    };
     for (size_t l = 0; l < P->launches.size(); ++l) {
-        if (P->comm && static_cast<int>(l) == P->optimizer_launch)
+        if (P->comm && static_cast<int>(l) == P->optimizer_launch) {
             for (Bucket& b : P->buckets) cuda_ok(cudaStreamWaitEvent(P->stream, b.done, 0), "cudaStreamWaitEvent");
+            join_loss();
+        }
         P->launches[l].run(P->stream);
         if (!P->comm) continue;
         for (Bucket& b : P->buckets) {
@@ -1550,6 +1707,7 @@ void enqueue_all(msx_plan* P) {
             cuda_ok(cudaEventRecord(b.done, P->comm_stream), "cudaEventRecord");
         }
     }
+    join_loss();  // a plan without an optimizer launch: the side stream rejoins here
 }
 
 // Waits for `event` at most `timeout_ms`, polling: never an unbounded wait.
@@ -2099,6 +2257,9 @@ int msx_comm_init(msx_plan* plan, int rank, int world, const void* unique_id_128
         plan->average_gradients = true;
         for (const Node& n : plan->program.nodes)
             if (n.op == Op::CrossEntropy) plan->average_gradients = false;
+        for (cudaEvent_t* e : {&plan->step_begun, &plan->weights_summed, &plan->loss_ready, &plan->loss_reduced})
+            cuda_ok(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "cudaEventCreate");
+        cuda_ok(cudaMalloc(&plan->d_weight_total, sizeof(float)), "cudaMalloc(weight total)");
         plan_buckets(plan);
         for (Bucket& b : plan->buckets) {
             cuda_ok(cudaEventCreateWithFlags(&b.ready, cudaEventDisableTiming), "cudaEventCreate");

@@ -376,6 +376,40 @@ def test_dropout_mask_and_values_match_the_cpu_in_bits(device, p_drop):
     assert abs(kept - (1 - p_drop)) < 0.01
 
 
+@pytest.mark.parametrize("rows,h", [(64, 128), (37, 96), (130, 768), (9, 33)])
+def test_a_sublayer_tail_and_the_summed_adjoint_of_its_layer_norm(device, rows, h):
+    """residual + dropout(x) with the layer norm of the sum is one launch, and a chain of Adds
+    that only the three gradients of a layer norm read is added inside their launch: the stored
+    sum is the separate kernels' bit for bit, the layer norm and its gradients stay inside the
+    kernel tolerance, and the listing shows the fused launches."""
+    r = rng(rows * 3 + h)
+    p = ProgramText()
+    x = p.input("x", "f32", [rows, h]); res = p.input("res", "f32", [rows, h]); token = p.input("M.forward.dropout#0", "i32", [2])
+    gamma = p.input("gamma", "f32", [h]); beta = p.input("beta", "f32", [h])
+    ga = p.input("ga", "f32", [rows, h]); gb = p.input("gb", "f32", [rows, h]); gc = p.input("gc", "f32", [rows, h]); gd = p.input("gd", "f32", [rows, h])
+    dropped = p.op("Dropout", [rows, h], [x, token], attr="[p = 0.1, site = M.forward.dropout#0]")
+    total = p.op("Add", [rows, h], [res, dropped])
+    y = p.op("LayerNorm", [rows, h], [total, gamma, beta])
+    s1 = p.op("Add", [rows, h], [ga, gb])
+    s2 = p.op("Add", [rows, h], [s1, gc])
+    s3 = p.op("Add", [rows, h], [s2, gd])
+    dx = p.op("LayerNormGradX", [rows, h], [total, gamma, s3])
+    dg = p.op("LayerNormGradGamma", [h], [total, s3])
+    db = p.op("SumRows", [h], [s3])
+    for value in (total, y, dx, dg, db):
+        p.output(value)
+    feed = {"x": values(r, rows, h), "res": values(r, rows, h), "M.forward.dropout#0": np.array([77, -3], dtype=np.int32),
+            "gamma": values(r, h) + 1, "beta": values(r, h), "ga": values(r, rows, h), "gb": values(r, rows, h),
+            "gc": values(r, rows, h), "gd": values(r, rows, h)}
+    listing = M.schedule_describe(p.text())
+    kernels = [l.split()[1] for l in listing.strip().splitlines()[:-1]]
+    assert "dropout_add_layer_norm" in kernels and "dropout" not in kernels and "binary" not in kernels
+    res_ = run_both(device, p.text(), feed, outputs=[(total, rows * h), (y, rows * h), (dx, rows * h), (dg, h), (db, h)], seed=99)
+    assert_bits_equal(res_[0][1], res_[0][0], "residual + dropout")
+    for (cpu, gpu), what in zip(res_[1:], ("layer norm", "dx", "dgamma", "dbeta")):
+        assert_kernel_close(gpu, cpu, scale=np.full(cpu.shape, max(1.0, float(np.abs(cpu).max()))), what=what)
+
+
 def test_bad_inputs_are_refused_like_the_interpreter_refuses_them(device):
     p = ProgramText()
     table = p.input("table", "f32", [5, 4]); ids = p.input("ids", "i32", [3])
