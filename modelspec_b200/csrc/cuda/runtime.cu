@@ -1675,25 +1675,29 @@ void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream
     nccl_ok(g_nccl.AllReduce(data, data, count, ncclFloat, average ? ncclAvg : ncclSum, P->comm, stream), "ncclAllReduce");
 }
 
-void enqueue_all(msx_plan* P) {
-    const bool side = P->comm && P->comm_stream;
+// Data parallel: what a step starts on the side stream before its first launch, and how the side
+// stream rejoins. Used by the step itself and by the launch-by-launch profile.
+void begin_side_work(msx_plan* P) {
     P->loss_in_flight = false;
-    if (side && P->early_weights >= 0) {
-        cuda_ok(cudaEventRecord(P->step_begun, P->stream), "cudaEventRecord");
-        cuda_ok(cudaStreamWaitEvent(P->comm_stream, P->step_begun, 0), "cudaStreamWaitEvent");
-        k::weight_sum(P->comm_stream, P->f(static_cast<uint32_t>(P->early_weights)), P->early_rows, P->d_weight_total);
-        all_reduce(P, P->d_weight_total, 1, false, P->comm_stream);
-        cuda_ok(cudaEventRecord(P->weights_summed, P->comm_stream), "cudaEventRecord");
-    }
-    auto join_loss = [&]() {
-        if (!P->loss_in_flight) return;
-        cuda_ok(cudaStreamWaitEvent(P->stream, P->loss_reduced, 0), "cudaStreamWaitEvent");
-        P->loss_in_flight = false;
-    };
+    if (!(P->comm && P->comm_stream) || P->early_weights < 0) return;
+    cuda_ok(cudaEventRecord(P->step_begun, P->stream), "cudaEventRecord");
+    cuda_ok(cudaStreamWaitEvent(P->comm_stream, P->step_begun, 0), "cudaStreamWaitEvent");
+    k::weight_sum(P->comm_stream, P->f(static_cast<uint32_t>(P->early_weights)), P->early_rows, P->d_weight_total);
+    all_reduce(P, P->d_weight_total, 1, false, P->comm_stream);
+    cuda_ok(cudaEventRecord(P->weights_summed, P->comm_stream), "cudaEventRecord");
+}
+void join_loss(msx_plan* P) {
+    if (!P->loss_in_flight) return;
+    cuda_ok(cudaStreamWaitEvent(P->stream, P->loss_reduced, 0), "cudaStreamWaitEvent");
+    P->loss_in_flight = false;
+}
+
+void enqueue_all(msx_plan* P) {
+    begin_side_work(P);
     for (size_t l = 0; l < P->launches.size(); ++l) {
         if (P->comm && static_cast<int>(l) == P->optimizer_launch) {
             for (Bucket& b : P->buckets) cuda_ok(cudaStreamWaitEvent(P->stream, b.done, 0), "cudaStreamWaitEvent");
-            join_loss();
+            join_loss(P);
         }
         P->launches[l].run(P->stream);
         if (!P->comm) continue;
@@ -1707,7 +1711,7 @@ void enqueue_all(msx_plan* P) {
             cuda_ok(cudaEventRecord(b.done, P->comm_stream), "cudaEventRecord");
         }
     }
-    join_loss();  // a plan without an optimizer launch: the side stream rejoins here
+    join_loss(P);  // a plan without an optimizer launch: the side stream rejoins here
 }
 
 // Waits for `event` at most `timeout_ms`, polling: never an unbounded wait.
@@ -2056,6 +2060,7 @@ int msx_profile_step_repeated(msx_plan* plan, uint32_t repeats, float* launch_ms
             std::memcpy(plan->pinned[0], plan->blob.data(), plan->input_bytes);
             cuda_ok(cudaMemcpyAsync(plan->d_inputs, plan->pinned[0], plan->input_bytes, cudaMemcpyHostToDevice, plan->stream), "cudaMemcpyAsync");
         }
+        begin_side_work(plan);
         cuda_ok(cudaEventRecord(events[0], plan->stream), "cudaEventRecord");
         for (size_t l = 0; l < plan->launches.size(); ++l) {
             const std::string& kernel = plan->launches[l].kernel;
@@ -2063,6 +2068,7 @@ int msx_profile_step_repeated(msx_plan* plan, uint32_t repeats, float* launch_ms
             for (uint32_t r = 0; r < (in_place ? 1u : repeats); ++r) plan->launches[l].run(plan->stream);
             cuda_ok(cudaEventRecord(events[l + 1], plan->stream), "cudaEventRecord");
         }
+        join_loss(plan);
         cuda_ok(cudaStreamSynchronize(plan->stream), "cudaStreamSynchronize");
         for (size_t l = 0; l < plan->launches.size(); ++l) {
             cuda_ok(cudaEventElapsedTime(&launch_ms[l], events[l], events[l + 1]), "cudaEventElapsedTime");
