@@ -217,9 +217,11 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
             const uint64_t hot_id = first + hot_item[slot];
             const uint32_t row = static_cast<uint32_t>(hot_id / groups), col0 = static_cast<uint32_t>(hot_id % groups) * span;
             const uint32_t at = hot_at[slot], count = hot_count[slot];
-            float4 held4[VEC == 4 ? LOADS : 1];
-            float held1[VEC == 1 ? LOADS : 1];
-            auto fetch = [&](uint32_t chunk_start) {
+            // Two chunks of loads are in flight while a third is added: one round trip to memory
+            // per chunk would otherwise be the whole cost of a hot row.
+            float4 held4[2][VEC == 4 ? LOADS : 1];
+            float held1[2][VEC == 1 ? LOADS : 1];
+            auto fetch = [&](uint32_t chunk_start, int set) {
 #pragma unroll
                 for (int j = 0; j < LOADS; ++j) {
                     const uint32_t f = threadIdx.x + 256 * j;
@@ -227,27 +229,33 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
                     const bool wanted = chunk_start + r < count && col0 + c < h;
                     const int32_t src = wanted ? __ldg(sorted_n + at + chunk_start + r) : 0;
                     const float* from = g + static_cast<uint64_t>(src) * h + col0 + c;
-                    if (VEC == 4) held4[j % (VEC == 4 ? LOADS : 1)] = wanted ? *reinterpret_cast<const float4*>(from) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    else held1[j % (VEC == 1 ? LOADS : 1)] = wanted ? *from : 0.0f;
+                    if (VEC == 4) held4[set][j % (VEC == 4 ? LOADS : 1)] = wanted ? *reinterpret_cast<const float4*>(from) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    else held1[set][j % (VEC == 1 ? LOADS : 1)] = wanted ? *from : 0.0f;
                 }
             };
             float acc = 0.0f;
-            fetch(0);
-            for (uint32_t start = 0; start < count; start += kHotChunk) {
+            fetch(0, 0);
+            if (kHotChunk < count) fetch(kHotChunk, 1);
+            for (uint32_t pair = 0; pair < count; pair += 2 * kHotChunk) {
 #pragma unroll
-                for (int j = 0; j < LOADS; ++j) {
-                    const uint32_t f = threadIdx.x + 256 * j;
-                    const uint32_t r = f / (span / VEC), c = (f % (span / VEC)) * VEC;
-                    if (VEC == 4) *reinterpret_cast<float4*>(&stage[r][c]) = held4[j % (VEC == 4 ? LOADS : 1)];
-                    else stage[r][c] = held1[j % (VEC == 1 ? LOADS : 1)];
+                for (int set = 0; set < 2; ++set) {
+                    const uint32_t start = pair + set * kHotChunk;
+                    if (start >= count) break;
+#pragma unroll
+                    for (int j = 0; j < LOADS; ++j) {
+                        const uint32_t f = threadIdx.x + 256 * j;
+                        const uint32_t r = f / (span / VEC), c = (f % (span / VEC)) * VEC;
+                        if (VEC == 4) *reinterpret_cast<float4*>(&stage[r][c]) = held4[set][j % (VEC == 4 ? LOADS : 1)];
+                        else stage[r][c] = held1[set][j % (VEC == 1 ? LOADS : 1)];
+                    }
+                    __syncthreads();
+                    if (start + 2 * kHotChunk < count) fetch(start + 2 * kHotChunk, set);
+                    if (threadIdx.x < span) {
+                        const uint32_t here = min(kHotChunk, count - start);
+                        for (uint32_t r = 0; r < here; ++r) acc = acc + stage[r][threadIdx.x];
+                    }
+                    __syncthreads();
                 }
-                __syncthreads();
-                if (start + kHotChunk < count) fetch(start + kHotChunk);  // in flight while the chain below runs
-                if (threadIdx.x < span) {
-                    const uint32_t here = min(kHotChunk, count - start);
-                    for (uint32_t r = 0; r < here; ++r) acc = acc + stage[r][threadIdx.x];
-                }
-                __syncthreads();
             }
             if (threadIdx.x < span && col0 + threadIdx.x < h) {
                 const uint64_t where = static_cast<uint64_t>(row) * h + col0 + threadIdx.x;

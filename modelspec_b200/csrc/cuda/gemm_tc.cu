@@ -33,6 +33,7 @@
 // makes every role leave its loop, frees the tensor memory and returns. A k range split across
 // CTAs (grid.z, k blocks dealt out round-robin) writes partial tiles that `splitk_reduce_kernel`
 // or the step's finalize launch adds in ascending split order (deterministic).
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -541,12 +542,14 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, float* __rest
 
 template <int BM, int BN, bool A_T, bool B_T> void launch(cudaStream_t s, const TcArgs& args, dim3 grid) {
     auto kernel = matmul_tc_kernel<BM, BN, A_T, B_T>;
-    static int configured_device = -1;  // the attribute is per device: set it when the device changes
+    // The attribute is per device: set it when the device changes (a second thread that sees a
+    // stale value only sets it once more).
+    static std::atomic<int> configured_device{-1};
     int device = 0;
     check(cudaGetDevice(&device), "cudaGetDevice");
-    if (device != configured_device) {
+    if (device != configured_device.load(std::memory_order_relaxed)) {
         check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Config<BM, BN>::TOTAL)), "matmul_tc shared memory");
-        configured_device = device;
+        configured_device.store(device, std::memory_order_relaxed);
     }
     kernel<<<grid, THREADS, Config<BM, BN>::TOTAL, s>>>(args);
     check_launch("matmul_tc");

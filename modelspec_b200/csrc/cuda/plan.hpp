@@ -7,14 +7,29 @@
 // gives every stored value its own buffer, schedule.rs:97-104), and the optimizer is one launch
 // over all parameters (the reference dispatches once per parameter, ir/kernel.rs:869-894).
 //
-// Fusions made here, each leaving the arithmetic of every element unchanged:
-//   * rank-0 constant expressions are folded on the host (one rounded f32 op each, as on device);
-//   * a Transpose read only by matmuls is folded into their operand flags; a Transpose of a
+// Fusions made here. Those marked (=) leave the arithmetic of every element unchanged; the others
+// change only the order in which a sum's terms are added (deterministic, tolerance class):
+//   * (=) rank-0 constant expressions are folded on the host (one rounded f32 op each, as on device);
+//   * (=) a Transpose read only by matmuls is folded into their operand flags; a Transpose of a
 //     matmul's result swaps and flips the matmul's operands instead (same products, same order);
-//   * the three attention gradient ops of one attention share one statistics pass;
-//   * LayerNormGradGamma and the SumRows of the same adjoint (the beta gradient) are one launch;
-//   * the SGD / AdamW update subgraph of every parameter is one multi-tensor launch, in place;
-//   * nodes no output depends on (the ungathered head beside a masked-row gather) are not run.
+//   * (=) add_rows(matmul(x, w), b): the bias is added in the matmul's epilogue;
+//   * (=) up to four matmuls of one shape and storage form whose operands exist (the Q, K, V
+//     projections of a layer, their input gradients, their weight gradients) are one launch;
+//   * (=) residual + dropout(x) followed by the layer norm of the sum is one launch;
+//   * (=) a chain of Adds that only the gradients of one layer norm read is added as that launch
+//     loads its adjoint;
+//   * (=) other + embedding_grad(...): the scatter adds `other` as it writes;
+//   * the attention forward keeps its probabilities for the backward of the same attention, and
+//     the three attention gradient ops are one launch group;
+//   * cross_entropy and cross_entropy_grad of the same logits are one launch;
+//   * LayerNormGradX, LayerNormGradGamma and the SumRows of the same adjoint are one launch;
+//   * column sums, layer-norm parameter gradients and split-k weight gradients that only the
+//     optimizer reads leave chunk partials; one launch per step adds them all, and the first
+//     stages of the small column sums share one launch too;
+//   * (=) the SGD / AdamW update subgraph of every parameter is one multi-tensor launch, in place;
+//   * (=) nodes no output depends on (the ungathered head beside a masked-row gather) are not run.
+// A matrix whose width is not a multiple of 4 floats and that only pitch-aware kernels touch is
+// stored with padded rows (Slot::pitch).
 #pragma once
 
 #include <functional>

@@ -14,6 +14,9 @@ uint32_t sum_rows_chunks(uint64_t rows);
 
 namespace {
 
+#ifndef MSX_LN_BACKWARD_BLOCKS
+#define MSX_LN_BACKWARD_BLOCKS 444
+#endif
 constexpr float kLayerNormEps = 1e-12f;
 constexpr int kWarpsPerBlock = 8;
 
@@ -566,7 +569,9 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
 }
 
 uint32_t backward_chunks(uint64_t rows) {
-    uint64_t per = (rows + 147) / 148;
+    // Three blocks per SM: a warp walks its rows one after another, each row a chain of loads and
+    // three warp reductions, so it is the number of warps in flight that hides that latency.
+    uint64_t per = (rows + MSX_LN_BACKWARD_BLOCKS - 1) / MSX_LN_BACKWARD_BLOCKS;
     if (per < 8) per = 8;
     uint64_t chunks = (rows + per - 1) / per;
     return static_cast<uint32_t>(chunks < 1 ? 1 : chunks);
