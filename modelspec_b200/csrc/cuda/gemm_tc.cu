@@ -87,6 +87,7 @@ template <int BM, int BN> struct Config {
 };
 
 constexpr int MAX_GROUP = 4;  // products of one shape that one launch can carry
+constexpr int MAX_JOBS = 24;  // products of different shapes that one launch can carry
 
 struct TcArgs {
     // Per product of the group (grid.z = product * splits + split when not batched):
@@ -105,6 +106,15 @@ struct TcArgs {
     uint32_t batch_inner;
     uint64_t a_outer, a_inner, b_outer, b_inner, c_outer, c_inner;
     uint32_t* status;
+    // Products of different shapes in one launch (one storage form, one tile width): a 1-D grid
+    // whose block b belongs to the job whose block range holds it; `job_count` = 0 otherwise.
+    uint32_t job_count;
+    struct Job {
+        const float* a;
+        const float* b;
+        float* c;  // C, or the job's split-K workspace
+        uint32_t m, n, k, lda, ldb, ldc, splits, first_block;
+    } jobs[MAX_JOBS];
 };
 
 #ifdef MSX_TC_TRACE
@@ -243,21 +253,38 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) TRACE(0);
-    const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    const uint32_t kblocks_total = (args.k + BK - 1) / BK;
+    // The problem this CTA works on: the launch's own, or one job of a launch that carries several.
+    uint32_t pm = args.m, pn = args.n, pk = args.k, plda = args.lda, pldb = args.ldb, pldc = args.ldc, psplits = args.splits;
+    uint32_t tile_x = blockIdx.x, tile_y = blockIdx.y, tile_z = blockIdx.z;
+    const float* job_a = nullptr;
+    const float* job_b = nullptr;
+    float* job_c = nullptr;
+    if (args.job_count) {
+        uint32_t j = 0;
+        while (j + 1 < args.job_count && args.jobs[j + 1].first_block <= blockIdx.x) ++j;
+        const TcArgs::Job& job = args.jobs[j];
+        pm = job.m; pn = job.n; pk = job.k; plda = job.lda; pldb = job.ldb; pldc = job.ldc; psplits = job.splits;
+        job_a = job.a; job_b = job.b; job_c = job.c;
+        const uint32_t local = blockIdx.x - job.first_block, across = (pn + BN - 1) / BN, down = (pm + BM - 1) / BM;
+        tile_x = local % across;
+        tile_y = (local / across) % down;
+        tile_z = local / (across * down);
+    }
+    const uint32_t m0 = tile_y * BM, n0 = tile_x * BN;
+    const uint32_t kblocks_total = (pk + BK - 1) / BK;
     const bool batched = args.batch_inner != 0;
-    const uint32_t z_outer = batched ? blockIdx.z / args.batch_inner : 0, z_inner = batched ? blockIdx.z % args.batch_inner : 0;
-    const uint32_t product = batched ? 0 : blockIdx.z / args.splits, split = batched ? 0 : blockIdx.z % args.splits;
+    const uint32_t z_outer = batched ? tile_z / args.batch_inner : 0, z_inner = batched ? tile_z % args.batch_inner : 0;
+    const uint32_t product = (batched || args.job_count) ? 0 : tile_z / psplits, split = batched ? 0 : tile_z % psplits;
     // A split k is dealt out block by block: split s takes k blocks s, s + splits, ... The CTAs of
     // the splits of one tile run side by side, so at any time they read neighbouring 128-byte
     // pieces of the same operand rows (one DRAM page) instead of pieces a whole k range apart.
-    const uint32_t stride = batched ? 1u : args.splits;
+    const uint32_t stride = batched ? 1u : psplits;
     const uint32_t kblocks = kblocks_total > split ? (kblocks_total - split + stride - 1) / stride : 0;
 
     // ---- loaders, first part: where this thread's chunks sit, and the first loads. They are issued
     // before the barriers and the tensor memory are set up, so that the set-up hides under them.
-    const float* __restrict__ a = args.a[product] + z_outer * args.a_outer + z_inner * args.a_inner;
-    const float* __restrict__ b = args.b[product] + z_outer * args.b_outer + z_inner * args.b_inner;
+    const float* __restrict__ a = job_a ? job_a : args.a[product] + z_outer * args.a_outer + z_inner * args.a_inner;
+    const float* __restrict__ b = job_b ? job_b : args.b[product] + z_outer * args.b_outer + z_inner * args.b_inner;
     constexpr int A_CHUNKS = BM * BK / 4 / LOADER_THREADS, B_CHUNKS = BN * BK / 4 / LOADER_THREADS;
     // Where this thread's chunks sit in a block does not depend on the block: the shared-memory
     // offsets, the address of each chunk in the first k block and whether all four of its elements
@@ -287,25 +314,25 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
         uint32_t row, col;
         a_place(i, &row, &col);
         aoff[i] = A_T ? mn_major_offset(row, col / 4) : k_major_offset(row, col / 4);
-        a_at[i] = A_T ? a + static_cast<uint64_t>(first_k + row) * args.lda + m0 + col
-                      : a + static_cast<uint64_t>(m0 + row) * args.lda + first_k + col;
-        a_whole[i] = args.a_vec && (A_T ? m0 + col + 4 <= args.m : m0 + row < args.m);
+        a_at[i] = A_T ? a + static_cast<uint64_t>(first_k + row) * plda + m0 + col
+                      : a + static_cast<uint64_t>(m0 + row) * plda + first_k + col;
+        a_whole[i] = args.a_vec && (A_T ? m0 + col + 4 <= pm : m0 + row < pm);
     }
 #pragma unroll
     for (int i = 0; i < B_CHUNKS; ++i) {
         uint32_t row, col;
         b_place(i, &row, &col);
         boff[i] = B_T ? k_major_offset(row, col / 4) : mn_major_offset(row, col / 4);
-        b_at[i] = B_T ? b + static_cast<uint64_t>(n0 + row) * args.ldb + first_k + col
-                      : b + static_cast<uint64_t>(first_k + row) * args.ldb + n0 + col;
-        b_whole[i] = args.b_vec && (B_T ? n0 + row < args.n : n0 + col + 4 <= args.n);
+        b_at[i] = B_T ? b + static_cast<uint64_t>(n0 + row) * pldb + first_k + col
+                      : b + static_cast<uint64_t>(first_k + row) * pldb + n0 + col;
+        b_whole[i] = args.b_vec && (B_T ? n0 + row < pn : n0 + col + 4 <= pn);
     }
     // Elements from one k block of this CTA to its next.
-    const uint64_t a_step = static_cast<uint64_t>(BK) * stride * (A_T ? args.lda : 1u);
-    const uint64_t b_step = static_cast<uint64_t>(BK) * stride * (B_T ? 1u : args.ldb);
+    const uint64_t a_step = static_cast<uint64_t>(BK) * stride * (A_T ? plda : 1u);
+    const uint64_t b_step = static_cast<uint64_t>(BK) * stride * (B_T ? 1u : pldb);
     auto fetch = [&](uint32_t kb, float4 (&av)[A_CHUNKS], float4 (&bv)[B_CHUNKS]) {
         const uint32_t k0 = (kb * stride + split) * BK;
-        const bool inside = k0 + BK <= args.k;
+        const bool inside = k0 + BK <= pk;
 #pragma unroll
         for (int i = 0; i < A_CHUNKS; ++i) {
             if (inside && a_whole[i]) {
@@ -316,12 +343,12 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
             a_place(i, &row, &col);
             if (A_T) {  // stored [k, m]: 4 consecutive m of one k row
                 uint32_t gk = k0 + row, gm = m0 + col;
-                uint32_t valid = gk < args.k ? in_range(gm, args.m) : 0u;
-                av[i] = load4(a, static_cast<uint64_t>(gk) * args.lda + gm, valid, args.a_vec);
+                uint32_t valid = gk < pk ? in_range(gm, pm) : 0u;
+                av[i] = load4(a, static_cast<uint64_t>(gk) * plda + gm, valid, args.a_vec);
             } else {    // stored [m, k]: 4 consecutive k of one row
                 uint32_t gm = m0 + row, gk = k0 + col;
-                uint32_t valid = gm < args.m ? in_range(gk, args.k) : 0u;
-                av[i] = load4(a, static_cast<uint64_t>(gm) * args.lda + gk, valid, args.a_vec);
+                uint32_t valid = gm < pm ? in_range(gk, pk) : 0u;
+                av[i] = load4(a, static_cast<uint64_t>(gm) * plda + gk, valid, args.a_vec);
             }
         }
 #pragma unroll
@@ -334,12 +361,12 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
             b_place(i, &row, &col);
             if (B_T) {  // stored [n, k]
                 uint32_t gn = n0 + row, gk = k0 + col;
-                uint32_t valid = gn < args.n ? in_range(gk, args.k) : 0u;
-                bv[i] = load4(b, static_cast<uint64_t>(gn) * args.ldb + gk, valid, args.b_vec);
+                uint32_t valid = gn < pn ? in_range(gk, pk) : 0u;
+                bv[i] = load4(b, static_cast<uint64_t>(gn) * pldb + gk, valid, args.b_vec);
             } else {    // stored [k, n]
                 uint32_t gk = k0 + row, gn = n0 + col;
-                uint32_t valid = gk < args.k ? in_range(gn, args.n) : 0u;
-                bv[i] = load4(b, static_cast<uint64_t>(gk) * args.ldb + gn, valid, args.b_vec);
+                uint32_t valid = gk < pk ? in_range(gn, pn) : 0u;
+                bv[i] = load4(b, static_cast<uint64_t>(gk) * pldb + gn, valid, args.b_vec);
             }
         }
     };
@@ -447,14 +474,14 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
         loaders_barrier(LOADER_THREADS);
         if (tid == 0) TRACE(13);
         float* __restrict__ out = batched ? args.c[0] + z_outer * args.c_outer + z_inner * args.c_inner
-                                          : args.c[product] + static_cast<uint64_t>(split) * args.m * args.ldc;
-        const float* __restrict__ bias_row = args.bias[product];
+                                          : (job_c ? job_c : args.c[product]) + static_cast<uint64_t>(split) * pm * pldc;
+        const float* __restrict__ bias_row = job_c ? nullptr : args.bias[product];
         constexpr uint32_t LANES_PER_ROW = BN / 4, ROWS_PER_PASS = 32 / LANES_PER_ROW;
         const uint32_t c4 = (lane % LANES_PER_ROW) * 4, gn = n0 + c4;
 #pragma unroll 4
         for (uint32_t r = warp * ROWS_PER_PASS + lane / LANES_PER_ROW; r < BM; r += 8 * ROWS_PER_PASS) {
             const uint32_t gm = m0 + r;
-            if (gm >= args.m || gn >= args.n) continue;
+            if (gm >= pm || gn >= pn) continue;
             const float4 h = *reinterpret_cast<const float4*>(tile_hi + r * PITCH + c4);
             const float4 l = WIDE ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(tile_lo + r * PITCH + c4);
             // `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
@@ -462,16 +489,16 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
             if (bias_row) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
-                    if (gn + q < args.n) v[q] = v[q] + bias_row[gn + q];
+                    if (gn + q < pn) v[q] = v[q] + bias_row[gn + q];
             }
-            float* dst = out + static_cast<uint64_t>(gm) * args.ldc + gn;
+            float* dst = out + static_cast<uint64_t>(gm) * pldc + gn;
             // Inside the pitch a whole float4 may be written: what lies past n is padding.
-            if (args.c_vec && (gn + 4 <= args.n || (args.c_padded && gn + 4 <= args.ldc))) {
+            if (args.c_vec && (gn + 4 <= pn || (args.c_padded && gn + 4 <= pldc))) {
                 *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
             } else {
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
-                    if (gn + q < args.n) dst[q] = v[q];
+                    if (gn + q < pn) dst[q] = v[q];
             }
         }
     } else {
@@ -684,6 +711,54 @@ void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_
                uint64_t k, float* workspace, uint32_t* status, const float* bias, bool leave_partials) {
     MatmulOperands one = {a, b, c, bias, workspace};
     matmul_tc_group(s, &one, 1, a_t, b_t, m, n, k, status, leave_partials);
+}
+
+// One job of matmul_tc_jobs: 64 x 64 tiles, k split so that a CTA gets about 8 k blocks (the jobs
+// of a launch fill the device together, so a job does not have to on its own).
+MatmulTcPlan matmul_tc_job_plan(uint64_t m, uint64_t n, uint64_t k) {
+    const uint64_t kblocks = (k + BK - 1) / BK;
+    uint64_t splits = kblocks / 8;
+    if (splits < 1) splits = 1;
+    if (splits > 32) splits = 32;
+    MatmulTcPlan p = {};
+    p.bm = 64;
+    p.bn = 64;
+    p.kblocks_per_split = static_cast<uint32_t>((kblocks + splits - 1) / splits);
+    p.splits = static_cast<uint32_t>(kblocks == 0 ? 1 : (kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split);
+    p.workspace_floats = p.splits > 1 ? p.splits * m * n : 0;
+    return p;
+}
+
+void matmul_tc_jobs(cudaStream_t s, const MatmulJob* jobs, uint32_t count, bool a_t, bool b_t, uint32_t* status) {
+    if (count == 0) return;
+    if (count > MAX_JOBS) throw std::invalid_argument("matmul_tc_jobs: more jobs than one launch carries");
+    TcArgs args = {};
+    args.splits = 1;
+    args.a_vec = args.b_vec = args.c_vec = 1;
+    args.status = status;
+    uint32_t blocks = 0;
+    for (uint32_t j = 0; j < count; ++j) {
+        const MatmulJob& job = jobs[j];
+        if (job.m == 0 || job.n == 0) throw std::invalid_argument("matmul_tc_jobs: an empty product");
+        const MatmulTcPlan p = matmul_tc_job_plan(job.m, job.n, job.k);
+        TcArgs::Job& to = args.jobs[args.job_count++];
+        to.a = job.a;
+        to.b = job.b;
+        to.c = p.splits > 1 ? job.workspace : job.c;
+        to.m = static_cast<uint32_t>(job.m);
+        to.n = static_cast<uint32_t>(job.n);
+        to.k = static_cast<uint32_t>(job.k);
+        to.lda = static_cast<uint32_t>(a_t ? job.m : job.k);
+        to.ldb = static_cast<uint32_t>(b_t ? job.k : job.n);
+        to.ldc = to.n;
+        to.splits = p.splits;
+        to.first_block = blocks;
+        blocks += static_cast<uint32_t>(((job.m + 63) / 64) * ((job.n + 63) / 64)) * p.splits;
+        args.a_vec = args.a_vec && aligned16(job.a) && to.lda % 4 == 0;
+        args.b_vec = args.b_vec && aligned16(job.b) && to.ldb % 4 == 0;
+        args.c_vec = args.c_vec && aligned16(to.c) && to.ldc % 4 == 0;
+    }
+    launch_tile(s, args, dim3(blocks), 64, 64, a_t, b_t);
 }
 
 void matmul_tc_batched(cudaStream_t s, const BatchedOperand& a, const BatchedOperand& b, const BatchedOperand& c, uint64_t m,

@@ -197,6 +197,21 @@ struct MatmulPitches {
 void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t count, bool a_t, bool b_t, uint64_t m, uint64_t n,
                      uint64_t k, uint32_t* status, bool leave_partials = false, MatmulPitches pitches = {});
 
+// Products of different shapes, one storage form, in one launch (the weight gradients of a step,
+// which only the optimizer reads and which would each fill a fraction of the device for a few
+// microseconds). A job whose k is split (matmul_tc_job_plan(m, n, k).splits > 1) leaves its partial
+// tiles in `workspace`, [split][m][n], for finalize_sums; otherwise it writes `c`.
+struct MatmulJob {
+    const float* a;
+    const float* b;
+    float* c;
+    float* workspace;  // matmul_tc_job_plan(m, n, k).workspace_floats floats, or null when that is 0
+    uint64_t m, n, k;
+};
+constexpr uint32_t kMatmulJobs = 24;  // jobs one launch carries
+MatmulTcPlan matmul_tc_job_plan(uint64_t m, uint64_t n, uint64_t k);
+void matmul_tc_jobs(cudaStream_t s, const MatmulJob* jobs, uint32_t count, bool a_t, bool b_t, uint32_t* status);
+
 // outer x inner independent products through one launch (grid.z = problem): matrix z of an
 // operand starts at base + (z / inner) * stride_outer + (z % inner) * stride_inner elements and
 // has `pitch` elements between rows as stored; `transposed` as in matmul (A stored [k, m], B

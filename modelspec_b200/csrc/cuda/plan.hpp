@@ -14,7 +14,10 @@
 //     matmul's result swaps and flips the matmul's operands instead (same products, same order);
 //   * (=) add_rows(matmul(x, w), b): the bias is added in the matmul's epilogue;
 //   * (=) up to four matmuls of one shape and storage form whose operands exist (the Q, K, V
-//     projections of a layer, their input gradients, their weight gradients) are one launch;
+//     projections of a layer, their input gradients) are one launch;
+//   * gradient-tagged matmuls whose result only the optimizer reads (weight gradients) wait for
+//     the end of the backward pass and run as jobs of one launch per storage form (their k split
+//     left as partial tiles for the finalize launch);
 //   * (=) residual + dropout(x) followed by the layer norm of the sum is one launch;
 //   * (=) a chain of Adds that only the gradients of one layer norm read is added as that launch
 //     loads its adjoint;

@@ -92,7 +92,7 @@ static NcclApi g_nccl;
 // A contiguous run of gradient bytes that is summed across ranks by one all-reduce, issued on
 // the side stream as soon as the launch that writes its last gradient has been enqueued.
 #ifndef MSX_DEFAULT_FUSIONS
-#define MSX_DEFAULT_FUSIONS 3u
+#define MSX_DEFAULT_FUSIONS 7u
 #endif
 
 struct Bucket {
@@ -223,7 +223,8 @@ void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream
 // The scheduler.
 
 // Tuning switch: MSX_FUSE is a bit mask of optional fusions (default: all). 1 sublayer tails
-// (dropout + residual + layer norm), 2 adjoint sums inside layer-norm backward.
+// (dropout + residual + layer norm), 2 adjoint sums inside layer-norm backward, 4 weight-gradient
+// matmuls as jobs of one launch.
 inline uint32_t fusion_mask() {
     static const uint32_t mask = [] {
         const char* text = std::getenv("MSX_FUSE");
@@ -270,12 +271,50 @@ struct Scheduler {
     };
     std::vector<DeferredRows> deferred_rows;
     static constexpr uint64_t kDeferredRowsBytes = 16ull << 20;
+    // Matmuls whose result only the optimizer reads (weight gradients) wait too: each would be a
+    // launch of a few dozen CTAs for a few microseconds; together, as jobs of one launch per
+    // storage form, they fill the device. Their operands stay alive until then, so the total is
+    // capped.
+    struct DeferredMatmul {
+        uint32_t a, b, result;
+        int workspace;
+        uint64_t m, n, k;
+    };
+    std::vector<DeferredMatmul> deferred_matmuls[4];  // by storage form: 2 * a_t + b_t
+    uint64_t deferred_matmul_bytes = 0;
+    static constexpr uint64_t kDeferredMatmulBytes = 2ull << 30;
     bool deferrable(uint32_t at) const {
         for (uint32_t u : users[at])
             if (node(u).tag != msx::Tag::Optimizer || !handled[u]) return false;
         return true;
     }
     void emit_finalize() {
+        for (int form = 0; form < 4; ++form) {
+            const std::vector<DeferredMatmul>& all = deferred_matmuls[form];
+            for (size_t begin = 0; begin < all.size(); begin += k::kMatmulJobs) {
+                const std::vector<DeferredMatmul> part(all.begin() + begin, all.begin() + std::min(all.size(), begin + k::kMatmulJobs));
+                std::vector<uint32_t> reads, writes;
+                uint64_t flop = 0;
+                for (const DeferredMatmul& d : part) {
+                    reads.push_back(d.a);
+                    reads.push_back(d.b);
+                    writes.push_back(d.workspace >= 0 ? static_cast<uint32_t>(d.workspace) : d.result);
+                    flop += 2 * d.m * d.n * d.k;
+                }
+                Node pseudo;
+                pseudo.id = node(part[0].result).id;
+                msx_plan* plan = P;
+                const bool a_t = (form & 2) != 0, b_t = (form & 1) != 0;
+                Launch& l = emit("matmul_jobs", pseudo, reads, writes, [=](cudaStream_t s) {
+                    std::vector<k::MatmulJob> jobs;
+                    for (const DeferredMatmul& d : part)
+                        jobs.push_back({plan->f(d.a), plan->f(d.b), plan->f(d.result),
+                                        d.workspace >= 0 ? plan->f(static_cast<uint32_t>(d.workspace)) : nullptr, d.m, d.n, d.k});
+                    k::matmul_tc_jobs(s, jobs.data(), static_cast<uint32_t>(jobs.size()), a_t, b_t, plan->d_status);
+                });
+                l.flop = flop;
+            }
+        }
         if (!deferred_rows.empty()) {
             std::vector<uint32_t> reads, writes;
             uint32_t blocks = 0;
@@ -718,6 +757,26 @@ struct Scheduler {
                 uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(in[0]);
                 std::vector<Product> group = {claim_product(at)};
                 const bool pitched = pitch_of(group[0].a) || pitch_of(group[0].b) || pitchable(group[0].result);
+                if ((fusion_mask() & 4u) && !(P->flags & MSX_PLAN_EXACT_MATMUL) && !pitched && group[0].bias < 0 &&
+                    nd.tag == msx::Tag::Gradient && deferrable(group[0].result)) {
+                    const uint64_t operand_bytes = (m * kk + kk * n) * 4;
+                    if (deferred_matmul_bytes + operand_bytes <= kDeferredMatmulBytes) {
+                        deferred_matmul_bytes += operand_bytes;
+                        const Product& p = group[0];
+                        const k::MatmulTcPlan job = k::matmul_tc_job_plan(m, n, kk);
+                        int ws = -1;
+                        if (job.workspace_floats) {
+                            ws = static_cast<int>(scratch(job.workspace_floats * 4));
+                            deferred.push_back({static_cast<uint32_t>(ws), 0, job.splits, m * n, p.result});
+                        }
+                        uint32_t a = p.a, b = p.b;
+                        const int form = (P->transposed(a) ? 2 : 0) + (P->transposed(b) ? 1 : 0);
+                        while (P->slots[a].kind == Slot::View) a = P->slots[a].index;
+                        while (P->slots[b].kind == Slot::View) b = P->slots[b].index;
+                        deferred_matmuls[form].push_back({a, b, p.result, ws, m, n, kk});
+                        break;
+                    }
+                }
                 // Later matmuls of the same shape and storage form whose operands already exist
                 // (the three projections of an attention layer, their gradients) join the launch.
                 if (!(P->flags & MSX_PLAN_EXACT_MATMUL) && !pitched)

@@ -34,9 +34,12 @@ class ProgramText:
     def input(self, name, dtype, shape):
         return self.node(tensor(dtype, shape), 'Input "%s"' % name)
 
-    def op(self, name, shape, operands, attr="", dtype="f32"):
+    def op(self, name, shape, operands, attr="", dtype="f32", tag=""):
         rest = name + (" " + attr if attr else "") + " " + ", ".join("%%%d" % o for o in operands)
-        return self.node(tensor(dtype, shape), rest)
+        at = self.node(tensor(dtype, shape), rest)
+        if tag:  # a training program's subgraph tag: "forward", "loss", "gradient", "optimizer"
+            self.lines[-1] = tag + " " + self.lines[-1]
+        return at
 
     def output(self, value):
         self.outputs.append("output %%%d" % value)

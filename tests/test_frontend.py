@@ -80,8 +80,8 @@ def test_bad_source_is_refused_with_a_message():
 def test_bert_tiny_step_schedule():
     """What the backend launches for BERT-tiny with the gather: the ungathered head is not run,
     every transpose is folded into a matmul, the three attention gradients share a launch pair,
-    the query/key/value projections of a layer (and their input and weight gradients) share a
-    matmul launch, the tail of a sublayer (dropout, residual add, layer norm) is one launch, the
+    the query/key/value projections of a layer (and their input gradients) share a matmul launch,
+    all weight gradients are jobs of one launch at the end of the backward pass, the tail of a sublayer (dropout, residual add, layer norm) is one launch, the
     sums of the projections' input gradients are formed inside the layer-norm backward that reads
     them, the bias gradients share one first-stage launch, the second stages of every column sum
     and split-k weight gradient are one launch, and the 41 AdamW updates are one launch."""
@@ -90,10 +90,13 @@ def test_bert_tiny_step_schedule():
     assert kernels.count("adamw_multi_tensor") == 1 and kernels[-1] == "adamw_multi_tensor"
     assert "transpose" not in kernels
     assert kernels.count("attention_forward") == 2 and kernels.count("attention_backward") == 2
-    # 42 products: 6 groups of 3 (2 layers x {projections, input gradients, weight gradients}) + 24.
-    assert kernels.count("matmul") == 30
+    # 42 products: 13 weight gradients as jobs of one launch, 4 groups of 3 (2 layers x
+    # {projections, input gradients}) and 17 launches of one product.
+    assert kernels.count("matmul") == 21 and kernels.count("matmul_jobs") == 1
     matmuls = [l for l in listing.strip().splitlines() if l.split()[1] == "matmul"]
-    assert sum(1 for l in matmuls if l.split("writes")[1].count("%") + l.split("writes")[1].count("scratch") >= 3) == 6
+    assert sum(1 for l in matmuls if l.split("writes")[1].count("%") + l.split("writes")[1].count("scratch") >= 3) == 4
+    jobs = [l for l in listing.strip().splitlines() if l.split()[1] == "matmul_jobs"][0]
+    assert len(jobs.split("reads")[1].split("writes")[0].split()) == 26
     assert kernels.count("finalize_sums") == 1 and kernels[-2] == "finalize_sums"
     assert "layer_norm_grad_x" not in kernels and kernels.count("layer_norm_backward") == 6
     assert kernels.count("cross_entropy_with_grad") == 1 and "cross_entropy_grad" not in kernels
@@ -103,7 +106,7 @@ def test_bert_tiny_step_schedule():
     backward = [l for l in listing.strip().splitlines() if l.split()[1] == "layer_norm_backward"]
     assert max(len(l.split("reads")[1].split("writes")[0].split()) for l in backward) == 6  # x, four addends, gamma
     assert "[4096, 30522]" not in listing
-    assert len(kernels) < 80
+    assert len(kernels) < 70
     totals = listing.strip().splitlines()[-1]
     arena, unshared = int(totals.split()[1]), int(totals.split()[4])
     assert arena < unshared

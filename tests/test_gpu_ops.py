@@ -123,6 +123,29 @@ def test_a_vocabulary_head_of_odd_width_through_padded_rows(device, rows, h, v):
         assert_kernel_close(gpu, cpu, scale=np.full(cpu.shape, max(1.0, float(np.abs(cpu).max()))), what=what)
 
 
+def test_weight_gradients_of_different_shapes_share_one_launch(device):
+    """Matmuls tagged `gradient` whose results nothing on the device reads (weight gradients) are
+    jobs of one launch: different shapes, tails in every dimension, split and unsplit k, the partial
+    tiles added by the finalize launch."""
+    r = rng(41)
+    shapes = [(4096, 128, 128), (4096, 128, 512), (1000, 100, 40), (300, 70, 130), (64, 33, 20), (8200, 64, 64)]
+    p = ProgramText()
+    feed, outs, refs = {}, [], []
+    for j, (k, m, n) in enumerate(shapes):
+        x = p.input("x%d" % j, "f32", [k, m]); g = p.input("g%d" % j, "f32", [k, n])
+        xt = p.op("Transpose", [m, k], [x], tag="gradient")
+        w = p.op("MatMul", [m, n], [xt, g], tag="gradient")
+        feed["x%d" % j] = values(r, k, m); feed["g%d" % j] = values(r, k, n)
+        outs.append((w, m * n)); p.output(w)
+        refs.append(np.abs(feed["x%d" % j].T.astype(np.float64)) @ np.abs(feed["g%d" % j].astype(np.float64)))
+    listing = M.schedule_describe(p.text())
+    kernels = [l.split()[1] for l in listing.strip().splitlines()[:-1]]
+    assert kernels.count("matmul_jobs") == 1 and "matmul" not in kernels and kernels[-1] == "finalize_sums"
+    res = run_both(device, p.text(), feed, outputs=outs, flags=M.PLAN_NO_GRAPH)
+    for (cpu, gpu), terms, shape in zip(res, refs, shapes):
+        assert_kernel_close(gpu, cpu, scale=terms.reshape(-1), what="weight gradient k, m, n = %r" % (shape,))
+
+
 def test_transposed_matmul_result_is_the_swapped_matmul(device):
     """Transpose(MatMul(A^T, G)) is scheduled as one matmul with its operands swapped."""
     r = rng(5)
