@@ -31,6 +31,9 @@
 //     stages of the small column sums share one launch too;
 //   * (=) the SGD / AdamW update subgraph of every parameter is one multi-tensor launch, in place;
 //   * (=) nodes no output depends on (the ungathered head beside a masked-row gather) are not run.
+// A heavy launch whose result is first read many launches later (the weight gradient of the tied
+// table, the 30,522-wide bias gradient) runs on a side stream beside the small launches between
+// it and its first reader; what it reads and writes stays allocated until that reader.
 // A matrix whose width is not a multiple of 4 floats and that only pitch-aware kernels touch is
 // stored with padded rows (Slot::pitch).
 #pragma once
@@ -68,6 +71,9 @@ struct Launch {
     uint32_t value = 0;                  // id of the node this launch is scheduled for
     std::vector<uint32_t> reads, writes; // slot positions (nodes first, then scratch slots)
     uint64_t flop = 0;
+    // >= 0: the launch runs on the plan's side stream from its place in the list, beside the
+    // launches that follow it, and the launch with this index is the first to wait for it.
+    int join_before = -1;
     std::function<void(cudaStream_t)> run;
 };
 

@@ -92,7 +92,7 @@ static NcclApi g_nccl;
 // A contiguous run of gradient bytes that is summed across ranks by one all-reduce, issued on
 // the side stream as soon as the launch that writes its last gradient has been enqueued.
 #ifndef MSX_DEFAULT_FUSIONS
-#define MSX_DEFAULT_FUSIONS 7u
+#define MSX_DEFAULT_FUSIONS 15u
 #endif
 
 struct Bucket {
@@ -153,6 +153,8 @@ struct msx_plan {
     uint32_t* counter(uint32_t index) const { return d_counters + index; }
     void* d_update_tables = nullptr;
     void* d_sum_jobs = nullptr;  // k::SumJob table of the deferred second stages
+    cudaStream_t side_stream = nullptr;              // launches with join_before >= 0 run here
+    std::vector<cudaEvent_t> side_fork, side_done;   // per launch (null for launches on the main stream)
     void* d_row_sum_jobs = nullptr;  // k::RowSumJob table of the column sums that share one launch
 
     int loss_pos = -1;
@@ -224,7 +226,7 @@ void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream
 
 // Tuning switch: MSX_FUSE is a bit mask of optional fusions (default: all). 1 sublayer tails
 // (dropout + residual + layer norm), 2 adjoint sums inside layer-norm backward, 4 weight-gradient
-// matmuls as jobs of one launch.
+// matmuls as jobs of one launch, 8 heavy launches with late readers on a side stream.
 inline uint32_t fusion_mask() {
     static const uint32_t mask = [] {
         const char* text = std::getenv("MSX_FUSE");
@@ -346,6 +348,34 @@ struct Scheduler {
              [=](cudaStream_t s) { k::finalize_sums(s, static_cast<const k::SumJob*>(plan->d_sum_jobs), jobs, blocks); });
     }
 
+    // A matmul or column-sum launch whose results are first read at least `kSideGap` launches
+    // later does not have to hold up the launches in between: it goes to the side stream.
+    static constexpr int kSideGap = 6;
+    void mark_side_launches() {
+        if (!(fusion_mask() & 8u)) return;
+        const int count = static_cast<int>(P->launches.size());
+        for (int l = 0; l < count; ++l) {
+            Launch& launch = P->launches[static_cast<size_t>(l)];
+            if (launch.kernel != "matmul" && launch.kernel != "sum_rows") continue;
+            bool eligible = !launch.writes.empty();
+            for (uint32_t w : launch.writes) {
+                const Slot& slot = P->slots[w];
+                if (slot.kind != Slot::Arena) eligible = false;
+                if (w < prog.nodes.size())
+                    for (const msx::Output& o : prog.outputs)
+                        if (pos(o.value) == w) eligible = false;  // an output: read by the host or a bucket, not by a launch
+            }
+            if (!eligible) continue;
+            int first_reader = count;
+            for (int later = l + 1; later < count; ++later)
+                for (uint32_t r : P->launches[static_cast<size_t>(later)].reads)
+                    for (uint32_t w : launch.writes)
+                        if (r == w) first_reader = std::min(first_reader, later);
+            if (first_reader == count || first_reader - l < kSideGap) continue;
+            launch.join_before = first_reader;
+        }
+    }
+
     uint32_t counters(uint64_t n) {
         uint32_t base = P->counters_used;
         P->counters_used += static_cast<uint32_t>(n);
@@ -402,6 +432,7 @@ struct Scheduler {
             if (live[at] && !handled[at]) schedule(at);
         emit_finalize();
         emit_optimizer();
+        mark_side_launches();
         for (const msx::Output& o : prog.outputs) {
             Slot& s = P->slots[pos(o.value)];
             s.keep = true;
@@ -1512,6 +1543,14 @@ void place_arena(msx_plan* P) {
                 slots[r].last = std::max(slots[r].last, static_cast<int>(l));
             }
     }
+    // A launch on the side stream may still be running until the launch that waits for it: what it
+    // reads and writes stays allocated until then.
+    for (const Launch& launch : P->launches) {
+        if (launch.join_before < 0) continue;
+        for (const std::vector<uint32_t>* touched : {&launch.reads, &launch.writes})
+            for (uint32_t t : *touched)
+                if (slots[t].kind == Slot::Arena) slots[t].last = std::max(slots[t].last, launch.join_before);
+    }
     // Gradients live side by side, in the order the step produces them, so that a bucket of
     // consecutive gradients is one contiguous all-reduce.
     std::vector<char> is_gradient(slots.size(), 0);
@@ -1635,6 +1674,14 @@ void allocate(msx_plan* P, const Scheduler& sched) {
     cuda_ok(cudaMemset(P->d_counters, 0, counter_bytes), "cudaMemset(counters)");
     cuda_ok(cudaEventCreate(&P->clock_start), "cudaEventCreate");
     cuda_ok(cudaEventCreate(&P->clock_stop), "cudaEventCreate");
+    P->side_fork.assign(P->launches.size(), nullptr);
+    P->side_done.assign(P->launches.size(), nullptr);
+    for (size_t l = 0; l < P->launches.size(); ++l) {
+        if (P->launches[l].join_before < 0) continue;
+        if (!P->side_stream) cuda_ok(cudaStreamCreateWithFlags(&P->side_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        cuda_ok(cudaEventCreateWithFlags(&P->side_fork[l], cudaEventDisableTiming), "cudaEventCreate");
+        cuda_ok(cudaEventCreateWithFlags(&P->side_done[l], cudaEventDisableTiming), "cudaEventCreate");
+    }
     if (!sched.deferred_rows.empty()) {
         std::vector<k::RowSumJob> jobs;
         uint32_t first_block = 0;
@@ -1710,6 +1757,14 @@ void release(msx_plan* P) {
     cudaFree(P->d_counters);
     cudaFree(P->d_update_tables);
     cudaFree(P->d_sum_jobs);
+    if (P->side_stream) {
+        cudaStreamSynchronize(P->side_stream);
+        cudaStreamDestroy(P->side_stream);
+    }
+    for (cudaEvent_t e : P->side_fork)
+        if (e) cudaEventDestroy(e);
+    for (cudaEvent_t e : P->side_done)
+        if (e) cudaEventDestroy(e);
     cudaFree(P->d_row_sum_jobs);
     for (int s = 0; s < kStagingSlots; ++s) {
         if (P->pinned[s]) cudaFreeHost(P->pinned[s]);
@@ -1753,12 +1808,26 @@ void join_loss(msx_plan* P) {
 
 void enqueue_all(msx_plan* P) {
     begin_side_work(P);
+    std::vector<char> joined(P->launches.size(), 0);
     for (size_t l = 0; l < P->launches.size(); ++l) {
+        // Side launches that this launch is the first to read: wait for them.
+        for (size_t earlier = 0; earlier < l; ++earlier)
+            if (P->launches[earlier].join_before == static_cast<int>(l) && P->side_done[earlier] && !joined[earlier]) {
+                cuda_ok(cudaStreamWaitEvent(P->stream, P->side_done[earlier], 0), "cudaStreamWaitEvent");
+                joined[earlier] = 1;
+            }
         if (P->comm && static_cast<int>(l) == P->optimizer_launch) {
             for (Bucket& b : P->buckets) cuda_ok(cudaStreamWaitEvent(P->stream, b.done, 0), "cudaStreamWaitEvent");
             join_loss(P);
         }
-        P->launches[l].run(P->stream);
+        if (P->launches[l].join_before >= 0 && P->side_stream && P->side_fork[l]) {
+            cuda_ok(cudaEventRecord(P->side_fork[l], P->stream), "cudaEventRecord");
+            cuda_ok(cudaStreamWaitEvent(P->side_stream, P->side_fork[l], 0), "cudaStreamWaitEvent");
+            P->launches[l].run(P->side_stream);
+            cuda_ok(cudaEventRecord(P->side_done[l], P->side_stream), "cudaEventRecord");
+        } else {
+            P->launches[l].run(P->stream);
+        }
         if (!P->comm) continue;
         for (Bucket& b : P->buckets) {
             if (b.after_launch != static_cast<int>(l)) continue;
@@ -2212,6 +2281,7 @@ uint64_t msx_plan_describe(const msx_plan* plan, char* out, uint64_t capacity) {
         text += " writes";
         for (uint32_t w : launch.writes) text += " " + name(w);
         if (launch.flop) text += " flop " + std::to_string(launch.flop);
+        if (launch.join_before >= 0) text += " beside " + std::to_string(launch.join_before);
         text += "\n";
     }
     if (out && capacity) {
