@@ -281,16 +281,18 @@ uint64_t embedding_grad_scratch_ints(uint64_t n, uint64_t rows) {
     return 2 * n;
 }
 
-void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* out, uint64_t n,
-                    uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status, const float* base) {
+void embedding_order(cudaStream_t s, const int32_t* ids, uint64_t n, uint64_t rows, int32_t* scratch, uint32_t* status) {
+    if (n == 0 || rows == 0) return;
+    order_kernel<<<static_cast<uint32_t>((n + 31) / 32), 256, 0, s>>>(ids, static_cast<uint32_t>(n), static_cast<uint32_t>(rows), scratch,
+                                                                      scratch + n, status);
+    check_launch("embedding_order");
+}
+
+void embedding_scatter(cudaStream_t s, const float* g, float* out, uint64_t n, uint64_t rows, uint64_t h, const int32_t* scratch,
+                       const float* base) {
     if (rows == 0 || h == 0) return;
-    int32_t* sorted_id = scratch;
-    int32_t* sorted_n = scratch + n;
-    if (n > 0) {
-        order_kernel<<<static_cast<uint32_t>((n + 31) / 32), 256, 0, s>>>(ids, static_cast<uint32_t>(n), static_cast<uint32_t>(rows), sorted_id,
-                                                                          sorted_n, status);
-        check_launch("embedding_grad");
-    }
+    const int32_t* sorted_id = scratch;
+    const int32_t* sorted_n = scratch + n;
     auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
     const bool vec = h % 4 == 0 && aligned(g) && aligned(out) && aligned(base);
     const uint64_t span = vec ? 128 : 32;
@@ -299,6 +301,12 @@ void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* o
     if (vec) scatter_kernel<4><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
     else scatter_kernel<1><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
     check_launch("embedding_grad");
+}
+
+void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* out, uint64_t n,
+                    uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status, const float* base) {
+    embedding_order(s, ids, n, rows, scratch, status);
+    embedding_scatter(s, g, out, n, rows, h, scratch, base);
 }
 
 }  // namespace k

@@ -151,6 +151,11 @@ void embedding(cudaStream_t s, const float* table, const int32_t* ids, float* ou
 uint64_t embedding_grad_scratch_ints(uint64_t n, uint64_t rows);
 void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* out, uint64_t n,
                     uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status, const float* base = nullptr);
+// Its two halves: the order of the occurrences depends on the ids alone and can be computed as
+// soon as they are on the device (beside the forward pass); the scatter needs g.
+void embedding_order(cudaStream_t s, const int32_t* ids, uint64_t n, uint64_t rows, int32_t* scratch, uint32_t* status);
+void embedding_scatter(cudaStream_t s, const float* g, float* out, uint64_t n, uint64_t rows, uint64_t h, const int32_t* scratch,
+                       const float* base = nullptr);
 
 // ---- matmul (gemm.cu) -------------------------------------------------------------------------
 // C[m, n] = op(A) x op(B) (+ bias[n]) with each element one ascending-k fused chain starting

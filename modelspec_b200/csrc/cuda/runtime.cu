@@ -290,6 +290,23 @@ struct Scheduler {
             if (node(u).tag != msx::Tag::Optimizer || !handled[u]) return false;
         return true;
     }
+    // Moves the launch just emitted up to right after the last launch that writes something it
+    // reads: it only feeds the finalize launch, so from there on it can run beside the rest of
+    // the backward pass (mark_side_launches puts it on the side stream).
+    void hoist_last_launch() {
+        if (!(fusion_mask() & 8u) || P->launches.size() < 2) return;
+        const size_t last = P->launches.size() - 1;
+        size_t earliest = 0;
+        for (size_t l = 0; l < last; ++l)
+            for (uint32_t w : P->launches[l].writes)
+                for (uint32_t r : P->launches[last].reads)
+                    if (r == w) earliest = l + 1;
+        if (earliest >= last) return;
+        Launch moved = std::move(P->launches[last]);
+        P->launches.pop_back();
+        P->launches.insert(P->launches.begin() + static_cast<std::ptrdiff_t>(earliest), std::move(moved));
+    }
+
     void emit_finalize() {
         for (int form = 0; form < 4; ++form) {
             const std::vector<DeferredMatmul>& all = deferred_matmuls[form];
@@ -310,11 +327,12 @@ struct Scheduler {
                 Launch& l = emit("matmul_jobs", pseudo, reads, writes, [=](cudaStream_t s) {
                     std::vector<k::MatmulJob> jobs;
                     for (const DeferredMatmul& d : part)
-                        jobs.push_back({plan->f(d.a), plan->f(d.b), plan->f(d.result),
-                                        d.workspace >= 0 ? plan->f(static_cast<uint32_t>(d.workspace)) : nullptr, d.m, d.n, d.k});
+                        jobs.push_back({plan->f(d.a), plan->f(d.b), plan->f(static_cast<uint32_t>(d.workspace)),
+                                        plan->f(static_cast<uint32_t>(d.workspace)), d.m, d.n, d.k});
                     k::matmul_tc_jobs(s, jobs.data(), static_cast<uint32_t>(jobs.size()), a_t, b_t, plan->d_status);
                 });
                 l.flop = flop;
+                hoist_last_launch();
             }
         }
         if (!deferred_rows.empty()) {
@@ -331,6 +349,7 @@ struct Scheduler {
             const uint32_t jobs = static_cast<uint32_t>(deferred_rows.size());
             emit("sum_rows_batched", pseudo, reads, writes,
                  [=](cudaStream_t s) { k::sum_rows_batched(s, static_cast<const k::RowSumJob*>(plan->d_row_sum_jobs), jobs, blocks); });
+            hoist_last_launch();
         }
         if (deferred.empty()) return;
         std::vector<uint32_t> reads, writes;
@@ -356,7 +375,9 @@ struct Scheduler {
         const int count = static_cast<int>(P->launches.size());
         for (int l = 0; l < count; ++l) {
             Launch& launch = P->launches[static_cast<size_t>(l)];
-            if (launch.kernel != "matmul" && launch.kernel != "sum_rows") continue;
+            if (launch.kernel != "matmul" && launch.kernel != "sum_rows" && launch.kernel != "embedding_order" &&
+                launch.kernel != "matmul_jobs" && launch.kernel != "sum_rows_batched")
+                continue;
             bool eligible = !launch.writes.empty();
             for (uint32_t w : launch.writes) {
                 const Slot& slot = P->slots[w];
@@ -795,11 +816,10 @@ struct Scheduler {
                         deferred_matmul_bytes += operand_bytes;
                         const Product& p = group[0];
                         const k::MatmulTcPlan job = k::matmul_tc_job_plan(m, n, kk);
-                        int ws = -1;
-                        if (job.workspace_floats) {
-                            ws = static_cast<int>(scratch(job.workspace_floats * 4));
-                            deferred.push_back({static_cast<uint32_t>(ws), 0, job.splits, m * n, p.result});
-                        }
+                        // An unsplit job writes one "partial" tile too: the launch then touches no
+                        // output, only scratch that the finalize launch reads, and may run beside others.
+                        const int ws = static_cast<int>(scratch(std::max<uint64_t>(job.workspace_floats, m * n) * 4));
+                        deferred.push_back({static_cast<uint32_t>(ws), 0, job.splits, m * n, p.result});
                         uint32_t a = p.a, b = p.b;
                         const int form = (P->transposed(a) ? 2 : 0) + (P->transposed(b) ? 1 : 0);
                         while (P->slots[a].kind == Slot::View) a = P->slots[a].index;
@@ -858,12 +878,27 @@ struct Scheduler {
                 emit("embedding", nd, in, {at}, [=](cudaStream_t s) {
                     k::embedding(s, plan->f(table), plan->i(ids), plan->f(at), n, rows, h, plan->d_status);
                 });
+                // The gradient of this lookup sorts the same ids: that half of it needs nothing
+                // else, so it is issued here (and runs beside the forward pass).
+                if ((fusion_mask() & 8u) && P->slots[ids].kind == Slot::Input && !orders.count({ids, rows}))
+                    for (uint32_t u : users[ids]) {
+                        const Node& grad = node(u);
+                        if (grad.op != Op::EmbeddingGrad || handled[u] || pos(grad.operands[0]) != ids || grad.rows != rows) continue;
+                        uint32_t tmp = scratch(k::embedding_grad_scratch_ints(n, rows) * 4);
+                        orders[{ids, rows}] = tmp;
+                        emit("embedding_order", nd, {ids}, {tmp}, [=](cudaStream_t s) {
+                            k::embedding_order(s, plan->i(ids), n, rows, plan->i(tmp), plan->d_status);
+                        });
+                        break;
+                    }
                 break;
             }
             case Op::EmbeddingGrad: {
                 uint32_t ids = in[0], g = in[1];
                 uint64_t n = rows_of(ids), rows = nd.rows, h = cols_of(g);
-                uint32_t tmp = scratch(k::embedding_grad_scratch_ints(n, rows) * 4);
+                auto ordered = orders.find({ids, rows});
+                const bool have_order = ordered != orders.end();
+                uint32_t tmp = have_order ? ordered->second : scratch(k::embedding_grad_scratch_ints(n, rows) * 4);
                 // other + embedding_grad(...) with nothing else reading the scatter (a tied weight's
                 // dense gradient plus its lookup gradient): the scatter adds `other` as it writes.
                 bool is_output = false;
@@ -879,17 +914,27 @@ struct Scheduler {
                             Slot& sum = P->slots[u];
                             sum.kind = Slot::Arena;
                             sum.bytes = std::max<uint64_t>(add.ty.count() * 4, 4);
-                            emit("embedding_grad", nd, {ids, g, other}, {u, tmp}, [=](cudaStream_t s) {
-                                k::embedding_grad(s, plan->i(ids), plan->f(g), plan->f(u), n, rows, h, plan->i(tmp), plan->d_status,
-                                                  plan->f(other));
-                            });
+                            if (have_order)
+                                emit("embedding_grad", nd, {g, other, tmp}, {u}, [=](cudaStream_t s) {
+                                    k::embedding_scatter(s, plan->f(g), plan->f(u), n, rows, h, plan->i(tmp), plan->f(other));
+                                });
+                            else
+                                emit("embedding_grad", nd, {ids, g, other}, {u, tmp}, [=](cudaStream_t s) {
+                                    k::embedding_grad(s, plan->i(ids), plan->f(g), plan->f(u), n, rows, h, plan->i(tmp), plan->d_status,
+                                                      plan->f(other));
+                                });
                             break;
                         }
                     }
                 }
-                emit("embedding_grad", nd, in, {at, tmp}, [=](cudaStream_t s) {
-                    k::embedding_grad(s, plan->i(ids), plan->f(g), plan->f(at), n, rows, h, plan->i(tmp), plan->d_status);
-                });
+                if (have_order)
+                    emit("embedding_grad", nd, {g, tmp}, {at}, [=](cudaStream_t s) {
+                        k::embedding_scatter(s, plan->f(g), plan->f(at), n, rows, h, plan->i(tmp));
+                    });
+                else
+                    emit("embedding_grad", nd, in, {at, tmp}, [=](cudaStream_t s) {
+                        k::embedding_grad(s, plan->i(ids), plan->f(g), plan->f(at), n, rows, h, plan->i(tmp), plan->d_status);
+                    });
                 break;
             }
             case Op::AddRows: {
@@ -1381,6 +1426,7 @@ struct Scheduler {
     }
 
     std::map<std::array<uint32_t, 5>, uint32_t> forward_probabilities;  // (q, k, v, mask, heads) -> scratch slot
+    std::map<std::pair<uint32_t, uint64_t>, uint32_t> orders;           // (ids, table rows) -> scratch slot of the sorted occurrences
 
     void schedule_attention(uint32_t at) {
         const Node& nd = node(at);
