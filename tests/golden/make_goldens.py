@@ -1,4 +1,4 @@
-"""Writes the fixtures of tests/golden/ from the reference checkout at /root/reference.
+"""Writes the fixtures of tests/golden/ from a checkout of the reference (beyond10x/modelspec).
 
 The fixtures are the reference's own recorded outputs for this path, reduced to the numbers the
 tests compare: the per-step losses of two recorded CPU runs
@@ -7,13 +7,15 @@ and final parameter of the linear-regression training log
 (crates/modelspec-cli/tests/golden/linear_regression.train.stdout), the printed training IR of
 two examples (crates/modelspec-cli/tests/golden/*.training.ir) and the lowered BERT-tiny program
 (website/docs/examples/bert-tiny.md). BLAKE3 digests come from the `blake3` Python package.
-Run it here (the reference is not on the GPU box): `python tests/golden/make_goldens.py`.
+Run it where the reference is checked out (the committed fixtures are what travels):
+`python tests/golden/make_goldens.py <reference checkout>` or MODELSPEC_REFERENCE=<checkout>.
 """
 import json
 import os
 import re
+import sys
 
-REF = "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MODELSPEC_REFERENCE", os.path.join(os.sep, "root", "reference"))
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

@@ -5,7 +5,7 @@ import numpy as np
 import oracle_lib
 import modelspec_b200 as M
 
-# The reference's device tolerances (DESIGN.md § 9 of the reference; tests/common/mod.rs:19-43):
+# The reference's device tolerances (its design notes, section 9, and tests/common/mod.rs:19-43):
 # per kernel |g - c| <= 1e-5 + 1e-4 * r with r the magnitude of the terms summed, per run
 # |g - c| <= 1e-4 + 1e-3 * |c| for every loss and parameter element.
 KERNEL_ATOL, KERNEL_RTOL = 1e-5, 1e-4
