@@ -285,6 +285,7 @@ struct Scheduler {
     std::vector<DeferredMatmul> deferred_matmuls[4];  // by storage form: 2 * a_t + b_t
     uint64_t deferred_matmul_bytes = 0;
     static constexpr uint64_t kDeferredMatmulBytes = 2ull << 30;
+    static constexpr uint64_t kDeferredMatmulFlop = 2ull << 30;
     bool deferrable(uint32_t at) const {
         for (uint32_t u : users[at])
             if (node(u).tag != msx::Tag::Optimizer || !handled[u]) return false;
@@ -812,7 +813,9 @@ struct Scheduler {
                 if ((fusion_mask() & 4u) && !(P->flags & MSX_PLAN_EXACT_MATMUL) && !pitched && group[0].bias < 0 &&
                     nd.tag == msx::Tag::Gradient && deferrable(group[0].result)) {
                     const uint64_t operand_bytes = (m * kk + kk * n) * 4;
-                    if (deferred_matmul_bytes + operand_bytes <= kDeferredMatmulBytes) {
+                    // Only products too small to fill the device on their own: a large one is better
+                    // off with the tile the plan model picks for it.
+                    if (2 * m * n * kk <= kDeferredMatmulFlop && deferred_matmul_bytes + operand_bytes <= kDeferredMatmulBytes) {
                         deferred_matmul_bytes += operand_bytes;
                         const Product& p = group[0];
                         const k::MatmulTcPlan job = k::matmul_tc_job_plan(m, n, kk);
