@@ -415,17 +415,20 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
     if (r >= rows) return;
     const uint32_t id_lo = static_cast<uint32_t>(token[0]), id_hi = static_cast<uint32_t>(token[1]);
     const uint64_t base = static_cast<uint64_t>(r) * h;
-    float v[ITEMS];
+    // The loads first, unconditional and from a clamped column, so that all are in flight before
+    // the Philox rounds of the first element start.
+    float v[ITEMS], xs[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) xs[i] = __ldg(x + base + min(i * 32 + lane, h - 1));
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) v[i] = __ldg(residual + base + min(i * 32 + lane, h - 1));
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const uint32_t c = i * 32 + lane;
-        v[i] = 0.0f;
-        if (c < h) {
-            const uint32_t w0 = philox_word0(static_cast<uint32_t>(index_base + base + c), 4u, id_lo, id_hi, seed_lo, seed_hi);
-            const float dropped = w0 >= threshold ? x[base + c] * scale : 0.0f;
-            v[i] = residual[base + c] + dropped;
-            sum_out[base + c] = v[i];
-        }
+        const uint32_t w0 = philox_word0(static_cast<uint32_t>(index_base + base + c), 4u, id_lo, id_hi, seed_lo, seed_hi);
+        const float dropped = w0 >= threshold ? xs[i] * scale : 0.0f;
+        v[i] = c < h ? v[i] + dropped : 0.0f;
+        if (c < h) sum_out[base + c] = v[i];
     }
     const float width = static_cast<float>(h);
     float sum = 0.0f;
@@ -475,19 +478,30 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
         gam[i] = (dx != nullptr && c < h) ? gamma[c] : 0.0f;
     }
     for (uint32_t r = r0 + warp; r < r1; r += 8) {
-        const float* xr = x + static_cast<uint64_t>(r) * h;
-        const float* gr = g + static_cast<uint64_t>(r) * h;
+        // All loads of an array are issued before any is used: unconditional, from a clamped
+        // column (what a column past h reads is discarded below), one array after another. A load
+        // under a condition of its own would wait for the one before it.
+        const uint64_t row_at = static_cast<uint64_t>(r) * h;
         float xv[ITEMS], gv[ITEMS];
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) {
-            uint32_t c = i * 32 + lane;
-            xv[i] = c < h ? xr[c] : 0.0f;
-            gv[i] = c < h ? gr[c] : 0.0f;
-            // The adjoint as a sum the program spells as a chain of Adds: ((g + g1) + g2) + g3.
-            if (g1 != nullptr && c < h) gv[i] = gv[i] + g1[static_cast<uint64_t>(r) * h + c];
-            if (g2 != nullptr && c < h) gv[i] = gv[i] + g2[static_cast<uint64_t>(r) * h + c];
-            if (g3 != nullptr && c < h) gv[i] = gv[i] + g3[static_cast<uint64_t>(r) * h + c];
+        for (int i = 0; i < ITEMS; ++i) xv[i] = __ldg(x + row_at + min(i * 32 + lane, h - 1));
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) gv[i] = __ldg(g + row_at + min(i * 32 + lane, h - 1));
+        // The adjoint as a sum the program spells as a chain of Adds: ((g + g1) + g2) + g3.
+        for (const float* more : {g1, g2, g3}) {
+            if (more == nullptr) continue;
+            float t[ITEMS];
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) t[i] = __ldg(more + row_at + min(i * 32 + lane, h - 1));
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) gv[i] = gv[i] + t[i];
         }
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i)
+            if (i * 32 + lane >= h) {
+                xv[i] = 0.0f;
+                gv[i] = 0.0f;
+            }
         float sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i)
