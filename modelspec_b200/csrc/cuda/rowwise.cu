@@ -316,23 +316,22 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
     } else {
         const float* row = logits + static_cast<uint64_t>(r) * ld;
         if (VEC == 4) {
+            // Unconditional loads from a clamped column (the pitch covers the whole float4 of the
+            // last valid column), so that all eight are in flight together; what lies past v is
+            // replaced afterwards.
+            const uint32_t last = (v - 1) & ~3u;
 #pragma unroll
             for (int i = 0; i < kWideItems; i += 4) {
-                const uint32_t c = column_of(i, tid);
-                float4 f = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-                if (c < v) f = __ldg(reinterpret_cast<const float4*>(row + c));  // the pitch covers the whole float4
-                x[i] = f.x;
-                x[i + 1] = c + 1 < v ? f.y : -INFINITY;
-                x[i + 2] = c + 2 < v ? f.z : -INFINITY;
-                x[i + 3] = c + 3 < v ? f.w : -INFINITY;
+                const float4 f = __ldg(reinterpret_cast<const float4*>(row + min(column_of(i, tid), last)));
+                x[i] = f.x; x[i + 1] = f.y; x[i + 2] = f.z; x[i + 3] = f.w;
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < kWideItems; ++i) {
-                const uint32_t c = column_of(i, tid);
-                x[i] = c < v ? __ldg(row + c) : -INFINITY;
-            }
+            for (int i = 0; i < kWideItems; ++i) x[i] = __ldg(row + min(column_of(i, tid), v - 1));
         }
+#pragma unroll
+        for (int i = 0; i < kWideItems; ++i)
+            if (column_of(i, tid) >= v) x[i] = -INFINITY;
         float m = -INFINITY;
 #pragma unroll
         for (int i = 0; i < kWideItems; ++i)
