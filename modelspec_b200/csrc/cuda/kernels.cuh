@@ -106,9 +106,21 @@ uint32_t layer_norm_backward_chunks(uint64_t rows);
 uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h);
 // g1, g2, g3, when not null, are further addends of the adjoint: the kernel reads ((g + g1) + g2) + g3
 // where the program has a chain of Adds that nothing else reads.
+// A dropout draw for `dropout`'s element numbering: element i of the matrix is kept iff word 0 of
+// its Philox block is at least `threshold`, and is then multiplied by `scale`.
+struct DropoutDraw {
+    const int32_t* token = nullptr;
+    uint64_t seed = 0;
+    uint32_t threshold = 0;
+    float scale = 1.0f;
+    uint64_t index_base = 0;
+};
+// `adjoint_draw`, when not null: the adjoint is dropout_grad of that sum. `dx_draw` and `dx_dropped`,
+// when not null: dropout_grad of dx is written to dx_dropped beside dx.
 void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
                          uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const float* g1 = nullptr,
-                         const float* g2 = nullptr, const float* g3 = nullptr);
+                         const float* g2 = nullptr, const float* g3 = nullptr, const DropoutDraw* adjoint_draw = nullptr,
+                         const DropoutDraw* dx_draw = nullptr, float* dx_dropped = nullptr);
 // sum_out = residual + dropout(x), out = layer_norm(sum_out, gamma, beta), rows of up to 1,024
 // elements (layer_norm_backward_supported(h)); the dropout draw is that of `dropout`.
 void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residual, const int32_t* token, uint64_t seed,

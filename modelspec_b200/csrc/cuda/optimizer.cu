@@ -28,15 +28,49 @@ __global__ void __launch_bounds__(256) adamw_kernel(const UpdateTensor* __restri
     uint64_t start = static_cast<uint64_t>(chunk_start[blockIdx.x]) * kUpdateChunk;
     uint64_t stop = start + kUpdateChunk < t.count ? start + kUpdateChunk : t.count;
     float lr = lr_t[0], k1 = c1[0], k2 = c2[0];
-    for (uint64_t i = start + threadIdx.x; i < stop; i += blockDim.x) {
-        float g = t.g[i], p = t.p[i], m = t.m[i], v = t.v[i];
+    auto update = [&](float g, float& p, float& m, float& v) {
         float m_next = c.beta1 * m + c.rest1 * g;
         float v_next = c.beta2 * v + (c.rest2 * g) * g;
         float direction = (m_next * k1) / (sqrtf(v_next * k2) + c.eps);
         float step = direction + c.weight_decay * p;
-        t.p[i] = p - lr * step;
-        t.m[i] = m_next;
-        t.v[i] = v_next;
+        p = p - lr * step;
+        m = m_next;
+        v = v_next;
+    };
+    const bool aligned = ((reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.m) |
+                           reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
+    if (aligned && stop - start == kUpdateChunk) {
+        // A whole chunk of 16-byte-aligned tensors: four float4 per thread and array, all sixteen
+        // loads issued before the first update.
+        constexpr int kVectors = kUpdateChunk / (256 * 4);
+        float4 g[kVectors], p[kVectors], m[kVectors], v[kVectors];
+#pragma unroll
+        for (int j = 0; j < kVectors; ++j) {
+            const uint64_t i = start + (j * 256 + threadIdx.x) * 4;
+            g[j] = *reinterpret_cast<const float4*>(t.g + i);
+            p[j] = *reinterpret_cast<const float4*>(t.p + i);
+            m[j] = *reinterpret_cast<const float4*>(t.m + i);
+            v[j] = *reinterpret_cast<const float4*>(t.v + i);
+        }
+#pragma unroll
+        for (int j = 0; j < kVectors; ++j) {
+            const uint64_t i = start + (j * 256 + threadIdx.x) * 4;
+            update(g[j].x, p[j].x, m[j].x, v[j].x);
+            update(g[j].y, p[j].y, m[j].y, v[j].y);
+            update(g[j].z, p[j].z, m[j].z, v[j].z);
+            update(g[j].w, p[j].w, m[j].w, v[j].w);
+            *reinterpret_cast<float4*>(t.p + i) = p[j];
+            *reinterpret_cast<float4*>(t.m + i) = m[j];
+            *reinterpret_cast<float4*>(t.v + i) = v[j];
+        }
+        return;
+    }
+    for (uint64_t i = start + threadIdx.x; i < stop; i += blockDim.x) {
+        float g = t.g[i], p = t.p[i], m = t.m[i], v = t.v[i];
+        update(g, p, m, v);
+        t.p[i] = p;
+        t.m[i] = m;
+        t.v[i] = v;
     }
 }
 

@@ -134,18 +134,26 @@ __global__ void sum_rows_stage1_wide(const float* __restrict__ g, uint32_t rows,
     }
 }
 
+// The job whose block range holds this block: the last one whose first block is not past it. Thread
+// t looks at job t, so the whole table costs the block one round trip to memory, not one per job.
+template <class Job>
+__device__ __forceinline__ uint32_t job_of_block(const Job* __restrict__ jobs, uint32_t count, uint32_t* which) {
+    const uint32_t threads = blockDim.x * blockDim.y;
+    for (uint32_t t = threadIdx.y * blockDim.x + threadIdx.x; t < count; t += threads) {
+        const bool begun = jobs[t].first_block <= blockIdx.x;
+        const bool last = t + 1 == count || jobs[t + 1].first_block > blockIdx.x;
+        if (begun && last) *which = t;
+    }
+    __syncthreads();
+    return *which;
+}
+
 // The first stage of many column sums in one launch: block b works on the job whose block range
 // holds it, on one 32-column block and one chunk of rows, exactly as sum_rows_stage1 does.
 __global__ void sum_rows_batched_kernel(const RowSumJob* __restrict__ jobs, uint32_t count) {
     __shared__ float shared[8][32];
     __shared__ uint32_t which;
-    if (threadIdx.x == 0 && threadIdx.y == 0) {
-        uint32_t j = 0;
-        while (j + 1 < count && jobs[j + 1].first_block <= blockIdx.x) ++j;
-        which = j;
-    }
-    __syncthreads();
-    const RowSumJob job = jobs[which];
+    const RowSumJob job = jobs[job_of_block(jobs, count, &which)];
     const uint32_t local = blockIdx.x - job.first_block, column_blocks = (job.width + 31) / 32;
     const uint32_t c = (local % column_blocks) * 32 + threadIdx.x, chunk = local / column_blocks;
     const uint32_t r0 = chunk * job.rows_per_chunk, r1 = min(job.rows, r0 + job.rows_per_chunk);
@@ -183,13 +191,7 @@ __global__ void sum_rows_stage2(const float* __restrict__ partial, uint32_t chun
 __global__ void finalize_sums_kernel(const SumJob* __restrict__ jobs, uint32_t count) {
     __shared__ float shared[8][32];
     __shared__ uint32_t which;
-    if (threadIdx.x == 0 && threadIdx.y == 0) {
-        uint32_t j = 0;
-        while (j + 1 < count && jobs[j + 1].first_block <= blockIdx.x) ++j;
-        which = j;
-    }
-    __syncthreads();
-    const SumJob job = jobs[which];
+    const SumJob job = jobs[job_of_block(jobs, count, &which)];
     const uint32_t block = blockIdx.x - job.first_block;
     if (job.chunks <= 64) {
         // Plain ascending order, one thread per column (what the two-launch forms of sum_rows and

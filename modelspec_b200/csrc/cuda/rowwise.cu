@@ -462,7 +462,8 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
     const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ g, const float* __restrict__ g1,
     const float* __restrict__ g2, const float* __restrict__ g3, float* __restrict__ dx,
     float* __restrict__ partial, uint32_t* __restrict__ counter, float* __restrict__ dgamma, float* __restrict__ dbeta,
-    uint32_t want, uint32_t rows, uint32_t h, uint32_t rows_per_chunk) {
+    uint32_t want, uint32_t rows, uint32_t h, uint32_t rows_per_chunk, DropoutDraw adjoint_draw, DropoutDraw dx_draw,
+    float* __restrict__ dx_dropped) {
     __shared__ float buf[8 * 32 * ITEMS];
     __shared__ bool is_last;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, chunks = gridDim.x;
@@ -494,6 +495,17 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
             for (int i = 0; i < ITEMS; ++i) t[i] = __ldg(more + row_at + min(i * 32 + lane, h - 1));
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) gv[i] = gv[i] + t[i];
+        }
+        // An adjoint that the program passes through dropout_grad first: the draw of element
+        // (r, c), on the sum.
+        if (adjoint_draw.token != nullptr) {
+            const uint32_t id_lo = static_cast<uint32_t>(adjoint_draw.token[0]), id_hi = static_cast<uint32_t>(adjoint_draw.token[1]);
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+                const uint32_t w0 = philox_word0(static_cast<uint32_t>(adjoint_draw.index_base + row_at + i * 32 + lane), 4u, id_lo, id_hi,
+                                                 static_cast<uint32_t>(adjoint_draw.seed), static_cast<uint32_t>(adjoint_draw.seed >> 32));
+                gv[i] = w0 >= adjoint_draw.threshold ? gv[i] * adjoint_draw.scale : 0.0f;
+            }
         }
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i)
@@ -534,7 +546,16 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
                 if (c < h) {
                     float gx = gv[i] * gam[i];
                     float xhat = (xv[i] - mean) * rstd;
-                    o[c] = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
+                    const float value = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
+                    o[c] = value;
+                    // dropout_grad of dx, for the reader that wants it masked (the projection before
+                    // this sublayer's dropout).
+                    if (dx_dropped != nullptr) {
+                        const uint32_t w0 = philox_word0(static_cast<uint32_t>(dx_draw.index_base + row_at + c), 4u,
+                                                         static_cast<uint32_t>(dx_draw.token[0]), static_cast<uint32_t>(dx_draw.token[1]),
+                                                         static_cast<uint32_t>(dx_draw.seed), static_cast<uint32_t>(dx_draw.seed >> 32));
+                        dx_dropped[row_at + c] = w0 >= dx_draw.threshold ? value * dx_draw.scale : 0.0f;
+                    }
                 }
             }
         }
@@ -659,14 +680,17 @@ uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h) { return 
 
 void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
                          uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const float* g1, const float* g2,
-                         const float* g3) {
+                         const float* g3, const DropoutDraw* adjoint_draw, const DropoutDraw* dx_draw, float* dx_dropped) {
     if (h == 0) return;
     uint32_t chunks = backward_chunks(rows);
     uint32_t per = static_cast<uint32_t>((rows + chunks - 1) / chunks);
     uint32_t items = static_cast<uint32_t>((h + 31) / 32);
     uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
     uint32_t want = (dgamma ? 1u : 0u) | (dbeta ? 2u : 0u);
-#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per)
+    const DropoutDraw none = {};
+    const DropoutDraw in_draw = adjoint_draw ? *adjoint_draw : none, out_draw = dx_draw ? *dx_draw : none;
+    if (dx == nullptr || dx_draw == nullptr) dx_dropped = nullptr;
+#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped)
     if (items <= 1) MSX_LN_BACKWARD(1);
     else if (items <= 2) MSX_LN_BACKWARD(2);
     else if (items <= 4) MSX_LN_BACKWARD(4);

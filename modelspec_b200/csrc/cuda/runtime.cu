@@ -92,7 +92,7 @@ static NcclApi g_nccl;
 // A contiguous run of gradient bytes that is summed across ranks by one all-reduce, issued on
 // the side stream as soon as the launch that writes its last gradient has been enqueued.
 #ifndef MSX_DEFAULT_FUSIONS
-#define MSX_DEFAULT_FUSIONS 15u
+#define MSX_DEFAULT_FUSIONS 31u
 #endif
 
 struct Bucket {
@@ -226,7 +226,8 @@ void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream
 
 // Tuning switch: MSX_FUSE is a bit mask of optional fusions (default: all). 1 sublayer tails
 // (dropout + residual + layer norm), 2 adjoint sums inside layer-norm backward, 4 weight-gradient
-// matmuls as jobs of one launch, 8 heavy launches with late readers on a side stream.
+// matmuls as jobs of one launch, 8 heavy launches with late readers on a side stream, 16
+// dropout_grad inside the layer-norm backward that makes or reads its operand.
 inline uint32_t fusion_mask() {
     static const uint32_t mask = [] {
         const char* text = std::getenv("MSX_FUSE");
@@ -370,7 +371,7 @@ struct Scheduler {
 
     // A matmul or column-sum launch whose results are first read at least `kSideGap` launches
     // later does not have to hold up the launches in between: it goes to the side stream.
-    static constexpr int kSideGap = 6;
+    static constexpr int kSideGap = 4;
     void mark_side_launches() {
         if (!(fusion_mask() & 8u)) return;
         const int count = static_cast<int>(P->launches.size());
@@ -1109,6 +1110,12 @@ struct Scheduler {
             case Op::Dropout:
             case Op::DropoutGrad: {
                 uint32_t x = nd.op == Op::Dropout ? in[0] : in[1], token = nd.op == Op::Dropout ? in[1] : in[0];
+                if (nd.op == Op::DropoutGrad && adjoint_draw_joins(at)) {
+                    // Drawn inside the layer-norm backward launch that alone reads it.
+                    adjoint_draws.insert(at);
+                    out.kind = Slot::Dead;
+                    break;
+                }
                 if (nd.ty.count() > (1ull << 32)) unsupported(nd, "a dropout draw addresses at most 2^32 elements");
                 uint32_t threshold = static_cast<uint32_t>(msx::dropout_keep_threshold(nd.p));
                 float scale = 1.0f / (1.0f - nd.p);
@@ -1185,8 +1192,15 @@ struct Scheduler {
         // Either the next Add of the chain ...
         if (users[at].size() == 1 && node(users[at][0]).op == Op::Add)
             return pos(node(users[at][0]).operands[0]) != pos(node(users[at][0]).operands[1]) && joins_layer_norm_adjoint(users[at][0], addends);
+        // ... or the dropout_grad that the same launch applies to the sum as it loads it ...
+        if (users[at].size() == 1 && node(users[at][0]).op == Op::DropoutGrad)
+            return pos(node(users[at][0]).operands[1]) == at && adjoint_draw_joins(users[at][0]);
         // ... or exactly the three gradient ops of one layer norm, which one launch will take.
-        if (!k::layer_norm_backward_supported(nd.ty.shape[1]) || users[at].size() != 3) return false;
+        return feeds_one_layer_norm_backward(at);
+    }
+    bool feeds_one_layer_norm_backward(uint32_t at) const {
+        const Node& nd = node(at);
+        if (nd.ty.rank() != 2 || !k::layer_norm_backward_supported(nd.ty.shape[1]) || users[at].size() != 3) return false;
         int dx = -1, dgamma = -1, dbeta = -1;
         for (uint32_t u : users[at]) {
             const Node& un = node(u);
@@ -1196,6 +1210,20 @@ struct Scheduler {
         }
         if (dx < 0 || dgamma < 0 || dbeta < 0) return false;
         return pos(node(static_cast<uint32_t>(dx)).operands[0]) == pos(node(static_cast<uint32_t>(dgamma)).operands[0]);
+    }
+
+    // A dropout_grad that only the gradients of one layer norm read: the backward launch draws the
+    // mask on the adjoint it loads, and the masked matrix is never stored.
+    std::set<uint32_t> adjoint_draws;
+    bool draw_is_fusable(const Node& nd) const {
+        return (fusion_mask() & 16u) && nd.op == Op::DropoutGrad && nd.ty.rank() == 2 && nd.ty.count() <= (1ull << 32) &&
+               node(pos(nd.operands[0])).op == Op::Input && node(pos(nd.operands[1])).ty.shape == nd.ty.shape;
+    }
+    bool adjoint_draw_joins(uint32_t at) const {
+        if (!draw_is_fusable(node(at))) return false;
+        for (const msx::Output& o : prog.outputs)
+            if (pos(o.value) == at) return false;
+        return feeds_one_layer_norm_backward(at);
     }
 
     // The gradients of one layer_norm (dx, dgamma and, as the column sums of the same adjoint,
@@ -1224,13 +1252,42 @@ struct Scheduler {
             for (uint32_t u : users[g])
                 if (u > at && node(u).op == Op::SumRows && !handled[u]) { dbeta = static_cast<int>(u); break; }
         // An adjoint that is an absorbed chain of Adds is read as its addends.
-        std::vector<uint32_t> adjoint = {g};
-        auto summed = adjoint_sums.find(g);
+        // ... and one that is an absorbed dropout_grad as the operand of that, drawn while loading.
+        struct Draw { int token = -1; uint32_t threshold = 0; float scale = 1.0f; };
+        auto draw_of = [&](uint32_t dropout_grad) {
+            const Node& d = node(dropout_grad);
+            Draw draw;
+            draw.token = static_cast<int>(pos(d.operands[0]));
+            draw.threshold = static_cast<uint32_t>(msx::dropout_keep_threshold(d.p));
+            draw.scale = 1.0f / (1.0f - d.p);
+            return draw;
+        };
+        Draw adjoint_draw, dx_draw;
+        uint32_t source = g;
+        if (adjoint_draws.count(g)) {
+            adjoint_draw = draw_of(g);
+            source = pos(node(g).operands[1]);
+        }
+        std::vector<uint32_t> adjoint = {source};
+        auto summed = adjoint_sums.find(source);
         if (summed != adjoint_sums.end()) adjoint = summed->second;
+        // dropout_grad of dx (the adjoint of the projection under this sublayer's dropout) is a
+        // second output of the launch.
+        int dropped = -1;
+        if (dx >= 0)
+            for (uint32_t u : users[static_cast<uint32_t>(dx)]) {
+                const Node& un = node(u);
+                if (handled[u] || !draw_is_fusable(un) || pos(un.operands[1]) != static_cast<uint32_t>(dx) || adjoint_draw_joins(u)) continue;
+                dropped = static_cast<int>(u);
+                dx_draw = draw_of(u);
+                break;
+            }
         std::vector<uint32_t> reads = {x}, writes;
         reads.insert(reads.end(), adjoint.begin(), adjoint.end());
         if (gamma >= 0) reads.push_back(static_cast<uint32_t>(gamma));
-        for (int other : {dx, dgamma, dbeta}) {
+        if (adjoint_draw.token >= 0) reads.push_back(static_cast<uint32_t>(adjoint_draw.token));
+        if (dx_draw.token >= 0) reads.push_back(static_cast<uint32_t>(dx_draw.token));
+        for (int other : {dx, dropped, dgamma, dbeta}) {
             if (other < 0) continue;
             uint32_t u = static_cast<uint32_t>(other);
             handled[u] = 1;
@@ -1242,31 +1299,46 @@ struct Scheduler {
         uint32_t tmp = scratch(k::layer_norm_backward_scratch_floats(r, h) * 4);
         msx_plan* plan = P;
         auto at_or_null = [plan](int p) -> float* { return p >= 0 ? plan->f(static_cast<uint32_t>(p)) : nullptr; };
+        auto draw_now = [plan, h](const Draw& d) {
+            k::DropoutDraw draw;
+            if (d.token < 0) return draw;
+            draw.token = plan->i(static_cast<uint32_t>(d.token));
+            draw.seed = plan->seed;
+            draw.threshold = d.threshold;
+            draw.scale = d.scale;
+            draw.index_base = plan->shard_rows_before * h;
+            return draw;
+        };
         const bool defer = (dgamma < 0 || deferrable(static_cast<uint32_t>(dgamma))) && (dbeta < 0 || deferrable(static_cast<uint32_t>(dbeta)));
         if (defer) {
             // dx is written here; the column sums stay as chunk sums until the finalize launch.
             std::vector<uint32_t> now;
             if (dx >= 0) now.push_back(static_cast<uint32_t>(dx));
+            if (dropped >= 0) now.push_back(static_cast<uint32_t>(dropped));
             now.push_back(tmp);
             const uint32_t chunks = k::layer_norm_backward_chunks(r);
             if (dgamma >= 0) deferred.push_back({tmp, 0, chunks, h, static_cast<uint32_t>(dgamma)});
             if (dbeta >= 0) deferred.push_back({tmp, static_cast<uint64_t>(chunks) * h, chunks, h, static_cast<uint32_t>(dbeta)});
             float* const wanted = reinterpret_cast<float*>(uintptr_t{1});  // only null or not is read
             emit("layer_norm_backward", nd, reads, now, [=](cudaStream_t s) {
+                const k::DropoutDraw in_draw = draw_now(adjoint_draw), out_draw = draw_now(dx_draw);
                 k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(dx), plan->f(tmp), nullptr,
                                        dgamma >= 0 ? wanted : nullptr, dbeta >= 0 ? wanted : nullptr, r, h,
                                        adjoint.size() > 1 ? plan->f(adjoint[1]) : nullptr, adjoint.size() > 2 ? plan->f(adjoint[2]) : nullptr,
-                                       adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr);
+                                       adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr, in_draw.token ? &in_draw : nullptr,
+                                       out_draw.token ? &out_draw : nullptr, at_or_null(dropped));
             });
             return true;
         }
         uint32_t ctr = counters(1);
         writes.push_back(tmp);
         emit("layer_norm_backward", nd, reads, writes, [=](cudaStream_t s) {
+            const k::DropoutDraw in_draw = draw_now(adjoint_draw), out_draw = draw_now(dx_draw);
             k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(dx), plan->f(tmp), plan->counter(ctr),
                                    at_or_null(dgamma), at_or_null(dbeta), r, h,
                                    adjoint.size() > 1 ? plan->f(adjoint[1]) : nullptr, adjoint.size() > 2 ? plan->f(adjoint[2]) : nullptr,
-                                   adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr);
+                                   adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr, in_draw.token ? &in_draw : nullptr,
+                                   out_draw.token ? &out_draw : nullptr, at_or_null(dropped));
         });
         return true;
     }

@@ -433,6 +433,42 @@ def test_a_sublayer_tail_and_the_summed_adjoint_of_its_layer_norm(device, rows, 
         assert_kernel_close(gpu, cpu, scale=np.full(cpu.shape, max(1.0, float(np.abs(cpu).max()))), what=what)
 
 
+@pytest.mark.parametrize("rows,h", [(64, 128), (37, 96), (130, 768), (9, 33)])
+def test_dropout_gradients_on_either_side_of_a_layer_norm_backward(device, rows, h):
+    """dropout_grad of a sum that only a layer norm's three gradients read is drawn while the
+    backward launch loads the sum, and dropout_grad of the dx it writes is a second output of the
+    same launch: no dropout or add launch is left, the masked dx has exactly the zeros of the
+    separate kernel's (the draw is the same) and the values of dx times the scale."""
+    r = rng(rows * 5 + h)
+    p = ProgramText()
+    x = p.input("x", "f32", [rows, h]); gamma = p.input("gamma", "f32", [h])
+    t_in = p.input("M.forward.dropout#0", "i32", [2]); t_out = p.input("M.forward.dropout#1", "i32", [2])
+    ga = p.input("ga", "f32", [rows, h]); gb = p.input("gb", "f32", [rows, h]); gc = p.input("gc", "f32", [rows, h])
+    s1 = p.op("Add", [rows, h], [ga, gb])
+    s2 = p.op("Add", [rows, h], [s1, gc])
+    g = p.op("DropoutGrad", [rows, h], [t_in, s2], attr="[p = 0.1, site = M.forward.dropout#0]")
+    dx = p.op("LayerNormGradX", [rows, h], [x, gamma, g])
+    dg = p.op("LayerNormGradGamma", [h], [x, g])
+    db = p.op("SumRows", [h], [g])
+    masked = p.op("DropoutGrad", [rows, h], [t_out, dx], attr="[p = 0.25, site = M.forward.dropout#1]")
+    for value in (dx, dg, db, masked):
+        p.output(value)
+    feed = {"x": values(r, rows, h), "gamma": values(r, h) + 1, "M.forward.dropout#0": np.array([5, 0], dtype=np.int32),
+            "M.forward.dropout#1": np.array([-9, 2], dtype=np.int32), "ga": values(r, rows, h), "gb": values(r, rows, h),
+            "gc": values(r, rows, h)}
+    listing = M.schedule_describe(p.text())
+    kernels = [l.split()[1] for l in listing.strip().splitlines()[:-1]]
+    assert kernels == ["layer_norm_backward", "finalize_sums"], listing
+    res = run_both(device, p.text(), feed, outputs=[(dx, rows * h), (dg, h), (db, h), (masked, rows * h)], seed=4242)
+    for (cpu, gpu), what in zip(res[:3], ("dx", "dgamma", "dbeta")):
+        assert_kernel_close(gpu, cpu, scale=np.full(cpu.shape, max(1.0, float(np.abs(cpu).max()))), what=what)
+    cpu_masked, gpu_masked = res[3]
+    gpu_dx = res[0][1]
+    assert np.array_equal(cpu_masked == 0, gpu_masked == 0) or np.array_equal((cpu_masked == 0) | (res[0][0] == 0), (gpu_masked == 0) | (gpu_dx == 0))
+    assert_bits_equal(gpu_masked, np.where(gpu_masked != 0, gpu_dx * np.float32(1.0 / (1.0 - 0.25)), np.float32(0)).astype(np.float32), "masked dx")
+    assert abs((gpu_masked != 0).mean() - 0.75) < 0.08
+
+
 def test_bad_inputs_are_refused_like_the_interpreter_refuses_them(device):
     p = ProgramText()
     table = p.input("table", "f32", [5, 4]); ids = p.input("ids", "i32", [3])
