@@ -126,6 +126,12 @@ void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, con
 void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residual, const int32_t* token, uint64_t seed,
                             uint32_t threshold, float scale, uint64_t index_base, const float* gamma, const float* beta,
                             float* sum_out, float* out, uint64_t rows, uint64_t h);
+// The general form: sum_out = residual + x (x through `x_draw` first when not null); with gamma
+// and beta, out = layer_norm(sum_out) (out may be null when only the next output is wanted) and,
+// with `out_draw`, out_dropped = dropout(out).
+void add_layer_norm(cudaStream_t s, const float* x, const float* residual, const DropoutDraw* x_draw, const float* gamma,
+                    const float* beta, float* sum_out, float* out, const DropoutDraw* out_draw, float* out_dropped, uint64_t rows,
+                    uint64_t h);
 void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t k);
 void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, uint64_t rows, uint64_t k);
 // Row losses max + ln(sum exp(x - max)) - x[label] into row_loss[rows], then

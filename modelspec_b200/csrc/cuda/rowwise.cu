@@ -403,16 +403,17 @@ inline uint32_t warp_row_blocks(uint64_t rows) { return static_cast<uint32_t>((r
 // dropout(x) + residual, then layer_norm of the sum, one warp per row with the row in registers:
 // the three launches of a transformer sublayer's tail as one. Every element goes through the same
 // rounded operations as the separate kernels (the Philox draw of element index_base + r h + c, the
-// scaled or zeroed value, one addition, the layer norm of the stored sum).
+// scaled or zeroed value, one addition, the layer norm of the stored sum). Each part is optional:
+// without a draw on x the sum is x + residual; without gamma the launch ends with the sum; with a
+// draw on the result, dropout of the layer norm is written to out_dropped (and out may be null).
 template <int ITEMS>
 __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
-    const float* __restrict__ x, const float* __restrict__ residual, const int32_t* __restrict__ token, uint32_t seed_lo,
-    uint32_t seed_hi, uint32_t threshold, float scale, uint64_t index_base, const float* __restrict__ gamma,
-    const float* __restrict__ beta, float* __restrict__ sum_out, float* __restrict__ out, uint32_t rows, uint32_t h) {
+    const float* __restrict__ x, const float* __restrict__ residual, DropoutDraw x_draw, const float* __restrict__ gamma,
+    const float* __restrict__ beta, float* __restrict__ sum_out, float* __restrict__ out, DropoutDraw out_draw,
+    float* __restrict__ out_dropped, uint32_t rows, uint32_t h) {
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (r >= rows) return;
-    const uint32_t id_lo = static_cast<uint32_t>(token[0]), id_hi = static_cast<uint32_t>(token[1]);
     const uint64_t base = static_cast<uint64_t>(r) * h;
     // The loads first, unconditional and from a clamped column, so that all are in flight before
     // the Philox rounds of the first element start.
@@ -421,14 +422,22 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
     for (int i = 0; i < ITEMS; ++i) xs[i] = __ldg(x + base + min(i * 32 + lane, h - 1));
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) v[i] = __ldg(residual + base + min(i * 32 + lane, h - 1));
+    if (x_draw.token != nullptr) {
+        const uint32_t id_lo = static_cast<uint32_t>(x_draw.token[0]), id_hi = static_cast<uint32_t>(x_draw.token[1]);
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const uint32_t w0 = philox_word0(static_cast<uint32_t>(x_draw.index_base + base + i * 32 + lane), 4u, id_lo, id_hi,
+                                             static_cast<uint32_t>(x_draw.seed), static_cast<uint32_t>(x_draw.seed >> 32));
+            xs[i] = w0 >= x_draw.threshold ? xs[i] * x_draw.scale : 0.0f;
+        }
+    }
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const uint32_t c = i * 32 + lane;
-        const uint32_t w0 = philox_word0(static_cast<uint32_t>(index_base + base + c), 4u, id_lo, id_hi, seed_lo, seed_hi);
-        const float dropped = w0 >= threshold ? xs[i] * scale : 0.0f;
-        v[i] = c < h ? v[i] + dropped : 0.0f;
+        v[i] = c < h ? v[i] + xs[i] : 0.0f;
         if (c < h) sum_out[base + c] = v[i];
     }
+    if (gamma == nullptr) return;
     const float width = static_cast<float>(h);
     float sum = 0.0f;
 #pragma unroll
@@ -443,10 +452,22 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
             q = fmaf(d, d, q);
         }
     const float rstd = 1.0f / sqrtf(warp_sum(q) / width + kLayerNormEps);
+    uint32_t id_lo = 0, id_hi = 0;
+    if (out_dropped != nullptr) {
+        id_lo = static_cast<uint32_t>(out_draw.token[0]);
+        id_hi = static_cast<uint32_t>(out_draw.token[1]);
+    }
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const uint32_t c = i * 32 + lane;
-        if (c < h) out[base + c] = (v[i] - mean) * rstd * gamma[c] + beta[c];
+        if (c >= h) continue;
+        const float y = (v[i] - mean) * rstd * gamma[c] + beta[c];
+        if (out != nullptr) out[base + c] = y;
+        if (out_dropped != nullptr) {
+            const uint32_t w0 = philox_word0(static_cast<uint32_t>(out_draw.index_base + base + c), 4u, id_lo, id_hi,
+                                             static_cast<uint32_t>(out_draw.seed), static_cast<uint32_t>(out_draw.seed >> 32));
+            out_dropped[base + c] = w0 >= out_draw.threshold ? y * out_draw.scale : 0.0f;
+        }
     }
 }
 
@@ -655,14 +676,16 @@ void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float
     check_launch("layer_norm_grad_gamma");
 }
 
-void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residual, const int32_t* token, uint64_t seed,
-                            uint32_t threshold, float scale, uint64_t index_base, const float* gamma, const float* beta,
-                            float* sum_out, float* out, uint64_t rows, uint64_t h) {
+void add_layer_norm(cudaStream_t s, const float* x, const float* residual, const DropoutDraw* x_draw, const float* gamma,
+                    const float* beta, float* sum_out, float* out, const DropoutDraw* out_draw, float* out_dropped, uint64_t rows,
+                    uint64_t h) {
     if (rows == 0 || h == 0) return;
     const uint32_t items = static_cast<uint32_t>((h + 31) / 32), blocks = static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
-    const uint32_t lo = static_cast<uint32_t>(seed), hi = static_cast<uint32_t>(seed >> 32), r = static_cast<uint32_t>(rows),
-                   hh = static_cast<uint32_t>(h);
-#define MSX_DROPOUT_LN(N) dropout_add_layer_norm_kernel<N><<<blocks, 256, 0, s>>>(x, residual, token, lo, hi, threshold, scale, index_base, gamma, beta, sum_out, out, r, hh)
+    const uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
+    const DropoutDraw none = {};
+    const DropoutDraw first = x_draw ? *x_draw : none, second = out_draw ? *out_draw : none;
+    if (out_draw == nullptr || gamma == nullptr) out_dropped = nullptr;
+#define MSX_DROPOUT_LN(N) dropout_add_layer_norm_kernel<N><<<blocks, 256, 0, s>>>(x, residual, first, gamma, beta, sum_out, out, second, out_dropped, r, hh)
     if (items <= 1) MSX_DROPOUT_LN(1);
     else if (items <= 2) MSX_DROPOUT_LN(2);
     else if (items <= 4) MSX_DROPOUT_LN(4);
@@ -671,7 +694,19 @@ void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residua
     else if (items <= 24) MSX_DROPOUT_LN(24);
     else MSX_DROPOUT_LN(32);
 #undef MSX_DROPOUT_LN
-    check_launch("dropout_add_layer_norm");
+    check_launch("add_layer_norm");
+}
+
+void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residual, const int32_t* token, uint64_t seed,
+                            uint32_t threshold, float scale, uint64_t index_base, const float* gamma, const float* beta,
+                            float* sum_out, float* out, uint64_t rows, uint64_t h) {
+    DropoutDraw draw;
+    draw.token = token;
+    draw.seed = seed;
+    draw.threshold = threshold;
+    draw.scale = scale;
+    draw.index_base = index_base;
+    add_layer_norm(s, x, residual, &draw, gamma, beta, sum_out, out, nullptr, nullptr, rows, h);
 }
 
 bool layer_norm_backward_supported(uint64_t h) { return h >= 1 && h <= 1024; }

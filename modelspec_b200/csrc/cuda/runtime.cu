@@ -775,6 +775,7 @@ struct Scheduler {
                     out.kind = Slot::Dead;
                     break;
                 }
+                if (nd.op == Op::Add && schedule_add_layer_norm(at)) break;
                 k::Binary op = nd.op == Op::Add ? k::Binary::Add : nd.op == Op::Sub ? k::Binary::Sub
                                : nd.op == Op::Mul ? k::Binary::Mul : k::Binary::Div;
                 bool sa = is_scalar_operand(in[0], nd), sb = is_scalar_operand(in[1], nd);
@@ -1155,6 +1156,20 @@ struct Scheduler {
                                 });
                                 break;
                             }
+                            // No layer norm reads the sum: residual + dropout(x) alone is one launch.
+                            handled[add_at] = 1;
+                            out.kind = Slot::Dead;
+                            Slot& slot = P->slots[add_at];
+                            slot.kind = Slot::Arena;
+                            slot.bytes = std::max<uint64_t>(add.ty.count() * 4, 4);
+                            const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
+                            const Draw draw = draw_of(at);
+                            emit("dropout_add", nd, {x, token, residual}, {add_at}, [=](cudaStream_t s) {
+                                const k::DropoutDraw first = launch_draw(plan, draw, h);
+                                k::add_layer_norm(s, plan->f(x), plan->f(residual), &first, nullptr, nullptr, plan->f(add_at), nullptr, nullptr,
+                                                  nullptr, r, h);
+                            });
+                            break;
                         }
                     }
                 }
@@ -1212,6 +1227,88 @@ struct Scheduler {
         return pos(node(static_cast<uint32_t>(dx)).operands[0]) == pos(node(static_cast<uint32_t>(dgamma)).operands[0]);
     }
 
+    // a + b with the layer norm of the sum and, when dropout is all that reads the layer norm, that
+    // dropout: one launch (the embedding sum of an encoder; every residual sum of a forward pass
+    // without dropout). The sum is stored as the separate kernel stores it.
+    bool schedule_add_layer_norm(uint32_t at) {
+        const Node& nd = node(at);
+        if (!(fusion_mask() & 1u) || nd.ty.rank() != 2 || !k::layer_norm_backward_supported(nd.ty.shape[1])) return false;
+        const uint32_t a = pos(nd.operands[0]), b = pos(nd.operands[1]);
+        if (node(a).ty.shape != nd.ty.shape || node(b).ty.shape != nd.ty.shape) return false;
+        auto is_output = [&](uint32_t v) {
+            for (const msx::Output& o : prog.outputs)
+                if (pos(o.value) == v) return true;
+            return false;
+        };
+        int norm = -1;
+        for (uint32_t u : users[at]) {
+            const Node& ln = node(u);
+            if (ln.op == Op::LayerNorm && !handled[u] && pos(ln.operands[0]) == at && pos(ln.operands[1]) < at && pos(ln.operands[2]) < at) {
+                norm = static_cast<int>(u);
+                break;
+            }
+        }
+        if (norm < 0) return false;
+        const uint32_t ln_at = static_cast<uint32_t>(norm);
+        const uint32_t gamma = pos(node(ln_at).operands[1]), beta = pos(node(ln_at).operands[2]);
+        int dropout = -1;
+        if (users[ln_at].size() == 1 && !is_output(ln_at)) {
+            const uint32_t u = users[ln_at][0];
+            const Node& d = node(u);
+            if (d.op == Op::Dropout && !handled[u] && pos(d.operands[0]) == ln_at && node(pos(d.operands[1])).op == Op::Input &&
+                d.ty.shape == nd.ty.shape && d.ty.count() <= (1ull << 32))
+                dropout = static_cast<int>(u);
+        }
+        std::vector<uint32_t> reads = {a, b, gamma, beta}, writes = {at};
+        Draw draw;
+        handled[ln_at] = 1;
+        if (dropout >= 0) {
+            draw = draw_of(static_cast<uint32_t>(dropout));
+            handled[static_cast<uint32_t>(dropout)] = 1;
+            P->slots[ln_at].kind = Slot::Dead;
+            reads.push_back(static_cast<uint32_t>(draw.token));
+            writes.push_back(static_cast<uint32_t>(dropout));
+        } else {
+            writes.push_back(ln_at);
+        }
+        for (uint32_t made : writes) {
+            Slot& slot = P->slots[made];
+            slot.kind = Slot::Arena;
+            slot.bytes = std::max<uint64_t>(node(made).ty.count() * 4, 4);
+        }
+        msx_plan* plan = P;
+        const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
+        emit(dropout >= 0 ? "add_layer_norm_dropout" : "add_layer_norm", nd, reads, writes, [=](cudaStream_t s) {
+            const k::DropoutDraw second = launch_draw(plan, draw, h);
+            k::add_layer_norm(s, plan->f(a), plan->f(b), nullptr, plan->f(gamma), plan->f(beta), plan->f(at),
+                              dropout >= 0 ? nullptr : plan->f(ln_at), dropout >= 0 ? &second : nullptr,
+                              dropout >= 0 ? plan->f(static_cast<uint32_t>(dropout)) : nullptr, r, h);
+        });
+        return true;
+    }
+
+    // The draw of a Dropout or DropoutGrad node as a fused launch takes it: the token's position
+    // now, its address, the seed and the shard's first element when the launch is issued.
+    struct Draw { int token = -1; uint32_t threshold = 0; float scale = 1.0f; };
+    Draw draw_of(uint32_t dropout) const {
+        const Node& d = node(dropout);
+        Draw draw;
+        draw.token = static_cast<int>(pos(d.operands[d.op == Op::Dropout ? 1 : 0]));
+        draw.threshold = static_cast<uint32_t>(msx::dropout_keep_threshold(d.p));
+        draw.scale = 1.0f / (1.0f - d.p);
+        return draw;
+    }
+    static k::DropoutDraw launch_draw(msx_plan* plan, const Draw& d, uint64_t row_width) {
+        k::DropoutDraw draw;
+        if (d.token < 0) return draw;
+        draw.token = plan->i(static_cast<uint32_t>(d.token));
+        draw.seed = plan->seed;
+        draw.threshold = d.threshold;
+        draw.scale = d.scale;
+        draw.index_base = plan->shard_rows_before * row_width;
+        return draw;
+    }
+
     // A dropout_grad that only the gradients of one layer norm read: the backward launch draws the
     // mask on the adjoint it loads, and the masked matrix is never stored.
     std::set<uint32_t> adjoint_draws;
@@ -1253,15 +1350,6 @@ struct Scheduler {
                 if (u > at && node(u).op == Op::SumRows && !handled[u]) { dbeta = static_cast<int>(u); break; }
         // An adjoint that is an absorbed chain of Adds is read as its addends.
         // ... and one that is an absorbed dropout_grad as the operand of that, drawn while loading.
-        struct Draw { int token = -1; uint32_t threshold = 0; float scale = 1.0f; };
-        auto draw_of = [&](uint32_t dropout_grad) {
-            const Node& d = node(dropout_grad);
-            Draw draw;
-            draw.token = static_cast<int>(pos(d.operands[0]));
-            draw.threshold = static_cast<uint32_t>(msx::dropout_keep_threshold(d.p));
-            draw.scale = 1.0f / (1.0f - d.p);
-            return draw;
-        };
         Draw adjoint_draw, dx_draw;
         uint32_t source = g;
         if (adjoint_draws.count(g)) {
@@ -1299,16 +1387,7 @@ struct Scheduler {
         uint32_t tmp = scratch(k::layer_norm_backward_scratch_floats(r, h) * 4);
         msx_plan* plan = P;
         auto at_or_null = [plan](int p) -> float* { return p >= 0 ? plan->f(static_cast<uint32_t>(p)) : nullptr; };
-        auto draw_now = [plan, h](const Draw& d) {
-            k::DropoutDraw draw;
-            if (d.token < 0) return draw;
-            draw.token = plan->i(static_cast<uint32_t>(d.token));
-            draw.seed = plan->seed;
-            draw.threshold = d.threshold;
-            draw.scale = d.scale;
-            draw.index_base = plan->shard_rows_before * h;
-            return draw;
-        };
+        auto draw_now = [plan, h](const Draw& d) { return launch_draw(plan, d, h); };
         const bool defer = (dgamma < 0 || deferrable(static_cast<uint32_t>(dgamma))) && (dbeta < 0 || deferrable(static_cast<uint32_t>(dbeta)));
         if (defer) {
             // dx is written here; the column sums stay as chunk sums until the finalize launch.

@@ -469,6 +469,37 @@ def test_dropout_gradients_on_either_side_of_a_layer_norm_backward(device, rows,
     assert abs((gpu_masked != 0).mean() - 0.75) < 0.08
 
 
+@pytest.mark.parametrize("rows,h", [(64, 128), (37, 96), (130, 768), (9, 33)])
+def test_sums_with_their_layer_norm_and_dropout_in_one_launch(device, rows, h):
+    """a + b with the layer norm of the sum and the dropout that alone reads it (an encoder's
+    embedding sum), a + b with a layer norm that something else reads too, and residual +
+    dropout(x) that no layer norm follows: one launch each, sums and dropout zeros bit for bit."""
+    r = rng(rows * 7 + h)
+    p = ProgramText()
+    a = p.input("a", "f32", [rows, h]); b = p.input("b", "f32", [rows, h]); c = p.input("c", "f32", [rows, h])
+    gamma = p.input("gamma", "f32", [h]); beta = p.input("beta", "f32", [h])
+    t0 = p.input("M.forward.dropout#0", "i32", [2]); t1 = p.input("M.forward.dropout#1", "i32", [2])
+    s1 = p.op("Add", [rows, h], [a, b])
+    n1 = p.op("LayerNorm", [rows, h], [s1, gamma, beta])
+    d1 = p.op("Dropout", [rows, h], [n1, t0], attr="[p = 0.1, site = M.forward.dropout#0]")
+    s2 = p.op("Add", [rows, h], [d1, c])
+    n2 = p.op("LayerNorm", [rows, h], [s2, gamma, beta])
+    d2 = p.op("Dropout", [rows, h], [n2, t1], attr="[p = 0.5, site = M.forward.dropout#1]")
+    s3 = p.op("Add", [rows, h], [s2, d2])
+    for value in (s1, d1, s2, n2, s3):
+        p.output(value)
+    feed = {"a": values(r, rows, h), "b": values(r, rows, h), "c": values(r, rows, h), "gamma": values(r, h) + 1, "beta": values(r, h),
+            "M.forward.dropout#0": np.array([3, 1], dtype=np.int32), "M.forward.dropout#1": np.array([-2, 8], dtype=np.int32)}
+    listing = M.schedule_describe(p.text())
+    kernels = [l.split()[1] for l in listing.strip().splitlines()[:-1]]
+    assert kernels == ["add_layer_norm_dropout", "add_layer_norm", "dropout_add"], listing
+    res = run_both(device, p.text(), feed, outputs=[(s1, rows * h), (d1, rows * h), (s2, rows * h), (n2, rows * h), (s3, rows * h)], seed=31337)
+    assert_bits_equal(res[0][1], res[0][0], "a + b")
+    for (cpu, gpu), what in zip(res[1:], ("dropout of the layer norm", "second sum", "second layer norm", "residual + dropout")):
+        assert np.array_equal(cpu == 0, gpu == 0), what
+        assert_kernel_close(gpu, cpu, scale=np.full(cpu.shape, max(1.0, float(np.abs(cpu).max()))), what=what)
+
+
 def test_bad_inputs_are_refused_like_the_interpreter_refuses_them(device):
     p = ProgramText()
     table = p.input("table", "f32", [5, 4]); ids = p.input("ids", "i32", [3])
