@@ -288,6 +288,7 @@ def main():
             "config": {"workload": args.config, "global_batch": cfg["batch"] * world, "seq_len": cfg["seq"], "vocab": cfg["vocab"],
                        "masked_rows": masked, "parallelism": "dp%d" % world,
                        "gradient_buckets": int(M.lib().msx_comm_bucket_count(plan.h)),
+                       "gradient_exchange": "peer memory" if M.lib().msx_comm_uses_peer_memory(plan.h) else ("nccl" if world > 1 else "none"),
                        "l2": "each step streams %.0f MB of intermediates (> 126 MB L2)" % (stats["algorithmic_bytes_per_step"] / 1e6)},
             "clocks": clocks,
             "e2e": {"value": world * 1e3 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,

@@ -179,6 +179,10 @@ int msx_comm_init(msx_plan* plan, int rank, int world, const void* unique_id_128
 int msx_comm_share(msx_plan* plan, msx_plan* owner);
 /* How many all-reduces one step issues for its gradients (about 25 MB each). */
 uint32_t msx_comm_bucket_count(const msx_plan* plan);
+/* 1 when the gradient buckets are summed by this library's own kernel over peer memory (every
+ * rank mapped every other rank's arena through CUDA IPC), 0 when by the NCCL all-reduce (a rank
+ * could not map a peer, more than 8 ranks, or MSX_PEER_REDUCE=0 in the environment). */
+uint32_t msx_comm_uses_peer_memory(const msx_plan* plan);
 
 /* ---- The training run above the plan -------------------------------------------------------
  *

@@ -74,6 +74,7 @@ SIGNATURES = {
     "msx_comm_unique_id": (C.c_int, [_P]),
     "msx_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P]),
     "msx_comm_bucket_count": (C.c_uint32, [_P]),
+    "msx_comm_uses_peer_memory": (C.c_uint32, [_P]),
     "msx_comm_share": (C.c_int, [_P, _P]),
     "msx_training_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_uint64]),
     "msx_training_create": (C.c_int, [_P, C.c_char_p, C.c_uint64, C.c_uint32, C.POINTER(_P)]),

@@ -159,6 +159,30 @@ void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t*
                              float* grad, uint64_t rows, uint64_t v, uint32_t* counter = nullptr, uint64_t ld = 0,
                              uint64_t ld_grad = 0);
 
+// ---- all-reduce over peer memory (peer_reduce.cu) ---------------------------------------------
+// `buffers[q]` is rank q's copy of the same `count` floats (this rank's own for q == rank, the
+// others mapped through CUDA IPC), `flags[q]` rank q's flag words (one per rank, zero before the
+// first launch). `epoch`, `arrivals` and `failed` are words of this rank's own, zero before the
+// first launch; every rank launches the same sequence of reductions on a channel (one stream),
+// one channel per set of these words. After the launch every copy holds scale x the sum over the
+// ranks, added in rank order by the rank that owns the element's slice. A wait that runs out
+// (10 s) raises bit 1 of *status and sets *failed, after which launches on the channel return
+// without waiting or summing.
+constexpr int kPeerRanks = 8;
+struct PeerReduceArgs {
+    float* buffers[kPeerRanks];
+    uint32_t* flags[kPeerRanks];
+    uint32_t* epoch;
+    uint32_t* arrivals;
+    uint32_t* failed;
+    uint32_t* status;
+    uint32_t rank, world;
+    uint64_t count;
+    float scale;
+    uint32_t mode;
+};
+void peer_all_reduce(cudaStream_t s, const PeerReduceArgs& args);
+
 // ---- embedding (embedding.cu) -----------------------------------------------------------------
 // out[n, :] = table[ids[n], :]; an id outside [0, rows) writes zeros and raises bit 0 of *status.
 void embedding(cudaStream_t s, const float* table, const int32_t* ids, float* out, uint64_t n,

@@ -190,6 +190,16 @@ struct msx_plan {
     cudaEvent_t step_begun = nullptr, weights_summed = nullptr, loss_ready = nullptr, loss_reduced = nullptr;
     bool loss_in_flight = false;     // set while a step is being enqueued
     uint64_t bucket_bytes = 25u << 20;
+    // Gradient buckets are summed by this backend's own kernel over peer memory when every rank
+    // could map every other rank's arena (CUDA IPC, one process per GPU of one machine); otherwise
+    // by the library's all-reduce. peer_arena[q] / peer_flags[q] are rank q's arena and flag words
+    // as mapped here (this rank's own at q == rank); d_peer_words holds the channel's launch count,
+    // block arrivals and failure mark.
+    bool peer_ready = false;
+    char* peer_arena[k::kPeerRanks] = {};
+    uint32_t* peer_flags[k::kPeerRanks] = {};
+    uint32_t* d_peer_flags = nullptr;
+    uint32_t* d_peer_words = nullptr;
 
     void* ptr(uint32_t pos) const {
         const Slot& s = slots[pos];
@@ -220,6 +230,7 @@ void cuda_ok(cudaError_t e, const char* what) {
 }
 
 void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream_t stream);
+void close_peer_reduce(msx_plan* P);
 
 // ---------------------------------------------------------------------------------------------
 // The scheduler.
@@ -1940,6 +1951,7 @@ void release(msx_plan* P) {
         if (b.ready) cudaEventDestroy(b.ready);
         if (b.done) cudaEventDestroy(b.done);
     }
+    close_peer_reduce(P);
     if (P->comm && P->owns_comm) g_nccl.CommDestroy(P->comm);
     if (P->comm_stream) cudaStreamDestroy(P->comm_stream);
     for (cudaEvent_t e : {P->step_begun, P->weights_summed, P->loss_ready, P->loss_reduced})
@@ -1978,6 +1990,79 @@ void release(msx_plan* P) {
     delete P;
 }
 
+void nccl_ok(ncclResult_t r, const char* what);
+
+// Maps every rank's arena and flag words into this process (CUDA IPC handles, exchanged through
+// the communicator as integers summed with zeros). The mapping is used only when it worked on
+// every rank; MSX_PEER_REDUCE=0 (set for all ranks alike) leaves it off.
+void setup_peer_reduce(msx_plan* P) {
+    const char* wanted = std::getenv("MSX_PEER_REDUCE");
+    if (wanted && std::strtol(wanted, nullptr, 0) == 0) return;
+    if (P->world < 2 || P->world > k::kPeerRanks || !P->arena) return;
+    constexpr size_t kWords = 2 * sizeof(cudaIpcMemHandle_t) / 4 + 1;  // two handles and a success mark
+    static_assert(sizeof(cudaIpcMemHandle_t) % 4 == 0, "handles travel as 32-bit words");
+    const size_t flag_bytes = k::kPeerRanks * sizeof(uint32_t);
+    cuda_ok(cudaMalloc(&P->d_peer_flags, flag_bytes), "cudaMalloc(peer flags)");
+    cuda_ok(cudaMemset(P->d_peer_flags, 0, flag_bytes), "cudaMemset(peer flags)");
+    cuda_ok(cudaMalloc(&P->d_peer_words, 4 * sizeof(uint32_t)), "cudaMalloc(peer words)");
+    cuda_ok(cudaMemset(P->d_peer_words, 0, 4 * sizeof(uint32_t)), "cudaMemset(peer words)");
+    std::vector<uint32_t> table(kWords * static_cast<size_t>(P->world), 0u);
+    uint32_t* mine = table.data() + kWords * static_cast<size_t>(P->rank);
+    cudaIpcMemHandle_t arena_handle, flag_handle;
+    bool ok = cudaIpcGetMemHandle(&arena_handle, P->arena) == cudaSuccess && cudaIpcGetMemHandle(&flag_handle, P->d_peer_flags) == cudaSuccess;
+    cudaGetLastError();
+    if (ok) {
+        std::memcpy(mine, &arena_handle, sizeof arena_handle);
+        std::memcpy(mine + sizeof(arena_handle) / 4, &flag_handle, sizeof flag_handle);
+        mine[kWords - 1] = 1;
+    }
+    uint32_t* d_table = nullptr;
+    cuda_ok(cudaMalloc(&d_table, table.size() * 4), "cudaMalloc(handle table)");
+    auto exchange = [&]() {
+        cuda_ok(cudaMemcpy(d_table, table.data(), table.size() * 4, cudaMemcpyHostToDevice), "cudaMemcpy(handle table)");
+        nccl_ok(g_nccl.AllReduce(d_table, d_table, table.size(), ncclUint32, ncclSum, P->comm, P->comm_stream), "ncclAllReduce(handles)");
+        cuda_ok(cudaStreamSynchronize(P->comm_stream), "cudaStreamSynchronize");
+        cuda_ok(cudaMemcpy(table.data(), d_table, table.size() * 4, cudaMemcpyDeviceToHost), "cudaMemcpy(handle table)");
+    };
+    exchange();
+    for (int q = 0; q < P->world && ok; ++q) ok = table[kWords * static_cast<size_t>(q) + kWords - 1] == 1;
+    for (int q = 0; q < P->world && ok; ++q) {
+        if (q == P->rank) {
+            P->peer_arena[q] = P->arena;
+            P->peer_flags[q] = P->d_peer_flags;
+            continue;
+        }
+        const uint32_t* theirs = table.data() + kWords * static_cast<size_t>(q);
+        std::memcpy(&arena_handle, theirs, sizeof arena_handle);
+        std::memcpy(&flag_handle, theirs + sizeof(arena_handle) / 4, sizeof flag_handle);
+        void* arena = nullptr;
+        void* flags = nullptr;
+        ok = cudaIpcOpenMemHandle(&arena, arena_handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+        if (ok) P->peer_arena[q] = static_cast<char*>(arena);
+        ok = ok && cudaIpcOpenMemHandle(&flags, flag_handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+        if (ok) P->peer_flags[q] = static_cast<uint32_t*>(flags);
+        cudaGetLastError();
+    }
+    // Every rank must agree: one that could not map a peer switches all of them to the library.
+    std::fill(table.begin(), table.end(), 0u);
+    table[static_cast<size_t>(P->rank)] = ok ? 1u : 0u;
+    exchange();
+    bool all = true;
+    for (int q = 0; q < P->world; ++q) all = all && table[static_cast<size_t>(q)] == 1;
+    cudaFree(d_table);
+    P->peer_ready = all;
+}
+
+void close_peer_reduce(msx_plan* P) {
+    for (int q = 0; q < k::kPeerRanks; ++q) {
+        if (q == P->rank) continue;
+        if (P->peer_arena[q]) cudaIpcCloseMemHandle(P->peer_arena[q]);
+        if (P->peer_flags[q]) cudaIpcCloseMemHandle(P->peer_flags[q]);
+    }
+    cudaFree(P->d_peer_flags);
+    cudaFree(P->d_peer_words);
+}
+
 void nccl_ok(ncclResult_t r, const char* what) {
     if (r != ncclSuccess) throw StatusError(MSX_LAUNCH_FAILED, std::string(what) + ": " + g_nccl.GetErrorString(r));
 }
@@ -1986,6 +2071,27 @@ void nccl_ok(ncclResult_t r, const char* what) {
 // that is not data parallel.
 void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream_t stream) {
     if (!P->comm) return;
+    const char* at = reinterpret_cast<const char*>(data);
+    if (P->peer_ready && stream == P->comm_stream && at >= P->arena && at + count * 4 <= P->arena + P->arena_bytes) {
+        // One channel: every reduction of arena data on the communication stream, which every
+        // rank issues in the same order.
+        k::PeerReduceArgs args = {};
+        const uint64_t offset = static_cast<uint64_t>(at - P->arena);
+        for (int q = 0; q < P->world; ++q) {
+            args.buffers[q] = reinterpret_cast<float*>(P->peer_arena[q] + offset);
+            args.flags[q] = P->peer_flags[q];
+        }
+        args.epoch = P->d_peer_words;
+        args.arrivals = P->d_peer_words + 1;
+        args.failed = P->d_peer_words + 2;
+        args.status = P->d_status;
+        args.rank = static_cast<uint32_t>(P->rank);
+        args.world = static_cast<uint32_t>(P->world);
+        args.count = count;
+        args.scale = average ? 1.0f / static_cast<float>(P->world) : 1.0f;
+        k::peer_all_reduce(stream, args);
+        return;
+    }
     nccl_ok(g_nccl.AllReduce(data, data, count, ncclFloat, average ? ncclAvg : ncclSum, P->comm, stream), "ncclAllReduce");
 }
 
@@ -2067,7 +2173,7 @@ int wait_all(msx_plan* P, uint32_t timeout_ms) {
         uint32_t bits = *P->pinned_status;
         *P->pinned_status = 0;
         cuda_ok(cudaMemsetAsync(P->d_status, 0, 4, P->stream), "cudaMemsetAsync");
-        if (bits & 2u) throw StatusError(MSX_TIMEOUT, "a bounded wait inside the tensor-core matmul ran out; the step's results are not valid");
+        if (bits & 2u) throw StatusError(MSX_TIMEOUT, "a bounded wait on the device ran out (tensor-core matmul, or a peer rank of the gradient all-reduce); the step's results are not valid");
         throw StatusError(MSX_BAD_INPUT, "an embedding id computed on the device is outside its table");
     }
     return MSX_OK;
@@ -2596,6 +2702,7 @@ int msx_comm_init(msx_plan* plan, int rank, int world, const void* unique_id_128
             cuda_ok(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "cudaEventCreate");
         cuda_ok(cudaMalloc(&plan->d_weight_total, sizeof(float)), "cudaMalloc(weight total)");
         plan_buckets(plan);
+        setup_peer_reduce(plan);
         for (Bucket& b : plan->buckets) {
             cuda_ok(cudaEventCreateWithFlags(&b.ready, cudaEventDisableTiming), "cudaEventCreate");
             cuda_ok(cudaEventCreateWithFlags(&b.done, cudaEventDisableTiming), "cudaEventCreate");
@@ -2618,6 +2725,7 @@ int msx_comm_share(msx_plan* plan, msx_plan* owner) {
 }
 
 uint32_t msx_comm_bucket_count(const msx_plan* plan) { return plan ? static_cast<uint32_t>(plan->buckets.size()) : 0; }
+uint32_t msx_comm_uses_peer_memory(const msx_plan* plan) { return plan && plan->peer_ready ? 1u : 0u; }
 
 uint64_t msx_compile(const char* source, const char* which, uint64_t masked_rows, char* out, uint64_t capacity) {
     if (!source || !which) return 0;

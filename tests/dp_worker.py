@@ -70,7 +70,8 @@ def main():
             for i, path in enumerate(cpu.param_paths()):
                 atol = 1e-4 + steps * 3e-3 * 1e-3 if path.endswith("_bk") else 1e-4
                 assert_run_close(params[i], cpu.read("param", i), "data-parallel parameter " + path, atol=atol)
-            print("DP_PARITY_OK world=%d buckets=%d last_loss=%.6f cpu=%.6f" % (world, buckets, losses[-1], cpu_losses[-1]), flush=True)
+            exchange = "peer" if M.lib().msx_comm_uses_peer_memory(run.step_plan.h) else "nccl"
+            print("DP_PARITY_OK world=%d buckets=%d exchange=%s last_loss=%.6f cpu=%.6f" % (world, buckets, exchange, losses[-1], cpu_losses[-1]), flush=True)
         except AssertionError as e:
             ok = False
             print("DP_PARITY_FAILED", e, flush=True)
