@@ -179,7 +179,6 @@ struct PeerReduceArgs {
     uint32_t rank, world;
     uint64_t count;
     float scale;
-    uint32_t mode;
 };
 void peer_all_reduce(cudaStream_t s, const PeerReduceArgs& args);
 

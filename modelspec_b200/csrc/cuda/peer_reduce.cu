@@ -13,8 +13,6 @@
 //
 // Every wait is bounded by the global timer: a rank that gives up raises bit 2 of *status, marks
 // the channel failed (later launches return at once) and leaves its copy unsummed.
-#include <cstdlib>
-
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -77,7 +75,7 @@ __device__ __forceinline__ void reduce_slice(const PeerReduceArgs& a, uint64_t l
     // before the first sum (a load from a peer takes microseconds; what bounds the kernel is how
     // many are in flight). A group past the end of the slice reads the turn's first group again
     // and stores nothing.
-    constexpr int GROUPS = WORLD <= 2 ? 4 : (WORLD <= 4 ? 2 : 2);
+    constexpr int GROUPS = WORLD <= 2 ? 4 : 2;
     const uint64_t lo4 = (lo + 3) & ~3ull, hi4 = hi & ~3ull;
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads * 4;
     for (uint64_t first = lo4 + (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) * 4; first < hi4; first += stride * GROUPS) {
@@ -86,7 +84,7 @@ __device__ __forceinline__ void reduce_slice(const PeerReduceArgs& a, uint64_t l
         for (int g = 0; g < GROUPS; ++g) {
             const uint64_t i = first + g * stride < hi4 ? first + g * stride : first;
 #pragma unroll
-            for (int q = 0; q < WORLD; ++q) v[g][q] = (a.mode & 1u) ? __ldcg(reinterpret_cast<const float4*>(a.buffers[q] + i)) : load_peer(a.buffers[q] + i);
+            for (int q = 0; q < WORLD; ++q) v[g][q] = load_peer(a.buffers[q] + i);
         }
 #pragma unroll
         for (int g = 0; g < GROUPS; ++g) {
@@ -139,7 +137,7 @@ __global__ void __launch_bounds__(kThreads) peer_all_reduce_kernel(PeerReduceArg
         }
         ok = wait_for_ranks(a, begun, &gave_up);
     }
-    if (ok && !(a.mode & 2u)) {
+    if (ok) {
         // Slices are multiples of four elements so that 16-byte accesses stay aligned.
         const uint64_t per = ((a.count + a.world - 1) / a.world + 3) & ~3ull;
         const uint64_t lo = min(a.count, per * a.rank), hi = min(a.count, lo + per);
@@ -183,12 +181,8 @@ void peer_all_reduce(cudaStream_t s, const PeerReduceArgs& args) {
     if (args.count == 0 || args.world < 2) return;
     const uint64_t per = (args.count + args.world - 1) / args.world;
     const uint64_t wanted = (per / 4 + kThreads - 1) / kThreads;
-    static const uint32_t max_blocks = [] { const char* t = std::getenv("MSX_PEER_BLOCKS"); return t ? static_cast<uint32_t>(std::atoi(t)) : 128u; }();
-    static const uint32_t mode = [] { const char* t = std::getenv("MSX_PEER_MODE"); return t ? static_cast<uint32_t>(std::atoi(t)) : 0u; }();
-    const uint32_t blocks = static_cast<uint32_t>(wanted < 1 ? 1 : (wanted > max_blocks ? max_blocks : wanted));
-    PeerReduceArgs tuned = args;
-    tuned.mode = mode;
-    peer_all_reduce_kernel<<<blocks, kThreads, 0, s>>>(tuned);
+    const uint32_t blocks = static_cast<uint32_t>(wanted < 1 ? 1 : (wanted > 128 ? 128 : wanted));
+    peer_all_reduce_kernel<<<blocks, kThreads, 0, s>>>(args);
     check_launch("peer_all_reduce");
 }
 

@@ -229,7 +229,7 @@ void cuda_ok(cudaError_t e, const char* what) {
     throw StatusError(status, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
 }
 
-void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream_t stream);
+void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream_t stream, bool exposed = true);
 void close_peer_reduce(msx_plan* P);
 
 // ---------------------------------------------------------------------------------------------
@@ -2069,10 +2069,13 @@ void nccl_ok(ncclResult_t r, const char* what) {
 
 // Sums (or averages) `count` floats in place across the ranks, on `stream`. A no-op for a plan
 // that is not data parallel.
-void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream_t stream) {
+void all_reduce(msx_plan* P, float* data, size_t count, bool average, cudaStream_t stream, bool exposed) {
     if (!P->comm) return;
     const char* at = reinterpret_cast<const char*>(data);
-    if (P->peer_ready && stream == P->comm_stream && at >= P->arena && at + count * 4 <= P->arena + P->arena_bytes) {
+    // A reduction that the step waits for goes through the backend's own kernel (lower latency, all
+    // links at once); one that runs behind the rest of the backward pass through the library, whose
+    // kernel leaves more of the device to the launches beside it.
+    if (exposed && P->peer_ready && stream == P->comm_stream && at >= P->arena && at + count * 4 <= P->arena + P->arena_bytes) {
         // One channel: every reduction of arena data on the communication stream, which every
         // rank issues in the same order.
         k::PeerReduceArgs args = {};
@@ -2112,6 +2115,9 @@ void join_loss(msx_plan* P) {
     P->loss_in_flight = false;
 }
 
+// A bucket closed this few launches before the optimizer has nothing left to hide behind.
+constexpr int kExposedLaunches = 6;
+
 void enqueue_all(msx_plan* P) {
     begin_side_work(P);
     std::vector<char> joined(P->launches.size(), 0);
@@ -2141,7 +2147,8 @@ void enqueue_all(msx_plan* P) {
             // while the rest of backward runs.
             cuda_ok(cudaEventRecord(b.ready, P->stream), "cudaEventRecord");
             cuda_ok(cudaStreamWaitEvent(P->comm_stream, b.ready, 0), "cudaStreamWaitEvent");
-            all_reduce(P, reinterpret_cast<float*>(P->arena + b.offset), b.bytes / 4, P->average_gradients, P->comm_stream);
+            const bool exposed = P->optimizer_launch < 0 || P->optimizer_launch - b.after_launch <= kExposedLaunches;
+            all_reduce(P, reinterpret_cast<float*>(P->arena + b.offset), b.bytes / 4, P->average_gradients, P->comm_stream, exposed);
             cuda_ok(cudaEventRecord(b.done, P->comm_stream), "cudaEventRecord");
         }
     }
