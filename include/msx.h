@@ -183,6 +183,17 @@ uint32_t msx_comm_bucket_count(const msx_plan* plan);
  * rank mapped every other rank's arena through CUDA IPC), 0 when by the NCCL all-reduce (a rank
  * could not map a peer, more than 8 ranks, or MSX_PEER_REDUCE=0 in the environment). */
 uint32_t msx_comm_uses_peer_memory(const msx_plan* plan);
+/* A check of the peer-memory all-reduce on ONE device: the launches of all `world` (2 to 8)
+ * ranks of an emulated job run one after the other over `world` copies of `count` floats.
+ * `host_copies[q]` is rank q's copy on the host, replaced by what the copy holds afterwards.
+ * With `peers_present` non-zero the flag words start as if every rank had already arrived at
+ * both rendezvous, so each launch goes straight to its slice; every copy must then hold
+ * scale x the sum of the copies. With 0 only rank 0's launch runs and waits for ranks that never
+ * come: it gives up after `wait_ms`, sums nothing, and a second launch returns at once because
+ * the channel is marked failed. `*status_bits` receives the status word the launches left
+ * (bit 1: a wait ran out). Nothing here needs a second GPU, and no launch waits for another. */
+int msx_peer_reduce_check(msx_device* device, uint32_t world, uint64_t count, float* const* host_copies, float scale,
+                          int peers_present, uint32_t wait_ms, uint32_t* status_bits);
 
 /* ---- The training run above the plan -------------------------------------------------------
  *

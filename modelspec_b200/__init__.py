@@ -75,6 +75,7 @@ SIGNATURES = {
     "msx_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P]),
     "msx_comm_bucket_count": (C.c_uint32, [_P]),
     "msx_comm_uses_peer_memory": (C.c_uint32, [_P]),
+    "msx_peer_reduce_check": (C.c_int, [_P, C.c_uint32, C.c_uint64, _P, C.c_float, C.c_int, C.c_uint32, _P]),
     "msx_comm_share": (C.c_int, [_P, _P]),
     "msx_training_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_uint64]),
     "msx_training_create": (C.c_int, [_P, C.c_char_p, C.c_uint64, C.c_uint32, C.POINTER(_P)]),
@@ -175,6 +176,18 @@ class Device:
         if self.h:
             lib().msx_close(self.h)
             self.h = None
+
+    def peer_reduce_check(self, copies, scale=1.0, peers_present=True, wait_ms=50):
+        """msx_peer_reduce_check: the peer-memory all-reduce launches of every rank, run one after
+        the other on this device over `copies` (one float32 array per rank). Returns what the
+        copies hold afterwards and the status word."""
+        import numpy as np
+        arrays = [np.ascontiguousarray(c, dtype=np.float32).copy() for c in copies]
+        pointers = (C.c_void_p * len(arrays))(*[a.ctypes.data for a in arrays])
+        status = C.c_uint32(0)
+        self.check(lib().msx_peer_reduce_check(self.h, len(arrays), arrays[0].size, pointers, scale, 1 if peers_present else 0,
+                                               wait_ms, C.byref(status)))
+        return arrays, status.value
 
 
 class Plan:

@@ -166,7 +166,7 @@ void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t*
 // first launch; every rank launches the same sequence of reductions on a channel (one stream),
 // one channel per set of these words. After the launch every copy holds scale x the sum over the
 // ranks, added in rank order by the rank that owns the element's slice. A wait that runs out
-// (10 s) raises bit 1 of *status and sets *failed, after which launches on the channel return
+// (10 s unless `wait_nanoseconds` says otherwise) raises bit 1 of *status and sets *failed, after which launches on the channel return
 // without waiting or summing.
 constexpr int kPeerRanks = 8;
 struct PeerReduceArgs {
@@ -179,6 +179,7 @@ struct PeerReduceArgs {
     uint32_t rank, world;
     uint64_t count;
     float scale;
+    uint64_t wait_nanoseconds;  // 0: the default limit
 };
 void peer_all_reduce(cudaStream_t s, const PeerReduceArgs& args);
 

@@ -58,7 +58,7 @@ __device__ bool wait_for_ranks(const PeerReduceArgs& a, uint32_t value, bool* ga
         const uint64_t start = global_timer();
         // Flag values only grow; the difference is compared so that a wrap of the counter is harmless.
         while (static_cast<int32_t>(load_acquire_system(flag) - value) < 0) {
-            if (global_timer() - start > kWaitNanoseconds) {
+            if (global_timer() - start > (a.wait_nanoseconds ? a.wait_nanoseconds : kWaitNanoseconds)) {
                 *gave_up = true;
                 break;
             }

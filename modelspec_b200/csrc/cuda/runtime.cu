@@ -2734,6 +2734,60 @@ int msx_comm_share(msx_plan* plan, msx_plan* owner) {
 uint32_t msx_comm_bucket_count(const msx_plan* plan) { return plan ? static_cast<uint32_t>(plan->buckets.size()) : 0; }
 uint32_t msx_comm_uses_peer_memory(const msx_plan* plan) { return plan && plan->peer_ready ? 1u : 0u; }
 
+int msx_peer_reduce_check(msx_device* device, uint32_t world, uint64_t count, float* const* host_copies, float scale,
+                          int peers_present, uint32_t wait_ms, uint32_t* status_bits) {
+    if (!device || !host_copies || !status_bits || world < 2 || world > static_cast<uint32_t>(k::kPeerRanks) || count == 0)
+        return MSX_BAD_ARGUMENT;
+    return guarded(device, [&]() -> int {
+        cuda_ok(cudaSetDevice(device->ordinal), "cudaSetDevice");
+        // One allocation: the copies (each on a 256-byte boundary), then per rank eight flag words
+        // and four channel words, then the status word.
+        const uint64_t pitch = align_up(count * 4);
+        const uint64_t words_at = pitch * world, bytes = words_at + (static_cast<uint64_t>(world) * 12 + 1) * 4;
+        char* base = nullptr;
+        cuda_ok(cudaMalloc(&base, bytes), "cudaMalloc(peer check)");
+        struct Free { char* p; ~Free() { cudaFree(p); } } release{base};
+        cuda_ok(cudaMemset(base, 0, bytes), "cudaMemset(peer check)");
+        for (uint32_t q = 0; q < world; ++q) {
+            if (!host_copies[q]) return MSX_BAD_ARGUMENT;
+            cuda_ok(cudaMemcpy(base + pitch * q, host_copies[q], count * 4, cudaMemcpyHostToDevice), "cudaMemcpy(copy)");
+        }
+        uint32_t* words = reinterpret_cast<uint32_t*>(base + words_at);
+        uint32_t* status = words + static_cast<uint64_t>(world) * 12;
+        if (peers_present) {
+            // Flag values only grow, so one large value stands for "arrived" at every rendezvous.
+            std::vector<uint32_t> arrived(static_cast<size_t>(world) * 12, 0u);
+            for (uint32_t q = 0; q < world; ++q)
+                for (uint32_t r = 0; r < world; ++r) arrived[static_cast<size_t>(q) * 12 + r] = 1u << 20;
+            cuda_ok(cudaMemcpy(words, arrived.data(), arrived.size() * 4, cudaMemcpyHostToDevice), "cudaMemcpy(flags)");
+        }
+        const uint32_t launches = peers_present ? world : 2u;  // without peers: rank 0 twice
+        for (uint32_t l = 0; l < launches; ++l) {
+            const uint32_t rank = peers_present ? l : 0u;
+            k::PeerReduceArgs args = {};
+            for (uint32_t q = 0; q < world; ++q) {
+                args.buffers[q] = reinterpret_cast<float*>(base + pitch * q);
+                args.flags[q] = words + static_cast<uint64_t>(q) * 12;
+            }
+            args.epoch = words + static_cast<uint64_t>(rank) * 12 + 8;
+            args.arrivals = args.epoch + 1;
+            args.failed = args.epoch + 2;
+            args.status = status;
+            args.rank = rank;
+            args.world = world;
+            args.count = count;
+            args.scale = scale;
+            args.wait_nanoseconds = static_cast<uint64_t>(wait_ms ? wait_ms : 1u) * 1000000ull;
+            k::peer_all_reduce(nullptr, args);
+            cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+        }
+        cuda_ok(cudaMemcpy(status_bits, status, 4, cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
+        for (uint32_t q = 0; q < world; ++q)
+            cuda_ok(cudaMemcpy(host_copies[q], base + pitch * q, count * 4, cudaMemcpyDeviceToHost), "cudaMemcpy(copy)");
+        return MSX_OK;
+    });
+}
+
 uint64_t msx_compile(const char* source, const char* which, uint64_t masked_rows, char* out, uint64_t capacity) {
     if (!source || !which) return 0;
     std::string text;

@@ -500,6 +500,39 @@ def test_sums_with_their_layer_norm_and_dropout_in_one_launch(device, rows, h):
         assert_kernel_close(gpu, cpu, scale=np.full(cpu.shape, max(1.0, float(np.abs(cpu).max()))), what=what)
 
 
+@pytest.mark.parametrize("world,count", [(2, 1), (2, 4099), (3, 10), (4, 100003), (8, 5), (8, 262144 + 7)])
+def test_the_peer_memory_all_reduce_sums_every_slice_in_rank_order(device, world, count):
+    """Every rank's launch of the gradient exchange, one after the other on one device with the
+    flag words already set: each copy ends as scale x (((c0 + c1) + c2) + ...), bit for bit, ragged
+    ends and slices shorter than a 16-byte group included."""
+    r = rng(world * 1000 + count)
+    copies = [values(r, count) for _ in range(world)]
+    scale = np.float32(1.0 / world)
+    after, status = device.peer_reduce_check(copies, scale=float(scale), peers_present=True)
+    assert status == 0
+    want = copies[0].copy()
+    for c in copies[1:]:
+        want = want + c
+    want = want * scale
+    for q in range(world):
+        assert_bits_equal(after[q], want, "copy of rank %d" % q)
+
+
+def test_the_peer_memory_all_reduce_gives_up_when_no_peer_arrives(device):
+    """Rank 0's launch with no other rank running: its wait ends after the limit, the copies are
+    left alone, the status word says so, and the next launch on the channel returns at once."""
+    import time
+    r = rng(77)
+    copies = [values(r, 4096) for _ in range(2)]
+    start = time.monotonic()
+    after, status = device.peer_reduce_check(copies, peers_present=False, wait_ms=200)
+    elapsed = time.monotonic() - start
+    assert status & 2
+    assert 0.19 < elapsed < 5.0  # one wait of 200 ms, not two
+    for q in range(2):
+        assert_bits_equal(after[q], copies[q], "copy of rank %d" % q)
+
+
 def test_bad_inputs_are_refused_like_the_interpreter_refuses_them(device):
     p = ProgramText()
     table = p.input("table", "f32", [5, 4]); ids = p.input("ids", "i32", [3])
