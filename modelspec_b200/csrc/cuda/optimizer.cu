@@ -40,28 +40,31 @@ __global__ void __launch_bounds__(256) adamw_kernel(const UpdateTensor* __restri
     const bool aligned = ((reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.m) |
                            reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
     if (aligned && stop - start == kUpdateChunk) {
-        // A whole chunk of 16-byte-aligned tensors: four float4 per thread and array, all sixteen
-        // loads issued before the first update.
-        constexpr int kVectors = kUpdateChunk / (256 * 4);
-        float4 g[kVectors], p[kVectors], m[kVectors], v[kVectors];
+        // A whole chunk of 16-byte-aligned tensors: two float4 per thread and array at a time,
+        // all eight loads issued before the first update.
+        constexpr int kVectors = 2, kTurns = kUpdateChunk / (256 * 4 * kVectors);
+#pragma unroll 1
+        for (int turn = 0; turn < kTurns; ++turn) {
+            float4 g[kVectors], p[kVectors], m[kVectors], v[kVectors];
 #pragma unroll
-        for (int j = 0; j < kVectors; ++j) {
-            const uint64_t i = start + (j * 256 + threadIdx.x) * 4;
-            g[j] = *reinterpret_cast<const float4*>(t.g + i);
-            p[j] = *reinterpret_cast<const float4*>(t.p + i);
-            m[j] = *reinterpret_cast<const float4*>(t.m + i);
-            v[j] = *reinterpret_cast<const float4*>(t.v + i);
-        }
+            for (int j = 0; j < kVectors; ++j) {
+                const uint64_t i = start + ((turn * kVectors + j) * 256 + threadIdx.x) * 4;
+                g[j] = *reinterpret_cast<const float4*>(t.g + i);
+                p[j] = *reinterpret_cast<const float4*>(t.p + i);
+                m[j] = *reinterpret_cast<const float4*>(t.m + i);
+                v[j] = *reinterpret_cast<const float4*>(t.v + i);
+            }
 #pragma unroll
-        for (int j = 0; j < kVectors; ++j) {
-            const uint64_t i = start + (j * 256 + threadIdx.x) * 4;
-            update(g[j].x, p[j].x, m[j].x, v[j].x);
-            update(g[j].y, p[j].y, m[j].y, v[j].y);
-            update(g[j].z, p[j].z, m[j].z, v[j].z);
-            update(g[j].w, p[j].w, m[j].w, v[j].w);
-            *reinterpret_cast<float4*>(t.p + i) = p[j];
-            *reinterpret_cast<float4*>(t.m + i) = m[j];
-            *reinterpret_cast<float4*>(t.v + i) = v[j];
+            for (int j = 0; j < kVectors; ++j) {
+                const uint64_t i = start + ((turn * kVectors + j) * 256 + threadIdx.x) * 4;
+                update(g[j].x, p[j].x, m[j].x, v[j].x);
+                update(g[j].y, p[j].y, m[j].y, v[j].y);
+                update(g[j].z, p[j].z, m[j].z, v[j].z);
+                update(g[j].w, p[j].w, m[j].w, v[j].w);
+                *reinterpret_cast<float4*>(t.p + i) = p[j];
+                *reinterpret_cast<float4*>(t.m + i) = m[j];
+                *reinterpret_cast<float4*>(t.v + i) = v[j];
+            }
         }
         return;
     }
