@@ -400,6 +400,144 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
 
 inline uint32_t warp_row_blocks(uint64_t rows) { return static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock); }
 
+// The same for rows of 16-byte pitch, as two blocks per SM: 512 threads hold 32 elements each in
+// registers and up to 32 more in shared memory (64 KB a block), so that one block's loads and
+// stores run under the other's reductions and exponentials. Elements bound for shared memory go
+// there straight from global memory (cp.async, 16 bytes), all in flight with the register loads;
+// every thread reads back only what it copied itself.
+constexpr int kSplitThreads = 512, kSplitRegisterItems = 32, kSplitSharedItems = 32;
+constexpr int kSplitSharedBytes = kSplitSharedItems * kSplitThreads * 4;
+__global__ void __launch_bounds__(kSplitThreads, 2)
+cross_entropy_fused_split_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+                                 const float* __restrict__ weights, const float* __restrict__ g,
+                                 const float* __restrict__ denominator, float* __restrict__ row_loss,
+                                 float* __restrict__ out, uint32_t v, uint32_t ld, uint32_t ld_out,
+                                 uint32_t* __restrict__ counter, float* __restrict__ loss) {
+    // Group k of this thread is the four columns from (k * 512 + tid) * 4 on: groups 0..7 live in
+    // registers, groups 8..15 in shared memory.
+    extern __shared__ float4 parked[];  // [kSplitSharedItems / 4][kSplitThreads]
+    __shared__ float shared[33];
+    __shared__ double shared64[33];
+    __shared__ bool is_last;
+    constexpr int kRegisterGroups = kSplitRegisterItems / 4, kSharedGroups = kSplitSharedItems / 4;
+    const uint32_t r = blockIdx.x, tid = threadIdx.x, rows = gridDim.x;
+    auto column_of = [tid](int group) { return (static_cast<uint32_t>(group) * kSplitThreads + tid) * 4; };
+    float* o = out + static_cast<uint64_t>(r) * ld_out;
+    float den;
+    if (denominator != nullptr) {
+        den = denominator[0];
+    } else {
+        double sum = 0.0;
+        for (uint32_t j = tid; j < rows; j += kSplitThreads) sum += static_cast<double>(weights[j]);
+        den = static_cast<float>(block_sum(sum, shared64));
+    }
+    const float w = weights[r];
+    float4 x[kRegisterGroups];
+    float total = 0.0f;
+    uint32_t label = 0;
+    // How many of the parked groups hold columns of the row at all (the same for every thread of
+    // a warp but the one the row ends in, whose later lanes have one fewer).
+    int parked_groups = 0;
+#pragma unroll
+    for (int k = 0; k < kSharedGroups; ++k)
+        if (column_of(kRegisterGroups + k) < v) parked_groups = k + 1;
+    if (w == 0.0f) {
+        if (tid == 0) row_loss[r] = 0.0f;
+    } else {
+        const float* row = logits + static_cast<uint64_t>(r) * ld;
+        const uint32_t last = (v - 1) & ~3u;
+#pragma unroll
+        for (int k = 0; k < kSharedGroups; ++k)
+            if (k < parked_groups) {
+                const uint32_t to = static_cast<uint32_t>(__cvta_generic_to_shared(&parked[k * kSplitThreads + tid]));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to), "l"(row + column_of(kRegisterGroups + k)) : "memory");
+            }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+        for (int k = 0; k < kRegisterGroups; ++k) x[k] = __ldg(reinterpret_cast<const float4*>(row + min(column_of(k), last)));
+        auto mask = [v](float4 f, uint32_t c) {
+            if (c >= v) f.x = -INFINITY;
+            if (c + 1 >= v) f.y = -INFINITY;
+            if (c + 2 >= v) f.z = -INFINITY;
+            if (c + 3 >= v) f.w = -INFINITY;
+            return f;
+        };
+        float m = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < kRegisterGroups; ++k) {
+            x[k] = mask(x[k], column_of(k));
+            m = fmaxf(fmaxf(m, fmaxf(x[k].x, x[k].y)), fmaxf(x[k].z, x[k].w));
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+        for (int k = 0; k < kSharedGroups; ++k)
+            if (k < parked_groups) {
+                const float4 f = mask(parked[k * kSplitThreads + tid], column_of(kRegisterGroups + k));
+                parked[k * kSplitThreads + tid] = f;
+                m = fmaxf(fmaxf(m, fmaxf(f.x, f.y)), fmaxf(f.z, f.w));
+            }
+        m = block_max(m, shared);
+        // exp(-inf) is 0: the masked columns add nothing and need no test of their own.
+        auto exponentials = [m](float4 f) { return make_float4(__expf(f.x - m), __expf(f.y - m), __expf(f.z - m), __expf(f.w - m)); };
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kRegisterGroups; ++k) {
+            x[k] = exponentials(x[k]);
+            sum += (x[k].x + x[k].y) + (x[k].z + x[k].w);
+        }
+#pragma unroll
+        for (int k = 0; k < kSharedGroups; ++k)
+            if (k < parked_groups) {
+                const float4 f = exponentials(parked[k * kSplitThreads + tid]);
+                parked[k * kSplitThreads + tid] = f;
+                sum += (f.x + f.y) + (f.z + f.w);
+            }
+        total = block_sum(sum, shared);
+        label = static_cast<uint32_t>(labels[r]);
+        if (tid == 0) row_loss[r] = m + logf(total) - (label < v ? row[label] : 0.0f);
+    }
+    if (tid == 0) {
+        __threadfence();
+        const uint32_t before = atomicAdd(counter, 1u);
+        is_last = before + 1u == rows;
+        if (is_last) *counter = 0u;
+    }
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        double num = 0.0, den64 = 0.0;
+        for (uint32_t j = tid; j < rows; j += kSplitThreads) {
+            double wj = static_cast<double>(weights[j]);
+            num = fma(wj, static_cast<double>(__ldcg(row_loss + j)), num);
+            den64 += wj;
+        }
+        num = block_sum(num, shared64);
+        den64 = block_sum(den64, shared64);
+        if (denominator != nullptr) den64 = static_cast<double>(denominator[0]);
+        if (tid == 0) loss[0] = den64 == 0.0 ? 0.0f : static_cast<float>(num / den64);
+    }
+    const bool zero = den == 0.0f || w == 0.0f;
+    const float scale = zero ? 0.0f : g[0] * w / den;
+    const float inverse = zero ? 0.0f : 1.0f / total;
+    auto gradient = [=](float4 f, uint32_t c) {
+        if (zero) return make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        return make_float4(scale * (f.x * inverse - (c == label ? 1.0f : 0.0f)), scale * (f.y * inverse - (c + 1 == label ? 1.0f : 0.0f)),
+                           scale * (f.z * inverse - (c + 2 == label ? 1.0f : 0.0f)), scale * (f.w * inverse - (c + 3 == label ? 1.0f : 0.0f)));
+    };
+    // Columns past v inside the pitch are padding nobody reads: the whole float4 is written.
+#pragma unroll
+    for (int k = 0; k < kRegisterGroups; ++k) {
+        const uint32_t c = column_of(k);
+        if (c < v) *reinterpret_cast<float4*>(o + c) = gradient(x[k], c);
+    }
+#pragma unroll
+    for (int k = 0; k < kSharedGroups; ++k)
+        if (k < parked_groups) {
+            const uint32_t c = column_of(kRegisterGroups + k);
+            *reinterpret_cast<float4*>(o + c) = gradient(zero ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : parked[k * kSplitThreads + tid], c);
+        }
+}
+
 // dropout(x) + residual, then layer_norm of the sum, one warp per row with the row in registers:
 // the three launches of a transformer sublayer's tail as one. Every element goes through the same
 // rounded operations as the separate kernels (the Philox draw of element index_base + r h + c, the
@@ -776,7 +914,17 @@ void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t*
         const float* den = denominator_ready ? denominator : nullptr;
         const bool vec = ld % 4 == 0 && ld_grad % 4 == 0 && reinterpret_cast<uintptr_t>(logits) % 16 == 0 &&
                          reinterpret_cast<uintptr_t>(grad) % 16 == 0;
-        if (vec)
+        // Long rows: two 512-thread blocks per SM. Short ones fit the registers of 1,024 threads.
+        if (vec && v > 16384) {
+            static const bool configured = [] {
+                cudaFuncSetAttribute(cross_entropy_fused_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSplitSharedBytes);
+                return true;
+            }();
+            (void)configured;
+            cross_entropy_fused_split_kernel<<<static_cast<uint32_t>(rows), kSplitThreads, kSplitSharedBytes, s>>>(logits, labels, weights, g, den,
+                                                                                                                  row_loss, grad, vv, l1, l2,
+                                                                                                                  counter, loss);
+        } else if (vec)
             cross_entropy_fused_wide_kernel<4><<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(logits, labels, weights, g, den, row_loss,
                                                                                                     grad, vv, l1, l2, counter, loss);
         else

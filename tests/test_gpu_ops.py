@@ -93,7 +93,7 @@ def test_tensor_core_matmul_within_the_kernel_tolerance(device, m, k, n, form):
     assert np.abs(gpu.astype(np.float64) - cpu).max() <= 4e-6 * max(terms.max(), 1e-30)
 
 
-@pytest.mark.parametrize("rows,h,v", [(64, 32, 50), (130, 64, 1002), (96, 128, 4099), (333, 32, 1002), (400, 16, 40001)])
+@pytest.mark.parametrize("rows,h,v", [(64, 32, 50), (130, 64, 1002), (96, 128, 4099), (333, 32, 1002), (400, 16, 40001), (96, 16, 30522)])
 def test_a_vocabulary_head_of_odd_width_through_padded_rows(device, rows, h, v):
     """logits = x W^T + b, cross entropy and its gradient, the bias gradient (column sums of the
     logits gradient) and both matmuls that read it, with a width that is not a multiple of 4: on
@@ -352,8 +352,10 @@ def test_attention_and_its_three_gradients(device, batch, q_len, k_len, heads, d
         assert not gpu[masked_rows].any() and not np.signbit(gpu[masked_rows]).any(), "a masked key's row is +0"
 
 
-@pytest.mark.parametrize("rows,v", [(5, 11), (64, 1000), (33, 30522)])
+@pytest.mark.parametrize("rows,v", [(5, 11), (64, 1000), (33, 30522), (33, 30524), (9, 16388), (7, 32768), (300, 20000)])
 def test_cross_entropy_and_its_gradient(device, rows, v):
+    """Rows of 16-byte pitch and more than 16,384 logits take the kernel that runs two blocks per SM
+    (part of the row in shared memory); 32,768 is the longest row it holds."""
     r = rng(rows + v)
     p = ProgramText()
     x = p.input("x", "f32", [rows, v]); labels = p.input("labels", "i32", [rows]); w = p.input("w", "f32", [rows])
