@@ -121,14 +121,14 @@ __device__ __forceinline__ uint32_t warp_lower_bound(const int32_t* __restrict__
 // mask token, a padding position: hundreds of occurrences) would be one warp waiting on memory
 // hundreds of times: the block takes it together instead, all 256 threads streaming 32
 // occurrences at a time into shared memory while one thread per column adds the previous 32 in
-// order. A row nobody read gets `base` (or zero). VEC = 4 reads and writes 16 bytes per lane and
-// needs h % 4 == 0 and 16-byte aligned g, base and out.
+// order. A row nobody read gets `base` (or zero); when base is out itself, such a row is left
+// alone and only the rows some id names are read and written. VEC = 4 reads and writes 16 bytes
+// per lane and needs h % 4 == 0 and 16-byte aligned g, base and out.
 constexpr uint32_t kHotRow = 32, kHotChunk = 32, kCachedIds = 4096;
 template <int VEC>
 __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ g, const int32_t* __restrict__ sorted_id,
                                                       const int32_t* __restrict__ sorted_n, uint32_t n,
-                                                      const float* __restrict__ base, float* __restrict__ out,
-                                                      uint32_t rows, uint32_t h) {
+                                                      const float* base, float* out, uint32_t rows, uint32_t h) {
     constexpr uint32_t span = VEC * 32;
     constexpr int LOADS = kHotChunk * span / VEC / 256;
     __shared__ float stage[kHotChunk][span];
@@ -145,10 +145,12 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
     const uint32_t groups = (h + span - 1) / span;
     const uint64_t items = static_cast<uint64_t>(rows) * groups;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (uint64_t first = static_cast<uint64_t>(blockIdx.x) * 8; first < items; first += static_cast<uint64_t>(gridDim.x) * 8) {
+    // Neighbouring rows go to different blocks: the hot rows of a vocabulary sit together (the most
+    // frequent tokens have neighbouring ids), and each is a serial job for the block that gets it.
+    for (uint64_t first = blockIdx.x; first < items; first += static_cast<uint64_t>(gridDim.x) * 8) {
         if (threadIdx.x == 0) hot_rows = 0;
         __syncthreads();
-        const uint64_t item = first + warp;
+        const uint64_t item = first + static_cast<uint64_t>(warp) * gridDim.x;
         if (item < items) {
             const uint32_t row = static_cast<uint32_t>(item / groups), col = static_cast<uint32_t>(item % groups) * span + lane * VEC;
             const bool in = col < h;
@@ -159,7 +161,7 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
             if (count > kHotRow) {
                 if (lane == 0) {
                     uint32_t slot = atomicAdd(&hot_rows, 1u);
-                    hot_item[slot] = static_cast<uint32_t>(item - first);
+                    hot_item[slot] = warp;
                     hot_at[slot] = at;
                     hot_count[slot] = count;
                 }
@@ -194,7 +196,8 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
                             for (int q = 0; q < VEC; ++q) acc[q] = acc[q] + v[e][q];
                         }
                 }
-                if (in) {
+                // In place (base is out): a row nobody read already holds its result.
+                if (in && !(count == 0 && base == out)) {
                     float* to = out + static_cast<uint64_t>(row) * h + col;
                     if (VEC == 4) {
                         float4 r = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
@@ -214,7 +217,7 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
         // warp took which slot does not change any sum).
         const uint32_t hot = hot_rows;
         for (uint32_t slot = 0; slot < hot; ++slot) {
-            const uint64_t hot_id = first + hot_item[slot];
+            const uint64_t hot_id = first + static_cast<uint64_t>(hot_item[slot]) * gridDim.x;
             const uint32_t row = static_cast<uint32_t>(hot_id / groups), col0 = static_cast<uint32_t>(hot_id % groups) * span;
             const uint32_t at = hot_at[slot], count = hot_count[slot];
             // Two chunks of loads are in flight while a third is added: one round trip to memory

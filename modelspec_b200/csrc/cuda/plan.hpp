@@ -54,7 +54,8 @@ struct Slot {
         Moment,    // an AdamW moment buffer (its input and its next value)
         Input,     // a host input in the upload region
         Const,     // a folded rank-0 constant in the constant table
-        View       // a Transpose folded away: reads its source with the transposed flag flipped
+        View       // stored as another value: a Transpose folded away (read with the transposed flag
+                   // flipped), or an addend that the launch which adds to it updates in place
     } kind = Dead;
     uint64_t bytes = 0;
     uint32_t pitch = 0;        // elements between rows as stored; 0 = the row width
@@ -63,6 +64,7 @@ struct Slot {
     char moment = 0;           // Moment: 'm' or 'v'
     float constant = 0.0f;     // Const
     int first = -1, last = -1; // launches that define and last read an Arena value
+    int last_write = -1;       // the last launch that writes it (a value updated in place has two)
     bool keep = false;         // an output: never reused
 };
 

@@ -391,20 +391,31 @@ struct Scheduler {
             if (launch.kernel != "matmul" && launch.kernel != "sum_rows" && launch.kernel != "embedding_order" &&
                 launch.kernel != "matmul_jobs" && launch.kernel != "sum_rows_batched")
                 continue;
+            auto stored_as = [this](uint32_t v) {
+                while (P->slots[v].kind == Slot::View) v = P->slots[v].index;
+                return v;
+            };
             bool eligible = !launch.writes.empty();
             for (uint32_t w : launch.writes) {
-                const Slot& slot = P->slots[w];
-                if (slot.kind != Slot::Arena) eligible = false;
-                if (w < prog.nodes.size())
+                const uint32_t home = stored_as(w);
+                if (P->slots[home].kind != Slot::Arena) eligible = false;
+                // An output is read by the host or a bucket, not by a launch; a value that a later
+                // launch turns into an output in place is read by that launch.
+                if (home == w && w < prog.nodes.size())
                     for (const msx::Output& o : prog.outputs)
-                        if (pos(o.value) == w) eligible = false;  // an output: read by the host or a bucket, not by a launch
+                        if (pos(o.value) == w) eligible = false;
             }
             if (!eligible) continue;
             int first_reader = count;
-            for (int later = l + 1; later < count; ++later)
-                for (uint32_t r : P->launches[static_cast<size_t>(later)].reads)
-                    for (uint32_t w : launch.writes)
-                        if (r == w) first_reader = std::min(first_reader, later);
+            for (int later = l + 1; later < count; ++later) {
+                const Launch& other = P->launches[static_cast<size_t>(later)];
+                for (uint32_t w : launch.writes) {
+                    for (uint32_t r : other.reads)
+                        if (stored_as(r) == stored_as(w)) first_reader = std::min(first_reader, later);
+                    for (uint32_t again : other.writes)
+                        if (stored_as(again) == stored_as(w)) first_reader = std::min(first_reader, later);
+                }
+            }
             if (first_reader == count || first_reader - l < kSideGap) continue;
             launch.join_before = first_reader;
         }
@@ -437,6 +448,12 @@ struct Scheduler {
         l.run = std::move(run);
         P->launches.push_back(std::move(l));
         return P->launches.back();
+    }
+
+    bool is_output_value(uint32_t v) const {
+        for (const msx::Output& o : prog.outputs)
+            if (pos(o.value) == v) return true;
+        return false;
     }
 
     bool is_scalar_operand(uint32_t operand_pos, const Node& result) const {
@@ -930,6 +947,14 @@ struct Scheduler {
                             Slot& sum = P->slots[u];
                             sum.kind = Slot::Arena;
                             sum.bytes = std::max<uint64_t>(add.ty.count() * 4, 4);
+                            // `other` is read by this sum alone and was written by an earlier launch:
+                            // it is stored where the sum goes, and the scatter touches only the rows
+                            // some id names (a table of 30,522 rows read by 4,096 ids: an eighth).
+                            if (users[other].size() == 1 && P->slots[other].kind == Slot::Arena && P->slots[other].pitch == 0 &&
+                                !is_output_value(other) && node(other).ty.shape == add.ty.shape) {
+                                P->slots[other].kind = Slot::View;
+                                P->slots[other].index = u;
+                            }
                             if (have_order)
                                 emit("embedding_grad", nd, {g, other, tmp}, {u}, [=](cudaStream_t s) {
                                     k::embedding_scatter(s, plan->f(g), plan->f(u), n, rows, h, plan->i(tmp), plan->f(other));
@@ -1739,12 +1764,22 @@ struct FreeList {
 
 void place_arena(msx_plan* P) {
     std::vector<Slot>& slots = P->slots;
+    // A value stored as another one is that one, wherever a launch names it.
+    auto stored_as = [&slots](uint32_t v) {
+        while (slots[v].kind == Slot::View) v = slots[v].index;
+        return v;
+    };
+    for (Launch& launch : P->launches) {
+        for (uint32_t& w : launch.writes) w = stored_as(w);
+        for (uint32_t& r : launch.reads) r = stored_as(r);
+    }
     for (size_t l = 0; l < P->launches.size(); ++l) {
         const Launch& launch = P->launches[l];
         for (uint32_t w : launch.writes)
             if (slots[w].kind == Slot::Arena) {
                 if (slots[w].first < 0) slots[w].first = static_cast<int>(l);
                 slots[w].last = std::max(slots[w].last, static_cast<int>(l));
+                slots[w].last_write = std::max(slots[w].last_write, static_cast<int>(l));
             }
         for (uint32_t r : launch.reads)
             if (slots[r].kind == Slot::Arena) {
@@ -1816,7 +1851,7 @@ void plan_buckets(msx_plan* P) {
             any = true;
         }
         open.bytes = s.offset + align_up(s.bytes) - open.offset;
-        open.after_launch = std::max(open.after_launch, s.first);
+        open.after_launch = std::max(open.after_launch, s.last_write);
         if (open.bytes >= P->bucket_bytes) {
             P->buckets.push_back(open);
             any = false;
