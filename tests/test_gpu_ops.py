@@ -275,9 +275,17 @@ def test_embedding_gradient_of_hot_rows_and_with_a_dense_addend(device, rows, h,
     d = p.op("EmbeddingGrad", [rows, h], [i, g], attr="[%d]" % rows)
     d2 = p.op("EmbeddingGrad", [rows, h], [i, g], attr="[%d]" % rows)
     tied = p.op("Add", [rows, h], [dense, d2])
-    p.output(d); p.output(tied)
+    # A dense addend that a launch made and nothing else reads is stored where the sum goes: the
+    # scatter then adds in place and leaves the rows no id names alone.
+    made = p.op("Mul", [rows, h], [dense, dense])
+    d3 = p.op("EmbeddingGrad", [rows, h], [i, g], attr="[%d]" % rows)
+    in_place = p.op("Add", [rows, h], [made, d3])
+    p.output(d); p.output(tied); p.output(in_place)
+    listing = M.schedule_describe(p.text()).strip().splitlines()
+    product = [l for l in listing if l.split()[1] == "binary"][0]
+    assert product.split("writes")[1].split()[0] == "%%%d" % in_place, listing
     res = run_both(device, p.text(), {"ids": ids, "g": values(r, n, h), "dense": values(r, rows, h)},
-                   outputs=[(d, rows * h), (tied, rows * h)])
+                   outputs=[(d, rows * h), (tied, rows * h), (in_place, rows * h)])
     for cpu, gpu in res:
         assert_bits_equal(gpu, cpu)
 
