@@ -116,11 +116,12 @@ struct DropoutDraw {
     uint64_t index_base = 0;
 };
 // `adjoint_draw`, when not null: the adjoint is dropout_grad of that sum. `dx_draw` and `dx_dropped`,
-// when not null: dropout_grad of dx is written to dx_dropped beside dx.
+// when not null: dropout_grad of dx is written to dx_dropped beside dx. `pre_activation` and
+// `dx_dropped`: gelu_grad(pre_activation, dx) is written to dx_dropped instead; dx may then be null.
 void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
                          uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const float* g1 = nullptr,
                          const float* g2 = nullptr, const float* g3 = nullptr, const DropoutDraw* adjoint_draw = nullptr,
-                         const DropoutDraw* dx_draw = nullptr, float* dx_dropped = nullptr);
+                         const DropoutDraw* dx_draw = nullptr, float* dx_dropped = nullptr, const float* pre_activation = nullptr);
 // sum_out = residual + dropout(x), out = layer_norm(sum_out, gamma, beta), rows of up to 1,024
 // elements (layer_norm_backward_supported(h)); the dropout draw is that of `dropout`.
 void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residual, const int32_t* token, uint64_t seed,
@@ -129,9 +130,10 @@ void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residua
 // The general form: sum_out = residual + x (x through `x_draw` first when not null); with gamma
 // and beta, out = layer_norm(sum_out) (out may be null when only the next output is wanted) and,
 // with `out_draw`, out_dropped = dropout(out).
+// With `gelu_first`, gelu(x) stands where the sum does (residual is null then): sum_out = gelu(x).
 void add_layer_norm(cudaStream_t s, const float* x, const float* residual, const DropoutDraw* x_draw, const float* gamma,
                     const float* beta, float* sum_out, float* out, const DropoutDraw* out_draw, float* out_dropped, uint64_t rows,
-                    uint64_t h);
+                    uint64_t h, bool gelu_first = false);
 void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t k);
 void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, uint64_t rows, uint64_t k);
 // Row losses max + ln(sum exp(x - max)) - x[label] into row_loss[rows], then

@@ -548,7 +548,7 @@ template <int ITEMS>
 __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
     const float* __restrict__ x, const float* __restrict__ residual, DropoutDraw x_draw, const float* __restrict__ gamma,
     const float* __restrict__ beta, float* __restrict__ sum_out, float* __restrict__ out, DropoutDraw out_draw,
-    float* __restrict__ out_dropped, uint32_t rows, uint32_t h) {
+    float* __restrict__ out_dropped, uint32_t rows, uint32_t h, bool gelu_first) {
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (r >= rows) return;
@@ -558,8 +558,15 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
     float v[ITEMS], xs[ITEMS];
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) xs[i] = __ldg(x + base + min(i * 32 + lane, h - 1));
+    if (residual != nullptr) {
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) v[i] = __ldg(residual + base + min(i * 32 + lane, h - 1));
+        for (int i = 0; i < ITEMS; ++i) v[i] = __ldg(residual + base + min(i * 32 + lane, h - 1));
+    }
+    // gelu(x) in the place of the sum (the head's transform: dense, gelu, layer norm).
+    if (gelu_first) {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) xs[i] = gelu_value(xs[i]);
+    }
     if (x_draw.token != nullptr) {
         const uint32_t id_lo = static_cast<uint32_t>(x_draw.token[0]), id_hi = static_cast<uint32_t>(x_draw.token[1]);
 #pragma unroll
@@ -572,7 +579,7 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         const uint32_t c = i * 32 + lane;
-        v[i] = c < h ? v[i] + xs[i] : 0.0f;
+        v[i] = c < h ? (residual != nullptr ? v[i] + xs[i] : xs[i]) : 0.0f;
         if (c < h) sum_out[base + c] = v[i];
     }
     if (gamma == nullptr) return;
@@ -622,19 +629,21 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
     const float* __restrict__ g2, const float* __restrict__ g3, float* __restrict__ dx,
     float* __restrict__ partial, uint32_t* __restrict__ counter, float* __restrict__ dgamma, float* __restrict__ dbeta,
     uint32_t want, uint32_t rows, uint32_t h, uint32_t rows_per_chunk, DropoutDraw adjoint_draw, DropoutDraw dx_draw,
-    float* __restrict__ dx_dropped) {
+    float* __restrict__ dx_dropped, const float* __restrict__ pre_activation) {
     __shared__ float buf[8 * 32 * ITEMS];
     __shared__ bool is_last;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, chunks = gridDim.x;
     const uint32_t r0 = blockIdx.x * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
     const float width = static_cast<float>(h);
+    // dx is formed when it is stored or when what is stored is a function of it.
+    const bool want_dx = dx != nullptr || dx_dropped != nullptr;
     float acc_g[ITEMS], acc_b[ITEMS], gam[ITEMS];
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
         acc_g[i] = 0.0f;
         acc_b[i] = 0.0f;
         uint32_t c = i * 32 + lane;
-        gam[i] = (dx != nullptr && c < h) ? gamma[c] : 0.0f;
+        gam[i] = (want_dx && c < h) ? gamma[c] : 0.0f;
     }
     for (uint32_t r = r0 + warp; r < r1; r += 8) {
         // All loads of an array are issued before any is used: unconditional, from a clamped
@@ -696,9 +705,14 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
                 s1 += gx;
                 s2 = fmaf(gx, xhat, s2);
             }
-        if (dx != nullptr) {
+        if (want_dx) {
             const float mean_gx = warp_sum(s1) / width, mean_gx_xhat = warp_sum(s2) / width;
-            float* o = dx + static_cast<uint64_t>(r) * h;
+            // The pre-activations of a gelu_grad on dx: loaded together, before the first is used.
+            float pre[ITEMS];
+            if (pre_activation != nullptr) {
+#pragma unroll
+                for (int i = 0; i < ITEMS; ++i) pre[i] = __ldg(pre_activation + row_at + min(i * 32 + lane, h - 1));
+            }
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
                 uint32_t c = i * 32 + lane;
@@ -706,10 +720,13 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
                     float gx = gv[i] * gam[i];
                     float xhat = (xv[i] - mean) * rstd;
                     const float value = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
-                    o[c] = value;
-                    // dropout_grad of dx, for the reader that wants it masked (the projection before
+                    if (dx != nullptr) dx[row_at + c] = value;
+                    // A function of dx for the reader that wants that: gelu_grad (the dense layer
+                    // before a gelu and this layer norm), or dropout_grad (the projection before
                     // this sublayer's dropout).
-                    if (dx_dropped != nullptr) {
+                    if (pre_activation != nullptr) {
+                        dx_dropped[row_at + c] = gelu_grad_value(pre[i], value);
+                    } else if (dx_dropped != nullptr) {
                         const uint32_t w0 = philox_word0(static_cast<uint32_t>(dx_draw.index_base + row_at + c), 4u,
                                                          static_cast<uint32_t>(dx_draw.token[0]), static_cast<uint32_t>(dx_draw.token[1]),
                                                          static_cast<uint32_t>(dx_draw.seed), static_cast<uint32_t>(dx_draw.seed >> 32));
@@ -816,14 +833,14 @@ void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float
 
 void add_layer_norm(cudaStream_t s, const float* x, const float* residual, const DropoutDraw* x_draw, const float* gamma,
                     const float* beta, float* sum_out, float* out, const DropoutDraw* out_draw, float* out_dropped, uint64_t rows,
-                    uint64_t h) {
+                    uint64_t h, bool gelu_first) {
     if (rows == 0 || h == 0) return;
     const uint32_t items = static_cast<uint32_t>((h + 31) / 32), blocks = static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
     const DropoutDraw none = {};
     const DropoutDraw first = x_draw ? *x_draw : none, second = out_draw ? *out_draw : none;
     if (out_draw == nullptr || gamma == nullptr) out_dropped = nullptr;
-#define MSX_DROPOUT_LN(N) dropout_add_layer_norm_kernel<N><<<blocks, 256, 0, s>>>(x, residual, first, gamma, beta, sum_out, out, second, out_dropped, r, hh)
+#define MSX_DROPOUT_LN(N) dropout_add_layer_norm_kernel<N><<<blocks, 256, 0, s>>>(x, residual, first, gamma, beta, sum_out, out, second, out_dropped, r, hh, gelu_first)
     if (items <= 1) MSX_DROPOUT_LN(1);
     else if (items <= 2) MSX_DROPOUT_LN(2);
     else if (items <= 4) MSX_DROPOUT_LN(4);
@@ -844,7 +861,7 @@ void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residua
     draw.threshold = threshold;
     draw.scale = scale;
     draw.index_base = index_base;
-    add_layer_norm(s, x, residual, &draw, gamma, beta, sum_out, out, nullptr, nullptr, rows, h);
+    add_layer_norm(s, x, residual, &draw, gamma, beta, sum_out, out, nullptr, nullptr, rows, h, false);
 }
 
 bool layer_norm_backward_supported(uint64_t h) { return h >= 1 && h <= 1024; }
@@ -853,7 +870,8 @@ uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h) { return 
 
 void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
                          uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const float* g1, const float* g2,
-                         const float* g3, const DropoutDraw* adjoint_draw, const DropoutDraw* dx_draw, float* dx_dropped) {
+                         const float* g3, const DropoutDraw* adjoint_draw, const DropoutDraw* dx_draw, float* dx_dropped,
+                         const float* pre_activation) {
     if (h == 0) return;
     uint32_t chunks = backward_chunks(rows);
     uint32_t per = static_cast<uint32_t>((rows + chunks - 1) / chunks);
@@ -862,8 +880,9 @@ void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, con
     uint32_t want = (dgamma ? 1u : 0u) | (dbeta ? 2u : 0u);
     const DropoutDraw none = {};
     const DropoutDraw in_draw = adjoint_draw ? *adjoint_draw : none, out_draw = dx_draw ? *dx_draw : none;
-    if (dx == nullptr || dx_draw == nullptr) dx_dropped = nullptr;
-#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped)
+    if (dx_draw == nullptr && pre_activation == nullptr) dx_dropped = nullptr;
+    if (dx_dropped == nullptr) pre_activation = nullptr;
+#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped, pre_activation)
     if (items <= 1) MSX_LN_BACKWARD(1);
     else if (items <= 2) MSX_LN_BACKWARD(2);
     else if (items <= 4) MSX_LN_BACKWARD(4);

@@ -818,6 +818,31 @@ struct Scheduler {
                 k::Unary op = nd.op == Op::Relu ? k::Unary::Relu : nd.op == Op::Sqrt ? k::Unary::Sqrt
                               : nd.op == Op::Gelu ? k::Unary::Gelu : k::Unary::Copy;
                 uint32_t a = in[0];
+                // gelu with the layer norm of its result (a head's transform): one launch writes both.
+                if (nd.op == Op::Gelu && (fusion_mask() & 1u) && nd.ty.rank() == 2 && k::layer_norm_backward_supported(nd.ty.shape[1])) {
+                    int norm = -1;
+                    for (uint32_t u : users[at]) {
+                        const Node& ln = node(u);
+                        if (ln.op == Op::LayerNorm && !handled[u] && pos(ln.operands[0]) == at && pos(ln.operands[1]) < at && pos(ln.operands[2]) < at) {
+                            norm = static_cast<int>(u);
+                            break;
+                        }
+                    }
+                    if (norm >= 0) {
+                        const uint32_t ln_at = static_cast<uint32_t>(norm);
+                        const uint32_t gamma = pos(node(ln_at).operands[1]), beta = pos(node(ln_at).operands[2]);
+                        handled[ln_at] = 1;
+                        Slot& slot = P->slots[ln_at];
+                        slot.kind = Slot::Arena;
+                        slot.bytes = std::max<uint64_t>(node(ln_at).ty.count() * 4, 4);
+                        const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
+                        emit("gelu_layer_norm", nd, {a, gamma, beta}, {at, ln_at}, [=](cudaStream_t s) {
+                            k::add_layer_norm(s, plan->f(a), nullptr, nullptr, plan->f(gamma), plan->f(beta), plan->f(at), plan->f(ln_at), nullptr,
+                                              nullptr, r, h, true);
+                        });
+                        break;
+                    }
+                }
                 emit(nd.op == Op::Gelu ? "gelu" : "unary", nd, in, {at}, [=](cudaStream_t s) { k::unary(s, op, plan->f(a), plan->f(at), count); });
                 break;
             }
@@ -1406,12 +1431,33 @@ struct Scheduler {
                 dx_draw = draw_of(u);
                 break;
             }
+        // gelu_grad of dx (the dense layer before a gelu and this layer norm) takes that place
+        // instead; a dx that nothing else reads is then not stored.
+        int pre_activation = -1;
+        bool store_dx = true;
+        if (dx >= 0 && dropped < 0 && (fusion_mask() & 16u))
+            for (uint32_t u : users[static_cast<uint32_t>(dx)]) {
+                const Node& un = node(u);
+                if (handled[u] || un.op != Op::GeluGrad || pos(un.operands[1]) != static_cast<uint32_t>(dx) ||
+                    pos(un.operands[0]) >= at || pos(un.operands[0]) == static_cast<uint32_t>(dx) || un.ty.shape != node(x).ty.shape)
+                    continue;
+                dropped = static_cast<int>(u);
+                pre_activation = static_cast<int>(pos(un.operands[0]));
+                store_dx = users[static_cast<uint32_t>(dx)].size() > 1 || is_output_value(static_cast<uint32_t>(dx));
+                break;
+            }
         std::vector<uint32_t> reads = {x}, writes;
         reads.insert(reads.end(), adjoint.begin(), adjoint.end());
         if (gamma >= 0) reads.push_back(static_cast<uint32_t>(gamma));
         if (adjoint_draw.token >= 0) reads.push_back(static_cast<uint32_t>(adjoint_draw.token));
         if (dx_draw.token >= 0) reads.push_back(static_cast<uint32_t>(dx_draw.token));
-        for (int other : {dx, dropped, dgamma, dbeta}) {
+        if (pre_activation >= 0) reads.push_back(static_cast<uint32_t>(pre_activation));
+        if (!store_dx) {
+            handled[static_cast<uint32_t>(dx)] = 1;
+            P->slots[static_cast<uint32_t>(dx)].kind = Slot::Dead;
+        }
+        const int stored_dx = store_dx ? dx : -1;
+        for (int other : {stored_dx, dropped, dgamma, dbeta}) {
             if (other < 0) continue;
             uint32_t u = static_cast<uint32_t>(other);
             handled[u] = 1;
@@ -1428,7 +1474,7 @@ struct Scheduler {
         if (defer) {
             // dx is written here; the column sums stay as chunk sums until the finalize launch.
             std::vector<uint32_t> now;
-            if (dx >= 0) now.push_back(static_cast<uint32_t>(dx));
+            if (stored_dx >= 0) now.push_back(static_cast<uint32_t>(stored_dx));
             if (dropped >= 0) now.push_back(static_cast<uint32_t>(dropped));
             now.push_back(tmp);
             const uint32_t chunks = k::layer_norm_backward_chunks(r);
@@ -1437,11 +1483,11 @@ struct Scheduler {
             float* const wanted = reinterpret_cast<float*>(uintptr_t{1});  // only null or not is read
             emit("layer_norm_backward", nd, reads, now, [=](cudaStream_t s) {
                 const k::DropoutDraw in_draw = draw_now(adjoint_draw), out_draw = draw_now(dx_draw);
-                k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(dx), plan->f(tmp), nullptr,
+                k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(stored_dx), plan->f(tmp), nullptr,
                                        dgamma >= 0 ? wanted : nullptr, dbeta >= 0 ? wanted : nullptr, r, h,
                                        adjoint.size() > 1 ? plan->f(adjoint[1]) : nullptr, adjoint.size() > 2 ? plan->f(adjoint[2]) : nullptr,
                                        adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr, in_draw.token ? &in_draw : nullptr,
-                                       out_draw.token ? &out_draw : nullptr, at_or_null(dropped));
+                                       out_draw.token ? &out_draw : nullptr, at_or_null(dropped), at_or_null(pre_activation));
             });
             return true;
         }
@@ -1449,11 +1495,11 @@ struct Scheduler {
         writes.push_back(tmp);
         emit("layer_norm_backward", nd, reads, writes, [=](cudaStream_t s) {
             const k::DropoutDraw in_draw = draw_now(adjoint_draw), out_draw = draw_now(dx_draw);
-            k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(dx), plan->f(tmp), plan->counter(ctr),
+            k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(stored_dx), plan->f(tmp), plan->counter(ctr),
                                    at_or_null(dgamma), at_or_null(dbeta), r, h,
                                    adjoint.size() > 1 ? plan->f(adjoint[1]) : nullptr, adjoint.size() > 2 ? plan->f(adjoint[2]) : nullptr,
                                    adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr, in_draw.token ? &in_draw : nullptr,
-                                   out_draw.token ? &out_draw : nullptr, at_or_null(dropped));
+                                   out_draw.token ? &out_draw : nullptr, at_or_null(dropped), at_or_null(pre_activation));
         });
         return true;
     }

@@ -543,6 +543,36 @@ def test_the_peer_memory_all_reduce_gives_up_when_no_peer_arrives(device):
         assert_bits_equal(after[q], copies[q], "copy of rank %d" % q)
 
 
+@pytest.mark.parametrize("rows,h,keep_dx", [(64, 128, False), (37, 96, True), (130, 768, False), (9, 33, True)])
+def test_a_gelu_on_either_side_of_a_layer_norm(device, rows, h, keep_dx):
+    """dense -> gelu -> layer norm (a masked-LM head's transform): gelu and the layer norm are one
+    launch that stores both, and in the backward pass gelu_grad is applied to the layer norm's dx by
+    the launch that forms it; dx itself is stored only if something else reads it."""
+    r = rng(rows * 11 + h)
+    p = ProgramText()
+    pre = p.input("pre", "f32", [rows, h]); gamma = p.input("gamma", "f32", [h]); beta = p.input("beta", "f32", [h])
+    g = p.input("g", "f32", [rows, h])
+    act = p.op("Gelu", [rows, h], [pre])
+    y = p.op("LayerNorm", [rows, h], [act, gamma, beta])
+    dx = p.op("LayerNormGradX", [rows, h], [act, gamma, g])
+    dg = p.op("LayerNormGradGamma", [h], [act, g])
+    db = p.op("SumRows", [h], [g])
+    dpre = p.op("GeluGrad", [rows, h], [pre, dx])
+    outputs = [act, y, dg, db, dpre] + ([dx] if keep_dx else [])
+    for value in outputs:
+        p.output(value)
+    feed = {"pre": values(r, rows, h) * 2, "gamma": values(r, h) + 1, "beta": values(r, h), "g": values(r, rows, h)}
+    listing = M.schedule_describe(p.text())
+    kernels = [l.split()[1] for l in listing.strip().splitlines()[:-1]]
+    assert kernels == ["gelu_layer_norm", "layer_norm_backward", "finalize_sums"], listing
+    backward = listing.strip().splitlines()[1]
+    assert ("%%%d" % dx in backward.split("writes")[1].split()) == keep_dx, listing
+    sizes = {act: rows * h, y: rows * h, dg: h, db: h, dpre: rows * h, dx: rows * h}
+    res = run_both(device, p.text(), feed, outputs=[(v, sizes[v]) for v in outputs], seed=1)
+    for (cpu, gpu), value in zip(res, outputs):
+        assert_kernel_close(gpu, cpu, scale=np.full(cpu.shape, max(1.0, float(np.abs(cpu).max()))), what="value %d" % value)
+
+
 def test_bad_inputs_are_refused_like_the_interpreter_refuses_them(device):
     p = ProgramText()
     table = p.input("table", "f32", [5, 4]); ids = p.input("ids", "i32", [3])
