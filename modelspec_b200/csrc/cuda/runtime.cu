@@ -378,6 +378,9 @@ struct Scheduler {
         const uint32_t jobs = static_cast<uint32_t>(deferred.size());
         emit("finalize_sums", pseudo, reads, writes,
              [=](cudaStream_t s) { k::finalize_sums(s, static_cast<const k::SumJob*>(plan->d_sum_jobs), jobs, blocks); });
+        // Issued as soon as the last partial sums exist: what follows them in the backward pass (the
+        // embedding gradients) does not read its results, so it runs beside that.
+        hoist_last_launch();
     }
 
     // A matmul or column-sum launch whose results are first read at least `kSideGap` launches
@@ -386,10 +389,16 @@ struct Scheduler {
     void mark_side_launches() {
         if (!(fusion_mask() & 8u)) return;
         const int count = static_cast<int>(P->launches.size());
-        for (int l = 0; l < count; ++l) {
+        // From the last launch back, so that a reader's own place is known: the side stream runs its
+        // launches in order, so a result that another side launch reads is waited for where that
+        // launch is, not where it is issued.
+        for (int l = count - 1; l >= 0; --l) {
             Launch& launch = P->launches[static_cast<size_t>(l)];
+            // finalize_sums writes outputs (gradients that the optimizer launch reads, and before it
+            // a data-parallel bucket: the bucket waits for the side launches that wrote into it).
+            const bool finalize = launch.kernel == "finalize_sums";
             if (launch.kernel != "matmul" && launch.kernel != "sum_rows" && launch.kernel != "embedding_order" &&
-                launch.kernel != "matmul_jobs" && launch.kernel != "sum_rows_batched")
+                launch.kernel != "matmul_jobs" && launch.kernel != "sum_rows_batched" && !finalize)
                 continue;
             auto stored_as = [this](uint32_t v) {
                 while (P->slots[v].kind == Slot::View) v = P->slots[v].index;
@@ -401,7 +410,7 @@ struct Scheduler {
                 if (P->slots[home].kind != Slot::Arena) eligible = false;
                 // An output is read by the host or a bucket, not by a launch; a value that a later
                 // launch turns into an output in place is read by that launch.
-                if (home == w && w < prog.nodes.size())
+                if (home == w && w < prog.nodes.size() && !finalize)
                     for (const msx::Output& o : prog.outputs)
                         if (pos(o.value) == w) eligible = false;
             }
@@ -409,14 +418,15 @@ struct Scheduler {
             int first_reader = count;
             for (int later = l + 1; later < count; ++later) {
                 const Launch& other = P->launches[static_cast<size_t>(later)];
+                const int needed_at = other.join_before >= 0 ? other.join_before : later;
                 for (uint32_t w : launch.writes) {
                     for (uint32_t r : other.reads)
-                        if (stored_as(r) == stored_as(w)) first_reader = std::min(first_reader, later);
+                        if (stored_as(r) == stored_as(w)) first_reader = std::min(first_reader, needed_at);
                     for (uint32_t again : other.writes)
-                        if (stored_as(again) == stored_as(w)) first_reader = std::min(first_reader, later);
+                        if (stored_as(again) == stored_as(w)) first_reader = std::min(first_reader, needed_at);
                 }
             }
-            if (first_reader == count || first_reader - l < kSideGap) continue;
+            if (first_reader == count || first_reader - l < (finalize ? 3 : kSideGap)) continue;
             launch.join_before = first_reader;
         }
     }
@@ -2224,6 +2234,14 @@ void enqueue_all(msx_plan* P) {
         if (!P->comm) continue;
         for (Bucket& b : P->buckets) {
             if (b.after_launch != static_cast<int>(l)) continue;
+            // Launches that run beside the main stream and have not been waited for yet may have
+            // written gradients of this bucket: the main stream waits for them first.
+            for (size_t earlier = 0; earlier <= l; ++earlier)
+                if (P->launches[earlier].join_before > static_cast<int>(l) && P->side_done[earlier] && !joined[earlier] &&
+                    P->launches[earlier].kernel == "finalize_sums") {
+                    cuda_ok(cudaStreamWaitEvent(P->stream, P->side_done[earlier], 0), "cudaStreamWaitEvent");
+                    joined[earlier] = 1;
+                }
             // The bucket's gradients are complete in stream order: reduce them on the side stream
             // while the rest of backward runs.
             cuda_ok(cudaEventRecord(b.ready, P->stream), "cudaEventRecord");
