@@ -76,6 +76,9 @@ struct Launch {
     // >= 0: the launch runs on the plan's side stream from its place in the list, beside the
     // launches that follow it, and the launch with this index is the first to wait for it.
     int join_before = -1;
+    // A side launch that writes outputs (gradients): a data-parallel bucket that holds them waits
+    // for it before it is reduced.
+    bool side_writes_outputs = false;
     std::function<void(cudaStream_t)> run;
 };
 

@@ -396,7 +396,16 @@ struct Scheduler {
             Launch& launch = P->launches[static_cast<size_t>(l)];
             // finalize_sums writes outputs (gradients that the optimizer launch reads, and before it
             // a data-parallel bucket: the bucket waits for the side launches that wrote into it).
-            const bool finalize = launch.kernel == "finalize_sums";
+            // So does the scatter of a lookup table's gradient that nothing but the optimizer reads
+            // (a position table's, beside the token table's).
+            bool finalize = launch.kernel == "finalize_sums";
+            if (launch.kernel == "embedding_grad" && !launch.writes.empty()) {
+                bool all_outputs = true;
+                for (uint32_t w : launch.writes)
+                    if (w < prog.nodes.size() ? !is_output_value(w) : true) all_outputs = false;
+                finalize = all_outputs;
+                if (!all_outputs) continue;
+            }
             if (launch.kernel != "matmul" && launch.kernel != "sum_rows" && launch.kernel != "embedding_order" &&
                 launch.kernel != "matmul_jobs" && launch.kernel != "sum_rows_batched" && !finalize)
                 continue;
@@ -426,8 +435,9 @@ struct Scheduler {
                         if (stored_as(again) == stored_as(w)) first_reader = std::min(first_reader, needed_at);
                 }
             }
-            if (first_reader == count || first_reader - l < (finalize ? 3 : kSideGap)) continue;
+            if (first_reader == count || first_reader - l < (finalize ? 2 : kSideGap)) continue;
             launch.join_before = first_reader;
+            launch.side_writes_outputs = finalize;
         }
     }
 
@@ -2238,7 +2248,7 @@ void enqueue_all(msx_plan* P) {
             // written gradients of this bucket: the main stream waits for them first.
             for (size_t earlier = 0; earlier <= l; ++earlier)
                 if (P->launches[earlier].join_before > static_cast<int>(l) && P->side_done[earlier] && !joined[earlier] &&
-                    P->launches[earlier].kernel == "finalize_sums") {
+                    P->launches[earlier].side_writes_outputs) {
                     cuda_ok(cudaStreamWaitEvent(P->stream, P->side_done[earlier], 0), "cudaStreamWaitEvent");
                     joined[earlier] = 1;
                 }
