@@ -132,6 +132,30 @@ def test_bert_tiny_step_schedule():
     assert arena < unshared
 
 
+def test_the_forward_program_schedule():
+    """The dropout-free forward program (held-out loss): every residual sum shares a launch with its
+    layer norm, the head's gelu with its layer norm, and nothing runs beside the main stream."""
+    listing = M.schedule_describe(M.compile_mspec(models.bert(), "forward", masked_rows=832))
+    kernels = [l.split()[1] for l in listing.strip().splitlines()[:-1]]
+    assert kernels.count("add_layer_norm") == 5 and "binary" not in kernels and "dropout" not in kernels
+    assert kernels.count("gelu_layer_norm") == 1 and "layer_norm" not in kernels and len(kernels) == 23
+    assert kernels.count("cross_entropy") == 1 and "cross_entropy_with_grad" not in kernels
+    assert " beside " not in listing
+
+
+def test_a_dense_gradient_is_stored_where_its_scatter_adds_to_it():
+    """The tied table of BERT-tiny: the head's weight-gradient product writes the slot of the
+    parameter's gradient (the sum), and the token table's scatter reads and writes that slot."""
+    lines = M.schedule_describe(M.compile_mspec(models.bert(), "step", masked_rows=832)).strip().splitlines()
+    scatter = [l for l in lines if l.split()[1] == "embedding_grad"][-1]
+    target = scatter.split("writes")[1].split()[0]
+    assert target in scatter.split("reads")[1].split("writes")[0].split()
+    product = [l for l in lines if l.split()[1] == "matmul" and l.split("writes")[1].split()[0] == target]
+    assert len(product) == 1 and " beside " in product[0]
+    # The launch the product is waited for at is that scatter.
+    assert product[0].split(" beside ")[1].strip() == scatter.split(":")[0]
+
+
 def test_unschedulable_programs_are_refused():
     with pytest.raises(M.MsxError) as err:
         M.schedule_describe('%0: Tensor<f32, [4, 3]> = Input "p"\n%1: Tensor<f32, [3]> = SigregColumns %0\noutput %1\n')
