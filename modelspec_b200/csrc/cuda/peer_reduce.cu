@@ -3,15 +3,16 @@
 // copies in rank order and stores the sum into slice r of all copies. One kernel per rank, two
 // rendezvous through flag words in peer memory (the copies are complete; the sums have landed).
 //
-// This stands where the reference's data-parallel trainers would call an all-reduce between the
-// backward pass and the optimizer step; the sum of an element is formed by one rank only, in rank
-// order 0 .. world - 1, so every rank holds the same bits and a run is repeatable.
+// The reference trains on one device and has nothing like it: this is the exchange between the
+// backward pass and the optimizer step of a data-parallel run. The sum of an element is formed by
+// one rank only, in rank order 0 .. world - 1, so every rank holds the same bits and a run is
+// repeatable.
 //
 // Why not the library's all-reduce: at 8 ranks it takes 100 us for the 16 MB of a tied embedding
 // table's gradient and 39 us for 4 bytes; each rank here reads 7/8 of the bucket's bytes once and
 // writes them once, all eight NVLink directions busy at the same time.
 //
-// Every wait is bounded by the global timer: a rank that gives up raises bit 2 of *status, marks
+// Every wait is bounded by the global timer: a rank that gives up raises bit 1 of *status, marks
 // the channel failed (later launches return at once) and leaves its copy unsummed.
 #include "common.cuh"
 #include "kernels.cuh"
