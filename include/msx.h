@@ -1,9 +1,13 @@
 /* msx: the C ABI of the B200 CUDA backend for ModelSpec's compiled training step.
  *
  * This is the boundary a `cuda` sibling of the reference's `vulkan` runtime module binds: plain
- * C, opaque handles, host pointers and byte counts, an int status from every call, no exceptions
- * and no unbounded waits. The shim owns every device allocation, stream, graph and communicator;
- * the caller owns host memory, which is copied before a call returns.
+ * C, opaque handles, host pointers and byte counts, an int status from every call, no
+ * exceptions. The library's own waits are bounded: host waits on events take a timeout, and the
+ * spin waits inside its kernels (tensor-core pipeline barriers, the peer-memory all-reduce) give
+ * up after a limit and raise a status bit. Calls into NCCL (communicator set-up, its all-reduce
+ * kernels) are bounded only by NCCL's own settings. The shim owns every device allocation,
+ * stream, graph and communicator; the caller owns host memory, which is copied before a call
+ * returns.
  *
  * What crosses the boundary is the training step in the text form the reference already prints
  * (`modelspec ir --stage training`, crates/modelspec-core/src/ir/print.rs:55-166): the tensor-SSA
@@ -125,6 +129,13 @@ int msx_loss(msx_plan* plan, float* loss, uint32_t timeout_ms);
 int msx_loss_of(msx_plan* plan, uint64_t step_number, float* loss, uint32_t timeout_ms);
 uint64_t msx_steps_submitted(const msx_plan* plan);
 
+/* Device time of submitted step `step_number` in milliseconds, between CUDA events recorded on
+ * the plan's stream before its input copy and after its loss read-back; the last 8 submitted
+ * steps keep theirs. With steps submitted back to back these times add up to the run's: the
+ * per-step view of the reference's training clock (cli/src/train.rs:17-33), from which a host
+ * takes the median step time the reference's benchmarks quote (vulkan/profile.rs:25). */
+int msx_step_ms(msx_plan* plan, uint64_t step_number, float* ms);
+
 /* Waits for every submitted step. */
 int msx_sync(msx_plan* plan, uint32_t timeout_ms);
 
@@ -143,7 +154,10 @@ uint64_t msx_plan_describe(const msx_plan* plan, char* out, uint64_t capacity);
 /* Per-launch device times of one step run kernel by kernel with a CUDA event after each launch
  * (not through the graph): the counterpart of the reference's `--profile` timestamps
  * (vulkan/profile.rs:1-60). `launch_ms` takes launches_per_step floats. The step is a real one:
- * parameters are updated. msx_launch_kernel / _bytes / _flop give each launch's kernel name and
+ * parameters are updated. On a data-parallel plan every rank must make the call together: the
+ * gradient buckets are summed across the ranks (on the plan's stream, outside any launch's time)
+ * before the optimizer launch, so the replicas stay equal, and the launches that hold a
+ * collective make the call run every launch once whatever `repeats` says. msx_launch_kernel / _bytes / _flop give each launch's kernel name and
  * its bytes read + written and FLOP by the reference's counting rule (ir/kernel.rs:1221-1306,
  * :1562-1579). */
 int msx_profile_step(msx_plan* plan, float* launch_ms, uint32_t capacity);
@@ -183,6 +197,12 @@ uint32_t msx_comm_bucket_count(const msx_plan* plan);
  * rank mapped every other rank's arena through CUDA IPC), 0 when by the NCCL all-reduce (a rank
  * could not map a peer, more than 8 ranks, or MSX_PEER_REDUCE=0 in the environment). */
 uint32_t msx_comm_uses_peer_memory(const msx_plan* plan);
+/* How long the optimizer launch of a data-parallel step waits for the gradient exchange after
+ * the backward pass has ended, in milliseconds: runs ONE real step launch by launch (not through
+ * the graph) on the staged inputs, with CUDA events on the plan's stream after the last launch
+ * before the optimizer and right before the optimizer launch. Every rank makes the call together.
+ * 0 for a plan that is not data parallel. */
+int msx_comm_exposed_ms(msx_plan* plan, float* ms);
 /* A check of the peer-memory all-reduce on ONE device: the launches of all `world` (2 to 8)
  * ranks of an emulated job run one after the other over `world` copies of `count` floats.
  * `host_copies[q]` is rank q's copy on the host, replaced by what the copy holds afterwards.
@@ -289,7 +309,8 @@ uint64_t msx_op_matmul_workspace(uint64_t m, uint64_t n, uint64_t k);
  *     (different streams without an ordering between them) race on it: order them. Nothing in
  *     the array has to be cleared between calls, since each call writes every partial sum it
  *     later reads.
- * The result has the bits of the plan's own `sum_rows` launch (same kernels). */
+ * The result has the bits of a plan's `sum_rows`: the same first-stage kernels, the chunk sums
+ * added in the same ascending order (here by a second launch). */
 int msx_sum_rows_static(const float* device_g, uint64_t rows, uint64_t columns, float* device_out, void* stream);
 const char* msx_static_last_error(void);
 

@@ -60,6 +60,8 @@ SIGNATURES = {
     "msx_sync": (C.c_int, [_P, C.c_uint32]),
     "msx_loss_of": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_float), C.c_uint32]),
     "msx_steps_submitted": (C.c_uint64, [_P]),
+    "msx_step_ms": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_float)]),
+    "msx_comm_exposed_ms": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "msx_profile_step": (C.c_int, [_P, C.POINTER(C.c_float), C.c_uint32]),
     "msx_profile_step_repeated": (C.c_int, [_P, C.c_uint32, C.POINTER(C.c_float), C.c_uint32]),
     "msx_launch_kernel": (C.c_char_p, [_P, C.c_uint32]),
@@ -281,6 +283,25 @@ class Plan:
         L = lib()
         return [(L.msx_launch_kernel(self.h, i).decode(), float(ms[i]), L.msx_launch_bytes(self.h, i),
                  L.msx_launch_flop(self.h, i)) for i in range(n)]
+
+    def steps_submitted(self):
+        return int(lib().msx_steps_submitted(self.h))
+
+    def step_ms(self, step_number):
+        """Device time of one of the last 8 submitted steps, in milliseconds."""
+        out = C.c_float()
+        self.device.check(lib().msx_step_ms(self.h, step_number, C.byref(out)))
+        return float(out.value)
+
+    def loss_of(self, step_number, timeout_ms=0):
+        out = C.c_float()
+        self.device.check(lib().msx_loss_of(self.h, step_number, C.byref(out), timeout_ms))
+        return np.float32(out.value)
+
+    def comm_exposed_ms(self):
+        out = C.c_float()
+        self.device.check(lib().msx_comm_exposed_ms(self.h, C.byref(out)))
+        return float(out.value)
 
     def elapsed_ms(self):
         total, steps = C.c_double(), C.c_uint64()

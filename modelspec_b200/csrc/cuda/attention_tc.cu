@@ -2,7 +2,7 @@
 // matmul over every (sequence, head) (gemm_tc.cu, 3xTF32), with two row kernels between them.
 //
 //   forward   S = Q_h K_h^T            -> P = masked softmax(S / sqrt(d))   -> O_h = P V_h
-//   backward  P recomputed as above;  dP = G_h V_h^T;  dS = scale P (dP - rowsum(P dP));
+//   backward  P as the forward left it (or computed again as above);  dP = G_h V_h^T;  dS = scale P (dP - rowsum(P dP));
 //             dV_h = P^T G_h;  dQ_h = dS K_h;  dK_h = dS^T Q_h
 //
 // Heads are addressed in place (row pitch H, head offset a * d), so nothing is gathered or

@@ -20,8 +20,11 @@ inline void check(cudaError_t e, const char* what) {
         throw CudaError(std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")", e);
 }
 
-// After a kernel launch: reports a launch-configuration error without synchronising.
-inline void check_launch(const char* kernel) { check(cudaPeekAtLastError(), kernel); }
+// After a kernel launch: reports a launch-configuration error without synchronising. The error
+// is taken (cudaGetLastError), not peeked at, so a non-sticky error that this thread left behind
+// earlier (the host application's own, or an earlier launch here) is reported once and does not
+// fail every later launch.
+inline void check_launch(const char* kernel) { check(cudaGetLastError(), kernel); }
 
 // ---- GELU, the tanh form evaluated as x / (1 + exp(-2u)) -------------------------------------
 // The operation order is the reference's (crates/modelspec-runtime/src/cpu/interpreter.rs:

@@ -9,7 +9,10 @@
 // allocator at all: its partial sums live in the file-scope device array below, which every GPU
 // that loads the library carries from load to exit (1 MiB).
 //
-// It runs the same two kernels as the plan's `sum_rows` launch, so its result has the same bits.
+// It runs the two-launch form of the column sum (a first stage that leaves chunk sums, the wide
+// one for rows of 1,024 or more columns on 16-byte boundaries, and a second stage that adds the
+// chunks in ascending order). A plan runs the same first stage and adds the chunks in the same
+// order inside that launch or in its finalize launch, so the results agree bit for bit.
 #include <cuda_runtime.h>
 
 #include <cstdio>

@@ -152,14 +152,20 @@ __global__ void __launch_bounds__(kThreads) peer_all_reduce_kernel(PeerReduceArg
             default: reduce_slice<8>(a, lo, hi); break;
         }
     }
+    // A block that gave up marks the channel before it counts itself as finished: the last block
+    // then knows that this rank's slice was not summed everywhere, whichever block it is.
+    if (!ok && threadIdx.x == 0) {
+        atomicOr(a.status, 2u);
+        atomicOr(a.failed, 1u);
+    }
     // The block's stores are out before it counts itself as finished.
     __threadfence_system();
     __syncthreads();
-    if (!last_block_arrives(a.arrivals, gridDim.x, &is_last)) {
-        if (!ok && threadIdx.x == 0) atomicOr(a.status, 2u);
-        return;
-    }
-    // The last block of this rank: every sum of this rank's slice has been stored everywhere.
+    if (!last_block_arrives(a.arrivals, gridDim.x, &is_last)) return;
+    // The last block of this rank: every sum of this rank's slice has been stored everywhere,
+    // unless some block gave up. Then the second rendezvous is not announced: the peers' waits for
+    // it run out and they fail too, instead of going on with a partly summed bucket.
+    ok = ok && *reinterpret_cast<volatile uint32_t*>(a.failed) == 0;
     if (ok) {
         if (threadIdx.x < a.world) {
             __threadfence_system();

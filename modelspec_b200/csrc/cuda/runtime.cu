@@ -141,12 +141,12 @@ struct msx_plan {
     bool blob_dirty = true;  // staged since the last upload
     char* pinned[kStagingSlots] = {};
     float* pinned_loss = nullptr;  // kStagingSlots floats
-    cudaEvent_t slot_done[kStagingSlots] = {};
+    cudaEvent_t slot_begin[kStagingSlots] = {}, slot_done[kStagingSlots] = {};  // around each submitted step
     bool slot_used[kStagingSlots] = {};
     std::vector<float> consts;
     float* d_consts = nullptr;
     uint32_t* d_status = nullptr;
-    uint32_t* pinned_status = nullptr;
+    uint32_t* pinned_status = nullptr;  // kStagingSlots words: the device status word as each step left it
     // Arrival counters of the one-launch two-stage reductions: zero between launches.
     uint32_t* d_counters = nullptr;
     uint32_t counters_used = 0;
@@ -189,6 +189,9 @@ struct msx_plan {
     float* d_weight_total = nullptr;
     cudaEvent_t step_begun = nullptr, weights_summed = nullptr, loss_ready = nullptr, loss_reduced = nullptr;
     bool loss_in_flight = false;     // set while a step is being enqueued
+    // msx_comm_exposed_ms: recorded on the main stream after the last launch before the optimizer
+    // and right before the optimizer launch (after the waits for the buckets), when set.
+    cudaEvent_t probe_backward_done = nullptr, probe_update_begins = nullptr;
     uint64_t bucket_bytes = 25u << 20;
     // Gradient buckets are summed by this backend's own kernel over peer memory when every rank
     // could map every other rank's arena (CUDA IPC, one process per GPU of one machine); otherwise
@@ -1970,11 +1973,12 @@ void allocate(msx_plan* P, const Scheduler& sched) {
     P->blob.assign(in_bytes, 0);
     for (int s = 0; s < kStagingSlots; ++s) {
         cuda_ok(cudaMallocHost(&P->pinned[s], in_bytes), "cudaMallocHost(staging)");
-        cuda_ok(cudaEventCreateWithFlags(&P->slot_done[s], cudaEventDisableTiming), "cudaEventCreate");
+        cuda_ok(cudaEventCreate(&P->slot_begin[s]), "cudaEventCreate");
+        cuda_ok(cudaEventCreate(&P->slot_done[s]), "cudaEventCreate");
     }
     cuda_ok(cudaMallocHost(&P->pinned_loss, kStagingSlots * sizeof(float)), "cudaMallocHost(loss)");
-    cuda_ok(cudaMallocHost(&P->pinned_status, sizeof(uint32_t)), "cudaMallocHost(status)");
-    *P->pinned_status = 0;
+    cuda_ok(cudaMallocHost(&P->pinned_status, kStagingSlots * sizeof(uint32_t)), "cudaMallocHost(status)");
+    std::memset(P->pinned_status, 0, kStagingSlots * sizeof(uint32_t));
     uint64_t const_bytes = std::max<uint64_t>(P->consts.size() * 4, 4);
     cuda_ok(cudaMalloc(&P->d_consts, const_bytes), "cudaMalloc(constants)");
     if (!P->consts.empty())
@@ -2081,6 +2085,7 @@ void release(msx_plan* P) {
     cudaFree(P->d_row_sum_jobs);
     for (int s = 0; s < kStagingSlots; ++s) {
         if (P->pinned[s]) cudaFreeHost(P->pinned[s]);
+        if (P->slot_begin[s]) cudaEventDestroy(P->slot_begin[s]);
         if (P->slot_done[s]) cudaEventDestroy(P->slot_done[s]);
     }
     if (P->pinned_loss) cudaFreeHost(P->pinned_loss);
@@ -2230,8 +2235,10 @@ void enqueue_all(msx_plan* P) {
                 joined[earlier] = 1;
             }
         if (P->comm && static_cast<int>(l) == P->optimizer_launch) {
+            if (P->probe_backward_done) cuda_ok(cudaEventRecord(P->probe_backward_done, P->stream), "cudaEventRecord");
             for (Bucket& b : P->buckets) cuda_ok(cudaStreamWaitEvent(P->stream, b.done, 0), "cudaStreamWaitEvent");
             join_loss(P);
+            if (P->probe_update_begins) cuda_ok(cudaEventRecord(P->probe_update_begins, P->stream), "cudaEventRecord");
         }
         if (P->launches[l].join_before >= 0 && P->side_stream && P->side_fork[l]) {
             cuda_ok(cudaEventRecord(P->side_fork[l], P->stream), "cudaEventRecord");
@@ -2277,6 +2284,18 @@ int wait_event(cudaEvent_t event, uint32_t timeout_ms) {
     }
 }
 
+// The device status word as the step of staging slot `slot` left it (copied out behind the step's
+// loss): a raised bit means the results of that step, and of every later one, are not valid. The
+// word is sticky on the device until this clears it.
+void check_status(msx_plan* P, int slot) {
+    const uint32_t bits = P->pinned_status[slot];
+    if (!bits) return;
+    for (int s = 0; s < kStagingSlots; ++s) P->pinned_status[s] = 0;
+    cuda_ok(cudaMemsetAsync(P->d_status, 0, 4, P->stream), "cudaMemsetAsync");
+    if (bits & 2u) throw StatusError(MSX_TIMEOUT, "a bounded wait on the device ran out (tensor-core matmul, or a peer rank of the gradient all-reduce); the step's results are not valid");
+    throw StatusError(MSX_BAD_INPUT, "an embedding id computed on the device is outside its table");
+}
+
 int wait_all(msx_plan* P, uint32_t timeout_ms) {
     if (P->steps == 0) {
         cuda_ok(cudaStreamSynchronize(P->stream), "cudaStreamSynchronize");
@@ -2285,13 +2304,7 @@ int wait_all(msx_plan* P, uint32_t timeout_ms) {
     int slot = static_cast<int>((P->steps - 1) % kStagingSlots);
     int rc = wait_event(P->slot_done[slot], timeout_ms == 0 ? 600000u : timeout_ms);
     if (rc != MSX_OK) return rc;
-    if (*P->pinned_status) {
-        uint32_t bits = *P->pinned_status;
-        *P->pinned_status = 0;
-        cuda_ok(cudaMemsetAsync(P->d_status, 0, 4, P->stream), "cudaMemsetAsync");
-        if (bits & 2u) throw StatusError(MSX_TIMEOUT, "a bounded wait on the device ran out (tensor-core matmul, or a peer rank of the gradient all-reduce); the step's results are not valid");
-        throw StatusError(MSX_BAD_INPUT, "an embedding id computed on the device is outside its table");
-    }
+    check_status(P, slot);
     return MSX_OK;
 }
 
@@ -2389,6 +2402,17 @@ const char* msx_last_error(const msx_device* device) { return device ? device->e
 void msx_internal_set_error(msx_device* device, const char* message) {
     if (device) device->error = message ? message : "";
     else g_open_error = message ? message : "";
+}
+
+// For the tests: sets the low byte of the plan's device status word in stream order, as a kernel
+// whose bounded wait ran out (bit 1) or that met a bad id (bit 0) would, without any kernel
+// misbehaving. Not part of the ABI.
+int msx_internal_raise_status(msx_plan* plan, uint32_t bits) {
+    if (!plan) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        cuda_ok(cudaMemsetAsync(plan->d_status, static_cast<int>(bits & 0xffu), 1, plan->stream), "cudaMemsetAsync(status)");
+        return MSX_OK;
+    });
 }
 
 int msx_plan_create(msx_device* device, const char* ir_text, uint64_t seed, uint32_t flags, msx_plan* shares,
@@ -2520,6 +2544,7 @@ int msx_run(msx_plan* plan) {
             if (rc != MSX_OK) throw StatusError(rc, "msx_run: a step submitted " + std::to_string(kStagingSlots) + " steps ago has not finished");
         }
         if (plan->clock_steps == 0) cuda_ok(cudaEventRecord(plan->clock_start, plan->stream), "cudaEventRecord");
+        cuda_ok(cudaEventRecord(plan->slot_begin[slot], plan->stream), "cudaEventRecord");
         if (plan->input_bytes && plan->blob_dirty) {
             plan->blob_dirty = false;
             std::memcpy(plan->pinned[slot], plan->blob.data(), plan->input_bytes);
@@ -2550,7 +2575,7 @@ int msx_run(msx_plan* plan) {
             cuda_ok(cudaMemcpyAsync(plan->pinned_loss + slot, plan->ptr(static_cast<uint32_t>(plan->loss_pos)), 4, cudaMemcpyDeviceToHost,
                                     plan->stream),
                     "cudaMemcpyAsync(loss)");
-        cuda_ok(cudaMemcpyAsync(plan->pinned_status, plan->d_status, 4, cudaMemcpyDeviceToHost, plan->stream), "cudaMemcpyAsync(status)");
+        cuda_ok(cudaMemcpyAsync(plan->pinned_status + slot, plan->d_status, 4, cudaMemcpyDeviceToHost, plan->stream), "cudaMemcpyAsync(status)");
         cuda_ok(cudaEventRecord(plan->clock_stop, plan->stream), "cudaEventRecord");
         cuda_ok(cudaEventRecord(plan->slot_done[slot], plan->stream), "cudaEventRecord");
         plan->slot_used[slot] = true;
@@ -2586,6 +2611,7 @@ int msx_loss_of(msx_plan* plan, uint64_t step_number, float* loss, uint32_t time
         int slot = static_cast<int>(step_number % kStagingSlots);
         int rc = wait_event(plan->slot_done[slot], timeout_ms == 0 ? 600000u : timeout_ms);
         if (rc != MSX_OK) return rc;
+        check_status(plan, slot);
         *loss = plan->pinned_loss[slot];
         return MSX_OK;
     });
@@ -2604,28 +2630,82 @@ int msx_profile_step_repeated(msx_plan* plan, uint32_t repeats, float* launch_ms
         cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
         int rc = wait_all(plan, 0);
         if (rc != MSX_OK) return rc;
-        std::vector<cudaEvent_t> events(plan->launches.size() + 1);
+        // A data-parallel step holds collectives (the loss and weight sums inside the cross-entropy
+        // launch, the gradient buckets before the update): every launch is then issued once, and
+        // the buckets are summed across the ranks before the optimizer launch, so that the
+        // replicas stay equal as after any other step.
+        if (plan->comm) repeats = 1;
+        const size_t count = plan->launches.size();
+        std::vector<cudaEvent_t> events(2 * count);
         for (cudaEvent_t& e : events) cuda_ok(cudaEventCreate(&e), "cudaEventCreate");
         if (plan->input_bytes) {
             std::memcpy(plan->pinned[0], plan->blob.data(), plan->input_bytes);
             cuda_ok(cudaMemcpyAsync(plan->d_inputs, plan->pinned[0], plan->input_bytes, cudaMemcpyHostToDevice, plan->stream), "cudaMemcpyAsync");
         }
         begin_side_work(plan);
-        cuda_ok(cudaEventRecord(events[0], plan->stream), "cudaEventRecord");
-        for (size_t l = 0; l < plan->launches.size(); ++l) {
+        for (size_t l = 0; l < count; ++l) {
             const std::string& kernel = plan->launches[l].kernel;
             const bool in_place = kernel == "adamw_multi_tensor" || kernel == "sgd_multi_tensor";
+            if (plan->comm && static_cast<int>(l) == plan->optimizer_launch) {
+                for (const Bucket& b : plan->buckets)
+                    all_reduce(plan, reinterpret_cast<float*>(plan->arena + b.offset), b.bytes / 4, plan->average_gradients, plan->stream, false);
+                join_loss(plan);
+            }
+            cuda_ok(cudaEventRecord(events[2 * l], plan->stream), "cudaEventRecord");
             for (uint32_t r = 0; r < (in_place ? 1u : repeats); ++r) plan->launches[l].run(plan->stream);
-            cuda_ok(cudaEventRecord(events[l + 1], plan->stream), "cudaEventRecord");
+            cuda_ok(cudaEventRecord(events[2 * l + 1], plan->stream), "cudaEventRecord");
         }
         join_loss(plan);
         cuda_ok(cudaStreamSynchronize(plan->stream), "cudaStreamSynchronize");
-        for (size_t l = 0; l < plan->launches.size(); ++l) {
-            cuda_ok(cudaEventElapsedTime(&launch_ms[l], events[l], events[l + 1]), "cudaEventElapsedTime");
+        for (size_t l = 0; l < count; ++l) {
+            cuda_ok(cudaEventElapsedTime(&launch_ms[l], events[2 * l], events[2 * l + 1]), "cudaEventElapsedTime");
             const std::string& kernel = plan->launches[l].kernel;
             if (kernel != "adamw_multi_tensor" && kernel != "sgd_multi_tensor") launch_ms[l] /= static_cast<float>(repeats);
         }
         for (cudaEvent_t e : events) cudaEventDestroy(e);
+        return MSX_OK;
+    });
+}
+
+int msx_step_ms(msx_plan* plan, uint64_t step_number, float* ms) {
+    if (!plan || !ms) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        if (step_number >= plan->steps || step_number + kStagingSlots < plan->steps)
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_step_ms: only the last " + std::to_string(kStagingSlots) + " submitted steps keep their time");
+        int slot = static_cast<int>(step_number % kStagingSlots);
+        int rc = wait_event(plan->slot_done[slot], 600000u);
+        if (rc != MSX_OK) return rc;
+        cuda_ok(cudaEventElapsedTime(ms, plan->slot_begin[slot], plan->slot_done[slot]), "cudaEventElapsedTime");
+        return MSX_OK;
+    });
+}
+
+int msx_comm_exposed_ms(msx_plan* plan, float* ms) {
+    if (!plan || !ms) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        *ms = 0.0f;
+        if (!plan->comm || plan->optimizer_launch < 0) return MSX_OK;
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        int rc = wait_all(plan, 0);
+        if (rc != MSX_OK) return rc;
+        cudaEvent_t before = nullptr, after = nullptr;
+        cuda_ok(cudaEventCreate(&before), "cudaEventCreate");
+        cuda_ok(cudaEventCreate(&after), "cudaEventCreate");
+        plan->probe_backward_done = before;
+        plan->probe_update_begins = after;
+        try {
+            enqueue_all(plan);
+            cuda_ok(cudaStreamSynchronize(plan->stream), "cudaStreamSynchronize");
+            cuda_ok(cudaEventElapsedTime(ms, before, after), "cudaEventElapsedTime");
+        } catch (...) {
+            plan->probe_backward_done = plan->probe_update_begins = nullptr;
+            cudaEventDestroy(before);
+            cudaEventDestroy(after);
+            throw;
+        }
+        plan->probe_backward_done = plan->probe_update_begins = nullptr;
+        cudaEventDestroy(before);
+        cudaEventDestroy(after);
         return MSX_OK;
     });
 }

@@ -8,14 +8,16 @@ and final parameter of the linear-regression training log
 two examples (crates/modelspec-cli/tests/golden/*.training.ir) and the lowered BERT-tiny program
 (website/docs/examples/bert-tiny.md). BLAKE3 digests come from the `blake3` Python package.
 Run it where the reference is checked out (the committed fixtures are what travels):
-`python tests/golden/make_goldens.py <reference checkout>` or MODELSPEC_REFERENCE=<checkout>.
+`python tests/golden/make_goldens.py <reference checkout>`.
 """
 import json
 import os
 import re
 import sys
 
-REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MODELSPEC_REFERENCE", os.path.join(os.sep, "root", "reference"))
+if len(sys.argv) != 2:
+    raise SystemExit(__doc__)
+REF = sys.argv[1]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

@@ -528,12 +528,14 @@ def test_the_peer_memory_all_reduce_sums_every_slice_in_rank_order(device, world
         assert_bits_equal(after[q], want, "copy of rank %d" % q)
 
 
-def test_the_peer_memory_all_reduce_gives_up_when_no_peer_arrives(device):
-    """Rank 0's launch with no other rank running: its wait ends after the limit, the copies are
-    left alone, the status word says so, and the next launch on the channel returns at once."""
+@pytest.mark.parametrize("count", [4096, 40000])
+def test_the_peer_memory_all_reduce_gives_up_when_no_peer_arrives(device, count):
+    """Rank 0's launch with no other rank running (one block, and ten blocks that all give up
+    side by side): its wait ends after the limit, the copies are left alone, the status word says
+    so, and the next launch on the channel returns at once."""
     import time
     r = rng(77)
-    copies = [values(r, 4096) for _ in range(2)]
+    copies = [values(r, count) for _ in range(2)]
     start = time.monotonic()
     after, status = device.peer_reduce_check(copies, peers_present=False, wait_ms=200)
     elapsed = time.monotonic() - start
@@ -598,3 +600,36 @@ def test_an_op_without_a_kernel_is_refused_at_plan_creation(device):
     with pytest.raises(M.MsxError) as err:
         M.Plan(device, text)
     assert err.value.status == M.UNSUPPORTED and "SigregColumns" in str(err.value)
+
+
+def test_a_raised_status_word_is_reported_by_the_lagged_loss_read_and_step_times_add_up(device):
+    """A host that reads losses a few steps behind the one it submits learns of a bounded wait
+    that ran out from that read, not only from a later sync: the status word is staged with each
+    step's loss. The word is set here by a memset in stream order (no kernel misbehaves)."""
+    import ctypes as C
+    p = ProgramText()
+    a = p.input("a", "f32", [8, 4]); b = p.input("b", "f32", [8, 4])
+    loss = p.op("Mse", [], [a, b])
+    p.output(loss)
+    plan = M.Plan(device, p.text())
+    try:
+        plan.set_input("a", np.ones(32, dtype=np.float32)); plan.set_input("b", np.zeros(32, dtype=np.float32))
+        for _ in range(3):
+            plan.run()
+        assert plan.loss_of(1) == np.float32(1.0)
+        times = [plan.step_ms(k) for k in range(3)]
+        assert all(0.0 < t < 50.0 for t in times), times
+        raise_status = M.lib().msx_internal_raise_status
+        raise_status.argtypes = [C.c_void_p, C.c_uint32]
+        assert raise_status(plan.h, 2) == M.OK
+        plan.run()
+        plan.run()
+        with pytest.raises(M.MsxError) as err:
+            plan.loss_of(3)
+        assert err.value.status == M.TIMEOUT
+        # The report cleared the word: later steps run and read normally.
+        plan.run()
+        assert plan.loss_of(5) == np.float32(1.0)
+        plan.sync()
+    finally:
+        plan.destroy()

@@ -138,6 +138,27 @@ def test_bert_tiny_at_full_size_with_the_masked_row_gather(device):
     assert stats["launches_per_step"] < 200
 
 
+def test_bert_mini_at_full_size(device):
+    """BERT-mini (4 layers, hidden 256, 4 heads, feed-forward 1024, vocabulary 30,522, 32 x 128
+    tokens, 832 gathered rows): the data-parallel configuration's per-GPU step, two steps and the
+    final loss through the default tensor-core plan."""
+    cfg = models.CONFIGS["bert_mini"]
+    source = cfg["source"](steps=2, warmup_steps=1)
+    out = train_both(device, source, 2, masked_rows=models.default_masked_rows(cfg["rows"]),
+                     feed=bert_feed(cfg["vocab"], cfg["seq"], cfg["batch"]))
+    check_run(out, "bert mini", key_bias_atol=1e-4 + 2 * 1e-4 * 1e-3)
+
+
+def test_bert_base_shaped_twin(device):
+    """The shapes of the BERT-base configuration that no smaller test meets: hidden 768 in 12
+    heads of 64, feed-forward 3072, 512 keys per sequence, vocabulary 30,522 behind the gather;
+    one layer and two sequences keep the CPU side to seconds."""
+    source = models.bert(name="BertBase", layers=1, hidden=768, heads=12, ffn=3072, vocab=30522, seq=512, batch=2,
+                         steps=2, warmup_steps=1)
+    out = train_both(device, source, 2, masked_rows=models.default_masked_rows(1024), feed=bert_feed(30522, 512, 2))
+    check_run(out, "bert base twin", key_bias_atol=1e-4 + 2 * 1e-4 * 1e-3)
+
+
 @pytest.mark.parametrize("source,steps,kwargs", [
     (models.linear_regression(), 60, dict(synthetic=True)),
     (models.two_layer_relu(), 60, dict(synthetic=True)),

@@ -50,6 +50,27 @@ def test_static_sum_rows_matches_the_plan_twice_in_a_row(device):
         assert np.array_equal(got, expected), "the same kernels give the same bits"
 
 
+@pytest.mark.parametrize("rows,h", [(833, 1024), (100, 2048), (4096, 4096), (7, 12)])
+def test_static_sum_rows_wide_rows_and_a_stream_of_the_callers(device, rows, h):
+    """Rows of 1,024 or more columns take the wide first stage; 4,096 columns is the most the
+    scratch holds; 7 rows are one chunk. The call is made on a stream of the caller's, not the
+    default one, and still has the plan's bits."""
+    import torch
+
+    L = M.lib()
+    g = np.random.default_rng(rows + h).standard_normal((rows, h)).astype(np.float32)
+    expected = plan_sum_rows(device, g)
+    d_g = torch.from_numpy(g).to("cuda:0")
+    d_out = torch.full((h,), float("nan"), dtype=torch.float32, device="cuda:0")
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream(device="cuda:0")
+    rc = L.msx_sum_rows_static(C.c_void_p(d_g.data_ptr()), rows, h, C.c_void_p(d_out.data_ptr()), C.c_void_p(stream.cuda_stream))
+    assert rc == M.OK, L.msx_static_last_error().decode()
+    stream.synchronize()
+    got = d_out.cpu().numpy()
+    assert np.array_equal(got, expected), "the chunk sums are added in the same order"
+
+
 def test_static_sum_rows_refuses_what_its_scratch_cannot_hold(device):
     import torch
 
