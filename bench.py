@@ -299,7 +299,6 @@ def main():
         barrier()
         assert counted == K
         block_ms.append(max_over_ranks(ms) / K)
-    clocks = sampler.stop()
     resident_ms = float(np.median(block_ms))
     median_ms = max_over_ranks(float(np.median(step_ms)))
 
@@ -323,6 +322,7 @@ def main():
     barrier()
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3
     e2e_ms = max_over_ranks(max(e2e_device_ms, e2e_wall_ms)) / K
+    clocks = sampler.stop()   # sampled through both timed legs
     assert all(np.isfinite(l) for l in losses), "a loss of the timed run is not finite"
 
     exposed_comm_ms = None
