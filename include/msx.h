@@ -46,8 +46,20 @@ enum {
 enum {
     MSX_PLAN_DEFAULT = 0,
     MSX_PLAN_NO_GRAPH = 1,  /* launch kernels one by one instead of through one CUDA graph */
-    MSX_PLAN_EXACT_MATMUL = 2 /* matmuls as f32 fused chains in ascending k, the bits of the
-                                 reference's CPU loop, instead of 3xTF32 on the tensor cores */
+    MSX_PLAN_EXACT_MATMUL = 2, /* matmuls as f32 fused chains in ascending k, the bits of the
+                                  reference's CPU loop, instead of 3xTF32 on the tensor cores */
+    MSX_PLAN_BF16 = 4          /* mixed precision, an extension: the reference's IR has f32 and i32
+                                  only (ir/tensor.rs:38-51). Every rank-2 intermediate (activations
+                                  and their adjoints) is stored as bf16 and every product runs as
+                                  bf16 x bf16 with f32 accumulation on TMA-fed tcgen05.mma; parameters,
+                                  AdamW moments, gradients, row statistics, losses and all sums stay
+                                  f32, and the optimizer launch writes a bf16 working copy of every
+                                  matrix parameter beside its f32 master. Tolerance class against the
+                                  f32 CPU run: losses within 2e-2 relative over 100 steps of the
+                                  BERT twin. Refused (MSX_UNSUPPORTED) for a program with an op that
+                                  has no bf16 kernel, a matmul operand that is a host input, or a
+                                  matrix whose row width is not a multiple of 8 (vocabulary-wide
+                                  logits are padded). Not combinable with MSX_PLAN_EXACT_MATMUL. */
 };
 
 typedef struct msx_stats {
@@ -175,6 +187,9 @@ uint64_t msx_launch_flop(const msx_plan* plan, uint32_t launch);
  * line of totals: what `modelspec ir --stage kernel` is to the Vulkan backend. Returns 0 with
  * the reason in msx_last_error(NULL) when the program cannot be scheduled. */
 uint64_t msx_schedule_describe(const char* ir_text, char* out, uint64_t capacity);
+/* The same under plan flags (MSX_PLAN_EXACT_MATMUL, MSX_PLAN_BF16): a value that a mixed-precision
+ * plan stores as bf16 is listed with the suffix `h`. */
+uint64_t msx_schedule_describe_with(const char* ir_text, uint32_t flags, char* out, uint64_t capacity);
 
 /* Device time of the steps run since the last call, in milliseconds, measured with CUDA events
  * on the plan's stream around each msx_run: the reference's training clock (cli/src/train.rs:
@@ -291,6 +306,15 @@ int msx_training_check_finite(msx_training* training);
 int msx_op_matmul(const float* a, int a_transposed, const float* b, int b_transposed, float* c, uint64_t m, uint64_t n,
                   uint64_t k, float* workspace, uint64_t workspace_floats, uint32_t* status, void* stream, int exact);
 uint64_t msx_op_matmul_workspace(uint64_t m, uint64_t n, uint64_t k);
+
+/* The same for the mixed-precision kernel: `a` and `b` are bf16 device matrices (dense, on 16-byte
+ * boundaries, row widths multiples of 8 elements), `c` is bf16 or f32 by `c_is_bf16`; the product
+ * is formed by tcgen05.mma kind::f16 from TMA-loaded tiles with f32 accumulation. The reference
+ * has no 16-bit type (ir/tensor.rs:38-51); this is the product a plan made with MSX_PLAN_BF16 runs.
+ * `workspace` holds msx_op_matmul_bf16_workspace(m, n, k) floats (a split k; 0 otherwise). */
+int msx_op_matmul_bf16(const void* a, int a_transposed, const void* b, int b_transposed, void* c, int c_is_bf16, uint64_t m,
+                       uint64_t n, uint64_t k, float* workspace, uint64_t workspace_floats, uint32_t* status, void* stream);
+uint64_t msx_op_matmul_bf16_workspace(uint64_t m, uint64_t n, uint64_t k);
 
 /* Column sums without any allocation: out[c] = sum over rows of g[r, c] for a row-major
  * [rows, columns] device matrix, the `SumRows` of a bias gradient. This function has no

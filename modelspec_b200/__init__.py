@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libmsx.so")
 
 OK, BAD_ARGUMENT, NO_DEVICE, OUT_OF_MEMORY, UNSUPPORTED, LAUNCH_FAILED, NON_FINITE, TIMEOUT, BAD_INPUT = range(9)
-PLAN_DEFAULT, PLAN_NO_GRAPH, PLAN_EXACT_MATMUL = 0, 1, 2
+PLAN_DEFAULT, PLAN_NO_GRAPH, PLAN_EXACT_MATMUL, PLAN_BF16 = 0, 1, 2, 4
 
 STATUS_NAMES = ["MSX_OK", "MSX_BAD_ARGUMENT", "MSX_NO_DEVICE", "MSX_OUT_OF_MEMORY", "MSX_UNSUPPORTED",
                 "MSX_LAUNCH_FAILED", "MSX_NON_FINITE", "MSX_TIMEOUT", "MSX_BAD_INPUT"]
@@ -72,6 +72,7 @@ SIGNATURES = {
     "msx_plan_stats": (C.c_int, [_P, C.POINTER(Stats)]),
     "msx_plan_describe": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
     "msx_schedule_describe": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_uint64]),
+    "msx_schedule_describe_with": (C.c_uint64, [C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint64]),
     "msx_elapsed_ms": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "msx_comm_unique_id": (C.c_int, [_P]),
     "msx_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P]),
@@ -96,6 +97,8 @@ SIGNATURES = {
     "msx_training_check_finite": (C.c_int, [_P]),
     "msx_op_matmul": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_uint64, C.c_uint64, C.c_uint64, _P, C.c_uint64, _P, _P, C.c_int]),
     "msx_op_matmul_workspace": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
+    "msx_op_matmul_bf16": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, _P, C.c_uint64, _P, _P]),
+    "msx_op_matmul_bf16_workspace": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
     "msx_sum_rows_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, _P, _P]),
     "msx_static_last_error": (C.c_char_p, []),
     "msx_compile": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_uint64, C.c_char_p, C.c_uint64]),
@@ -137,9 +140,10 @@ def compile_mspec(source, which="step", masked_rows=0):
     return _text(lambda buf, cap: lib().msx_compile(source.encode(), which.encode(), masked_rows, buf, cap))
 
 
-def schedule_describe(ir_text):
-    """The kernel launches the backend schedules for a program, one per line; needs no GPU."""
-    return _text(lambda buf, cap: lib().msx_schedule_describe(ir_text.encode(), buf, cap))
+def schedule_describe(ir_text, flags=PLAN_DEFAULT):
+    """The kernel launches the backend schedules for a program, one per line; needs no GPU. Under
+    PLAN_BF16 the values stored as bf16 carry the suffix `h`."""
+    return _text(lambda buf, cap: lib().msx_schedule_describe_with(ir_text.encode(), flags, buf, cap))
 
 
 def comm_unique_id():

@@ -8,7 +8,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libmsx.so")
 
-SOURCES = ["cuda/pointwise.cu", "cuda/reduce.cu", "cuda/rowwise.cu", "cuda/embedding.cu", "cuda/gemm.cu", "cuda/gemm_tc.cu",
+SOURCES = ["cuda/pointwise.cu", "cuda/reduce.cu", "cuda/rowwise.cu", "cuda/embedding.cu", "cuda/gemm.cu", "cuda/gemm_tc.cu", "cuda/gemm_bf16.cu",
            "cuda/attention.cu", "cuda/attention_tc.cu", "cuda/optimizer.cu", "cuda/runtime.cu", "cuda/noalloc.cu", "cuda/peer_reduce.cu", "host/training.cpp"]
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

@@ -116,5 +116,100 @@ void attention_tc_backward(cudaStream_t s, const float* q, const float* k, const
     if (dk) matmul_tc_batched(s, transposed(hd.scores(dp)), hd.q(q), hd.kv(dk), hd.s, hd.d, hd.l, hd.b, hd.a, status);
 }
 
+// ---- mixed precision ----------------------------------------------------------------------------
+// The same launches for a plan that stores activations as bf16: the products run on the bf16
+// kernel (gemm_bf16.cu), scores and their adjoints are written in f32 (a scratch matrix that only
+// the row kernel after it reads), and the row kernels store the probabilities and the score
+// gradients as bf16 for the products that follow.
+
+namespace {
+
+// One warp per score row: p = softmax over the unmasked keys of scores * scale, stored as bf16.
+__global__ void masked_softmax_half_kernel(const float* __restrict__ scores, const float* __restrict__ mask, bf16* __restrict__ p,
+                                           uint32_t rows, uint32_t rows_per_sequence, uint32_t s, float scale) {
+    uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    int lane = threadIdx.x & 31;
+    const float* x = scores + static_cast<uint64_t>(row) * s;
+    bf16* out = p + static_cast<uint64_t>(row) * s;
+    const float* m = mask + static_cast<uint64_t>(row / rows_per_sequence) * s;
+    float best = -INFINITY;
+    for (uint32_t j = lane; j < s; j += 32)
+        if (m[j] != 0.0f) best = fmaxf(best, x[j] * scale);
+    best = warp_max(best);
+    float total = 0.0f;
+    for (uint32_t j = lane; j < s; j += 32) total += m[j] != 0.0f ? expf(x[j] * scale - best) : 0.0f;
+    total = warp_sum(total);
+    for (uint32_t j = lane; j < s; j += 32) out[j] = __float2bfloat16_rn(m[j] != 0.0f ? expf(x[j] * scale - best) / total : 0.0f);
+}
+
+// dS = scale * P * (dP - sum_j P dP), stored as bf16.
+__global__ void score_grad_half_kernel(const bf16* __restrict__ p, const float* __restrict__ dp, bf16* __restrict__ ds, uint32_t rows,
+                                       uint32_t s, float scale) {
+    uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    int lane = threadIdx.x & 31;
+    const bf16* pr = p + static_cast<uint64_t>(row) * s;
+    const float* dr = dp + static_cast<uint64_t>(row) * s;
+    bf16* out = ds + static_cast<uint64_t>(row) * s;
+    float dot = 0.0f;
+    for (uint32_t j = lane; j < s; j += 32) dot = fmaf(__bfloat162float(pr[j]), dr[j], dot);
+    dot = warp_sum(dot);
+    for (uint32_t j = lane; j < s; j += 32) out[j] = __float2bfloat16_rn(__bfloat162float(pr[j]) * (dr[j] - dot) * scale);
+}
+
+struct HalfHeads {
+    Heads hd;
+    HalfMatrix q(const void* x, bool transposed = false) const { return {x, hd.h, static_cast<uint64_t>(hd.l) * hd.h, hd.d, transposed}; }
+    HalfMatrix kv(const void* x, bool transposed = false) const { return {x, hd.h, static_cast<uint64_t>(hd.s) * hd.h, hd.d, transposed}; }
+    HalfMatrix scores(const void* x, bool transposed = false) const {
+        return {x, hd.s, static_cast<uint64_t>(hd.a) * hd.l * hd.s, static_cast<uint64_t>(hd.l) * hd.s, transposed};
+    }
+    HalfResult to_q(void* x) const { return {x, true, hd.h, static_cast<uint64_t>(hd.l) * hd.h, hd.d}; }
+    HalfResult to_kv(void* x) const { return {x, true, hd.h, static_cast<uint64_t>(hd.s) * hd.h, hd.d}; }
+    HalfResult to_scores(float* x) const { return {x, false, hd.s, static_cast<uint64_t>(hd.a) * hd.l * hd.s, static_cast<uint64_t>(hd.l) * hd.s}; }
+};
+
+void half_probabilities(cudaStream_t s, const void* q, const void* k, const float* mask, void* p, float* scores, const HalfHeads& hh,
+                        uint32_t* status) {
+    const Heads& hd = hh.hd;
+    // S[i, j] = sum_c q[i, c] k[j, c]: B is the keys stored [n, k].
+    matmul_bf16(s, hh.q(q), hh.kv(k, true), hh.to_scores(scores), hd.l, hd.s, hd.d, hd.b, hd.a, nullptr, nullptr, status);
+    const uint32_t rows = hd.rows();
+    masked_softmax_half_kernel<<<(rows + 7) / 8, 256, 0, s>>>(scores, mask, static_cast<bf16*>(p), rows, hd.a * hd.l, hd.s, hd.scale);
+    check_launch("attention masked_softmax");
+}
+
+}  // namespace
+
+void attention_bf16_forward(cudaStream_t s, const void* q, const void* k, const void* v, const float* mask, void* out, void* p,
+                            float* scores, AttentionShape sh, uint32_t* status) {
+    if (sh.batch == 0 || sh.q_len == 0) return;
+    const HalfHeads hh = {heads_of(sh)};
+    const Heads& hd = hh.hd;
+    half_probabilities(s, q, k, mask, p, scores, hh, status);
+    // O[i, c] = sum_j P[i, j] v[j, c]
+    matmul_bf16(s, hh.scores(p), hh.kv(v), hh.to_q(out), hd.l, hd.d, hd.s, hd.b, hd.a, nullptr, nullptr, status);
+}
+
+void attention_bf16_backward(cudaStream_t s, const void* q, const void* k, const void* v, const float* mask, const void* g, void* dq,
+                             void* dk, void* dv, void* p, void* ds, float* scores, AttentionShape sh, uint32_t* status, bool p_ready) {
+    if (sh.batch == 0 || sh.q_len == 0) return;
+    const HalfHeads hh = {heads_of(sh)};
+    const Heads& hd = hh.hd;
+    if (!p_ready) half_probabilities(s, q, k, mask, p, scores, hh, status);
+    // dV[j, c] = sum_i P[i, j] g[i, c]: A is P stored [k, m].
+    if (dv) matmul_bf16(s, hh.scores(p, true), hh.q(g), hh.to_kv(dv), hd.s, hd.d, hd.l, hd.b, hd.a, nullptr, nullptr, status);
+    if (!dq && !dk) return;
+    // dP[i, j] = sum_c g[i, c] v[j, c], in f32.
+    matmul_bf16(s, hh.q(g), hh.kv(v, true), hh.to_scores(scores), hd.l, hd.s, hd.d, hd.b, hd.a, nullptr, nullptr, status);
+    const uint32_t rows = hd.rows();
+    score_grad_half_kernel<<<(rows + 7) / 8, 256, 0, s>>>(static_cast<const bf16*>(p), scores, static_cast<bf16*>(ds), rows, hd.s, hd.scale);
+    check_launch("attention score_grad");
+    // dQ[i, c] = sum_j dS[i, j] k[j, c];  dK[j, c] = sum_i dS[i, j] q[i, c]
+    if (dq) matmul_bf16(s, hh.scores(ds), hh.kv(k), hh.to_q(dq), hd.l, hd.d, hd.s, hd.b, hd.a, nullptr, nullptr, status);
+    if (dk) matmul_bf16(s, hh.scores(ds, true), hh.q(q), hh.to_kv(dk), hd.s, hd.d, hd.l, hd.b, hd.a, nullptr, nullptr, status);
+}
+
 }  // namespace k
 }  // namespace msx

@@ -1,9 +1,11 @@
 // Shared device helpers and the host-side launch check.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <initializer_list>
 #include <stdexcept>
 #include <string>
 
@@ -25,6 +27,47 @@ inline void check(cudaError_t e, const char* what) {
 // earlier (the host application's own, or an earlier launch here) is reported once and does not
 // fail every later launch.
 inline void check_launch(const char* kernel) { check(cudaGetLastError(), kernel); }
+
+// ---- elements of either storage type ------------------------------------------------------------
+// A mixed-precision plan stores activations as bf16; the kernels that touch them are templates on
+// the element type and compute in f32 whatever it is. One element, or four consecutive ones (16
+// bytes of f32, 8 bytes of bf16; the address a multiple of that).
+using bf16 = __nv_bfloat16;
+__device__ __forceinline__ float load1(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float load1(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void store1(float* p, float v) { *p = v; }
+__device__ __forceinline__ void store1(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ float4 load4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+// `v` as an array of that element type would hold it.
+__device__ __forceinline__ float stored_as(float v, const float*) { return v; }
+__device__ __forceinline__ float stored_as(float v, const bf16*) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// Whether `p` may be read or written four elements at a time.
+template <class T> inline bool aligned4(const T* p) { return reinterpret_cast<uintptr_t>(p) % (4 * sizeof(T)) == 0; }
+
+// The activation operands of one launch share one storage type: true when all are bf16.
+inline bool all_half(std::initializer_list<bool> halves, const char* kernel) {
+    bool any = false, all = true;
+    for (bool h : halves) {
+        any = any || h;
+        all = all && h;
+    }
+    if (any && !all) throw std::invalid_argument(std::string(kernel) + ": f32 and bf16 activation operands in one launch");
+    return all;
+}
 
 // ---- GELU, the tanh form evaluated as x / (1 + exp(-2u)) -------------------------------------
 // The operation order is the reference's (crates/modelspec-runtime/src/cpu/interpreter.rs:

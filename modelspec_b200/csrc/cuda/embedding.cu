@@ -20,8 +20,9 @@ namespace k {
 
 namespace {
 
-__global__ void embedding_kernel(const float* __restrict__ table, const int32_t* __restrict__ ids,
-                                 float* __restrict__ out, uint64_t n, uint32_t rows, uint32_t h,
+template <class TI, class TO>
+__global__ void embedding_kernel(const TI* __restrict__ table, const int32_t* __restrict__ ids,
+                                 TO* __restrict__ out, uint64_t n, uint32_t rows, uint32_t h,
                                  uint32_t* __restrict__ status) {
     // One warp per output row, 128-bit copies when the row length allows.
     uint64_t row = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -31,15 +32,12 @@ __global__ void embedding_kernel(const float* __restrict__ table, const int32_t*
         int32_t id = ids[row];
         bool ok = id >= 0 && static_cast<uint32_t>(id) < rows;
         if (!ok && lane == 0) atomicOr(status, 1u);
-        const float* src = table + static_cast<uint64_t>(ok ? id : 0) * h;
-        float* dst = out + row * h;
-        if (h % 4 == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
-            for (uint32_t j = lane; j < h / 4; j += 32) {
-                float4 v = ok ? reinterpret_cast<const float4*>(src)[j] : make_float4(0.f, 0.f, 0.f, 0.f);
-                reinterpret_cast<float4*>(dst)[j] = v;
-            }
+        const TI* src = table + static_cast<uint64_t>(ok ? id : 0) * h;
+        TO* dst = out + row * h;
+        if (h % 4 == 0 && reinterpret_cast<uintptr_t>(table) % (4 * sizeof(TI)) == 0 && reinterpret_cast<uintptr_t>(out) % (4 * sizeof(TO)) == 0) {
+            for (uint32_t j = lane; j < h / 4; j += 32) store4(dst + 4 * j, ok ? load4(src + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f));
         } else {
-            for (uint32_t j = lane; j < h; j += 32) dst[j] = ok ? src[j] : 0.0f;
+            for (uint32_t j = lane; j < h; j += 32) store1(dst + j, ok ? load1(src + j) : 0.0f);
         }
     }
 }
@@ -125,10 +123,10 @@ __device__ __forceinline__ uint32_t warp_lower_bound(const int32_t* __restrict__
 // alone and only the rows some id names are read and written. VEC = 4 reads and writes 16 bytes
 // per lane and needs h % 4 == 0 and 16-byte aligned g, base and out.
 constexpr uint32_t kHotRow = 32, kHotChunk = 32, kCachedIds = 4096;
-template <int VEC>
-__global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ g, const int32_t* __restrict__ sorted_id,
+template <int VEC, class TG, class TO>
+__global__ void __launch_bounds__(256) scatter_kernel(const TG* __restrict__ g, const int32_t* __restrict__ sorted_id,
                                                       const int32_t* __restrict__ sorted_n, uint32_t n,
-                                                      const float* base, float* out, uint32_t rows, uint32_t h) {
+                                                      const float* base, TO* out, uint32_t rows, uint32_t h) {
     constexpr uint32_t span = VEC * 32;
     constexpr int LOADS = kHotChunk * span / VEC / 256;
     __shared__ float stage[kHotChunk][span];
@@ -176,13 +174,13 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         const int32_t src = __shfl_sync(0xffffffffu, entry, e);
-                        const float* from = g + static_cast<uint64_t>(src) * h + col;
+                        const TG* from = g + static_cast<uint64_t>(src) * h + col;
                         if (static_cast<uint32_t>(e) < here && in) {
                             if (VEC == 4) {
-                                const float4 f = *reinterpret_cast<const float4*>(from);
+                                const float4 f = load4(from);
                                 v[e][0] = f.x; v[e][1 % VEC] = f.y; v[e][2 % VEC] = f.z; v[e][3 % VEC] = f.w;
                             } else {
-                                v[e][0] = *from;
+                                v[e][0] = load1(from);
                             }
                         } else {
 #pragma unroll
@@ -197,17 +195,17 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
                         }
                 }
                 // In place (base is out): a row nobody read already holds its result.
-                if (in && !(count == 0 && base == out)) {
-                    float* to = out + static_cast<uint64_t>(row) * h + col;
+                if (in && !(count == 0 && static_cast<const void*>(base) == static_cast<const void*>(out))) {
+                    TO* to = out + static_cast<uint64_t>(row) * h + col;
                     if (VEC == 4) {
                         float4 r = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
                         if (base) {
                             const float4 b = *reinterpret_cast<const float4*>(base + static_cast<uint64_t>(row) * h + col);
                             r.x = b.x + r.x; r.y = b.y + r.y; r.z = b.z + r.z; r.w = b.w + r.w;
                         }
-                        *reinterpret_cast<float4*>(to) = r;
+                        store4(to, r);
                     } else {
-                        *to = base ? base[static_cast<uint64_t>(row) * h + col] + acc[0] : acc[0];
+                        store1(to, base ? base[static_cast<uint64_t>(row) * h + col] + acc[0] : acc[0]);
                     }
                 }
             }
@@ -231,9 +229,9 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
                     const uint32_t r = f / (span / VEC), c = (f % (span / VEC)) * VEC;
                     const bool wanted = chunk_start + r < count && col0 + c < h;
                     const int32_t src = wanted ? __ldg(sorted_n + at + chunk_start + r) : 0;
-                    const float* from = g + static_cast<uint64_t>(src) * h + col0 + c;
-                    if (VEC == 4) held4[set][j % (VEC == 4 ? LOADS : 1)] = wanted ? *reinterpret_cast<const float4*>(from) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    else held1[set][j % (VEC == 1 ? LOADS : 1)] = wanted ? *from : 0.0f;
+                    const TG* from = g + static_cast<uint64_t>(src) * h + col0 + c;
+                    if (VEC == 4) held4[set][j % (VEC == 4 ? LOADS : 1)] = wanted ? load4(from) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    else held1[set][j % (VEC == 1 ? LOADS : 1)] = wanted ? load1(from) : 0.0f;
                 }
             };
             float acc = 0.0f;
@@ -262,7 +260,7 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
             }
             if (threadIdx.x < span && col0 + threadIdx.x < h) {
                 const uint64_t where = static_cast<uint64_t>(row) * h + col0 + threadIdx.x;
-                out[where] = base ? base[where] + acc : acc;
+                store1(out + where, base ? base[where] + acc : acc);
             }
         }
     }
@@ -270,12 +268,17 @@ __global__ void __launch_bounds__(256) scatter_kernel(const float* __restrict__ 
 
 }  // namespace
 
-void embedding(cudaStream_t s, const float* table, const int32_t* ids, float* out, uint64_t n,
+void embedding(cudaStream_t s, In table, const int32_t* ids, Out out, uint64_t n,
                uint64_t rows, uint64_t h, uint32_t* status) {
     if (n == 0 || h == 0) return;
     uint64_t blocks = (n * 32 + 255) / 256;
     uint32_t grid = static_cast<uint32_t>(blocks > 148 * 16 ? 148 * 16 : blocks);
-    embedding_kernel<<<grid, 256, 0, s>>>(table, ids, out, n, static_cast<uint32_t>(rows), static_cast<uint32_t>(h), status);
+    const uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
+    // A mixed-precision plan gathers from an f32 parameter table or a bf16 activation into bf16.
+    if (table.half && out.half) embedding_kernel<<<grid, 256, 0, s>>>(static_cast<const bf16*>(table.p), ids, static_cast<bf16*>(out.p), n, r, hh, status);
+    else if (out.half) embedding_kernel<<<grid, 256, 0, s>>>(table.f32(), ids, static_cast<bf16*>(out.p), n, r, hh, status);
+    else if (!table.half) embedding_kernel<<<grid, 256, 0, s>>>(table.f32(), ids, out.f32(), n, r, hh, status);
+    else throw std::invalid_argument("embedding: a bf16 table gathered into f32");
     check_launch("embedding");
 }
 
@@ -291,13 +294,12 @@ void embedding_order(cudaStream_t s, const int32_t* ids, uint64_t n, uint64_t ro
     check_launch("embedding_order");
 }
 
-void embedding_scatter(cudaStream_t s, const float* g, float* out, uint64_t n, uint64_t rows, uint64_t h, const int32_t* scratch,
-                       const float* base) {
-    if (rows == 0 || h == 0) return;
+namespace {
+template <class TG, class TO>
+void launch_scatter(cudaStream_t s, const TG* g, TO* out, uint64_t n, uint64_t rows, uint64_t h, const int32_t* scratch, const float* base) {
     const int32_t* sorted_id = scratch;
     const int32_t* sorted_n = scratch + n;
-    auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-    const bool vec = h % 4 == 0 && aligned(g) && aligned(out) && aligned(base);
+    const bool vec = h % 4 == 0 && aligned4(g) && aligned4(out) && reinterpret_cast<uintptr_t>(base) % 16 == 0;
     const uint64_t span = vec ? 128 : 32;
     const uint64_t blocks = (rows * ((h + span - 1) / span) + 7) / 8;
     const uint32_t grid = static_cast<uint32_t>(blocks > 148 * 6 ? 148 * 6 : blocks);
@@ -305,8 +307,26 @@ void embedding_scatter(cudaStream_t s, const float* g, float* out, uint64_t n, u
     else scatter_kernel<1><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
     check_launch("embedding_grad");
 }
+}  // namespace
 
-void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* out, uint64_t n,
+void embedding_scatter(cudaStream_t s, In g, Out out, uint64_t n, uint64_t rows, uint64_t h, const int32_t* scratch,
+                       const float* base) {
+    if (rows == 0 || h == 0) return;
+    // A mixed-precision plan scatters a bf16 adjoint into an f32 parameter gradient (with or
+    // without an f32 addend) or into a bf16 activation adjoint (the gathered rows of a head).
+    if (g.half && out.half) {
+        if (base) throw std::invalid_argument("embedding_grad: an f32 addend of a bf16 result");
+        launch_scatter(s, static_cast<const bf16*>(g.p), static_cast<bf16*>(out.p), n, rows, h, scratch, base);
+    } else if (g.half) {
+        launch_scatter(s, static_cast<const bf16*>(g.p), out.f32(), n, rows, h, scratch, base);
+    } else if (!out.half) {
+        launch_scatter(s, g.f32(), out.f32(), n, rows, h, scratch, base);
+    } else {
+        throw std::invalid_argument("embedding_grad: an f32 adjoint scattered into bf16");
+    }
+}
+
+void embedding_grad(cudaStream_t s, const int32_t* ids, In g, Out out, uint64_t n,
                     uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status, const float* base) {
     embedding_order(s, ids, n, rows, scratch, status);
     embedding_scatter(s, g, out, n, rows, h, scratch, base);

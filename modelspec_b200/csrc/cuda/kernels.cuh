@@ -13,16 +13,40 @@
 namespace msx {
 namespace k {
 
+// A device array whose elements are f32 or, in a mixed-precision plan, bf16. The launchers that
+// take these compute in f32 whatever the storage; the activation operands of one launch are all of
+// one type (parameters, partial sums and whole-tensor results are always f32). A plain float
+// pointer converts to either.
+struct In {
+    const void* p = nullptr;
+    bool half = false;
+    In() = default;
+    In(const float* f) : p(f) {}
+    In(const void* q, bool h) : p(q), half(h) {}
+    explicit operator bool() const { return p != nullptr; }
+    const float* f32() const { return static_cast<const float*>(p); }
+};
+struct Out {
+    void* p = nullptr;
+    bool half = false;
+    Out() = default;
+    Out(float* f) : p(f) {}
+    Out(void* q, bool h) : p(q), half(h) {}
+    explicit operator bool() const { return p != nullptr; }
+    float* f32() const { return static_cast<float*>(p); }
+    operator In() const { return In(p, half); }
+};
+
 // ---- pointwise (pointwise.cu) -----------------------------------------------------------------
 enum class Binary : int { Add, Sub, Mul, Div };
 // out[i] = a[i] op b[i]; an operand with `*_scalar` set is one element read for every i.
 void binary(cudaStream_t s, Binary op, const float* a, bool a_scalar, const float* b, bool b_scalar,
             float* out, uint64_t n);
 enum class Unary : int { Relu, Sqrt, Gelu, Copy };
-void unary(cudaStream_t s, Unary op, const float* a, float* out, uint64_t n);
+void unary(cudaStream_t s, Unary op, In a, Out out, uint64_t n);
 // out[i] = a[i] > 0 ? g[i] : 0 (relu) or gelu'(a[i]) * g[i] (gelu).
 void relu_grad(cudaStream_t s, const float* a, const float* g, float* out, uint64_t n);
-void gelu_grad(cudaStream_t s, const float* a, const float* g, float* out, uint64_t n);
+void gelu_grad(cudaStream_t s, In a, In g, Out out, uint64_t n);
 void fill_from_scalar(cudaStream_t s, const float* scalar, float* out, uint64_t n);
 // out[r, c] = x[r, c] + b[c]
 void add_rows(cudaStream_t s, const float* x, const float* b, float* out, uint64_t rows, uint64_t h);
@@ -32,8 +56,8 @@ void transpose(cudaStream_t s, const float* a, float* out, uint64_t rows, uint64
 // Philox4x32-10 dropout: element i (global index index_base + i) is kept iff word 0 of
 // philox([index, 4, token[0], token[1]], [seed lo, seed hi]) >= threshold; kept -> x * scale,
 // dropped -> +0. `token` is the i32[2] device input of the site.
-void dropout(cudaStream_t s, const float* x, const int32_t* token, uint64_t seed, uint32_t threshold,
-             float scale, uint64_t index_base, float* out, uint64_t n);
+void dropout(cudaStream_t s, In x, const int32_t* token, uint64_t seed, uint32_t threshold,
+             float scale, uint64_t index_base, Out out, uint64_t n);
 
 // ---- reductions (reduce.cu) -------------------------------------------------------------------
 // Whole-tensor sums in f64, rounded to f32 once. `scratch` holds at least reduce_scratch_doubles()
@@ -49,7 +73,7 @@ uint64_t sum_rows_scratch_floats(uint64_t rows, uint64_t h);
 // same result) instead of a second one.
 // With `out` null only the chunk sums are written, as scratch[chunk][h]: finalize_sums adds them.
 uint64_t sum_rows_counters(uint64_t h);
-void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out,
+void sum_rows(cudaStream_t s, In g, uint64_t rows, uint64_t h, float* scratch, float* out,
               uint32_t* counters = nullptr, uint64_t ld = 0);
 
 // The first stages of many column sums (the bias gradients of a step) in one launch: job j sums
@@ -57,11 +81,11 @@ void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* 
 // partial[chunk][width], as sum_rows with a null `out` does; finalize_sums adds the chunks.
 // `first_block` = the blocks (row_sum_job_blocks each) of the jobs before this one.
 struct RowSumJob {
-    const float* g;
+    const void* g;
     float* partial;
-    uint32_t rows, width, ld, rows_per_chunk, first_block, reserved;
+    uint32_t rows, width, ld, rows_per_chunk, first_block, half;  // half: g holds bf16 elements
 };
-RowSumJob row_sum_job(const float* g, float* partial, uint64_t rows, uint64_t h, uint64_t ld, uint32_t first_block);
+RowSumJob row_sum_job(In g, float* partial, uint64_t rows, uint64_t h, uint64_t ld, uint32_t first_block);
 uint32_t row_sum_job_blocks(uint64_t rows, uint64_t h);
 void sum_rows_batched(cudaStream_t s, const RowSumJob* d_jobs, uint32_t jobs, uint32_t blocks);
 
@@ -118,21 +142,22 @@ struct DropoutDraw {
 // `adjoint_draw`, when not null: the adjoint is dropout_grad of that sum. `dx_draw` and `dx_dropped`,
 // when not null: dropout_grad of dx is written to dx_dropped beside dx. `pre_activation` and
 // `dx_dropped`: gelu_grad(pre_activation, dx) is written to dx_dropped instead; dx may then be null.
-void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
-                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const float* g1 = nullptr,
-                         const float* g2 = nullptr, const float* g3 = nullptr, const DropoutDraw* adjoint_draw = nullptr,
-                         const DropoutDraw* dx_draw = nullptr, float* dx_dropped = nullptr, const float* pre_activation = nullptr);
+void layer_norm_backward(cudaStream_t s, In x, const float* gamma, In g, Out dx, float* scratch,
+                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, In g1 = In(),
+                         In g2 = In(), In g3 = In(), const DropoutDraw* adjoint_draw = nullptr,
+                         const DropoutDraw* dx_draw = nullptr, Out dx_dropped = Out(), In pre_activation = In());
 // sum_out = residual + dropout(x), out = layer_norm(sum_out, gamma, beta), rows of up to 1,024
 // elements (layer_norm_backward_supported(h)); the dropout draw is that of `dropout`.
-void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residual, const int32_t* token, uint64_t seed,
+void dropout_add_layer_norm(cudaStream_t s, In x, In residual, const int32_t* token, uint64_t seed,
                             uint32_t threshold, float scale, uint64_t index_base, const float* gamma, const float* beta,
-                            float* sum_out, float* out, uint64_t rows, uint64_t h);
+                            Out sum_out, Out out, uint64_t rows, uint64_t h);
 // The general form: sum_out = residual + x (x through `x_draw` first when not null); with gamma
 // and beta, out = layer_norm(sum_out) (out may be null when only the next output is wanted) and,
 // with `out_draw`, out_dropped = dropout(out).
 // With `gelu_first`, gelu(x) stands where the sum does (residual is null then): sum_out = gelu(x).
-void add_layer_norm(cudaStream_t s, const float* x, const float* residual, const DropoutDraw* x_draw, const float* gamma,
-                    const float* beta, float* sum_out, float* out, const DropoutDraw* out_draw, float* out_dropped, uint64_t rows,
+// sum_out may be null when only the layer norm is wanted (a plain layer norm: residual null too).
+void add_layer_norm(cudaStream_t s, In x, In residual, const DropoutDraw* x_draw, const float* gamma,
+                    const float* beta, Out sum_out, Out out, const DropoutDraw* out_draw, Out out_dropped, uint64_t rows,
                     uint64_t h, bool gelu_first = false);
 void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t k);
 void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, uint64_t rows, uint64_t k);
@@ -140,7 +165,7 @@ void softmax_grad(cudaStream_t s, const float* y, const float* g, float* out, ui
 // loss = sum w * l / sum w (f64 sums, one rounding; 0 when the weights sum to 0).
 // `global_den`, when not null, is a device float that replaces the weight sum in the division:
 // a data-parallel shard divides its own numerator by the weight sum of the whole batch.
-void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
+void cross_entropy(cudaStream_t s, In logits, const int32_t* labels, const float* weights,
                    float* row_loss, const float* global_den, float* loss, uint64_t rows, uint64_t v, uint64_t ld = 0);
 // out[0] = f32(sum of the weights in f64).
 void weight_sum(cudaStream_t s, const float* weights, uint64_t rows, float* out);
@@ -156,9 +181,9 @@ void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labe
 // parallel) the loss divides by it too. `counter`, when not null, is one word that is zero before
 // the first launch and left zero by every launch: rows of up to 32,768 logits then take one
 // launch in all (weight sum and final loss included) and one read of the logits from memory.
-void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
+void cross_entropy_with_grad(cudaStream_t s, In logits, const int32_t* labels, const float* weights,
                              const float* g, bool denominator_ready, float* denominator, float* row_loss, float* loss,
-                             float* grad, uint64_t rows, uint64_t v, uint32_t* counter = nullptr, uint64_t ld = 0,
+                             Out grad, uint64_t rows, uint64_t v, uint32_t* counter = nullptr, uint64_t ld = 0,
                              uint64_t ld_grad = 0);
 
 // ---- all-reduce over peer memory (peer_reduce.cu) ---------------------------------------------
@@ -187,18 +212,18 @@ void peer_all_reduce(cudaStream_t s, const PeerReduceArgs& args);
 
 // ---- embedding (embedding.cu) -----------------------------------------------------------------
 // out[n, :] = table[ids[n], :]; an id outside [0, rows) writes zeros and raises bit 0 of *status.
-void embedding(cudaStream_t s, const float* table, const int32_t* ids, float* out, uint64_t n,
+void embedding(cudaStream_t s, In table, const int32_t* ids, Out out, uint64_t n,
                uint64_t rows, uint64_t h, uint32_t* status);
 // out = zeros[rows, h] with g[n, :] added to row ids[n] in ascending n: bit-exact with a
 // sequential loop. `scratch` holds embedding_grad_scratch_ints(n, rows) ints. With `base`
 // ([rows, h]) the result is base + that tensor, element by element.
 uint64_t embedding_grad_scratch_ints(uint64_t n, uint64_t rows);
-void embedding_grad(cudaStream_t s, const int32_t* ids, const float* g, float* out, uint64_t n,
+void embedding_grad(cudaStream_t s, const int32_t* ids, In g, Out out, uint64_t n,
                     uint64_t rows, uint64_t h, int32_t* scratch, uint32_t* status, const float* base = nullptr);
 // Its two halves: the order of the occurrences depends on the ids alone and can be computed as
 // soon as they are on the device (beside the forward pass); the scatter needs g.
 void embedding_order(cudaStream_t s, const int32_t* ids, uint64_t n, uint64_t rows, int32_t* scratch, uint32_t* status);
-void embedding_scatter(cudaStream_t s, const float* g, float* out, uint64_t n, uint64_t rows, uint64_t h, const int32_t* scratch,
+void embedding_scatter(cudaStream_t s, In g, Out out, uint64_t n, uint64_t rows, uint64_t h, const int32_t* scratch,
                        const float* base = nullptr);
 
 // ---- matmul (gemm.cu) -------------------------------------------------------------------------
@@ -274,6 +299,35 @@ struct BatchedOperand {
 void matmul_tc_batched(cudaStream_t s, const BatchedOperand& a, const BatchedOperand& b, const BatchedOperand& c,
                        uint64_t m, uint64_t n, uint64_t k, uint32_t outer, uint32_t inner, uint32_t* status);
 
+// ---- matmul on bf16 operands (gemm_bf16.cu) ---------------------------------------------------
+// Mixed-precision plans: operands stored as bf16, products by tcgen05.mma kind::f16 fed by TMA,
+// f32 accumulation, the result stored as bf16 or f32. An operand is `outer` x `inner` matrices of
+// `pitch` elements between rows; matrix (o, i) starts stride_outer * o + stride_inner * i elements
+// after `base`. `transposed`: A is stored [k, m], B is stored [n, k] (as for the f32 kernels).
+// TMA sources: base on a 16-byte boundary, pitch and strides multiples of 8 elements.
+struct HalfMatrix {
+    const void* base;  // bf16 elements
+    uint32_t pitch;
+    uint64_t stride_outer, stride_inner;
+    bool transposed;
+};
+struct HalfResult {
+    void* base;
+    bool half;       // bf16 elements, else f32
+    uint32_t pitch;  // 0 = n
+    uint64_t stride_outer, stride_inner;
+};
+struct MatmulBf16Plan {
+    uint32_t bn, splits, kblocks_per_split;
+    uint64_t workspace_floats;  // split-k partial tiles [split][m][n]; 0 when k is not split
+};
+MatmulBf16Plan matmul_bf16_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems = 1);
+// `workspace` holds matmul_bf16_plan(m, n, k, outer * inner).workspace_floats floats. With
+// `leave_partials` a split k stops at the partial tiles for finalize_sums (no bias then). A wait
+// that runs out inside the kernel raises bit 1 of *status.
+void matmul_bf16(cudaStream_t s, const HalfMatrix& a, const HalfMatrix& b, const HalfResult& c, uint64_t m, uint64_t n, uint64_t k,
+                 uint32_t outer, uint32_t inner, float* workspace, const float* bias, uint32_t* status, bool leave_partials = false);
+
 // ---- attention (attention.cu) -----------------------------------------------------------------
 struct AttentionShape {
     uint32_t batch, q_len, k_len, heads, head_dim;  // q rows = batch * q_len, k rows = batch * k_len
@@ -301,6 +355,15 @@ void attention_tc_backward(cudaStream_t s, const float* q, const float* k, const
                            const float* g, float* dq, float* dk, float* dv, float* p, float* dp,
                            AttentionShape shape, uint32_t* status, bool p_ready = false);
 
+// The same for a mixed-precision plan: q, k, v, g, out and the gradients are bf16 [rows, H], `p`
+// (kept for the backward) and `ds` hold attention_tc_scratch_floats(shape) bf16 elements, `scores`
+// as many floats (the f32 scores, then the f32 score adjoints; dead after the call).
+void attention_bf16_forward(cudaStream_t s, const void* q, const void* k, const void* v, const float* mask, void* out, void* p,
+                            float* scores, AttentionShape shape, uint32_t* status);
+void attention_bf16_backward(cudaStream_t s, const void* q, const void* k, const void* v, const float* mask, const void* g, void* dq,
+                             void* dk, void* dv, void* p, void* ds, float* scores, AttentionShape shape, uint32_t* status,
+                             bool p_ready = false);
+
 // ---- optimizer (optimizer.cu) -----------------------------------------------------------------
 struct UpdateTensor {
     float* p;
@@ -308,6 +371,7 @@ struct UpdateTensor {
     float* m;
     float* v;
     uint64_t count;
+    void* p16;  // the bf16 working copy of p that a mixed-precision plan's matmuls read, or null
 };
 struct AdamWConstants {
     float beta1, rest1, beta2, rest2, eps, weight_decay;
@@ -319,6 +383,8 @@ constexpr uint32_t kUpdateChunk = 4096;
 void adamw(cudaStream_t s, const UpdateTensor* d_tensors, const uint32_t* d_chunk_tensor,
            const uint32_t* d_chunk_start, uint32_t chunks, AdamWConstants c, const float* lr_t,
            const float* c1, const float* c2);
+// p16[i] = bf16(p[i]): the working copy of a parameter after its f32 master was uploaded.
+void working_copy(cudaStream_t s, const float* p, void* p16, uint64_t n);
 // p -= lr * g, `lr` a device scalar.
 void sgd(cudaStream_t s, const UpdateTensor* d_tensors, const uint32_t* d_chunk_tensor,
          const uint32_t* d_chunk_start, uint32_t chunks, const float* lr);

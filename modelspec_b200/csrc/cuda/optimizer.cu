@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(256) adamw_kernel(const UpdateTensor* __restri
                 *reinterpret_cast<float4*>(t.p + i) = p[j];
                 *reinterpret_cast<float4*>(t.m + i) = m[j];
                 *reinterpret_cast<float4*>(t.v + i) = v[j];
+                // The bf16 working copy the next step's matmuls read (mixed-precision plans).
+                if (t.p16 != nullptr) store4(static_cast<bf16*>(t.p16) + i, p[j]);
             }
         }
         return;
@@ -74,7 +76,14 @@ __global__ void __launch_bounds__(256) adamw_kernel(const UpdateTensor* __restri
         t.p[i] = p;
         t.m[i] = m;
         t.v[i] = v;
+        if (t.p16 != nullptr) store1(static_cast<bf16*>(t.p16) + i, p);
     }
+}
+
+// The bf16 working copy of a parameter from its f32 master (after an upload).
+__global__ void working_copy_kernel(const float* __restrict__ p, bf16* __restrict__ p16, uint64_t n) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) store1(p16 + i, p[i]);
 }
 
 __global__ void __launch_bounds__(256) sgd_kernel(const UpdateTensor* __restrict__ tensors,
@@ -85,7 +94,11 @@ __global__ void __launch_bounds__(256) sgd_kernel(const UpdateTensor* __restrict
     uint64_t start = static_cast<uint64_t>(chunk_start[blockIdx.x]) * kUpdateChunk;
     uint64_t stop = start + kUpdateChunk < t.count ? start + kUpdateChunk : t.count;
     float rate = lr[0];
-    for (uint64_t i = start + threadIdx.x; i < stop; i += blockDim.x) t.p[i] = t.p[i] - rate * t.g[i];
+    for (uint64_t i = start + threadIdx.x; i < stop; i += blockDim.x) {
+        const float p = t.p[i] - rate * t.g[i];
+        t.p[i] = p;
+        if (t.p16 != nullptr) store1(static_cast<bf16*>(t.p16) + i, p);
+    }
 }
 
 }  // namespace
@@ -96,6 +109,13 @@ void adamw(cudaStream_t s, const UpdateTensor* d_tensors, const uint32_t* d_chun
     if (chunks == 0) return;
     adamw_kernel<<<chunks, 256, 0, s>>>(d_tensors, d_chunk_tensor, d_chunk_start, c, lr_t, c1, c2);
     check_launch("adamw");
+}
+
+void working_copy(cudaStream_t s, const float* p, void* p16, uint64_t n) {
+    if (n == 0) return;
+    const uint64_t blocks = (n + 255) / 256;
+    working_copy_kernel<<<static_cast<uint32_t>(blocks > 148 * 8 ? 148 * 8 : blocks), 256, 0, s>>>(p, static_cast<bf16*>(p16), n);
+    check_launch("working_copy");
 }
 
 void sgd(cudaStream_t s, const UpdateTensor* d_tensors, const uint32_t* d_chunk_tensor,

@@ -59,6 +59,7 @@ struct Slot {
     } kind = Dead;
     uint64_t bytes = 0;
     uint32_t pitch = 0;        // elements between rows as stored; 0 = the row width
+    bool half = false;         // stored as bf16 (a mixed-precision plan's activations), else 4-byte elements
     uint64_t offset = 0;       // Arena, Input: byte offset; Const: index into the constant table
     uint32_t index = 0;        // Param, Moment: parameter index; View: position of the source
     char moment = 0;           // Moment: 'm' or 'v'

@@ -68,29 +68,30 @@ __device__ __forceinline__ float apply(Unary op, float x) {
     }
 }
 
-__global__ void unary_kernel(Unary op, const float* __restrict__ a, float* __restrict__ out, uint64_t n) {
+template <class T>
+__global__ void unary_kernel(Unary op, const T* __restrict__ a, T* __restrict__ out, uint64_t n) {
     uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    bool vec = reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0;
+    bool vec = reinterpret_cast<uintptr_t>(out) % (4 * sizeof(T)) == 0 && reinterpret_cast<uintptr_t>(a) % (4 * sizeof(T)) == 0;
     uint64_t n4 = vec ? n / 4 : 0;
     for (uint64_t j = i; j < n4; j += stride) {
-        float4 v = reinterpret_cast<const float4*>(a)[j];
+        float4 v = load4(a + 4 * j);
         v.x = apply(op, v.x);
         v.y = apply(op, v.y);
         v.z = apply(op, v.z);
         v.w = apply(op, v.w);
-        reinterpret_cast<float4*>(out)[j] = v;
+        store4(out + 4 * j, v);
     }
-    for (uint64_t j = n4 * 4 + i; j < n; j += stride) out[j] = apply(op, a[j]);
+    for (uint64_t j = n4 * 4 + i; j < n; j += stride) store1(out + j, apply(op, load1(a + j)));
 }
 
-template <bool GELU>
-__global__ void act_grad_kernel(const float* __restrict__ a, const float* __restrict__ g,
-                                float* __restrict__ out, uint64_t n) {
+template <bool GELU, class T>
+__global__ void act_grad_kernel(const T* __restrict__ a, const T* __restrict__ g,
+                                T* __restrict__ out, uint64_t n) {
     uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t j = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n; j += stride) {
-        float x = a[j], gg = g[j];
-        out[j] = GELU ? gelu_grad_value(x, gg) : (x > 0.0f ? gg : 0.0f);
+        float x = load1(a + j), gg = load1(g + j);
+        store1(out + j, GELU ? gelu_grad_value(x, gg) : (x > 0.0f ? gg : 0.0f));
     }
 }
 
@@ -127,14 +128,15 @@ __global__ void transpose_kernel(const float* __restrict__ a, float* __restrict_
     }
 }
 
-__global__ void dropout_kernel(const float* __restrict__ x, const int32_t* __restrict__ token,
+template <class T>
+__global__ void dropout_kernel(const T* __restrict__ x, const int32_t* __restrict__ token,
                                uint32_t seed_lo, uint32_t seed_hi, uint32_t threshold, float scale,
-                               uint64_t index_base, float* __restrict__ out, uint64_t n) {
+                               uint64_t index_base, T* __restrict__ out, uint64_t n) {
     uint32_t id_lo = static_cast<uint32_t>(token[0]), id_hi = static_cast<uint32_t>(token[1]);
     uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t j = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n; j += stride) {
         uint32_t w0 = philox_word0(static_cast<uint32_t>(index_base + j), 4u, id_lo, id_hi, seed_lo, seed_hi);
-        out[j] = w0 >= threshold ? x[j] * scale : 0.0f;
+        store1(out + j, w0 >= threshold ? load1(x + j) * scale : 0.0f);
     }
 }
 
@@ -151,21 +153,28 @@ void binary(cudaStream_t s, Binary op, const float* a, bool a_scalar, const floa
     check_launch("binary");
 }
 
-void unary(cudaStream_t s, Unary op, const float* a, float* out, uint64_t n) {
+void unary(cudaStream_t s, Unary op, In a, Out out, uint64_t n) {
     if (n == 0) return;
-    unary_kernel<<<blocks_for((n + 3) / 4), kThreads, 0, s>>>(op, a, out, n);
+    if (all_half({a.half, out.half}, "unary"))
+        unary_kernel<<<blocks_for((n + 3) / 4), kThreads, 0, s>>>(op, static_cast<const bf16*>(a.p), static_cast<bf16*>(out.p), n);
+    else
+        unary_kernel<<<blocks_for((n + 3) / 4), kThreads, 0, s>>>(op, a.f32(), out.f32(), n);
     check_launch("unary");
 }
 
 void relu_grad(cudaStream_t s, const float* a, const float* g, float* out, uint64_t n) {
     if (n == 0) return;
-    act_grad_kernel<false><<<blocks_for(n), kThreads, 0, s>>>(a, g, out, n);
+    act_grad_kernel<false, float><<<blocks_for(n), kThreads, 0, s>>>(a, g, out, n);
     check_launch("relu_grad");
 }
 
-void gelu_grad(cudaStream_t s, const float* a, const float* g, float* out, uint64_t n) {
+void gelu_grad(cudaStream_t s, In a, In g, Out out, uint64_t n) {
     if (n == 0) return;
-    act_grad_kernel<true><<<blocks_for(n), kThreads, 0, s>>>(a, g, out, n);
+    if (all_half({a.half, g.half, out.half}, "gelu_grad"))
+        act_grad_kernel<true, bf16><<<blocks_for(n), kThreads, 0, s>>>(static_cast<const bf16*>(a.p), static_cast<const bf16*>(g.p),
+                                                                       static_cast<bf16*>(out.p), n);
+    else
+        act_grad_kernel<true, float><<<blocks_for(n), kThreads, 0, s>>>(a.f32(), g.f32(), out.f32(), n);
     check_launch("gelu_grad");
 }
 
@@ -189,12 +198,15 @@ void transpose(cudaStream_t s, const float* a, float* out, uint64_t rows, uint64
     check_launch("transpose");
 }
 
-void dropout(cudaStream_t s, const float* x, const int32_t* token, uint64_t seed, uint32_t threshold,
-             float scale, uint64_t index_base, float* out, uint64_t n) {
+void dropout(cudaStream_t s, In x, const int32_t* token, uint64_t seed, uint32_t threshold,
+             float scale, uint64_t index_base, Out out, uint64_t n) {
     if (n == 0) return;
-    dropout_kernel<<<blocks_for(n), kThreads, 0, s>>>(x, token, static_cast<uint32_t>(seed),
-                                                      static_cast<uint32_t>(seed >> 32), threshold, scale,
-                                                      index_base, out, n);
+    const uint32_t lo = static_cast<uint32_t>(seed), hi = static_cast<uint32_t>(seed >> 32);
+    if (all_half({x.half, out.half}, "dropout"))
+        dropout_kernel<<<blocks_for(n), kThreads, 0, s>>>(static_cast<const bf16*>(x.p), token, lo, hi, threshold, scale, index_base,
+                                                          static_cast<bf16*>(out.p), n);
+    else
+        dropout_kernel<<<blocks_for(n), kThreads, 0, s>>>(x.f32(), token, lo, hi, threshold, scale, index_base, out.f32(), n);
     check_launch("dropout");
 }
 

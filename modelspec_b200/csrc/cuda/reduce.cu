@@ -57,7 +57,8 @@ uint32_t whole_blocks(uint64_t n) {
 // `counters`, when not null, holds one zeroed word per column block: the last chunk block of a
 // column block to finish adds the chunk sums in ascending chunk order (what sum_rows_stage2 does
 // as a second launch) and writes `out`.
-__global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint32_t h, uint32_t ld, uint32_t rows_per_chunk,
+template <class T>
+__global__ void sum_rows_stage1(const T* __restrict__ g, uint32_t rows, uint32_t h, uint32_t ld, uint32_t rows_per_chunk,
                                 float* __restrict__ partial, uint32_t* __restrict__ counters, float* __restrict__ out) {
     __shared__ float shared[8][32];
     __shared__ bool is_last;
@@ -71,11 +72,11 @@ __global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint
         for (; r + 56 < r1; r += 64) {
             float v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __ldg(g + static_cast<uint64_t>(r + 8 * j) * ld + c);
+            for (int j = 0; j < 8; ++j) v[j] = load1(g + static_cast<uint64_t>(r + 8 * j) * ld + c);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc += v[j];
         }
-        for (; r < r1; r += 8) acc += __ldg(g + static_cast<uint64_t>(r) * ld + c);
+        for (; r < r1; r += 8) acc += load1(g + static_cast<uint64_t>(r) * ld + c);
     }
     shared[threadIdx.y][threadIdx.x] = acc;
     __syncthreads();
@@ -97,7 +98,8 @@ __global__ void sum_rows_stage1(const float* __restrict__ g, uint32_t rows, uint
 // The same with four columns per lane (16-byte loads) for matrices whose rows start on 16-byte
 // boundaries: a block covers 128 columns. Only the chunk sums are written (the second stage is
 // the step's finalize launch or sum_rows_stage2).
-__global__ void sum_rows_stage1_wide(const float* __restrict__ g, uint32_t rows, uint32_t h, uint32_t ld, uint32_t rows_per_chunk,
+template <class T>
+__global__ void sum_rows_stage1_wide(const T* __restrict__ g, uint32_t rows, uint32_t h, uint32_t ld, uint32_t rows_per_chunk,
                                      float* __restrict__ partial) {
     __shared__ float4 shared[8][32];
     const uint32_t c = (blockIdx.x * 32 + threadIdx.x) * 4;
@@ -108,12 +110,12 @@ __global__ void sum_rows_stage1_wide(const float* __restrict__ g, uint32_t rows,
         for (; r + 24 < r1; r += 32) {
             float4 v[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(g + static_cast<uint64_t>(r + 8 * j) * ld + c));
+            for (int j = 0; j < 4; ++j) v[j] = load4(g + static_cast<uint64_t>(r + 8 * j) * ld + c);
 #pragma unroll
             for (int j = 0; j < 4; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
         }
         for (; r < r1; r += 8) {
-            const float4 v = __ldg(reinterpret_cast<const float4*>(g + static_cast<uint64_t>(r) * ld + c));
+            const float4 v = load4(g + static_cast<uint64_t>(r) * ld + c);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
     }
@@ -158,16 +160,21 @@ __global__ void sum_rows_batched_kernel(const RowSumJob* __restrict__ jobs, uint
     const uint32_t c = (local % column_blocks) * 32 + threadIdx.x, chunk = local / column_blocks;
     const uint32_t r0 = chunk * job.rows_per_chunk, r1 = min(job.rows, r0 + job.rows_per_chunk);
     float acc = 0.0f;
-    if (c < job.width) {
+    // The same loop for either element type of the job's matrix (one type per block).
+    auto column_sum = [&](auto* g) {
         uint32_t r = r0 + threadIdx.y;
         for (; r + 56 < r1; r += 64) {
             float v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __ldg(job.g + static_cast<uint64_t>(r + 8 * j) * job.ld + c);
+            for (int j = 0; j < 8; ++j) v[j] = load1(g + static_cast<uint64_t>(r + 8 * j) * job.ld + c);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc += v[j];
         }
-        for (; r < r1; r += 8) acc += __ldg(job.g + static_cast<uint64_t>(r) * job.ld + c);
+        for (; r < r1; r += 8) acc += load1(g + static_cast<uint64_t>(r) * job.ld + c);
+    };
+    if (c < job.width) {
+        if (job.half) column_sum(static_cast<const bf16*>(job.g));
+        else column_sum(static_cast<const float*>(job.g));
     }
     shared[threadIdx.y][threadIdx.x] = acc;
     __syncthreads();
@@ -222,9 +229,10 @@ __global__ void finalize_sums_kernel(const SumJob* __restrict__ jobs, uint32_t c
 
 }  // namespace
 
-RowSumJob row_sum_job(const float* g, float* partial, uint64_t rows, uint64_t h, uint64_t ld, uint32_t first_block) {
+RowSumJob row_sum_job(In g, float* partial, uint64_t rows, uint64_t h, uint64_t ld, uint32_t first_block) {
     RowSumJob job = {};
-    job.g = g;
+    job.g = g.p;
+    job.half = g.half ? 1u : 0u;
     job.partial = partial;
     job.rows = static_cast<uint32_t>(rows);
     job.width = static_cast<uint32_t>(h);
@@ -275,15 +283,13 @@ uint64_t sum_rows_scratch_floats(uint64_t rows, uint64_t h) { return sum_rows_ch
 
 uint64_t sum_rows_counters(uint64_t h) { return (h + 31) / 32; }
 
-void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* scratch, float* out, uint32_t* counters,
-              uint64_t ld) {
-    if (h == 0) return;
-    if (ld == 0) ld = h;
+namespace {
+template <class T>
+void launch_sum_rows(cudaStream_t s, const T* g, uint64_t rows, uint64_t h, float* scratch, float* out, uint32_t* counters, uint64_t ld) {
     uint32_t chunks = sum_rows_chunks(rows);
     uint32_t rows_per_chunk = static_cast<uint32_t>((rows + chunks - 1) / chunks);
-    // Wide matrices with 16-byte-aligned rows: four columns per lane, chunk sums only.
-    const bool wide = h >= 1024 && ld % 4 == 0 && reinterpret_cast<uintptr_t>(g) % 16 == 0 && (out == nullptr || counters == nullptr) &&
-                      !(chunks == 1 && out);
+    // Wide matrices whose rows can be read four elements at a time: four columns per lane, chunk sums only.
+    const bool wide = h >= 1024 && ld % 4 == 0 && aligned4(g) && (out == nullptr || counters == nullptr) && !(chunks == 1 && out);
     if (wide) {
         dim3 grid(static_cast<uint32_t>((h + 127) / 128), chunks);
         sum_rows_stage1_wide<<<grid, dim3(32, 8), 0, s>>>(g, static_cast<uint32_t>(rows), static_cast<uint32_t>(h), static_cast<uint32_t>(ld),
@@ -301,6 +307,15 @@ void sum_rows(cudaStream_t s, const float* g, uint64_t rows, uint64_t h, float* 
                                                                                 static_cast<uint32_t>(h), out);
         check_launch("sum_rows");
     }
+}
+}  // namespace
+
+void sum_rows(cudaStream_t s, In g, uint64_t rows, uint64_t h, float* scratch, float* out, uint32_t* counters,
+              uint64_t ld) {
+    if (h == 0) return;
+    if (ld == 0) ld = h;
+    if (g.half) launch_sum_rows(s, static_cast<const bf16*>(g.p), rows, h, scratch, out, counters, ld);
+    else launch_sum_rows(s, g.f32(), rows, h, scratch, out, counters, ld);
 }
 
 }  // namespace k

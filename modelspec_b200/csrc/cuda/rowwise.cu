@@ -139,16 +139,17 @@ constexpr int kRowThreads = 256;
 
 // Max of the row (the first element, replaced only by a greater one: NaN never wins) and the sum
 // of exp(x - max), by a block.
-__device__ __forceinline__ void block_row_softmax(const float* __restrict__ row, uint32_t v, float* shared,
+template <class T>
+__device__ __forceinline__ void block_row_softmax(const T* __restrict__ row, uint32_t v, float* shared,
                                                   float* max, float* total) {
     float m = -INFINITY;
     for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) {
-        float x = row[c];
+        float x = load1(row + c);
         if (x > m) m = x;
     }
     m = block_max(m, shared);
     float s = 0.0f;
-    for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) s += expf(row[c] - m);
+    for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) s += expf(load1(row + c) - m);
     *max = m;
     *total = block_sum(s, shared);
 }
@@ -174,7 +175,8 @@ __global__ void softmax_grad_kernel(const float* __restrict__ y, const float* __
     for (uint32_t c = threadIdx.x; c < k; c += blockDim.x) o[c] = yr[c] * (gr[c] - d);
 }
 
-__global__ void cross_entropy_rows_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+template <class T>
+__global__ void cross_entropy_rows_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels,
                                           const float* __restrict__ weights, float* __restrict__ row_loss,
                                           uint32_t v, uint32_t ld) {
     __shared__ float shared[33];
@@ -184,12 +186,12 @@ __global__ void cross_entropy_rows_kernel(const float* __restrict__ logits, cons
         if (threadIdx.x == 0) row_loss[r] = 0.0f;
         return;
     }
-    const float* row = logits + static_cast<uint64_t>(r) * ld;
+    const T* row = logits + static_cast<uint64_t>(r) * ld;
     float max, total;
     block_row_softmax(row, v, shared, &max, &total);
     if (threadIdx.x == 0) {
         int32_t label = labels[r];
-        float picked = (label >= 0 && static_cast<uint32_t>(label) < v) ? row[label] : 0.0f;
+        float picked = (label >= 0 && static_cast<uint32_t>(label) < v) ? load1(row + label) : 0.0f;
         row_loss[r] = max + logf(total) - picked;
     }
 }
@@ -245,32 +247,33 @@ __global__ void cross_entropy_grad_kernel(const float* __restrict__ logits, cons
 // Loss row and gradient row in one visit of the logits row: max, sum of exp, then
 // scale * (p - onehot) while the row is still in cache. The same formulas, in the same order, as
 // the two separate kernels.
-__global__ void cross_entropy_fused_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+template <class T>
+__global__ void cross_entropy_fused_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels,
                                            const float* __restrict__ weights, const float* __restrict__ g,
                                            const float* __restrict__ denominator, float* __restrict__ row_loss,
-                                           float* __restrict__ out, uint32_t v, uint32_t ld, uint32_t ld_out) {
+                                           T* __restrict__ out, uint32_t v, uint32_t ld, uint32_t ld_out) {
     __shared__ float shared[33];
     uint32_t r = blockIdx.x;
-    float* o = out + static_cast<uint64_t>(r) * ld_out;
+    T* o = out + static_cast<uint64_t>(r) * ld_out;
     float den = denominator[0], w = weights[r];
     if (w == 0.0f) {
         if (threadIdx.x == 0) row_loss[r] = 0.0f;
-        for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) o[c] = 0.0f;
+        for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) store1(o + c, 0.0f);
         return;
     }
-    const float* row = logits + static_cast<uint64_t>(r) * ld;
+    const T* row = logits + static_cast<uint64_t>(r) * ld;
     float max, total;
     block_row_softmax(row, v, shared, &max, &total);
     uint32_t label = static_cast<uint32_t>(labels[r]);
-    if (threadIdx.x == 0) row_loss[r] = max + logf(total) - (label < v ? row[label] : 0.0f);
+    if (threadIdx.x == 0) row_loss[r] = max + logf(total) - (label < v ? load1(row + label) : 0.0f);
     if (den == 0.0f) {
-        for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) o[c] = 0.0f;
+        for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) store1(o + c, 0.0f);
         return;
     }
     float scale = g[0] * w / den;
     for (uint32_t c = threadIdx.x; c < v; c += blockDim.x) {
         float target = c == label ? 1.0f : 0.0f;
-        o[c] = scale * (expf(row[c] - max) / total - target);
+        store1(o + c, scale * (expf(load1(row + c) - max) / total - target));
     }
 }
 
@@ -282,12 +285,12 @@ __global__ void cross_entropy_fused_kernel(const float* __restrict__ logits, con
 // memory traffic.
 // VEC = 4 reads and writes 16 bytes per thread (row pitches that are multiples of 4 floats).
 constexpr int kWideThreads = 1024, kWideItems = 32;
-template <int VEC>
+template <int VEC, class T>
 __global__ void __launch_bounds__(kWideThreads, 1)
-cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+cross_entropy_fused_wide_kernel(const T* __restrict__ logits, const int32_t* __restrict__ labels,
                                 const float* __restrict__ weights, const float* __restrict__ g,
                                 const float* __restrict__ denominator, float* __restrict__ row_loss,
-                                float* __restrict__ out, uint32_t v, uint32_t ld, uint32_t ld_out,
+                                T* __restrict__ out, uint32_t v, uint32_t ld, uint32_t ld_out,
                                 uint32_t* __restrict__ counter, float* __restrict__ loss) {
     // Element i of this thread is column column_of(i): consecutive threads take consecutive
     // (groups of VEC) columns.
@@ -296,7 +299,7 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
     __shared__ double shared64[33];
     __shared__ bool is_last;
     const uint32_t r = blockIdx.x, tid = threadIdx.x, rows = gridDim.x;
-    float* o = out + static_cast<uint64_t>(r) * ld_out;
+    T* o = out + static_cast<uint64_t>(r) * ld_out;
     // The weight sum: given (the whole batch's, data parallel), or summed here by every block in
     // the same order (f64 over the block, one rounding), so that no launch has to precede this one.
     float den;
@@ -314,7 +317,7 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
     if (w == 0.0f) {
         if (tid == 0) row_loss[r] = 0.0f;
     } else {
-        const float* row = logits + static_cast<uint64_t>(r) * ld;
+        const T* row = logits + static_cast<uint64_t>(r) * ld;
         if (VEC == 4) {
             // Unconditional loads from a clamped column (the pitch covers the whole float4 of the
             // last valid column), so that all eight are in flight together; what lies past v is
@@ -322,12 +325,12 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
             const uint32_t last = (v - 1) & ~3u;
 #pragma unroll
             for (int i = 0; i < kWideItems; i += 4) {
-                const float4 f = __ldg(reinterpret_cast<const float4*>(row + min(column_of(i, tid), last)));
+                const float4 f = load4(row + min(column_of(i, tid), last));
                 x[i] = f.x; x[i + 1] = f.y; x[i + 2] = f.z; x[i + 3] = f.w;
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < kWideItems; ++i) x[i] = __ldg(row + min(column_of(i, tid), v - 1));
+            for (int i = 0; i < kWideItems; ++i) x[i] = load1(row + min(column_of(i, tid), v - 1));
         }
 #pragma unroll
         for (int i = 0; i < kWideItems; ++i)
@@ -348,7 +351,7 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
         }
         total = block_sum(sum, shared);
         label = static_cast<uint32_t>(labels[r]);
-        if (tid == 0) row_loss[r] = m + logf(total) - (label < v ? row[label] : 0.0f);
+        if (tid == 0) row_loss[r] = m + logf(total) - (label < v ? load1(row + label) : 0.0f);
     }
     // The loss, by the last block to get here: sum of w * l over sum of w, f64 sums, one rounding.
     // Only thread 0's row loss has to be visible to that block, so only thread 0 fences, and the
@@ -387,13 +390,13 @@ cross_entropy_fused_wide_kernel(const float* __restrict__ logits, const int32_t*
         for (int i = 0; i < kWideItems; i += 4) {
             const uint32_t c = column_of(i, tid);
             // Columns past v inside the pitch are padding nobody reads: the whole float4 is written.
-            if (c < v) *reinterpret_cast<float4*>(o + c) = make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]);
+            if (c < v) store4(o + c, make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]));
         }
     } else {
 #pragma unroll
         for (int i = 0; i < kWideItems; ++i) {
             const uint32_t c = column_of(i, tid);
-            if (c < v) o[c] = x[i];
+            if (c < v) store1(o + c, x[i]);
         }
     }
 }
@@ -544,11 +547,11 @@ cross_entropy_fused_split_kernel(const float* __restrict__ logits, const int32_t
 // scaled or zeroed value, one addition, the layer norm of the stored sum). Each part is optional:
 // without a draw on x the sum is x + residual; without gamma the launch ends with the sum; with a
 // draw on the result, dropout of the layer norm is written to out_dropped (and out may be null).
-template <int ITEMS>
+template <int ITEMS, class T>
 __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
-    const float* __restrict__ x, const float* __restrict__ residual, DropoutDraw x_draw, const float* __restrict__ gamma,
-    const float* __restrict__ beta, float* __restrict__ sum_out, float* __restrict__ out, DropoutDraw out_draw,
-    float* __restrict__ out_dropped, uint32_t rows, uint32_t h, bool gelu_first) {
+    const T* __restrict__ x, const T* __restrict__ residual, DropoutDraw x_draw, const float* __restrict__ gamma,
+    const float* __restrict__ beta, T* __restrict__ sum_out, T* __restrict__ out, DropoutDraw out_draw,
+    T* __restrict__ out_dropped, uint32_t rows, uint32_t h, bool gelu_first) {
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (r >= rows) return;
@@ -557,10 +560,10 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
     // the Philox rounds of the first element start.
     float v[ITEMS], xs[ITEMS];
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) xs[i] = __ldg(x + base + min(i * 32 + lane, h - 1));
+    for (int i = 0; i < ITEMS; ++i) xs[i] = load1(x + base + min(i * 32 + lane, h - 1));
     if (residual != nullptr) {
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) v[i] = __ldg(residual + base + min(i * 32 + lane, h - 1));
+        for (int i = 0; i < ITEMS; ++i) v[i] = load1(residual + base + min(i * 32 + lane, h - 1));
     }
     // gelu(x) in the place of the sum (the head's transform: dense, gelu, layer norm).
     if (gelu_first) {
@@ -580,7 +583,9 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
     for (int i = 0; i < ITEMS; ++i) {
         const uint32_t c = i * 32 + lane;
         v[i] = c < h ? (residual != nullptr ? v[i] + xs[i] : xs[i]) : 0.0f;
-        if (c < h) sum_out[base + c] = v[i];
+        // What is stored is what the layer norm below reads: the sum as its storage type holds it.
+        v[i] = stored_as(v[i], static_cast<const T*>(nullptr));
+        if (c < h && sum_out != nullptr) store1(sum_out + base + c, v[i]);
     }
     if (gamma == nullptr) return;
     const float width = static_cast<float>(h);
@@ -607,11 +612,11 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
         const uint32_t c = i * 32 + lane;
         if (c >= h) continue;
         const float y = (v[i] - mean) * rstd * gamma[c] + beta[c];
-        if (out != nullptr) out[base + c] = y;
+        if (out != nullptr) store1(out + base + c, y);
         if (out_dropped != nullptr) {
             const uint32_t w0 = philox_word0(static_cast<uint32_t>(out_draw.index_base + base + c), 4u, id_lo, id_hi,
                                              static_cast<uint32_t>(out_draw.seed), static_cast<uint32_t>(out_draw.seed >> 32));
-            out_dropped[base + c] = w0 >= out_draw.threshold ? y * out_draw.scale : 0.0f;
+            store1(out_dropped + base + c, w0 >= out_draw.threshold ? y * out_draw.scale : 0.0f);
         }
     }
 }
@@ -623,13 +628,13 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
 // chunks w, w + 8, ... in ascending order and the eight sums are added in ascending w. Every
 // output is a fixed expression of the inputs: deterministic, tolerance class against a
 // sequential column sum. dx (with gamma), dgamma and dbeta may each be null.
-template <int ITEMS>
+template <int ITEMS, class T>
 __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
-    const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ g, const float* __restrict__ g1,
-    const float* __restrict__ g2, const float* __restrict__ g3, float* __restrict__ dx,
+    const T* __restrict__ x, const float* __restrict__ gamma, const T* __restrict__ g, const T* __restrict__ g1,
+    const T* __restrict__ g2, const T* __restrict__ g3, T* __restrict__ dx,
     float* __restrict__ partial, uint32_t* __restrict__ counter, float* __restrict__ dgamma, float* __restrict__ dbeta,
     uint32_t want, uint32_t rows, uint32_t h, uint32_t rows_per_chunk, DropoutDraw adjoint_draw, DropoutDraw dx_draw,
-    float* __restrict__ dx_dropped, const float* __restrict__ pre_activation) {
+    T* __restrict__ dx_dropped, const T* __restrict__ pre_activation) {
     __shared__ float buf[8 * 32 * ITEMS];
     __shared__ bool is_last;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, chunks = gridDim.x;
@@ -652,15 +657,15 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
         const uint64_t row_at = static_cast<uint64_t>(r) * h;
         float xv[ITEMS], gv[ITEMS];
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) xv[i] = __ldg(x + row_at + min(i * 32 + lane, h - 1));
+        for (int i = 0; i < ITEMS; ++i) xv[i] = load1(x + row_at + min(i * 32 + lane, h - 1));
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) gv[i] = __ldg(g + row_at + min(i * 32 + lane, h - 1));
+        for (int i = 0; i < ITEMS; ++i) gv[i] = load1(g + row_at + min(i * 32 + lane, h - 1));
         // The adjoint as a sum the program spells as a chain of Adds: ((g + g1) + g2) + g3.
-        for (const float* more : {g1, g2, g3}) {
+        for (const T* more : {g1, g2, g3}) {
             if (more == nullptr) continue;
             float t[ITEMS];
 #pragma unroll
-            for (int i = 0; i < ITEMS; ++i) t[i] = __ldg(more + row_at + min(i * 32 + lane, h - 1));
+            for (int i = 0; i < ITEMS; ++i) t[i] = load1(more + row_at + min(i * 32 + lane, h - 1));
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) gv[i] = gv[i] + t[i];
         }
@@ -711,7 +716,7 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
             float pre[ITEMS];
             if (pre_activation != nullptr) {
 #pragma unroll
-                for (int i = 0; i < ITEMS; ++i) pre[i] = __ldg(pre_activation + row_at + min(i * 32 + lane, h - 1));
+                for (int i = 0; i < ITEMS; ++i) pre[i] = load1(pre_activation + row_at + min(i * 32 + lane, h - 1));
             }
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
@@ -720,17 +725,17 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
                     float gx = gv[i] * gam[i];
                     float xhat = (xv[i] - mean) * rstd;
                     const float value = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
-                    if (dx != nullptr) dx[row_at + c] = value;
+                    if (dx != nullptr) store1(dx + row_at + c, value);
                     // A function of dx for the reader that wants that: gelu_grad (the dense layer
                     // before a gelu and this layer norm), or dropout_grad (the projection before
                     // this sublayer's dropout).
                     if (pre_activation != nullptr) {
-                        dx_dropped[row_at + c] = gelu_grad_value(pre[i], value);
+                        store1(dx_dropped + row_at + c, gelu_grad_value(pre[i], value));
                     } else if (dx_dropped != nullptr) {
                         const uint32_t w0 = philox_word0(static_cast<uint32_t>(dx_draw.index_base + row_at + c), 4u,
                                                          static_cast<uint32_t>(dx_draw.token[0]), static_cast<uint32_t>(dx_draw.token[1]),
                                                          static_cast<uint32_t>(dx_draw.seed), static_cast<uint32_t>(dx_draw.seed >> 32));
-                        dx_dropped[row_at + c] = w0 >= dx_draw.threshold ? value * dx_draw.scale : 0.0f;
+                        store1(dx_dropped + row_at + c, w0 >= dx_draw.threshold ? value * dx_draw.scale : 0.0f);
                     }
                 }
             }
@@ -776,6 +781,39 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
             }
         }
     }
+}
+
+// The one-read kernels: f32 rows of more than 16,384 logits with a 16-byte pitch as two 512-thread
+// blocks per SM, every other case as one 1,024-thread block with the row in registers.
+void launch_cross_entropy_one_read(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights, const float* g,
+                                   const float* den, float* row_loss, float* grad, uint32_t vv, uint32_t l1, uint32_t l2, uint32_t* counter,
+                                   float* loss, uint64_t rows, bool vec) {
+    if (vec && vv > 16384) {
+        static const bool configured = [] {
+            cudaFuncSetAttribute(cross_entropy_fused_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSplitSharedBytes);
+            return true;
+        }();
+        (void)configured;
+        cross_entropy_fused_split_kernel<<<static_cast<uint32_t>(rows), kSplitThreads, kSplitSharedBytes, s>>>(logits, labels, weights, g, den,
+                                                                                                              row_loss, grad, vv, l1, l2,
+                                                                                                              counter, loss);
+    } else if (vec) {
+        cross_entropy_fused_wide_kernel<4><<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(logits, labels, weights, g, den, row_loss,
+                                                                                                grad, vv, l1, l2, counter, loss);
+    } else {
+        cross_entropy_fused_wide_kernel<1><<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(logits, labels, weights, g, den, row_loss,
+                                                                                                grad, vv, l1, l2, counter, loss);
+    }
+}
+void launch_cross_entropy_one_read(cudaStream_t s, const bf16* logits, const int32_t* labels, const float* weights, const float* g,
+                                   const float* den, float* row_loss, bf16* grad, uint32_t vv, uint32_t l1, uint32_t l2, uint32_t* counter,
+                                   float* loss, uint64_t rows, bool vec) {
+    if (vec)
+        cross_entropy_fused_wide_kernel<4><<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(logits, labels, weights, g, den, row_loss,
+                                                                                                grad, vv, l1, l2, counter, loss);
+    else
+        cross_entropy_fused_wide_kernel<1><<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(logits, labels, weights, g, den, row_loss,
+                                                                                                grad, vv, l1, l2, counter, loss);
 }
 
 uint32_t backward_chunks(uint64_t rows) {
@@ -831,15 +869,12 @@ void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float
     check_launch("layer_norm_grad_gamma");
 }
 
-void add_layer_norm(cudaStream_t s, const float* x, const float* residual, const DropoutDraw* x_draw, const float* gamma,
-                    const float* beta, float* sum_out, float* out, const DropoutDraw* out_draw, float* out_dropped, uint64_t rows,
-                    uint64_t h, bool gelu_first) {
-    if (rows == 0 || h == 0) return;
+namespace {
+template <class T>
+void launch_add_layer_norm(cudaStream_t s, const T* x, const T* residual, const DropoutDraw& first, const float* gamma, const float* beta,
+                           T* sum_out, T* out, const DropoutDraw& second, T* out_dropped, uint64_t rows, uint64_t h, bool gelu_first) {
     const uint32_t items = static_cast<uint32_t>((h + 31) / 32), blocks = static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
-    const DropoutDraw none = {};
-    const DropoutDraw first = x_draw ? *x_draw : none, second = out_draw ? *out_draw : none;
-    if (out_draw == nullptr || gamma == nullptr) out_dropped = nullptr;
 #define MSX_DROPOUT_LN(N) dropout_add_layer_norm_kernel<N><<<blocks, 256, 0, s>>>(x, residual, first, gamma, beta, sum_out, out, second, out_dropped, r, hh, gelu_first)
     if (items <= 1) MSX_DROPOUT_LN(1);
     else if (items <= 2) MSX_DROPOUT_LN(2);
@@ -851,37 +886,55 @@ void add_layer_norm(cudaStream_t s, const float* x, const float* residual, const
 #undef MSX_DROPOUT_LN
     check_launch("add_layer_norm");
 }
+template <class T> const T* typed(In a) { return static_cast<const T*>(a.p); }
+template <class T> T* typed(Out a) { return static_cast<T*>(a.p); }
+}  // namespace
 
-void dropout_add_layer_norm(cudaStream_t s, const float* x, const float* residual, const int32_t* token, uint64_t seed,
+void add_layer_norm(cudaStream_t s, In x, In residual, const DropoutDraw* x_draw, const float* gamma,
+                    const float* beta, Out sum_out, Out out, const DropoutDraw* out_draw, Out out_dropped, uint64_t rows,
+                    uint64_t h, bool gelu_first) {
+    if (rows == 0 || h == 0) return;
+    const DropoutDraw none = {};
+    const DropoutDraw first = x_draw ? *x_draw : none, second = out_draw ? *out_draw : none;
+    if (out_draw == nullptr || gamma == nullptr) out_dropped = Out();
+    // The element type of the launch is that of x; the optional operands that are present share it.
+    const bool half = x.half;
+    for (bool other : {residual ? residual.half : half, sum_out ? sum_out.half : half, out ? out.half : half, out_dropped ? out_dropped.half : half})
+        if (other != half) throw std::invalid_argument("add_layer_norm: f32 and bf16 activation operands in one launch");
+    if (half)
+        launch_add_layer_norm(s, typed<bf16>(x), typed<bf16>(residual), first, gamma, beta, typed<bf16>(sum_out), typed<bf16>(out), second,
+                              typed<bf16>(out_dropped), rows, h, gelu_first);
+    else
+        launch_add_layer_norm(s, typed<float>(x), typed<float>(residual), first, gamma, beta, typed<float>(sum_out), typed<float>(out), second,
+                              typed<float>(out_dropped), rows, h, gelu_first);
+}
+
+void dropout_add_layer_norm(cudaStream_t s, In x, In residual, const int32_t* token, uint64_t seed,
                             uint32_t threshold, float scale, uint64_t index_base, const float* gamma, const float* beta,
-                            float* sum_out, float* out, uint64_t rows, uint64_t h) {
+                            Out sum_out, Out out, uint64_t rows, uint64_t h) {
     DropoutDraw draw;
     draw.token = token;
     draw.seed = seed;
     draw.threshold = threshold;
     draw.scale = scale;
     draw.index_base = index_base;
-    add_layer_norm(s, x, residual, &draw, gamma, beta, sum_out, out, nullptr, nullptr, rows, h, false);
+    add_layer_norm(s, x, residual, &draw, gamma, beta, sum_out, out, nullptr, Out(), rows, h, false);
 }
 
 bool layer_norm_backward_supported(uint64_t h) { return h >= 1 && h <= 1024; }
 uint32_t layer_norm_backward_chunks(uint64_t rows) { return backward_chunks(rows); }
 uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h) { return 2ull * backward_chunks(rows) * h; }
 
-void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, const float* g, float* dx, float* scratch,
-                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const float* g1, const float* g2,
-                         const float* g3, const DropoutDraw* adjoint_draw, const DropoutDraw* dx_draw, float* dx_dropped,
-                         const float* pre_activation) {
-    if (h == 0) return;
+namespace {
+template <class T>
+void launch_layer_norm_backward(cudaStream_t s, const T* x, const float* gamma, const T* g, T* dx, float* scratch, uint32_t* counter,
+                                float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const T* g1, const T* g2, const T* g3,
+                                const DropoutDraw& in_draw, const DropoutDraw& out_draw, T* dx_dropped, const T* pre_activation) {
     uint32_t chunks = backward_chunks(rows);
     uint32_t per = static_cast<uint32_t>((rows + chunks - 1) / chunks);
     uint32_t items = static_cast<uint32_t>((h + 31) / 32);
     uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
     uint32_t want = (dgamma ? 1u : 0u) | (dbeta ? 2u : 0u);
-    const DropoutDraw none = {};
-    const DropoutDraw in_draw = adjoint_draw ? *adjoint_draw : none, out_draw = dx_draw ? *dx_draw : none;
-    if (dx_draw == nullptr && pre_activation == nullptr) dx_dropped = nullptr;
-    if (dx_dropped == nullptr) pre_activation = nullptr;
 #define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped, pre_activation)
     if (items <= 1) MSX_LN_BACKWARD(1);
     else if (items <= 2) MSX_LN_BACKWARD(2);
@@ -892,6 +945,30 @@ void layer_norm_backward(cudaStream_t s, const float* x, const float* gamma, con
     else MSX_LN_BACKWARD(32);
 #undef MSX_LN_BACKWARD
     check_launch("layer_norm_backward");
+}
+}  // namespace
+
+void layer_norm_backward(cudaStream_t s, In x, const float* gamma, In g, Out dx, float* scratch,
+                         uint32_t* counter, float* dgamma, float* dbeta, uint64_t rows, uint64_t h, In g1, In g2,
+                         In g3, const DropoutDraw* adjoint_draw, const DropoutDraw* dx_draw, Out dx_dropped,
+                         In pre_activation) {
+    if (h == 0) return;
+    const DropoutDraw none = {};
+    const DropoutDraw in_draw = adjoint_draw ? *adjoint_draw : none, out_draw = dx_draw ? *dx_draw : none;
+    if (dx_draw == nullptr && !pre_activation) dx_dropped = Out();
+    if (!dx_dropped) pre_activation = In();
+    const bool half = x.half;
+    for (bool other : {g.half, g1 ? g1.half : half, g2 ? g2.half : half, g3 ? g3.half : half, dx ? dx.half : half,
+                       dx_dropped ? dx_dropped.half : half, pre_activation ? pre_activation.half : half})
+        if (other != half) throw std::invalid_argument("layer_norm_backward: f32 and bf16 activation operands in one launch");
+    if (half)
+        launch_layer_norm_backward(s, typed<bf16>(x), gamma, typed<bf16>(g), typed<bf16>(dx), scratch, counter, dgamma, dbeta, rows, h,
+                                   typed<bf16>(g1), typed<bf16>(g2), typed<bf16>(g3), in_draw, out_draw, typed<bf16>(dx_dropped),
+                                   typed<bf16>(pre_activation));
+    else
+        launch_layer_norm_backward(s, typed<float>(x), gamma, typed<float>(g), typed<float>(dx), scratch, counter, dgamma, dbeta, rows, h,
+                                   typed<float>(g1), typed<float>(g2), typed<float>(g3), in_draw, out_draw, typed<float>(dx_dropped),
+                                   typed<float>(pre_activation));
 }
 
 void softmax(cudaStream_t s, const float* x, float* out, uint64_t rows, uint64_t k) {
@@ -911,44 +988,32 @@ void weight_sum(cudaStream_t s, const float* weights, uint64_t rows, float* out)
     check_launch("weight_sum");
 }
 
-void cross_entropy(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
+void cross_entropy(cudaStream_t s, In logits, const int32_t* labels, const float* weights,
                    float* row_loss, const float* global_den, float* loss, uint64_t rows, uint64_t v, uint64_t ld) {
     if (ld == 0) ld = v;
     if (rows > 0) {
-        cross_entropy_rows_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(logits, labels, weights, row_loss,
-                                                                                      static_cast<uint32_t>(v), static_cast<uint32_t>(ld));
+        if (logits.half)
+            cross_entropy_rows_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(typed<bf16>(logits), labels, weights, row_loss,
+                                                                                          static_cast<uint32_t>(v), static_cast<uint32_t>(ld));
+        else
+            cross_entropy_rows_kernel<<<static_cast<uint32_t>(rows), kRowThreads, 0, s>>>(typed<float>(logits), labels, weights, row_loss,
+                                                                                          static_cast<uint32_t>(v), static_cast<uint32_t>(ld));
         check_launch("cross_entropy");
     }
     cross_entropy_loss_kernel<<<1, 1024, 0, s>>>(row_loss, weights, static_cast<uint32_t>(rows), global_den, loss);
     check_launch("cross_entropy");
 }
 
-void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,
-                             const float* g, bool denominator_ready, float* denominator, float* row_loss, float* loss,
-                             float* grad, uint64_t rows, uint64_t v, uint32_t* counter, uint64_t ld, uint64_t ld_grad) {
-    if (ld == 0) ld = v;
-    if (ld_grad == 0) ld_grad = v;
+namespace {
+template <class T>
+void launch_cross_entropy_with_grad(cudaStream_t s, const T* logits, const int32_t* labels, const float* weights, const float* g,
+                                    bool denominator_ready, float* denominator, float* row_loss, float* loss, T* grad, uint64_t rows,
+                                    uint64_t v, uint32_t* counter, uint64_t ld, uint64_t ld_grad) {
     const uint32_t vv = static_cast<uint32_t>(v), l1 = static_cast<uint32_t>(ld), l2 = static_cast<uint32_t>(ld_grad);
     if (rows > 0 && counter != nullptr && v <= static_cast<uint64_t>(kWideThreads) * kWideItems) {
         const float* den = denominator_ready ? denominator : nullptr;
-        const bool vec = ld % 4 == 0 && ld_grad % 4 == 0 && reinterpret_cast<uintptr_t>(logits) % 16 == 0 &&
-                         reinterpret_cast<uintptr_t>(grad) % 16 == 0;
-        // Long rows: two 512-thread blocks per SM. Short ones fit the registers of 1,024 threads.
-        if (vec && v > 16384) {
-            static const bool configured = [] {
-                cudaFuncSetAttribute(cross_entropy_fused_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSplitSharedBytes);
-                return true;
-            }();
-            (void)configured;
-            cross_entropy_fused_split_kernel<<<static_cast<uint32_t>(rows), kSplitThreads, kSplitSharedBytes, s>>>(logits, labels, weights, g, den,
-                                                                                                                  row_loss, grad, vv, l1, l2,
-                                                                                                                  counter, loss);
-        } else if (vec)
-            cross_entropy_fused_wide_kernel<4><<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(logits, labels, weights, g, den, row_loss,
-                                                                                                    grad, vv, l1, l2, counter, loss);
-        else
-            cross_entropy_fused_wide_kernel<1><<<static_cast<uint32_t>(rows), kWideThreads, 0, s>>>(logits, labels, weights, g, den, row_loss,
-                                                                                                    grad, vv, l1, l2, counter, loss);
+        const bool vec = ld % 4 == 0 && ld_grad % 4 == 0 && aligned4(logits) && aligned4(grad);
+        launch_cross_entropy_one_read(s, logits, labels, weights, g, den, row_loss, grad, vv, l1, l2, counter, loss, rows, vec);
         check_launch("cross_entropy_with_grad");
         return;
     }
@@ -963,6 +1028,20 @@ void cross_entropy_with_grad(cudaStream_t s, const float* logits, const int32_t*
     }
     cross_entropy_loss_kernel<<<1, 1024, 0, s>>>(row_loss, weights, static_cast<uint32_t>(rows), denominator_ready ? denominator : nullptr, loss);
     check_launch("cross_entropy_with_grad");
+}
+}  // namespace
+
+void cross_entropy_with_grad(cudaStream_t s, In logits, const int32_t* labels, const float* weights,
+                             const float* g, bool denominator_ready, float* denominator, float* row_loss, float* loss,
+                             Out grad, uint64_t rows, uint64_t v, uint32_t* counter, uint64_t ld, uint64_t ld_grad) {
+    if (ld == 0) ld = v;
+    if (ld_grad == 0) ld_grad = v;
+    if (all_half({logits.half, grad.half}, "cross_entropy_with_grad"))
+        launch_cross_entropy_with_grad(s, typed<bf16>(logits), labels, weights, g, denominator_ready, denominator, row_loss, loss,
+                                       typed<bf16>(grad), rows, v, counter, ld, ld_grad);
+    else
+        launch_cross_entropy_with_grad(s, typed<float>(logits), labels, weights, g, denominator_ready, denominator, row_loss, loss,
+                                       typed<float>(grad), rows, v, counter, ld, ld_grad);
 }
 
 void cross_entropy_grad(cudaStream_t s, const float* logits, const int32_t* labels, const float* weights,

@@ -135,6 +135,10 @@ struct msx_plan {
     uint64_t arena_bytes = 0, unshared_bytes = 0;
     std::vector<float*> params, m, v;  // by parameter index; null when the program has none
     std::vector<char> owns_param;
+    // Mixed precision: the bf16 working copy of every matrix parameter, which the matmuls read; the
+    // optimizer launch and msx_param_upload keep it equal to the rounded f32 master.
+    std::vector<void*> params16;
+    std::vector<char> owns_param16;
     char* d_inputs = nullptr;
     uint64_t input_bytes = 0;
     std::vector<char> blob;  // the staged inputs, host side
@@ -217,6 +221,20 @@ struct msx_plan {
         }
     }
     float* f(uint32_t pos) const { return static_cast<float*>(ptr(pos)); }
+    // The same with the storage type, for the launchers that take either.
+    bool half(uint32_t pos) const {
+        const Slot& s = slots[pos];
+        return s.kind == Slot::View ? half(s.index) : s.half;
+    }
+    k::In in(uint32_t pos) const { return k::In(ptr(pos), half(pos)); }
+    k::Out out(uint32_t pos) const { return k::Out(ptr(pos), half(pos)); }
+    // A matmul operand of a mixed-precision plan: a bf16 activation, or the working copy of a parameter.
+    const void* h16(uint32_t pos) const {
+        const Slot& s = slots[pos];
+        if (s.kind == Slot::View) return h16(s.index);
+        if (s.kind == Slot::Param) return params16[s.index];
+        return s.kind == Slot::Arena && s.half ? arena + s.offset : nullptr;
+    }
     int32_t* i(uint32_t pos) const { return static_cast<int32_t*>(ptr(pos)); }
     bool transposed(uint32_t pos) const {
         const Slot& s = slots[pos];
@@ -450,6 +468,46 @@ struct Scheduler {
         return base;
     }
 
+    // A mixed-precision plan (MSX_PLAN_BF16) stores every rank-2 f32 intermediate as bf16;
+    // program outputs (the loss, the gradients the optimizer and the buckets read), vectors,
+    // scalars, partial sums and everything the host supplies stay f32.
+    bool mixed() const { return (P->flags & MSX_PLAN_BF16) != 0; }
+    bool stored_half(const Node& n) const {
+        if (!mixed() || n.ty.rank() != 2 || n.ty.i32) return false;
+        for (const msx::Output& o : prog.outputs)
+            if (o.value == n.id) return false;
+        return true;
+    }
+    void make_arena(Slot& slot, const Node& n) {
+        slot.kind = Slot::Arena;
+        slot.half = stored_half(n);
+        slot.bytes = std::max<uint64_t>(n.ty.count() * (slot.half ? 2 : 4), 4);
+    }
+    // Every bf16 matrix a launch touches has rows of a multiple of 8 elements as stored (16 bytes:
+    // what TMA and the 8-byte accesses of the row kernels need), by its width or by its pitch.
+    void check_half_widths() const {
+        for (const Launch& l : P->launches)
+            for (const std::vector<uint32_t>* touched : {&l.reads, &l.writes})
+                for (uint32_t t : *touched) {
+                    const Slot& slot = P->slots[t];
+                    if (t >= prog.nodes.size() || slot.kind != Slot::Arena || !slot.half) continue;
+                    const Node& n = node(t);
+                    if ((slot.pitch ? slot.pitch : n.ty.shape[1]) % 8 != 0)
+                        throw StatusError(MSX_UNSUPPORTED, "E-TARGET-011: %" + std::to_string(n.id) + " " + msx::op_name(n.op) +
+                                                               ": a bf16 plan stores matrices whose rows are a multiple of 8 elements");
+                }
+    }
+    // The launches whose kernels read and write bf16 activations.
+    static bool half_capable(const std::string& kernel) {
+        static const char* const names[] = {"embedding", "embedding_grad", "add_layer_norm", "add_layer_norm_dropout", "dropout_add_layer_norm",
+                                            "dropout_add", "gelu_layer_norm", "layer_norm", "matmul", "attention_forward", "attention_backward",
+                                            "gelu", "unary", "gelu_grad", "dropout", "layer_norm_backward", "cross_entropy_with_grad",
+                                            "cross_entropy", "sum_rows", "sum_rows_batched"};
+        for (const char* name : names)
+            if (kernel == name) return true;
+        return false;
+    }
+
     uint32_t scratch(uint64_t bytes) {
         Slot s;
         s.kind = Slot::Arena;
@@ -469,6 +527,11 @@ struct Scheduler {
         l.reads = std::move(reads);
         l.writes = std::move(writes);
         l.run = std::move(run);
+        if (mixed() && !half_capable(l.kernel))
+            for (const std::vector<uint32_t>* touched : {&l.reads, &l.writes})
+                for (uint32_t t : *touched)
+                    if (P->slots[t].half) unsupported(n, std::string("its kernel (") + kernel + ") has no bf16 form, and a bf16 plan stores %" +
+                                                             (t < prog.nodes.size() ? std::to_string(node(t).id) : std::string("scratch")) + " as bf16");
         P->launches.push_back(std::move(l));
         return P->launches.back();
     }
@@ -506,6 +569,7 @@ struct Scheduler {
             if (live[at] && !handled[at]) schedule(at);
         emit_finalize();
         emit_optimizer();
+        if (mixed()) check_half_widths();
         mark_side_launches();
         for (const msx::Output& o : prog.outputs) {
             Slot& s = P->slots[pos(o.value)];
@@ -528,6 +592,8 @@ struct Scheduler {
         P->m.assign(np, nullptr);
         P->v.assign(np, nullptr);
         P->owns_param.assign(np, 0);
+        P->params16.assign(np, nullptr);
+        P->owns_param16.assign(np, 0);
         uint64_t offset = 0;
         for (uint32_t at = 0; at < prog.nodes.size(); ++at) {
             const Node& nd = node(at);
@@ -802,8 +868,7 @@ struct Scheduler {
         const Node& nd = node(at);
         msx_plan* plan = P;
         Slot& out = P->slots[at];
-        out.kind = Slot::Arena;
-        out.bytes = std::max<uint64_t>(nd.ty.count() * 4, 4);
+        make_arena(out, nd);
         std::vector<uint32_t> in;
         for (uint32_t o : nd.operands) in.push_back(pos(o));
         const uint64_t count = nd.ty.count();
@@ -856,17 +921,16 @@ struct Scheduler {
                         const uint32_t gamma = pos(node(ln_at).operands[1]), beta = pos(node(ln_at).operands[2]);
                         handled[ln_at] = 1;
                         Slot& slot = P->slots[ln_at];
-                        slot.kind = Slot::Arena;
-                        slot.bytes = std::max<uint64_t>(node(ln_at).ty.count() * 4, 4);
+                        make_arena(slot, node(ln_at));
                         const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
                         emit("gelu_layer_norm", nd, {a, gamma, beta}, {at, ln_at}, [=](cudaStream_t s) {
-                            k::add_layer_norm(s, plan->f(a), nullptr, nullptr, plan->f(gamma), plan->f(beta), plan->f(at), plan->f(ln_at), nullptr,
-                                              nullptr, r, h, true);
+                            k::add_layer_norm(s, plan->in(a), k::In(), nullptr, plan->f(gamma), plan->f(beta), plan->out(at), plan->out(ln_at), nullptr,
+                                              k::Out(), r, h, true);
                         });
                         break;
                     }
                 }
-                emit(nd.op == Op::Gelu ? "gelu" : "unary", nd, in, {at}, [=](cudaStream_t s) { k::unary(s, op, plan->f(a), plan->f(at), count); });
+                emit(nd.op == Op::Gelu ? "gelu" : "unary", nd, in, {at}, [=](cudaStream_t s) { k::unary(s, op, plan->in(a), plan->out(at), count); });
                 break;
             }
             case Op::ReluGrad:
@@ -874,7 +938,7 @@ struct Scheduler {
                 bool gelu = nd.op == Op::GeluGrad;
                 uint32_t a = in[0], g = in[1];
                 emit(gelu ? "gelu_grad" : "relu_grad", nd, in, {at}, [=](cudaStream_t s) {
-                    if (gelu) k::gelu_grad(s, plan->f(a), plan->f(g), plan->f(at), count);
+                    if (gelu) k::gelu_grad(s, plan->in(a), plan->in(g), plan->out(at), count);
                     else k::relu_grad(s, plan->f(a), plan->f(g), plan->f(at), count);
                 });
                 break;
@@ -888,7 +952,7 @@ struct Scheduler {
                 uint64_t m = nd.ty.shape[0], n = nd.ty.shape[1], kk = cols_of(in[0]);
                 std::vector<Product> group = {claim_product(at)};
                 const bool pitched = pitch_of(group[0].a) || pitch_of(group[0].b) || pitchable(group[0].result);
-                if ((fusion_mask() & 4u) && !(P->flags & MSX_PLAN_EXACT_MATMUL) && !pitched && group[0].bias < 0 &&
+                if ((fusion_mask() & 4u) && !(P->flags & MSX_PLAN_EXACT_MATMUL) && !mixed() && !pitched && group[0].bias < 0 &&
                     nd.tag == msx::Tag::Gradient && deferrable(group[0].result)) {
                     const uint64_t operand_bytes = (m * kk + kk * n) * 4;
                     // Only products too small to fill the device on their own: a large one is better
@@ -911,7 +975,7 @@ struct Scheduler {
                 }
                 // Later matmuls of the same shape and storage form whose operands already exist
                 // (the three projections of an attention layer, their gradients) join the launch.
-                if (!(P->flags & MSX_PLAN_EXACT_MATMUL) && !pitched)
+                if (!(P->flags & MSX_PLAN_EXACT_MATMUL) && !mixed() && !pitched)
                     for (uint32_t later = at + 1; later < prog.nodes.size() && later < at + 64 && group.size() < 4; ++later)
                         if (joins(later, group[0], at, m, n, kk)) group.push_back(claim_product(later));
                 emit_matmul(nd, group, m, n, kk);
@@ -957,7 +1021,7 @@ struct Scheduler {
                 uint32_t table = in[0], ids = in[1];
                 uint64_t n = rows_of(ids), rows = rows_of(table), h = cols_of(table);
                 emit("embedding", nd, in, {at}, [=](cudaStream_t s) {
-                    k::embedding(s, plan->f(table), plan->i(ids), plan->f(at), n, rows, h, plan->d_status);
+                    k::embedding(s, plan->in(table), plan->i(ids), plan->out(at), n, rows, h, plan->d_status);
                 });
                 // The gradient of this lookup sorts the same ids: that half of it needs nothing
                 // else, so it is issued here (and runs beside the forward pass).
@@ -993,8 +1057,7 @@ struct Scheduler {
                             handled[u] = 1;
                             out.kind = Slot::Dead;
                             Slot& sum = P->slots[u];
-                            sum.kind = Slot::Arena;
-                            sum.bytes = std::max<uint64_t>(add.ty.count() * 4, 4);
+                            make_arena(sum, add);
                             // `other` is read by this sum alone and was written by an earlier launch:
                             // it is stored where the sum goes, and the scatter touches only the rows
                             // some id names (a table of 30,522 rows read by 4,096 ids: an eighth).
@@ -1005,11 +1068,11 @@ struct Scheduler {
                             }
                             if (have_order)
                                 emit("embedding_grad", nd, {g, other, tmp}, {u}, [=](cudaStream_t s) {
-                                    k::embedding_scatter(s, plan->f(g), plan->f(u), n, rows, h, plan->i(tmp), plan->f(other));
+                                    k::embedding_scatter(s, plan->in(g), plan->out(u), n, rows, h, plan->i(tmp), plan->f(other));
                                 });
                             else
                                 emit("embedding_grad", nd, {ids, g, other}, {u, tmp}, [=](cudaStream_t s) {
-                                    k::embedding_grad(s, plan->i(ids), plan->f(g), plan->f(u), n, rows, h, plan->i(tmp), plan->d_status,
+                                    k::embedding_grad(s, plan->i(ids), plan->in(g), plan->out(u), n, rows, h, plan->i(tmp), plan->d_status,
                                                       plan->f(other));
                                 });
                             break;
@@ -1018,11 +1081,11 @@ struct Scheduler {
                 }
                 if (have_order)
                     emit("embedding_grad", nd, {g, tmp}, {at}, [=](cudaStream_t s) {
-                        k::embedding_scatter(s, plan->f(g), plan->f(at), n, rows, h, plan->i(tmp));
+                        k::embedding_scatter(s, plan->in(g), plan->out(at), n, rows, h, plan->i(tmp));
                     });
                 else
                     emit("embedding_grad", nd, in, {at, tmp}, [=](cudaStream_t s) {
-                        k::embedding_grad(s, plan->i(ids), plan->f(g), plan->f(at), n, rows, h, plan->i(tmp), plan->d_status);
+                        k::embedding_grad(s, plan->i(ids), plan->in(g), plan->out(at), n, rows, h, plan->i(tmp), plan->d_status);
                     });
                 break;
             }
@@ -1045,18 +1108,26 @@ struct Scheduler {
                 }
                 if (deferrable(at)) {
                     uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4);
-                    emit("sum_rows", nd, in, {tmp}, [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), nullptr, nullptr, ld); });
+                    emit("sum_rows", nd, in, {tmp}, [=](cudaStream_t s) { k::sum_rows(s, plan->in(g), r, h, plan->f(tmp), nullptr, nullptr, ld); });
                     deferred.push_back({tmp, 0, k::sum_rows_chunks(r), h, at});
                     break;
                 }
                 uint32_t tmp = scratch(k::sum_rows_scratch_floats(r, h) * 4), ctr = counters(k::sum_rows_counters(h));
                 emit("sum_rows", nd, in, {at, tmp},
-                     [=](cudaStream_t s) { k::sum_rows(s, plan->f(g), r, h, plan->f(tmp), plan->f(at), plan->counter(ctr), ld); });
+                     [=](cudaStream_t s) { k::sum_rows(s, plan->in(g), r, h, plan->f(tmp), plan->f(at), plan->counter(ctr), ld); });
                 break;
             }
             case Op::LayerNorm: {
                 uint32_t x = in[0], gamma = in[1], beta = in[2];
                 uint64_t r = rows_of(x), h = cols_of(x);
+                if (out.half) {
+                    // bf16 rows go through the kernel of the fused tails, with nothing fused to it.
+                    if (!k::layer_norm_backward_supported(h)) unsupported(nd, "a bf16 layer norm of rows longer than 1,024");
+                    emit("layer_norm", nd, in, {at}, [=](cudaStream_t s) {
+                        k::add_layer_norm(s, plan->in(x), k::In(), nullptr, plan->f(gamma), plan->f(beta), k::Out(), plan->out(at), nullptr, k::Out(), r, h);
+                    });
+                    break;
+                }
                 emit("layer_norm", nd, in, {at}, [=](cudaStream_t s) {
                     k::layer_norm(s, plan->f(x), plan->f(gamma), plan->f(beta), plan->f(at), r, h);
                 });
@@ -1130,8 +1201,7 @@ struct Scheduler {
                     uint32_t gpos = static_cast<uint32_t>(grad), seed = pos(node(gpos).operands[3]);
                     handled[gpos] = 1;
                     Slot& gs = P->slots[gpos];
-                    gs.kind = Slot::Arena;
-                    gs.bytes = std::max<uint64_t>(node(gpos).ty.count() * 4, 4);
+                    make_arena(gs, node(gpos));
                     if (pitchable(gpos)) set_pitch(gpos);
                     const uint64_t ld_grad = gs.pitch;
                     uint32_t ctr = counters(1);
@@ -1149,8 +1219,8 @@ struct Scheduler {
                             k::weight_sum(s, plan->f(weights), r, total);
                             all_reduce(plan, total, 1, false, s);
                         }
-                        k::cross_entropy_with_grad(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(seed), plan->comm != nullptr,
-                                                   total, plan->f(row_loss), plan->f(at), plan->f(gpos), r, v, plan->counter(ctr), ld,
+                        k::cross_entropy_with_grad(s, plan->in(logits), plan->i(labels), plan->f(weights), plan->f(seed), plan->comm != nullptr,
+                                                   total, plan->f(row_loss), plan->f(at), plan->out(gpos), r, v, plan->counter(ctr), ld,
                                                    ld_grad);
                         if (side) {
                             cuda_ok(cudaEventRecord(plan->loss_ready, s), "cudaEventRecord");
@@ -1170,7 +1240,7 @@ struct Scheduler {
                         k::weight_sum(s, plan->f(weights), r, plan->f(den));
                         all_reduce(plan, plan->f(den), 1, false, s);
                     }
-                    k::cross_entropy(s, plan->f(logits), plan->i(labels), plan->f(weights), plan->f(row_loss),
+                    k::cross_entropy(s, plan->in(logits), plan->i(labels), plan->f(weights), plan->f(row_loss),
                                      plan->comm ? plan->f(den) : nullptr, plan->f(at), r, v, ld);
                     all_reduce(plan, plan->f(at), 1, false, s);
                 });
@@ -1229,14 +1299,13 @@ struct Scheduler {
                                 out.kind = Slot::Dead;
                                 for (uint32_t made : {add_at, ln_at}) {
                                     Slot& slot = P->slots[made];
-                                    slot.kind = Slot::Arena;
-                                    slot.bytes = std::max<uint64_t>(node(made).ty.count() * 4, 4);
+                                    make_arena(slot, node(made));
                                 }
                                 const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
                                 emit("dropout_add_layer_norm", nd, {x, token, residual, gamma, beta}, {add_at, ln_at}, [=](cudaStream_t s) {
-                                    k::dropout_add_layer_norm(s, plan->f(x), plan->f(residual), plan->i(token), plan->seed, threshold, scale,
+                                    k::dropout_add_layer_norm(s, plan->in(x), plan->in(residual), plan->i(token), plan->seed, threshold, scale,
                                                               plan->shard_rows_before * row_width, plan->f(gamma), plan->f(beta),
-                                                              plan->f(add_at), plan->f(ln_at), r, h);
+                                                              plan->out(add_at), plan->out(ln_at), r, h);
                                 });
                                 break;
                             }
@@ -1244,22 +1313,21 @@ struct Scheduler {
                             handled[add_at] = 1;
                             out.kind = Slot::Dead;
                             Slot& slot = P->slots[add_at];
-                            slot.kind = Slot::Arena;
-                            slot.bytes = std::max<uint64_t>(add.ty.count() * 4, 4);
+                            make_arena(slot, add);
                             const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
                             const Draw draw = draw_of(at);
                             emit("dropout_add", nd, {x, token, residual}, {add_at}, [=](cudaStream_t s) {
                                 const k::DropoutDraw first = launch_draw(plan, draw, h);
-                                k::add_layer_norm(s, plan->f(x), plan->f(residual), &first, nullptr, nullptr, plan->f(add_at), nullptr, nullptr,
-                                                  nullptr, r, h);
+                                k::add_layer_norm(s, plan->in(x), plan->in(residual), &first, nullptr, nullptr, plan->out(add_at), k::Out(), nullptr,
+                                                  k::Out(), r, h);
                             });
                             break;
                         }
                     }
                 }
                 emit("dropout", nd, in, {at}, [=](cudaStream_t s) {
-                    k::dropout(s, plan->f(x), plan->i(token), plan->seed, threshold, scale, plan->shard_rows_before * row_width,
-                               plan->f(at), count);
+                    k::dropout(s, plan->in(x), plan->i(token), plan->seed, threshold, scale, plan->shard_rows_before * row_width,
+                               plan->out(at), count);
                 });
                 break;
             }
@@ -1357,16 +1425,15 @@ struct Scheduler {
         }
         for (uint32_t made : writes) {
             Slot& slot = P->slots[made];
-            slot.kind = Slot::Arena;
-            slot.bytes = std::max<uint64_t>(node(made).ty.count() * 4, 4);
+            make_arena(slot, node(made));
         }
         msx_plan* plan = P;
         const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
         emit(dropout >= 0 ? "add_layer_norm_dropout" : "add_layer_norm", nd, reads, writes, [=](cudaStream_t s) {
             const k::DropoutDraw second = launch_draw(plan, draw, h);
-            k::add_layer_norm(s, plan->f(a), plan->f(b), nullptr, plan->f(gamma), plan->f(beta), plan->f(at),
-                              dropout >= 0 ? nullptr : plan->f(ln_at), dropout >= 0 ? &second : nullptr,
-                              dropout >= 0 ? plan->f(static_cast<uint32_t>(dropout)) : nullptr, r, h);
+            k::add_layer_norm(s, plan->in(a), plan->in(b), nullptr, plan->f(gamma), plan->f(beta), plan->out(at),
+                              dropout >= 0 ? k::Out() : plan->out(ln_at), dropout >= 0 ? &second : nullptr,
+                              dropout >= 0 ? plan->out(static_cast<uint32_t>(dropout)) : k::Out(), r, h);
         });
         return true;
     }
@@ -1485,13 +1552,14 @@ struct Scheduler {
             uint32_t u = static_cast<uint32_t>(other);
             handled[u] = 1;
             Slot& slot = P->slots[u];
-            slot.kind = Slot::Arena;
-            slot.bytes = std::max<uint64_t>(node(u).ty.count() * 4, 4);
+            make_arena(slot, node(u));
             writes.push_back(u);
         }
         uint32_t tmp = scratch(k::layer_norm_backward_scratch_floats(r, h) * 4);
         msx_plan* plan = P;
         auto at_or_null = [plan](int p) -> float* { return p >= 0 ? plan->f(static_cast<uint32_t>(p)) : nullptr; };
+        auto in_or_null = [plan](int p) { return p >= 0 ? plan->in(static_cast<uint32_t>(p)) : k::In(); };
+        auto out_or_null = [plan](int p) { return p >= 0 ? plan->out(static_cast<uint32_t>(p)) : k::Out(); };
         auto draw_now = [plan, h](const Draw& d) { return launch_draw(plan, d, h); };
         const bool defer = (dgamma < 0 || deferrable(static_cast<uint32_t>(dgamma))) && (dbeta < 0 || deferrable(static_cast<uint32_t>(dbeta)));
         if (defer) {
@@ -1506,11 +1574,11 @@ struct Scheduler {
             float* const wanted = reinterpret_cast<float*>(uintptr_t{1});  // only null or not is read
             emit("layer_norm_backward", nd, reads, now, [=](cudaStream_t s) {
                 const k::DropoutDraw in_draw = draw_now(adjoint_draw), out_draw = draw_now(dx_draw);
-                k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(stored_dx), plan->f(tmp), nullptr,
+                k::layer_norm_backward(s, plan->in(x), at_or_null(gamma), plan->in(adjoint[0]), out_or_null(stored_dx), plan->f(tmp), nullptr,
                                        dgamma >= 0 ? wanted : nullptr, dbeta >= 0 ? wanted : nullptr, r, h,
-                                       adjoint.size() > 1 ? plan->f(adjoint[1]) : nullptr, adjoint.size() > 2 ? plan->f(adjoint[2]) : nullptr,
-                                       adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr, in_draw.token ? &in_draw : nullptr,
-                                       out_draw.token ? &out_draw : nullptr, at_or_null(dropped), at_or_null(pre_activation));
+                                       adjoint.size() > 1 ? plan->in(adjoint[1]) : k::In(), adjoint.size() > 2 ? plan->in(adjoint[2]) : k::In(),
+                                       adjoint.size() > 3 ? plan->in(adjoint[3]) : k::In(), in_draw.token ? &in_draw : nullptr,
+                                       out_draw.token ? &out_draw : nullptr, out_or_null(dropped), in_or_null(pre_activation));
             });
             return true;
         }
@@ -1518,11 +1586,11 @@ struct Scheduler {
         writes.push_back(tmp);
         emit("layer_norm_backward", nd, reads, writes, [=](cudaStream_t s) {
             const k::DropoutDraw in_draw = draw_now(adjoint_draw), out_draw = draw_now(dx_draw);
-            k::layer_norm_backward(s, plan->f(x), at_or_null(gamma), plan->f(adjoint[0]), at_or_null(stored_dx), plan->f(tmp), plan->counter(ctr),
+            k::layer_norm_backward(s, plan->in(x), at_or_null(gamma), plan->in(adjoint[0]), out_or_null(stored_dx), plan->f(tmp), plan->counter(ctr),
                                    at_or_null(dgamma), at_or_null(dbeta), r, h,
-                                   adjoint.size() > 1 ? plan->f(adjoint[1]) : nullptr, adjoint.size() > 2 ? plan->f(adjoint[2]) : nullptr,
-                                   adjoint.size() > 3 ? plan->f(adjoint[3]) : nullptr, in_draw.token ? &in_draw : nullptr,
-                                   out_draw.token ? &out_draw : nullptr, at_or_null(dropped), at_or_null(pre_activation));
+                                   adjoint.size() > 1 ? plan->in(adjoint[1]) : k::In(), adjoint.size() > 2 ? plan->in(adjoint[2]) : k::In(),
+                                   adjoint.size() > 3 ? plan->in(adjoint[3]) : k::In(), in_draw.token ? &in_draw : nullptr,
+                                   out_draw.token ? &out_draw : nullptr, out_or_null(dropped), in_or_null(pre_activation));
         });
         return true;
     }
@@ -1534,7 +1602,7 @@ struct Scheduler {
     bool pitchable(uint32_t v) const {
         if (P->flags & MSX_PLAN_EXACT_MATMUL) return false;
         const msx::Type& t = node(v).ty;
-        if (t.rank() != 2 || t.i32 || t.shape[1] % 4 == 0 || t.shape[1] < 8) return false;
+        if (t.rank() != 2 || t.i32 || t.shape[1] % (mixed() ? 8 : 4) == 0 || t.shape[1] < 8) return false;
         for (const msx::Output& o : prog.outputs)
             if (pos(o.value) == v) return false;
         for (uint32_t u : users[v]) {
@@ -1553,8 +1621,9 @@ struct Scheduler {
     void set_pitch(uint32_t v) {
         const msx::Type& t = node(v).ty;
         Slot& s = P->slots[v];
-        s.pitch = static_cast<uint32_t>((t.shape[1] + 3) / 4 * 4);
-        s.bytes = t.shape[0] * s.pitch * 4;
+        const uint64_t unit = mixed() ? 8 : 4;  // rows start on 16-byte boundaries
+        s.pitch = static_cast<uint32_t>((t.shape[1] + unit - 1) / unit * unit);
+        s.bytes = t.shape[0] * s.pitch * (s.half ? 2 : 4);
     }
     uint32_t pitch_of(uint32_t p) const {
         const Slot& s = P->slots[p];
@@ -1591,14 +1660,12 @@ struct Scheduler {
         Product p = describe_product(at);
         handled[at] = 1;
         Slot& own = P->slots[at];
-        own.kind = Slot::Arena;
-        own.bytes = std::max<uint64_t>(node(at).ty.count() * 4, 4);
+        make_arena(own, node(at));
         if (p.result != at) {
             handled[p.result] = 1;
             own.kind = Slot::Dead;
             Slot& r = P->slots[p.result];
-            r.kind = Slot::Arena;
-            r.bytes = std::max<uint64_t>(node(p.result).ty.count() * 4, 4);
+            make_arena(r, node(p.result));
         }
         return p;
     }
@@ -1634,6 +1701,10 @@ struct Scheduler {
         }
         const Product first = group[0];
         const bool a_t_flip = first.flip_a, b_t_flip = first.flip_b;
+        if (mixed()) {
+            emit_matmul_bf16(nd, first, reads, m, n, kk);
+            return;
+        }
         if (P->flags & MSX_PLAN_EXACT_MATMUL) {
             const uint32_t a = first.a, b = first.b, at = first.result;
             const int bias = first.bias;
@@ -1684,6 +1755,106 @@ struct Scheduler {
         l.flop = 2 * m * n * kk * count;
     }
 
+    // Attention and its gradients of a mixed-precision plan: the batched products on the bf16
+    // kernel, probabilities kept as bf16 from the forward launch to the backward one, scores and
+    // their adjoints as an f32 scratch matrix that lives inside one launch group.
+    void schedule_attention_bf16(uint32_t at, k::AttentionShape shape, uint64_t pair_flop) {
+        const Node& nd = node(at);
+        msx_plan* plan = P;
+        const uint32_t q = pos(nd.operands[0]), kk = pos(nd.operands[1]), v = pos(nd.operands[2]), mask = pos(nd.operands[3]);
+        if (shape.k_len % 8 != 0 || shape.head_dim % 8 != 0) unsupported(nd, "a bf16 plan needs key counts and head widths that are multiples of 8");
+        for (uint32_t operand : {q, kk, v})
+            if (!P->half(operand)) unsupported(nd, "a bf16 plan's attention reads bf16 activations");
+        const uint64_t count = k::attention_tc_scratch_floats(shape);
+        auto half_scratch = [&](void) {
+            const uint32_t slot = scratch(count * 2);
+            P->slots[slot].half = true;
+            return slot;
+        };
+        if (nd.op == Op::Attention) {
+            const uint32_t probs = half_scratch(), scores = scratch(count * 4);
+            forward_probabilities[{q, kk, v, mask, static_cast<uint32_t>(nd.heads)}] = probs;
+            Launch& l = emit("attention_forward", nd, {q, kk, v, mask}, {at, probs, scores}, [=](cudaStream_t s) {
+                k::attention_bf16_forward(s, plan->ptr(q), plan->ptr(kk), plan->ptr(v), plan->f(mask), plan->ptr(at), plan->ptr(probs),
+                                          plan->f(scores), shape, plan->d_status);
+            });
+            l.flop = 2 * pair_flop;
+            return;
+        }
+        const uint32_t g = pos(nd.operands[4]);
+        if (!P->half(g)) unsupported(nd, "a bf16 plan's attention reads bf16 activations");
+        int dq = -1, dk = -1, dv = -1;
+        for (uint32_t u : users[g]) {
+            const Node& other = node(u);
+            if (handled[u] && u != at) continue;
+            if (other.op != Op::AttentionGradQ && other.op != Op::AttentionGradK && other.op != Op::AttentionGradV) continue;
+            if (other.operands != nd.operands || other.heads != nd.heads) continue;
+            int& target = other.op == Op::AttentionGradQ ? dq : other.op == Op::AttentionGradK ? dk : dv;
+            if (target < 0) target = static_cast<int>(u);
+        }
+        std::vector<uint32_t> reads = {q, kk, v, mask, g}, writes;
+        for (int t : {dq, dk, dv})
+            if (t >= 0) {
+                handled[static_cast<size_t>(t)] = 1;
+                make_arena(P->slots[static_cast<size_t>(t)], node(static_cast<uint32_t>(t)));
+                writes.push_back(static_cast<uint32_t>(t));
+            }
+        auto kept = forward_probabilities.find({q, kk, v, mask, static_cast<uint32_t>(nd.heads)});
+        const bool p_ready = kept != forward_probabilities.end();
+        const uint32_t probs = p_ready ? kept->second : half_scratch();
+        const uint32_t dscores = half_scratch(), scores = scratch(count * 4);
+        writes.push_back(dscores);
+        writes.push_back(scores);
+        if (p_ready) reads.push_back(probs);
+        else writes.push_back(probs);
+        auto or_null = [plan](int p) -> void* { return p >= 0 ? plan->ptr(static_cast<uint32_t>(p)) : nullptr; };
+        Launch& l = emit("attention_backward", nd, reads, writes, [=](cudaStream_t s) {
+            k::attention_bf16_backward(s, plan->ptr(q), plan->ptr(kk), plan->ptr(v), plan->f(mask), plan->ptr(g), or_null(dq), or_null(dk),
+                                       or_null(dv), plan->ptr(probs), plan->ptr(dscores), plan->f(scores), shape, plan->d_status, p_ready);
+        });
+        l.flop = pair_flop * (1 + (dv >= 0) + ((dq >= 0 || dk >= 0) ? 1 : 0) + (dq >= 0) + (dk >= 0));
+    }
+
+    // The product of a mixed-precision plan: bf16 operands in place (an activation, or the working
+    // copy of a parameter), the result in the storage type of its slot, a split k reduced by the
+    // launch or, for a weight gradient, left as f32 partial tiles for the finalize launch.
+    void emit_matmul_bf16(const Node& nd, const Product& p, const std::vector<uint32_t>& reads, uint64_t m, uint64_t n, uint64_t kk) {
+        msx_plan* plan = P;
+        for (uint32_t operand : {p.a, p.b}) {
+            uint32_t home = operand;
+            while (P->slots[home].kind == Slot::View) home = P->slots[home].index;
+            const Slot& slot = P->slots[home];
+            const bool ok = (slot.kind == Slot::Arena && slot.half) || (slot.kind == Slot::Param && node(home).ty.rank() == 2);
+            if (!ok) unsupported(nd, "a bf16 plan multiplies bf16 activations and matrix parameters; %" + std::to_string(node(home).id) + " is neither");
+        }
+        const k::MatmulBf16Plan tc = k::matmul_bf16_plan(m, n, kk);
+        const bool defer = tc.workspace_floats != 0 && p.bias < 0 && deferrable(p.result);
+        if (pitchable(p.result)) set_pitch(p.result);
+        std::vector<uint32_t> writes;
+        int ws = -1;
+        if (tc.workspace_floats) {
+            ws = static_cast<int>(scratch(tc.workspace_floats * 4));
+            writes.push_back(static_cast<uint32_t>(ws));
+        }
+        if (defer) deferred.push_back({static_cast<uint32_t>(ws), 0, tc.splits, m * n, p.result});
+        else writes.push_back(p.result);
+        const bool a_t = P->transposed(p.a) != p.flip_a, b_t = P->transposed(p.b) != p.flip_b;
+        const uint32_t a_pitch = pitch_of(p.a) ? pitch_of(p.a) : static_cast<uint32_t>(a_t ? m : kk);
+        const uint32_t b_pitch = pitch_of(p.b) ? pitch_of(p.b) : static_cast<uint32_t>(b_t ? kk : n);
+        const uint32_t c_pitch = P->slots[p.result].pitch;
+        const uint32_t a = p.a, b = p.b, result = p.result;
+        const int bias = p.bias;
+        Launch& l = emit("matmul", nd, reads, writes, [=](cudaStream_t s) {
+            const k::HalfMatrix A = {plan->h16(a), a_pitch, 0, 0, a_t};
+            const k::HalfMatrix B = {plan->h16(b), b_pitch, 0, 0, b_t};
+            const k::HalfResult C = {plan->ptr(result), plan->half(result), c_pitch, 0, 0};
+            if (!A.base || !B.base) throw StatusError(MSX_LAUNCH_FAILED, "a matmul operand of a bf16 plan has no bf16 storage");
+            k::matmul_bf16(s, A, B, C, m, n, kk, 1, 1, ws >= 0 ? plan->f(static_cast<uint32_t>(ws)) : nullptr,
+                           bias >= 0 ? plan->f(static_cast<uint32_t>(bias)) : nullptr, plan->d_status, defer);
+        });
+        l.flop = 2 * m * n * kk;
+    }
+
     std::map<std::array<uint32_t, 5>, uint32_t> forward_probabilities;  // (q, k, v, mask, heads) -> scratch slot
     std::map<std::pair<uint32_t, uint64_t>, uint32_t> orders;           // (ids, table rows) -> scratch slot of the sorted occurrences
 
@@ -1703,6 +1874,10 @@ struct Scheduler {
         if (shape.head_dim > 128) unsupported(nd, "a head wider than 128");
         const bool simt = (P->flags & MSX_PLAN_EXACT_MATMUL) != 0;
         const uint64_t pair_flop = 2ull * shape.batch * shape.q_len * shape.k_len * shape.heads * shape.head_dim;
+        if (mixed()) {
+            schedule_attention_bf16(at, shape, pair_flop);
+            return;
+        }
         if (nd.op == Op::Attention) {
             if (simt) {
                 Launch& l = emit("attention_forward", nd, {q, kk, v, mask}, {at}, [=](cudaStream_t s) {
@@ -1738,8 +1913,7 @@ struct Scheduler {
             if (t >= 0) {
                 handled[static_cast<size_t>(t)] = 1;
                 Slot& s = P->slots[static_cast<size_t>(t)];
-                s.kind = Slot::Arena;
-                s.bytes = node(static_cast<uint32_t>(t)).ty.count() * 4;
+                make_arena(s, node(static_cast<uint32_t>(t)));
             }
         std::vector<uint32_t> reads = {q, kk, v, mask, g};
         if (!simt) {
@@ -1959,6 +2133,23 @@ void allocate(msx_plan* P, const Scheduler& sched) {
                 P->param_bytes += bytes;
             }
         }
+        // Mixed precision: every matrix parameter gets the bf16 working copy the matmuls read
+        // (the owner's, for a plan that shares its parameters).
+        if (param_used[p] && (P->flags & MSX_PLAN_BF16) && prog.params[p].ty.rank() == 2) {
+            void* shared16 = nullptr;
+            if (P->shares && !P->owns_param[p]) {
+                int at = P->shares->program.param_index(prog.params[p].path);
+                if (at >= 0) shared16 = P->shares->params16[static_cast<size_t>(at)];
+            }
+            if (shared16) {
+                P->params16[p] = shared16;
+            } else {
+                cuda_ok(cudaMalloc(&P->params16[p], bytes / 2), "cudaMalloc(parameter working copy)");
+                P->owns_param16[p] = 1;
+                P->param_bytes += bytes / 2;
+                k::working_copy(P->stream, P->params[p], P->params16[p], prog.params[p].ty.count());
+            }
+        }
         if (moment_used[p]) {
             cuda_ok(cudaMalloc(&P->m[p], bytes), "cudaMalloc(moment)");
             cuda_ok(cudaMalloc(&P->v[p], bytes), "cudaMalloc(moment)");
@@ -2002,7 +2193,7 @@ void allocate(msx_plan* P, const Scheduler& sched) {
         std::vector<k::RowSumJob> jobs;
         uint32_t first_block = 0;
         for (const Scheduler::DeferredRows& d : sched.deferred_rows) {
-            jobs.push_back(k::row_sum_job(static_cast<const float*>(P->ptr(d.g)), static_cast<float*>(P->ptr(d.partial)), d.rows, d.width,
+            jobs.push_back(k::row_sum_job(P->in(d.g), static_cast<float*>(P->ptr(d.partial)), d.rows, d.width,
                                           d.ld, first_block));
             first_block += k::row_sum_job_blocks(d.rows, d.width);
         }
@@ -2034,6 +2225,7 @@ void allocate(msx_plan* P, const Scheduler& sched) {
             t.m = P->m[u.param];
             t.v = P->v[u.param];
             t.count = prog.params[u.param].ty.count();
+            t.p16 = P->params16[u.param];
             tensors.push_back(t);
         }
         size_t table_bytes = tensors.size() * sizeof(k::UpdateTensor);
@@ -2065,6 +2257,7 @@ void release(msx_plan* P) {
     cudaFree(P->arena);
     for (size_t p = 0; p < P->params.size(); ++p) {
         if (P->owns_param[p]) cudaFree(P->params[p]);
+        if (P->owns_param16[p]) cudaFree(P->params16[p]);
         cudaFree(P->m[p]);
         cudaFree(P->v[p]);
     }
@@ -2425,6 +2618,8 @@ int msx_plan_create(msx_device* device, const char* ir_text, uint64_t seed, uint
         P->device = device;
         P->seed = seed;
         P->flags = flags;
+        if ((flags & MSX_PLAN_BF16) && (flags & MSX_PLAN_EXACT_MATMUL))
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_plan_create: MSX_PLAN_BF16 and MSX_PLAN_EXACT_MATMUL exclude each other");
         P->shares = shares;
         try {
             P->program = msx::parse_program(ir_text);
@@ -2484,7 +2679,14 @@ static int transfer(msx_plan* plan, float* device_ptr, uint64_t expect, void* ho
 
 int msx_param_upload(msx_plan* plan, uint32_t index, const void* host, uint64_t bytes) {
     if (!plan || index >= plan->program.params.size()) return MSX_BAD_ARGUMENT;
-    return transfer(plan, plan->params[index], msx_plan_param_bytes(plan, index), const_cast<void*>(host), bytes, true, "msx_param_upload");
+    int rc = transfer(plan, plan->params[index], msx_plan_param_bytes(plan, index), const_cast<void*>(host), bytes, true, "msx_param_upload");
+    if (rc != MSX_OK || !plan->params16[index]) return rc;
+    // The bf16 working copy follows its f32 master.
+    return guarded(plan->device, [&]() -> int {
+        k::working_copy(plan->stream, plan->params[index], plan->params16[index], plan->program.params[index].ty.count());
+        cuda_ok(cudaStreamSynchronize(plan->stream), "cudaStreamSynchronize");
+        return MSX_OK;
+    });
 }
 int msx_param_download(msx_plan* plan, uint32_t index, void* host, uint64_t bytes) {
     if (!plan || index >= plan->program.params.size()) return MSX_BAD_ARGUMENT;
@@ -2773,8 +2975,10 @@ uint64_t msx_plan_describe(const msx_plan* plan, char* out, uint64_t capacity) {
     if (!plan) return 0;
     std::string text;
     auto name = [&](uint32_t slot) {
-        if (slot < plan->program.nodes.size()) return "%" + std::to_string(plan->program.nodes[slot].id);
-        return "scratch" + std::to_string(slot - plan->program.nodes.size());
+        // A value a mixed-precision plan stores as bf16 carries the suffix `h`.
+        const std::string suffix = plan->half(slot) ? "h" : "";
+        if (slot < plan->program.nodes.size()) return "%" + std::to_string(plan->program.nodes[slot].id) + suffix;
+        return "scratch" + std::to_string(slot - plan->program.nodes.size()) + suffix;
     };
     for (size_t l = 0; l < plan->launches.size(); ++l) {
         const Launch& launch = plan->launches[l];
@@ -2831,9 +3035,35 @@ int msx_op_matmul(const float* a, int a_transposed, const float* b, int b_transp
 
 uint64_t msx_op_matmul_workspace(uint64_t m, uint64_t n, uint64_t k) { return k::matmul_tc_plan(m, n, k).workspace_floats; }
 
+int msx_op_matmul_bf16(const void* a, int a_transposed, const void* b, int b_transposed, void* c, int c_is_bf16, uint64_t m, uint64_t n,
+                       uint64_t k, float* workspace, uint64_t workspace_floats, uint32_t* status, void* stream) {
+    if (!a || !b || !c || !status) return MSX_BAD_ARGUMENT;
+    return guarded(nullptr, [&]() -> int {
+        const uint64_t need = k::matmul_bf16_plan(m, n, k).workspace_floats;
+        if (need > workspace_floats || (need && !workspace))
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_op_matmul_bf16: the product needs " + std::to_string(need) + " workspace floats");
+        try {
+            k::HalfMatrix A = {a, static_cast<uint32_t>(a_transposed ? m : k), 0, 0, a_transposed != 0};
+            k::HalfMatrix B = {b, static_cast<uint32_t>(b_transposed ? k : n), 0, 0, b_transposed != 0};
+            k::HalfResult C = {c, c_is_bf16 != 0, static_cast<uint32_t>(n), 0, 0};
+            k::matmul_bf16(static_cast<cudaStream_t>(stream), A, B, C, m, n, k, 1, 1, workspace, nullptr, status);
+        } catch (const std::invalid_argument& e) {
+            throw StatusError(MSX_BAD_ARGUMENT, e.what());
+        }
+        return MSX_OK;
+    });
+}
+
+uint64_t msx_op_matmul_bf16_workspace(uint64_t m, uint64_t n, uint64_t k) { return k::matmul_bf16_plan(m, n, k).workspace_floats; }
+
 uint64_t msx_schedule_describe(const char* ir_text, char* out, uint64_t capacity) {
+    return msx_schedule_describe_with(ir_text, MSX_PLAN_DEFAULT, out, capacity);
+}
+
+uint64_t msx_schedule_describe_with(const char* ir_text, uint32_t flags, char* out, uint64_t capacity) {
     if (!ir_text) return 0;
     msx_plan* P = new msx_plan;
+    P->flags = flags;
     std::string text;
     int rc = guarded(nullptr, [&]() -> int {
         try {
