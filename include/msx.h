@@ -316,6 +316,16 @@ int msx_op_matmul_bf16(const void* a, int a_transposed, const void* b, int b_tra
                        uint64_t n, uint64_t k, float* workspace, uint64_t workspace_floats, uint32_t* status, void* stream);
 uint64_t msx_op_matmul_bf16_workspace(uint64_t m, uint64_t n, uint64_t k);
 
+/* The fused attention kernels of a mixed-precision plan on the caller's device buffers: q, k, v
+ * (and g, the adjoint of the result) are bf16 [batch * len, heads * head_dim], `mask` is f32
+ * [batch, k_len] of 0 / 1. Writes `out` (bf16) and `stats` (2 floats per (row, head): the softmax
+ * maximum and sum); with `g` not null also dq, dk, dv (bf16, each may be null). The op is the
+ * reference's Attention / AttentionGradQ/K/V (cpu/interpreter.rs:1035-1119); the score matrix
+ * stays on the SM. Heads of up to 64 columns (a multiple of 8), up to 512 keys and queries. */
+int msx_op_attention_bf16(const void* q, const void* k, const void* v, const float* mask, const void* g, void* out, void* dq, void* dk,
+                          void* dv, float* stats, uint32_t batch, uint32_t q_len, uint32_t k_len, uint32_t heads, uint32_t head_dim,
+                          uint32_t* status, void* stream);
+
 /* Column sums without any allocation: out[c] = sum over rows of g[r, c] for a row-major
  * [rows, columns] device matrix, the `SumRows` of a bias gradient. This function has no
  * counterpart in the reference. It exists for hosts that cannot allocate device memory once they

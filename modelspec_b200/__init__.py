@@ -99,6 +99,7 @@ SIGNATURES = {
     "msx_op_matmul_workspace": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
     "msx_op_matmul_bf16": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, _P, C.c_uint64, _P, _P]),
     "msx_op_matmul_bf16_workspace": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
+    "msx_op_attention_bf16": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _P, _P]),
     "msx_sum_rows_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, _P, _P]),
     "msx_static_last_error": (C.c_char_p, []),
     "msx_compile": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_uint64, C.c_char_p, C.c_uint64]),

@@ -37,6 +37,17 @@ __device__ __forceinline__ float load1(const float* p) { return __ldg(p); }
 __device__ __forceinline__ float load1(const bf16* p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void store1(float* p, float v) { *p = v; }
 __device__ __forceinline__ void store1(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+// Two consecutive elements (the address a multiple of their size).
+__device__ __forceinline__ float2 load2(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
+__device__ __forceinline__ float2 load2(const bf16* p) {
+    const uint32_t raw = __ldg(reinterpret_cast<const uint32_t*>(p));
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
+}
+__device__ __forceinline__ void store2(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+__device__ __forceinline__ void store2(bf16* p, float2 v) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<const uint32_t*>(&pair);
+}
 __device__ __forceinline__ float4 load4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 __device__ __forceinline__ float4 load4(const bf16* p) {
     const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
@@ -51,6 +62,28 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
     raw.x = *reinterpret_cast<const uint32_t*>(&lo);
     raw.y = *reinterpret_cast<const uint32_t*>(&hi);
     *reinterpret_cast<uint2*>(p) = raw;
+}
+// Eight consecutive bf16 elements (16 bytes; the address a multiple of 16).
+struct float8 {
+    float4 lo, hi;
+};
+__device__ __forceinline__ float8 load8(const bf16* p) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.z));
+    const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.w));
+    return {make_float4(a.x, a.y, b.x, b.y), make_float4(c.x, c.y, d.x, d.y)};
+}
+__device__ __forceinline__ void store8(bf16* p, const float8& v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.lo.x, v.lo.y), b = __floats2bfloat162_rn(v.lo.z, v.lo.w);
+    const __nv_bfloat162 c = __floats2bfloat162_rn(v.hi.x, v.hi.y), d = __floats2bfloat162_rn(v.hi.z, v.hi.w);
+    uint4 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&a);
+    raw.y = *reinterpret_cast<const uint32_t*>(&b);
+    raw.z = *reinterpret_cast<const uint32_t*>(&c);
+    raw.w = *reinterpret_cast<const uint32_t*>(&d);
+    *reinterpret_cast<uint4*>(p) = raw;
 }
 // `v` as an array of that element type would hold it.
 __device__ __forceinline__ float stored_as(float v, const float*) { return v; }

@@ -364,6 +364,18 @@ void attention_bf16_backward(cudaStream_t s, const void* q, const void* k, const
                              void* dk, void* dv, void* p, void* ds, float* scores, AttentionShape shape, uint32_t* status,
                              bool p_ready = false);
 
+// Fused attention for mixed-precision plans (attention_fused.cu): the forward as one kernel that
+// never stores the scores (it writes O and, per (row, head), the softmax maximum and sum:
+// attention_fused_stats_floats(shape) floats), the three gradients as one kernel that reads those
+// statistics and O. Heads of up to 64 columns (a multiple of 8), up to 512 keys and queries a
+// sequence; attention_fused_supported says whether a shape qualifies. dq, dk, dv may each be null.
+bool attention_fused_supported(AttentionShape shape);
+uint64_t attention_fused_stats_floats(AttentionShape shape);
+void attention_fused_forward(cudaStream_t s, const void* q, const void* k, const void* v, const float* mask, void* out, float* stats,
+                             AttentionShape shape, uint32_t* status);
+void attention_fused_backward(cudaStream_t s, const void* q, const void* k, const void* v, const float* mask, const void* g, const void* o,
+                              const float* stats, void* dq, void* dk, void* dv, AttentionShape shape, uint32_t* status);
+
 // ---- optimizer (optimizer.cu) -----------------------------------------------------------------
 struct UpdateTensor {
     float* p;

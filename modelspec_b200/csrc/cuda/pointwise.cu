@@ -72,6 +72,20 @@ template <class T>
 __global__ void unary_kernel(Unary op, const T* __restrict__ a, T* __restrict__ out, uint64_t n) {
     uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if constexpr (sizeof(T) == 2) {
+        // bf16: 16 bytes (eight elements) per thread and turn.
+        if (reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0) {
+            const uint64_t n8 = n / 8;
+            for (uint64_t j = i; j < n8; j += stride) {
+                float8 v = load8(a + 8 * j);
+                v.lo.x = apply(op, v.lo.x); v.lo.y = apply(op, v.lo.y); v.lo.z = apply(op, v.lo.z); v.lo.w = apply(op, v.lo.w);
+                v.hi.x = apply(op, v.hi.x); v.hi.y = apply(op, v.hi.y); v.hi.z = apply(op, v.hi.z); v.hi.w = apply(op, v.hi.w);
+                store8(out + 8 * j, v);
+            }
+            for (uint64_t j = n8 * 8 + i; j < n; j += stride) store1(out + j, apply(op, load1(a + j)));
+            return;
+        }
+    }
     bool vec = reinterpret_cast<uintptr_t>(out) % (4 * sizeof(T)) == 0 && reinterpret_cast<uintptr_t>(a) % (4 * sizeof(T)) == 0;
     uint64_t n4 = vec ? n / 4 : 0;
     for (uint64_t j = i; j < n4; j += stride) {
@@ -89,9 +103,26 @@ template <bool GELU, class T>
 __global__ void act_grad_kernel(const T* __restrict__ a, const T* __restrict__ g,
                                 T* __restrict__ out, uint64_t n) {
     uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    auto one = [](float x, float gg) { return GELU ? gelu_grad_value(x, gg) : (x > 0.0f ? gg : 0.0f); };
+    if constexpr (sizeof(T) == 2) {
+        // bf16: 16 bytes (eight elements) of each array per thread and turn.
+        if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(g)) % 16 == 0) {
+            const uint64_t n8 = n / 8;
+            for (uint64_t j = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n8; j += stride) {
+                const float8 x = load8(a + 8 * j), gg = load8(g + 8 * j);
+                float8 r;
+                r.lo = make_float4(one(x.lo.x, gg.lo.x), one(x.lo.y, gg.lo.y), one(x.lo.z, gg.lo.z), one(x.lo.w, gg.lo.w));
+                r.hi = make_float4(one(x.hi.x, gg.hi.x), one(x.hi.y, gg.hi.y), one(x.hi.z, gg.hi.z), one(x.hi.w, gg.hi.w));
+                store8(out + 8 * j, r);
+            }
+            for (uint64_t j = n8 * 8 + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n; j += stride)
+                store1(out + j, one(load1(a + j), load1(g + j)));
+            return;
+        }
+    }
     for (uint64_t j = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n; j += stride) {
         float x = load1(a + j), gg = load1(g + j);
-        store1(out + j, GELU ? gelu_grad_value(x, gg) : (x > 0.0f ? gg : 0.0f));
+        store1(out + j, one(x, gg));
     }
 }
 
@@ -156,7 +187,7 @@ void binary(cudaStream_t s, Binary op, const float* a, bool a_scalar, const floa
 void unary(cudaStream_t s, Unary op, In a, Out out, uint64_t n) {
     if (n == 0) return;
     if (all_half({a.half, out.half}, "unary"))
-        unary_kernel<<<blocks_for((n + 3) / 4), kThreads, 0, s>>>(op, static_cast<const bf16*>(a.p), static_cast<bf16*>(out.p), n);
+        unary_kernel<<<blocks_for((n + 7) / 8), kThreads, 0, s>>>(op, static_cast<const bf16*>(a.p), static_cast<bf16*>(out.p), n);
     else
         unary_kernel<<<blocks_for((n + 3) / 4), kThreads, 0, s>>>(op, a.f32(), out.f32(), n);
     check_launch("unary");
@@ -171,7 +202,7 @@ void relu_grad(cudaStream_t s, const float* a, const float* g, float* out, uint6
 void gelu_grad(cudaStream_t s, In a, In g, Out out, uint64_t n) {
     if (n == 0) return;
     if (all_half({a.half, g.half, out.half}, "gelu_grad"))
-        act_grad_kernel<true, bf16><<<blocks_for(n), kThreads, 0, s>>>(static_cast<const bf16*>(a.p), static_cast<const bf16*>(g.p),
+        act_grad_kernel<true, bf16><<<blocks_for((n + 7) / 8), kThreads, 0, s>>>(static_cast<const bf16*>(a.p), static_cast<const bf16*>(g.p),
                                                                        static_cast<bf16*>(out.p), n);
     else
         act_grad_kernel<true, float><<<blocks_for(n), kThreads, 0, s>>>(a.f32(), g.f32(), out.f32(), n);

@@ -541,13 +541,50 @@ cross_entropy_fused_split_kernel(const float* __restrict__ logits, const int32_t
         }
 }
 
+// How a warp holds a row in registers: lane l keeps ITEMS values, V consecutive columns per turn of
+// 32 V columns. V = 1 (one 4-byte load per value; the f32 layout) or V = 2 (a bf16 pair per 4-byte
+// load, so that a warp's load still covers 128 contiguous bytes).
+template <int V> __device__ __forceinline__ uint32_t column_of(int i, uint32_t lane) {
+    return static_cast<uint32_t>(i / V) * (32u * V) + lane * V + static_cast<uint32_t>(i % V);
+}
+// The row's values from clamped columns (what a column past h reads is discarded by the caller):
+// unconditional, so that every load of a row is in flight before the first use.
+template <int ITEMS, int V, class T>
+__device__ __forceinline__ void load_row(const T* __restrict__ row, uint32_t lane, uint32_t h, float (&to)[ITEMS]) {
+    if constexpr (V == 1) {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) to[i] = load1(row + min(i * 32 + lane, h - 1));
+    } else {
+        static_assert(ITEMS % 2 == 0, "pairs");
+#pragma unroll
+        for (int j = 0; j < ITEMS / 2; ++j) {
+            const float2 f = load2(row + min(j * 64 + lane * 2, h - 2));
+            to[2 * j] = f.x;
+            to[2 * j + 1] = f.y;
+        }
+    }
+}
+template <int ITEMS, int V, class T>
+__device__ __forceinline__ void store_row(T* __restrict__ row, uint32_t lane, uint32_t h, const float (&from)[ITEMS]) {
+    if constexpr (V == 1) {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i)
+            if (i * 32 + lane < h) store1(row + i * 32 + lane, from[i]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < ITEMS / 2; ++j)
+            if (j * 64 + lane * 2 < h) store2(row + j * 64 + lane * 2, make_float2(from[2 * j], from[2 * j + 1]));  // h is even
+    }
+}
+
 // dropout(x) + residual, then layer_norm of the sum, one warp per row with the row in registers:
 // the three launches of a transformer sublayer's tail as one. Every element goes through the same
 // rounded operations as the separate kernels (the Philox draw of element index_base + r h + c, the
 // scaled or zeroed value, one addition, the layer norm of the stored sum). Each part is optional:
 // without a draw on x the sum is x + residual; without gamma the launch ends with the sum; with a
-// draw on the result, dropout of the layer norm is written to out_dropped (and out may be null).
-template <int ITEMS, class T>
+// draw on the result, dropout of the layer norm is written to out_dropped (and out may be null);
+// sum_out may be null when only the layer norm is wanted.
+template <int ITEMS, int V, class T>
 __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
     const T* __restrict__ x, const T* __restrict__ residual, DropoutDraw x_draw, const float* __restrict__ gamma,
     const float* __restrict__ beta, T* __restrict__ sum_out, T* __restrict__ out, DropoutDraw out_draw,
@@ -556,15 +593,10 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
     const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (r >= rows) return;
     const uint64_t base = static_cast<uint64_t>(r) * h;
-    // The loads first, unconditional and from a clamped column, so that all are in flight before
-    // the Philox rounds of the first element start.
+    // The loads first, so that all are in flight before the Philox rounds of the first element start.
     float v[ITEMS], xs[ITEMS];
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) xs[i] = load1(x + base + min(i * 32 + lane, h - 1));
-    if (residual != nullptr) {
-#pragma unroll
-        for (int i = 0; i < ITEMS; ++i) v[i] = load1(residual + base + min(i * 32 + lane, h - 1));
-    }
+    load_row<ITEMS, V>(x + base, lane, h, xs);
+    if (residual != nullptr) load_row<ITEMS, V>(residual + base, lane, h, v);
     // gelu(x) in the place of the sum (the head's transform: dense, gelu, layer norm).
     if (gelu_first) {
 #pragma unroll
@@ -574,30 +606,30 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
         const uint32_t id_lo = static_cast<uint32_t>(x_draw.token[0]), id_hi = static_cast<uint32_t>(x_draw.token[1]);
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
-            const uint32_t w0 = philox_word0(static_cast<uint32_t>(x_draw.index_base + base + i * 32 + lane), 4u, id_lo, id_hi,
+            const uint32_t w0 = philox_word0(static_cast<uint32_t>(x_draw.index_base + base + column_of<V>(i, lane)), 4u, id_lo, id_hi,
                                              static_cast<uint32_t>(x_draw.seed), static_cast<uint32_t>(x_draw.seed >> 32));
             xs[i] = w0 >= x_draw.threshold ? xs[i] * x_draw.scale : 0.0f;
         }
     }
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
-        const uint32_t c = i * 32 + lane;
+        const uint32_t c = column_of<V>(i, lane);
         v[i] = c < h ? (residual != nullptr ? v[i] + xs[i] : xs[i]) : 0.0f;
         // What is stored is what the layer norm below reads: the sum as its storage type holds it.
         v[i] = stored_as(v[i], static_cast<const T*>(nullptr));
-        if (c < h && sum_out != nullptr) store1(sum_out + base + c, v[i]);
     }
+    if (sum_out != nullptr) store_row<ITEMS, V>(sum_out + base, lane, h, v);
     if (gamma == nullptr) return;
     const float width = static_cast<float>(h);
     float sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i)
-        if (i * 32 + lane < h) sum += v[i];
+        if (column_of<V>(i, lane) < h) sum += v[i];
     const float mean = warp_sum(sum) / width;
     float q = 0.0f;
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i)
-        if (i * 32 + lane < h) {
+        if (column_of<V>(i, lane) < h) {
             float d = v[i] - mean;
             q = fmaf(d, d, q);
         }
@@ -607,18 +639,22 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
         id_lo = static_cast<uint32_t>(out_draw.token[0]);
         id_hi = static_cast<uint32_t>(out_draw.token[1]);
     }
+    float dropped[ITEMS];
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
-        const uint32_t c = i * 32 + lane;
-        if (c >= h) continue;
-        const float y = (v[i] - mean) * rstd * gamma[c] + beta[c];
-        if (out != nullptr) store1(out + base + c, y);
-        if (out_dropped != nullptr) {
+        const uint32_t c = column_of<V>(i, lane);
+        const uint32_t cc = min(c, h - 1);
+        const float y = (v[i] - mean) * rstd * gamma[cc] + beta[cc];
+        v[i] = y;
+        dropped[i] = 0.0f;
+        if (out_dropped != nullptr && c < h) {
             const uint32_t w0 = philox_word0(static_cast<uint32_t>(out_draw.index_base + base + c), 4u, id_lo, id_hi,
                                              static_cast<uint32_t>(out_draw.seed), static_cast<uint32_t>(out_draw.seed >> 32));
-            store1(out_dropped + base + c, w0 >= out_draw.threshold ? y * out_draw.scale : 0.0f);
+            dropped[i] = w0 >= out_draw.threshold ? y * out_draw.scale : 0.0f;
         }
     }
+    if (out != nullptr) store_row<ITEMS, V>(out + base, lane, h, v);
+    if (out_dropped != nullptr) store_row<ITEMS, V>(out_dropped + base, lane, h, dropped);
 }
 
 // layer_norm_grad_x, layer_norm_grad_gamma and the beta gradient in one launch. A block takes a
@@ -628,7 +664,7 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
 // chunks w, w + 8, ... in ascending order and the eight sums are added in ascending w. Every
 // output is a fixed expression of the inputs: deterministic, tolerance class against a
 // sequential column sum. dx (with gamma), dgamma and dbeta may each be null.
-template <int ITEMS, class T>
+template <int ITEMS, int V, class T>
 __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
     const T* __restrict__ x, const float* __restrict__ gamma, const T* __restrict__ g, const T* __restrict__ g1,
     const T* __restrict__ g2, const T* __restrict__ g3, T* __restrict__ dx,
@@ -647,7 +683,7 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
     for (int i = 0; i < ITEMS; ++i) {
         acc_g[i] = 0.0f;
         acc_b[i] = 0.0f;
-        uint32_t c = i * 32 + lane;
+        uint32_t c = column_of<V>(i, lane);
         gam[i] = (want_dx && c < h) ? gamma[c] : 0.0f;
     }
     for (uint32_t r = r0 + warp; r < r1; r += 8) {
@@ -656,16 +692,13 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
         // under a condition of its own would wait for the one before it.
         const uint64_t row_at = static_cast<uint64_t>(r) * h;
         float xv[ITEMS], gv[ITEMS];
-#pragma unroll
-        for (int i = 0; i < ITEMS; ++i) xv[i] = load1(x + row_at + min(i * 32 + lane, h - 1));
-#pragma unroll
-        for (int i = 0; i < ITEMS; ++i) gv[i] = load1(g + row_at + min(i * 32 + lane, h - 1));
+        load_row<ITEMS, V>(x + row_at, lane, h, xv);
+        load_row<ITEMS, V>(g + row_at, lane, h, gv);
         // The adjoint as a sum the program spells as a chain of Adds: ((g + g1) + g2) + g3.
         for (const T* more : {g1, g2, g3}) {
             if (more == nullptr) continue;
             float t[ITEMS];
-#pragma unroll
-            for (int i = 0; i < ITEMS; ++i) t[i] = load1(more + row_at + min(i * 32 + lane, h - 1));
+            load_row<ITEMS, V>(more + row_at, lane, h, t);
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) gv[i] = gv[i] + t[i];
         }
@@ -675,26 +708,26 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
             const uint32_t id_lo = static_cast<uint32_t>(adjoint_draw.token[0]), id_hi = static_cast<uint32_t>(adjoint_draw.token[1]);
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
-                const uint32_t w0 = philox_word0(static_cast<uint32_t>(adjoint_draw.index_base + row_at + i * 32 + lane), 4u, id_lo, id_hi,
+                const uint32_t w0 = philox_word0(static_cast<uint32_t>(adjoint_draw.index_base + row_at + column_of<V>(i, lane)), 4u, id_lo, id_hi,
                                                  static_cast<uint32_t>(adjoint_draw.seed), static_cast<uint32_t>(adjoint_draw.seed >> 32));
                 gv[i] = w0 >= adjoint_draw.threshold ? gv[i] * adjoint_draw.scale : 0.0f;
             }
         }
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i)
-            if (i * 32 + lane >= h) {
+            if (column_of<V>(i, lane) >= h) {
                 xv[i] = 0.0f;
                 gv[i] = 0.0f;
             }
         float sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i)
-            if (i * 32 + lane < h) sum += xv[i];
+            if (column_of<V>(i, lane) < h) sum += xv[i];
         const float mean = warp_sum(sum) / width;
         float q = 0.0f;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i)
-            if (i * 32 + lane < h) {
+            if (column_of<V>(i, lane) < h) {
                 float d = xv[i] - mean;
                 q = fmaf(d, d, q);
             }
@@ -702,7 +735,7 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
         float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i)
-            if (i * 32 + lane < h) {
+            if (column_of<V>(i, lane) < h) {
                 float xhat = (xv[i] - mean) * rstd;
                 acc_g[i] = fmaf(gv[i], xhat, acc_g[i]);
                 acc_b[i] += gv[i];
@@ -714,31 +747,30 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
             const float mean_gx = warp_sum(s1) / width, mean_gx_xhat = warp_sum(s2) / width;
             // The pre-activations of a gelu_grad on dx: loaded together, before the first is used.
             float pre[ITEMS];
-            if (pre_activation != nullptr) {
-#pragma unroll
-                for (int i = 0; i < ITEMS; ++i) pre[i] = load1(pre_activation + row_at + min(i * 32 + lane, h - 1));
-            }
+            if (pre_activation != nullptr) load_row<ITEMS, V>(pre_activation + row_at, lane, h, pre);
+            float second[ITEMS];
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
-                uint32_t c = i * 32 + lane;
-                if (c < h) {
-                    float gx = gv[i] * gam[i];
-                    float xhat = (xv[i] - mean) * rstd;
-                    const float value = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
-                    if (dx != nullptr) store1(dx + row_at + c, value);
-                    // A function of dx for the reader that wants that: gelu_grad (the dense layer
-                    // before a gelu and this layer norm), or dropout_grad (the projection before
-                    // this sublayer's dropout).
-                    if (pre_activation != nullptr) {
-                        store1(dx_dropped + row_at + c, gelu_grad_value(pre[i], value));
-                    } else if (dx_dropped != nullptr) {
-                        const uint32_t w0 = philox_word0(static_cast<uint32_t>(dx_draw.index_base + row_at + c), 4u,
-                                                         static_cast<uint32_t>(dx_draw.token[0]), static_cast<uint32_t>(dx_draw.token[1]),
-                                                         static_cast<uint32_t>(dx_draw.seed), static_cast<uint32_t>(dx_draw.seed >> 32));
-                        store1(dx_dropped + row_at + c, w0 >= dx_draw.threshold ? value * dx_draw.scale : 0.0f);
-                    }
+                const uint32_t c = column_of<V>(i, lane);
+                float gx = gv[i] * gam[i];
+                float xhat = (xv[i] - mean) * rstd;
+                const float value = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
+                xv[i] = value;  // the dx row, in the registers of the x row
+                second[i] = 0.0f;
+                // A function of dx for the reader that wants that: gelu_grad (the dense layer
+                // before a gelu and this layer norm), or dropout_grad (the projection before
+                // this sublayer's dropout).
+                if (pre_activation != nullptr) {
+                    second[i] = gelu_grad_value(pre[i], value);
+                } else if (dx_dropped != nullptr && c < h) {
+                    const uint32_t w0 = philox_word0(static_cast<uint32_t>(dx_draw.index_base + row_at + c), 4u,
+                                                     static_cast<uint32_t>(dx_draw.token[0]), static_cast<uint32_t>(dx_draw.token[1]),
+                                                     static_cast<uint32_t>(dx_draw.seed), static_cast<uint32_t>(dx_draw.seed >> 32));
+                    second[i] = w0 >= dx_draw.threshold ? value * dx_draw.scale : 0.0f;
                 }
             }
+            if (dx != nullptr) store_row<ITEMS, V>(dx + row_at, lane, h, xv);
+            if (dx_dropped != nullptr) store_row<ITEMS, V>(dx_dropped + row_at, lane, h, second);
         }
     }
     if (want == 0) return;
@@ -752,7 +784,9 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
         for (int i = 0; i < ITEMS; ++i) buf[(warp * ITEMS + i) * 32 + lane] = pass == 0 ? acc_g[i] : acc_b[i];
         __syncthreads();
         for (uint32_t c = threadIdx.x; c < h; c += 256) {
-            uint32_t i = c >> 5, l = c & 31;
+            // Column c is value i of lane l (the inverse of column_of).
+            const uint32_t turn = c / (32u * V), within = c % (32u * V);
+            const uint32_t i = turn * V + within % V, l = within / V;
             float total = buf[i * 32 + l];
 #pragma unroll
             for (int w = 1; w < 8; ++w) total += buf[(w * ITEMS + i) * 32 + l];
@@ -875,7 +909,11 @@ void launch_add_layer_norm(cudaStream_t s, const T* x, const T* residual, const 
                            T* sum_out, T* out, const DropoutDraw& second, T* out_dropped, uint64_t rows, uint64_t h, bool gelu_first) {
     const uint32_t items = static_cast<uint32_t>((h + 31) / 32), blocks = static_cast<uint32_t>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
-#define MSX_DROPOUT_LN(N) dropout_add_layer_norm_kernel<N><<<blocks, 256, 0, s>>>(x, residual, first, gamma, beta, sum_out, out, second, out_dropped, r, hh, gelu_first)
+    // bf16 rows of even width are held as pairs (4-byte loads); everything else one value per load.
+    constexpr int PAIR = sizeof(T) == 2 ? 2 : 1;
+    const bool pairs = PAIR == 2 && h % 2 == 0 && items >= 2;
+#define MSX_DROPOUT_LN(N) do { if (pairs) dropout_add_layer_norm_kernel<N, (N % 2 == 0 ? PAIR : 1)><<<blocks, 256, 0, s>>>(x, residual, first, gamma, beta, sum_out, out, second, out_dropped, r, hh, gelu_first); \
+        else dropout_add_layer_norm_kernel<N, 1><<<blocks, 256, 0, s>>>(x, residual, first, gamma, beta, sum_out, out, second, out_dropped, r, hh, gelu_first); } while (0)
     if (items <= 1) MSX_DROPOUT_LN(1);
     else if (items <= 2) MSX_DROPOUT_LN(2);
     else if (items <= 4) MSX_DROPOUT_LN(4);
@@ -935,7 +973,10 @@ void launch_layer_norm_backward(cudaStream_t s, const T* x, const float* gamma, 
     uint32_t items = static_cast<uint32_t>((h + 31) / 32);
     uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);
     uint32_t want = (dgamma ? 1u : 0u) | (dbeta ? 2u : 0u);
-#define MSX_LN_BACKWARD(N) layer_norm_backward_kernel<N><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped, pre_activation)
+    constexpr int PAIR = sizeof(T) == 2 ? 2 : 1;
+    const bool pairs = PAIR == 2 && h % 2 == 0 && items >= 2;
+#define MSX_LN_BACKWARD(N) do { if (pairs) layer_norm_backward_kernel<N, (N % 2 == 0 ? PAIR : 1)><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped, pre_activation); \
+        else layer_norm_backward_kernel<N, 1><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped, pre_activation); } while (0)
     if (items <= 1) MSX_LN_BACKWARD(1);
     else if (items <= 2) MSX_LN_BACKWARD(2);
     else if (items <= 4) MSX_LN_BACKWARD(4);

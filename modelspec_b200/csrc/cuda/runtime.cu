@@ -92,7 +92,7 @@ static NcclApi g_nccl;
 // A contiguous run of gradient bytes that is summed across ranks by one all-reduce, issued on
 // the side stream as soon as the launch that writes its last gradient has been enqueued.
 #ifndef MSX_DEFAULT_FUSIONS
-#define MSX_DEFAULT_FUSIONS 31u
+#define MSX_DEFAULT_FUSIONS 63u
 #endif
 
 struct Bucket {
@@ -259,7 +259,8 @@ void close_peer_reduce(msx_plan* P);
 // Tuning switch: MSX_FUSE is a bit mask of optional fusions (default: all). 1 sublayer tails
 // (dropout + residual + layer norm), 2 adjoint sums inside layer-norm backward, 4 weight-gradient
 // matmuls as jobs of one launch, 8 heavy launches with late readers on a side stream, 16
-// dropout_grad inside the layer-norm backward that makes or reads its operand.
+// dropout_grad inside the layer-norm backward that makes or reads its operand, 32 the fused
+// attention kernels of a mixed-precision plan (off: batched products with row kernels between).
 inline uint32_t fusion_mask() {
     static const uint32_t mask = [] {
         const char* text = std::getenv("MSX_FUSE");
@@ -1765,6 +1766,48 @@ struct Scheduler {
         if (shape.k_len % 8 != 0 || shape.head_dim % 8 != 0) unsupported(nd, "a bf16 plan needs key counts and head widths that are multiples of 8");
         for (uint32_t operand : {q, kk, v})
             if (!P->half(operand)) unsupported(nd, "a bf16 plan's attention reads bf16 activations");
+        // One kernel forward (O and the softmax statistics), one kernel for the three gradients,
+        // when the shape fits them and the forward of the same attention is in the program.
+        const std::array<uint32_t, 5> key = {q, kk, v, mask, static_cast<uint32_t>(nd.heads)};
+        const bool fused = (fusion_mask() & 32u) && k::attention_fused_supported(shape);
+        if (fused && nd.op == Op::Attention) {
+            const uint32_t stats = scratch(k::attention_fused_stats_floats(shape) * 4);
+            fused_forward[key] = {stats, at};
+            Launch& l = emit("attention_forward", nd, {q, kk, v, mask}, {at, stats}, [=](cudaStream_t s) {
+                k::attention_fused_forward(s, plan->ptr(q), plan->ptr(kk), plan->ptr(v), plan->f(mask), plan->ptr(at), plan->f(stats), shape,
+                                           plan->d_status);
+            });
+            l.flop = 2 * pair_flop;
+            return;
+        }
+        if (fused && nd.op != Op::Attention && fused_forward.count(key)) {
+            const uint32_t g = pos(nd.operands[4]);
+            if (!P->half(g)) unsupported(nd, "a bf16 plan's attention reads bf16 activations");
+            const uint32_t stats = fused_forward[key].first, o = fused_forward[key].second;
+            int dq = -1, dk = -1, dv = -1;
+            for (uint32_t u : users[g]) {
+                const Node& other = node(u);
+                if (handled[u] && u != at) continue;
+                if (other.op != Op::AttentionGradQ && other.op != Op::AttentionGradK && other.op != Op::AttentionGradV) continue;
+                if (other.operands != nd.operands || other.heads != nd.heads) continue;
+                int& target = other.op == Op::AttentionGradQ ? dq : other.op == Op::AttentionGradK ? dk : dv;
+                if (target < 0) target = static_cast<int>(u);
+            }
+            std::vector<uint32_t> writes;
+            for (int t : {dq, dk, dv})
+                if (t >= 0) {
+                    handled[static_cast<size_t>(t)] = 1;
+                    make_arena(P->slots[static_cast<size_t>(t)], node(static_cast<uint32_t>(t)));
+                    writes.push_back(static_cast<uint32_t>(t));
+                }
+            auto or_null = [plan](int p) -> void* { return p >= 0 ? plan->ptr(static_cast<uint32_t>(p)) : nullptr; };
+            Launch& l = emit("attention_backward", nd, {q, kk, v, mask, g, stats, o}, writes, [=](cudaStream_t s) {
+                k::attention_fused_backward(s, plan->ptr(q), plan->ptr(kk), plan->ptr(v), plan->f(mask), plan->ptr(g), plan->ptr(o),
+                                            plan->f(stats), or_null(dq), or_null(dk), or_null(dv), shape, plan->d_status);
+            });
+            l.flop = pair_flop * 5;
+            return;
+        }
         const uint64_t count = k::attention_tc_scratch_floats(shape);
         auto half_scratch = [&](void) {
             const uint32_t slot = scratch(count * 2);
@@ -1856,6 +1899,7 @@ struct Scheduler {
     }
 
     std::map<std::array<uint32_t, 5>, uint32_t> forward_probabilities;  // (q, k, v, mask, heads) -> scratch slot
+    std::map<std::array<uint32_t, 5>, std::pair<uint32_t, uint32_t>> fused_forward;  // -> (statistics scratch, the forward's output)
     std::map<std::pair<uint32_t, uint64_t>, uint32_t> orders;           // (ids, table rows) -> scratch slot of the sorted occurrences
 
     void schedule_attention(uint32_t at) {
@@ -3055,6 +3099,25 @@ int msx_op_matmul_bf16(const void* a, int a_transposed, const void* b, int b_tra
 }
 
 uint64_t msx_op_matmul_bf16_workspace(uint64_t m, uint64_t n, uint64_t k) { return k::matmul_bf16_plan(m, n, k).workspace_floats; }
+
+int msx_op_attention_bf16(const void* q, const void* k, const void* v, const float* mask, const void* g, void* out, void* dq, void* dk,
+                          void* dv, float* stats, uint32_t batch, uint32_t q_len, uint32_t k_len, uint32_t heads, uint32_t head_dim,
+                          uint32_t* status, void* stream) {
+    if (!q || !k || !v || !mask || !out || !stats || !status) return MSX_BAD_ARGUMENT;
+    return guarded(nullptr, [&]() -> int {
+        k::AttentionShape shape = {batch, q_len, k_len, heads, head_dim};
+        if (!k::attention_fused_supported(shape))
+            throw StatusError(MSX_UNSUPPORTED, "msx_op_attention_bf16: heads of up to 64 columns (a multiple of 8), up to 512 keys and queries");
+        try {
+            cudaStream_t s = static_cast<cudaStream_t>(stream);
+            k::attention_fused_forward(s, q, k, v, mask, out, stats, shape, status);
+            if (g) k::attention_fused_backward(s, q, k, v, mask, g, out, stats, dq, dk, dv, shape, status);
+        } catch (const std::invalid_argument& e) {
+            throw StatusError(MSX_BAD_ARGUMENT, e.what());
+        }
+        return MSX_OK;
+    });
+}
 
 uint64_t msx_schedule_describe(const char* ir_text, char* out, uint64_t capacity) {
     return msx_schedule_describe_with(ir_text, MSX_PLAN_DEFAULT, out, capacity);

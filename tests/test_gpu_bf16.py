@@ -146,3 +146,54 @@ def test_bf16_plan_refuses_what_it_has_no_kernel_for(device):
     with pytest.raises(M.MsxError) as err:
         M.Plan(device, p.text(), flags=M.PLAN_BF16 | M.PLAN_EXACT_MATMUL)
     assert err.value.status == M.BAD_ARGUMENT
+
+
+@pytest.mark.parametrize("batch,seq,heads,d", [(2, 128, 2, 64), (1, 512, 3, 64), (2, 200, 2, 32), (3, 16, 2, 16), (1, 384, 1, 64)])
+def test_fused_attention_and_its_gradients_against_the_oracle(device, batch, seq, heads, d):
+    """Attention and AttentionGradQ/K/V as the two fused kernels, on bf16-valued q, k, v, g with a
+    few keys masked out, against the oracle's f32 ops on the same values. Probabilities and score
+    gradients pass through bf16 (8 significant bits) on their way to the tensor core and the
+    results are stored as bf16: every element within 2 % of its tensor's largest magnitude."""
+    import torch
+    r = np.random.default_rng(batch * 1000 + seq + heads + d)
+    h, rows = heads * d, batch * seq
+    t = {name: torch.from_numpy(r.standard_normal((rows, h)).astype(np.float32)).to(torch.bfloat16) for name in "qkvg"}
+    mask = np.ones((batch, seq), dtype=np.float32)
+    mask[0, seq - 3:] = 0.0
+    if seq > 130:
+        mask[batch - 1, 125:131] = 0.0
+    p = ProgramText()
+    ids = {name: p.input(name, "f32", [rows, h]) for name in "qkvg"}
+    im = p.input("mask", "f32", [batch, seq])
+    attr = "[heads = %d]" % heads
+    out = p.op("Attention", [rows, h], [ids["q"], ids["k"], ids["v"], im], attr)
+    grads = [p.op(op, [rows, h], [ids["q"], ids["k"], ids["v"], im, ids["g"]], attr) for op in ("AttentionGradQ", "AttentionGradK", "AttentionGradV")]
+    for value in [out] + grads:
+        p.output(value)
+    session = oracle_lib.Session(p.text())
+    for name in "qkvg":
+        session.set_input(name, t[name].float().numpy())
+    session.set_input("mask", mask)
+    session.run()
+    want = [session.value(v, rows * h).reshape(rows, h) for v in [out] + grads]
+
+    d_in = {name: t[name].cuda() for name in "qkvg"}
+    d_mask = torch.from_numpy(mask).cuda()
+    d_out = [torch.full((rows, h), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+    stats = torch.zeros(rows * heads * 2, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    ptr = lambda x: C.c_void_p(x.data_ptr())
+    rc = M.lib().msx_op_attention_bf16(ptr(d_in["q"]), ptr(d_in["k"]), ptr(d_in["v"]), ptr(d_mask), ptr(d_in["g"]), ptr(d_out[0]), ptr(d_out[1]),
+                                       ptr(d_out[2]), ptr(d_out[3]), ptr(stats), batch, seq, seq, heads, d, ptr(status), None)
+    assert rc == M.OK, M.lib().msx_last_error(None).decode()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded wait inside a kernel ran out"
+    for name, got, c in zip(("out", "dq", "dk", "dv"), d_out, want):
+        got = got.float().cpu().numpy().astype(np.float64)
+        assert np.isfinite(got).all(), name
+        worst = float(np.abs(got - c).max())
+        assert worst <= 2e-2 * float(np.abs(c).max()), "%s: worst |g - c| = %g, largest |c| = %g" % (name, worst, np.abs(c).max())
+    # A masked key takes no part: its dK and dV rows are zeros.
+    dk = d_out[2].float().cpu().numpy()
+    assert not dk[seq - 3:seq].any()
