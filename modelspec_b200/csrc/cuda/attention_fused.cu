@@ -40,7 +40,8 @@ using namespace tc;
 
 constexpr uint32_t TILE = 128;                 // rows of a tile (queries or keys)
 constexpr uint32_t TILE_BYTES = TILE * 128;    // 64 bf16 columns a row
-constexpr int THREADS = 192;                   // warp 0 loads, warp 1 issues MMAs, warps 2-5 own a row each
+constexpr int ROW_WARPS = 16;                  // four threads a row: 32 score columns, 16 result columns each
+constexpr int THREADS = 64 + 32 * ROW_WARPS;   // warp 0 loads, warp 1 issues MMAs, warps 2-17 do the row work
 
 struct FusedArgs {
     const float* mask;   // [batch, keys]
@@ -57,17 +58,12 @@ struct FusedArgs {
     CoordOrder order;    // of every [rows, H] operand's tensor map
 };
 
-// Which keys of key tile `tile` count (inside the sequence and not masked out), as 128 floats of
-// the calling warp's own (no other warp reads or writes them, so a warp that gives up strands nobody).
-__device__ __forceinline__ void fill_key_mask(float* mine, const float* __restrict__ mask, uint32_t seq, uint32_t tile, uint32_t k_len,
-                                              uint32_t lane) {
-    __syncwarp();
-#pragma unroll
-    for (uint32_t c = lane; c < TILE; c += 32) {
-        const uint32_t key = tile * TILE + c;
-        mine[c] = (key < k_len && mask[static_cast<uint64_t>(seq) * k_len + key] != 0.0f) ? 1.0f : 0.0f;
-    }
-    __syncwarp();
+// Which of the 32 keys from `first` on count (inside the sequence and not masked out): bit c for
+// key first + c, the same word in every lane of the warp.
+__device__ __forceinline__ uint32_t keys_that_count(const float* __restrict__ mask, uint32_t seq, uint32_t first, uint32_t k_len, uint32_t lane) {
+    const uint32_t key = first + lane;
+    const bool counts = key < k_len && mask[static_cast<uint64_t>(seq) * k_len + key] != 0.0f;
+    return __ballot_sync(0xffffffffu, counts);
 }
 
 // One [128 rows, 64 columns] tile of a [rows, H] operand: rows row0.. of sequence `seq`, head `head`.
@@ -80,12 +76,37 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, 
     tma_load(dst, map, bar, 0, upper);
 }
 
-// A row of up to 64 f32 values as bf16 to global memory, 16 bytes at a time.
-__device__ __forceinline__ void store_row_bf16(void* base, uint64_t element, const float (&v)[64], uint32_t d) {
-    bf16* to = static_cast<bf16*>(base) + element;
+// 32 lanes x 16 consecutive columns of tensor memory.
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// 32 f32 values of row `row`, columns chunk * 32 .., as bf16 into a pair of [128 rows, 64 columns]
+// tiles (columns 0-63 in the first, 64-127 in the second) in the layout the tensor core reads.
+__device__ __forceinline__ void store_chunk_bf16(char* tile_pair, uint32_t row, uint32_t chunk, const float (&v)[32]) {
+    char* to = tile_pair + (chunk >> 1) * TILE_BYTES;
+    const uint32_t first16 = (chunk & 1u) * 4;  // 16-byte chunk index of column chunk * 32 within its tile row
 #pragma unroll
-    for (uint32_t c = 0; c < 64; c += 8) {  // constant bounds: v stays in registers
-        if (c + 8 > d) break;
+    for (int c = 0; c < 32; c += 8) {
+        float8 f;
+        f.lo = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+        f.hi = make_float4(v[c + 4], v[c + 5], v[c + 6], v[c + 7]);
+        store8(reinterpret_cast<bf16*>(to + swizzled_chunk(row, first16 + (c >> 3))), f);
+    }
+}
+
+// 16 f32 values as bf16 to global memory (columns c0 .. c0 + 15 of a head's row, those below d).
+__device__ __forceinline__ void store_part_bf16(void* base, uint64_t element, const float (&v)[16], uint32_t c0, uint32_t d) {
+    bf16* to = static_cast<bf16*>(base) + element + c0;
+#pragma unroll
+    for (uint32_t c = 0; c < 16; c += 8) {
+        if (c0 + c + 8 > d) break;
         float8 f;
         f.lo = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
         f.hi = make_float4(v[c + 4], v[c + 5], v[c + 6], v[c + 7]);
@@ -94,26 +115,27 @@ __device__ __forceinline__ void store_row_bf16(void* base, uint64_t element, con
 }
 
 // ---- forward --------------------------------------------------------------------------------------
-// Shared memory: Q, K, V tiles (16 KB each), P as two 16 KB tiles, then barriers.
-// Tensor memory: S at columns [0, 128), P V at [128, 192).
-constexpr uint32_t FWD_TILES = 5 * TILE_BYTES;
-constexpr uint32_t FWD_SMEM = FWD_TILES + 1024 /* alignment slack */ + 2560 /* barriers, key masks */;
-constexpr uint32_t FWD_TMEM = 256;
+// Shared memory: Q, two stages of K, V, P as two tiles (112 KB), then barriers and the exchange of
+// row maxima and sums between the four threads of a row.
+// Tensor memory: S of even key tiles at columns [0, 128), of odd ones at [128, 256), P V at [256, 320).
+constexpr uint32_t FWD_TILES = 7 * TILE_BYTES;
+constexpr uint32_t FWD_SMEM = FWD_TILES + 1024 /* alignment slack */ + 256 /* barriers */ + 2 * 4 * TILE * 4 /* row exchange */;
+constexpr uint32_t FWD_TMEM = 512;
 
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, 1)
 attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const FusedArgs args) {
     extern __shared__ char smem_raw[];
     char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     char* q_tile = tiles;
-    char* k_tile = tiles + TILE_BYTES;
-    char* v_tile = tiles + 2 * TILE_BYTES;
-    char* p_tile = tiles + 3 * TILE_BYTES;  // two tiles: keys 0-63 and 64-127 of the key tile
+    auto k_tile = [&](uint32_t stage) { return tiles + (1 + stage) * TILE_BYTES; };
+    char* v_tile = tiles + 3 * TILE_BYTES;
+    char* p_tile = tiles + 4 * TILE_BYTES;  // two tiles: keys 0-63 and 64-127 of the key tile
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + FWD_TILES);
-    enum { Q_FULL, K_FULL, K_EMPTY, V_FULL, V_EMPTY, S_FULL, P_READY, PV_FULL, BARS };
+    enum { Q_FULL, K_FULL0, K_FULL1, K_EMPTY0, K_EMPTY1, V_FULL, V_EMPTY, S_FULL0, S_FULL1, P_READY, PV_FULL, ROWS_MET, BARS };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BARS);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
-    float* key_masks = reinterpret_cast<float*>(tmem_slot + 2);  // 128 floats a row warp: 1 for a key that counts
+    float* exchange = reinterpret_cast<float*>(tiles + FWD_TILES + 256);  // [2][4 column chunks][128 rows]
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t q0 = blockIdx.x * TILE, head = blockIdx.y, seq = blockIdx.z;
@@ -121,7 +143,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     auto bar = [&](int which) { return smem_u32(&bars[which]); };
 
     if (tid == 0) {
-        for (int b = 0; b < BARS; ++b) mbar_init(bar(b), b == P_READY ? 4u : 1u);
+        for (int b = 0; b < BARS; ++b) mbar_init(bar(b), (b == P_READY || b == ROWS_MET) ? static_cast<uint32_t>(ROW_WARPS) : 1u);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -133,56 +155,66 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
+    const uint32_t tmem_pv = tmem_base + 256;
 
     if (warp == 0) {
         if (lane == 0) {
             bool alive = true;
-            uint32_t armed = 0;  // bit 0 Q, 1 K, 2 V: a copy was issued for it
-            uint32_t k_phase = 0, v_phase = 0;
+            uint32_t armed = 0, k_phase[2] = {0, 0}, v_phase = 0;  // armed: bit 0 Q, 1-2 the K stages, 3 V
             mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
             load_tile(smem_u32(q_tile), &map_q, bar(Q_FULL), args.order, q0, head, seq);
             armed |= 1u;
             for (uint32_t j = 0; j < key_tiles && alive; ++j) {
-                alive = mbar_wait(bar(K_EMPTY), (j & 1u) ^ 1u, abort_flag, args.status);
+                const uint32_t stage = j & 1u, use = j >> 1;
+                alive = mbar_wait(bar(K_EMPTY0 + stage), (use & 1u) ^ 1u, abort_flag, args.status);
                 if (!alive) break;
-                mbar_expect_tx(bar(K_FULL), TILE_BYTES);
-                load_tile(smem_u32(k_tile), &map_k, bar(K_FULL), args.order, j * TILE, head, seq);
-                armed |= 2u;
-                k_phase = j & 1u;
+                mbar_expect_tx(bar(K_FULL0 + stage), TILE_BYTES);
+                load_tile(smem_u32(k_tile(stage)), &map_k, bar(K_FULL0 + stage), args.order, j * TILE, head, seq);
+                armed |= 2u << stage;
+                k_phase[stage] = use & 1u;
                 alive = mbar_wait(bar(V_EMPTY), (j & 1u) ^ 1u, abort_flag, args.status);
                 if (!alive) break;
                 mbar_expect_tx(bar(V_FULL), TILE_BYTES);
                 load_tile(smem_u32(v_tile), &map_v, bar(V_FULL), args.order, j * TILE, head, seq);
-                armed |= 4u;
+                armed |= 8u;
                 v_phase = j & 1u;
             }
             if (!alive) {
                 // The copies already issued still write into this CTA's shared memory: wait (bounded).
                 if (armed & 1u) for (uint32_t spin = 0; spin < WAIT_LIMIT && !mbar_try_wait(bar(Q_FULL), 0); ++spin) {}
-                if (armed & 2u) for (uint32_t spin = 0; spin < WAIT_LIMIT && !mbar_try_wait(bar(K_FULL), k_phase); ++spin) {}
-                if (armed & 4u) for (uint32_t spin = 0; spin < WAIT_LIMIT && !mbar_try_wait(bar(V_FULL), v_phase); ++spin) {}
+                for (uint32_t stage = 0; stage < 2; ++stage)
+                    if (armed & (2u << stage)) for (uint32_t spin = 0; spin < WAIT_LIMIT && !mbar_try_wait(bar(K_FULL0 + stage), k_phase[stage]); ++spin) {}
+                if (armed & 8u) for (uint32_t spin = 0; spin < WAIT_LIMIT && !mbar_try_wait(bar(V_FULL), v_phase); ++spin) {}
             }
         }
     } else if (warp == 1) {
         const uint32_t idesc_s = instruction_descriptor(TILE, TILE, false, false);
         const uint32_t idesc_pv = instruction_descriptor(TILE, 64, false, true);
-        bool alive = mbar_wait(bar(Q_FULL), 0, abort_flag, args.status);
-        for (uint32_t j = 0; j < key_tiles && alive; ++j) {
-            const uint32_t ph = j & 1u;
-            alive = mbar_wait(bar(K_FULL), ph, abort_flag, args.status);
-            if (!alive) break;
+        // S_j = Q K_j^T into its half of the score columns: k runs over the 64 head columns, 16
+        // (32 bytes of a row) per MMA. S_j+1 is issued before P_j V_j, so that it runs under the
+        // softmax of tile j.
+        auto scores = [&](uint32_t j) -> bool {
+            const uint32_t stage = j & 1u;
+            if (!mbar_wait(bar(K_FULL0 + stage), (j >> 1) & 1u, abort_flag, args.status)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
-                // S = Q K^T: k runs over the 64 head columns, 16 (32 bytes of a row) per MMA.
 #pragma unroll
                 for (uint32_t ks = 0; ks < 4; ++ks)
-                    mma_bf16(tmem_s, tile_descriptor(smem_u32(q_tile) + ks * 32, 16), tile_descriptor(smem_u32(k_tile) + ks * 32, 16), idesc_s, ks != 0);
-                mma_commit(bar(K_EMPTY));
-                mma_commit(bar(S_FULL));
+                    mma_bf16(tmem_base + stage * 128, tile_descriptor(smem_u32(q_tile) + ks * 32, 16), tile_descriptor(smem_u32(k_tile(stage)) + ks * 32, 16),
+                             idesc_s, ks != 0);
+                mma_commit(bar(K_EMPTY0 + stage));
+                mma_commit(bar(S_FULL0 + stage));
             }
             __syncwarp();
-            alive = mbar_wait(bar(P_READY), ph, abort_flag, args.status);
+            return true;
+        };
+        bool alive = mbar_wait(bar(Q_FULL), 0, abort_flag, args.status);
+        if (alive) alive = scores(0);
+        for (uint32_t j = 0; j < key_tiles && alive; ++j) {
+            const uint32_t ph = j & 1u;
+            // The rows have read S_j-1 (they arrived at P_READY of tile j - 1 after it): its columns are free.
+            if (j + 1 < key_tiles) alive = scores(j + 1);
+            if (alive) alive = mbar_wait(bar(P_READY), ph, abort_flag, args.status);
             if (alive) alive = mbar_wait(bar(V_FULL), ph, abort_flag, args.status);
             if (!alive) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -199,62 +231,66 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             __syncwarp();
         }
     } else {
-        // One query row a thread: row q0 + t of the sequence, lane t of tensor memory.
-        const uint32_t quarter = warp & 3u, t = quarter * 32 + lane;
+        // Four threads a query row: row q0 + t (lane t of tensor memory), score columns
+        // chunk * 32 .. of a key tile and result columns chunk * 16 ... The lanes of tensor memory a
+        // warp may read are those of its index modulo 4.
+        const uint32_t quarter = warp & 3u, chunk = (warp - 2) >> 2, t = quarter * 32 + lane;
         const uint32_t lane_base = (quarter * 32u) << 16;
         const uint32_t row = q0 + t;
-        float best = -INFINITY, total = 0.0f;
-        float o[64];
+        float best = -INFINITY, total = 0.0f;  // total: over this thread's columns only, until the end
+        float o[16];
 #pragma unroll
-        for (int c = 0; c < 64; ++c) o[c] = 0.0f;
+        for (int c = 0; c < 16; ++c) o[c] = 0.0f;
         bool alive = true;
+        uint32_t meetings = 0;  // completed phases of ROWS_MET
+        // The four threads of every row exchange a value each (the maximum of their columns, at the
+        // end their sum) through shared memory; the warps meet at an mbarrier with a bounded wait.
+        auto exchange_with_row = [&](float mine, float (&all)[4]) -> bool {
+            float* slot = exchange + (meetings & 1u) * 4 * TILE;
+            slot[chunk * TILE + t] = mine;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(ROWS_MET));
+            bool ok = mbar_wait(bar(ROWS_MET), meetings & 1u, abort_flag, args.status);
+            ok = __all_sync(0xffffffffu, ok);
+            ++meetings;
+            if (!ok) return false;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) all[c] = slot[c * TILE + t];
+            return true;
+        };
         for (uint32_t j = 0; j < key_tiles; ++j) {
-            const uint32_t ph = j & 1u;
-            float* key_mask = key_masks + quarter * TILE;
-            fill_key_mask(key_mask, args.mask, seq, j, args.k_len, lane);
-            alive = mbar_wait(bar(S_FULL), ph, abort_flag, args.status);
+            const uint32_t ph = j & 1u, stage = j & 1u;
+            const uint32_t counts = keys_that_count(args.mask, seq, j * TILE + chunk * 32, args.k_len, lane);
+            alive = mbar_wait(bar(S_FULL0 + stage), (j >> 1) & 1u, abort_flag, args.status);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // Pass 1: the row's maximum over the tile.
-            float tile_best = -INFINITY;
-#pragma unroll 1
-            for (uint32_t c0 = 0; c0 < TILE; c0 += 32) {
-                uint32_t r[32];
-                tmem_load32(tmem_s + lane_base + c0, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            uint32_t r[32];
+            tmem_load32(tmem_base + stage * 128 + lane_base + chunk * 32, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float sc[32];
+            float mine = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    if (key_mask[c0 + c] != 0.0f) tile_best = fmaxf(tile_best, __uint_as_float(r[c]) * args.scale);
+            for (int c = 0; c < 32; ++c) {
+                sc[c] = ((counts >> c) & 1u) ? __uint_as_float(r[c]) * args.scale : -INFINITY;
+                mine = fmaxf(mine, sc[c]);
             }
-            const float new_best = fmaxf(best, tile_best);
+            float parts[4];
+            alive = exchange_with_row(mine, parts);
+            if (!alive) break;
+            const float new_best = fmaxf(fmaxf(best, fmaxf(parts[0], parts[1])), fmaxf(parts[2], parts[3]));
             // exp(-inf - -inf) never forms: a row that has seen no key yet keeps zeros.
             const float shrink = best == -INFINITY ? 0.0f : __expf(best - new_best);
             float tile_total = 0.0f;
-            // Pass 2: the probabilities (before normalisation), as bf16 into the two P tiles.
-#pragma unroll 1
-            for (uint32_t c0 = 0; c0 < TILE; c0 += 32) {
-                uint32_t r[32];
-                tmem_load32(tmem_s + lane_base + c0, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float p[32];
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    p[c] = key_mask[c0 + c] != 0.0f ? __expf(__uint_as_float(r[c]) * args.scale - new_best) : 0.0f;
-                    tile_total += p[c];
-                }
-                char* to = p_tile + (c0 >> 6) * TILE_BYTES;
-#pragma unroll
-                for (int c = 0; c < 32; c += 8) {
-                    float8 f;
-                    f.lo = make_float4(p[c], p[c + 1], p[c + 2], p[c + 3]);
-                    f.hi = make_float4(p[c + 4], p[c + 5], p[c + 6], p[c + 7]);
-                    store8(reinterpret_cast<bf16*>(to + swizzled_chunk(t, ((c0 & 63u) + c) >> 3)), f);
-                }
+            for (int c = 0; c < 32; ++c) {
+                sc[c] = ((counts >> c) & 1u) ? __expf(sc[c] - new_best) : 0.0f;
+                tile_total += sc[c];
             }
             total = total * shrink + tile_total;
             best = new_best;
-            // P is in shared memory: visible to the tensor core, then one arrival per warp.
+            // The P tiles are free: P_j-1 V_j-1 was complete before this thread read its result.
+            store_chunk_bf16(p_tile, t, chunk, sc);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -263,26 +299,28 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t pv[16];
+            tmem_load16(tmem_pv + lane_base + chunk * 16, pv);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (uint32_t c0 = 0; c0 < 64; c0 += 32) {
-                uint32_t r[32];
-                tmem_load32(tmem_pv + lane_base + c0, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int c = 0; c < 32; ++c) o[c0 + c] = o[c0 + c] * shrink + __uint_as_float(r[c]);
-            }
+            for (int c = 0; c < 16; ++c) o[c] = o[c] * shrink + __uint_as_float(pv[c]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
-        if (alive && row < args.q_len) {
-            const float inverse = total > 0.0f ? 1.0f / total : 0.0f;
+        if (alive) {
+            float parts[4];
+            alive = exchange_with_row(total, parts);
+            if (alive && row < args.q_len) {
+                const float sum = (parts[0] + parts[1]) + (parts[2] + parts[3]);
+                const float inverse = sum > 0.0f ? 1.0f / sum : 0.0f;
 #pragma unroll
-            for (int c = 0; c < 64; ++c) o[c] *= inverse;
-            const uint64_t global_row = static_cast<uint64_t>(seq) * args.q_len + row;
-            store_row_bf16(args.out, global_row * args.h + head * args.d, o, args.d);
-            if (args.stats != nullptr) {
-                float* st = args.stats + (global_row * args.heads + head) * 2;
-                st[0] = best;
-                st[1] = total;
+                for (int c = 0; c < 16; ++c) o[c] *= inverse;
+                const uint64_t global_row = static_cast<uint64_t>(seq) * args.q_len + row;
+                store_part_bf16(args.out, global_row * args.h + head * args.d, o, chunk * 16, args.d);
+                if (args.stats != nullptr && chunk == 0) {
+                    float* st = args.stats + (global_row * args.heads + head) * 2;
+                    st[0] = best;
+                    st[1] = sum;
+                }
             }
         }
     }
@@ -293,11 +331,11 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
 // ---- backward -------------------------------------------------------------------------------------
 // Shared memory: K_j, V_j, two stages of (Q_i, G_i), P (two tiles), dS (two tiles): 160 KB; then
-// barriers, the key mask of the tile and the row statistics of every query (max, 1 / sum, D).
+// barriers and the row statistics of every query (max, 1 / sum, D).
 // Tensor memory (512 columns): S / dP [0, 128), dV [128, 192), dK [192, 256), dQ_i [256 + 64 i, ..).
 constexpr uint32_t BWD_TILES = 10 * TILE_BYTES;
 constexpr uint32_t BWD_ROWS = 512;
-constexpr uint32_t BWD_SMEM = BWD_TILES + 1024 /* alignment slack */ + 2560 /* barriers, key masks */ + 3 * BWD_ROWS * 4;
+constexpr uint32_t BWD_SMEM = BWD_TILES + 1024 /* alignment slack */ + 256 /* barriers */ + 3 * BWD_ROWS * 4;
 constexpr uint32_t BWD_TMEM = 512;
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -316,14 +354,14 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     // DP_FULL: the S / dP region holds a product. P_DONE, DS_DONE: the row threads have written P
     // (and are done with S) / dS. P_FREE, DS_FREE: the MMAs that read the P / dS tiles are complete.
     // ACC_FULL: dV_j and dK_j are complete; ACC_EMPTY: they have been drained. DQ_FULL: everything is.
+    // STATS_MET: every row's statistics are in shared memory.
     enum { KV_FULL, KV_EMPTY, QG_FULL0, QG_FULL1, QG_EMPTY0, QG_EMPTY1, S_FULL, DP_FULL, P_DONE, DS_DONE, P_FREE, DS_FREE, ACC_FULL, ACC_EMPTY,
-           DQ_FULL, BARS };
+           DQ_FULL, STATS_MET, BARS };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BARS);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
-    float* key_masks = reinterpret_cast<float*>(tmem_slot + 2);  // 128 floats a row warp
-    float* row_best = key_masks + 4 * TILE;                      // [BWD_ROWS]
-    float* row_inverse = row_best + BWD_ROWS;                    // 1 / sum of exp
-    float* row_dot = row_inverse + BWD_ROWS;                     // D_i
+    float* row_best = reinterpret_cast<float*>(tiles + BWD_TILES + 256);  // [BWD_ROWS]
+    float* row_inverse = row_best + BWD_ROWS;                             // 1 / sum of exp
+    float* row_dot = row_inverse + BWD_ROWS;                              // D_i
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t head = blockIdx.x, seq = blockIdx.y;
@@ -331,7 +369,8 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     auto bar = [&](int which) { return smem_u32(&bars[which]); };
 
     if (tid == 0) {
-        for (int b = 0; b < BARS; ++b) mbar_init(bar(b), (b == P_DONE || b == DS_DONE || b == ACC_EMPTY) ? 4u : 1u);
+        for (int b = 0; b < BARS; ++b)
+            mbar_init(bar(b), (b == P_DONE || b == DS_DONE || b == ACC_EMPTY || b == STATS_MET) ? static_cast<uint32_t>(ROW_WARPS) : 1u);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -442,12 +481,15 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             }
         }
     } else {
-        const uint32_t quarter = warp & 3u, t = quarter * 32 + lane;
+        // Four threads a row of a tile (lane t of tensor memory): score columns chunk * 32 .., and
+        // columns chunk * 16 .. of the gradients when they are drained.
+        const uint32_t quarter = warp & 3u, chunk = (warp - 2) >> 2, t = quarter * 32 + lane;
         const uint32_t lane_base = (quarter * 32u) << 16;
         bool alive = true;
-        // Row statistics of every query of this (sequence, head): the forward's max and sum, and
-        // D = sum_c O g over the head's columns.
-        for (uint32_t row = t; row < query_tiles * TILE; row += TILE) {
+        // Row statistics of every query of this (sequence, head), one row a thread: the forward's
+        // max and sum, and D = sum_c O g over the head's columns.
+        {
+            const uint32_t row = chunk * TILE + t;
             float best = 0.0f, inverse = 0.0f, dot = 0.0f;
             if (row < args.q_len) {
                 const uint64_t global_row = static_cast<uint64_t>(seq) * args.q_len + row;
@@ -465,11 +507,14 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             row_best[row] = best;
             row_inverse[row] = inverse;  // 0 for a row past the end: its probabilities are zeros
             row_dot[row] = dot;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(STATS_MET));
+            alive = mbar_wait(bar(STATS_MET), 0, abort_flag, args.status);
+            alive = __all_sync(0xffffffffu, alive);
         }
         uint32_t pair = 0;
         for (uint32_t j = 0; j < key_tiles && alive; ++j) {
-            float* key_mask = key_masks + quarter * TILE;
-            fill_key_mask(key_mask, args.mask, seq, j, args.k_len, lane);
+            const uint32_t counts = keys_that_count(args.mask, seq, j * TILE + chunk * 32, args.k_len, lane);
             for (uint32_t i = 0; i < query_tiles; ++i, ++pair) {
                 const uint32_t ph = pair & 1u;
                 const uint32_t row = i * TILE + t;
@@ -480,24 +525,13 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-                for (uint32_t c0 = 0; c0 < TILE; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_load32(tmem_sp + lane_base + c0, r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    float p[32];
+                uint32_t r[32];
+                tmem_load32(tmem_sp + lane_base + chunk * 32, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float p[32];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        p[c] = key_mask[c0 + c] != 0.0f ? __expf(__uint_as_float(r[c]) * args.scale - best) * inverse : 0.0f;
-                    char* to = p_tile + (c0 >> 6) * TILE_BYTES;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
-                        float8 f;
-                        f.lo = make_float4(p[c], p[c + 1], p[c + 2], p[c + 3]);
-                        f.hi = make_float4(p[c + 4], p[c + 5], p[c + 6], p[c + 7]);
-                        store8(reinterpret_cast<bf16*>(to + swizzled_chunk(t, ((c0 & 63u) + c) >> 3)), f);
-                    }
-                }
+                for (int c = 0; c < 32; ++c) p[c] = ((counts >> c) & 1u) ? __expf(__uint_as_float(r[c]) * args.scale - best) * inverse : 0.0f;
+                store_chunk_bf16(p_tile, t, chunk, p);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -507,29 +541,11 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-                for (uint32_t c0 = 0; c0 < TILE; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_load32(tmem_sp + lane_base + c0, r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    const char* from = p_tile + (c0 >> 6) * TILE_BYTES;
-                    char* to = ds_tile + (c0 >> 6) * TILE_BYTES;
+                tmem_load32(tmem_sp + lane_base + chunk * 32, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
-                        const uint32_t at = swizzled_chunk(t, ((c0 & 63u) + c) >> 3);
-                        // This thread's own probabilities, as the tensor core reads them (bf16).
-                        const uint4 raw = *reinterpret_cast<const uint4*>(from + at);
-                        const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                        const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-                        const float2 p2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.z));
-                        const float2 p3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.w));
-                        auto ds = [&](float p, int k) { return p * (__uint_as_float(r[c + k]) - dot) * args.scale; };
-                        float8 f;
-                        f.lo = make_float4(ds(p0.x, 0), ds(p0.y, 1), ds(p1.x, 2), ds(p1.y, 3));
-                        f.hi = make_float4(ds(p2.x, 4), ds(p2.y, 5), ds(p3.x, 6), ds(p3.y, 7));
-                        store8(reinterpret_cast<bf16*>(to + at), f);
-                    }
-                }
+                for (int c = 0; c < 32; ++c) p[c] = p[c] * (__uint_as_float(r[c]) - dot) * args.scale;  // dS
+                store_chunk_bf16(ds_tile, t, chunk, p);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -543,18 +559,16 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t key = j * TILE + t;
             const uint64_t key_at = (static_cast<uint64_t>(seq) * args.k_len + key) * args.h + head * args.d;
+#pragma unroll
             for (int which = 0; which < 2; ++which) {
-                float v[64];
+                uint32_t raw[16];
+                tmem_load16((which == 0 ? tmem_dv : tmem_dk) + lane_base + chunk * 16, raw);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float v[16];
 #pragma unroll
-                for (uint32_t c0 = 0; c0 < 64; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_load32((which == 0 ? tmem_dv : tmem_dk) + lane_base + c0, r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c0 + c] = __uint_as_float(r[c]);
-                }
+                for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(raw[c]);
                 void* to = which == 0 ? args.dv : args.dk;
-                if (to != nullptr && key < args.k_len) store_row_bf16(to, key_at, v, args.d);
+                if (to != nullptr && key < args.k_len) store_part_bf16(to, key_at, v, chunk * 16, args.d);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -567,17 +581,14 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         if (alive && args.dq != nullptr) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (uint32_t i = 0; i < query_tiles; ++i) {
-                float v[64];
+                uint32_t raw[16];
+                tmem_load16(tmem_dq + 64 * i + lane_base + chunk * 16, raw);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float v[16];
 #pragma unroll
-                for (uint32_t c0 = 0; c0 < 64; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_load32(tmem_dq + 64 * i + lane_base + c0, r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c0 + c] = __uint_as_float(r[c]);
-                }
+                for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(raw[c]);
                 const uint32_t row = i * TILE + t;
-                if (row < args.q_len) store_row_bf16(args.dq, (static_cast<uint64_t>(seq) * args.q_len + row) * args.h + head * args.d, v, args.d);
+                if (row < args.q_len) store_part_bf16(args.dq, (static_cast<uint64_t>(seq) * args.q_len + row) * args.h + head * args.d, v, chunk * 16, args.d);
             }
         }
     }

@@ -664,28 +664,55 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
 // chunks w, w + 8, ... in ascending order and the eight sums are added in ascending w. Every
 // output is a fixed expression of the inputs: deterministic, tolerance class against a
 // sequential column sum. dx (with gamma), dgamma and dbeta may each be null.
+// Rows of 512 or more elements (ITEMS >= 16) keep their column sums in shared memory instead of
+// registers (the same additions in the same order), and gamma is read where it is used: with the
+// sums and gamma in registers a thread needs about 250 of them, one block of 8 warps fills an SM's
+// register file, and the loads of a row have nothing to hide behind.
 template <int ITEMS, int V, class T>
-__global__ void __launch_bounds__(256) layer_norm_backward_kernel(
+__global__ void __launch_bounds__(256, ITEMS >= 16 ? 2 : 1) layer_norm_backward_kernel(
     const T* __restrict__ x, const float* __restrict__ gamma, const T* __restrict__ g, const T* __restrict__ g1,
     const T* __restrict__ g2, const T* __restrict__ g3, T* __restrict__ dx,
     float* __restrict__ partial, uint32_t* __restrict__ counter, float* __restrict__ dgamma, float* __restrict__ dbeta,
     uint32_t want, uint32_t rows, uint32_t h, uint32_t rows_per_chunk, DropoutDraw adjoint_draw, DropoutDraw dx_draw,
     T* __restrict__ dx_dropped, const T* __restrict__ pre_activation) {
-    __shared__ float buf[8 * 32 * ITEMS];
+    constexpr bool WIDE = ITEMS >= 16;
+    extern __shared__ float backward_sums[];  // 8 * 32 * ITEMS floats, twice that for wide rows
+    float* const buf = backward_sums;
+    float* const buf_b = backward_sums + (WIDE ? 8 * 32 * ITEMS : 0);
     __shared__ bool is_last;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, chunks = gridDim.x;
     const uint32_t r0 = blockIdx.x * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
     const float width = static_cast<float>(h);
     // dx is formed when it is stored or when what is stored is a function of it.
     const bool want_dx = dx != nullptr || dx_dropped != nullptr;
-    float acc_g[ITEMS], acc_b[ITEMS], gam[ITEMS];
+    constexpr int HELD = WIDE ? 1 : ITEMS;
+    float acc_g[HELD], acc_b[HELD], gam[HELD];
+    // This thread's column sums when they live in shared memory: value i at [i * 32].
+    float* const sum_g = buf + warp * ITEMS * 32 + lane;
+    float* const sum_b = buf_b + (WIDE ? warp * ITEMS * 32 + lane : 0);
+    if constexpr (WIDE) {
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-        acc_g[i] = 0.0f;
-        acc_b[i] = 0.0f;
-        uint32_t c = column_of<V>(i, lane);
-        gam[i] = (want_dx && c < h) ? gamma[c] : 0.0f;
+        for (int i = 0; i < ITEMS; ++i) {
+            sum_g[i * 32] = 0.0f;
+            sum_b[i * 32] = 0.0f;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            acc_g[i] = 0.0f;
+            acc_b[i] = 0.0f;
+            uint32_t c = column_of<V>(i, lane);
+            gam[i] = (want_dx && c < h) ? gamma[c] : 0.0f;
+        }
     }
+    auto gamma_of = [&](int i) -> float {
+        if constexpr (WIDE) {
+            const uint32_t c = column_of<V>(i, lane);
+            return (want_dx && c < h) ? __ldg(gamma + c) : 0.0f;
+        } else {
+            return gam[i];
+        }
+    };
     for (uint32_t r = r0 + warp; r < r1; r += 8) {
         // All loads of an array are issued before any is used: unconditional, from a clamped
         // column (what a column past h reads is discarded below), one array after another. A load
@@ -737,9 +764,14 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
         for (int i = 0; i < ITEMS; ++i)
             if (column_of<V>(i, lane) < h) {
                 float xhat = (xv[i] - mean) * rstd;
-                acc_g[i] = fmaf(gv[i], xhat, acc_g[i]);
-                acc_b[i] += gv[i];
-                float gx = gv[i] * gam[i];
+                if constexpr (WIDE) {
+                    sum_g[i * 32] = fmaf(gv[i], xhat, sum_g[i * 32]);
+                    sum_b[i * 32] += gv[i];
+                } else {
+                    acc_g[i] = fmaf(gv[i], xhat, acc_g[i]);
+                    acc_b[i] += gv[i];
+                }
+                float gx = gv[i] * gamma_of(i);
                 s1 += gx;
                 s2 = fmaf(gx, xhat, s2);
             }
@@ -752,7 +784,7 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
                 const uint32_t c = column_of<V>(i, lane);
-                float gx = gv[i] * gam[i];
+                float gx = gv[i] * gamma_of(i);
                 float xhat = (xv[i] - mean) * rstd;
                 const float value = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
                 xv[i] = value;  // the dx row, in the registers of the x row
@@ -780,16 +812,19 @@ __global__ void __launch_bounds__(256) layer_norm_backward_kernel(
     for (int pass = 0; pass < 2; ++pass) {
         if ((want & (1u << pass)) == 0) continue;
         __syncthreads();
+        if constexpr (!WIDE) {
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) buf[(warp * ITEMS + i) * 32 + lane] = pass == 0 ? acc_g[i] : acc_b[i];
+            for (int i = 0; i < ITEMS; ++i) buf[(warp * ITEMS + i) * 32 + lane] = pass == 0 ? acc_g[i] : acc_b[i];
+        }
         __syncthreads();
+        const float* const sums = (WIDE && pass == 1) ? buf_b : buf;
         for (uint32_t c = threadIdx.x; c < h; c += 256) {
             // Column c is value i of lane l (the inverse of column_of).
             const uint32_t turn = c / (32u * V), within = c % (32u * V);
             const uint32_t i = turn * V + within % V, l = within / V;
-            float total = buf[i * 32 + l];
+            float total = sums[i * 32 + l];
 #pragma unroll
-            for (int w = 1; w < 8; ++w) total += buf[(w * ITEMS + i) * 32 + l];
+            for (int w = 1; w < 8; ++w) total += sums[(w * ITEMS + i) * 32 + l];
             (pass == 0 ? partial_gamma : partial_beta)[c] = total;
         }
     }
@@ -975,8 +1010,16 @@ void launch_layer_norm_backward(cudaStream_t s, const T* x, const float* gamma, 
     uint32_t want = (dgamma ? 1u : 0u) | (dbeta ? 2u : 0u);
     constexpr int PAIR = sizeof(T) == 2 ? 2 : 1;
     const bool pairs = PAIR == 2 && h % 2 == 0 && items >= 2;
-#define MSX_LN_BACKWARD(N) do { if (pairs) layer_norm_backward_kernel<N, (N % 2 == 0 ? PAIR : 1)><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped, pre_activation); \
-        else layer_norm_backward_kernel<N, 1><<<chunks, 256, 0, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped, pre_activation); } while (0)
+    // Shared memory of the column sums: one array of 8 x 32 x N floats, two for rows of 512 or more.
+#define MSX_LN_BACKWARD_ONE(N, W) do { \
+        auto kernel = layer_norm_backward_kernel<N, W, T>; \
+        constexpr uint32_t bytes = (N >= 16 ? 2u : 1u) * 8u * 32u * N * 4u; \
+        if (bytes > 40000u) { \
+            static const bool configured = [kernel] { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)); return true; }(); \
+            (void)configured; \
+        } \
+        kernel<<<chunks, 256, bytes, s>>>(x, gamma, g, g1, g2, g3, dx, scratch, counter, dgamma, dbeta, want, r, hh, per, in_draw, out_draw, dx_dropped, pre_activation); } while (0)
+#define MSX_LN_BACKWARD(N) do { if (pairs) MSX_LN_BACKWARD_ONE(N, (N % 2 == 0 ? PAIR : 1)); else MSX_LN_BACKWARD_ONE(N, 1); } while (0)
     if (items <= 1) MSX_LN_BACKWARD(1);
     else if (items <= 2) MSX_LN_BACKWARD(2);
     else if (items <= 4) MSX_LN_BACKWARD(4);
@@ -985,6 +1028,7 @@ void launch_layer_norm_backward(cudaStream_t s, const T* x, const float* gamma, 
     else if (items <= 24) MSX_LN_BACKWARD(24);
     else MSX_LN_BACKWARD(32);
 #undef MSX_LN_BACKWARD
+#undef MSX_LN_BACKWARD_ONE
     check_launch("layer_norm_backward");
 }
 }  // namespace
