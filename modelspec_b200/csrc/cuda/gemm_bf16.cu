@@ -56,7 +56,8 @@ template <int BN> struct Cfg {
     static constexpr uint32_t B_BYTES = BN * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-    static constexpr uint32_t TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr uint32_t STORE_BYTES = 4 * 2 * 4096;  // per drain warp two slabs of 32 rows x 128 bytes for its TMA stores
+    static constexpr uint32_t TOTAL = STAGES * STAGE_BYTES + STORE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr uint32_t TMEM_COLUMNS = 2 * BN;
 };
 
@@ -70,7 +71,8 @@ struct Bf16Args {
     uint64_t c_outer, c_inner;  // elements between the C matrices of consecutive batch indices
     uint32_t out_half;          // C is bf16 (never the workspace)
     uint32_t c_vec;             // every row of C starts on a 16-byte boundary
-    CoordOrder a_order, b_order;
+    uint32_t c_tma;             // C is written by TMA stores through map_c (else by the threads' own stores)
+    CoordOrder a_order, b_order, c_order;
 };
 
 // The work item `w` of a launch: its tile, batch index and k split.
@@ -101,13 +103,15 @@ __device__ __forceinline__ void place(const CoordOrder& order, uint32_t row, uin
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
-matmul_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Bf16Args args) {
+matmul_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                   const Bf16Args args) {
     using C = Cfg<BN>;
     constexpr int STAGES = C::STAGES;
     extern __shared__ char smem_raw[];
     // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows of 128 bytes.
     char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * C::STAGE_BYTES);
+    char* store_slabs = tiles + STAGES * C::STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(store_slabs + C::STORE_BYTES);
     // bars[0, STAGES) full, [STAGES, 2 STAGES) empty, then accumulator full [2], accumulator empty [2].
     uint64_t* acc_full = bars + 2 * STAGES;
     uint64_t* acc_empty = acc_full + 2;
@@ -130,6 +134,7 @@ matmul_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        if (args.c_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLUMNS) : "memory");
@@ -237,6 +242,7 @@ matmul_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // ---- drain warps: tensor memory -> registers -> C ----------------------------------------
         const uint32_t quarter = warp & 3u;  // the 32 lanes of tensor memory this warp may read
         uint32_t item = 0;
+        uint32_t turn = 0;  // TMA stores issued by this warp so far: they alternate between its two slabs
         bool alive = true;
         for (uint32_t w = blockIdx.x; w < total && alive; w += gridDim.x, ++item) {
             const Work k = work_of(args, w);
@@ -251,56 +257,113 @@ matmul_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             const bool partial = args.splits > 1;
             const uint64_t row_at = (partial ? static_cast<uint64_t>(k.split) * args.m * args.n : z_at) + static_cast<uint64_t>(row) * args.ldc;
             const bool half_out = args.out_half != 0 && !partial;
+            if (args.c_tma) {
+                // Coalesced: the warp's 32 rows of a 128-byte column slab go to shared memory (each
+                // lane its row, 16-byte pieces swizzled as the tensor map expects) and from there to
+                // C by one TMA store, which clips what lies outside the matrix. Two slabs a warp:
+                // one is being stored while the next is filled. No other warp takes part.
+                const uint32_t slab_cols = half_out ? 64u : 32u;
+                char* const my_slabs = store_slabs + quarter * 2 * 4096;
+                uint32_t upper[3];
+                place(args.c_order, k.tile_m * BM + quarter * 32u, partial ? 0u : k.z_inner, partial ? k.split : k.z_outer, upper);
+                const bool rows_inside = k.tile_m * BM + quarter * 32u < args.m;  // else nothing of this warp's is stored
 #pragma unroll 1
-            for (uint32_t c0 = 0; c0 < static_cast<uint32_t>(BN); c0 += 32) {
-                const uint32_t col = k.tile_n * BN + c0;
-                if (col >= args.n) break;  // the same for the whole warp
-                uint32_t r[32];
-                if (has_k) {
-                    tmem_load32(tmem_base + acc * BN + c0 + ((quarter * 32u) << 16), r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                } else {
+                for (uint32_t c0 = 0; c0 < static_cast<uint32_t>(BN); c0 += slab_cols, ++turn) {
+                    const uint32_t col = k.tile_n * BN + c0;
+                    if (col >= args.n) break;  // the same for the whole warp
+                    char* const slab = my_slabs + (turn & 1u) * 4096;
+                    // The store that last read this slab (two turns ago) has finished reading it.
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = 0u;  // an empty k range is a zero product
+                    for (uint32_t part = 0; part < 2; ++part) {
+                        if (part == 1 && !half_out) break;
+                        uint32_t r[32];
+                        if (has_k) {
+                            tmem_load32(tmem_base + acc * BN + c0 + part * 32 + ((quarter * 32u) << 16), r);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) r[j] = 0u;
+                        }
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        if (args.bias != nullptr && !partial) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + part * 32 + j < args.n) v[j] += __ldg(args.bias + col + part * 32 + j);
+                        }
+                        if (half_out) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                float8 f;
+                                f.lo = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                f.hi = make_float4(v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
+                                store8(reinterpret_cast<bf16*>(slab + swizzled_chunk(lane, part * 4 + (j >> 3))), f);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(slab + swizzled_chunk(lane, j >> 2)) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0 && rows_inside) tma_store(&map_c, smem_u32(slab), col, upper);
                 }
-                if (row >= args.m) continue;
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                if (args.bias != nullptr && !partial) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col + j < args.n) v[j] += __ldg(args.bias + col + j);
-                }
-                const bool whole = col + 32 <= args.n && args.c_vec;
-                if (half_out) {
-                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.c) + row_at + col;
-                    if (whole) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint4 packed;
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                            packed.x = *reinterpret_cast<uint32_t*>(&p0);
-                            packed.y = *reinterpret_cast<uint32_t*>(&p1);
-                            packed.z = *reinterpret_cast<uint32_t*>(&p2);
-                            packed.w = *reinterpret_cast<uint32_t*>(&p3);
-                            *reinterpret_cast<uint4*>(out + j) = packed;
+            } else {
+#pragma unroll 1
+                for (uint32_t c0 = 0; c0 < static_cast<uint32_t>(BN); c0 += 32) {
+                    const uint32_t col = k.tile_n * BN + c0;
+                    if (col >= args.n) break;  // the same for the whole warp
+                    uint32_t r[32];
+                    if (has_k) {
+                        tmem_load32(tmem_base + acc * BN + c0 + ((quarter * 32u) << 16), r);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    } else {
+    #pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = 0u;  // an empty k range is a zero product
+                    }
+                    if (row >= args.m) continue;
+                    float v[32];
+    #pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (args.bias != nullptr && !partial) {
+    #pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < args.n) v[j] += __ldg(args.bias + col + j);
+                    }
+                    const bool whole = col + 32 <= args.n && args.c_vec;
+                    if (half_out) {
+                        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.c) + row_at + col;
+                        if (whole) {
+    #pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 packed;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                packed.x = *reinterpret_cast<uint32_t*>(&p0);
+                                packed.y = *reinterpret_cast<uint32_t*>(&p1);
+                                packed.z = *reinterpret_cast<uint32_t*>(&p2);
+                                packed.w = *reinterpret_cast<uint32_t*>(&p3);
+                                *reinterpret_cast<uint4*>(out + j) = packed;
+                            }
+                        } else {
+    #pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < args.n) out[j] = __float2bfloat16_rn(v[j]);
                         }
                     } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < args.n) out[j] = __float2bfloat16_rn(v[j]);
-                    }
-                } else {
-                    float* out = static_cast<float*>(args.c) + row_at + col;
-                    if (whole) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < args.n) out[j] = v[j];
+                        float* out = static_cast<float*>(args.c) + row_at + col;
+                        if (whole) {
+    #pragma unroll
+                            for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+    #pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < args.n) out[j] = v[j];
+                        }
                     }
                 }
             }
@@ -309,6 +372,8 @@ matmul_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
         }
+        // The last stores still read this CTA's shared memory.
+        if (lane == 0) tma_store_wait_read<0>();
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -333,7 +398,7 @@ __global__ void splitk_reduce_bf16_kernel(const float* __restrict__ ws, void* __
 }
 
 template <int BN, bool A_MN, bool B_MN>
-void launch(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, const Bf16Args& args, uint32_t blocks) {
+void launch(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const Bf16Args& args, uint32_t blocks) {
     auto kernel = matmul_bf16_kernel<BN, A_MN, B_MN>;
     static std::atomic<int> configured_device{-1};
     int device = 0;
@@ -342,16 +407,17 @@ void launch(cudaStream_t s, const CUtensorMap& map_a, const CUtensorMap& map_b, 
         check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg<BN>::TOTAL)), "matmul_bf16 shared memory");
         configured_device.store(device, std::memory_order_relaxed);
     }
-    kernel<<<blocks, THREADS, Cfg<BN>::TOTAL, s>>>(map_a, map_b, args);
+    kernel<<<blocks, THREADS, Cfg<BN>::TOTAL, s>>>(map_a, map_b, map_c, args);
     check_launch("matmul_bf16");
 }
 
 template <int BN>
-void launch_forms(cudaStream_t s, const CUtensorMap& a, const CUtensorMap& b, const Bf16Args& args, uint32_t blocks, bool a_mn, bool b_mn) {
-    if (a_mn && b_mn) launch<BN, true, true>(s, a, b, args, blocks);
-    else if (a_mn) launch<BN, true, false>(s, a, b, args, blocks);
-    else if (b_mn) launch<BN, false, true>(s, a, b, args, blocks);
-    else launch<BN, false, false>(s, a, b, args, blocks);
+void launch_forms(cudaStream_t s, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const Bf16Args& args, uint32_t blocks, bool a_mn,
+                  bool b_mn) {
+    if (a_mn && b_mn) launch<BN, true, true>(s, a, b, c, args, blocks);
+    else if (a_mn) launch<BN, true, false>(s, a, b, c, args, blocks);
+    else if (b_mn) launch<BN, false, true>(s, a, b, c, args, blocks);
+    else launch<BN, false, false>(s, a, b, c, args, blocks);
 }
 
 int sm_count() {
@@ -435,12 +501,25 @@ void matmul_bf16(cudaStream_t s, const HalfMatrix& a, const HalfMatrix& b, const
                  (partial ? (m * n) % 4 == 0 : (c.stride_outer % unit == 0 && c.stride_inner % unit == 0));
     args.a_order = a_order;
     args.b_order = b_order;
+    // C through TMA stores when its rows can be addressed that way: the result matrices as the
+    // operands are described, the split-k workspace as `splits` dense [m, n] matrices.
+    CUtensorMap map_c = map_a;
+    {
+        const bool float_out = partial || !c.half;
+        HalfMatrix target = {args.c, args.ldc, partial ? m * n : c.stride_outer, partial ? 0 : c.stride_inner, false};
+        if (tma_addressable(target, float_out)) {
+            CoordOrder c_order = {};
+            map_c = encode(target, n, m, partial ? 1 : inner, partial ? p.splits : outer, 32, &c_order, "C", float_out);
+            args.c_order = c_order;
+            args.c_tma = 1;
+        }
+    }
     const uint64_t total = static_cast<uint64_t>(args.m_tiles) * args.n_tiles * problems * p.splits;
     const uint32_t blocks = static_cast<uint32_t>(std::min<uint64_t>(total, static_cast<uint64_t>(sm_count())));
     const bool a_mn = a.transposed, b_mn = !b.transposed;
-    if (p.bn == 256) launch_forms<256>(s, map_a, map_b, args, blocks, a_mn, b_mn);
-    else if (p.bn == 128) launch_forms<128>(s, map_a, map_b, args, blocks, a_mn, b_mn);
-    else launch_forms<64>(s, map_a, map_b, args, blocks, a_mn, b_mn);
+    if (p.bn == 256) launch_forms<256>(s, map_a, map_b, map_c, args, blocks, a_mn, b_mn);
+    else if (p.bn == 128) launch_forms<128>(s, map_a, map_b, map_c, args, blocks, a_mn, b_mn);
+    else launch_forms<64>(s, map_a, map_b, map_c, args, blocks, a_mn, b_mn);
     if (partial && !leave_partials) {
         const uint64_t count = m * n, wanted = (count + 255) / 256;
         splitk_reduce_bf16_kernel<<<static_cast<uint32_t>(std::min<uint64_t>(wanted, 148 * 8)), 256, 0, s>>>(

@@ -90,6 +90,19 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 
+// One box of a 4-dimensional tensor map from shared memory to global memory (what lies outside the
+// tensor is not written), as a bulk group of the issuing thread.
+__device__ __forceinline__ void tma_store(const CUtensorMap* map, uint32_t src, uint32_t x, const uint32_t (&upper)[3]) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(upper[0]), "r"(upper[1]), "r"(upper[2])
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until all but the newest `Pending` store groups of this thread have read their shared memory.
+template <int Pending> __device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(Pending) : "memory");
+}
+
 // Byte offset of the 16-byte chunk `c16` (8 bf16 elements) of row `row` in a tile of 128-byte rows
 // with the 128-byte swizzle TMA writes and tcgen05 reads: 8-row groups of 1024 bytes, the chunk
 // index xor-ed with the row within its group.
@@ -132,11 +145,18 @@ inline EncodeTiled encode_tiled() {
 // The tensor map of one operand as stored: `cols` contiguous elements per row, `rows` rows `pitch`
 // elements apart, `inner` x `outer` such matrices. `box_rows` rows of 64 elements make one load.
 // The three upper dimensions are listed by ascending stride; `order` says where each went.
+// `float_elements`: the matrix holds f32 (a result tile written by a TMA store: 32 elements, 128
+// bytes, a box row) instead of bf16 (64 elements a box row).
+inline bool tma_addressable(const HalfMatrix& x, bool float_elements = false) {
+    const uint64_t unit = float_elements ? 4 : 8;  // elements in 16 bytes
+    return reinterpret_cast<uintptr_t>(x.base) % 16 == 0 && x.pitch % unit == 0 && x.stride_inner % unit == 0 && x.stride_outer % unit == 0;
+}
 inline CUtensorMap encode(const HalfMatrix& x, uint64_t cols, uint64_t rows, uint32_t inner, uint32_t outer, uint32_t box_rows, CoordOrder* order,
-                   const char* what) {
-    if (reinterpret_cast<uintptr_t>(x.base) % 16 != 0 || x.pitch % 8 != 0 || x.stride_inner % 8 != 0 || x.stride_outer % 8 != 0)
+                   const char* what, bool float_elements = false) {
+    if (!tma_addressable(x, float_elements))
         throw std::invalid_argument(std::string("matmul_bf16: operand ") + what +
-                                    " is not a TMA source (base on 16 bytes, pitch and batch strides multiples of 8 elements)");
+                                    " is not a TMA source (base on 16 bytes, pitch and batch strides multiples of 16 bytes)");
+    const uint64_t esize = float_elements ? 4 : 2;
     struct Dim { uint64_t size, stride; int which; };  // which: 0 row, 1 inner, 2 outer
     const uint64_t whole = static_cast<uint64_t>(x.pitch) * rows;
     Dim dims[3] = {{rows, x.pitch, 0}, {inner, inner > 1 ? x.stride_inner : 0, 1}, {outer, outer > 1 ? x.stride_outer : 0, 2}};
@@ -147,15 +167,16 @@ inline CUtensorMap encode(const HalfMatrix& x, uint64_t cols, uint64_t rows, uin
         if (d.size <= 1 && d.which != 0) d.stride = top;
     std::stable_sort(dims, dims + 3, [](const Dim& l, const Dim& r) { return l.stride < r.stride; });
     cuuint64_t gdim[4] = {cols, dims[0].size, dims[1].size, dims[2].size};
-    cuuint64_t gstride[3] = {dims[0].stride * 2, dims[1].stride * 2, dims[2].stride * 2};
-    cuuint32_t box[4] = {64, 1, 1, 1}, estride[4] = {1, 1, 1, 1};
+    cuuint64_t gstride[3] = {dims[0].stride * esize, dims[1].stride * esize, dims[2].stride * esize};
+    cuuint32_t box[4] = {float_elements ? 32u : 64u, 1, 1, 1}, estride[4] = {1, 1, 1, 1};
     for (int d = 0; d < 3; ++d) {
         if (dims[d].which == 0) { order->row = static_cast<uint8_t>(d); box[d + 1] = box_rows; }
         if (dims[d].which == 1) order->inner = static_cast<uint8_t>(d);
         if (dims[d].which == 2) order->outer = static_cast<uint8_t>(d);
     }
     CUtensorMap map;
-    CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(x.base), gdim, gstride, box, estride,
+    CUresult r = encode_tiled()(&map, float_elements ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                                const_cast<void*>(x.base), gdim, gstride, box, estride,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw std::invalid_argument(std::string("matmul_bf16: cuTensorMapEncodeTiled refused operand ") + what + " (" + std::to_string(static_cast<int>(r)) + ")");
