@@ -48,6 +48,11 @@ enum {
     MSX_PLAN_NO_GRAPH = 1,  /* launch kernels one by one instead of through one CUDA graph */
     MSX_PLAN_EXACT_MATMUL = 2, /* matmuls as f32 fused chains in ascending k, the bits of the
                                   reference's CPU loop, instead of 3xTF32 on the tensor cores */
+    MSX_PLAN_GUARD = 8,        /* for tests: every intermediate value keeps storage of its own for the
+                                  whole step (no reuse by liveness), followed by 16 sentinel words
+                                  that msx_plan_check_guards inspects: the guard words the reference's
+                                  device tests keep after every output
+                                  (crates/modelspec-runtime/tests/common/mod.rs:100-117) */
     MSX_PLAN_BF16 = 4          /* mixed precision, an extension: the reference's IR has f32 and i32
                                   only (ir/tensor.rs:38-51). Every rank-2 intermediate (activations
                                   and their adjoints) is stored as bf16 and every product runs as
@@ -75,6 +80,17 @@ typedef struct msx_stats {
                                             reference's counting rule (ir/kernel.rs:1562-1579) */
     uint64_t matmul_flop_per_step;       /* 2 m k n over the step's matmuls */
 } msx_stats;
+
+/* What a plan did, counted as it ran: RunStats of the reference (vulkan/runner.rs:87-131). One
+ * submitted step is one submit (a CUDA graph launch) of `dispatches_per_step` kernels; kernels
+ * of a stream run in order, so there are no barriers to count; `peak_device_bytes` is what the plan
+ * allocated at creation (it allocates nothing afterwards). */
+typedef struct msx_run_stats {
+    uint64_t steps, host_waits, submits, dispatches, dispatches_per_step, barriers_per_step;
+    uint64_t bytes_uploaded, bytes_downloaded, device_allocations, peak_device_bytes;
+    uint32_t tolerance_class;   /* 0 bit-for-bit matmuls (MSX_PLAN_EXACT_MATMUL), 1 tolerance */
+    double elapsed_us;          /* host time from the first submit to the end of the last wait */
+} msx_run_stats;
 
 /* Replaces the device-selection half of vulkan::runner::on_device
  * (crates/modelspec-runtime/src/vulkan/runner.rs:412-436). */
@@ -157,6 +173,25 @@ int msx_sync(msx_plan* plan, uint32_t timeout_ms);
 int msx_value_download(msx_plan* plan, uint32_t value_id, void* host, uint64_t bytes);
 
 int msx_plan_stats(const msx_plan* plan, msx_stats* out);
+int msx_plan_run_stats(const msx_plan* plan, msx_run_stats* out);
+
+/* The lines `train --stats` prints for a device run, field for field as RunStats displays them
+ * (vulkan/runner.rs:143-163: `steps: N`, `host waits: N`, ... `pipeline creation us: T`). Copies at
+ * most `capacity` bytes, NUL-terminated; returns the bytes needed. */
+uint64_t msx_stats_report(const msx_plan* plan, char* out, uint64_t capacity);
+
+/* The lines `train --profile` prints (Profile::report, vulkan/profile.rs:237-338): one
+ * `profile dispatch <plan> <position> <kernel> <entry> calls <n> total_us <t> mean_us <m> flop <f>
+ * bytes <b> gflop_per_s <g> gb_per_s <h>` line per launch of `plan` (named `step`) and, when not
+ * null, of `final_plan` (named `final`), the counters of the run as `profile <counter> <value>`
+ * lines, and `profile step_total ...`. The times come from msx_profile_step_repeated (a real
+ * step runs on each plan; `repeats` as there). Returns 0 on failure (message in msx_last_error). */
+uint64_t msx_profile_report(msx_plan* plan, msx_plan* final_plan, uint32_t repeats, char* out, uint64_t capacity);
+
+/* For a plan made with MSX_PLAN_GUARD: waits for the submitted steps and checks the 16 sentinel
+ * words after every intermediate value and scratch area. MSX_LAUNCH_FAILED names the first value
+ * whose guard a kernel overwrote and the launch that last wrote that value. */
+int msx_plan_check_guards(msx_plan* plan);
 
 /* One line per scheduled kernel: `<index> <kernel> <value> reads ... writes ...`, the CUDA
  * counterpart of the `plan step` listing of `modelspec ir --stage kernel` (ir/print.rs:226-266).
@@ -290,6 +325,17 @@ int msx_training_loss(msx_training* training, float* loss);
 /* The final loss line: the forward program, dropout the identity, on the current parameters and
  * the current batch. */
 int msx_training_final_loss(msx_training* training, float* loss);
+
+/* `infer --backend cuda`: the forward program, dropout the identity, on the current parameters and
+ * the current batch, as the reference runs the loss steps of its plan once on the device
+ * (vulkan/runner.rs:381-386; cli/src/infer.rs:1-60). `prediction` receives the output of the one
+ * `model.forward(...)` call, row-major (msx_training_prediction_count elements), `loss` the loss of
+ * the batch. msx_training_infer_report formats the two lines the CLI prints:
+ * `prediction: <type> = [v, ...]` and `loss <v>`, numbers as Rust displays an f32
+ * (infer.rs:251-262); returns the bytes needed, 0 on failure. */
+uint64_t msx_training_prediction_count(const msx_training* training);
+int msx_training_infer(msx_training* training, float* prediction, uint64_t bytes, float* loss);
+uint64_t msx_training_infer_report(msx_training* training, char* out, uint64_t capacity);
 
 /* E-TRAIN-001 over the state: MSX_NON_FINITE naming the first parameter or moment that holds a
  * NaN or an infinity. Reads every parameter back; call it at the cadence the host can afford. */

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libmsx.so")
 
 OK, BAD_ARGUMENT, NO_DEVICE, OUT_OF_MEMORY, UNSUPPORTED, LAUNCH_FAILED, NON_FINITE, TIMEOUT, BAD_INPUT = range(9)
-PLAN_DEFAULT, PLAN_NO_GRAPH, PLAN_EXACT_MATMUL, PLAN_BF16 = 0, 1, 2, 4
+PLAN_DEFAULT, PLAN_NO_GRAPH, PLAN_EXACT_MATMUL, PLAN_BF16, PLAN_GUARD = 0, 1, 2, 4, 8
 
 STATUS_NAMES = ["MSX_OK", "MSX_BAD_ARGUMENT", "MSX_NO_DEVICE", "MSX_OUT_OF_MEMORY", "MSX_UNSUPPORTED",
                 "MSX_LAUNCH_FAILED", "MSX_NON_FINITE", "MSX_TIMEOUT", "MSX_BAD_INPUT"]
@@ -70,6 +70,7 @@ SIGNATURES = {
     "msx_training_loss_of": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_float)]),
     "msx_value_download": (C.c_int, [_P, C.c_uint32, _P, C.c_uint64]),
     "msx_plan_stats": (C.c_int, [_P, C.POINTER(Stats)]),
+    "msx_plan_check_guards": (C.c_int, [_P]),
     "msx_plan_describe": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
     "msx_schedule_describe": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_uint64]),
     "msx_schedule_describe_with": (C.c_uint64, [C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint64]),
@@ -95,6 +96,12 @@ SIGNATURES = {
     "msx_training_loss": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "msx_training_final_loss": (C.c_int, [_P, C.POINTER(C.c_float)]),
     "msx_training_check_finite": (C.c_int, [_P]),
+    "msx_training_prediction_count": (C.c_uint64, [_P]),
+    "msx_training_infer": (C.c_int, [_P, _P, C.c_uint64, C.POINTER(C.c_float)]),
+    "msx_training_infer_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
+    "msx_plan_run_stats": (C.c_int, [_P, _P]),
+    "msx_stats_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
+    "msx_profile_report": (C.c_uint64, [_P, _P, C.c_uint32, C.c_char_p, C.c_uint64]),
     "msx_op_matmul": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_uint64, C.c_uint64, C.c_uint64, _P, C.c_uint64, _P, _P, C.c_int]),
     "msx_op_matmul_workspace": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
     "msx_op_matmul_bf16": (C.c_int, [_P, C.c_int, _P, C.c_int, _P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, _P, C.c_uint64, _P, _P]),
@@ -279,6 +286,26 @@ class Plan:
     def describe(self):
         return _text(lambda buf, cap: lib().msx_plan_describe(self.h, buf, cap))
 
+    def stats_report(self):
+        """The lines `train --stats` prints for a device run."""
+        return _text(lambda buf, cap: lib().msx_stats_report(self.h, buf, cap))
+
+    def profile_report(self, final_plan=None, repeats=1):
+        """The lines `train --profile` prints: runs one step launch by launch on each plan."""
+        other = final_plan.h if final_plan is not None else None
+        n = lib().msx_profile_report(self.h, other, repeats, None, 0)
+        if n == 0:
+            raise MsxError(LAUNCH_FAILED, self.device.error())
+        # The sizing call ran a step too; the lines of the second call (whose times may print with
+        # a digit more) are the ones returned.
+        buf = C.create_string_buffer(n + 4096)
+        lib().msx_profile_report(self.h, other, repeats, buf, n + 4096)
+        return buf.value.decode()
+
+    def check_guards(self):
+        """For a PLAN_GUARD plan: raises when a kernel wrote past the end of a value."""
+        self.device.check(lib().msx_plan_check_guards(self.h))
+
     def profile_step(self, repeats=1):
         """Runs one step launch by launch (each launch `repeats` times back to back, its time
         divided by `repeats`); returns [(kernel, ms, bytes, flop)] per launch."""
@@ -372,3 +399,20 @@ class Training:
 
     def check_finite(self):
         self.check(lib().msx_training_check_finite(self.h))
+
+    def infer(self):
+        """The forward program on the current parameters and batch: (prediction, loss)."""
+        n = lib().msx_training_prediction_count(self.h)
+        out = np.empty(n, dtype=np.float32)
+        loss = C.c_float()
+        self.check(lib().msx_training_infer(self.h, out.ctypes.data, out.nbytes, C.byref(loss)))
+        return out, np.float32(loss.value)
+
+    def infer_report(self):
+        """The two lines `infer` prints: `prediction: <type> = [...]` and `loss <v>`."""
+        n = lib().msx_training_infer_report(self.h, None, 0)
+        if n == 0:
+            raise MsxError(UNSUPPORTED, lib().msx_training_last_error(self.h).decode())
+        buf = C.create_string_buffer(n)
+        lib().msx_training_infer_report(self.h, buf, n)
+        return buf.value.decode()

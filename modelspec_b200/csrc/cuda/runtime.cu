@@ -13,6 +13,7 @@
 #include <algorithm>
 #include <array>
 #include <chrono>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -38,6 +39,8 @@ namespace k = msx::k;
 namespace {
 
 constexpr uint64_t kAlign = 256;
+constexpr uint64_t kGuardBytes = 64;          // 16 sentinel words after every value of a MSX_PLAN_GUARD plan
+constexpr uint32_t kGuardWord = 0xA5C3A5C3u;
 constexpr int kStagingSlots = 8;  // steps in flight before msx_run waits (the reference's SUBMIT_STEPS)
 
 uint64_t align_up(uint64_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
@@ -160,6 +163,15 @@ struct msx_plan {
     cudaStream_t side_stream = nullptr;              // launches with join_before >= 0 run here
     std::vector<cudaEvent_t> side_fork, side_done;   // per launch (null for launches on the main stream)
     void* d_row_sum_jobs = nullptr;  // k::RowSumJob table of the column sums that share one launch
+
+    // What the plan did, counted as it ran: the fields of the reference's RunStats that have a
+    // meaning here (vulkan/runner.rs:87-131). A step is one submit (a graph launch) of
+    // launches.size() dispatches; barriers are stream order, so none are counted.
+    uint64_t host_waits = 0, submits = 0, dispatches = 0, bytes_uploaded = 0, bytes_downloaded = 0;
+    uint64_t device_allocations = 0, device_bytes = 0;
+    double submitted_ms = 0.0;  // host time from the first submit to the end of the last wait
+    std::chrono::steady_clock::time_point first_submit, last_wait;
+    bool timing_begun = false;
 
     int loss_pos = -1;
     uint64_t steps = 0;
@@ -2106,16 +2118,20 @@ void place_arena(msx_plan* P) {
             if (!slots[s].keep) ends[static_cast<size_t>(slots[s].last)].push_back(s);
             P->unshared_bytes += align_up(slots[s].bytes);
         }
+    // MSX_PLAN_GUARD: every value keeps storage of its own for the whole step, followed by 64
+    // bytes of a sentinel that no kernel may touch (msx_plan_check_guards looks at them).
+    const bool guarded_plan = (P->flags & MSX_PLAN_GUARD) != 0;
     FreeList free;
     for (size_t l = 0; l < P->launches.size(); ++l) {
-        for (uint32_t s : starts[l]) slots[s].offset = free.take(slots[s].bytes);
-        for (uint32_t s : ends[l]) free.give(slots[s].offset, slots[s].bytes);
+        for (uint32_t s : starts[l]) slots[s].offset = free.take(slots[s].bytes + (guarded_plan ? kGuardBytes : 0));
+        if (!guarded_plan)
+            for (uint32_t s : ends[l]) free.give(slots[s].offset, slots[s].bytes);
     }
     P->gradient_region_offset = align_up(free.end);
     uint64_t at = P->gradient_region_offset;
     for (uint32_t g : P->gradient_slots) {
         slots[g].offset = at;
-        at += align_up(slots[g].bytes);
+        at += align_up(slots[g].bytes + (guarded_plan ? kGuardBytes : 0));
         P->unshared_bytes += align_up(slots[g].bytes);
     }
     P->gradient_region_bytes = at - P->gradient_region_offset;
@@ -2147,13 +2163,29 @@ void plan_buckets(msx_plan* P) {
     if (any) P->buckets.push_back(open);
 }
 
+// cudaMalloc for a plan, counted (device_allocations, peak_device_bytes of the run statistics).
+template <class T> cudaError_t plan_malloc(msx_plan* P, T** out, size_t bytes) {
+    cudaError_t e = cudaMalloc(out, bytes);
+    if (e == cudaSuccess) {
+        ++P->device_allocations;
+        P->device_bytes += bytes;
+    }
+    return e;
+}
+
 void allocate(msx_plan* P, const Scheduler& sched) {
     const Program& prog = P->program;
     cuda_ok(cudaStreamCreateWithFlags(&P->stream, cudaStreamNonBlocking), "cudaStreamCreate");
-    cuda_ok(cudaMalloc(&P->arena, P->arena_bytes), "cudaMalloc(arena)");
+    cuda_ok(plan_malloc(P, &P->arena, P->arena_bytes), "cudaMalloc(arena)");
     // The gaps between gradients are summed with them across ranks: keep them finite.
     if (P->gradient_region_bytes)
         cuda_ok(cudaMemset(P->arena + P->gradient_region_offset, 0, P->gradient_region_bytes), "cudaMemset(gradients)");
+    if (P->flags & MSX_PLAN_GUARD) {
+        std::vector<uint32_t> sentinel(kGuardBytes / 4, kGuardWord);
+        for (const Slot& s : P->slots)
+            if (s.kind == Slot::Arena && s.first >= 0)
+                cuda_ok(cudaMemcpy(P->arena + s.offset + (s.bytes + 3) / 4 * 4, sentinel.data(), kGuardBytes, cudaMemcpyHostToDevice), "cudaMemcpy(guard)");
+    }
     std::vector<char> param_used(prog.params.size(), 0), moment_used(prog.params.size(), 0);
     for (const Slot& s : P->slots) {
         if (s.kind == Slot::Param) param_used[s.index] = 1;
@@ -2171,7 +2203,7 @@ void allocate(msx_plan* P, const Scheduler& sched) {
             if (shared) {
                 P->params[p] = shared;
             } else {
-                cuda_ok(cudaMalloc(&P->params[p], bytes), "cudaMalloc(parameter)");
+                cuda_ok(plan_malloc(P, &P->params[p], bytes), "cudaMalloc(parameter)");
                 cuda_ok(cudaMemset(P->params[p], 0, bytes), "cudaMemset(parameter)");
                 P->owns_param[p] = 1;
                 P->param_bytes += bytes;
@@ -2188,22 +2220,22 @@ void allocate(msx_plan* P, const Scheduler& sched) {
             if (shared16) {
                 P->params16[p] = shared16;
             } else {
-                cuda_ok(cudaMalloc(&P->params16[p], bytes / 2), "cudaMalloc(parameter working copy)");
+                cuda_ok(plan_malloc(P, &P->params16[p], bytes / 2), "cudaMalloc(parameter working copy)");
                 P->owns_param16[p] = 1;
                 P->param_bytes += bytes / 2;
                 k::working_copy(P->stream, P->params[p], P->params16[p], prog.params[p].ty.count());
             }
         }
         if (moment_used[p]) {
-            cuda_ok(cudaMalloc(&P->m[p], bytes), "cudaMalloc(moment)");
-            cuda_ok(cudaMalloc(&P->v[p], bytes), "cudaMalloc(moment)");
+            cuda_ok(plan_malloc(P, &P->m[p], bytes), "cudaMalloc(moment)");
+            cuda_ok(plan_malloc(P, &P->v[p], bytes), "cudaMalloc(moment)");
             cuda_ok(cudaMemset(P->m[p], 0, bytes), "cudaMemset(moment)");
             cuda_ok(cudaMemset(P->v[p], 0, bytes), "cudaMemset(moment)");
             P->param_bytes += 2 * bytes;
         }
     }
     uint64_t in_bytes = std::max<uint64_t>(P->input_bytes, kAlign);
-    cuda_ok(cudaMalloc(&P->d_inputs, in_bytes), "cudaMalloc(inputs)");
+    cuda_ok(plan_malloc(P, &P->d_inputs, in_bytes), "cudaMalloc(inputs)");
     cuda_ok(cudaMemset(P->d_inputs, 0, in_bytes), "cudaMemset(inputs)");
     P->blob.assign(in_bytes, 0);
     for (int s = 0; s < kStagingSlots; ++s) {
@@ -2215,13 +2247,13 @@ void allocate(msx_plan* P, const Scheduler& sched) {
     cuda_ok(cudaMallocHost(&P->pinned_status, kStagingSlots * sizeof(uint32_t)), "cudaMallocHost(status)");
     std::memset(P->pinned_status, 0, kStagingSlots * sizeof(uint32_t));
     uint64_t const_bytes = std::max<uint64_t>(P->consts.size() * 4, 4);
-    cuda_ok(cudaMalloc(&P->d_consts, const_bytes), "cudaMalloc(constants)");
+    cuda_ok(plan_malloc(P, &P->d_consts, const_bytes), "cudaMalloc(constants)");
     if (!P->consts.empty())
         cuda_ok(cudaMemcpy(P->d_consts, P->consts.data(), P->consts.size() * 4, cudaMemcpyHostToDevice), "cudaMemcpy(constants)");
-    cuda_ok(cudaMalloc(&P->d_status, 4), "cudaMalloc(status)");
+    cuda_ok(plan_malloc(P, &P->d_status, 4), "cudaMalloc(status)");
     cuda_ok(cudaMemset(P->d_status, 0, 4), "cudaMemset(status)");
     uint64_t counter_bytes = std::max<uint64_t>(P->counters_used, 1) * 4;
-    cuda_ok(cudaMalloc(&P->d_counters, counter_bytes), "cudaMalloc(counters)");
+    cuda_ok(plan_malloc(P, &P->d_counters, counter_bytes), "cudaMalloc(counters)");
     cuda_ok(cudaMemset(P->d_counters, 0, counter_bytes), "cudaMemset(counters)");
     cuda_ok(cudaEventCreate(&P->clock_start), "cudaEventCreate");
     cuda_ok(cudaEventCreate(&P->clock_stop), "cudaEventCreate");
@@ -2241,7 +2273,7 @@ void allocate(msx_plan* P, const Scheduler& sched) {
                                           d.ld, first_block));
             first_block += k::row_sum_job_blocks(d.rows, d.width);
         }
-        cuda_ok(cudaMalloc(&P->d_row_sum_jobs, jobs.size() * sizeof(k::RowSumJob)), "cudaMalloc(row sum jobs)");
+        cuda_ok(plan_malloc(P, &P->d_row_sum_jobs, jobs.size() * sizeof(k::RowSumJob)), "cudaMalloc(row sum jobs)");
         cuda_ok(cudaMemcpy(P->d_row_sum_jobs, jobs.data(), jobs.size() * sizeof(k::RowSumJob), cudaMemcpyHostToDevice), "cudaMemcpy(row sum jobs)");
     }
     if (!sched.deferred.empty()) {
@@ -2257,7 +2289,7 @@ void allocate(msx_plan* P, const Scheduler& sched) {
             first_block += k::sum_job_blocks(d.chunks, d.width);
             jobs.push_back(job);
         }
-        cuda_ok(cudaMalloc(&P->d_sum_jobs, jobs.size() * sizeof(k::SumJob)), "cudaMalloc(sum jobs)");
+        cuda_ok(plan_malloc(P, &P->d_sum_jobs, jobs.size() * sizeof(k::SumJob)), "cudaMalloc(sum jobs)");
         cuda_ok(cudaMemcpy(P->d_sum_jobs, jobs.data(), jobs.size() * sizeof(k::SumJob), cudaMemcpyHostToDevice), "cudaMemcpy(sum jobs)");
     }
     if (!sched.updates.empty()) {
@@ -2274,7 +2306,7 @@ void allocate(msx_plan* P, const Scheduler& sched) {
         }
         size_t table_bytes = tensors.size() * sizeof(k::UpdateTensor);
         size_t chunk_bytes = sched.update_chunk_tensor.size() * 4;
-        cuda_ok(cudaMalloc(&P->d_update_tables, table_bytes + 2 * chunk_bytes), "cudaMalloc(update tables)");
+        cuda_ok(plan_malloc(P, &P->d_update_tables, table_bytes + 2 * chunk_bytes), "cudaMalloc(update tables)");
         char* base = static_cast<char*>(P->d_update_tables);
         cuda_ok(cudaMemcpy(base, tensors.data(), table_bytes, cudaMemcpyHostToDevice), "cudaMemcpy(update tables)");
         cuda_ok(cudaMemcpy(base + table_bytes, sched.update_chunk_tensor.data(), chunk_bytes, cudaMemcpyHostToDevice), "cudaMemcpy");
@@ -2534,6 +2566,11 @@ void check_status(msx_plan* P, int slot) {
 }
 
 int wait_all(msx_plan* P, uint32_t timeout_ms) {
+    ++P->host_waits;
+    struct Stamp {
+        msx_plan* plan;
+        ~Stamp() { plan->last_wait = std::chrono::steady_clock::now(); }
+    } stamp{P};
     if (P->steps == 0) {
         cuda_ok(cudaStreamSynchronize(P->stream), "cudaStreamSynchronize");
         return MSX_OK;
@@ -2716,6 +2753,7 @@ static int transfer(msx_plan* plan, float* device_ptr, uint64_t expect, void* ho
         cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
         if (upload) cuda_ok(cudaMemcpyAsync(device_ptr, host, bytes, cudaMemcpyHostToDevice, plan->stream), what);
         else cuda_ok(cudaMemcpyAsync(host, device_ptr, bytes, cudaMemcpyDeviceToHost, plan->stream), what);
+        (upload ? plan->bytes_uploaded : plan->bytes_downloaded) += bytes;
         cuda_ok(cudaStreamSynchronize(plan->stream), what);
         return MSX_OK;
     });
@@ -2791,7 +2829,15 @@ int msx_run(msx_plan* plan) {
         }
         if (plan->clock_steps == 0) cuda_ok(cudaEventRecord(plan->clock_start, plan->stream), "cudaEventRecord");
         cuda_ok(cudaEventRecord(plan->slot_begin[slot], plan->stream), "cudaEventRecord");
+        if (!plan->timing_begun) {
+            plan->timing_begun = true;
+            plan->first_submit = plan->last_wait = std::chrono::steady_clock::now();
+        }
+        ++plan->submits;
+        plan->dispatches += plan->launches.size();
+        plan->bytes_downloaded += (plan->loss_pos >= 0 ? 4 : 0) + 4;
         if (plan->input_bytes && plan->blob_dirty) {
+            plan->bytes_uploaded += plan->input_bytes;
             plan->blob_dirty = false;
             std::memcpy(plan->pinned[slot], plan->blob.data(), plan->input_bytes);
             cuda_ok(cudaMemcpyAsync(plan->d_inputs, plan->pinned[slot], plan->input_bytes, cudaMemcpyHostToDevice, plan->stream),
@@ -2994,6 +3040,31 @@ int msx_value_download(msx_plan* plan, uint32_t value_id, void* host, uint64_t b
     });
 }
 
+int msx_plan_check_guards(msx_plan* plan) {
+    if (!plan) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        if (!(plan->flags & MSX_PLAN_GUARD)) throw StatusError(MSX_BAD_ARGUMENT, "msx_plan_check_guards: the plan was not made with MSX_PLAN_GUARD");
+        int rc = wait_all(plan, 0);
+        if (rc != MSX_OK) return rc;
+        std::vector<uint32_t> words(kGuardBytes / 4);
+        for (uint32_t at = 0; at < plan->slots.size(); ++at) {
+            const Slot& s = plan->slots[at];
+            if (s.kind != Slot::Arena || s.first < 0) continue;
+            cuda_ok(cudaMemcpy(words.data(), plan->arena + s.offset + (s.bytes + 3) / 4 * 4, kGuardBytes, cudaMemcpyDeviceToHost), "cudaMemcpy(guard)");
+            for (size_t w = 0; w < words.size(); ++w)
+                if (words[w] != kGuardWord) {
+                    const std::string name = at < plan->program.nodes.size() ? "%" + std::to_string(plan->program.nodes[at].id)
+                                                                             : "scratch" + std::to_string(at - plan->program.nodes.size());
+                    std::string writer = "?";
+                    if (s.last_write >= 0) writer = plan->launches[static_cast<size_t>(s.last_write)].kernel;
+                    throw StatusError(MSX_LAUNCH_FAILED, "guard word " + std::to_string(w) + " after " + name + " (" + std::to_string(s.bytes) +
+                                                             " bytes, last written by " + writer + ") was overwritten");
+                }
+        }
+        return MSX_OK;
+    });
+}
+
 int msx_plan_stats(const msx_plan* plan, msx_stats* out) {
     if (!plan || !out) return MSX_BAD_ARGUMENT;
     std::memset(out, 0, sizeof *out);
@@ -3013,6 +3084,123 @@ int msx_plan_stats(const msx_plan* plan, msx_stats* out) {
         if (l.kernel == "sgd_multi_tensor") out->algorithmic_bytes_per_step += l.flop / 2 * 8;
     }
     return MSX_OK;
+}
+
+namespace {
+uint64_t copy_text(const std::string& text, char* out, uint64_t capacity) {
+    if (out && capacity) {
+        size_t n = std::min<size_t>(capacity - 1, text.size());
+        std::memcpy(out, text.data(), n);
+        out[n] = 0;
+    }
+    return text.size() + 1;
+}
+std::string fixed3(double v) {
+    char buf[64];
+    std::snprintf(buf, sizeof buf, "%.3f", v);
+    return buf;
+}
+}  // namespace
+
+int msx_plan_run_stats(const msx_plan* plan, msx_run_stats* out) {
+    if (!plan || !out) return MSX_BAD_ARGUMENT;
+    std::memset(out, 0, sizeof *out);
+    out->steps = plan->steps;
+    out->host_waits = plan->host_waits;
+    out->submits = plan->submits;
+    out->dispatches = plan->dispatches;
+    out->dispatches_per_step = plan->launches.size();
+    out->barriers_per_step = 0;
+    out->bytes_uploaded = plan->bytes_uploaded;
+    out->bytes_downloaded = plan->bytes_downloaded;
+    out->device_allocations = plan->device_allocations;
+    out->peak_device_bytes = plan->device_bytes;
+    out->tolerance_class = (plan->flags & MSX_PLAN_EXACT_MATMUL) ? 0u : 1u;
+    out->elapsed_us = plan->timing_begun ? std::chrono::duration<double, std::micro>(plan->last_wait - plan->first_submit).count() : 0.0;
+    return MSX_OK;
+}
+
+uint64_t msx_stats_report(const msx_plan* plan, char* out, uint64_t capacity) {
+    msx_run_stats s;
+    if (msx_plan_run_stats(plan, &s) != MSX_OK) return 0;
+    // The lines of `train --stats`, field for field (vulkan/runner.rs:143-163). A CUDA plan has no
+    // pipelines to create: its kernels are compiled into the library.
+    std::string text;
+    text += "steps: " + std::to_string(s.steps) + "\n";
+    text += "host waits: " + std::to_string(s.host_waits) + "\n";
+    text += "submits: " + std::to_string(s.submits) + "\n";
+    text += "dispatches: " + std::to_string(s.dispatches) + "\n";
+    text += "dispatches per step: " + std::to_string(s.dispatches_per_step) + "\n";
+    text += "barriers per step: " + std::to_string(s.barriers_per_step) + "\n";
+    text += "bytes uploaded: " + std::to_string(s.bytes_uploaded) + "\n";
+    text += "bytes downloaded: " + std::to_string(s.bytes_downloaded) + "\n";
+    text += "device allocations: " + std::to_string(s.device_allocations) + "\n";
+    text += "peak device bytes: " + std::to_string(s.peak_device_bytes) + "\n";
+    text += std::string("numerics class: ") + (s.tolerance_class ? "tolerance" : "bit-for-bit") + "\n";
+    text += "us per step: " + fixed3(s.steps ? s.elapsed_us / static_cast<double>(s.steps) : 0.0) + "\n";
+    text += "pipelines: 0\n";
+    text += "pipeline creation us: 0.000\n";
+    return copy_text(text, out, capacity);
+}
+
+uint64_t msx_profile_report(msx_plan* plan, msx_plan* final_plan, uint32_t repeats, char* out, uint64_t capacity) {
+    if (!plan) return 0;
+    std::string text;
+    int rc = guarded(plan->device, [&]() -> int {
+        // One `profile dispatch` line per launch of the step plan, then of the final-loss plan, in
+        // the reference's format (vulkan/profile.rs:237-338): the kernel's number is its rank among
+        // the plan's distinct kernels, its entry the kernel's name.
+        double step_us = 0.0;
+        unsigned long long step_flop = 0, step_bytes = 0;
+        for (msx_plan* which : {plan, final_plan}) {
+            if (!which) continue;
+            std::vector<float> ms(which->launches.size());
+            int r = msx_profile_step_repeated(which, repeats ? repeats : 1, ms.data(), static_cast<uint32_t>(ms.size()));
+            if (r != MSX_OK) return r;
+            std::vector<std::string> kernels;
+            for (size_t l = 0; l < which->launches.size(); ++l) {
+                const Launch& launch = which->launches[l];
+                size_t id = std::find(kernels.begin(), kernels.end(), launch.kernel) - kernels.begin();
+                if (id == kernels.size()) kernels.push_back(launch.kernel);
+                const double us = static_cast<double>(ms[l]) * 1e3;
+                const unsigned long long flop = msx_launch_flop(which, static_cast<uint32_t>(l)), bytes = msx_launch_bytes(which, static_cast<uint32_t>(l));
+                text += std::string("profile dispatch ") + (which == plan ? "step " : "final ") + std::to_string(l) + " " + std::to_string(id) + " " +
+                        launch.kernel + " calls 1 total_us " + fixed3(us) + " mean_us " + fixed3(us) + " flop " + std::to_string(flop) + " bytes " +
+                        std::to_string(bytes);
+                if (us > 0.0) text += " gflop_per_s " + fixed3(static_cast<double>(flop) / us / 1e3) + " gb_per_s " + fixed3(static_cast<double>(bytes) / us / 1e3);
+                else text += " gflop_per_s unavailable gb_per_s unavailable";
+                text += "\n";
+                if (which == plan) {
+                    step_us += us;
+                    step_flop += flop;
+                    step_bytes += bytes;
+                }
+            }
+        }
+        text += "profile pipeline statistics: not reported\n";
+        msx_run_stats s;
+        msx_plan_run_stats(plan, &s);
+        text += "profile dispatches " + std::to_string(s.dispatches) + "\n";
+        text += "profile submits " + std::to_string(s.submits) + "\n";
+        text += "profile host_waits " + std::to_string(s.host_waits) + "\n";
+        text += "profile barriers_per_step " + std::to_string(s.barriers_per_step) + "\n";
+        text += "profile bytes_uploaded " + std::to_string(s.bytes_uploaded) + "\n";
+        text += "profile bytes_downloaded " + std::to_string(s.bytes_downloaded) + "\n";
+        text += "profile device_allocations " + std::to_string(s.device_allocations) + "\n";
+        text += "profile peak_device_bytes " + std::to_string(s.peak_device_bytes) + "\n";
+        text += "profile pipeline_creation_us 0.000\n";
+        text += "profile compile_us 0.000\n";
+        // The steady time of a step: the profiled launches one after another (the graph replay of a
+        // step is shorter: msx_elapsed_ms, msx_step_ms).
+        text += "profile steady_us_per_step " + fixed3(step_us) + "\n";
+        text += "profile step_total flop " + std::to_string(step_flop) + " bytes " + std::to_string(step_bytes);
+        if (step_us > 0.0) text += " gflop_per_s " + fixed3(static_cast<double>(step_flop) / step_us / 1e3) + " gb_per_s " + fixed3(static_cast<double>(step_bytes) / step_us / 1e3);
+        else text += " gflop_per_s unavailable gb_per_s unavailable";
+        text += " uncounted_sites 0\n";
+        return MSX_OK;
+    });
+    if (rc != MSX_OK) return 0;
+    return copy_text(text, out, capacity);
 }
 
 uint64_t msx_plan_describe(const msx_plan* plan, char* out, uint64_t capacity) {

@@ -23,6 +23,8 @@ struct msx_training {
     msx::Compiled compiled;
     msx_plan* step = nullptr;
     msx_plan* forward = nullptr;
+    msx_plan* infer = nullptr;  // the forward program with the prediction as a second output, made on first use
+    uint32_t flags = 0;
     std::string error;
     std::map<std::string, std::vector<char>> batch;  // declared inputs and targets, by name
     std::vector<std::string> sites;                  // dropout token inputs of the step
@@ -116,6 +118,7 @@ int msx_training_create(msx_device* device, const char* source, uint64_t masked_
     *out = nullptr;
     msx_training* t = new msx_training;
     t->device = device;
+    t->flags = flags;
     int rc = guarded(t, [&] {
         try {
             t->compiled = msx::compile_training(source, masked_rows);
@@ -154,6 +157,7 @@ int msx_training_create(msx_device* device, const char* source, uint64_t masked_
 
 void msx_training_destroy(msx_training* t) {
     if (!t) return;
+    if (t->infer) msx_plan_destroy(t->infer);
     if (t->forward) msx_plan_destroy(t->forward);
     if (t->step) msx_plan_destroy(t->step);
     delete t;
@@ -314,6 +318,56 @@ int msx_training_final_loss(msx_training* t, float* loss) {
         ok(t, msx_run(t->forward));
         ok(t, msx_loss(t->forward, loss, 0));
     });
+}
+
+uint64_t msx_training_prediction_count(const msx_training* t) {
+    return t ? t->compiled.forward.node(t->compiled.prediction).ty.count() : 0;
+}
+
+int msx_training_infer(msx_training* t, float* prediction, uint64_t bytes, float* loss) {
+    if (!t || !prediction || !loss) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        if (bytes != msx_training_prediction_count(t) * 4)
+            throw Fail{MSX_BAD_ARGUMENT, "the prediction is " + c.forward.node(c.prediction).ty.str() + ": " +
+                                             std::to_string(msx_training_prediction_count(t) * 4) + " bytes"};
+        if (!t->infer) {
+            // The forward program (dropout the identity) with the model's output kept beside the
+            // loss, on the run's parameter buffers.
+            msx::Program program = c.forward;
+            program.outputs.push_back(msx::Output{c.prediction, msx::Role::Plain, 0, 0});
+            std::string ir = msx::print_program(program);
+            ok(t, msx_plan_create(t->device, ir.c_str(), c.config.seed, t->flags, t->step, &t->infer));
+        }
+        ok(t, msx_sync(t->step, 0));
+        gather_masked(t, c.config.steps, false);
+        stage_batch(t, t->infer, input_names(t->infer));
+        ok(t, msx_run(t->infer));
+        ok(t, msx_loss(t->infer, loss, 0));
+        ok(t, msx_value_download(t->infer, c.prediction, prediction, bytes));
+    });
+}
+
+uint64_t msx_training_infer_report(msx_training* t, char* out, uint64_t capacity) {
+    if (!t) return 0;
+    std::string text;
+    std::vector<float> prediction(msx_training_prediction_count(t));
+    float loss = 0.0f;
+    if (msx_training_infer(t, prediction.data(), prediction.size() * 4, &loss) != MSX_OK) return 0;
+    // `prediction: <type> = [v, ...]` and `loss <v>`, floats as Rust's Display prints them
+    // (crates/modelspec-cli/src/infer.rs:251-262).
+    text = "prediction: " + t->compiled.forward.node(t->compiled.prediction).ty.str() + " = [";
+    for (size_t i = 0; i < prediction.size(); ++i) {
+        if (i) text += ", ";
+        text += msx::f32_display(prediction[i]);
+    }
+    text += "]\nloss " + msx::f32_display(loss) + "\n";
+    if (out && capacity) {
+        size_t n = std::min<size_t>(capacity - 1, text.size());
+        std::memcpy(out, text.data(), n);
+        out[n] = 0;
+    }
+    return text.size() + 1;
 }
 
 int msx_training_check_finite(msx_training* t) {

@@ -52,7 +52,8 @@ def run_both(device, text, inputs, params=(), outputs=(), seed=None, flags=M.PLA
     """Evaluates `text` on the oracle and on the GPU; returns [(oracle, gpu)] per output id,
     `outputs` being (value id, element count) pairs."""
     session = oracle_lib.Session(text)
-    plan = M.Plan(device, text, seed=seed or 0, flags=flags)
+    # Every op-level run keeps guard words after each value and checks them afterwards.
+    plan = M.Plan(device, text, seed=seed or 0, flags=flags | M.PLAN_GUARD)
     try:
         for name, value in inputs.items():
             session.set_input(name, value)
@@ -65,6 +66,7 @@ def run_both(device, text, inputs, params=(), outputs=(), seed=None, flags=M.PLA
         session.run()
         plan.run()
         plan.sync()
+        plan.check_guards()
         return [(session.value(v, n).astype(np.float32), plan.value(v, n)) for v, n in outputs]
     finally:
         plan.destroy()
@@ -126,6 +128,9 @@ def train_both(device, source, steps, masked_rows=0, feed=None, synthetic=False,
         cpu_losses.append(cpu.final_loss())
         gpu_losses.append(gpu.final_loss())
         paths = cpu.param_paths()
+        if flags & M.PLAN_GUARD:
+            gpu.step_plan.check_guards()
+            gpu.forward_plan.check_guards()
         out = {"paths": paths, "cpu_losses": np.array(cpu_losses, dtype=np.float32),
                "gpu_losses": np.array(gpu_losses, dtype=np.float32), "cpu_params": [], "gpu_params": [],
                "stats": gpu.step_plan.stats()}

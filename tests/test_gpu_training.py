@@ -177,6 +177,18 @@ def test_exact_matmul_mode_tracks_the_cpu_more_closely(device):
     assert np.abs(exact["gpu_losses"] - exact["cpu_losses"]).max() <= 2e-6 * np.abs(exact["cpu_losses"]).max()
 
 
+@pytest.mark.parametrize("flags", [M.PLAN_GUARD, M.PLAN_GUARD | M.PLAN_BF16])
+def test_no_kernel_of_a_bert_step_writes_past_its_values(device, flags):
+    """The BERT twin with every intermediate in storage of its own and 16 guard words behind it
+    (as the reference's device tests keep after every output): five steps and the final loss,
+    f32 and mixed precision, then every guard is still intact."""
+    source = models.bert(name="BertTiny", hidden=32, heads=2, ffn=64, vocab=300, seq=16, batch=8, steps=5, warmup_steps=1)
+    out = train_both(device, source, 5, masked_rows=64, feed=bert_feed(300, 16, 8), flags=flags)
+    assert np.isfinite(out["gpu_losses"]).all()
+    if not flags & M.PLAN_BF16:
+        check_run(out, "guarded bert twin", key_bias_atol=1e-4 + 5 * 1e-4 * 1e-3)
+
+
 def test_graph_and_direct_launches_agree_in_bits(device):
     source = models.bert(name="BertTiny", hidden=32, heads=2, ffn=64, vocab=300, seq=16, batch=8, steps=5, warmup_steps=1)
     runs = [train_both(device, source, 5, masked_rows=64, feed=bert_feed(300, 16, 8), flags=flags)
