@@ -337,6 +337,46 @@ uint64_t msx_training_prediction_count(const msx_training* training);
 int msx_training_infer(msx_training* training, float* prediction, uint64_t bytes, float* loss);
 uint64_t msx_training_infer_report(msx_training* training, char* out, uint64_t capacity);
 
+/* ---- held-out evaluation (`--eval-every`) --------------------------------------------------------
+ * Replaces the device side of the reference's held-out evaluation: every batch of the HeldOut
+ * split runs the steps of the plan the prediction is computed from, dropout off, without the loss
+ * sum, and the logits are reduced on the device to the weighted sum of the row losses and the
+ * count of correct rows; one small state comes down per evaluation
+ * (crates/modelspec-runtime/src/vulkan/stepwise.rs:32-46, :1648-1790;
+ * spirv/emit/heldout.rs:1-24; train/eval.rs:167-355).
+ *
+ * The plan-level piece. `logits` names a rank-2 f32 output [rows, classes] of `plan` (a program
+ * whose outputs hold the prediction). The labels and weights of all `batches` batches are
+ * uploaded once (msx_heldout_targets; a label outside the classes is MSX_BAD_INPUT with the
+ * reference's message, train/eval.rs:86-93) and stay on the device. An evaluation is
+ * msx_heldout_begin, then for every batch in order: msx_set_input of its tensors, msx_run,
+ * msx_heldout_add (all without a host wait), then msx_heldout_sums, the evaluation's one wait.
+ * `numerator` is the f64 sum over every row, in batch and row order, of f64(weight) x f64(nll)
+ * with nll = max + ln(sum exp(x - max)) - x[label] in f32 (rows of weight +0 and finite logits add
+ * +0 without their softmax, eval.rs:436-442); `correct` counts the rows of positive weight whose
+ * first largest logit (the lowest class among ties) is their label in a row without a NaN. */
+typedef struct msx_heldout msx_heldout;
+int msx_heldout_create(msx_plan* plan, uint32_t logits, uint32_t batches, msx_heldout** out);
+void msx_heldout_destroy(msx_heldout* heldout);
+int msx_heldout_targets(msx_heldout* heldout, uint32_t batch, const int32_t* labels, const float* weights, uint64_t rows);
+int msx_heldout_begin(msx_heldout* heldout);
+int msx_heldout_add(msx_heldout* heldout, uint32_t batch);
+int msx_heldout_sums(msx_heldout* heldout, double* numerator, uint64_t* correct, uint32_t timeout_ms);
+
+/* The whole evaluation of a training run. msx_training_heldout_begin declares `batches` held-out
+ * batches and names the declared tensors that hold each row's label (i32) and weight (f32), which
+ * the reduction reads whether or not the prediction depends on them; the prediction must be f32
+ * logits [rows, V], one row per label (the reference's EvalError::Prediction otherwise).
+ * msx_training_heldout_set gives batch `batch` its declared tensor `name` (every declared input the
+ * prediction reads, and the labels and weights); the batches are drawn once per run and read by
+ * every evaluation. msx_training_heldout_evaluate evaluates the current parameters:
+ * loss = f32(numerator / sum of the weights), both whole-split f64 sums, 0 when the weights sum
+ * to 0; accuracy = correct / selected in f32 over the rows of positive weight, 0 when none is
+ * selected (HeldOut::metrics_of_sums, train/eval.rs:325-355). */
+int msx_training_heldout_begin(msx_training* training, uint32_t batches, const char* labels, const char* weights);
+int msx_training_heldout_set(msx_training* training, uint32_t batch, const char* name, const void* host, uint64_t bytes);
+int msx_training_heldout_evaluate(msx_training* training, float* loss, float* accuracy);
+
 /* E-TRAIN-001 over the state: MSX_NON_FINITE naming the first parameter or moment that holds a
  * NaN or an infinity. Reads every parameter back; call it at the cadence the host can afford. */
 int msx_training_check_finite(msx_training* training);

@@ -99,6 +99,15 @@ SIGNATURES = {
     "msx_training_prediction_count": (C.c_uint64, [_P]),
     "msx_training_infer": (C.c_int, [_P, _P, C.c_uint64, C.POINTER(C.c_float)]),
     "msx_training_infer_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
+    "msx_heldout_create": (C.c_int, [_P, C.c_uint32, C.c_uint32, C.POINTER(_P)]),
+    "msx_heldout_destroy": (None, [_P]),
+    "msx_heldout_targets": (C.c_int, [_P, C.c_uint32, _P, _P, C.c_uint64]),
+    "msx_heldout_begin": (C.c_int, [_P]),
+    "msx_heldout_add": (C.c_int, [_P, C.c_uint32]),
+    "msx_heldout_sums": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.c_uint32]),
+    "msx_training_heldout_begin": (C.c_int, [_P, C.c_uint32, C.c_char_p, C.c_char_p]),
+    "msx_training_heldout_set": (C.c_int, [_P, C.c_uint32, C.c_char_p, _P, C.c_uint64]),
+    "msx_training_heldout_evaluate": (C.c_int, [_P, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "msx_plan_run_stats": (C.c_int, [_P, _P]),
     "msx_stats_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
     "msx_profile_report": (C.c_uint64, [_P, _P, C.c_uint32, C.c_char_p, C.c_uint64]),
@@ -341,6 +350,39 @@ class Plan:
         return total.value, steps.value
 
 
+class HeldOut:
+    """The held-out reduction of a plan's logits on the device (msx_heldout): targets once, then
+    per evaluation begin(), add(batch) after each batch's run, and sums()."""
+
+    def __init__(self, plan, logits, batches):
+        self.plan = plan
+        h = _P()
+        plan.device.check(lib().msx_heldout_create(plan.h, logits, batches, C.byref(h)))
+        self.h = h
+
+    def destroy(self):
+        if self.h:
+            lib().msx_heldout_destroy(self.h)
+            self.h = None
+
+    def targets(self, batch, labels, weights):
+        labels = np.ascontiguousarray(labels, dtype=np.int32)
+        weights = np.ascontiguousarray(weights, dtype=np.float32)
+        self.plan.device.check(lib().msx_heldout_targets(self.h, batch, labels.ctypes.data, weights.ctypes.data, labels.size))
+
+    def begin(self):
+        self.plan.device.check(lib().msx_heldout_begin(self.h))
+
+    def add(self, batch):
+        self.plan.device.check(lib().msx_heldout_add(self.h, batch))
+
+    def sums(self, timeout_ms=0):
+        """(numerator, correct) of the batches added since begin(); the evaluation's one wait."""
+        numerator, correct = C.c_double(), C.c_uint64()
+        self.plan.device.check(lib().msx_heldout_sums(self.h, C.byref(numerator), C.byref(correct), timeout_ms))
+        return float(numerator.value), int(correct.value)
+
+
 class Training:
     """One training run (msx_training): the host loop of `train --backend cuda`."""
 
@@ -407,6 +449,21 @@ class Training:
         loss = C.c_float()
         self.check(lib().msx_training_infer(self.h, out.ctypes.data, out.nbytes, C.byref(loss)))
         return out, np.float32(loss.value)
+
+    def heldout_begin(self, batches, labels, weights):
+        """Declares the held-out split of the run: `batches` batches, and the names of the declared
+        tensors that hold the rows' labels and weights."""
+        self.check(lib().msx_training_heldout_begin(self.h, batches, labels.encode(), weights.encode()))
+
+    def heldout_set(self, batch, name, array):
+        a = np.ascontiguousarray(array)
+        self.check(lib().msx_training_heldout_set(self.h, batch, name.encode(), a.ctypes.data, a.nbytes))
+
+    def heldout_evaluate(self):
+        """The held-out (loss, accuracy) of the current parameters, reduced on the device."""
+        loss, accuracy = C.c_float(), C.c_float()
+        self.check(lib().msx_training_heldout_evaluate(self.h, C.byref(loss), C.byref(accuracy)))
+        return np.float32(loss.value), np.float32(accuracy.value)
 
     def infer_report(self):
         """The two lines `infer` prints: `prediction: <type> = [...]` and `loss <v>`."""

@@ -186,6 +186,20 @@ void cross_entropy_with_grad(cudaStream_t s, In logits, const int32_t* labels, c
                              Out grad, uint64_t rows, uint64_t v, uint32_t* counter = nullptr, uint64_t ld = 0,
                              uint64_t ld_grad = 0);
 
+// ---- held-out reduction (heldout.cu) -----------------------------------------------------------
+// The running sums of one evaluation, all zero before its first batch.
+struct HeldOutState {
+    double numerator;            // sum of f64(w) x f64(nll) over every row so far, in batch and row order
+    unsigned long long correct;  // rows of positive weight whose first largest logit is their label
+    uint32_t started;            // whether the numerator holds a term yet (the first term starts the sum)
+    uint32_t arrived;            // rows of the batch in flight that are done; zero between launches
+};
+// Adds the rows of one batch of logits [rows, classes] (row pitch `pitch` floats, 0 = classes) to
+// `state`: one launch. `terms[rows]` and `hits[rows]` are scratch. A label outside the classes
+// reads class 0: the host refuses such a batch before it is evaluated.
+void heldout_rows(cudaStream_t s, const float* logits, uint64_t pitch, const int32_t* labels, const float* weights, uint64_t rows,
+                  uint64_t classes, double* terms, uint32_t* hits, HeldOutState* state);
+
 // ---- all-reduce over peer memory (peer_reduce.cu) ---------------------------------------------
 // `buffers[q]` is rank q's copy of the same `count` floats (this rank's own for q == rank, the
 // others mapped through CUDA IPC), `flags[q]` rank q's flag words (one per rank, zero before the

@@ -3040,6 +3040,149 @@ int msx_value_download(msx_plan* plan, uint32_t value_id, void* host, uint64_t b
     });
 }
 
+// ---- held-out reduction ---------------------------------------------------------------------
+}  // extern "C"
+
+struct msx_heldout {
+    msx_plan* plan = nullptr;
+    uint32_t at = 0;           // position of the logits in the plan's program
+    uint64_t rows = 0, classes = 0;
+    uint32_t batches = 0;
+    int32_t* d_labels = nullptr;   // [batches][rows], resident for the run
+    float* d_weights = nullptr;    // [batches][rows]
+    double* d_terms = nullptr;     // [rows] scratch
+    uint32_t* d_hits = nullptr;    // [rows] scratch
+    k::HeldOutState* d_state = nullptr;
+    k::HeldOutState* pinned = nullptr;
+    cudaEvent_t done = nullptr;
+    std::vector<char> given;       // which batches have their targets
+    bool begun = false;
+};
+
+extern "C" {
+
+int msx_heldout_create(msx_plan* plan, uint32_t logits, uint32_t batches, msx_heldout** out) {
+    if (!plan || !out) return MSX_BAD_ARGUMENT;
+    *out = nullptr;
+    return guarded(plan->device, [&]() -> int {
+        int at = plan->program.position(logits);
+        if (at < 0) throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_create: %" + std::to_string(logits) + " is not defined");
+        const Slot& s = plan->slots[static_cast<size_t>(at)];
+        const msx::Type& ty = plan->program.nodes[static_cast<size_t>(at)].ty;
+        if (ty.i32 || ty.rank() != 2 || ty.shape[0] == 0 || ty.shape[1] == 0 || ty.count() > 0xffffffffull)
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_create: the logits are " + ty.str() + ", not f32 [rows, classes] of 1 to 2^32 - 1 elements");
+        if (!s.keep || s.kind != Slot::Arena || s.half)
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_create: %" + std::to_string(logits) + " is not an f32 output of the plan");
+        if (batches == 0) throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_create: no batches");
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        std::unique_ptr<msx_heldout> h(new msx_heldout());
+        h->plan = plan;
+        h->at = static_cast<uint32_t>(at);
+        h->rows = ty.shape[0];
+        h->classes = ty.shape[1];
+        h->batches = batches;
+        h->given.assign(batches, 0);
+        const size_t all = static_cast<size_t>(batches) * h->rows;
+        cudaError_t e = plan_malloc(plan, &h->d_labels, all * 4);
+        if (e == cudaSuccess) e = plan_malloc(plan, &h->d_weights, all * 4);
+        if (e == cudaSuccess) e = plan_malloc(plan, &h->d_terms, h->rows * 8);
+        if (e == cudaSuccess) e = plan_malloc(plan, &h->d_hits, h->rows * 4);
+        if (e == cudaSuccess) e = plan_malloc(plan, &h->d_state, sizeof(k::HeldOutState));
+        if (e == cudaSuccess) e = cudaMallocHost(&h->pinned, sizeof(k::HeldOutState));
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->done, cudaEventDisableTiming);
+        if (e != cudaSuccess) {
+            msx_heldout_destroy(h.release());
+            cuda_ok(e, "msx_heldout_create");
+        }
+        *out = h.release();
+        return MSX_OK;
+    });
+}
+
+void msx_heldout_destroy(msx_heldout* h) {
+    if (!h) return;
+    cudaSetDevice(h->plan->device->ordinal);
+    cudaStreamSynchronize(h->plan->stream);
+    cudaFree(h->d_labels);
+    cudaFree(h->d_weights);
+    cudaFree(h->d_terms);
+    cudaFree(h->d_hits);
+    cudaFree(h->d_state);
+    if (h->pinned) cudaFreeHost(h->pinned);
+    if (h->done) cudaEventDestroy(h->done);
+    delete h;
+}
+
+int msx_heldout_targets(msx_heldout* h, uint32_t batch, const int32_t* labels, const float* weights, uint64_t rows) {
+    if (!h || !labels || !weights) return MSX_BAD_ARGUMENT;
+    msx_plan* plan = h->plan;
+    return guarded(plan->device, [&]() -> int {
+        if (batch >= h->batches) throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_targets: batch " + std::to_string(batch) + " of " + std::to_string(h->batches));
+        if (rows != h->rows)
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_targets: held-out batch " + std::to_string(batch) + " has not " + std::to_string(h->rows) + " rows");
+        for (uint64_t n = 0; n < rows; ++n)
+            if (labels[n] < 0 || static_cast<uint64_t>(labels[n]) >= h->classes)
+                throw StatusError(MSX_BAD_INPUT, "held-out batch " + std::to_string(batch) + ", row " + std::to_string(n) + ": label " +
+                                                     std::to_string(labels[n]) + " is not below the " + std::to_string(h->classes) + " classes");
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        // Ordered on the plan's stream behind any evaluation still reading the old targets.
+        cuda_ok(cudaMemcpyAsync(h->d_labels + batch * rows, labels, rows * 4, cudaMemcpyHostToDevice, plan->stream), "cudaMemcpyAsync(labels)");
+        cuda_ok(cudaMemcpyAsync(h->d_weights + batch * rows, weights, rows * 4, cudaMemcpyHostToDevice, plan->stream), "cudaMemcpyAsync(weights)");
+        cuda_ok(cudaStreamSynchronize(plan->stream), "cudaStreamSynchronize");
+        plan->bytes_uploaded += rows * 8;
+        h->given[batch] = 1;
+        return MSX_OK;
+    });
+}
+
+int msx_heldout_begin(msx_heldout* h) {
+    if (!h) return MSX_BAD_ARGUMENT;
+    return guarded(h->plan->device, [&]() -> int {
+        cuda_ok(cudaSetDevice(h->plan->device->ordinal), "cudaSetDevice");
+        cuda_ok(cudaMemsetAsync(h->d_state, 0, sizeof(k::HeldOutState), h->plan->stream), "cudaMemsetAsync(held-out state)");
+        h->begun = true;
+        return MSX_OK;
+    });
+}
+
+int msx_heldout_add(msx_heldout* h, uint32_t batch) {
+    if (!h) return MSX_BAD_ARGUMENT;
+    msx_plan* plan = h->plan;
+    return guarded(plan->device, [&]() -> int {
+        if (!h->begun) throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_add: no evaluation was begun");
+        if (batch >= h->batches || !h->given[batch])
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_add: held-out batch " + std::to_string(batch) + " has no labels and weights");
+        if (plan->steps == 0) throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_add: the plan has not run the batch");
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        k::heldout_rows(plan->stream, static_cast<const float*>(plan->ptr(h->at)), plan->slots[h->at].pitch, h->d_labels + static_cast<size_t>(batch) * h->rows,
+                        h->d_weights + static_cast<size_t>(batch) * h->rows, h->rows, h->classes, h->d_terms, h->d_hits, h->d_state);
+        ++plan->dispatches;
+        return MSX_OK;
+    });
+}
+
+int msx_heldout_sums(msx_heldout* h, double* numerator, uint64_t* correct, uint32_t timeout_ms) {
+    if (!h || !numerator || !correct) return MSX_BAD_ARGUMENT;
+    msx_plan* plan = h->plan;
+    return guarded(plan->device, [&]() -> int {
+        if (!h->begun) throw StatusError(MSX_BAD_ARGUMENT, "msx_heldout_sums: no evaluation was begun");
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        cuda_ok(cudaMemcpyAsync(h->pinned, h->d_state, sizeof(k::HeldOutState), cudaMemcpyDeviceToHost, plan->stream), "cudaMemcpyAsync(held-out state)");
+        cuda_ok(cudaEventRecord(h->done, plan->stream), "cudaEventRecord");
+        int rc = wait_event(h->done, timeout_ms == 0 ? 600000u : timeout_ms);
+        ++plan->host_waits;
+        plan->last_wait = std::chrono::steady_clock::now();
+        if (rc != MSX_OK) return rc;
+        plan->bytes_downloaded += sizeof(k::HeldOutState);
+        // The batches' own steps were waited for with the state: a wait of theirs that gave up shows here.
+        if (plan->steps) check_status(plan, static_cast<int>((plan->steps - 1) % kStagingSlots));
+        *numerator = h->pinned->numerator;
+        *correct = h->pinned->correct;
+        h->begun = false;
+        return MSX_OK;
+    });
+}
+
 int msx_plan_check_guards(msx_plan* plan) {
     if (!plan) return MSX_BAD_ARGUMENT;
     return guarded(plan->device, [&]() -> int {

@@ -24,6 +24,13 @@ struct msx_training {
     msx_plan* step = nullptr;
     msx_plan* forward = nullptr;
     msx_plan* infer = nullptr;  // the forward program with the prediction as a second output, made on first use
+    // Held-out evaluation: the steps the prediction is computed from, the device reduction of its
+    // logits, and the batches of the split, drawn once per run.
+    msx_plan* predict = nullptr;
+    msx_heldout* heldout = nullptr;
+    std::string heldout_labels, heldout_weights;
+    std::vector<std::map<std::string, std::vector<char>>> heldout_batches;
+    std::set<std::string> predict_inputs;
     uint32_t flags = 0;
     std::string error;
     std::map<std::string, std::vector<char>> batch;  // declared inputs and targets, by name
@@ -157,6 +164,8 @@ int msx_training_create(msx_device* device, const char* source, uint64_t masked_
 
 void msx_training_destroy(msx_training* t) {
     if (!t) return;
+    if (t->heldout) msx_heldout_destroy(t->heldout);
+    if (t->predict) msx_plan_destroy(t->predict);
     if (t->infer) msx_plan_destroy(t->infer);
     if (t->forward) msx_plan_destroy(t->forward);
     if (t->step) msx_plan_destroy(t->step);
@@ -337,7 +346,7 @@ int msx_training_infer(msx_training* t, float* prediction, uint64_t bytes, float
             msx::Program program = c.forward;
             program.outputs.push_back(msx::Output{c.prediction, msx::Role::Plain, 0, 0});
             std::string ir = msx::print_program(program);
-            ok(t, msx_plan_create(t->device, ir.c_str(), c.config.seed, t->flags, t->step, &t->infer));
+            ok(t, msx_plan_create(t->device, ir.c_str(), c.config.seed, t->flags, t->forward, &t->infer));
         }
         ok(t, msx_sync(t->step, 0));
         gather_masked(t, c.config.steps, false);
@@ -368,6 +377,99 @@ uint64_t msx_training_infer_report(msx_training* t, char* out, uint64_t capacity
         out[n] = 0;
     }
     return text.size() + 1;
+}
+
+// ---- held-out evaluation (crates/modelspec-runtime/src/train/eval.rs:167-355) ---------------------
+
+int msx_training_heldout_begin(msx_training* t, uint32_t batches, const char* labels, const char* weights) {
+    if (!t || !labels || !weights) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        if (t->heldout) throw Fail{MSX_BAD_ARGUMENT, "the held-out batches of this run are already declared"};
+        if (batches == 0) throw Fail{MSX_BAD_ARGUMENT, "a held-out split of no batch"};
+        const msx::DataDecl *l = declared(t, labels), *w = declared(t, weights);
+        if (!l || !l->ty.i32 || !w || w->ty.i32 || l->ty.count() != w->ty.count())
+            throw Fail{MSX_BAD_ARGUMENT, std::string("`") + labels + "` and `" + weights + "` are not declared i32 labels and f32 weights of one row each"};
+        const uint64_t rows = l->ty.count();
+        // eval.rs:143-163: the prediction is f32 logits [rows, V], one row per position of the batch.
+        const msx::Type& ty = c.forward.node(c.prediction).ty;
+        if (ty.i32 || ty.rank() != 2 || ty.shape[0] != rows || ty.shape[1] == 0)
+            throw Fail{MSX_BAD_ARGUMENT, "--eval-every reads the prediction as f32 logits [" + std::to_string(rows) +
+                                             ", V], one row per position of the batch; the model's prediction is " + ty.str()};
+        // The steps the prediction is computed from, without the loss sum (stepwise.rs:32-35), on the
+        // run's parameter buffers.
+        msx::Program program = c.forward;
+        program.outputs = {msx::Output{c.prediction, msx::Role::Plain, 0, 0}};
+        program = msx::dce(std::move(program));
+        std::string ir = msx::print_program(program);
+        ok(t, msx_plan_create(t->device, ir.c_str(), c.config.seed, t->flags, t->forward, &t->predict));
+        t->predict_inputs = input_names(t->predict);
+        ok(t, msx_heldout_create(t->predict, c.prediction, batches, &t->heldout));
+        t->heldout_labels = labels;
+        t->heldout_weights = weights;
+        t->heldout_batches.assign(batches, {});
+    });
+}
+
+int msx_training_heldout_set(msx_training* t, uint32_t batch, const char* name, const void* host, uint64_t bytes) {
+    if (!t || !name || !host) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        if (!t->heldout) throw Fail{MSX_BAD_ARGUMENT, "no held-out batches are declared"};
+        if (batch >= t->heldout_batches.size())
+            throw Fail{MSX_BAD_ARGUMENT, "held-out batch " + std::to_string(batch) + " of " + std::to_string(t->heldout_batches.size())};
+        const msx::DataDecl* d = declared(t, name);
+        if (!d) throw Fail{MSX_BAD_ARGUMENT, std::string("the train block declares no `") + name + "`"};
+        if (bytes != d->ty.count() * 4)
+            throw Fail{MSX_BAD_ARGUMENT, std::string("`") + name + "` is " + d->ty.str() + ": " + std::to_string(d->ty.count() * 4) + " bytes"};
+        const char* b = static_cast<const char*>(host);
+        auto& held = t->heldout_batches[batch];
+        held[name].assign(b, b + bytes);
+        // Both targets of a batch given: they go to the device, where they stay.
+        auto l = held.find(t->heldout_labels), w = held.find(t->heldout_weights);
+        if ((name == t->heldout_labels || name == t->heldout_weights) && l != held.end() && w != held.end())
+            ok(t, msx_heldout_targets(t->heldout, batch, reinterpret_cast<const int32_t*>(l->second.data()),
+                                      reinterpret_cast<const float*>(w->second.data()), l->second.size() / 4));
+    });
+}
+
+int msx_training_heldout_evaluate(msx_training* t, float* loss, float* accuracy) {
+    if (!t || !loss || !accuracy) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        if (!t->heldout) throw Fail{MSX_BAD_ARGUMENT, "no held-out batches are declared"};
+        // The prediction plan runs on its own stream: the submitted updates first.
+        ok(t, msx_sync(t->step, 0));
+        ok(t, msx_heldout_begin(t->heldout));
+        // HeldOut::metrics_of_sums (eval.rs:325-355): the denominator and the selected rows are the
+        // split's own weights, summed from the first term in batch and row order.
+        bool any = false;
+        double denominator = 0.0;
+        uint64_t selected = 0;
+        for (uint32_t b = 0; b < t->heldout_batches.size(); ++b) {
+            const auto& held = t->heldout_batches[b];
+            for (const std::string& name : t->predict_inputs) {
+                auto it = held.find(name);
+                if (it == held.end()) throw Fail{MSX_BAD_INPUT, "held-out batch " + std::to_string(b) + " holds no `" + name + "`"};
+                ok(t, msx_set_input(t->predict, name.c_str(), it->second.data(), it->second.size()));
+            }
+            auto w = held.find(t->heldout_weights);
+            if (w == held.end() || !held.count(t->heldout_labels))
+                throw Fail{MSX_BAD_INPUT, "held-out batch " + std::to_string(b) + " holds no labels and weights"};
+            ok(t, msx_run(t->predict));
+            ok(t, msx_heldout_add(t->heldout, b));
+            const float* weights = reinterpret_cast<const float*>(w->second.data());
+            for (size_t n = 0; n < w->second.size() / 4; ++n) {
+                const double wide = static_cast<double>(weights[n]);
+                denominator = any ? denominator + wide : wide;
+                any = true;
+                if (weights[n] > 0.0f) ++selected;
+            }
+        }
+        double numerator = 0.0;
+        uint64_t correct = 0;
+        ok(t, msx_heldout_sums(t->heldout, &numerator, &correct, 0));
+        *loss = denominator == 0.0 ? 0.0f : static_cast<float>(numerator / denominator);
+        *accuracy = selected == 0 ? 0.0f : static_cast<float>(correct) / static_cast<float>(selected);
+    });
 }
 
 int msx_training_check_finite(msx_training* t) {

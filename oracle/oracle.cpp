@@ -844,6 +844,86 @@ struct Trainer {
         forward.run(compiled.forward);
         return forward.val(compiled.forward.outputs[0].value)[0];
     }
+
+    // The model's prediction for the current batch on the current parameters, from the forward
+    // program (dropout the identity), as held-out evaluation reads it (train/eval.rs:279-296).
+    std::vector<float> predict() {
+        forward.inputs = inputs;
+        forward.ids = ids;
+        forward.params = params;
+        Program program = compiled.forward;
+        program.outputs = {msx::Output{compiled.prediction, msx::Role::Plain, 0, 0}};
+        forward.run(program);
+        return forward.val(compiled.prediction);
+    }
+};
+
+// The held-out reduction (crates/modelspec-runtime/src/train/eval.rs:409-499): the running sums
+// over every row of every batch, in batch order and then row order.
+struct Tally {
+    bool has_numerator = false, has_denominator = false;
+    double numerator = 0.0, denominator = 0.0;
+    uint64_t correct = 0, selected = 0, softmaxes = 0;
+
+    // eval.rs:490-499: the maximum the first element replaced by each later greater one, the sum
+    // in ascending order from its first term.
+    static float row_nll(const float* row, size_t v, size_t label) {
+        float max = row[0];
+        for (size_t c = 1; c < v; ++c)
+            if (row[c] > max) max = row[c];
+        float total = std::exp(row[0] - max);
+        for (size_t c = 1; c < v; ++c) total = total + std::exp(row[c] - max);
+        return max + std::log(total) - row[label];
+    }
+    // eval.rs:481-484.
+    static bool nll_is_finite(const float* row, size_t v) {
+        bool small = true;
+        for (size_t c = 0; c < v; ++c) small = small & (std::fabs(row[c]) < 5.0e37f);
+        return small;
+    }
+    // train/runner.rs:631-638: the first maximum, or none when the row holds a NaN.
+    static long argmax(const float* row, size_t v) {
+        for (size_t c = 0; c < v; ++c)
+            if (std::isnan(row[c])) return -1;
+        size_t best = 0;
+        for (size_t c = 1; c < v; ++c)
+            if (row[c] > row[best]) best = c;
+        return static_cast<long>(best);
+    }
+    // eval.rs:421-457. `skipping` false is the tally "as it was before it skipped rows"
+    // (eval.rs:514-547), which the reference's tests hold the skipping one to.
+    void add(const float* logits, const int32_t* labels, const float* weights, size_t rows, size_t v, bool skipping) {
+        for (size_t n = 0; n < rows; ++n) {
+            const float* row = logits + n * v;
+            if (labels[n] < 0 || static_cast<size_t>(labels[n]) >= v)
+                throw msx::Error("held-out row " + std::to_string(n) + ": label " + std::to_string(labels[n]) + " is not below the " +
+                                 std::to_string(v) + " classes");
+            const size_t target = static_cast<size_t>(labels[n]);
+            const float weight = weights[n];
+            uint32_t bits;
+            std::memcpy(&bits, &weight, 4);
+            if (skipping && bits == 0 && nll_is_finite(row, v)) {
+                numerator = has_numerator ? numerator + 0.0 : 0.0;
+                denominator = has_denominator ? denominator + 0.0 : 0.0;
+                has_numerator = has_denominator = true;
+                continue;
+            }
+            ++softmaxes;
+            const double wide = static_cast<double>(weight), nll = static_cast<double>(row_nll(row, v, target));
+            numerator = has_numerator ? std::fma(wide, nll, numerator) : wide * nll;
+            denominator = has_denominator ? denominator + wide : wide;
+            has_numerator = has_denominator = true;
+            if (weight > 0.0f) {
+                ++selected;
+                if (argmax(row, v) == static_cast<long>(target)) ++correct;
+            }
+        }
+    }
+    // eval.rs:459-475.
+    void metrics(float* loss, float* accuracy) const {
+        *loss = denominator == 0.0 ? 0.0f : static_cast<float>(numerator / denominator);
+        *accuracy = selected == 0 ? 0.0f : static_cast<float>(correct) / static_cast<float>(selected);
+    }
 };
 
 // A bare program evaluated once, for op-level checks; f32 or f64 arithmetic.
@@ -937,6 +1017,29 @@ int orc_trainer_read(void* h, int which, uint64_t i, float* out, uint64_t n) {
         if (v.size() != n) throw msx::Error("length mismatch");
         std::memcpy(out, v.data(), n * sizeof(float));
     });
+}
+int orc_trainer_predict(void* h, float* out, uint64_t n) {
+    return guarded([&] {
+        std::vector<float> v = static_cast<orc::Trainer*>(h)->predict();
+        if (v.size() != n) throw msx::Error("length mismatch");
+        std::memcpy(out, v.data(), n * sizeof(float));
+    });
+}
+// The held-out tally: create, add batches of logits [rows, classes] in order, read the metrics.
+void* orc_tally_create() { return new orc::Tally(); }
+void orc_tally_destroy(void* h) { delete static_cast<orc::Tally*>(h); }
+int orc_tally_add(void* h, const float* logits, const int32_t* labels, const float* weights, uint64_t rows, uint64_t classes, int skipping) {
+    return guarded([&] { static_cast<orc::Tally*>(h)->add(logits, labels, weights, rows, classes, skipping != 0); });
+}
+// sums: numerator, denominator; counts: correct, selected, softmaxes.
+void orc_tally_read(void* h, float* loss, float* accuracy, double sums[2], uint64_t counts[3]) {
+    const orc::Tally* t = static_cast<orc::Tally*>(h);
+    t->metrics(loss, accuracy);
+    sums[0] = t->numerator;
+    sums[1] = t->denominator;
+    counts[0] = t->correct;
+    counts[1] = t->selected;
+    counts[2] = t->softmaxes;
 }
 int orc_trainer_write_param(void* h, uint64_t i, const float* data, uint64_t n) {
     return guarded([&] {

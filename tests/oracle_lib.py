@@ -50,6 +50,13 @@ def lib():
         L.orc_trainer_param_len.argtypes = [C.c_void_p, C.c_uint64]
         L.orc_trainer_read.argtypes = [C.c_void_p, C.c_int, C.c_uint64, C.c_void_p, C.c_uint64]
         L.orc_trainer_write_param.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]
+        L.orc_trainer_predict.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
+        L.orc_tally_create.restype = C.c_void_p
+        L.orc_tally_destroy.argtypes = [C.c_void_p]
+        L.orc_tally_destroy.restype = None
+        L.orc_tally_add.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int]
+        L.orc_tally_read.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_void_p, C.c_void_p]
+        L.orc_tally_read.restype = None
         L.orc_session_set_f32.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_uint64]
         L.orc_session_set_i32.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_uint64]
         L.orc_session_set_param.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]
@@ -144,9 +151,42 @@ class Trainer:
         _check(lib().orc_trainer_read(self.h, {"param": 0, "m": 1, "v": 2, "grad": 3}[which], i, out.ctypes.data, n))
         return out
 
+    def predict(self, n):
+        """The model's prediction for the current batch, from the dropout-free forward program."""
+        out = np.empty(n, dtype=np.float32)
+        _check(lib().orc_trainer_predict(self.h, out.ctypes.data, n))
+        return out
+
     def write_param(self, i, array):
         a = _f32(array)
         _check(lib().orc_trainer_write_param(self.h, i, a.ctypes.data, a.size))
+
+
+class Tally:
+    """The held-out reduction: batches of logits [rows, classes] in order, then the metrics."""
+
+    def __init__(self, skipping=True):
+        self.h = C.c_void_p(lib().orc_tally_create())
+        self.skipping = skipping
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().orc_tally_destroy(self.h)
+            self.h = None
+
+    def add(self, logits, labels, weights):
+        logits, labels, weights = _f32(logits), _i32(labels), _f32(weights)
+        rows = labels.size
+        _check(lib().orc_tally_add(self.h, logits.ctypes.data, labels.ctypes.data, weights.ctypes.data, rows, logits.size // max(rows, 1),
+                                   1 if self.skipping else 0))
+
+    def read(self):
+        """(loss, accuracy, numerator, denominator, correct, selected, softmaxes)."""
+        loss, accuracy = C.c_float(), C.c_float()
+        sums = np.zeros(2, dtype=np.float64)
+        counts = np.zeros(3, dtype=np.uint64)
+        lib().orc_tally_read(self.h, C.byref(loss), C.byref(accuracy), sums.ctypes.data, counts.ctypes.data)
+        return (np.float32(loss.value), np.float32(accuracy.value), float(sums[0]), float(sums[1]), int(counts[0]), int(counts[1]), int(counts[2]))
 
 
 class Session:

@@ -57,7 +57,10 @@ def test_infer_on_a_bert_twin_in_both_precisions(device):
                 gpu.step(k, 3)
             prediction, loss = gpu.infer()
             assert prediction.shape == (8 * 16 * 304,) and np.isfinite(prediction).all()
-            assert loss == gpu.final_loss()
+            # The plan that keeps the prediction adds the decoder bias in its own launch, the
+            # final-loss plan in the product's epilogue: the same loss within the run tolerance.
+            final = float(gpu.final_loss())
+            assert abs(float(loss) - final) <= 1e-4 + (2e-2 if flags & M.PLAN_BF16 else 1e-3) * abs(final)
             results.append((prediction, float(loss)))
         finally:
             gpu.destroy()
