@@ -412,6 +412,14 @@ int msx_op_attention_bf16(const void* q, const void* k, const void* v, const flo
                           void* dv, float* stats, uint32_t batch, uint32_t q_len, uint32_t k_len, uint32_t heads, uint32_t head_dim,
                           uint32_t* status, void* stream);
 
+/* The held-out row reduction on the caller's device buffers: the rows of `logits` (f32
+ * [rows, classes], `pitch` floats between rows, 0 = classes) with their labels and weights are
+ * added to `state`, 24 bytes {f64 numerator, u64 correct, u32 started, u32 arrived} that are zero
+ * before the first batch of an evaluation. `scratch` holds 12 * rows bytes. One launch; what
+ * msx_heldout_add runs (spirv/emit/heldout.rs:1-24 of the reference). */
+int msx_op_heldout_rows(const float* logits, uint64_t pitch, const int32_t* labels, const float* weights, uint64_t rows, uint64_t classes,
+                        void* scratch, void* state, void* stream);
+
 /* Column sums without any allocation: out[c] = sum over rows of g[r, c] for a row-major
  * [rows, columns] device matrix, the `SumRows` of a bias gradient. This function has no
  * counterpart in the reference. It exists for hosts that cannot allocate device memory once they

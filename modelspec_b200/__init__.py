@@ -99,6 +99,7 @@ SIGNATURES = {
     "msx_training_prediction_count": (C.c_uint64, [_P]),
     "msx_training_infer": (C.c_int, [_P, _P, C.c_uint64, C.POINTER(C.c_float)]),
     "msx_training_infer_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
+    "msx_op_heldout_rows": (C.c_int, [_P, C.c_uint64, _P, _P, C.c_uint64, C.c_uint64, _P, _P, _P]),
     "msx_heldout_create": (C.c_int, [_P, C.c_uint32, C.c_uint32, C.POINTER(_P)]),
     "msx_heldout_destroy": (None, [_P]),
     "msx_heldout_targets": (C.c_int, [_P, C.c_uint32, _P, _P, C.c_uint64]),

@@ -60,14 +60,21 @@ template <class F> __device__ __forceinline__ void visit(const float* row, uint3
     if (threadIdx.x < head) f(__ldg(row + threadIdx.x), threadIdx.x);
     const uint32_t body = (classes - head) / 4;
     const float4* wide = reinterpret_cast<const float4*>(row + head);
-    for (uint32_t j = threadIdx.x; j < body; j += THREADS) {
-        const float4 v = __ldg(wide + j);
-        const uint32_t i = head + 4 * j;
+    auto four = [&](const float4& v, uint32_t i) {
         f(v.x, i);
         f(v.y, i + 1);
         f(v.z, i + 2);
         f(v.w, i + 3);
+    };
+    uint32_t j = threadIdx.x;
+    for (; j + 3 * THREADS < body; j += 4 * THREADS) {  // four loads in flight per thread
+        const float4 a = __ldg(wide + j), b = __ldg(wide + j + THREADS), c = __ldg(wide + j + 2 * THREADS), d = __ldg(wide + j + 3 * THREADS);
+        four(a, head + 4 * j);
+        four(b, head + 4 * (j + THREADS));
+        four(c, head + 4 * (j + 2 * THREADS));
+        four(d, head + 4 * (j + 3 * THREADS));
     }
+    for (; j < body; j += THREADS) four(__ldg(wide + j), head + 4 * j);
     const uint32_t tail = head + 4 * body;
     if (tail + threadIdx.x < classes) f(__ldg(row + tail + threadIdx.x), tail + threadIdx.x);
 }
@@ -155,12 +162,22 @@ __global__ void __launch_bounds__(THREADS) heldout_rows_kernel(const float* __re
         }
         __syncthreads();
         if (threadIdx.x == 0) {
-            for (uint32_t i = 0; i < here; ++i) {
-                // The first term starts the sum; each later one is added (its product is exact, so
-                // the host's fused multiply-add rounds to the same f64).
-                sum = started ? sum + staged[i] : staged[i];
+            // The first term starts the sum; each later one is added (its product is exact, so
+            // the host's fused multiply-add rounds to the same f64).
+            uint32_t i = 0;
+            if (!started) {
+                sum = staged[0];
                 started = true;
+                i = 1;
             }
+            for (; i + 8 <= here; i += 8) {
+                double t[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) t[u] = staged[i + u];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) sum += t[u];
+            }
+            for (; i < here; ++i) sum += staged[i];
         }
         __syncthreads();
     }

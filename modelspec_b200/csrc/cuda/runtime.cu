@@ -3450,6 +3450,20 @@ int msx_op_attention_bf16(const void* q, const void* k, const void* v, const flo
     });
 }
 
+int msx_op_heldout_rows(const float* logits, uint64_t pitch, const int32_t* labels, const float* weights, uint64_t rows, uint64_t classes,
+                        void* scratch, void* state, void* stream) {
+    if (!logits || !labels || !weights || !scratch || !state) return MSX_BAD_ARGUMENT;
+    static_assert(sizeof(k::HeldOutState) == 24, "the state the header describes");
+    return guarded(nullptr, [&]() -> int {
+        if (rows == 0 || classes == 0 || rows * classes > 0xffffffffull || (pitch && pitch < classes))
+            throw StatusError(MSX_BAD_ARGUMENT, "msx_op_heldout_rows: logits of 1 to 2^32 - 1 elements, rows at least `classes` floats apart");
+        double* terms = static_cast<double*>(scratch);
+        k::heldout_rows(static_cast<cudaStream_t>(stream), logits, pitch, labels, weights, rows, classes, terms,
+                        reinterpret_cast<uint32_t*>(terms + rows), static_cast<k::HeldOutState*>(state));
+        return MSX_OK;
+    });
+}
+
 uint64_t msx_schedule_describe(const char* ir_text, char* out, uint64_t capacity) {
     return msx_schedule_describe_with(ir_text, MSX_PLAN_DEFAULT, out, capacity);
 }
