@@ -377,6 +377,50 @@ int msx_training_heldout_begin(msx_training* training, uint32_t batches, const c
 int msx_training_heldout_set(msx_training* training, uint32_t batch, const char* name, const void* host, uint64_t bytes);
 int msx_training_heldout_evaluate(msx_training* training, float* loss, float* accuracy);
 
+/* ---- packed masked-language-model data (`train --data <packed directory>`) ----------------------
+ * The directory the reference's `pack` writes: binding.json, packed.json, train.tokens and
+ * heldout.tokens (little-endian i32 ids, sequences of exactly seq_len ids, no padding).
+ * msx_packed_open reads and checks it as the reference does (dataset/mlm.rs:583-660,
+ * train/data.rs:1443-1483, :1605-1613): the binding's id is the id of its fields, the record
+ * lists a Train and a HeldOut split, 5 < vocabulary_size <= 2^31, every file has the length and
+ * the blake3 hash of its record, every id is inside the vocabulary, and the record belongs to the
+ * binding. MSX_BAD_INPUT with the reference's reason otherwise (msx_last_error(NULL)). */
+typedef struct msx_packed msx_packed;
+#define MSX_SPLIT_TRAIN 0
+#define MSX_SPLIT_HELDOUT 1
+int msx_packed_open(const char* dir, msx_packed** out);
+void msx_packed_close(msx_packed* packed);
+const char* msx_packed_last_error(const msx_packed* packed);
+uint64_t msx_packed_seq_len(const msx_packed* packed);
+uint64_t msx_packed_vocabulary(const msx_packed* packed);
+uint64_t msx_packed_sequences(const msx_packed* packed, int split);
+const char* msx_packed_binding_id(const msx_packed* packed);
+
+/* The order in which epoch `epoch` of a run with seed `seed` visits the Train sequences
+ * (dataset/mlm.rs:662-675); `count` is msx_packed_sequences(packed, MSX_SPLIT_TRAIN). */
+int msx_packed_epoch_order(msx_packed* packed, uint64_t seed, uint64_t epoch, uint32_t* out, uint64_t count);
+
+/* `mlm_batch` (dataset/mlm.rs:708-788): the batch of step `step` of a split for a run with seed
+ * `seed` and `batch_size` sequences per step, flattened to batch_size * seq_len rows. Train step k
+ * is batch k mod (n / B) of epoch k / (n / B) in epoch order; HeldOut step k is batch k mod (n / B)
+ * in stored order, its masking drawn with id k + 2^63. Any output may be null. */
+int msx_packed_batch(msx_packed* packed, int split, uint64_t seed, uint64_t step, uint64_t batch_size, int32_t* ids, int32_t* positions,
+                     float* key_mask, int32_t* labels, float* weights);
+
+/* Binds a packed directory to the run's declarations as the reference's `packed` does
+ * (train/data.rs:1588-1745): every declaration names a batch tensor (E-DATA-005), has its dtype
+ * and the shape [B, S] or [B*S] (E-DATA-006), is read by the loss (E-DATA-003); an embedding table
+ * that reads `ids` and the logits of the cross_entropy that reads `labels` are as wide as the
+ * packed vocabulary (E-DATA-006); the Train split holds at least B sequences. `packed` must
+ * outlive the training. msx_training_feed_packed makes the Train batch of step `step` the current
+ * batch (then msx_training_step). msx_training_heldout_packed draws the batches 0 .. n / B of the
+ * HeldOut split once and declares them for msx_training_heldout_evaluate; fewer than B sequences is
+ * the reference's EvalError::TooFewSequences (`dir` is named in that message). */
+int msx_training_bind_packed(msx_training* training, msx_packed* packed);
+int msx_training_feed_packed(msx_training* training, uint64_t step);
+int msx_training_heldout_packed(msx_training* training, const char* dir);
+uint32_t msx_training_heldout_batches(const msx_training* training);
+
 /* E-TRAIN-001 over the state: MSX_NON_FINITE naming the first parameter or moment that holds a
  * NaN or an infinity. Reads every parameter back; call it at the cadence the host can afford. */
 int msx_training_check_finite(msx_training* training);

@@ -109,6 +109,19 @@ SIGNATURES = {
     "msx_training_heldout_begin": (C.c_int, [_P, C.c_uint32, C.c_char_p, C.c_char_p]),
     "msx_training_heldout_set": (C.c_int, [_P, C.c_uint32, C.c_char_p, _P, C.c_uint64]),
     "msx_training_heldout_evaluate": (C.c_int, [_P, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "msx_packed_open": (C.c_int, [C.c_char_p, C.POINTER(_P)]),
+    "msx_packed_close": (None, [_P]),
+    "msx_packed_last_error": (C.c_char_p, [_P]),
+    "msx_packed_seq_len": (C.c_uint64, [_P]),
+    "msx_packed_vocabulary": (C.c_uint64, [_P]),
+    "msx_packed_sequences": (C.c_uint64, [_P, C.c_int]),
+    "msx_packed_binding_id": (C.c_char_p, [_P]),
+    "msx_packed_epoch_order": (C.c_int, [_P, C.c_uint64, C.c_uint64, _P, C.c_uint64]),
+    "msx_packed_batch": (C.c_int, [_P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, _P, _P, _P, _P, _P]),
+    "msx_training_bind_packed": (C.c_int, [_P, _P]),
+    "msx_training_feed_packed": (C.c_int, [_P, C.c_uint64]),
+    "msx_training_heldout_packed": (C.c_int, [_P, C.c_char_p]),
+    "msx_training_heldout_batches": (C.c_uint32, [_P]),
     "msx_plan_run_stats": (C.c_int, [_P, _P]),
     "msx_stats_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
     "msx_profile_report": (C.c_uint64, [_P, _P, C.c_uint32, C.c_char_p, C.c_uint64]),
@@ -351,6 +364,59 @@ class Plan:
         return total.value, steps.value
 
 
+SPLIT_TRAIN, SPLIT_HELDOUT = 0, 1
+
+
+class Packed:
+    """A packed masked-language-model directory (msx_packed): the reference's `--data <packed>`."""
+
+    def __init__(self, directory):
+        h = _P()
+        rc = lib().msx_packed_open(str(directory).encode(), C.byref(h))
+        if rc != OK:
+            raise MsxError(rc, lib().msx_last_error(None).decode())
+        self.h = h
+        self.dir = str(directory)
+
+    def close(self):
+        if self.h:
+            lib().msx_packed_close(self.h)
+            self.h = None
+
+    def check(self, rc):
+        if rc != OK:
+            raise MsxError(rc, lib().msx_packed_last_error(self.h).decode())
+
+    @property
+    def seq_len(self):
+        return int(lib().msx_packed_seq_len(self.h))
+
+    @property
+    def vocabulary(self):
+        return int(lib().msx_packed_vocabulary(self.h))
+
+    @property
+    def binding_id(self):
+        return lib().msx_packed_binding_id(self.h).decode()
+
+    def sequences(self, split):
+        return int(lib().msx_packed_sequences(self.h, split))
+
+    def epoch_order(self, seed, epoch):
+        out = np.empty(self.sequences(SPLIT_TRAIN), dtype=np.uint32)
+        self.check(lib().msx_packed_epoch_order(self.h, seed, epoch, out.ctypes.data, out.size))
+        return out
+
+    def batch(self, split, seed, step, batch_size):
+        """`mlm_batch`: a dict of ids, positions, key_mask, labels, weights of batch_size * S rows."""
+        rows = batch_size * self.seq_len
+        out = {"ids": np.empty(rows, np.int32), "positions": np.empty(rows, np.int32), "key_mask": np.empty(rows, np.float32),
+               "labels": np.empty(rows, np.int32), "weights": np.empty(rows, np.float32)}
+        self.check(lib().msx_packed_batch(self.h, split, seed, step, batch_size, *(out[k].ctypes.data for k in
+                                                                                   ("ids", "positions", "key_mask", "labels", "weights"))))
+        return out
+
+
 class HeldOut:
     """The held-out reduction of a plan's logits on the device (msx_heldout): targets once, then
     per evaluation begin(), add(batch) after each batch's run, and sums()."""
@@ -459,6 +525,20 @@ class Training:
     def heldout_set(self, batch, name, array):
         a = np.ascontiguousarray(array)
         self.check(lib().msx_training_heldout_set(self.h, batch, name.encode(), a.ctypes.data, a.nbytes))
+
+    def bind_packed(self, packed):
+        """Feeds the run from a packed directory; `packed` must stay open while the run lives."""
+        self.check(lib().msx_training_bind_packed(self.h, packed.h))
+        self._packed = packed
+
+    def feed_packed(self, step):
+        """Makes the Train batch of `step` the current batch."""
+        self.check(lib().msx_training_feed_packed(self.h, step))
+
+    def heldout_packed(self):
+        """Draws the HeldOut batches of the bound directory once; returns how many there are."""
+        self.check(lib().msx_training_heldout_packed(self.h, self._packed.dir.encode()))
+        return int(lib().msx_training_heldout_batches(self.h))
 
     def heldout_evaluate(self):
         """The held-out (loss, accuracy) of the current parameters, reduced on the device."""

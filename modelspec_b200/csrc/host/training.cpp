@@ -6,6 +6,7 @@
 // Per step the host supplies what the reference's host supplies (stepwise.rs:475-543): the AdamW
 // scalars of t = step + 1, the dropout token of every site at this step, the masked-row gather of
 // the batch, and the batch itself. Parameters start from their initializers on Philox stream 0.
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <map>
@@ -30,7 +31,12 @@ struct msx_training {
     msx_heldout* heldout = nullptr;
     std::string heldout_labels, heldout_weights;
     std::vector<std::map<std::string, std::vector<char>>> heldout_batches;
+    std::vector<std::vector<float>> heldout_row_weights;  // per batch, once its targets are on the device
     std::set<std::string> predict_inputs;
+    // A packed --data directory bound to the declarations (train/data.rs:1488-1500).
+    msx_packed* packed = nullptr;
+    uint64_t packed_batch = 0;
+    std::vector<std::string> packed_bound;  // the declared batch tensors, in source order
     uint32_t flags = 0;
     std::string error;
     std::map<std::string, std::vector<char>> batch;  // declared inputs and targets, by name
@@ -381,33 +387,46 @@ uint64_t msx_training_infer_report(msx_training* t, char* out, uint64_t capacity
 
 // ---- held-out evaluation (crates/modelspec-runtime/src/train/eval.rs:167-355) ---------------------
 
+namespace {
+
+// The steps the prediction is computed from, without the loss sum (stepwise.rs:32-35), on the
+// run's parameter buffers, and the device reduction of its logits for `batches` batches of `rows`
+// rows (eval.rs:143-163: the prediction is f32 logits [rows, V], one row per position).
+void heldout_declare(msx_training* t, uint32_t batches, uint64_t rows) {
+    const msx::Compiled& c = t->compiled;
+    if (t->heldout) throw Fail{MSX_BAD_ARGUMENT, "the held-out batches of this run are already declared"};
+    if (batches == 0) throw Fail{MSX_BAD_ARGUMENT, "a held-out split of no batch"};
+    const msx::Type& ty = c.forward.node(c.prediction).ty;
+    if (ty.i32 || ty.rank() != 2 || ty.shape[0] != rows || ty.shape[1] == 0)
+        throw Fail{MSX_BAD_ARGUMENT, "--eval-every reads the prediction as f32 logits [" + std::to_string(rows) +
+                                         ", V], one row per position of the batch; the model's prediction is " + ty.str()};
+    msx::Program program = c.forward;
+    program.outputs = {msx::Output{c.prediction, msx::Role::Plain, 0, 0}};
+    program = msx::dce(std::move(program));
+    std::string ir = msx::print_program(program);
+    ok(t, msx_plan_create(t->device, ir.c_str(), c.config.seed, t->flags, t->forward, &t->predict));
+    t->predict_inputs = input_names(t->predict);
+    ok(t, msx_heldout_create(t->predict, c.prediction, batches, &t->heldout));
+    t->heldout_batches.assign(batches, {});
+    t->heldout_row_weights.assign(batches, {});
+}
+
+void heldout_targets(msx_training* t, uint32_t batch, const int32_t* labels, const float* weights, uint64_t rows) {
+    ok(t, msx_heldout_targets(t->heldout, batch, labels, weights, rows));
+    t->heldout_row_weights[batch].assign(weights, weights + rows);
+}
+
+}  // namespace
+
 int msx_training_heldout_begin(msx_training* t, uint32_t batches, const char* labels, const char* weights) {
     if (!t || !labels || !weights) return MSX_BAD_ARGUMENT;
     return guarded(t, [&] {
-        const msx::Compiled& c = t->compiled;
-        if (t->heldout) throw Fail{MSX_BAD_ARGUMENT, "the held-out batches of this run are already declared"};
-        if (batches == 0) throw Fail{MSX_BAD_ARGUMENT, "a held-out split of no batch"};
         const msx::DataDecl *l = declared(t, labels), *w = declared(t, weights);
         if (!l || !l->ty.i32 || !w || w->ty.i32 || l->ty.count() != w->ty.count())
             throw Fail{MSX_BAD_ARGUMENT, std::string("`") + labels + "` and `" + weights + "` are not declared i32 labels and f32 weights of one row each"};
-        const uint64_t rows = l->ty.count();
-        // eval.rs:143-163: the prediction is f32 logits [rows, V], one row per position of the batch.
-        const msx::Type& ty = c.forward.node(c.prediction).ty;
-        if (ty.i32 || ty.rank() != 2 || ty.shape[0] != rows || ty.shape[1] == 0)
-            throw Fail{MSX_BAD_ARGUMENT, "--eval-every reads the prediction as f32 logits [" + std::to_string(rows) +
-                                             ", V], one row per position of the batch; the model's prediction is " + ty.str()};
-        // The steps the prediction is computed from, without the loss sum (stepwise.rs:32-35), on the
-        // run's parameter buffers.
-        msx::Program program = c.forward;
-        program.outputs = {msx::Output{c.prediction, msx::Role::Plain, 0, 0}};
-        program = msx::dce(std::move(program));
-        std::string ir = msx::print_program(program);
-        ok(t, msx_plan_create(t->device, ir.c_str(), c.config.seed, t->flags, t->forward, &t->predict));
-        t->predict_inputs = input_names(t->predict);
-        ok(t, msx_heldout_create(t->predict, c.prediction, batches, &t->heldout));
+        heldout_declare(t, batches, l->ty.count());
         t->heldout_labels = labels;
         t->heldout_weights = weights;
-        t->heldout_batches.assign(batches, {});
     });
 }
 
@@ -427,8 +446,8 @@ int msx_training_heldout_set(msx_training* t, uint32_t batch, const char* name, 
         // Both targets of a batch given: they go to the device, where they stay.
         auto l = held.find(t->heldout_labels), w = held.find(t->heldout_weights);
         if ((name == t->heldout_labels || name == t->heldout_weights) && l != held.end() && w != held.end())
-            ok(t, msx_heldout_targets(t->heldout, batch, reinterpret_cast<const int32_t*>(l->second.data()),
-                                      reinterpret_cast<const float*>(w->second.data()), l->second.size() / 4));
+            heldout_targets(t, batch, reinterpret_cast<const int32_t*>(l->second.data()), reinterpret_cast<const float*>(w->second.data()),
+                            l->second.size() / 4);
     });
 }
 
@@ -451,17 +470,15 @@ int msx_training_heldout_evaluate(msx_training* t, float* loss, float* accuracy)
                 if (it == held.end()) throw Fail{MSX_BAD_INPUT, "held-out batch " + std::to_string(b) + " holds no `" + name + "`"};
                 ok(t, msx_set_input(t->predict, name.c_str(), it->second.data(), it->second.size()));
             }
-            auto w = held.find(t->heldout_weights);
-            if (w == held.end() || !held.count(t->heldout_labels))
-                throw Fail{MSX_BAD_INPUT, "held-out batch " + std::to_string(b) + " holds no labels and weights"};
+            const std::vector<float>& weights = t->heldout_row_weights[b];
+            if (weights.empty()) throw Fail{MSX_BAD_INPUT, "held-out batch " + std::to_string(b) + " holds no labels and weights"};
             ok(t, msx_run(t->predict));
             ok(t, msx_heldout_add(t->heldout, b));
-            const float* weights = reinterpret_cast<const float*>(w->second.data());
-            for (size_t n = 0; n < w->second.size() / 4; ++n) {
-                const double wide = static_cast<double>(weights[n]);
+            for (float weight : weights) {
+                const double wide = static_cast<double>(weight);
                 denominator = any ? denominator + wide : wide;
                 any = true;
-                if (weights[n] > 0.0f) ++selected;
+                if (weight > 0.0f) ++selected;
             }
         }
         double numerator = 0.0;
@@ -471,6 +488,147 @@ int msx_training_heldout_evaluate(msx_training* t, float* loss, float* accuracy)
         *accuracy = selected == 0 ? 0.0f : static_cast<float>(correct) / static_cast<float>(selected);
     });
 }
+
+// ---- packed --data (crates/modelspec-runtime/src/train/data.rs:1485-1760) ------------------------
+
+namespace {
+
+const char* const kBatchTensors[5] = {"ids", "positions", "key_mask", "labels", "weights"};
+bool batch_tensor_is_i32(const std::string& name) { return name == "ids" || name == "positions" || name == "labels"; }
+std::string batch_tensor_names() { return "ids, positions, key_mask, labels, weights"; }
+
+// Draws batch `step` of a split as the declared tensors hold it, by declaration name.
+void draw_packed(msx_training* t, int split, uint64_t step, std::map<std::string, std::vector<char>>* out, std::vector<int32_t>* labels,
+                 std::vector<float>* weights) {
+    const uint64_t rows = t->packed_batch * msx_packed_seq_len(t->packed);
+    std::vector<int32_t> ids(rows), positions(rows);
+    std::vector<float> key_mask(rows);
+    labels->resize(rows);
+    weights->resize(rows);
+    if (msx_packed_batch(t->packed, split, t->compiled.config.seed, step, t->packed_batch, ids.data(), positions.data(), key_mask.data(),
+                         labels->data(), weights->data()) != MSX_OK)
+        throw Fail{MSX_BAD_INPUT, std::string(msx_packed_last_error(t->packed))};
+    for (const std::string& name : t->packed_bound) {
+        const void* from = name == "ids" ? static_cast<const void*>(ids.data())
+                           : name == "positions" ? static_cast<const void*>(positions.data())
+                           : name == "key_mask" ? static_cast<const void*>(key_mask.data())
+                           : name == "labels" ? static_cast<const void*>(labels->data())
+                                              : static_cast<const void*>(weights->data());
+        const char* b = static_cast<const char*>(from);
+        (*out)[name].assign(b, b + rows * 4);
+    }
+}
+
+}  // namespace
+
+int msx_training_bind_packed(msx_training* t, msx_packed* packed) {
+    if (!t || !packed) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        const uint64_t seq_len = msx_packed_seq_len(packed), vocabulary = msx_packed_vocabulary(packed);
+        const auto& decls = c.config.data;  // in source order
+        // bind (data.rs:1630-1745), its refusals in the reference's order.
+        if (decls.empty()) throw Fail{MSX_BAD_INPUT, "E-DATA-005: a run on a packed directory declares no batch tensor (" + batch_tensor_names() + ")"};
+        for (const msx::DataDecl& d : decls)
+            if (std::find_if(std::begin(kBatchTensors), std::end(kBatchTensors), [&](const char* n) { return d.name == n; }) == std::end(kBatchTensors))
+                throw Fail{MSX_BAD_INPUT, std::string("E-DATA-005: the ") + (d.target ? "target" : "input") + " `" + d.name +
+                                              "` names no tensor of the masked-language-model batch (" + batch_tensor_names() + ")"};
+        const msx::DataDecl* first = nullptr;
+        for (const char* name : kBatchTensors) {
+            for (const msx::DataDecl& d : decls)
+                if (!first && d.name == name) first = &d;
+        }
+        auto type_text = [&](const std::string& name, const std::string& shape) {
+            return std::string("Tensor<") + (batch_tensor_is_i32(name) ? "i32" : "f32") + ", [" + shape + "]>";
+        };
+        auto mismatch = [&](const msx::DataDecl& d, const std::string& expected) {
+            return Fail{MSX_BAD_INPUT, std::string("E-DATA-006: the ") + (d.target ? "target" : "input") + " `" + d.name +
+                                           "` is not of the type of the batch tensor `" + d.name + "`: it is " + d.ty.str() + ", expected " + expected};
+        };
+        uint64_t batch = 0;
+        const auto& shape = first->ty.shape;
+        const bool positive = std::all_of(shape.begin(), shape.end(), [](uint64_t n) { return n > 0; });
+        if (positive && shape.size() == 2 && shape[1] == seq_len) batch = shape[0];
+        else if (positive && shape.size() == 1 && shape[0] % seq_len == 0) batch = shape[0] / seq_len;
+        if (batch == 0)
+            throw mismatch(*first, type_text(first->name, "B, " + std::to_string(seq_len)) + " or " + type_text(first->name, "B·" + std::to_string(seq_len)));
+        const uint64_t rows = batch * seq_len;
+        for (const msx::DataDecl& d : decls) {
+            const bool fits = d.ty.i32 == batch_tensor_is_i32(d.name) &&
+                              ((d.ty.shape.size() == 2 && d.ty.shape[0] == batch && d.ty.shape[1] == seq_len) ||
+                               (d.ty.shape.size() == 1 && d.ty.shape[0] == rows));
+            if (!fits)
+                throw mismatch(d, type_text(d.name, std::to_string(batch) + ", " + std::to_string(seq_len)) + " or " + type_text(d.name, std::to_string(rows)));
+        }
+        // refuse_unread (data.rs:307-338): every declaration has an Input node of the forward program.
+        const msx::Program& fwd = c.forward_with_dropout;
+        auto input_of = [&](const std::string& name) -> int64_t {
+            for (uint32_t in : fwd.inputs)
+                if (fwd.node(in).name == name) return in;
+            return -1;
+        };
+        for (const msx::DataDecl& d : decls)
+            if (input_of(d.name) < 0)
+                throw Fail{MSX_BAD_INPUT, std::string("E-DATA-003: the ") + (d.target ? "target" : "input") + " `" + d.name + "` is not read by the loss"};
+        // refuse_vocabulary (data.rs:1760-1840): the widths the packed vocabulary fixes.
+        const int64_t ids = input_of("ids"), labels = input_of("labels");
+        for (const msx::Node& n : fwd.nodes) {
+            const bool table = n.op == msx::Op::Embedding && ids >= 0 && n.operands.size() > 1 && n.operands[1] == static_cast<uint32_t>(ids);
+            const bool logits = n.op == msx::Op::CrossEntropy && labels >= 0 && n.operands.size() > 1 && n.operands[1] == static_cast<uint32_t>(labels);
+            if (!table && !logits) continue;
+            const msx::Node& value = fwd.node(n.operands[0]);
+            const size_t axis = table ? 0 : 1;
+            if (value.ty.shape.size() <= axis || value.ty.shape[axis] == vocabulary) continue;
+            std::string named = "%" + std::to_string(value.id);
+            if (value.op == msx::Op::ParamRead) named = fwd.params[value.param].path;
+            throw Fail{MSX_BAD_INPUT, std::string("E-DATA-006: the ") + (table ? "table" : "logits") + " `" + named + "` of the `" +
+                                          (table ? "embedding" : "cross_entropy") + "` that reads `" + (table ? "ids" : "labels") + "` has " +
+                                          std::to_string(value.ty.shape[axis]) + (table ? " rows" : " classes") + ", not the " + std::to_string(vocabulary) +
+                                          " tokens of the packed vocabulary"};
+        }
+        const uint64_t sequences = msx_packed_sequences(packed, MSX_SPLIT_TRAIN);
+        if (batch > sequences)
+            throw Fail{MSX_BAD_INPUT, "a batch of " + std::to_string(batch) + " sequences, more than the " + std::to_string(sequences) + " of the Train split"};
+        t->packed = packed;
+        t->packed_batch = batch;
+        t->packed_bound.clear();
+        for (const msx::DataDecl& d : decls) t->packed_bound.push_back(d.name);
+    });
+}
+
+int msx_training_feed_packed(msx_training* t, uint64_t step) {
+    if (!t) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        if (!t->packed) throw Fail{MSX_BAD_ARGUMENT, "no packed directory is bound"};
+        std::vector<int32_t> labels;
+        std::vector<float> weights;
+        draw_packed(t, MSX_SPLIT_TRAIN, step, &t->batch, &labels, &weights);
+    });
+}
+
+int msx_training_heldout_packed(msx_training* t, const char* dir_for_messages) {
+    if (!t) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        if (!t->packed) throw Fail{MSX_BAD_ARGUMENT, "no packed directory is bound"};
+        // HeldOut::new (eval.rs:167-199): the batches b = 0 .. n / B of the split, drawn once.
+        const uint64_t sequences = msx_packed_sequences(t->packed, MSX_SPLIT_HELDOUT);
+        if (sequences < t->packed_batch)
+            throw Fail{MSX_BAD_INPUT, std::string("the HeldOut split of ") + (dir_for_messages ? dir_for_messages : "the packed directory") + " holds " +
+                                          std::to_string(sequences) + " sequences, fewer than the batch of " + std::to_string(t->packed_batch) +
+                                          " that --eval-every evaluates"};
+        const uint64_t batches = sequences / t->packed_batch;
+        if (batches > 0xffffffffull) throw Fail{MSX_BAD_INPUT, "too many held-out batches"};
+        heldout_declare(t, static_cast<uint32_t>(batches), t->packed_batch * msx_packed_seq_len(t->packed));
+        for (uint32_t b = 0; b < batches; ++b) {
+            std::vector<int32_t> labels;
+            std::vector<float> weights;
+            draw_packed(t, MSX_SPLIT_HELDOUT, b, &t->heldout_batches[b], &labels, &weights);
+            heldout_targets(t, b, labels.data(), weights.data(), labels.size());
+        }
+    });
+}
+
+uint32_t msx_training_heldout_batches(const msx_training* t) { return t ? static_cast<uint32_t>(t->heldout_batches.size()) : 0; }
 
 int msx_training_check_finite(msx_training* t) {
     if (!t) return MSX_BAD_ARGUMENT;
