@@ -71,7 +71,11 @@ def refused(device, source, packed, code, text):
 
 def test_declarations_a_packed_directory_cannot_feed_are_refused(device, packed):
     refused(device, models.linear_regression(steps=2), packed, "E-DATA-005", "the input `x` names no tensor of the masked-language-model batch")
-    refused(device, models.bert(steps=2, **{**SHAPE, "seq": 8}), packed, "E-DATA-006", "is not of the type of the batch tensor `ids`")
+    # 4 x 8 ids are two sequences of 16, so `ids` gives B = 2 and the [4, 8] key mask does not fit; 4 x 5 ids give no B at all.
+    refused(device, models.bert(steps=2, **{**SHAPE, "seq": 8}), packed, "E-DATA-006",
+            "the input `key_mask` is not of the type of the batch tensor `key_mask`: it is Tensor<f32, [4, 8]>, expected Tensor<f32, [2, 16]> or Tensor<f32, [32]>")
+    refused(device, models.bert(steps=2, **{**SHAPE, "seq": 5}), packed, "E-DATA-006",
+            "the input `ids` is not of the type of the batch tensor `ids`: it is Tensor<i32, [20]>, expected Tensor<i32, [B, 16]> or Tensor<i32, [B·16]>")
     refused(device, models.bert(steps=2, **{**SHAPE, "vocab": VOCAB + 3}), packed, "E-DATA-006",
             "the table `BertTiny.tok_table` of the `embedding` that reads `ids` has 64 rows, not the 61 tokens of the packed vocabulary")
     refused(device, models.bert(steps=2, **{**SHAPE, "batch": 40}), packed, "", "a batch of 40 sequences, more than the 37 of the Train split")
