@@ -421,6 +421,59 @@ int msx_training_feed_packed(msx_training* training, uint64_t step);
 int msx_training_heldout_packed(msx_training* training, const char* dir);
 uint32_t msx_training_heldout_batches(const msx_training* training);
 
+/* ---- `.msckpt` checkpoints ------------------------------------------------------------------------
+ * Writer and validating reader of the reference's checkpoint format version 1, byte for byte
+ * (crates/modelspec-runtime/src/train/checkpoint.rs:1-22, :420-517, :640-921): 56-byte header,
+ * compact JSON manifest, 64-byte-aligned little-endian f32 payloads in path order, blake3 checksum,
+ * payload hash and checkpoint id. msx_checkpoint_read refuses what the reference's reader refuses,
+ * with its codes in the message: E-CKPT-001 (header, checksum, manifest, invariants), E-CKPT-002
+ * (sizes, offsets, alignment, overlap, non-zero gap bytes), E-CKPT-004 (payload hash);
+ * MSX_BAD_INPUT, text from msx_last_error(NULL). A checkpoint is built with msx_checkpoint_new,
+ * msx_checkpoint_set_optimizer and one msx_checkpoint_add per tensor (`slot` NULL for a parameter,
+ * "m" / "v" for an AdamW moment, written as the manifest's optimizer_slots, which the reference's
+ * format defines and its writer leaves empty). Lists: 0 the parameters, 1 the optimizer slots. */
+typedef struct msx_checkpoint msx_checkpoint;
+#define MSX_OPTIMIZER_SGD 0
+#define MSX_OPTIMIZER_ADAMW 1
+#define MSX_OPTIMIZER_OTHER 2 /* a kind this backend reads but does not run (Muon) */
+int msx_checkpoint_new(uint64_t step, uint64_t seed, const char* schema_hash, msx_checkpoint** out);
+void msx_checkpoint_destroy(msx_checkpoint* checkpoint);
+const char* msx_checkpoint_last_error(const msx_checkpoint* checkpoint);
+int msx_checkpoint_set_optimizer(msx_checkpoint* checkpoint, int kind, double learning_rate, double weight_decay, double beta1, double beta2,
+                                 double epsilon, uint64_t warmup_steps);
+int msx_checkpoint_add(msx_checkpoint* checkpoint, const char* path, const char* slot, const uint64_t* shape, uint32_t rank, const float* data);
+/* The file's bytes: returns their count; copies them when `capacity` holds them. */
+uint64_t msx_checkpoint_encode(msx_checkpoint* checkpoint, void* out, uint64_t capacity);
+/* Writes `<path>.tmp`, then renames it over `path` (checkpoint.rs:629-665). */
+int msx_checkpoint_write(msx_checkpoint* checkpoint, const char* path);
+int msx_checkpoint_read(const char* path, msx_checkpoint** out);
+uint64_t msx_checkpoint_step(const msx_checkpoint* checkpoint);
+uint64_t msx_checkpoint_seed(const msx_checkpoint* checkpoint);
+const char* msx_checkpoint_schema_hash(const msx_checkpoint* checkpoint);
+const char* msx_checkpoint_id(const msx_checkpoint* checkpoint); /* set by encode, write and read */
+int msx_checkpoint_optimizer(const msx_checkpoint* checkpoint, int* kind, double* learning_rate, double* weight_decay, double* beta1,
+                             double* beta2, double* epsilon, uint64_t* warmup_steps);
+uint64_t msx_checkpoint_optimizer_json(const msx_checkpoint* checkpoint, char* out, uint64_t capacity);
+uint32_t msx_checkpoint_count(const msx_checkpoint* checkpoint, int list);
+const char* msx_checkpoint_path(const msx_checkpoint* checkpoint, int list, uint32_t index);
+const char* msx_checkpoint_slot(const msx_checkpoint* checkpoint, int list, uint32_t index);
+uint32_t msx_checkpoint_rank(const msx_checkpoint* checkpoint, int list, uint32_t index);
+const uint64_t* msx_checkpoint_shape(const msx_checkpoint* checkpoint, int list, uint32_t index);
+const float* msx_checkpoint_data(const msx_checkpoint* checkpoint, int list, uint32_t index);
+
+/* The checkpoint of a run after `step` updates (Checkpoint::of_state, checkpoint.rs:420-451): every
+ * parameter read back from the device in path order, the schema hash of the training program's
+ * parameters, the optimizer of the train block, the run's seed at counter 0; for AdamW also both
+ * moments of every parameter. msx_training_resume loads it into a run (Checkpoint::resume_into,
+ * checkpoint.rs:519-609): E-CKPT-003 at the first parameter path or shape that differs in path
+ * order, then at a differing schema hash, then at a differing optimizer; an AdamW checkpoint of a
+ * step above 0 without moments is refused as the reference refuses it (train/runner.rs:335-347).
+ * `start_step` receives the checkpoint's step: the run continues with msx_training_step(start_step,
+ * end), and equals the run that never stopped. */
+int msx_training_checkpoint(msx_training* training, uint64_t step, msx_checkpoint** out);
+int msx_training_resume(msx_training* training, const msx_checkpoint* checkpoint, uint64_t* start_step);
+const char* msx_training_schema_hash(msx_training* training);
+
 /* E-TRAIN-001 over the state: MSX_NON_FINITE naming the first parameter or moment that holds a
  * NaN or an infinity. Reads every parameter back; call it at the cadence the host can afford. */
 int msx_training_check_finite(msx_training* training);

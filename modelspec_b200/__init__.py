@@ -122,6 +122,29 @@ SIGNATURES = {
     "msx_training_feed_packed": (C.c_int, [_P, C.c_uint64]),
     "msx_training_heldout_packed": (C.c_int, [_P, C.c_char_p]),
     "msx_training_heldout_batches": (C.c_uint32, [_P]),
+    "msx_checkpoint_new": (C.c_int, [C.c_uint64, C.c_uint64, C.c_char_p, C.POINTER(_P)]),
+    "msx_checkpoint_destroy": (None, [_P]),
+    "msx_checkpoint_last_error": (C.c_char_p, [_P]),
+    "msx_checkpoint_set_optimizer": (C.c_int, [_P, C.c_int, C.c_double, C.c_double, C.c_double, C.c_double, C.c_double, C.c_uint64]),
+    "msx_checkpoint_add": (C.c_int, [_P, C.c_char_p, C.c_char_p, _P, C.c_uint32, _P]),
+    "msx_checkpoint_encode": (C.c_uint64, [_P, _P, C.c_uint64]),
+    "msx_checkpoint_write": (C.c_int, [_P, C.c_char_p]),
+    "msx_checkpoint_read": (C.c_int, [C.c_char_p, C.POINTER(_P)]),
+    "msx_checkpoint_step": (C.c_uint64, [_P]),
+    "msx_checkpoint_seed": (C.c_uint64, [_P]),
+    "msx_checkpoint_schema_hash": (C.c_char_p, [_P]),
+    "msx_checkpoint_id": (C.c_char_p, [_P]),
+    "msx_checkpoint_optimizer": (C.c_int, [_P, C.POINTER(C.c_int)] + [C.POINTER(C.c_double)] * 5 + [C.POINTER(C.c_uint64)]),
+    "msx_checkpoint_optimizer_json": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
+    "msx_checkpoint_count": (C.c_uint32, [_P, C.c_int]),
+    "msx_checkpoint_path": (C.c_char_p, [_P, C.c_int, C.c_uint32]),
+    "msx_checkpoint_slot": (C.c_char_p, [_P, C.c_int, C.c_uint32]),
+    "msx_checkpoint_rank": (C.c_uint32, [_P, C.c_int, C.c_uint32]),
+    "msx_checkpoint_shape": (C.POINTER(C.c_uint64), [_P, C.c_int, C.c_uint32]),
+    "msx_checkpoint_data": (C.POINTER(C.c_float), [_P, C.c_int, C.c_uint32]),
+    "msx_training_checkpoint": (C.c_int, [_P, C.c_uint64, C.POINTER(_P)]),
+    "msx_training_resume": (C.c_int, [_P, _P, C.POINTER(C.c_uint64)]),
+    "msx_training_schema_hash": (C.c_char_p, [_P]),
     "msx_plan_run_stats": (C.c_int, [_P, _P]),
     "msx_stats_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
     "msx_profile_report": (C.c_uint64, [_P, _P, C.c_uint32, C.c_char_p, C.c_uint64]),
@@ -365,6 +388,73 @@ class Plan:
 
 
 SPLIT_TRAIN, SPLIT_HELDOUT = 0, 1
+OPTIMIZER_SGD, OPTIMIZER_ADAMW, OPTIMIZER_OTHER = 0, 1, 2
+
+
+class Checkpoint:
+    """A `.msckpt` checkpoint in memory (msx_checkpoint): built tensor by tensor or read from a file."""
+
+    def __init__(self, step=0, seed=0, schema_hash="", handle=None):
+        if handle is None:
+            handle = _P()
+            rc = lib().msx_checkpoint_new(step, seed, schema_hash.encode(), C.byref(handle))
+            if rc != OK:
+                raise MsxError(rc, "msx_checkpoint_new")
+        self.h = handle
+
+    @classmethod
+    def read(cls, path):
+        h = _P()
+        rc = lib().msx_checkpoint_read(str(path).encode(), C.byref(h))
+        if rc != OK:
+            raise MsxError(rc, lib().msx_last_error(None).decode())
+        return cls(handle=h)
+
+    def destroy(self):
+        if self.h:
+            lib().msx_checkpoint_destroy(self.h)
+            self.h = None
+
+    def check(self, rc):
+        if rc != OK:
+            raise MsxError(rc, lib().msx_checkpoint_last_error(self.h).decode())
+
+    def set_optimizer(self, kind, learning_rate, weight_decay=0.0, beta1=0.0, beta2=0.0, epsilon=0.0, warmup_steps=0):
+        self.check(lib().msx_checkpoint_set_optimizer(self.h, kind, learning_rate, weight_decay, beta1, beta2, epsilon, warmup_steps))
+
+    def add(self, path, array, slot=None):
+        a = np.ascontiguousarray(array, dtype=np.float32)
+        shape = (C.c_uint64 * a.ndim)(*a.shape)
+        self.check(lib().msx_checkpoint_add(self.h, path.encode(), slot.encode() if slot else None, shape, a.ndim, a.ctypes.data))
+
+    def encode(self):
+        n = lib().msx_checkpoint_encode(self.h, None, 0)
+        buf = C.create_string_buffer(n)
+        lib().msx_checkpoint_encode(self.h, buf, n)
+        return buf.raw
+
+    def write(self, path):
+        self.check(lib().msx_checkpoint_write(self.h, str(path).encode()))
+
+    step = property(lambda self: int(lib().msx_checkpoint_step(self.h)))
+    seed = property(lambda self: int(lib().msx_checkpoint_seed(self.h)))
+    schema_hash = property(lambda self: lib().msx_checkpoint_schema_hash(self.h).decode())
+    id = property(lambda self: lib().msx_checkpoint_id(self.h).decode())
+
+    def optimizer_json(self):
+        return _text(lambda buf, cap: lib().msx_checkpoint_optimizer_json(self.h, buf, cap))
+
+    def tensors(self, slots=False):
+        """[(path, slot, array)] of the parameters, or of the optimizer slots."""
+        L, which = lib(), 1 if slots else 0
+        out = []
+        for i in range(L.msx_checkpoint_count(self.h, which)):
+            rank = L.msx_checkpoint_rank(self.h, which, i)
+            shape = tuple(int(L.msx_checkpoint_shape(self.h, which, i)[d]) for d in range(rank))
+            n = int(np.prod(shape)) if rank else 1
+            data = np.ctypeslib.as_array(L.msx_checkpoint_data(self.h, which, i), shape=(n,)).copy().reshape(shape)
+            out.append((L.msx_checkpoint_path(self.h, which, i).decode(), L.msx_checkpoint_slot(self.h, which, i).decode(), data))
+        return out
 
 
 class Packed:
@@ -539,6 +629,21 @@ class Training:
         """Draws the HeldOut batches of the bound directory once; returns how many there are."""
         self.check(lib().msx_training_heldout_packed(self.h, self._packed.dir.encode()))
         return int(lib().msx_training_heldout_batches(self.h))
+
+    def checkpoint(self, step):
+        """The run's state after `step` updates as a Checkpoint (parameters, and AdamW moments)."""
+        h = _P()
+        self.check(lib().msx_training_checkpoint(self.h, step, C.byref(h)))
+        return Checkpoint(handle=h)
+
+    def resume(self, checkpoint):
+        """Loads a checkpoint into the run; returns the step the run continues from."""
+        start = C.c_uint64()
+        self.check(lib().msx_training_resume(self.h, checkpoint.h, C.byref(start)))
+        return int(start.value)
+
+    def schema_hash(self):
+        return lib().msx_training_schema_hash(self.h).decode()
 
     def heldout_evaluate(self):
         """The held-out (loss, accuracy) of the current parameters, reduced on the device."""

@@ -3,7 +3,9 @@
 // numbers keep their text so that a u64 is read without passing through a double.
 #pragma once
 
+#include <cmath>
 #include <cstdint>
+#include <cstdio>
 #include <cstdlib>
 #include <memory>
 #include <stdexcept>
@@ -230,6 +232,34 @@ inline std::string quoted(const std::string& text) {
         }
     }
     return out + "\"";
+}
+
+// A finite f64 as serde_json writes it (the ryu crate's layout of the shortest digits that read
+// back to the same f64): plain decimals while the decimal point stays within 16 digits of the
+// first one or at most five zeros follow "0.", exponent form otherwise; an integer keeps ".0".
+inline std::string f64_text(double v) {
+    if (v == 0.0) return std::signbit(v) ? "-0.0" : "0.0";
+    std::string sign = v < 0 ? "-" : "";
+    double a = std::fabs(v);
+    char buf[64];
+    for (int prec = 0; prec < 17; ++prec) {
+        std::snprintf(buf, sizeof buf, "%.*e", prec, a);
+        if (std::strtod(buf, nullptr) == a) break;
+    }
+    std::string s(buf);
+    size_t e = s.find('e');
+    int kk = std::atoi(s.c_str() + e + 1) + 1;  // a = 0.d1d2...dn x 10^kk
+    std::string digits;
+    for (char c : s.substr(0, e))
+        if (c >= '0' && c <= '9') digits.push_back(c);
+    while (digits.size() > 1 && digits.back() == '0') digits.pop_back();
+    int n = static_cast<int>(digits.size()), k = kk - n;
+    if (k >= 0 && kk <= 16) return sign + digits + std::string(static_cast<size_t>(k), '0') + ".0";
+    if (kk > 0 && kk <= 16) return sign + digits.substr(0, static_cast<size_t>(kk)) + "." + digits.substr(static_cast<size_t>(kk));
+    if (kk > -5 && kk <= 0) return sign + "0." + std::string(static_cast<size_t>(-kk), '0') + digits;
+    std::string out = sign + digits.substr(0, 1);
+    if (n > 1) out += "." + digits.substr(1);
+    return out + "e" + std::to_string(kk - 1);
 }
 
 }  // namespace json

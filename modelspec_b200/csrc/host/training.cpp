@@ -10,11 +10,13 @@
 #include <cmath>
 #include <cstring>
 #include <map>
+#include <memory>
 #include <set>
 
 #include "../../../include/msx.h"
 #include "../core/frontend.hpp"
 #include "../core/init.hpp"
+#include "../core/schema.hpp"
 
 // Defined beside msx_last_error: records a message on the device handle.
 extern "C" void msx_internal_set_error(msx_device* device, const char* message);
@@ -34,6 +36,7 @@ struct msx_training {
     std::vector<std::vector<float>> heldout_row_weights;  // per batch, once its targets are on the device
     std::set<std::string> predict_inputs;
     // A packed --data directory bound to the declarations (train/data.rs:1488-1500).
+    std::string schema;  // the schema hash of the training program's parameters, made on first use
     msx_packed* packed = nullptr;
     uint64_t packed_batch = 0;
     std::vector<std::string> packed_bound;  // the declared batch tensors, in source order
@@ -629,6 +632,149 @@ int msx_training_heldout_packed(msx_training* t, const char* dir_for_messages) {
 }
 
 uint32_t msx_training_heldout_batches(const msx_training* t) { return t ? static_cast<uint32_t>(t->heldout_batches.size()) : 0; }
+
+// ---- checkpoints (crates/modelspec-runtime/src/train/checkpoint.rs:420-451, :519-609) --------------
+
+namespace {
+
+// OptimizerConfig::of (checkpoint.rs:114-152): the f32 hyperparameters widened to f64.
+void optimizer_of(const msx_training* t, int* kind, double v[5], uint64_t* warmup) {
+    const msx::TrainConfig& c = t->compiled.config;
+    *kind = c.rule == msx::Rule::AdamW ? MSX_OPTIMIZER_ADAMW : MSX_OPTIMIZER_SGD;
+    v[0] = static_cast<double>(c.lr);
+    v[1] = static_cast<double>(c.adamw.weight_decay);
+    v[2] = static_cast<double>(c.adamw.beta1);
+    v[3] = static_cast<double>(c.adamw.beta2);
+    v[4] = static_cast<double>(c.adamw.eps);
+    *warmup = c.adamw.warmup_steps;
+}
+
+std::string shape_text(const std::vector<uint64_t>& shape) {
+    std::string s = "[";
+    for (size_t i = 0; i < shape.size(); ++i) s += (i ? ", " : "") + std::to_string(shape[i]);
+    return s + "]";
+}
+
+}  // namespace
+
+const char* msx_training_schema_hash(msx_training* t) {
+    if (!t) return "";
+    if (t->schema.empty()) t->schema = msx::schema_hash(t->compiled.step.params);
+    return t->schema.c_str();
+}
+
+int msx_training_checkpoint(msx_training* t, uint64_t step, msx_checkpoint** out) {
+    if (!t || !out) return MSX_BAD_ARGUMENT;
+    *out = nullptr;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        ok(t, msx_sync(t->step, 0));
+        msx_checkpoint* ckpt = nullptr;
+        if (msx_checkpoint_new(step, c.config.seed, msx_training_schema_hash(t), &ckpt) != MSX_OK) throw Fail{MSX_UNSUPPORTED, "no checkpoint"};
+        std::unique_ptr<msx_checkpoint, void (*)(msx_checkpoint*)> holder(ckpt, msx_checkpoint_destroy);
+        int kind;
+        double v[5];
+        uint64_t warmup;
+        optimizer_of(t, &kind, v, &warmup);
+        msx_checkpoint_set_optimizer(ckpt, kind, v[0], v[1], v[2], v[3], v[4], warmup);
+        auto add = [&](const msx::Param& p, const char* slot, const std::vector<float>& value) {
+            if (msx_checkpoint_add(ckpt, p.path.c_str(), slot, p.ty.shape.data(), static_cast<uint32_t>(p.ty.shape.size()), value.data()) != MSX_OK)
+                throw Fail{MSX_BAD_ARGUMENT, std::string("cannot write checkpoint: ") + msx_checkpoint_last_error(ckpt)};
+        };
+        const auto& params = c.forward.params;
+        std::vector<float> value;
+        for (uint32_t p = 0; p < params.size(); ++p) {
+            value.resize(params[p].ty.count());
+            // The forward plan holds every parameter the prediction or the loss reads (the step's own
+            // buffers, shared); one that neither reads has no value to record.
+            if (msx_param_download(t->forward, p, value.data(), value.size() * 4) != MSX_OK &&
+                msx_param_download(t->step, p, value.data(), value.size() * 4) != MSX_OK)
+                continue;
+            add(params[p], nullptr, value);
+            if (kind != MSX_OPTIMIZER_ADAMW) continue;
+            for (char which : {'m', 'v'}) {
+                if (msx_moment_download(t->step, p, which, value.data(), value.size() * 4) != MSX_OK) continue;
+                const char slot[2] = {which, 0};
+                add(params[p], slot, value);
+            }
+        }
+        *out = holder.release();
+    });
+}
+
+int msx_training_resume(msx_training* t, const msx_checkpoint* ckpt, uint64_t* start_step) {
+    if (!t || !ckpt || !start_step) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        auto mismatch = [](const std::string& what) { return Fail{MSX_BAD_INPUT, "E-CKPT-003: the checkpoint does not match the compiled file: " + what}; };
+        // parameters_for (checkpoint.rs:519-585): both sides in path order, the first difference named.
+        std::vector<uint32_t> ours(c.forward.params.size());
+        for (uint32_t p = 0; p < ours.size(); ++p) ours[p] = p;
+        std::sort(ours.begin(), ours.end(), [&](uint32_t a, uint32_t b) { return c.forward.params[a].path < c.forward.params[b].path; });
+        const uint32_t theirs = msx_checkpoint_count(ckpt, 0);
+        for (uint32_t i = 0; i < std::max<uint32_t>(theirs, static_cast<uint32_t>(ours.size())); ++i) {
+            const std::string their_path = i < theirs ? std::string("`") + msx_checkpoint_path(ckpt, 0, i) + "`" : "none";
+            const std::string our_path = i < ours.size() ? "`" + c.forward.params[ours[i]].path + "`" : "none";
+            if (their_path != our_path) throw mismatch("a parameter path differs (checkpoint " + their_path + ", compiled file " + our_path + ")");
+            const msx::Param& p = c.forward.params[ours[i]];
+            if (p.ty.i32) throw mismatch("parameter `" + p.path + "` has dtype f32 in the checkpoint and i32 in the compiled file");
+            const uint64_t* shape = msx_checkpoint_shape(ckpt, 0, i);
+            std::vector<uint64_t> their_shape(shape, shape + msx_checkpoint_rank(ckpt, 0, i));
+            if (their_shape != p.ty.shape)
+                throw mismatch("parameter `" + p.path + "` has another shape (checkpoint " + shape_text(their_shape) + ", compiled file " + p.ty.str() + ")");
+        }
+        if (std::string(msx_checkpoint_schema_hash(ckpt)) != msx_training_schema_hash(t))
+            throw mismatch(std::string("the schema hash differs (checkpoint ") + msx_checkpoint_schema_hash(ckpt) + ", compiled file " + t->schema + ")");
+        // resume_into (checkpoint.rs:587-609): the optimizer is that of the compiled file.
+        int kind, their_kind;
+        double v[5], w[5];
+        uint64_t warmup, their_warmup;
+        optimizer_of(t, &kind, v, &warmup);
+        msx_checkpoint_optimizer(ckpt, &their_kind, &w[0], &w[1], &w[2], &w[3], &w[4], &their_warmup);
+        bool same = kind == their_kind && v[0] == w[0];
+        if (same && kind == MSX_OPTIMIZER_ADAMW) same = v[1] == w[1] && v[2] == w[2] && v[3] == w[3] && v[4] == w[4] && warmup == their_warmup;
+        if (!same) {
+            std::vector<char> text(msx_checkpoint_optimizer_json(ckpt, nullptr, 0));
+            msx_checkpoint_optimizer_json(ckpt, text.data(), text.size());
+            throw mismatch(std::string("the optimizer differs (checkpoint ") + text.data() + ")");
+        }
+        // The moments of an AdamW run: both of every parameter the step updates, or a step-0
+        // checkpoint, whose moments are zero.
+        const uint64_t step = msx_checkpoint_step(ckpt);
+        std::map<std::pair<std::string, std::string>, uint32_t> slots;
+        for (uint32_t i = 0; i < msx_checkpoint_count(ckpt, 1); ++i) slots[{msx_checkpoint_path(ckpt, 1, i), msx_checkpoint_slot(ckpt, 1, i)}] = i;
+        ok(t, msx_sync(t->step, 0));
+        for (uint32_t i = 0; i < ours.size(); ++i) {
+            const uint32_t p = ours[i];
+            const msx::Param& param = c.forward.params[p];
+            const uint64_t bytes = param.ty.count() * 4;
+            int rs = msx_param_upload(t->step, p, msx_checkpoint_data(ckpt, 0, i), bytes);
+            int rf = msx_param_upload(t->forward, p, msx_checkpoint_data(ckpt, 0, i), bytes);
+            if (rs != MSX_OK && rf != MSX_OK) continue;  // a parameter neither program reads
+            if (kind != MSX_OPTIMIZER_ADAMW) continue;
+            for (char which : {'m', 'v'}) {
+                auto it = slots.find({param.path, std::string(1, which)});
+                std::vector<float> zeros;
+                const float* data = nullptr;
+                if (it != slots.end()) {
+                    const uint64_t* shape = msx_checkpoint_shape(ckpt, 1, it->second);
+                    std::vector<uint64_t> their_shape(shape, shape + msx_checkpoint_rank(ckpt, 1, it->second));
+                    if (their_shape != param.ty.shape) throw mismatch("slot `" + std::string(1, which) + "` of `" + param.path + "` has another shape");
+                    data = msx_checkpoint_data(ckpt, 1, it->second);
+                } else if (step == 0) {
+                    zeros.assign(param.ty.count(), 0.0f);
+                    data = zeros.data();
+                } else {
+                    throw Fail{MSX_BAD_INPUT, "the checkpoint of step " + std::to_string(step) + " holds no first and second moments of `" + param.path +
+                                                  "`; an `adamw` run resumes only from a checkpoint that holds them, or from step 0"};
+                }
+                int rc = msx_moment_upload(t->step, p, which, data, bytes);
+                (void)rc;  // a parameter the step does not update has no moments
+            }
+        }
+        *start_step = step;
+    });
+}
 
 int msx_training_check_finite(msx_training* t) {
     if (!t) return MSX_BAD_ARGUMENT;
