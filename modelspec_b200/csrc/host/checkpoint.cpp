@@ -450,7 +450,10 @@ int msx_checkpoint_add(msx_checkpoint* c, const char* path, const char* slot, co
         t.shape.assign(shape, shape + rank);
         if (t.count() == 0) throw Refused{MSX_BAD_ARGUMENT, std::string("parameter `") + path + "` has a zero dimension"};
         t.data.assign(data, data + t.count());
-        (t.slot.empty() ? c->parameters : c->slots).push_back(std::move(t));
+        // Both lists stay in (path, slot) order, the order of the file.
+        std::vector<Tensor>& list = t.slot.empty() ? c->parameters : c->slots;
+        auto at = std::upper_bound(list.begin(), list.end(), t, [](const Tensor& a, const Tensor& b) { return a.path != b.path ? a.path < b.path : a.slot < b.slot; });
+        list.insert(at, std::move(t));
     });
 }
 
