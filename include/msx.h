@@ -337,6 +337,26 @@ uint64_t msx_training_prediction_count(const msx_training* training);
 int msx_training_infer(msx_training* training, float* prediction, uint64_t bytes, float* loss);
 uint64_t msx_training_infer_report(msx_training* training, char* out, uint64_t capacity);
 
+/* ---- restore and replay --------------------------------------------------------------------------
+ * The reference runs its steps in segments of several per submission, and when a step's loss is
+ * not finite it stops the run at that step with the parameters and moments after that step, as
+ * one step per submission leaves them: each segment first copies the state it starts from into a
+ * device buffer of its own, and the failing segment copies it back and runs its steps through the
+ * failing one again (crates/modelspec-runtime/src/vulkan/stepwise.rs:84-92, :1024-1082).
+ *
+ * msx_state_snapshot copies every parameter and moment of `plan` into a device buffer of the
+ * plan's (allocated by the first call), msx_state_restore copies them back (and rewrites the bf16
+ * working copies of a mixed-precision plan); both are ordered on the plan's stream and wait for
+ * nothing. msx_training_set_replay_window(training, n) takes a snapshot before every n-th step and
+ * keeps the batches of the steps since (n = 0, the default, takes none);
+ * msx_training_rewind(training, step) then leaves the run as it was after the update of `step`, a
+ * step at or after the last snapshot: snapshot restored, the steps from it through `step` run
+ * again on their own batches, tokens and scalars. The steps after `step` are forgotten. */
+int msx_state_snapshot(msx_plan* plan);
+int msx_state_restore(msx_plan* plan);
+int msx_training_set_replay_window(msx_training* training, uint32_t steps);
+int msx_training_rewind(msx_training* training, uint64_t step);
+
 /* ---- held-out evaluation (`--eval-every`) --------------------------------------------------------
  * Replaces the device side of the reference's held-out evaluation: every batch of the HeldOut
  * split runs the steps of the plan the prediction is computed from, dropout off, without the loss

@@ -145,6 +145,10 @@ SIGNATURES = {
     "msx_training_checkpoint": (C.c_int, [_P, C.c_uint64, C.POINTER(_P)]),
     "msx_training_resume": (C.c_int, [_P, _P, C.POINTER(C.c_uint64)]),
     "msx_training_schema_hash": (C.c_char_p, [_P]),
+    "msx_state_snapshot": (C.c_int, [_P]),
+    "msx_state_restore": (C.c_int, [_P]),
+    "msx_training_set_replay_window": (C.c_int, [_P, C.c_uint32]),
+    "msx_training_rewind": (C.c_int, [_P, C.c_uint64]),
     "msx_plan_run_stats": (C.c_int, [_P, _P]),
     "msx_stats_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
     "msx_profile_report": (C.c_uint64, [_P, _P, C.c_uint32, C.c_char_p, C.c_uint64]),
@@ -629,6 +633,14 @@ class Training:
         """Draws the HeldOut batches of the bound directory once; returns how many there are."""
         self.check(lib().msx_training_heldout_packed(self.h, self._packed.dir.encode()))
         return int(lib().msx_training_heldout_batches(self.h))
+
+    def set_replay_window(self, steps):
+        """Takes a device snapshot of the state before every `steps`-th step (0: none)."""
+        self.check(lib().msx_training_set_replay_window(self.h, steps))
+
+    def rewind(self, step):
+        """Leaves the run as it was after the update of `step` (restore the snapshot, replay)."""
+        self.check(lib().msx_training_rewind(self.h, step))
 
     def checkpoint(self, step):
         """The run's state after `step` updates as a Checkpoint (parameters, and AdamW moments)."""

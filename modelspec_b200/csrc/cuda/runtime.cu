@@ -141,6 +141,10 @@ struct msx_plan {
     // Mixed precision: the bf16 working copy of every matrix parameter, which the matmuls read; the
     // optimizer launch and msx_param_upload keep it equal to the rounded f32 master.
     std::vector<void*> params16;
+    // msx_state_snapshot: a copy of every parameter and moment, one allocation, made on first use.
+    float* backup = nullptr;
+    uint64_t backup_floats = 0;
+    bool backup_filled = false;
     std::vector<char> owns_param16;
     char* d_inputs = nullptr;
     uint64_t input_bytes = 0;
@@ -2357,6 +2361,7 @@ void release(msx_plan* P) {
         if (P->slot_begin[s]) cudaEventDestroy(P->slot_begin[s]);
         if (P->slot_done[s]) cudaEventDestroy(P->slot_done[s]);
     }
+    if (P->backup) cudaFree(P->backup);
     if (P->pinned_loss) cudaFreeHost(P->pinned_loss);
     if (P->pinned_status) cudaFreeHost(P->pinned_status);
     if (P->clock_start) cudaEventDestroy(P->clock_start);
@@ -2783,6 +2788,59 @@ int msx_moment_download(msx_plan* plan, uint32_t index, char which, void* host, 
     if (!plan || index >= plan->program.params.size() || (which != 'm' && which != 'v')) return MSX_BAD_ARGUMENT;
     return transfer(plan, (which == 'm' ? plan->m : plan->v)[index], msx_plan_param_bytes(plan, index), host, bytes, false,
                     "msx_moment_download");
+}
+
+}  // extern "C"
+
+// The state a later step overwrites: every parameter, then every moment, in parameter order.
+template <class F> static void for_each_state_tensor(msx_plan* plan, F visit) {
+    for (size_t p = 0; p < plan->program.params.size(); ++p) {
+        const uint64_t count = plan->program.params[p].ty.count();
+        if (plan->params[p]) visit(plan->params[p], count, static_cast<int>(p));
+        if (plan->m[p]) visit(plan->m[p], count, -1);
+        if (plan->v[p]) visit(plan->v[p], count, -1);
+    }
+}
+
+extern "C" {
+
+int msx_state_snapshot(msx_plan* plan) {
+    if (!plan) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        if (!plan->backup) {
+            uint64_t floats = 0;
+            for_each_state_tensor(plan, [&](float*, uint64_t count, int) { floats += (count + 3) / 4 * 4; });
+            cuda_ok(plan_malloc(plan, &plan->backup, std::max<uint64_t>(floats, 4) * 4), "cudaMalloc(state backup)");
+            plan->backup_floats = floats;
+        }
+        uint64_t at = 0;
+        for_each_state_tensor(plan, [&](float* from, uint64_t count, int) {
+            cuda_ok(cudaMemcpyAsync(plan->backup + at, from, count * 4, cudaMemcpyDeviceToDevice, plan->stream), "cudaMemcpyAsync(state backup)");
+            at += (count + 3) / 4 * 4;
+        });
+        plan->backup_filled = true;
+        return MSX_OK;
+    });
+}
+
+int msx_state_restore(msx_plan* plan) {
+    if (!plan) return MSX_BAD_ARGUMENT;
+    return guarded(plan->device, [&]() -> int {
+        if (!plan->backup_filled) throw StatusError(MSX_BAD_ARGUMENT, "msx_state_restore: no snapshot was taken");
+        cuda_ok(cudaSetDevice(plan->device->ordinal), "cudaSetDevice");
+        uint64_t at = 0;
+        for_each_state_tensor(plan, [&](float* to, uint64_t count, int param) {
+            cuda_ok(cudaMemcpyAsync(to, plan->backup + at, count * 4, cudaMemcpyDeviceToDevice, plan->stream), "cudaMemcpyAsync(state restore)");
+            at += (count + 3) / 4 * 4;
+            // The bf16 working copy follows its f32 master.
+            if (param >= 0 && plan->params16[static_cast<size_t>(param)])
+                k::working_copy(plan->stream, to, plan->params16[static_cast<size_t>(param)], count);
+        });
+        // The status word of the abandoned steps goes with them.
+        cuda_ok(cudaMemsetAsync(plan->d_status, 0, 4, plan->stream), "cudaMemsetAsync(status)");
+        return MSX_OK;
+    });
 }
 
 int msx_set_input(msx_plan* plan, const char* name, const void* host, uint64_t bytes) {

@@ -36,6 +36,14 @@ struct msx_training {
     std::vector<std::vector<float>> heldout_row_weights;  // per batch, once its targets are on the device
     std::set<std::string> predict_inputs;
     // A packed --data directory bound to the declarations (train/data.rs:1488-1500).
+    // Restore and replay (stepwise.rs:84-92): a snapshot before every `window`-th step, and what
+    // each step since was run on.
+    uint32_t window = 0;
+    struct Replayed {
+        uint64_t step, end;
+        std::map<std::string, std::vector<char>> batch;
+    };
+    std::vector<Replayed> since_snapshot;
     std::string schema;  // the schema hash of the training program's parameters, made on first use
     msx_packed* packed = nullptr;
     uint64_t packed_batch = 0;
@@ -281,29 +289,75 @@ int msx_training_synthetic(msx_training* t) {
     });
 }
 
+namespace {
+
+// Step `step` of a run that ends at `end`, on the current batch: the host inputs of the step
+// (stepwise.rs:475-543), then one submission.
+void submit_step(msx_training* t, uint64_t step, uint64_t end) {
+    const msx::Compiled& c = t->compiled;
+    if (c.config.rule == msx::Rule::AdamW) {
+        msx::StepScalars s = msx::adamw_scalars(c.config.adamw, c.config.lr, step + 1, end);
+        if (t->step_inputs.count("optimizer.lr_t")) {
+            ok(t, msx_set_input(t->step, "optimizer.lr_t", &s.lr_t, 4));
+            ok(t, msx_set_input(t->step, "optimizer.c1", &s.c1, 4));
+            ok(t, msx_set_input(t->step, "optimizer.c2", &s.c2, 4));
+        }
+    }
+    stage_batch(t, t->step, t->step_inputs);
+    gather_masked(t, step, true);
+    for (const std::string& site : t->sites) {
+        int32_t token[2];
+        msx::dropout_token(site, step, token);
+        ok(t, msx_set_input(t->step, site.c_str(), token, 8));
+    }
+    t->submitted_as[step] = msx_steps_submitted(t->step);
+    if (t->submitted_as.size() > 64) t->submitted_as.erase(t->submitted_as.begin());
+    ok(t, msx_run(t->step));
+    t->submitted = true;
+}
+
+}  // namespace
+
 int msx_training_step(msx_training* t, uint64_t step, uint64_t end) {
     if (!t) return MSX_BAD_ARGUMENT;
     return guarded(t, [&] {
-        const msx::Compiled& c = t->compiled;
-        if (c.config.rule == msx::Rule::AdamW) {
-            msx::StepScalars s = msx::adamw_scalars(c.config.adamw, c.config.lr, step + 1, end);
-            if (t->step_inputs.count("optimizer.lr_t")) {
-                ok(t, msx_set_input(t->step, "optimizer.lr_t", &s.lr_t, 4));
-                ok(t, msx_set_input(t->step, "optimizer.c1", &s.c1, 4));
-                ok(t, msx_set_input(t->step, "optimizer.c2", &s.c2, 4));
+        if (t->window) {
+            if (t->since_snapshot.empty() || t->since_snapshot.size() >= t->window) {
+                ok(t, msx_state_snapshot(t->step));
+                t->since_snapshot.clear();
             }
+            t->since_snapshot.push_back({step, end, t->batch});
         }
-        stage_batch(t, t->step, t->step_inputs);
-        gather_masked(t, step, true);
-        for (const std::string& site : t->sites) {
-            int32_t token[2];
-            msx::dropout_token(site, step, token);
-            ok(t, msx_set_input(t->step, site.c_str(), token, 8));
+        submit_step(t, step, end);
+    });
+}
+
+int msx_training_set_replay_window(msx_training* t, uint32_t steps) {
+    if (!t) return MSX_BAD_ARGUMENT;
+    t->window = steps;
+    t->since_snapshot.clear();
+    return MSX_OK;
+}
+
+int msx_training_rewind(msx_training* t, uint64_t step) {
+    if (!t) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        size_t last = t->since_snapshot.size();
+        for (size_t i = 0; i < t->since_snapshot.size(); ++i)
+            if (t->since_snapshot[i].step == step) last = i;
+        if (last == t->since_snapshot.size())
+            throw Fail{MSX_BAD_ARGUMENT, "step " + std::to_string(step) + " was not run since the last snapshot" +
+                                             (t->window ? "" : " (no replay window is set)")};
+        // The steps in flight finish first (their status, a wait that gave up included, is dropped
+        // with them), then the segment's start comes back and its steps run again through `step`.
+        msx_sync(t->step, 0);
+        ok(t, msx_state_restore(t->step));
+        t->since_snapshot.resize(last + 1);
+        for (const msx_training::Replayed& r : t->since_snapshot) {
+            t->batch = r.batch;
+            submit_step(t, r.step, r.end);
         }
-        t->submitted_as[step] = msx_steps_submitted(t->step);
-        if (t->submitted_as.size() > 64) t->submitted_as.erase(t->submitted_as.begin());
-        ok(t, msx_run(t->step));
-        t->submitted = true;
+        ok(t, msx_sync(t->step, 0));
     });
 }
 
