@@ -138,6 +138,12 @@ struct DropoutDraw {
     uint32_t threshold = 0;
     float scale = 1.0f;
     uint64_t index_base = 0;
+    // The keep decisions of the site as one bit per element, 32 consecutive columns of a row per
+    // word (rows of a multiple of 32 columns only). A launch that draws the site writes them when
+    // `bits` is set and `stored` is not; a later launch of the same step (the dropout_grad of the
+    // site) given `stored` reads them instead of drawing again. Null: every launch draws.
+    uint32_t* bits = nullptr;
+    bool stored = false;
 };
 // `adjoint_draw`, when not null: the adjoint is dropout_grad of that sum. `dx_draw` and `dx_dropped`,
 // when not null: dropout_grad of dx is written to dx_dropped beside dx. `pre_activation` and

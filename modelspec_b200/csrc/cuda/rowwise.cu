@@ -577,6 +577,70 @@ __device__ __forceinline__ void store_row(T* __restrict__ row, uint32_t lane, ui
     }
 }
 
+// The keep decisions of one row as the warp holds it (bit i of `mask` = item i of this lane) to
+// and from their stored form: word w of the row holds columns 32 w .. 32 w + 31, bit = column
+// modulo 32. The row has a multiple of 32 columns, at most 1,024: one word per lane.
+__device__ __forceinline__ uint32_t spread16(uint32_t x) {  // bit b of the low half to bit 2 b
+    x = (x | (x << 8)) & 0x00FF00FFu;
+    x = (x | (x << 4)) & 0x0F0F0F0Fu;
+    x = (x | (x << 2)) & 0x33333333u;
+    x = (x | (x << 1)) & 0x55555555u;
+    return x;
+}
+template <int ITEMS, int V>
+__device__ __forceinline__ void save_keep_bits(uint32_t* __restrict__ row_words, uint32_t lane, uint32_t h, uint32_t mask) {
+    uint32_t mine = 0;
+    if constexpr (V == 1) {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const uint32_t word = __ballot_sync(0xffffffffu, (mask >> i) & 1u);  // columns 32 i + lane
+            if (lane == static_cast<uint32_t>(i)) mine = word;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < ITEMS / 2; ++j) {
+            // Lane l holds columns 64 j + 2 l and + 1: lanes 0-15 fill word 2 j, lanes 16-31 word 2 j + 1.
+            const uint32_t even = __ballot_sync(0xffffffffu, (mask >> (2 * j)) & 1u), odd = __ballot_sync(0xffffffffu, (mask >> (2 * j + 1)) & 1u);
+            if (lane == static_cast<uint32_t>(2 * j)) mine = spread16(even & 0xffffu) | (spread16(odd & 0xffffu) << 1);
+            if (lane == static_cast<uint32_t>(2 * j + 1)) mine = spread16(even >> 16) | (spread16(odd >> 16) << 1);
+        }
+    }
+    if (lane < h / 32) row_words[lane] = mine;
+}
+template <int ITEMS, int V>
+__device__ __forceinline__ uint32_t load_keep_bits(const uint32_t* __restrict__ row_words, uint32_t lane, uint32_t h) {
+    const uint32_t mine = lane < h / 32 ? __ldg(row_words + lane) : 0u;
+    uint32_t mask = 0;
+    if constexpr (V == 1) {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) mask |= ((__shfl_sync(0xffffffffu, mine, i) >> lane) & 1u) << i;
+    } else {
+#pragma unroll
+        for (int j = 0; j < ITEMS / 2; ++j) {
+            const uint32_t word = __shfl_sync(0xffffffffu, mine, 2 * j + static_cast<int>(lane >> 4));
+            mask |= ((word >> (2 * (lane & 15u))) & 3u) << (2 * j);
+        }
+    }
+    return mask;
+}
+// The keep decisions of a row for one site: read when an earlier launch of the step stored them,
+// else drawn (element index_base + row h + column of Philox stream 4) and stored when asked.
+template <int ITEMS, int V>
+__device__ __forceinline__ uint32_t keep_mask(const DropoutDraw& draw, uint64_t row_at, uint32_t lane, uint32_t h) {
+    uint32_t* const row_words = draw.bits ? draw.bits + row_at / 32 : nullptr;
+    if (draw.stored && row_words != nullptr) return load_keep_bits<ITEMS, V>(row_words, lane, h);
+    const uint32_t id_lo = static_cast<uint32_t>(draw.token[0]), id_hi = static_cast<uint32_t>(draw.token[1]);
+    uint32_t mask = 0;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        const uint32_t w0 = philox_word0(static_cast<uint32_t>(draw.index_base + row_at + column_of<V>(i, lane)), 4u, id_lo, id_hi,
+                                         static_cast<uint32_t>(draw.seed), static_cast<uint32_t>(draw.seed >> 32));
+        mask |= (w0 >= draw.threshold ? 1u : 0u) << i;
+    }
+    if (row_words != nullptr) save_keep_bits<ITEMS, V>(row_words, lane, h, mask);
+    return mask;
+}
+
 // dropout(x) + residual, then layer_norm of the sum, one warp per row with the row in registers:
 // the three launches of a transformer sublayer's tail as one. Every element goes through the same
 // rounded operations as the separate kernels (the Philox draw of element index_base + r h + c, the
@@ -603,13 +667,9 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
         for (int i = 0; i < ITEMS; ++i) xs[i] = gelu_value(xs[i]);
     }
     if (x_draw.token != nullptr) {
-        const uint32_t id_lo = static_cast<uint32_t>(x_draw.token[0]), id_hi = static_cast<uint32_t>(x_draw.token[1]);
+        const uint32_t keep = keep_mask<ITEMS, V>(x_draw, base, lane, h);
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) {
-            const uint32_t w0 = philox_word0(static_cast<uint32_t>(x_draw.index_base + base + column_of<V>(i, lane)), 4u, id_lo, id_hi,
-                                             static_cast<uint32_t>(x_draw.seed), static_cast<uint32_t>(x_draw.seed >> 32));
-            xs[i] = w0 >= x_draw.threshold ? xs[i] * x_draw.scale : 0.0f;
-        }
+        for (int i = 0; i < ITEMS; ++i) xs[i] = (keep >> i) & 1u ? xs[i] * x_draw.scale : 0.0f;
     }
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
@@ -634,11 +694,7 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
             q = fmaf(d, d, q);
         }
     const float rstd = 1.0f / sqrtf(warp_sum(q) / width + kLayerNormEps);
-    uint32_t id_lo = 0, id_hi = 0;
-    if (out_dropped != nullptr) {
-        id_lo = static_cast<uint32_t>(out_draw.token[0]);
-        id_hi = static_cast<uint32_t>(out_draw.token[1]);
-    }
+    const uint32_t keep_out = out_dropped != nullptr ? keep_mask<ITEMS, V>(out_draw, base, lane, h) : 0u;
     float dropped[ITEMS];
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
@@ -646,12 +702,7 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
         const uint32_t cc = min(c, h - 1);
         const float y = (v[i] - mean) * rstd * gamma[cc] + beta[cc];
         v[i] = y;
-        dropped[i] = 0.0f;
-        if (out_dropped != nullptr && c < h) {
-            const uint32_t w0 = philox_word0(static_cast<uint32_t>(out_draw.index_base + base + c), 4u, id_lo, id_hi,
-                                             static_cast<uint32_t>(out_draw.seed), static_cast<uint32_t>(out_draw.seed >> 32));
-            dropped[i] = w0 >= out_draw.threshold ? y * out_draw.scale : 0.0f;
-        }
+        dropped[i] = (out_dropped != nullptr && c < h && ((keep_out >> i) & 1u)) ? y * out_draw.scale : 0.0f;
     }
     if (out != nullptr) store_row<ITEMS, V>(out + base, lane, h, v);
     if (out_dropped != nullptr) store_row<ITEMS, V>(out_dropped + base, lane, h, dropped);
@@ -732,13 +783,9 @@ __global__ void __launch_bounds__(256, ITEMS >= 16 ? 2 : 1) layer_norm_backward_
         // An adjoint that the program passes through dropout_grad first: the draw of element
         // (r, c), on the sum.
         if (adjoint_draw.token != nullptr) {
-            const uint32_t id_lo = static_cast<uint32_t>(adjoint_draw.token[0]), id_hi = static_cast<uint32_t>(adjoint_draw.token[1]);
+            const uint32_t keep = keep_mask<ITEMS, V>(adjoint_draw, row_at, lane, h);
 #pragma unroll
-            for (int i = 0; i < ITEMS; ++i) {
-                const uint32_t w0 = philox_word0(static_cast<uint32_t>(adjoint_draw.index_base + row_at + column_of<V>(i, lane)), 4u, id_lo, id_hi,
-                                                 static_cast<uint32_t>(adjoint_draw.seed), static_cast<uint32_t>(adjoint_draw.seed >> 32));
-                gv[i] = w0 >= adjoint_draw.threshold ? gv[i] * adjoint_draw.scale : 0.0f;
-            }
+            for (int i = 0; i < ITEMS; ++i) gv[i] = (keep >> i) & 1u ? gv[i] * adjoint_draw.scale : 0.0f;
         }
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i)
@@ -781,6 +828,7 @@ __global__ void __launch_bounds__(256, ITEMS >= 16 ? 2 : 1) layer_norm_backward_
             float pre[ITEMS];
             if (pre_activation != nullptr) load_row<ITEMS, V>(pre_activation + row_at, lane, h, pre);
             float second[ITEMS];
+            const uint32_t keep_dx = (pre_activation == nullptr && dx_dropped != nullptr) ? keep_mask<ITEMS, V>(dx_draw, row_at, lane, h) : 0u;
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
                 const uint32_t c = column_of<V>(i, lane);
@@ -795,10 +843,7 @@ __global__ void __launch_bounds__(256, ITEMS >= 16 ? 2 : 1) layer_norm_backward_
                 if (pre_activation != nullptr) {
                     second[i] = gelu_grad_value(pre[i], value);
                 } else if (dx_dropped != nullptr && c < h) {
-                    const uint32_t w0 = philox_word0(static_cast<uint32_t>(dx_draw.index_base + row_at + c), 4u,
-                                                     static_cast<uint32_t>(dx_draw.token[0]), static_cast<uint32_t>(dx_draw.token[1]),
-                                                     static_cast<uint32_t>(dx_draw.seed), static_cast<uint32_t>(dx_draw.seed >> 32));
-                    second[i] = w0 >= dx_draw.threshold ? value * dx_draw.scale : 0.0f;
+                    second[i] = (keep_dx >> i) & 1u ? value * dx_draw.scale : 0.0f;
                 }
             }
             if (dx != nullptr) store_row<ITEMS, V>(dx + row_at, lane, h, xv);

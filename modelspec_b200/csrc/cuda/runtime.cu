@@ -95,7 +95,7 @@ static NcclApi g_nccl;
 // A contiguous run of gradient bytes that is summed across ranks by one all-reduce, issued on
 // the side stream as soon as the launch that writes its last gradient has been enqueued.
 #ifndef MSX_DEFAULT_FUSIONS
-#define MSX_DEFAULT_FUSIONS 63u
+#define MSX_DEFAULT_FUSIONS 127u
 #endif
 
 struct Bucket {
@@ -276,7 +276,9 @@ void close_peer_reduce(msx_plan* P);
 // (dropout + residual + layer norm), 2 adjoint sums inside layer-norm backward, 4 weight-gradient
 // matmuls as jobs of one launch, 8 heavy launches with late readers on a side stream, 16
 // dropout_grad inside the layer-norm backward that makes or reads its operand, 32 the fused
-// attention kernels of a mixed-precision plan (off: batched products with row kernels between).
+// attention kernels of a mixed-precision plan (off: batched products with row kernels between),
+// 64 the keep decisions of a dropout site stored by the forward launch that draws them, one bit
+// per element, and read by the site's dropout_grad (off: every launch draws again).
 inline uint32_t fusion_mask() {
     static const uint32_t mask = [] {
         const char* text = std::getenv("MSX_FUSE");
@@ -1319,10 +1321,14 @@ struct Scheduler {
                                     make_arena(slot, node(made));
                                 }
                                 const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
-                                emit("dropout_add_layer_norm", nd, {x, token, residual, gamma, beta}, {add_at, ln_at}, [=](cudaStream_t s) {
-                                    k::dropout_add_layer_norm(s, plan->in(x), plan->in(residual), plan->i(token), plan->seed, threshold, scale,
-                                                              plan->shard_rows_before * row_width, plan->f(gamma), plan->f(beta),
-                                                              plan->out(add_at), plan->out(ln_at), r, h);
+                                Draw draw = draw_of(at);
+                                std::vector<uint32_t> made = {add_at, ln_at};
+                                const int bits = store_bits(draw, r, h);
+                                if (bits >= 0) made.push_back(static_cast<uint32_t>(bits));
+                                emit("dropout_add_layer_norm", nd, {x, token, residual, gamma, beta}, made, [=](cudaStream_t s) {
+                                    const k::DropoutDraw first = launch_draw(plan, draw, h);
+                                    k::add_layer_norm(s, plan->in(x), plan->in(residual), &first, plan->f(gamma), plan->f(beta), plan->out(add_at),
+                                                      plan->out(ln_at), nullptr, k::Out(), r, h);
                                 });
                                 break;
                             }
@@ -1332,8 +1338,11 @@ struct Scheduler {
                             Slot& slot = P->slots[add_at];
                             make_arena(slot, add);
                             const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
-                            const Draw draw = draw_of(at);
-                            emit("dropout_add", nd, {x, token, residual}, {add_at}, [=](cudaStream_t s) {
+                            Draw draw = draw_of(at);
+                            std::vector<uint32_t> made = {add_at};
+                            const int bits = store_bits(draw, r, h);
+                            if (bits >= 0) made.push_back(static_cast<uint32_t>(bits));
+                            emit("dropout_add", nd, {x, token, residual}, made, [=](cudaStream_t s) {
                                 const k::DropoutDraw first = launch_draw(plan, draw, h);
                                 k::add_layer_norm(s, plan->in(x), plan->in(residual), &first, nullptr, nullptr, plan->out(add_at), k::Out(), nullptr,
                                                   k::Out(), r, h);
@@ -1446,6 +1455,11 @@ struct Scheduler {
         }
         msx_plan* plan = P;
         const uint64_t r = nd.ty.shape[0], h = nd.ty.shape[1];
+        if (dropout >= 0) {
+            // The decisions of the dropout behind the layer norm, kept for its gradient.
+            const int bits = store_bits(draw, r, h);
+            if (bits >= 0) writes.push_back(static_cast<uint32_t>(bits));
+        }
         emit(dropout >= 0 ? "add_layer_norm_dropout" : "add_layer_norm", nd, reads, writes, [=](cudaStream_t s) {
             const k::DropoutDraw second = launch_draw(plan, draw, h);
             k::add_layer_norm(s, plan->in(a), plan->in(b), nullptr, plan->f(gamma), plan->f(beta), plan->out(at),
@@ -1457,7 +1471,29 @@ struct Scheduler {
 
     // The draw of a Dropout or DropoutGrad node as a fused launch takes it: the token's position
     // now, its address, the seed and the shard's first element when the launch is issued.
-    struct Draw { int token = -1; uint32_t threshold = 0; float scale = 1.0f; };
+    struct Draw { int token = -1; uint32_t threshold = 0; float scale = 1.0f; int bits = -1; bool stored = false; };
+    // The keep decisions a forward launch stored for the dropout_grad of the same site: by the
+    // site's token input, the scratch slot of the bits and the shape they were drawn for.
+    struct KeptBits { uint32_t slot; uint64_t rows, width; };
+    std::map<int, KeptBits> kept_bits;
+    // A forward launch that draws `d` on [rows, width] stores its decisions (fusion bit 64) when a
+    // row kernel can hold them a word per lane; the returned scratch slot joins the launch's writes.
+    int store_bits(Draw& d, uint64_t rows, uint64_t width) {
+        if (!(fusion_mask() & 64u) || d.token < 0 || width % 32 != 0 || width > 1024 || rows == 0 || kept_bits.count(d.token)) return -1;
+        const uint32_t slot = scratch(rows * width / 8);
+        kept_bits[d.token] = {slot, rows, width};
+        d.bits = static_cast<int>(slot);
+        d.stored = false;
+        return d.bits;
+    }
+    // The dropout_grad of a site whose decisions were stored reads them; the slot joins the reads.
+    int stored_bits(Draw& d, uint64_t rows, uint64_t width) const {
+        auto kept = d.token < 0 ? kept_bits.end() : kept_bits.find(d.token);
+        if (kept == kept_bits.end() || kept->second.rows != rows || kept->second.width != width) return -1;
+        d.bits = static_cast<int>(kept->second.slot);
+        d.stored = true;
+        return d.bits;
+    }
     Draw draw_of(uint32_t dropout) const {
         const Node& d = node(dropout);
         Draw draw;
@@ -1474,6 +1510,10 @@ struct Scheduler {
         draw.threshold = d.threshold;
         draw.scale = d.scale;
         draw.index_base = plan->shard_rows_before * row_width;
+        if (d.bits >= 0) {
+            draw.bits = static_cast<uint32_t*>(plan->ptr(static_cast<uint32_t>(d.bits)));
+            draw.stored = d.stored;
+        }
         return draw;
     }
 
@@ -1558,6 +1598,10 @@ struct Scheduler {
         if (gamma >= 0) reads.push_back(static_cast<uint32_t>(gamma));
         if (adjoint_draw.token >= 0) reads.push_back(static_cast<uint32_t>(adjoint_draw.token));
         if (dx_draw.token >= 0) reads.push_back(static_cast<uint32_t>(dx_draw.token));
+        for (Draw* d : {&adjoint_draw, &dx_draw}) {
+            const int bits = stored_bits(*d, r, h);
+            if (bits >= 0) reads.push_back(static_cast<uint32_t>(bits));
+        }
         if (pre_activation >= 0) reads.push_back(static_cast<uint32_t>(pre_activation));
         if (!store_dx) {
             handled[static_cast<uint32_t>(dx)] = 1;

@@ -115,7 +115,7 @@ def test_bert_tiny_step_schedule():
     # on the dx that three of them write, and on the summed adjoint that the embedding's reads.
     assert kernels.count("dropout") == 1
     backward = [l for l in listing.strip().splitlines() if l.split()[1] == "layer_norm_backward"]
-    assert max(len(l.split("reads")[1].split("writes")[0].split()) for l in backward) == 7  # x, four addends, gamma, token
+    assert max(len(l.split("reads")[1].split("writes")[0].split()) for l in backward) == 8  # x, four addends, gamma, token, the site's stored keep decisions
     assert sum(1 for l in backward if l.split("writes")[1].count("%") == 2) == 3
     assert sum(1 for l in backward if l.split("writes")[1].count("%") == 1) == 3  # one of them the gelu gradient alone
     assert "[4096, 30522]" not in listing

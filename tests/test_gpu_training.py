@@ -229,3 +229,23 @@ def test_a_non_finite_loss_is_reported_not_trained_through(device):
         assert err.value.status == M.NON_FINITE and "LinearReg.w" in str(err.value)
     finally:
         t.destroy()
+
+
+def test_stored_dropout_decisions_give_the_bits_of_drawing_them_again(device):
+    """MSX_FUSE bit 64: the backward launches read the keep decisions the forward launches stored
+    instead of drawing them again. Same decisions, same arithmetic: every loss and every parameter
+    and moment after four steps has the same bits with the bit on and off, in both precisions."""
+    import json
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    results = []
+    for mask in ("63", "127"):
+        env = dict(os.environ, MSX_FUSE=mask, PYTHONPATH=os.pathsep.join([os.path.dirname(here), here, os.environ.get("PYTHONPATH", "")]))
+        done = subprocess.run([sys.executable, os.path.join(here, "fuse_worker.py")], env=env, capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        results.append(json.loads(done.stdout.strip().splitlines()[-1]))
+    for precision in ("f32", "bf16"):
+        assert results[0][precision]["losses"] == results[1][precision]["losses"], precision
+        assert results[0][precision]["state"] == results[1][precision]["state"], precision
