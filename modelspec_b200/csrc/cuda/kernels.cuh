@@ -123,10 +123,10 @@ void layer_norm_grad_gamma(cudaStream_t s, const float* x, const float* g, float
 // `scratch` holds layer_norm_backward_scratch_floats(rows, h) floats; `counter` is one word that
 // is zero before the first launch and left zero by every launch.
 // With `counter` null the chunk sums stay in `scratch` for finalize_sums: dgamma's as
-// scratch[chunk][h], dbeta's after them, layer_norm_backward_chunks(rows) chunks each; the dgamma
+// scratch[chunk][h], dbeta's after them, layer_norm_backward_chunks(rows, h) chunks each; the dgamma
 // and dbeta pointers then only say which are wanted.
 bool layer_norm_backward_supported(uint64_t h);
-uint32_t layer_norm_backward_chunks(uint64_t rows);
+uint32_t layer_norm_backward_chunks(uint64_t rows, uint64_t h);
 uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h);
 // g1, g2, g3, when not null, are further addends of the adjoint: the kernel reads ((g + g1) + g2) + g3
 // where the program has a chain of Adds that nothing else reads.

@@ -14,6 +14,9 @@ uint32_t sum_rows_chunks(uint64_t rows);
 
 namespace {
 
+#ifndef MSX_LN_BACKWARD_WIDE_BLOCKS
+#define MSX_LN_BACKWARD_WIDE_BLOCKS 296
+#endif
 #ifndef MSX_LN_BACKWARD_BLOCKS
 #define MSX_LN_BACKWARD_BLOCKS 444
 #endif
@@ -930,10 +933,13 @@ void launch_cross_entropy_one_read(cudaStream_t s, const bf16* logits, const int
                                                                                                 grad, vv, l1, l2, counter, loss);
 }
 
-uint32_t backward_chunks(uint64_t rows) {
+uint32_t backward_chunks(uint64_t rows, uint64_t h) {
     // Three blocks per SM: a warp walks its rows one after another, each row a chain of loads and
-    // three warp reductions, so it is the number of warps in flight that hides that latency.
-    uint64_t per = (rows + MSX_LN_BACKWARD_BLOCKS - 1) / MSX_LN_BACKWARD_BLOCKS;
+    // three warp reductions, so it is the number of warps in flight that hides that latency. Rows
+    // of more than 256 elements keep their column sums in shared memory, two blocks per SM: one wave
+    // of 296 blocks instead of a full wave and a half one.
+    const uint64_t blocks = h > 256 ? MSX_LN_BACKWARD_WIDE_BLOCKS : MSX_LN_BACKWARD_BLOCKS;
+    uint64_t per = (rows + blocks - 1) / blocks;
     if (per < 8) per = 8;
     uint64_t chunks = (rows + per - 1) / per;
     return static_cast<uint32_t>(chunks < 1 ? 1 : chunks);
@@ -1040,15 +1046,15 @@ void dropout_add_layer_norm(cudaStream_t s, In x, In residual, const int32_t* to
 }
 
 bool layer_norm_backward_supported(uint64_t h) { return h >= 1 && h <= 1024; }
-uint32_t layer_norm_backward_chunks(uint64_t rows) { return backward_chunks(rows); }
-uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h) { return 2ull * backward_chunks(rows) * h; }
+uint32_t layer_norm_backward_chunks(uint64_t rows, uint64_t h) { return backward_chunks(rows, h); }
+uint64_t layer_norm_backward_scratch_floats(uint64_t rows, uint64_t h) { return 2ull * backward_chunks(rows, h) * h; }
 
 namespace {
 template <class T>
 void launch_layer_norm_backward(cudaStream_t s, const T* x, const float* gamma, const T* g, T* dx, float* scratch, uint32_t* counter,
                                 float* dgamma, float* dbeta, uint64_t rows, uint64_t h, const T* g1, const T* g2, const T* g3,
                                 const DropoutDraw& in_draw, const DropoutDraw& out_draw, T* dx_dropped, const T* pre_activation) {
-    uint32_t chunks = backward_chunks(rows);
+    uint32_t chunks = backward_chunks(rows, h);
     uint32_t per = static_cast<uint32_t>((rows + chunks - 1) / chunks);
     uint32_t items = static_cast<uint32_t>((h + 31) / 32);
     uint32_t r = static_cast<uint32_t>(rows), hh = static_cast<uint32_t>(h);

@@ -1629,7 +1629,7 @@ struct Scheduler {
             if (stored_dx >= 0) now.push_back(static_cast<uint32_t>(stored_dx));
             if (dropped >= 0) now.push_back(static_cast<uint32_t>(dropped));
             now.push_back(tmp);
-            const uint32_t chunks = k::layer_norm_backward_chunks(r);
+            const uint32_t chunks = k::layer_norm_backward_chunks(r, h);
             if (dgamma >= 0) deferred.push_back({tmp, 0, chunks, h, static_cast<uint32_t>(dgamma)});
             if (dbeta >= 0) deferred.push_back({tmp, static_cast<uint64_t>(chunks) * h, chunks, h, static_cast<uint32_t>(dbeta)});
             float* const wanted = reinterpret_cast<float*>(uintptr_t{1});  // only null or not is read
