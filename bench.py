@@ -31,6 +31,20 @@ METRIC = "train_steps_per_sec"
 UNIT = "steps/s (batches of 32 sequences, whole job)"
 
 
+
+_LINE_OUT = None  # the descriptor standard output had when the process started (set in main)
+
+
+def emit_line(record):
+    """The one JSON line of a run, on the process's original standard output."""
+    data = (json.dumps(record) + "\n").encode()
+    if _LINE_OUT is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_LINE_OUT, data)
+
+
 def workload(name):
     cfg = models.CONFIGS[name]
     if cfg["kind"] != "bert":
@@ -138,14 +152,14 @@ def reference_arm(args, cfg):
     value = 1.0 / sec
     sample = ("%d steps (%d warm-up) of one GPU's share of the workload, 32 sequences a step, on the CPU port of the "
               "reference interpreter with %d threads (the interpreter itself is single-threaded)" % (steps, warm, threads))
-    print(json.dumps({
+    emit_line({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": sec * 1e3, "median_ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": config_of(args, cfg, args.gpus, masked),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
+    })
 
 
 def dp_parity(M, dist, rank, world, local):
@@ -216,6 +230,12 @@ def main():
     ap.add_argument("--blocks", type=int, default=7, help="how many times the block of --steps steps is timed")
     ap.add_argument("--flags", type=int, default=0, help="plan flags (modelspec_b200.PLAN_*)")
     args = ap.parse_args()
+    # Standard output carries the one JSON line and nothing else: what libraries print there (NCCL
+    # announces its version on stdout) goes to standard error from here on.
+    global _LINE_OUT
+    sys.stdout.flush()
+    _LINE_OUT = os.dup(1)
+    os.dup2(2, 1)
     cfg = workload(args.config)
     if args.impl == "reference":
         reference_arm(args, cfg)
@@ -408,7 +428,7 @@ def main():
                 "gradient_exchange": "peer memory" if M.lib().msx_comm_uses_peer_memory(plan.h) else "nccl",
                 "exposed_comm_ms": exposed_comm_ms}
             line["dp_parity"] = parity
-        print(json.dumps(line))
+        emit_line(line)
     run.destroy()
     device.close()
     if dist is not None:
