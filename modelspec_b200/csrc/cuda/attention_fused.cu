@@ -115,10 +115,13 @@ __device__ __forceinline__ void store_part_bf16(void* base, uint64_t element, co
 }
 
 // ---- forward --------------------------------------------------------------------------------------
-// Shared memory: Q, two stages of K, V, P as two tiles (112 KB), then barriers and the exchange of
-// row maxima and sums between the four threads of a row.
-// Tensor memory: S of even key tiles at columns [0, 128), of odd ones at [128, 256), P V at [256, 320).
-constexpr uint32_t FWD_TILES = 7 * TILE_BYTES;
+// Shared memory: Q, two stages of K, V, two stages of P (two tiles each): 128 KB, then barriers and
+// the exchange of row maxima and sums between the four threads of a row.
+// Tensor memory: S of even key tiles at columns [0, 128), of odd ones at [128, 256); P V of even key
+// tiles at [256, 320), of odd ones at [320, 384). P and P V are double-buffered so that the rows
+// add P_j V_j to their result one key tile late, after the softmax of tile j + 1: the product's
+// latency is off their path.
+constexpr uint32_t FWD_TILES = 8 * TILE_BYTES;
 constexpr uint32_t FWD_SMEM = FWD_TILES + 1024 /* alignment slack */ + 256 /* barriers */ + 2 * 4 * TILE * 4 /* row exchange */;
 constexpr uint32_t FWD_TMEM = 512;
 
@@ -130,9 +133,9 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     char* q_tile = tiles;
     auto k_tile = [&](uint32_t stage) { return tiles + (1 + stage) * TILE_BYTES; };
     char* v_tile = tiles + 3 * TILE_BYTES;
-    char* p_tile = tiles + 4 * TILE_BYTES;  // two tiles: keys 0-63 and 64-127 of the key tile
+    auto p_tile = [&](uint32_t stage) { return tiles + (4 + 2 * stage) * TILE_BYTES; };  // two tiles a stage: keys 0-63 and 64-127 of the key tile
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + FWD_TILES);
-    enum { Q_FULL, K_FULL0, K_FULL1, K_EMPTY0, K_EMPTY1, V_FULL, V_EMPTY, S_FULL0, S_FULL1, P_READY, PV_FULL, ROWS_MET, BARS };
+    enum { Q_FULL, K_FULL0, K_FULL1, K_EMPTY0, K_EMPTY1, V_FULL, V_EMPTY, S_FULL0, S_FULL1, P_READY, PV_FULL0, PV_FULL1, ROWS_MET, BARS };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BARS);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
     float* exchange = reinterpret_cast<float*>(tiles + FWD_TILES + 256);  // [2][4 column chunks][128 rows]
@@ -223,10 +226,10 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // keys), 16 rows (2048 bytes) of the V tile.
 #pragma unroll
                 for (uint32_t ks = 0; ks < 8; ++ks)
-                    mma_bf16(tmem_pv, tile_descriptor(smem_u32(p_tile) + (ks >> 2) * TILE_BYTES + (ks & 3u) * 32, 16),
+                    mma_bf16(tmem_pv + ph * 64, tile_descriptor(smem_u32(p_tile(ph)) + (ks >> 2) * TILE_BYTES + (ks & 3u) * 32, 16),
                              tile_descriptor(smem_u32(v_tile) + ks * 2048, TILE_BYTES), idesc_pv, ks != 0);
                 mma_commit(bar(V_EMPTY));
-                mma_commit(bar(PV_FULL));
+                mma_commit(bar(PV_FULL0 + ph));
             }
             __syncwarp();
         }
@@ -258,8 +261,24 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int c = 0; c < 4; ++c) all[c] = slot[c * TILE + t];
             return true;
         };
+        // P_j V_j is added one key tile late (after the softmax of tile j + 1), with the factor by
+        // which the maximum moved at tile j: o_j = o_j-1 * shrink_j + P_j V_j.
+        float pending_shrink = 0.0f;
+        auto add_product = [&](uint32_t j) -> bool {
+            bool ok = mbar_wait(bar(PV_FULL0 + (j & 1u)), (j >> 1) & 1u, abort_flag, args.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t pv[16];
+            tmem_load16(tmem_pv + (j & 1u) * 64 + lane_base + chunk * 16, pv);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < 16; ++c) o[c] = o[c] * pending_shrink + __uint_as_float(pv[c]);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            return true;
+        };
         for (uint32_t j = 0; j < key_tiles; ++j) {
-            const uint32_t ph = j & 1u, stage = j & 1u;
+            const uint32_t stage = j & 1u;
             const uint32_t counts = keys_that_count(args.mask, seq, j * TILE + chunk * 32, args.k_len, lane);
             alive = mbar_wait(bar(S_FULL0 + stage), (j >> 1) & 1u, abort_flag, args.status);
             alive = __all_sync(0xffffffffu, alive);
@@ -289,23 +308,20 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             total = total * shrink + tile_total;
             best = new_best;
-            // The P tiles are free: P_j-1 V_j-1 was complete before this thread read its result.
-            store_chunk_bf16(p_tile, t, chunk, sc);
+            // This stage of P is free: P_j-2 V_j-2 was complete before this thread added it, a tile ago.
+            store_chunk_bf16(p_tile(stage), t, chunk, sc);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(P_READY));
-            alive = mbar_wait(bar(PV_FULL), ph, abort_flag, args.status);
-            alive = __all_sync(0xffffffffu, alive);
-            if (!alive) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t pv[16];
-            tmem_load16(tmem_pv + lane_base + chunk * 16, pv);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < 16; ++c) o[c] = o[c] * shrink + __uint_as_float(pv[c]);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            // The product of the tile before, which ran under this tile's softmax.
+            if (j > 0) {
+                alive = add_product(j - 1);
+                if (!alive) break;
+            }
+            pending_shrink = shrink;
         }
+        if (alive && key_tiles > 0) alive = add_product(key_tiles - 1);
         if (alive) {
             float parts[4];
             alive = exchange_with_row(total, parts);
