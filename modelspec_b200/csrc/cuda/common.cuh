@@ -119,6 +119,27 @@ __device__ __forceinline__ float gelu_grad_value(float x, float g) {
     return (s + 2.0f * (s * x) * r * slope) * g;
 }
 
+// The same two functions where the result is stored as bf16 (mixed-precision plans, which have no
+// reference bits to keep): the hardware exponential and reciprocal, about 2^-21 relative, far
+// inside the 2^-9 of the stored value, and r = 1 - s instead of a second exponential. Half the
+// special-function work per element: gelu_grad over a [16384, 3072] matrix is otherwise bound by
+// it, not by memory.
+__device__ __forceinline__ float logistic_fast(float v) { return __fdividef(1.0f, 1.0f + __expf(0.0f - v)); }
+template <class T> __device__ __forceinline__ float gelu_value_for(float x) {
+    if constexpr (sizeof(T) == 2) return x * logistic_fast(gelu_twice_inner(x));
+    else return gelu_value(x);
+}
+template <class T> __device__ __forceinline__ float gelu_grad_value_for(float x, float g) {
+    if constexpr (sizeof(T) == 2) {
+        const float scale = 0.7978845608028654f, cubic = 0.044715f;
+        const float s = logistic_fast(gelu_twice_inner(x)), r = 1.0f - s;
+        const float slope = scale * (1.0f + 3.0f * cubic * x * x);
+        return (s + 2.0f * (s * x) * r * slope) * g;
+    } else {
+        return gelu_grad_value(x, g);
+    }
+}
+
 // ---- Philox4x32-10, word 0 of the block ------------------------------------------------------
 // Counter [c0, c1, c2, c3], key [k0, k1] (Salmon et al., SC 2011); the reference draws a dropout
 // decision from word 0 alone (crates/modelspec-runtime/src/train/init.rs:91-112, :160-165).

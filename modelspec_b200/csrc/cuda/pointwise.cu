@@ -59,11 +59,11 @@ __global__ void binary_kernel(Binary op, const float* __restrict__ a, const floa
     }
 }
 
-__device__ __forceinline__ float apply(Unary op, float x) {
+template <class T> __device__ __forceinline__ float apply_as(Unary op, float x) {
     switch (op) {
         case Unary::Relu: return x > 0.0f ? x : 0.0f;
         case Unary::Sqrt: return sqrtf(x);
-        case Unary::Gelu: return gelu_value(x);
+        case Unary::Gelu: return gelu_value_for<T>(x);
         default: return x;
     }
 }
@@ -78,11 +78,11 @@ __global__ void unary_kernel(Unary op, const T* __restrict__ a, T* __restrict__ 
             const uint64_t n8 = n / 8;
             for (uint64_t j = i; j < n8; j += stride) {
                 float8 v = load8(a + 8 * j);
-                v.lo.x = apply(op, v.lo.x); v.lo.y = apply(op, v.lo.y); v.lo.z = apply(op, v.lo.z); v.lo.w = apply(op, v.lo.w);
-                v.hi.x = apply(op, v.hi.x); v.hi.y = apply(op, v.hi.y); v.hi.z = apply(op, v.hi.z); v.hi.w = apply(op, v.hi.w);
+                v.lo.x = apply_as<T>(op, v.lo.x); v.lo.y = apply_as<T>(op, v.lo.y); v.lo.z = apply_as<T>(op, v.lo.z); v.lo.w = apply_as<T>(op, v.lo.w);
+                v.hi.x = apply_as<T>(op, v.hi.x); v.hi.y = apply_as<T>(op, v.hi.y); v.hi.z = apply_as<T>(op, v.hi.z); v.hi.w = apply_as<T>(op, v.hi.w);
                 store8(out + 8 * j, v);
             }
-            for (uint64_t j = n8 * 8 + i; j < n; j += stride) store1(out + j, apply(op, load1(a + j)));
+            for (uint64_t j = n8 * 8 + i; j < n; j += stride) store1(out + j, apply_as<T>(op, load1(a + j)));
             return;
         }
     }
@@ -90,20 +90,20 @@ __global__ void unary_kernel(Unary op, const T* __restrict__ a, T* __restrict__ 
     uint64_t n4 = vec ? n / 4 : 0;
     for (uint64_t j = i; j < n4; j += stride) {
         float4 v = load4(a + 4 * j);
-        v.x = apply(op, v.x);
-        v.y = apply(op, v.y);
-        v.z = apply(op, v.z);
-        v.w = apply(op, v.w);
+        v.x = apply_as<T>(op, v.x);
+        v.y = apply_as<T>(op, v.y);
+        v.z = apply_as<T>(op, v.z);
+        v.w = apply_as<T>(op, v.w);
         store4(out + 4 * j, v);
     }
-    for (uint64_t j = n4 * 4 + i; j < n; j += stride) store1(out + j, apply(op, load1(a + j)));
+    for (uint64_t j = n4 * 4 + i; j < n; j += stride) store1(out + j, apply_as<T>(op, load1(a + j)));
 }
 
 template <bool GELU, class T>
 __global__ void act_grad_kernel(const T* __restrict__ a, const T* __restrict__ g,
                                 T* __restrict__ out, uint64_t n) {
     uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-    auto one = [](float x, float gg) { return GELU ? gelu_grad_value(x, gg) : (x > 0.0f ? gg : 0.0f); };
+    auto one = [](float x, float gg) { return GELU ? gelu_grad_value_for<T>(x, gg) : (x > 0.0f ? gg : 0.0f); };
     if constexpr (sizeof(T) == 2) {
         // bf16: 16 bytes (eight elements) of each array per thread and turn.
         if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(g)) % 16 == 0) {
@@ -116,6 +116,19 @@ __global__ void act_grad_kernel(const T* __restrict__ a, const T* __restrict__ g
                 store8(out + 8 * j, r);
             }
             for (uint64_t j = n8 * 8 + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n; j += stride)
+                store1(out + j, one(load1(a + j), load1(g + j)));
+            return;
+        }
+    }
+    if constexpr (sizeof(T) == 4) {
+        // f32: 16 bytes (four elements) of each array per thread and turn.
+        if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(g)) % 16 == 0) {
+            const uint64_t n4 = n / 4;
+            for (uint64_t j = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n4; j += stride) {
+                const float4 x = load4(a + 4 * j), gg = load4(g + 4 * j);
+                store4(out + 4 * j, make_float4(one(x.x, gg.x), one(x.y, gg.y), one(x.z, gg.z), one(x.w, gg.w)));
+            }
+            for (uint64_t j = n4 * 4 + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n; j += stride)
                 store1(out + j, one(load1(a + j), load1(g + j)));
             return;
         }
@@ -195,7 +208,7 @@ void unary(cudaStream_t s, Unary op, In a, Out out, uint64_t n) {
 
 void relu_grad(cudaStream_t s, const float* a, const float* g, float* out, uint64_t n) {
     if (n == 0) return;
-    act_grad_kernel<false, float><<<blocks_for(n), kThreads, 0, s>>>(a, g, out, n);
+    act_grad_kernel<false, float><<<blocks_for((n + 3) / 4), kThreads, 0, s>>>(a, g, out, n);
     check_launch("relu_grad");
 }
 
@@ -205,7 +218,7 @@ void gelu_grad(cudaStream_t s, In a, In g, Out out, uint64_t n) {
         act_grad_kernel<true, bf16><<<blocks_for((n + 7) / 8), kThreads, 0, s>>>(static_cast<const bf16*>(a.p), static_cast<const bf16*>(g.p),
                                                                        static_cast<bf16*>(out.p), n);
     else
-        act_grad_kernel<true, float><<<blocks_for(n), kThreads, 0, s>>>(a.f32(), g.f32(), out.f32(), n);
+        act_grad_kernel<true, float><<<blocks_for((n + 3) / 4), kThreads, 0, s>>>(a.f32(), g.f32(), out.f32(), n);
     check_launch("gelu_grad");
 }
 

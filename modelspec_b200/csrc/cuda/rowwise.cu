@@ -667,7 +667,7 @@ __global__ void __launch_bounds__(256) dropout_add_layer_norm_kernel(
     // gelu(x) in the place of the sum (the head's transform: dense, gelu, layer norm).
     if (gelu_first) {
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) xs[i] = gelu_value(xs[i]);
+        for (int i = 0; i < ITEMS; ++i) xs[i] = gelu_value_for<T>(xs[i]);
     }
     if (x_draw.token != nullptr) {
         const uint32_t keep = keep_mask<ITEMS, V>(x_draw, base, lane, h);
@@ -844,7 +844,7 @@ __global__ void __launch_bounds__(256, ITEMS >= 16 ? 2 : 1) layer_norm_backward_
                 // before a gelu and this layer norm), or dropout_grad (the projection before
                 // this sublayer's dropout).
                 if (pre_activation != nullptr) {
-                    second[i] = gelu_grad_value(pre[i], value);
+                    second[i] = gelu_grad_value_for<T>(pre[i], value);
                 } else if (dx_dropped != nullptr && c < h) {
                     second[i] = (keep_dx >> i) & 1u ? value * dx_draw.scale : 0.0f;
                 }
