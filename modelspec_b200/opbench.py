@@ -3,7 +3,7 @@ caller's: the entry points `msx_op_matmul`, `msx_op_matmul_bf16` and `msx_op_att
 for exactly this (a single kernel on a small case, for `ncu` and for tuning).
 
     python -m modelspec_b200.opbench matmul_bf16 M N K [--form nn|nt|tn|tt] [--f32-out] [--reps R]
-    python -m modelspec_b200.opbench matmul_f32 M N K [--form ...] [--reps R]
+    python -m modelspec_b200.opbench matmul_f32 M N K [--form ...] [--exact] [--reps R]
     python -m modelspec_b200.opbench attention_bf16 BATCH SEQ HEADS HEAD_DIM [--forward-only] [--reps R]
     python -m modelspec_b200.opbench heldout_rows ROWS CLASSES [--selected FRACTION] [--reps R]
 
@@ -38,6 +38,7 @@ def main():
     ap.add_argument("dims", type=int, nargs="+")
     ap.add_argument("--form", default="nn", choices=["nn", "nt", "tn", "tt"])
     ap.add_argument("--f32-out", action="store_true")
+    ap.add_argument("--exact", action="store_true", help="matmul_f32: the exact fused-chain kernel instead of the tensor cores")
     ap.add_argument("--forward-only", action="store_true")
     ap.add_argument("--selected", type=float, default=0.15, help="fraction of rows of weight 1 (the rest have weight 0)")
     ap.add_argument("--reps", type=int, default=20)
@@ -64,7 +65,7 @@ def main():
                 rc = L.msx_op_matmul_bf16(ptr(a), int(a_t), ptr(b), int(b_t), ptr(c), int(c.dtype == torch.bfloat16), m, n, k, ptr(ws), need,
                                           ptr(status), stream)
             else:
-                rc = L.msx_op_matmul(ptr(a), int(a_t), ptr(b), int(b_t), ptr(c), m, n, k, ptr(ws), need, ptr(status), stream, 0)
+                rc = L.msx_op_matmul(ptr(a), int(a_t), ptr(b), int(b_t), ptr(c), m, n, k, ptr(ws), need, ptr(status), stream, int(args.exact))
             if rc != M.OK:
                 raise SystemExit(L.msx_last_error(None).decode())
 
