@@ -416,6 +416,10 @@ uint64_t msx_packed_vocabulary(const msx_packed* packed);
 uint64_t msx_packed_sequences(const msx_packed* packed, int split);
 const char* msx_packed_binding_id(const msx_packed* packed);
 
+/* The `data` line a run on a packed directory prints first (cli/src/train.rs:1506-1519); returns
+ * the bytes needed. */
+uint64_t msx_packed_data_line(const msx_packed* packed, char* out, uint64_t capacity);
+
 /* The order in which epoch `epoch` of a run with seed `seed` visits the Train sequences
  * (dataset/mlm.rs:662-675); `count` is msx_packed_sequences(packed, MSX_SPLIT_TRAIN). */
 int msx_packed_epoch_order(msx_packed* packed, uint64_t seed, uint64_t epoch, uint32_t* out, uint64_t count);
@@ -440,6 +444,23 @@ int msx_training_bind_packed(msx_training* training, msx_packed* packed);
 int msx_training_feed_packed(msx_training* training, uint64_t step);
 int msx_training_heldout_packed(msx_training* training, const char* dir);
 uint32_t msx_training_heldout_batches(const msx_training* training);
+
+/* ---- a whole run and its standard output --------------------------------------------------------
+ * `train --backend cuda` as one call: the steps `start` .. `start + steps` of the train block (the
+ * run's `steps`; `start` > 0 after msx_training_resume), fed from the bound packed directory when
+ * there is one and from the current batch otherwise (the reference's synthetic feed trains on one
+ * batch), the held-out split evaluated at every multiple of `eval_every` and at the last step when
+ * held-out batches are declared and `eval_every` > 0, and the loss after the last update from the
+ * forward program without dropout. The text is the reference's standard output for the run
+ * (crates/modelspec-cli/src/train.rs:7-17, :1494-1560): the `data` line of a packed run,
+ * `init @<path>: <type> = [v, ...]` for every parameter in path order, `step <k> loss <v>` at the
+ * first step, every 50 steps, the last step and every evaluated step, `eval <k> loss <l> accuracy
+ * <a>` after an evaluated step's line, and `param @<path>: ...` for every parameter after the last
+ * step; every f32 in its shortest round-trip form. A loss that is not finite stops the run at that
+ * step (MSX_NON_FINITE, E-TRAIN-001): the text then ends with that step's line and has no `param`
+ * lines. msx_training_report copies the text of the last run (returns the bytes needed). */
+int msx_training_run(msx_training* training, uint64_t start, uint64_t eval_every);
+uint64_t msx_training_report(const msx_training* training, char* out, uint64_t capacity);
 
 /* ---- `.msckpt` checkpoints ------------------------------------------------------------------------
  * Writer and validating reader of the reference's checkpoint format version 1, byte for byte

@@ -149,6 +149,9 @@ SIGNATURES = {
     "msx_state_restore": (C.c_int, [_P]),
     "msx_training_set_replay_window": (C.c_int, [_P, C.c_uint32]),
     "msx_training_rewind": (C.c_int, [_P, C.c_uint64]),
+    "msx_packed_data_line": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
+    "msx_training_run": (C.c_int, [_P, C.c_uint64, C.c_uint64]),
+    "msx_training_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
     "msx_plan_run_stats": (C.c_int, [_P, _P]),
     "msx_stats_report": (C.c_uint64, [_P, C.c_char_p, C.c_uint64]),
     "msx_profile_report": (C.c_uint64, [_P, _P, C.c_uint32, C.c_char_p, C.c_uint64]),
@@ -496,6 +499,9 @@ class Packed:
     def sequences(self, split):
         return int(lib().msx_packed_sequences(self.h, split))
 
+    def data_line(self):
+        return _text(lambda buf, cap: lib().msx_packed_data_line(self.h, buf, cap))
+
     def epoch_order(self, seed, epoch):
         out = np.empty(self.sequences(SPLIT_TRAIN), dtype=np.uint32)
         self.check(lib().msx_packed_epoch_order(self.h, seed, epoch, out.ctypes.data, out.size))
@@ -633,6 +639,17 @@ class Training:
         """Draws the HeldOut batches of the bound directory once; returns how many there are."""
         self.check(lib().msx_training_heldout_packed(self.h, self._packed.dir.encode()))
         return int(lib().msx_training_heldout_batches(self.h))
+
+    def run(self, start=0, eval_every=0):
+        """The whole run of the train block from step `start`; returns the text `train` prints for it.
+        A run that stops at a loss that is not finite raises, with the text so far in `report()`."""
+        rc = lib().msx_training_run(self.h, start, eval_every)
+        if rc != OK:
+            raise MsxError(rc, lib().msx_training_last_error(self.h).decode())
+        return self.report()
+
+    def report(self):
+        return _text(lambda buf, cap: lib().msx_training_report(self.h, buf, cap))
 
     def set_replay_window(self, steps):
         """Takes a device snapshot of the state before every `steps`-th step (0: none)."""

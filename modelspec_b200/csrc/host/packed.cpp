@@ -255,6 +255,28 @@ uint64_t msx_packed_vocabulary(const msx_packed* p) { return p ? p->vocabulary :
 uint64_t msx_packed_sequences(const msx_packed* p, int split) { return p && (split == 0 || split == 1) ? p->sequences(split) : 0; }
 const char* msx_packed_binding_id(const msx_packed* p) { return p ? p->binding_id.c_str() : ""; }
 
+// The `data` line a run on a packed directory prints first (crates/modelspec-cli/src/train.rs:
+// 1506-1519): `data dataset <id> tokenizer <id> seq_len <n> masking <a>/<b>/<c>/<d> binding <id>`,
+// the rates as Rust displays an f64.
+uint64_t msx_packed_data_line(const msx_packed* p, char* out, uint64_t capacity) {
+    if (!p) return 0;
+    auto rate = [](double v) {
+        std::string text = msx::json::f64_text(v);
+        // Rust's Display never writes an exponent and drops a fraction of zero.
+        if (text.size() > 2 && text.compare(text.size() - 2, 2, ".0") == 0) text.resize(text.size() - 2);
+        return text;
+    };
+    const std::string line = "data dataset " + p->dataset_id + " tokenizer " + p->tokenizer_id + " seq_len " + std::to_string(p->seq_len) +
+                             " masking " + rate(p->policy.selection_rate) + "/" + rate(p->policy.mask_fraction) + "/" +
+                             rate(p->policy.random_fraction) + "/" + rate(p->policy.keep_fraction) + " binding " + p->binding_id + "\n";
+    if (out && capacity) {
+        const size_t n = std::min<size_t>(capacity - 1, line.size());
+        std::memcpy(out, line.data(), n);
+        out[n] = 0;
+    }
+    return line.size() + 1;
+}
+
 int msx_packed_epoch_order(msx_packed* p, uint64_t seed, uint64_t epoch, uint32_t* out, uint64_t count) {
     if (!p || !out) return MSX_BAD_ARGUMENT;
     return guarded(p, [&] {

@@ -44,6 +44,7 @@ struct msx_training {
         std::map<std::string, std::vector<char>> batch;
     };
     std::vector<Replayed> since_snapshot;
+    std::string report;  // the standard output of the last msx_training_run
     std::string schema;  // the schema hash of the training program's parameters, made on first use
     msx_packed* packed = nullptr;
     uint64_t packed_batch = 0;
@@ -828,6 +829,110 @@ int msx_training_resume(msx_training* t, const msx_checkpoint* ckpt, uint64_t* s
         }
         *start_step = step;
     });
+}
+
+// ---- a whole run (crates/modelspec-cli/src/train.rs:1494-1560; train/runner.rs:365-512) ---------------
+
+namespace {
+
+// `<label> @<path>: <type> = [v, ...]` for every parameter the run holds, in path order.
+void parameter_lines(msx_training* t, const char* label, std::string* out) {
+    const auto& params = t->compiled.forward.params;
+    std::vector<uint32_t> order(params.size());
+    for (uint32_t p = 0; p < order.size(); ++p) order[p] = p;
+    std::sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return params[a].path < params[b].path; });
+    std::vector<float> value;
+    for (uint32_t p : order) {
+        value.resize(params[p].ty.count());
+        if (msx_param_download(t->forward, p, value.data(), value.size() * 4) != MSX_OK &&
+            msx_param_download(t->step, p, value.data(), value.size() * 4) != MSX_OK)
+            continue;
+        *out += std::string(label) + " @" + params[p].path + ": " + params[p].ty.str() + " = [";
+        for (size_t i = 0; i < value.size(); ++i) {
+            if (i) *out += ", ";
+            *out += msx::f32_display(value[i]);
+        }
+        *out += "]\n";
+    }
+}
+
+constexpr uint64_t kLossEvery = 50;  // cli/src/train.rs LOSS_EVERY
+
+}  // namespace
+
+int msx_training_run(msx_training* t, uint64_t start, uint64_t eval_every) {
+    if (!t) return MSX_BAD_ARGUMENT;
+    t->report.clear();
+    return guarded(t, [&] {
+        const uint64_t steps = t->compiled.config.steps, end = start + steps;
+        if (end < start) throw Fail{MSX_BAD_ARGUMENT, "the run's steps overflow the step counter"};
+        std::string& out = t->report;
+        if (t->packed) {
+            std::vector<char> line(msx_packed_data_line(t->packed, nullptr, 0));
+            msx_packed_data_line(t->packed, line.data(), line.size());
+            out += line.data();
+        }
+        parameter_lines(t, "init", &out);
+        const bool evaluating = eval_every > 0 && t->heldout != nullptr;
+        auto evaluated = [&](uint64_t k) { return evaluating && (k % eval_every == 0 || k == end); };
+        // Losses are read a few steps behind the submissions; the lines come out in step order.
+        std::map<uint64_t, std::pair<float, float>> evals;
+        auto lines_of = [&](uint64_t k, float loss) {
+            if (k == start || k % kLossEvery == 0 || k == end || evals.count(k)) out += "step " + std::to_string(k) + " loss " + msx::f32_display(loss) + "\n";
+            auto e = evals.find(k);
+            if (e != evals.end())
+                out += "eval " + std::to_string(k) + " loss " + msx::f32_display(e->second.first) + " accuracy " + msx::f32_display(e->second.second) + "\n";
+        };
+        auto read_loss = [&](uint64_t k) {
+            float loss = 0.0f;
+            const int rc = msx_training_loss_of(t, k, &loss);
+            if (rc == MSX_NON_FINITE) {
+                // The run stops at this step: its line is the last one, and there are no `param` lines.
+                ok(t, msx_loss_of(t->step, t->submitted_as.at(k), &loss, 0));
+                lines_of(k, loss);
+                throw Fail{MSX_NON_FINITE, t->error};
+            }
+            if (rc != MSX_OK) throw Fail{rc, t->error};
+            lines_of(k, loss);
+        };
+        constexpr uint64_t kBehind = 4;
+        uint64_t next_read = start;
+        for (uint64_t k = start; k < end; ++k) {
+            if (evaluated(k)) {
+                float loss = 0.0f, accuracy = 0.0f;
+                if (msx_training_heldout_evaluate(t, &loss, &accuracy) != MSX_OK) throw Fail{MSX_LAUNCH_FAILED, t->error};
+                evals[k] = {loss, accuracy};
+            }
+            if (t->packed && msx_training_feed_packed(t, k) != MSX_OK) throw Fail{MSX_BAD_INPUT, t->error};
+            if (msx_training_step(t, k, end) != MSX_OK) throw Fail{MSX_LAUNCH_FAILED, t->error};
+            while (next_read + kBehind <= k) read_loss(next_read++);
+        }
+        while (next_read < end) read_loss(next_read++);
+        // The loss after the last update: the forward program without dropout on the batch of step
+        // `end` (a packed run: the batch that step would train on; runner.rs:466-485).
+        if (t->packed && msx_training_feed_packed(t, end) != MSX_OK) throw Fail{MSX_BAD_INPUT, t->error};
+        if (evaluated(end)) {
+            float loss = 0.0f, accuracy = 0.0f;
+            if (msx_training_heldout_evaluate(t, &loss, &accuracy) != MSX_OK) throw Fail{MSX_LAUNCH_FAILED, t->error};
+            evals[end] = {loss, accuracy};
+        }
+        float last = 0.0f;
+        if (msx_training_final_loss(t, &last) != MSX_OK) throw Fail{MSX_LAUNCH_FAILED, t->error};
+        lines_of(end, last);
+        if (!std::isfinite(last)) throw Fail{MSX_NON_FINITE, "E-TRAIN-001: the loss after the last update is not finite"};
+        if (msx_training_check_finite(t) != MSX_OK) throw Fail{MSX_NON_FINITE, t->error};
+        parameter_lines(t, "param", &out);
+    });
+}
+
+uint64_t msx_training_report(const msx_training* t, char* out, uint64_t capacity) {
+    if (!t) return 0;
+    if (out && capacity) {
+        const size_t n = std::min<size_t>(capacity - 1, t->report.size());
+        std::memcpy(out, t->report.data(), n);
+        out[n] = 0;
+    }
+    return t->report.size() + 1;
 }
 
 int msx_training_check_finite(msx_training* t) {
