@@ -3,9 +3,9 @@
 //
 // Each f32 operand x is split into hi (its top 11 significant bits) and lo = x - hi, both exact
 // tf32 values (the tensor core keeps 11 significant bits of lo, so x is represented to about
-// 2^-21 |x|), and a product is summed as hi*hi + hi*lo + lo*hi + lo*lo in f32 accumulators: two
-// orders below the kernel tolerance 1e-5 + 1e-4 r. The exact kernel (gemm.cu) stays for
-// bit-level parity runs.
+// 2^-21 |x|), and a product is summed as hi*hi + hi*lo + lo*hi (+ lo*lo where it comes for free,
+// in the 64-row tile) in f32 accumulators: two orders below the kernel tolerance 1e-5 + 1e-4 r.
+// The exact kernel (gemm.cu) stays for bit-level parity runs.
 //
 // One tcgen05.mma of this shape costs about the same 100-130 cycles whatever its width (its 128
 // rows of A are read 32 bytes at a time), so the four partial products are not four MMAs: the hi
@@ -38,6 +38,7 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "tcgen05.cuh"
 
 namespace msx {
 namespace k {
@@ -64,25 +65,26 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives
 #define MSX_TC_KB32 400.0
 #define MSX_TC_KB64 560.0
 #define MSX_TC_KB128 1100.0
-// The 128 x 128 tile: one CTA per SM, eight MMAs of 128 x 256 x 8 per k block.
-#define MSX_TC_FIXED_WIDE 9000.0
-#define MSX_TC_KB_WIDE 2200.0
+// The 128 x 128 tile (a persistent CTA per SM): per launch, per k block (four MMAs of
+// 128 x 256 x 8 and four of 128 x 128 x 8) and per tile.
+#define MSX_TC_FIXED_WIDE 8000.0
+#define MSX_TC_KB_WIDE 2300.0
+#define MSX_TC_TILE_WIDE 500.0
+#define MSX_TC_DRAIN_WIDE 5000.0  // a tile's drain, which bounds a tile of few k blocks
 // Operand bytes all SMs together pull through the L2 per SM cycle.
 #define MSX_TC_BYTES_PER_CYCLE 3800.0
 #define MSX_TC_REDUCE_FIXED 8000.0
 #define MSX_TC_REDUCE_BYTES_PER_CYCLE 3000.0
 #endif
 
-// BM = 64: the tile described above, two CTAs per SM. BM = 128 (with BN = 128): a 128 x 128 tile
-// for products large enough to be bound by operand traffic: the hi and lo halves of A are two
-// 128-row operands, two MMAs per k slice add their products with the stacked B into the same
-// accumulator, and the tile reads half the A and B bytes per output of the narrow one. One CTA
-// per SM then (three 64 KB stages).
+// The 64-row tile described above, two CTAs per SM (the 128 x 128 tile is a kernel of its own,
+// further down).
 template <int BM, int BN> struct Config {
-    static constexpr int STAGES = BM == 128 ? 3 : (BN == 128 ? 2 : (BN == 64 ? 3 : 4));  // shared-memory stages
-    static constexpr int SETS = BN == 32 ? 4 : ((BN == 128 && BM == 64) ? 2 : 3);       // register sets of loads in flight
-    static constexpr int CTAS_PER_SM = BM == 128 ? 1 : 2;
-    static constexpr uint32_t A_BYTES = 2 * 128 * BK * 4 * BM / 128;  // BM 64: hi rows 0-63, lo rows 64-127; BM 128: hi tile, lo tile
+    static_assert(BM == 64, "the stacked-A tile has 64 rows");
+    static constexpr int STAGES = BN == 128 ? 2 : (BN == 64 ? 3 : 4);  // shared-memory stages
+    static constexpr int SETS = BN == 32 ? 4 : (BN == 128 ? 2 : 3);    // register sets of loads in flight
+    static constexpr int CTAS_PER_SM = 2;
+    static constexpr uint32_t A_BYTES = 2 * BM * BK * 4;  // hi rows 0-63, lo rows 64-127
     static constexpr uint32_t B_BYTES = 2 * BN * BK * 4;  // hi columns 0..BN-1, lo columns BN..2BN-1
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -99,11 +101,14 @@ struct TcArgs {
     float* c[MAX_GROUP];           // C, or the split-K workspace [splits][m][n]
     const float* bias[MAX_GROUP];  // added to every row of C by the CTA that writes C; null for none
     uint32_t splits;
+    uint32_t products;             // how many of a[], b[], c[] are used
     uint32_t m, n, k;
     uint32_t lda, ldb, ldc;        // row pitch, in elements, of each matrix as stored
     uint32_t kblocks_per_split;
     uint32_t a_vec, b_vec, c_vec;  // 16-byte accesses are aligned for this operand
     uint32_t c_padded;             // the columns of C between n and ldc are padding that may be overwritten
+    uint32_t c_tma;                // the 128 x 128 tile writes C (or the split-k workspace) by TMA stores
+    tc::CoordOrder c_order;        // where the row and split coordinates sit in the tensor maps of C
     // Batched products: grid.z = batch index z, split as (z / inner, z % inner); each matrix of
     // problem z starts at outer * stride_outer + inner * stride_inner elements. inner = 0: not batched.
     uint32_t batch_inner;
@@ -137,8 +142,23 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One poll of a barrier phase. The thread may sleep in the instruction for up to the hinted time
+// and is woken when the phase completes: a waiting role then costs the SM's shared-memory pipe
+// next to nothing, where a tight polling loop of 256 threads slows the roles that are working.
+#ifndef MSX_TC_WAIT_HINT_NS
+#define MSX_TC_WAIT_HINT_NS 0
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#if MSX_TC_WAIT_HINT_NS > 0
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(MSX_TC_WAIT_HINT_NS))
+        : "memory");
+#else
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -146,6 +166,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
+#endif
     return ok != 0;
 }
 // Waits for `parity` of `bar`; false when the wait ran out or another role gave up.
@@ -157,6 +178,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     atomicOr(status, 2u);
     return false;
+}
+
+// The same, polled by one lane for its warp (all lanes must call it together).
+__device__ __forceinline__ bool warp_mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
+    uint32_t ok = 0;
+    if ((threadIdx.x & 31u) == 0) ok = mbar_wait(bar, parity, abort_flag, status) ? 1u : 0u;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    // The lanes that did not poll observe the phase themselves before they touch what it guards.
+    if (ok) mbar_try_wait(bar, parity);
+    return ok != 0;
 }
 
 __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
@@ -183,6 +214,16 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
 }
@@ -243,7 +284,6 @@ __device__ __forceinline__ void loaders_barrier(uint32_t threads) {
 template <int BM, int BN, bool A_T, bool B_T>
 __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_tc_kernel(TcArgs args) {
     using Cfg = Config<BM, BN>;
-    constexpr bool WIDE = BM == 128;
     constexpr int STAGES = Cfg::STAGES, SETS = Cfg::SETS;
     extern __shared__ char smem_raw[];
     // Tiles need 1024-byte alignment for the swizzle pattern to line up with address bits.
@@ -445,11 +485,10 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
         constexpr uint32_t PITCH = BN + 4;  // 16-byte phases of consecutive rows fall on distinct banks
         const bool drains = BN != 32 || half == 0;  // a 32-column tile is one block per lane quarter
         float* tile_hi = reinterpret_cast<float*>(tiles);
-        float* tile_lo = tile_hi + 64 * PITCH;  // BM 64 only: the sums of the A_lo rows
+        float* tile_lo = tile_hi + 64 * PITCH;  // the sums of the A_lo rows
         if (drains) {
-            // BM 128: lane quarter q holds tile rows 32 q ..; BM 64: quarters 0-1 the A_hi rows, 2-3 the A_lo rows.
-            float* to_row = WIDE ? tile_hi + (quarter * 32u + lane) * PITCH
-                                 : (quarter < 2 ? tile_hi : tile_lo) + ((quarter & 1u) * 32u + lane) * PITCH;
+            // Lane quarters 0-1 hold the A_hi rows, 2-3 the A_lo rows.
+            float* to_row = (quarter < 2 ? tile_hi : tile_lo) + ((quarter & 1u) * 32u + lane) * PITCH;
 #pragma unroll
             for (int part = 0; part < PARTS; ++part) {
                 const uint32_t col = BN == 128 ? half * 64u + part * 32u : (BN == 64 ? half * 32u : 0u);
@@ -486,7 +525,7 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
             const uint32_t gm = m0 + r;
             if (gm >= pm || gn >= pn) continue;
             const float4 h = *reinterpret_cast<const float4*>(tile_hi + r * PITCH + c4);
-            const float4 l = WIDE ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(tile_lo + r * PITCH + c4);
+            const float4 l = *reinterpret_cast<const float4*>(tile_lo + r * PITCH + c4);
             // `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
             float v[4] = {(h.x + l.x) + 0.0f, (h.y + l.y) + 0.0f, (h.z + l.z) + 0.0f, (h.w + l.w) + 0.0f};
             if (bias_row) {
@@ -541,7 +580,6 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
                     const uint32_t a_step = (A_T ? ks * 1024u : ks * 32u) >> 4;
                     const uint32_t b_step = (B_T ? ks * 32u : ks * 1024u) >> 4;
                     mma_tf32(tmem_base, desc(a_high, a16 + a_step), desc(b_high, b16 + b_step), idesc, (kb | ks) != 0u);
-                    if (WIDE) mma_tf32(tmem_base, desc(a_high, a16 + (Cfg::A_BYTES >> 5) + a_step), desc(b_high, b16 + b_step), idesc, 1u);
                 }
                 mma_commit(smem_u32(&bars[STAGES + stage]));                   // frees the stage when they finish
                 if (kb < 4) TRACE(8 + kb);
@@ -557,6 +595,437 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
     if (tid == 0) TRACE(12);
     if (warp == 8) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLUMNS) : "memory");
+    }
+}
+
+#ifdef MSX_TC_TRACE
+// Phase timestamps of CTA 0 of the persistent kernel, for tuning builds only.
+#define WTRACE(slot) do { if (blockIdx.x == 0 && (slot) < 256) (&g_trace[0][0])[(slot)] = clock64(); } while (0)
+#else
+#define WTRACE(slot) do { } while (0)
+#endif
+
+// ---- the 128 x 128 tile as a persistent kernel ---------------------------------------------------
+// For products large enough to be bound by operand traffic. The hi and lo halves of A are two
+// 128-row operands; per 8-deep k slice one MMA of A_hi with the stacked B (N = 256: the hi and lo
+// columns) and one of A_lo with B_hi alone (N = 128) add hi*hi + lo*hi and hi*lo into the two
+// column halves of one accumulator (lo*lo, below 2^-20 of a product, is left out). One CTA per SM
+// walks the launch's tiles (block b takes units b, b + grid, ...), so the set-up of a CTA is paid
+// once and the drain of a tile runs under the k loop of the next one:
+//   warps 0-7   load, split and store the k blocks of all the CTA's tiles as one sequence (the
+//               loads of the next tile's first blocks are in flight while this tile's last are
+//               stored);
+//   warp 8      issues the MMAs into one of two accumulators of 256 tensor-memory columns;
+//   warps 12-15 drain the other accumulator: a lane quarter each, 32 columns at a time into a
+//               shared-memory slab of their own (two per warp), which a TMA store writes to C
+//               while the next slab is filled.
+struct Wide {
+#ifndef MSX_TC_WIDE_SETS
+#define MSX_TC_WIDE_SETS 2
+#endif
+#ifndef MSX_TC_WIDE_ORDER
+#define MSX_TC_WIDE_ORDER 1
+#endif
+#ifndef MSX_TC_WIDE_WARP_SYNC
+#define MSX_TC_WIDE_WARP_SYNC 0
+#endif
+    static constexpr int STAGES = 3, SETS = MSX_TC_WIDE_SETS, DRAIN_WARPS = 4;  // SETS: register sets of loads in flight
+    // Four groups of four warps: two of loaders, one whose first warp issues the MMAs, one of
+    // drain warps. The register file is dealt out again by group after the set-up (the loaders'
+    // loads in flight are registers): 8 x 176 + 4 x 56 + 4 x 104 = 16 x 128.
+    static constexpr int THREADS = 512, DRAIN_FIRST_WARP = 12;
+    static constexpr uint32_t A_BYTES = 2 * 128 * BK * 4;  // hi tile, lo tile
+    static constexpr uint32_t B_BYTES = 2 * 128 * BK * 4;  // hi columns 0-127, lo columns 128-255
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t SLAB_BYTES = 32 * 128;                     // 32 rows of 32 floats
+    static constexpr uint32_t DRAIN_BYTES = DRAIN_WARPS * 2 * SLAB_BYTES;  // two slabs per drain warp
+    static constexpr uint32_t TOTAL = STAGES * STAGE_BYTES + DRAIN_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr uint32_t ACC_COLUMNS = 256, TMEM_COLUMNS = 512;
+};
+
+// Which tile, split and product unit `u` of a launch is: the tiles of one column of tiles are
+// neighbours (they share their B block), then the splits of a tile, then the columns.
+struct WideUnit {
+    uint32_t m0, n0, split, product, kblocks;
+};
+__device__ __forceinline__ WideUnit wide_unit(const TcArgs& args, uint32_t u, uint32_t down, uint32_t across, uint32_t kblocks_total) {
+    WideUnit w;
+    w.m0 = (u % down) * 128u;
+    u /= down;
+    w.split = u % args.splits;
+    u /= args.splits;
+    w.n0 = (u % across) * 128u;
+    w.product = u / across;
+    w.kblocks = kblocks_total > w.split ? (kblocks_total - w.split + args.splits - 1) / args.splits : 0u;
+    return w;
+}
+
+// The tensor maps of the results of a launch's products (or of their split-k workspaces).
+struct WideMaps {
+    CUtensorMap c[MAX_GROUP];
+};
+
+template <bool A_T, bool B_T>
+__global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs args, const __grid_constant__ WideMaps maps) {
+    constexpr int STAGES = Wide::STAGES, SETS = Wide::SETS;
+    extern __shared__ char smem_raw[];
+    char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    char* drain_slabs = tiles + STAGES * Wide::STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * Wide::STAGE_BYTES + Wide::DRAIN_BYTES);
+    // bars[0 .. STAGES) full, [STAGES .. 2 STAGES) empty, then accumulator b ready (2), accumulator
+    // b drained (2); then the TMEM address and the abort flag.
+    uint64_t* acc_full = bars + 2 * STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(acc_empty + 3);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t pm = args.m, pn = args.n, pk = args.k, plda = args.lda, pldb = args.ldb, pldc = args.ldc;
+    const uint32_t down = (pm + 127) / 128, across = (pn + 127) / 128;
+    const uint32_t kblocks_total = (pk + BK - 1) / BK;
+    const uint32_t units = down * across * args.splits * args.products;
+    const uint32_t stride = args.splits;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars[s]), MSX_TC_WIDE_WARP_SYNC ? LOADER_THREADS / 32 : LOADER_THREADS);  // one arrival per loader warp
+            mbar_init(smem_u32(&bars[STAGES + s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), Wide::DRAIN_WARPS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Wide::TMEM_COLUMNS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 8) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 176;" ::: "memory");
+        // ---- loaders ----------------------------------------------------------------------------
+        // How many k blocks this CTA stores in all: the sequence the stages count along.
+        uint32_t total = 0;
+        for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) total += wide_unit(args, u, down, across, kblocks_total).kblocks;
+        constexpr int CHUNKS = 128 * BK / 4 / LOADER_THREADS;  // 16-byte chunks of one operand block a thread moves
+        // Chunk i of a thread lies a fixed number of rows after its chunk 0, in the matrix and in
+        // the shared-memory tile alike, so one offset, one address and one mask of row checks per
+        // operand describe them all (registers are what bounds the loads in flight here).
+        constexpr uint32_t A_ROWS = A_T ? LOADER_THREADS / 32 : LOADER_THREADS / 8;  // rows from chunk i to chunk i + 1
+        constexpr uint32_t B_ROWS = B_T ? LOADER_THREADS / 8 : LOADER_THREADS / 32;
+        constexpr uint32_t A_TILE_STEP = A_T ? A_ROWS * 128u : (A_ROWS / 8) * 1024u;  // the same in tile bytes
+        constexpr uint32_t B_TILE_STEP = B_T ? (B_ROWS / 8) * 1024u : B_ROWS * 128u;
+        const uint32_t a_row = A_T ? tid >> 5 : tid >> 3, a_col = A_T ? (tid & 31u) * 4 : (tid & 7u) * 4;  // (k, m) or (m, k)
+        const uint32_t b_row = B_T ? tid >> 3 : tid >> 5, b_col = B_T ? (tid & 7u) * 4 : (tid & 31u) * 4;  // (n, k) or (k, n)
+        const uint32_t aoff = A_T ? mn_major_offset(a_row, a_col / 4) : k_major_offset(a_row, a_col / 4);
+        const uint32_t boff = B_T ? k_major_offset(b_row, b_col / 4) : mn_major_offset(b_row, b_col / 4);
+        // The tile whose blocks are being fetched: its operands, the address of chunk 0 in its
+        // first k block and, bit i, whether all four elements of chunk i lie inside the matrix rows.
+        uint32_t f_unit = blockIdx.x, f_kb = 0;
+        WideUnit f = {};
+        const float* __restrict__ fa = nullptr;
+        const float* __restrict__ fb = nullptr;
+        const float* a_at = nullptr;
+        const float* b_at = nullptr;
+        uint32_t a_whole = 0, b_whole = 0;
+        const uint64_t a_step = static_cast<uint64_t>(BK) * stride * (A_T ? plda : 1u);
+        const uint64_t b_step = static_cast<uint64_t>(BK) * stride * (B_T ? 1u : pldb);
+        auto open_unit = [&](uint32_t u) {
+            f = wide_unit(args, u, down, across, kblocks_total);
+            f_kb = 0;
+            fa = args.a[f.product];
+            fb = args.b[f.product];
+            const uint32_t first_k = f.split * BK;
+            a_at = A_T ? fa + static_cast<uint64_t>(first_k + a_row) * plda + f.m0 + a_col
+                       : fa + static_cast<uint64_t>(f.m0 + a_row) * plda + first_k + a_col;
+            b_at = B_T ? fb + static_cast<uint64_t>(f.n0 + b_row) * pldb + first_k + b_col
+                       : fb + static_cast<uint64_t>(first_k + b_row) * pldb + f.n0 + b_col;
+            a_whole = b_whole = 0;
+#pragma unroll
+            for (int i = 0; i < CHUNKS; ++i) {
+                if (args.a_vec && (A_T ? f.m0 + a_col + 4 <= pm : f.m0 + a_row + i * A_ROWS < pm)) a_whole |= 1u << i;
+                if (args.b_vec && (B_T ? f.n0 + b_row + i * B_ROWS < pn : f.n0 + b_col + 4 <= pn)) b_whole |= 1u << i;
+            }
+        };
+        // The next k block of the sequence into one register set.
+        auto fetch_next = [&](float4 (&av)[CHUNKS], float4 (&bv)[CHUNKS]) {
+            const uint32_t k0 = (f_kb * stride + f.split) * BK;
+            const bool inside = k0 + BK <= pk;
+            const float* a_block = a_at + f_kb * a_step;
+            const float* b_block = b_at + f_kb * b_step;
+#pragma unroll
+            for (int i = 0; i < CHUNKS; ++i) {
+                if (inside && (a_whole >> i & 1u)) {
+                    av[i] = load4(a_block + static_cast<uint64_t>(i * A_ROWS) * plda, 0, 4, true);
+                    continue;
+                }
+                const uint32_t row = a_row + i * A_ROWS;
+                if (A_T) {
+                    const uint32_t gk = k0 + row, gm = f.m0 + a_col;
+                    av[i] = load4(fa, static_cast<uint64_t>(gk) * plda + gm, gk < pk ? in_range(gm, pm) : 0u, args.a_vec);
+                } else {
+                    const uint32_t gm = f.m0 + row, gk = k0 + a_col;
+                    av[i] = load4(fa, static_cast<uint64_t>(gm) * plda + gk, gm < pm ? in_range(gk, pk) : 0u, args.a_vec);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < CHUNKS; ++i) {
+                if (inside && (b_whole >> i & 1u)) {
+                    bv[i] = load4(b_block + static_cast<uint64_t>(i * B_ROWS) * pldb, 0, 4, true);
+                    continue;
+                }
+                const uint32_t row = b_row + i * B_ROWS;
+                if (B_T) {
+                    const uint32_t gn = f.n0 + row, gk = k0 + b_col;
+                    bv[i] = load4(fb, static_cast<uint64_t>(gn) * pldb + gk, gn < pn ? in_range(gk, pk) : 0u, args.b_vec);
+                } else {
+                    const uint32_t gk = k0 + row, gn = f.n0 + b_col;
+                    bv[i] = load4(fb, static_cast<uint64_t>(gk) * pldb + gn, gk < pk ? in_range(gn, pn) : 0u, args.b_vec);
+                }
+            }
+            if (++f_kb == f.kblocks) {
+                f_unit += gridDim.x;
+                if (f_unit < units) open_unit(f_unit);
+            }
+        };
+        float4 av[SETS][CHUNKS], bv[SETS][CHUNKS];
+        if (total > 0) open_unit(f_unit);
+#pragma unroll
+        for (int s = 0; s < SETS - 1; ++s)
+            if (static_cast<uint32_t>(s) < total) fetch_next(av[s], bv[s]);
+        bool alive = true;
+        uint32_t stage = 0, parity = 1;  // the parity a free stage shows
+        uint32_t deposited = 0;
+        (void)deposited;
+        auto deposit = [&](const float4 (&a_regs)[CHUNKS], const float4 (&b_regs)[CHUNKS]) -> bool {
+            char* a_tile = tiles + stage * Wide::STAGE_BYTES;
+            char* b_tile = a_tile + Wide::A_BYTES;
+            // The stage is free once the MMAs that read its previous contents have completed.
+            if (tid == 0 && deposited < 24) WTRACE(64 + 2 * deposited);
+#if MSX_TC_WIDE_WARP_SYNC
+            if (!warp_mbar_wait(smem_u32(&bars[STAGES + stage]), parity, abort_flag, args.status)) return false;
+#else
+            if (!mbar_wait(smem_u32(&bars[STAGES + stage]), parity, abort_flag, args.status)) return false;
+#endif
+            if (tid == 0 && deposited < 24) WTRACE(65 + 2 * deposited);
+            ++deposited;
+            const bool stamped = tid == 0 && deposited >= 9 && deposited < 17;
+            if (stamped) WTRACE(160 + 6 * (deposited - 9));
+#pragma unroll
+            for (int i = 0; i < CHUNKS; ++i) store_split(a_tile, aoff + i * A_TILE_STEP, aoff + i * A_TILE_STEP + Wide::A_BYTES / 2, a_regs[i]);
+            if (stamped) WTRACE(161 + 6 * (deposited - 9));
+#pragma unroll
+            for (int i = 0; i < CHUNKS; ++i) store_split(b_tile, boff + i * B_TILE_STEP, boff + i * B_TILE_STEP + Wide::B_BYTES / 2, b_regs[i]);
+            if (stamped) WTRACE(162 + 6 * (deposited - 9));
+            // Every lane makes its stores visible to the tensor core's async-proxy reads; one
+            // lane then arrives for the warp (256 arrivals on one barrier word are 256 serialised
+            // shared-memory atomics per k block).
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#if MSX_TC_WIDE_WARP_SYNC
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars[stage]));
+#else
+            if (stamped) WTRACE(163 + 6 * (deposited - 9));
+            mbar_arrive(smem_u32(&bars[stage]));
+#endif
+            if (stamped) WTRACE(164 + 6 * (deposited - 9));
+            if (++stage == STAGES) { stage = 0; parity ^= 1u; }
+            return true;
+        };
+        for (uint32_t g0 = 0; g0 < total && alive; g0 += SETS) {
+#pragma unroll
+            for (int s = 0; s < SETS; ++s) {
+                const uint32_t g = g0 + s;
+                if (g >= total || !alive) break;
+#if MSX_TC_WIDE_ORDER == 0
+                if (g + SETS - 1 < total) fetch_next(av[(s + SETS - 1) % SETS], bv[(s + SETS - 1) % SETS]);
+                alive = deposit(av[s], bv[s]);
+#else
+                // The block's stores and their fence first, the next loads after them: a fence
+                // that followed freshly issued loads would wait for them.
+                alive = deposit(av[s], bv[s]);
+                if (g + SETS - 1 < total) fetch_next(av[(s + SETS - 1) % SETS], bv[(s + SETS - 1) % SETS]);
+#endif
+            }
+        }
+    } else if (warp < Wide::DRAIN_FIRST_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
+        if (warp == 8) {
+        // ---- the MMA warp ---------------------------------------------------------------------------
+        // Instruction descriptors: f32 accumulator, tf32 A and B, their majors, N >> 3, M >> 4.
+        const uint32_t idesc_lo = (1u << 4) | (2u << 7) | (2u << 10) | ((A_T ? 1u : 0u) << 15) | ((B_T ? 0u : 1u) << 16) |
+                                  (static_cast<uint32_t>(128 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+        const uint32_t idesc_hi = (idesc_lo & ~(0x3Fu << 17)) | (static_cast<uint32_t>(256 >> 3) << 17);
+        constexpr uint32_t a_lbo = A_T ? BK * 128u : 16u, b_lbo = B_T ? 16u : BK * 128u;
+        constexpr uint32_t a_sbo = A_T ? 512u : 1024u, b_sbo = B_T ? 1024u : 512u;
+        constexpr uint32_t a_type = A_T ? 1u : 2u, b_type = B_T ? 2u : 1u;
+        constexpr uint32_t a_high = ((a_sbo >> 4) & 0x3FFFu) | (1u << 14) | (a_type << 29);
+        constexpr uint32_t b_high = ((b_sbo >> 4) & 0x3FFFu) | (1u << 14) | (b_type << 29);
+        constexpr uint32_t a_low = ((a_lbo >> 4) & 0x3FFFu) << 16, b_low = ((b_lbo >> 4) & 0x3FFFu) << 16;
+        const uint32_t tiles16 = (smem_u32(tiles) & 0x3FFFFu) >> 4;
+        auto desc = [](uint32_t high, uint32_t low) { return (static_cast<uint64_t>(high) << 32) | low; };
+        bool alive = true;
+        uint32_t stage = 0, parity = 0, turn = 0;
+        for (uint32_t u = blockIdx.x; u < units && alive; u += gridDim.x, ++turn) {
+            const uint32_t kblocks = wide_unit(args, u, down, across, kblocks_total).kblocks;
+            if (kblocks == 0) continue;
+            const uint32_t acc = turn & 1u;
+            // The accumulator is free once the drain warps have read its previous tile.
+            if (lane == 0 && turn < 8) WTRACE(32 + 3 * turn);
+            alive = mbar_wait(smem_u32(&acc_empty[acc]), ((turn >> 1) & 1u) ^ 1u, abort_flag, args.status);
+            if (lane == 0 && turn < 8) WTRACE(33 + 3 * turn);
+            for (uint32_t kb = 0; kb < kblocks && alive; ++kb) {
+                alive = mbar_wait(smem_u32(&bars[stage]), parity, abort_flag, args.status);
+                if (!alive) break;
+                if (lane == 0 && turn < 8 && kb + 1 == kblocks) WTRACE(34 + 3 * turn);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (lane == 0) {
+                    const uint32_t a16 = a_low + tiles16 + stage * (Wide::STAGE_BYTES >> 4);
+                    const uint32_t b16 = b_low + tiles16 + stage * (Wide::STAGE_BYTES >> 4) + (Wide::A_BYTES >> 4);
+                    const uint32_t to = tmem_base + acc * Wide::ACC_COLUMNS;
+#pragma unroll
+                    for (uint32_t ks = 0; ks < BK / 8; ++ks) {
+                        const uint32_t a_at = (A_T ? ks * 1024u : ks * 32u) >> 4;
+                        const uint32_t b_at = (B_T ? ks * 32u : ks * 1024u) >> 4;
+                        mma_tf32(to, desc(a_high, a16 + a_at), desc(b_high, b16 + b_at), idesc_hi, (kb | ks) != 0u);
+                        mma_tf32(to, desc(a_high, a16 + (Wide::A_BYTES >> 5) + a_at), desc(b_high, b16 + b_at), idesc_lo, 1u);
+                    }
+                    mma_commit(smem_u32(&bars[STAGES + stage]));               // frees the stage when they finish
+                    if (kb + 1 == kblocks) mma_commit(smem_u32(&acc_full[acc]));  // and, at the end, hands the tile to the drain
+                }
+                if (++stage == STAGES) { stage = 0; parity ^= 1u; }
+                __syncwarp();
+            }
+        }
+        }
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;" ::: "memory");
+        // ---- the drain warps: tensor memory -> a shared-memory slab -> C ---------------------------
+        // A warp reads its lane quarter (the tensor-memory lanes a warp may read are 32 (warp % 4)
+        // ..) 32 columns at a time: the sums of the two accumulator halves (and the bias) go row
+        // by row into a slab of 32 rows x 128 bytes in the 128-byte swizzle (the 16-byte chunks of
+        // a row xor-ed with the row), which one TMA store then writes (what lies outside C is not
+        // written), or, where C cannot be a TMA target, the warp itself as 128-byte row segments.
+        const uint32_t quarter = warp & 3u;
+        char* const my_slabs = drain_slabs + (warp - Wide::DRAIN_FIRST_WARP) * 2 * Wide::SLAB_BYTES;
+        bool alive = true;
+        uint32_t turn = 0, filled = 0;
+        for (uint32_t u = blockIdx.x; u < units && alive; u += gridDim.x, ++turn) {
+            const WideUnit w = wide_unit(args, u, down, across, kblocks_total);
+            if (w.kblocks == 0) continue;
+            const uint32_t acc = turn & 1u;
+            // The tile's 128 bias values, four per lane, fetched before the wait for the tile: a
+            // load issued inside the drain would queue behind the loaders' traffic.
+            const float* __restrict__ bias_row = args.bias[w.product];
+            float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (bias_row) {
+                const uint32_t at = w.n0 + 4 * lane;
+                if (at + 4 <= pn && reinterpret_cast<uintptr_t>(bias_row) % 16 == 0) {
+                    bias4 = __ldg(reinterpret_cast<const float4*>(bias_row + at));
+                } else {
+                    if (at < pn) bias4.x = __ldg(bias_row + at);
+                    if (at + 1 < pn) bias4.y = __ldg(bias_row + at + 1);
+                    if (at + 2 < pn) bias4.z = __ldg(bias_row + at + 2);
+                    if (at + 3 < pn) bias4.w = __ldg(bias_row + at + 3);
+                }
+            }
+            if (warp == Wide::DRAIN_FIRST_WARP && lane == 0 && turn < 8) WTRACE(4 * turn);
+            alive = warp_mbar_wait(smem_u32(&acc_full[acc]), (turn >> 1) & 1u, abort_flag, args.status);
+            if (!alive) break;
+            if (warp == Wide::DRAIN_FIRST_WARP && lane == 0 && turn < 8) WTRACE(4 * turn + 1);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float* __restrict__ out = args.c[w.product] + static_cast<uint64_t>(w.split) * pm * pldc;
+            const uint32_t first_row = w.m0 + quarter * 32u;
+            uint32_t upper[3] = {0u, 0u, 0u};
+            upper[args.c_order.row] = first_row;
+            upper[args.c_order.outer] = w.split;
+#pragma unroll 1
+            for (uint32_t col = 0; col < 128; col += 32, ++filled) {
+                char* const slab = my_slabs + (filled & 1u) * Wide::SLAB_BYTES;
+                const bool traced = warp == Wide::DRAIN_FIRST_WARP && lane == 0 && turn == 3;
+                if (traced) WTRACE(128 + (col >> 5) * 5);
+                // The store that last read this slab (two chunks ago) has finished reading it.
+                if (args.c_tma) {
+                    if (lane == 0) tc::tma_store_wait_read<1>();
+                    __syncwarp();
+                }
+                if (traced) WTRACE(129 + (col >> 5) * 5);
+                uint32_t r1[32], r2[32];
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * Wide::ACC_COLUMNS + col;
+                tmem_load32(taddr, r1);
+                tmem_load32(taddr + 128, r2);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (col == 96) {
+                    // The whole accumulator is in registers or stored: the MMA warp may write it again.
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+                    if (warp == Wide::DRAIN_FIRST_WARP && lane == 0 && turn < 8) WTRACE(4 * turn + 2);
+                }
+                if (traced) WTRACE(130 + (col >> 5) * 5);
+                const uint32_t gn0 = w.n0 + col;
+                if (gn0 >= pn) continue;  // the same for the whole warp
+#pragma unroll
+                for (uint32_t j = 0; j < 32; j += 4) {
+                    float4 v;
+                    // `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
+                    v.x = (__uint_as_float(r1[j]) + __uint_as_float(r2[j])) + 0.0f;
+                    v.y = (__uint_as_float(r1[j + 1]) + __uint_as_float(r2[j + 1])) + 0.0f;
+                    v.z = (__uint_as_float(r1[j + 2]) + __uint_as_float(r2[j + 2])) + 0.0f;
+                    v.w = (__uint_as_float(r1[j + 3]) + __uint_as_float(r2[j + 3])) + 0.0f;
+                    if (bias_row) {
+                        // Columns col + j .. + 3 are held by lane (col + j) / 4 (zeros past n).
+                        const uint32_t holder = (col + j) >> 2;
+                        v.x = v.x + __shfl_sync(0xffffffffu, bias4.x, holder);
+                        v.y = v.y + __shfl_sync(0xffffffffu, bias4.y, holder);
+                        v.z = v.z + __shfl_sync(0xffffffffu, bias4.z, holder);
+                        v.w = v.w + __shfl_sync(0xffffffffu, bias4.w, holder);
+                    }
+                    *reinterpret_cast<float4*>(slab + tc::swizzled_chunk(lane, j >> 2)) = v;
+                }
+                if (traced) WTRACE(131 + (col >> 5) * 5);
+                if (args.c_tma) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0 && first_row < pm) tc::tma_store(&maps.c[w.product], smem_u32(slab), gn0, upper);
+                    if (traced) WTRACE(132 + (col >> 5) * 5);
+                    continue;
+                }
+                __syncwarp();
+                const uint32_t c4 = (lane & 7u) * 4, gn = gn0 + c4;
+#pragma unroll
+                for (uint32_t pass = 0; pass < 8; ++pass) {
+                    const uint32_t row = pass * 4 + (lane >> 3), gm = first_row + row;
+                    if (gm >= pm || gn >= pn) continue;
+                    const float4 v = *reinterpret_cast<const float4*>(slab + tc::swizzled_chunk(row, lane & 7u));
+                    float* dst = out + static_cast<uint64_t>(gm) * pldc + gn;
+                    // Inside the pitch a whole float4 may be written: what lies past n is padding.
+                    if (args.c_vec && (gn + 4 <= pn || (args.c_padded && gn + 4 <= pldc))) {
+                        *reinterpret_cast<float4*>(dst) = v;
+                    } else {
+                        if (gn < pn) dst[0] = v.x;
+                        if (gn + 1 < pn) dst[1] = v.y;
+                        if (gn + 2 < pn) dst[2] = v.z;
+                        if (gn + 3 < pn) dst[3] = v.w;
+                    }
+                }
+                __syncwarp();
+            }
+            if (warp == Wide::DRAIN_FIRST_WARP && lane == 0 && turn < 8) WTRACE(4 * turn + 3);
+        }
+        // The slabs must outlive the stores that read them.
+        if (args.c_tma && lane == 0) tc::tma_store_wait_read<0>();
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Wide::TMEM_COLUMNS) : "memory");
     }
 }
 
@@ -592,8 +1061,36 @@ template <int BM, int BN> void launch_forms(cudaStream_t s, const TcArgs& args, 
     else launch<BM, BN, false, false>(s, args, grid);
 }
 
-void launch_tile(cudaStream_t s, const TcArgs& args, dim3 grid, uint32_t bm, uint32_t bn, bool a_t, bool b_t) {
-    if (bm == 128) launch_forms<128, 128>(s, args, grid, a_t, b_t);
+template <bool A_T, bool B_T> void launch_wide(cudaStream_t s, const TcArgs& args, const WideMaps& maps, uint32_t units) {
+    auto kernel = matmul_tc_wide_kernel<A_T, B_T>;
+    static std::atomic<int> configured_device{-1};
+    static std::atomic<int> sm_count{0};
+    int device = 0;
+    check(cudaGetDevice(&device), "cudaGetDevice");
+    if (device != configured_device.load(std::memory_order_relaxed)) {
+        check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Wide::TOTAL)), "matmul_tc_wide shared memory");
+        int sms = 0;
+        check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
+        sm_count.store(sms, std::memory_order_relaxed);
+        configured_device.store(device, std::memory_order_relaxed);
+    }
+    // One CTA per SM, each walking its share of the units.
+    uint32_t sms = static_cast<uint32_t>(sm_count.load(std::memory_order_relaxed));
+#ifdef MSX_TC_TRACE
+    if (const char* forced = std::getenv("MSX_TC_WIDE_GRID")) sms = static_cast<uint32_t>(std::atoi(forced));
+#endif
+    kernel<<<units < sms ? units : sms, Wide::THREADS, Wide::TOTAL, s>>>(args, maps);
+    check_launch("matmul_tc_wide");
+}
+
+void launch_tile(cudaStream_t s, const TcArgs& args, dim3 grid, uint32_t bm, uint32_t bn, bool a_t, bool b_t, const WideMaps* maps = nullptr) {
+    if (bm == 128) {
+        const uint32_t units = grid.x * grid.y * grid.z;
+        if (a_t && b_t) launch_wide<true, true>(s, args, *maps, units);
+        else if (a_t) launch_wide<true, false>(s, args, *maps, units);
+        else if (b_t) launch_wide<false, true>(s, args, *maps, units);
+        else launch_wide<false, false>(s, args, *maps, units);
+    }
     else if (bn == 32) launch_forms<64, 32>(s, args, grid, a_t, b_t);
     else if (bn == 64) launch_forms<64, 64>(s, args, grid, a_t, b_t);
     else launch_forms<64, 128>(s, args, grid, a_t, b_t);
@@ -631,7 +1128,7 @@ MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problem
         if (const char* forced = std::getenv("MSX_TC_FORCE_BM"))
             if (static_cast<uint32_t>(std::atoi(forced)) != rows[w]) continue;
 #endif
-        if (rows[w] == 128 && problems > 1) continue;  // batched products stay on the narrow tiles
+        if (rows[w] == 128 && (problems > 1 || kblocks == 0)) continue;  // batched and empty products stay on the narrow tiles
         const uint64_t m_tiles = (m + rows[w] - 1) / rows[w], n_tiles = (n + widths[w] - 1) / widths[w];
         const uint64_t tiles = m_tiles * n_tiles * problems * group;
         const uint64_t most = problems > 1 ? 1 : (kblocks / 2 > 0 ? kblocks / 2 : 1);
@@ -641,7 +1138,7 @@ MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problem
             if (used != splits) continue;  // the same partition as a smaller count
             const uint64_t per_sm = (tiles * splits + 147) / 148;
             const uint64_t together = rows[w] == 128 ? 1 : 2;  // CTAs that share an SM and overlap
-            const double fixed = rows[w] == 128 ? MSX_TC_FIXED_WIDE : MSX_TC_FIXED;
+            const double fixed = MSX_TC_FIXED;
             const double paired = static_cast<double>((per_sm + together - 1) / together) * (fixed + static_cast<double>(per) * latency[w]);
             const double streamed = static_cast<double>(per_sm * per) * per_block[w];
             // Every tile reads its rows of A and columns of B over k; what the SMs can pull
@@ -651,6 +1148,12 @@ MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problem
                                   static_cast<double>(m * n * (splits > 1 ? splits : 1)));
             const double traffic = bytes / MSX_TC_BYTES_PER_CYCLE;
             double cost = paired > streamed ? paired : streamed;
+            // The persistent kernel pays its set-up and its last drain once; a tile's drain runs
+            // under the next tile's k loop.
+            if (rows[w] == 128) {
+                const double k_loop = static_cast<double>(per) * MSX_TC_KB_WIDE;
+                cost = MSX_TC_FIXED_WIDE + static_cast<double>(per_sm) * ((k_loop > MSX_TC_DRAIN_WIDE ? k_loop : MSX_TC_DRAIN_WIDE) + MSX_TC_TILE_WIDE);
+            }
             if (traffic > cost) cost = traffic;
             if (splits > 1) cost += MSX_TC_REDUCE_FIXED + static_cast<double>(m * n * (splits + 1)) * 4.0 / MSX_TC_REDUCE_BYTES_PER_CYCLE;
             if (best.bn == 0 || cost < best_cost) {
@@ -681,6 +1184,7 @@ void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t co
     args.ldc = (pitches.c && p.splits == 1) ? pitches.c : static_cast<uint32_t>(n);
     if (pitches.c && p.splits > 1) throw std::invalid_argument("matmul_tc_group: a pitched result with a split k");
     args.splits = p.splits;
+    args.products = count;
     args.kblocks_per_split = p.kblocks_per_split;
     // A float4 read starts at a multiple of 4 elements within a row, so rows must keep that phase.
     args.a_vec = args.lda % 4 == 0;
@@ -698,7 +1202,25 @@ void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t co
     }
     args.status = status;
     dim3 grid(static_cast<uint32_t>((n + p.bn - 1) / p.bn), static_cast<uint32_t>((m + p.bm - 1) / p.bm), p.splits * count);
-    launch_tile(s, args, grid, p.bm, p.bn, a_t, b_t);
+    WideMaps maps = {};
+    if (p.bm == 128) {
+        // C through TMA stores when its rows can be addressed that way: the result as it is
+        // stored, the split-k workspace as `splits` dense [m, n] matrices.
+        const bool partial = p.splits > 1;
+        bool addressable = true;
+        for (uint32_t g = 0; g < count; ++g) {
+            const HalfMatrix target = {args.c[g], args.ldc, partial ? m * n : 0, 0, false};
+            addressable = addressable && tc::tma_addressable(target, true);
+        }
+        if (addressable) {
+            for (uint32_t g = 0; g < count; ++g) {
+                const HalfMatrix target = {args.c[g], args.ldc, partial ? m * n : 0, 0, false};
+                maps.c[g] = tc::encode(target, n, m, 1, partial ? p.splits : 1, 32, &args.c_order, "C", true);
+            }
+            args.c_tma = 1;
+        }
+    }
+    launch_tile(s, args, grid, p.bm, p.bn, a_t, b_t, &maps);
     if (p.splits > 1 && !leave_partials) {
         uint64_t total = m * n;
         uint64_t blocks = (total + 255) / 256;

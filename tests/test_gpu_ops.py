@@ -79,11 +79,13 @@ def matmul_program(form, m, k, n, r):
 
 
 @pytest.mark.parametrize("m,k,n", [(128, 32, 128), (128, 64, 64), (8, 4, 1), (64, 784, 128), (130, 129, 67), (300, 1000, 40),
-                                   (832, 128, 1002), (256, 4096, 128), (70, 3003, 130), (1, 1, 1)])
+                                   (832, 128, 1002), (256, 4096, 128), (70, 3003, 130), (1, 1, 1), (1300, 100, 4001), (2100, 330, 2500)])
 @pytest.mark.parametrize("form", ["nn", "tn", "nt", "tt"])
 def test_tensor_core_matmul_within_the_kernel_tolerance(device, m, k, n, form):
     """3xTF32 on tcgen05: every storage form, tile tails in m, n and k, unaligned rows (no
-    16-byte loads), and k split across CTAs; |g - c| <= 1e-5 + 1e-4 r with r = sum |a||b|."""
+    16-byte loads), k split across CTAs, and more 128 x 128 tiles than SMs (a CTA of the persistent
+    kernel then walks several, the drain of one under the k loop of the next);
+    |g - c| <= 1e-5 + 1e-4 r with r = sum |a||b|."""
     r = rng(m * 7 + k * 3 + n)
     text, feed, out, am, bm = matmul_program(form, m, k, n, r)
     [(cpu, gpu)] = run_both(device, text, feed, outputs=[(out, m * n)], flags=M.PLAN_NO_GRAPH)
