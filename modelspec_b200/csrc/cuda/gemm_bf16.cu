@@ -247,6 +247,18 @@ matmul_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         for (uint32_t w = blockIdx.x; w < total && alive; w += gridDim.x, ++item) {
             const Work k = work_of(args, w);
             const uint32_t acc = item & 1u, acc_phase = (item >> 1) & 1u;
+            const bool partial = args.splits > 1;
+            // The tile's bias values, lane l holding columns l, l + 32, ..., fetched before the
+            // wait for the tile (a load issued inside the drain waits behind everything else the
+            // SM has in flight) and handed round by shuffles.
+            float held[BN / 32];
+            if (args.bias != nullptr && !partial) {
+#pragma unroll
+                for (int i = 0; i < BN / 32; ++i) {
+                    const uint32_t c = k.tile_n * BN + i * 32 + lane;
+                    held[i] = c < args.n ? __ldg(args.bias + c) : 0.0f;
+                }
+            }
             alive = mbar_wait(smem_u32(&acc_full[acc]), acc_phase, abort_flag, args.status);
             alive = __all_sync(0xffffffffu, alive);  // tcgen05.ld is warp-wide: decide as a warp
             if (!alive) break;
@@ -254,7 +266,6 @@ matmul_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             const bool has_k = k.kb1 > k.kb0;
             const uint32_t row = k.tile_m * BM + quarter * 32u + lane;
             const uint64_t z_at = static_cast<uint64_t>(k.z_outer) * args.c_outer + static_cast<uint64_t>(k.z_inner) * args.c_inner;
-            const bool partial = args.splits > 1;
             const uint64_t row_at = (partial ? static_cast<uint64_t>(k.split) * args.m * args.n : z_at) + static_cast<uint64_t>(row) * args.ldc;
             const bool half_out = args.out_half != 0 && !partial;
             if (args.c_tma) {
@@ -290,9 +301,13 @@ matmul_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
                         if (args.bias != nullptr && !partial) {
+                            const uint32_t group = (c0 + part * 32) >> 5;
+                            float mine = held[0];
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col + part * 32 + j < args.n) v[j] += __ldg(args.bias + col + part * 32 + j);
+                            for (int q = 1; q < BN / 32; ++q)
+                                if (group == static_cast<uint32_t>(q)) mine = held[q];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, mine, j);
                         }
                         if (half_out) {
 #pragma unroll

@@ -416,7 +416,17 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
     // SETS register sets: the loads of the next SETS - 1 blocks are in flight while a block is
     // split and stored.
     float4 av[SETS][A_CHUNKS], bv[SETS][B_CHUNKS];
+    // The four bias values this thread adds in the epilogue, fetched with the first loads: a load
+    // issued in the epilogue would be a round trip to memory with nothing to hide behind.
+    const float* __restrict__ bias_row = (job_c || args.job_count) ? nullptr : args.bias[product];
+    float bias_mine[4] = {0.f, 0.f, 0.f, 0.f};
     if (warp < 8) {
+        if (bias_row) {
+            const uint32_t gn = n0 + (lane % (BN / 4)) * 4;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (gn + q < pn) bias_mine[q] = __ldg(bias_row + gn + q);
+        }
 #pragma unroll
         for (int s = 0; s < SETS - 1; ++s)
             if (static_cast<uint32_t>(s) < kblocks) fetch(s, av[s], bv[s]);
@@ -517,7 +527,6 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
         if (tid == 0) TRACE(13);
         float* __restrict__ out = batched ? args.c[0] + z_outer * args.c_outer + z_inner * args.c_inner
                                           : (job_c ? job_c : args.c[product]) + static_cast<uint64_t>(split) * pm * pldc;
-        const float* __restrict__ bias_row = job_c ? nullptr : args.bias[product];
         constexpr uint32_t LANES_PER_ROW = BN / 4, ROWS_PER_PASS = 32 / LANES_PER_ROW;
         const uint32_t c4 = (lane % LANES_PER_ROW) * 4, gn = n0 + c4;
 #pragma unroll 4
@@ -530,8 +539,7 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
             float v[4] = {(h.x + l.x) + 0.0f, (h.y + l.y) + 0.0f, (h.z + l.z) + 0.0f, (h.w + l.w) + 0.0f};
             if (bias_row) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    if (gn + q < pn) v[q] = v[q] + bias_row[gn + q];
+                for (int q = 0; q < 4; ++q) v[q] = v[q] + bias_mine[q];
             }
             float* dst = out + static_cast<uint64_t>(gm) * pldc + gn;
             // Inside the pitch a whole float4 may be written: what lies past n is padding.

@@ -877,8 +877,8 @@ int msx_training_run(msx_training* t, uint64_t start, uint64_t eval_every) {
         auto evaluated = [&](uint64_t k) { return evaluating && (k % eval_every == 0 || k == end); };
         // Losses are read a few steps behind the submissions; the lines come out in step order.
         std::map<uint64_t, std::pair<float, float>> evals;
-        auto lines_of = [&](uint64_t k, float loss) {
-            if (k == start || k % kLossEvery == 0 || k == end || evals.count(k)) out += "step " + std::to_string(k) + " loss " + msx::f32_display(loss) + "\n";
+        auto lines_of = [&](uint64_t k, float loss, bool last = false) {
+            if (k == start || k % kLossEvery == 0 || k == end || last || evals.count(k)) out += "step " + std::to_string(k) + " loss " + msx::f32_display(loss) + "\n";
             auto e = evals.find(k);
             if (e != evals.end())
                 out += "eval " + std::to_string(k) + " loss " + msx::f32_display(e->second.first) + " accuracy " + msx::f32_display(e->second.second) + "\n";
@@ -887,9 +887,10 @@ int msx_training_run(msx_training* t, uint64_t start, uint64_t eval_every) {
             float loss = 0.0f;
             const int rc = msx_training_loss_of(t, k, &loss);
             if (rc == MSX_NON_FINITE) {
-                // The run stops at this step: its line is the last one, and there are no `param` lines.
+                // The run stops at this step: its line is the last one (the last loss of a run
+                // always has its line), and there are no `param` lines.
                 ok(t, msx_loss_of(t->step, t->submitted_as.at(k), &loss, 0));
-                lines_of(k, loss);
+                lines_of(k, loss, true);
                 throw Fail{MSX_NON_FINITE, t->error};
             }
             if (rc != MSX_OK) throw Fail{rc, t->error};
