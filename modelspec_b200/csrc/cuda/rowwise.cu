@@ -824,6 +824,9 @@ __global__ void __launch_bounds__(256, ITEMS >= 16 ? 2 : 1) layer_norm_backward_
                 float gx = gv[i] * gamma_of(i);
                 s1 += gx;
                 s2 = fmaf(gx, xhat, s2);
+                // The dx row below is a function of these two: kept in the registers of x and g.
+                xv[i] = xhat;
+                gv[i] = gx;
             }
         if (want_dx) {
             const float mean_gx = warp_sum(s1) / width, mean_gx_xhat = warp_sum(s2) / width;
@@ -835,8 +838,7 @@ __global__ void __launch_bounds__(256, ITEMS >= 16 ? 2 : 1) layer_norm_backward_
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i) {
                 const uint32_t c = column_of<V>(i, lane);
-                float gx = gv[i] * gamma_of(i);
-                float xhat = (xv[i] - mean) * rstd;
+                const float gx = gv[i], xhat = xv[i];
                 const float value = rstd * ((gx - mean_gx) - xhat * mean_gx_xhat);
                 xv[i] = value;  // the dx row, in the registers of the x row
                 second[i] = 0.0f;
