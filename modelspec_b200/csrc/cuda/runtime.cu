@@ -388,39 +388,72 @@ struct Scheduler {
                 hoist_last_launch();
             }
         }
-        if (!deferred_rows.empty()) {
+        finish_deferred_sums();
+    }
+
+    // The deferred sums entered since the last call, as one launch for the first stages of the
+    // column sums and one for every second stage: the job tables are cut here, each launch
+    // walking its own part.
+    void finish_deferred_sums() {
+        if (deferred_rows.size() > rows_finished) {
             std::vector<uint32_t> reads, writes;
             uint32_t blocks = 0;
-            for (const DeferredRows& d : deferred_rows) {
+            for (size_t i = rows_finished; i < deferred_rows.size(); ++i) {
+                const DeferredRows& d = deferred_rows[i];
                 reads.push_back(d.g);
                 writes.push_back(d.partial);
                 blocks += k::row_sum_job_blocks(d.rows, d.width);
             }
             Node pseudo;
-            pseudo.id = node(deferred_rows[0].g).id;
+            pseudo.id = node(deferred_rows[rows_finished].g).id;
             msx_plan* plan = P;
-            const uint32_t jobs = static_cast<uint32_t>(deferred_rows.size());
-            emit("sum_rows_batched", pseudo, reads, writes,
-                 [=](cudaStream_t s) { k::sum_rows_batched(s, static_cast<const k::RowSumJob*>(plan->d_row_sum_jobs), jobs, blocks); });
+            const size_t first = rows_finished;
+            const uint32_t jobs = static_cast<uint32_t>(deferred_rows.size() - rows_finished);
+            emit("sum_rows_batched", pseudo, reads, writes, [=](cudaStream_t s) {
+                k::sum_rows_batched(s, static_cast<const k::RowSumJob*>(plan->d_row_sum_jobs) + first, jobs, blocks);
+            });
             hoist_last_launch();
+            rows_cuts.push_back(rows_finished);
+            rows_finished = deferred_rows.size();
         }
-        if (deferred.empty()) return;
+        if (deferred.size() == sums_finished) return;
         std::vector<uint32_t> reads, writes;
         uint32_t blocks = 0;
-        for (const Deferred& d : deferred) {
+        for (size_t i = sums_finished; i < deferred.size(); ++i) {
+            const Deferred& d = deferred[i];
             reads.push_back(d.partial);
             writes.push_back(d.out);
             blocks += k::sum_job_blocks(d.chunks, d.width);
         }
         Node pseudo;
-        pseudo.id = node(deferred[0].out).id;
+        pseudo.id = node(deferred[sums_finished].out).id;
         msx_plan* plan = P;
-        const uint32_t jobs = static_cast<uint32_t>(deferred.size());
-        emit("finalize_sums", pseudo, reads, writes,
-             [=](cudaStream_t s) { k::finalize_sums(s, static_cast<const k::SumJob*>(plan->d_sum_jobs), jobs, blocks); });
-        // Issued as soon as the last partial sums exist: what follows them in the backward pass (the
-        // embedding gradients) does not read its results, so it runs beside that.
+        const size_t first = sums_finished;
+        const uint32_t jobs = static_cast<uint32_t>(deferred.size() - sums_finished);
+        emit("finalize_sums", pseudo, reads, writes, [=](cudaStream_t s) {
+            k::finalize_sums(s, static_cast<const k::SumJob*>(plan->d_sum_jobs) + first, jobs, blocks);
+        });
+        // Issued as soon as the last partial sums exist: what follows them in the backward pass
+        // does not read its results, so it runs beside that.
         hoist_last_launch();
+        sums_cuts.push_back(sums_finished);
+        sums_finished = deferred.size();
+    }
+    // Where each launch's part of the two job tables starts.
+    std::vector<size_t> rows_cuts, sums_cuts;
+    size_t rows_finished = 0, sums_finished = 0;
+    // A large model's deferred sums are finished a layer's worth at a time rather than all at the
+    // end of the backward pass: the gradients they complete can then be exchanged (a data-parallel
+    // run reduces a bucket as soon as the launch that completes it has been issued) while the
+    // layers below are still being differentiated. Products waiting as jobs of one launch write
+    // partial sums of their own, so nothing is finished early while any wait.
+    static constexpr uint64_t kFinishSumsBytes = 24ull << 20;
+    void finish_deferred_sums_when_large() {
+        for (int form = 0; form < 4; ++form)
+            if (!deferred_matmuls[form].empty()) return;
+        uint64_t pending = 0;
+        for (size_t i = sums_finished; i < deferred.size(); ++i) pending += deferred[i].width * 4;
+        if (pending >= kFinishSumsBytes) finish_deferred_sums();
     }
 
     // A matmul or column-sum launch whose results are first read at least `kSideGap` launches
@@ -585,7 +618,10 @@ struct Scheduler {
         plan_optimizer();
         fold_transposes();
         for (uint32_t at = 0; at < n; ++at)
-            if (live[at] && !handled[at]) schedule(at);
+            if (live[at] && !handled[at]) {
+                schedule(at);
+                finish_deferred_sums_when_large();
+            }
         emit_finalize();
         emit_optimizer();
         if (mixed()) check_half_widths();
@@ -2320,6 +2356,8 @@ void allocate(msx_plan* P, const Scheduler& sched) {
         std::vector<k::RowSumJob> jobs;
         uint32_t first_block = 0;
         for (const Scheduler::DeferredRows& d : sched.deferred_rows) {
+            // A launch counts its blocks from the start of its own part of the table.
+            if (std::find(sched.rows_cuts.begin(), sched.rows_cuts.end(), jobs.size()) != sched.rows_cuts.end()) first_block = 0;
             jobs.push_back(k::row_sum_job(P->in(d.g), static_cast<float*>(P->ptr(d.partial)), d.rows, d.width,
                                           d.ld, first_block));
             first_block += k::row_sum_job_blocks(d.rows, d.width);
@@ -2331,6 +2369,7 @@ void allocate(msx_plan* P, const Scheduler& sched) {
         std::vector<k::SumJob> jobs;
         uint32_t first_block = 0;
         for (const Scheduler::Deferred& d : sched.deferred) {
+            if (std::find(sched.sums_cuts.begin(), sched.sums_cuts.end(), jobs.size()) != sched.sums_cuts.end()) first_block = 0;
             k::SumJob job = {};
             job.partial = static_cast<const float*>(P->ptr(d.partial)) + d.offset;
             job.out = static_cast<float*>(P->ptr(d.out));
