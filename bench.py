@@ -12,7 +12,9 @@ CPU oracle (a port of the reference's single-threaded interpreter) timed on this
 `--impl reference` times that CPU port alone with every host thread.
 """
 import argparse
+import datetime
 import json
+import math
 import os
 import subprocess
 import sys
@@ -64,6 +66,9 @@ def ncu_traffic(config, kernel, flop, nbytes):
     return entry["dram_bytes"] if entry else None
 
 
+# The most blocks of --steps steps one invocation times (a short step gets more than --blocks).
+kMostBlocks = 40
+
 L2_NOTE = "no explicit flush: every step streams over 1 GB of intermediates through the 126 MB L2"
 
 
@@ -85,20 +90,27 @@ class ClockSampler:
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_power_cap,timestamp")
 
     def __init__(self, gpu_index):
+        # Started before the warm-up (nvidia-smi takes a few hundred milliseconds to deliver its
+        # first sample); only the samples between begin() and stop() are kept.
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.begun = time.time()
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
+    def begin(self):
+        self.begun = time.time()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        ended = time.time()
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -110,6 +122,9 @@ class ClockSampler:
         sm, mx, reasons = [], [], set()
         for r in rows:
             try:
+                taken = datetime.datetime.strptime(r[9].strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if taken < self.begun or taken > ended:
+                    continue
                 sm.append(float(r[1])); mx.append(float(r[2]))
             except (ValueError, IndexError):
                 continue
@@ -227,7 +242,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-steps", type=int, default=2, help="steps of the single-threaded CPU baseline (rank 0, N=1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--blocks", type=int, default=7, help="how many times the block of --steps steps is timed")
+    ap.add_argument("--blocks", type=int, default=None,
+                    help="how many times the block of --steps steps is timed (default: 7, more for a step so short that "
+                         "7 blocks would last under 0.6 s, fewer for one so long that they would last over 20 s)")
     ap.add_argument("--flags", type=int, default=0, help="plan flags (modelspec_b200.PLAN_*)")
     args = ap.parse_args()
     # Standard output carries the one JSON line and nothing else: what libraries print there (NCCL
@@ -258,8 +275,8 @@ def main():
         parity = dp_parity(M, dist, rank, world, local)
 
     W, K = max(args.warmup, 3), args.steps
-    blocks_asked = max(1, args.blocks)
-    total = W + K * (blocks_asked + 1)
+    blocks_asked = max(1, args.blocks if args.blocks is not None else 7)
+    total = W + K * (max(blocks_asked, kMostBlocks) + 1)
     end = total + 8
     source = cfg["source"](steps=end, warmup_steps=max(1, total // 10))
     masked = models.default_masked_rows(cfg["rows"])
@@ -295,15 +312,21 @@ def main():
     # reference's training clock) and one pair around every step (for the median step time).
     for name, value in batch_of(0).items():
         run.set_input(name, value)
+    sampler = ClockSampler(local)
     t0 = time.perf_counter()
     for k in range(W):
         run.step(k, end)
     barrier()
-    warm_ms = (time.perf_counter() - t0) * 1e3 / W
+    warm_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / W)  # every rank times the same number of blocks
     # A long step (the BERT-base-shaped configuration) gets fewer blocks: about 20 s in all.
     blocks = int(max(1, min(blocks_asked, 20000.0 / max(warm_ms * K, 1e-3))))
+    # A short step gets more blocks, so that the timed region lasts long enough (0.6 s) for the
+    # clock sampler to see it several times.
+    if args.blocks is None:
+        last_ms = max_over_ranks(plan.step_ms(plan.steps_submitted() - 1))  # the warm-up's average holds the first step's set-up
+        blocks = int(max(blocks, min(kMostBlocks, math.ceil(600.0 / max(last_ms * K, 1e-3)))))
     lag = 4
-    sampler = ClockSampler(local)
+    sampler.begin()
     block_ms, step_ms = [], []
     for _ in range(blocks):
         barrier()

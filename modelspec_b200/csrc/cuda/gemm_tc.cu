@@ -142,23 +142,8 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// One poll of a barrier phase. The thread may sleep in the instruction for up to the hinted time
-// and is woken when the phase completes: a waiting role then costs the SM's shared-memory pipe
-// next to nothing, where a tight polling loop of 256 threads slows the roles that are working.
-#ifndef MSX_TC_WAIT_HINT_NS
-#define MSX_TC_WAIT_HINT_NS 0
-#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-#if MSX_TC_WAIT_HINT_NS > 0
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(MSX_TC_WAIT_HINT_NS))
-        : "memory");
-#else
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -166,7 +151,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
-#endif
     return ok != 0;
 }
 // Waits for `parity` of `bar`; false when the wait ran out or another role gave up.
@@ -631,12 +615,6 @@ struct Wide {
 #ifndef MSX_TC_WIDE_SETS
 #define MSX_TC_WIDE_SETS 2
 #endif
-#ifndef MSX_TC_WIDE_ORDER
-#define MSX_TC_WIDE_ORDER 1
-#endif
-#ifndef MSX_TC_WIDE_WARP_SYNC
-#define MSX_TC_WIDE_WARP_SYNC 0
-#endif
     static constexpr int STAGES = 3, SETS = MSX_TC_WIDE_SETS, DRAIN_WARPS = 4;  // SETS: register sets of loads in flight
     // Four groups of four warps: two of loaders, one whose first warp issues the MMAs, one of
     // drain warps. The register file is dealt out again by group after the set-up (the loaders'
@@ -696,7 +674,7 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&bars[s]), MSX_TC_WIDE_WARP_SYNC ? LOADER_THREADS / 32 : LOADER_THREADS);  // one arrival per loader warp
+            mbar_init(smem_u32(&bars[s]), LOADER_THREADS);
             mbar_init(smem_u32(&bars[STAGES + s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -816,33 +794,16 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
             char* b_tile = a_tile + Wide::A_BYTES;
             // The stage is free once the MMAs that read its previous contents have completed.
             if (tid == 0 && deposited < 24) WTRACE(64 + 2 * deposited);
-#if MSX_TC_WIDE_WARP_SYNC
-            if (!warp_mbar_wait(smem_u32(&bars[STAGES + stage]), parity, abort_flag, args.status)) return false;
-#else
             if (!mbar_wait(smem_u32(&bars[STAGES + stage]), parity, abort_flag, args.status)) return false;
-#endif
             if (tid == 0 && deposited < 24) WTRACE(65 + 2 * deposited);
             ++deposited;
-            const bool stamped = tid == 0 && deposited >= 9 && deposited < 17;
-            if (stamped) WTRACE(160 + 6 * (deposited - 9));
 #pragma unroll
             for (int i = 0; i < CHUNKS; ++i) store_split(a_tile, aoff + i * A_TILE_STEP, aoff + i * A_TILE_STEP + Wide::A_BYTES / 2, a_regs[i]);
-            if (stamped) WTRACE(161 + 6 * (deposited - 9));
 #pragma unroll
             for (int i = 0; i < CHUNKS; ++i) store_split(b_tile, boff + i * B_TILE_STEP, boff + i * B_TILE_STEP + Wide::B_BYTES / 2, b_regs[i]);
-            if (stamped) WTRACE(162 + 6 * (deposited - 9));
-            // Every lane makes its stores visible to the tensor core's async-proxy reads; one
-            // lane then arrives for the warp (256 arrivals on one barrier word are 256 serialised
-            // shared-memory atomics per k block).
+            // Make the generic-proxy stores visible to the tensor core's async-proxy reads.
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#if MSX_TC_WIDE_WARP_SYNC
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars[stage]));
-#else
-            if (stamped) WTRACE(163 + 6 * (deposited - 9));
             mbar_arrive(smem_u32(&bars[stage]));
-#endif
-            if (stamped) WTRACE(164 + 6 * (deposited - 9));
             if (++stage == STAGES) { stage = 0; parity ^= 1u; }
             return true;
         };
@@ -851,15 +812,8 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
             for (int s = 0; s < SETS; ++s) {
                 const uint32_t g = g0 + s;
                 if (g >= total || !alive) break;
-#if MSX_TC_WIDE_ORDER == 0
-                if (g + SETS - 1 < total) fetch_next(av[(s + SETS - 1) % SETS], bv[(s + SETS - 1) % SETS]);
-                alive = deposit(av[s], bv[s]);
-#else
-                // The block's stores and their fence first, the next loads after them: a fence
-                // that followed freshly issued loads would wait for them.
                 alive = deposit(av[s], bv[s]);
                 if (g + SETS - 1 < total) fetch_next(av[(s + SETS - 1) % SETS], bv[(s + SETS - 1) % SETS]);
-#endif
             }
         }
     } else if (warp < Wide::DRAIN_FIRST_WARP) {
