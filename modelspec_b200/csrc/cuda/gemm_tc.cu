@@ -68,7 +68,7 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives
 // The 128 x 128 tile (a persistent CTA per SM): per launch, per k block (four MMAs of
 // 128 x 256 x 8 and four of 128 x 128 x 8) and per tile.
 #define MSX_TC_FIXED_WIDE 8000.0
-#define MSX_TC_KB_WIDE 2300.0
+#define MSX_TC_KB_WIDE 1550.0
 #define MSX_TC_TILE_WIDE 500.0
 #define MSX_TC_DRAIN_WIDE 5000.0  // a tile's drain, which bounds a tile of few k blocks
 // Operand bytes all SMs together pull through the L2 per SM cycle.
@@ -109,6 +109,7 @@ struct TcArgs {
     uint32_t c_padded;             // the columns of C between n and ldc are padding that may be overwritten
     uint32_t c_tma;                // the 128 x 128 tile writes C (or the split-k workspace) by TMA stores
     tc::CoordOrder c_order;        // where the row and split coordinates sit in the tensor maps of C
+    tc::CoordOrder a_order, b_order;  // the same for the operands of the 128 x 128 tile
     // Batched products: grid.z = batch index z, split as (z / inner, z % inner); each matrix of
     // problem z starts at outer * stride_outer + inner * stride_inner elements. inner = 0: not batched.
     uint32_t batch_inner;
@@ -603,29 +604,30 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
 // columns) and one of A_lo with B_hi alone (N = 128) add hi*hi + lo*hi and hi*lo into the two
 // column halves of one accumulator (lo*lo, below 2^-20 of a product, is left out). One CTA per SM
 // walks the launch's tiles (block b takes units b, b + grid, ...), so the set-up of a CTA is paid
-// once and the drain of a tile runs under the k loop of the next one:
-//   warps 0-7   load, split and store the k blocks of all the CTA's tiles as one sequence (the
-//               loads of the next tile's first blocks are in flight while this tile's last are
-//               stored);
+// once and the drain of a tile runs under the k loop of the next one. The raw f32 blocks come in
+// by TMA (zero-filled past the matrix edges, so no role checks bounds): loads issued by threads
+// kept too few bytes in flight to hide their latency (a k block took 1,860 cycles to load, split
+// and store against 1,070 for its MMAs).
+//   warps 0-7   split: read a raw k block (A 128 x 32, B 128 x 32) from its shared-memory slot,
+//               store the hi and lo halves in the layouts tcgen05 reads, free the slot;
 //   warp 8      issues the MMAs into one of two accumulators of 256 tensor-memory columns;
+//   warp 9      issues the TMA loads of the k blocks of all the CTA's tiles as one sequence, two
+//               blocks ahead of the splitters;
 //   warps 12-15 drain the other accumulator: a lane quarter each, 32 columns at a time into a
 //               shared-memory slab of their own (two per warp), which a TMA store writes to C
 //               while the next slab is filled.
 struct Wide {
-#ifndef MSX_TC_WIDE_SETS
-#define MSX_TC_WIDE_SETS 2
-#endif
-    static constexpr int STAGES = 3, SETS = MSX_TC_WIDE_SETS, DRAIN_WARPS = 4;  // SETS: register sets of loads in flight
-    // Four groups of four warps: two of loaders, one whose first warp issues the MMAs, one of
-    // drain warps. The register file is dealt out again by group after the set-up (the loaders'
-    // loads in flight are registers): 8 x 176 + 4 x 56 + 4 x 104 = 16 x 128.
+    static constexpr int STAGES = 2, DRAIN_WARPS = 4;  // split stages, and as many raw slots
+    // Four groups of four warps: two of splitters, one with the MMA and the TMA warp, one of drain
+    // warps.
     static constexpr int THREADS = 512, DRAIN_FIRST_WARP = 12;
     static constexpr uint32_t A_BYTES = 2 * 128 * BK * 4;  // hi tile, lo tile
     static constexpr uint32_t B_BYTES = 2 * 128 * BK * 4;  // hi columns 0-127, lo columns 128-255
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t RAW_OPERAND_BYTES = 128 * BK * 4, RAW_BYTES = 2 * RAW_OPERAND_BYTES;  // A block, B block
     static constexpr uint32_t SLAB_BYTES = 32 * 128;                     // 32 rows of 32 floats
     static constexpr uint32_t DRAIN_BYTES = DRAIN_WARPS * 2 * SLAB_BYTES;  // two slabs per drain warp
-    static constexpr uint32_t TOTAL = STAGES * STAGE_BYTES + DRAIN_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr uint32_t TOTAL = STAGES * (STAGE_BYTES + RAW_BYTES) + DRAIN_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr uint32_t ACC_COLUMNS = 256, TMEM_COLUMNS = 512;
 };
 
@@ -646,36 +648,44 @@ __device__ __forceinline__ WideUnit wide_unit(const TcArgs& args, uint32_t u, ui
     return w;
 }
 
-// The tensor maps of the results of a launch's products (or of their split-k workspaces).
+// The tensor maps of a launch's products: the operands as stored (boxes of 32 floats by 128 rows
+// for an operand stored with k along its rows, by 32 rows for one stored with k down its columns)
+// and the results (or their split-k workspaces).
 struct WideMaps {
-    CUtensorMap c[MAX_GROUP];
+    CUtensorMap a[MAX_GROUP], b[MAX_GROUP], c[MAX_GROUP];
 };
 
 template <bool A_T, bool B_T>
 __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs args, const __grid_constant__ WideMaps maps) {
-    constexpr int STAGES = Wide::STAGES, SETS = Wide::SETS;
+    constexpr int STAGES = Wide::STAGES;
     extern __shared__ char smem_raw[];
     char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    char* drain_slabs = tiles + STAGES * Wide::STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * Wide::STAGE_BYTES + Wide::DRAIN_BYTES);
-    // bars[0 .. STAGES) full, [STAGES .. 2 STAGES) empty, then accumulator b ready (2), accumulator
-    // b drained (2); then the TMEM address and the abort flag.
-    uint64_t* acc_full = bars + 2 * STAGES;
+    char* raw_blocks = tiles + STAGES * Wide::STAGE_BYTES;
+    char* drain_slabs = raw_blocks + STAGES * Wide::RAW_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(drain_slabs + Wide::DRAIN_BYTES);
+    // Barriers: split stage s filled / free, raw slot s filled / free, accumulator b ready /
+    // drained; then the TMEM address and the abort flag.
+    uint64_t* split_full = bars;
+    uint64_t* split_empty = bars + STAGES;
+    uint64_t* raw_full = bars + 2 * STAGES;
+    uint64_t* raw_empty = bars + 3 * STAGES;
+    uint64_t* acc_full = bars + 4 * STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(acc_empty + 3);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t pm = args.m, pn = args.n, pk = args.k, plda = args.lda, pldb = args.ldb, pldc = args.ldc;
+    const uint32_t pm = args.m, pn = args.n, pk = args.k, pldc = args.ldc;
     const uint32_t down = (pm + 127) / 128, across = (pn + 127) / 128;
     const uint32_t kblocks_total = (pk + BK - 1) / BK;
     const uint32_t units = down * across * args.splits * args.products;
-    const uint32_t stride = args.splits;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&bars[s]), LOADER_THREADS);
-            mbar_init(smem_u32(&bars[STAGES + s]), 1);
+            mbar_init(smem_u32(&split_full[s]), LOADER_THREADS);
+            mbar_init(smem_u32(&split_empty[s]), 1);
+            mbar_init(smem_u32(&raw_full[s]), 1);  // the TMA warp's arrival, with the bytes it expects
+            mbar_init(smem_u32(&raw_empty[s]), LOADER_THREADS);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&acc_full[b]), 1);
@@ -694,130 +704,54 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < 8) {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 176;" ::: "memory");
-        // ---- loaders ----------------------------------------------------------------------------
-        // How many k blocks this CTA stores in all: the sequence the stages count along.
+        // ---- the splitters: raw block -> (hi, lo) -> the swizzled tiles tcgen05 reads -------------
+        // How many k blocks this CTA works through in all: the sequence the stages count along.
         uint32_t total = 0;
         for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) total += wide_unit(args, u, down, across, kblocks_total).kblocks;
+        // A raw block lies as its TMA load left it, in the 128-byte swizzle: an operand stored
+        // with k along its rows as 128 rows of 128 bytes, one stored with k down its columns as
+        // four panels of 32 k rows of 128 bytes (32 of the 128 tile rows or columns each). Chunk i
+        // of a thread lies a fixed number of rows after its chunk 0, in the raw block and in the
+        // split tile alike.
         constexpr int CHUNKS = 128 * BK / 4 / LOADER_THREADS;  // 16-byte chunks of one operand block a thread moves
-        // Chunk i of a thread lies a fixed number of rows after its chunk 0, in the matrix and in
-        // the shared-memory tile alike, so one offset, one address and one mask of row checks per
-        // operand describe them all (registers are what bounds the loads in flight here).
-        constexpr uint32_t A_ROWS = A_T ? LOADER_THREADS / 32 : LOADER_THREADS / 8;  // rows from chunk i to chunk i + 1
-        constexpr uint32_t B_ROWS = B_T ? LOADER_THREADS / 8 : LOADER_THREADS / 32;
-        constexpr uint32_t A_TILE_STEP = A_T ? A_ROWS * 128u : (A_ROWS / 8) * 1024u;  // the same in tile bytes
-        constexpr uint32_t B_TILE_STEP = B_T ? (B_ROWS / 8) * 1024u : B_ROWS * 128u;
-        const uint32_t a_row = A_T ? tid >> 5 : tid >> 3, a_col = A_T ? (tid & 31u) * 4 : (tid & 7u) * 4;  // (k, m) or (m, k)
-        const uint32_t b_row = B_T ? tid >> 3 : tid >> 5, b_col = B_T ? (tid & 7u) * 4 : (tid & 31u) * 4;  // (n, k) or (k, n)
-        const uint32_t aoff = A_T ? mn_major_offset(a_row, a_col / 4) : k_major_offset(a_row, a_col / 4);
-        const uint32_t boff = B_T ? k_major_offset(b_row, b_col / 4) : mn_major_offset(b_row, b_col / 4);
-        // The tile whose blocks are being fetched: its operands, the address of chunk 0 in its
-        // first k block and, bit i, whether all four elements of chunk i lie inside the matrix rows.
-        uint32_t f_unit = blockIdx.x, f_kb = 0;
-        WideUnit f = {};
-        const float* __restrict__ fa = nullptr;
-        const float* __restrict__ fb = nullptr;
-        const float* a_at = nullptr;
-        const float* b_at = nullptr;
-        uint32_t a_whole = 0, b_whole = 0;
-        const uint64_t a_step = static_cast<uint64_t>(BK) * stride * (A_T ? plda : 1u);
-        const uint64_t b_step = static_cast<uint64_t>(BK) * stride * (B_T ? 1u : pldb);
-        auto open_unit = [&](uint32_t u) {
-            f = wide_unit(args, u, down, across, kblocks_total);
-            f_kb = 0;
-            fa = args.a[f.product];
-            fb = args.b[f.product];
-            const uint32_t first_k = f.split * BK;
-            a_at = A_T ? fa + static_cast<uint64_t>(first_k + a_row) * plda + f.m0 + a_col
-                       : fa + static_cast<uint64_t>(f.m0 + a_row) * plda + first_k + a_col;
-            b_at = B_T ? fb + static_cast<uint64_t>(f.n0 + b_row) * pldb + first_k + b_col
-                       : fb + static_cast<uint64_t>(first_k + b_row) * pldb + f.n0 + b_col;
-            a_whole = b_whole = 0;
-#pragma unroll
-            for (int i = 0; i < CHUNKS; ++i) {
-                if (args.a_vec && (A_T ? f.m0 + a_col + 4 <= pm : f.m0 + a_row + i * A_ROWS < pm)) a_whole |= 1u << i;
-                if (args.b_vec && (B_T ? f.n0 + b_row + i * B_ROWS < pn : f.n0 + b_col + 4 <= pn)) b_whole |= 1u << i;
-            }
-        };
-        // The next k block of the sequence into one register set.
-        auto fetch_next = [&](float4 (&av)[CHUNKS], float4 (&bv)[CHUNKS]) {
-            const uint32_t k0 = (f_kb * stride + f.split) * BK;
-            const bool inside = k0 + BK <= pk;
-            const float* a_block = a_at + f_kb * a_step;
-            const float* b_block = b_at + f_kb * b_step;
-#pragma unroll
-            for (int i = 0; i < CHUNKS; ++i) {
-                if (inside && (a_whole >> i & 1u)) {
-                    av[i] = load4(a_block + static_cast<uint64_t>(i * A_ROWS) * plda, 0, 4, true);
-                    continue;
-                }
-                const uint32_t row = a_row + i * A_ROWS;
-                if (A_T) {
-                    const uint32_t gk = k0 + row, gm = f.m0 + a_col;
-                    av[i] = load4(fa, static_cast<uint64_t>(gk) * plda + gm, gk < pk ? in_range(gm, pm) : 0u, args.a_vec);
-                } else {
-                    const uint32_t gm = f.m0 + row, gk = k0 + a_col;
-                    av[i] = load4(fa, static_cast<uint64_t>(gm) * plda + gk, gm < pm ? in_range(gk, pk) : 0u, args.a_vec);
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < CHUNKS; ++i) {
-                if (inside && (b_whole >> i & 1u)) {
-                    bv[i] = load4(b_block + static_cast<uint64_t>(i * B_ROWS) * pldb, 0, 4, true);
-                    continue;
-                }
-                const uint32_t row = b_row + i * B_ROWS;
-                if (B_T) {
-                    const uint32_t gn = f.n0 + row, gk = k0 + b_col;
-                    bv[i] = load4(fb, static_cast<uint64_t>(gn) * pldb + gk, gn < pn ? in_range(gk, pk) : 0u, args.b_vec);
-                } else {
-                    const uint32_t gk = k0 + row, gn = f.n0 + b_col;
-                    bv[i] = load4(fb, static_cast<uint64_t>(gk) * pldb + gn, gk < pk ? in_range(gn, pn) : 0u, args.b_vec);
-                }
-            }
-            if (++f_kb == f.kblocks) {
-                f_unit += gridDim.x;
-                if (f_unit < units) open_unit(f_unit);
-            }
-        };
-        float4 av[SETS][CHUNKS], bv[SETS][CHUNKS];
-        if (total > 0) open_unit(f_unit);
-#pragma unroll
-        for (int s = 0; s < SETS - 1; ++s)
-            if (static_cast<uint32_t>(s) < total) fetch_next(av[s], bv[s]);
+        constexpr uint32_t A_TILE_STEP = A_T ? (LOADER_THREADS / 32) * 128u : (LOADER_THREADS / 64) * 1024u;
+        constexpr uint32_t B_TILE_STEP = B_T ? (LOADER_THREADS / 64) * 1024u : (LOADER_THREADS / 32) * 128u;
+        constexpr uint32_t A_RAW_STEP = A_T ? 1024u : 4096u, B_RAW_STEP = B_T ? 4096u : 1024u;  // 8 k rows, or 32 rows
+        const uint32_t a_row = A_T ? tid >> 5 : tid >> 3, a_chunk = A_T ? tid & 31u : tid & 7u;  // (k, m) or (m, k)
+        const uint32_t b_row = B_T ? tid >> 3 : tid >> 5, b_chunk = B_T ? tid & 7u : tid & 31u;  // (n, k) or (k, n)
+        const uint32_t aoff = A_T ? mn_major_offset(a_row, a_chunk) : k_major_offset(a_row, a_chunk);
+        const uint32_t boff = B_T ? k_major_offset(b_row, b_chunk) : mn_major_offset(b_row, b_chunk);
+        const uint32_t a_raw = A_T ? (a_chunk >> 3) * 4096u + tc::swizzled_chunk(a_row, a_chunk & 7u) : tc::swizzled_chunk(a_row, a_chunk);
+        const uint32_t b_raw = B_T ? tc::swizzled_chunk(b_row, b_chunk) : (b_chunk >> 3) * 4096u + tc::swizzled_chunk(b_row, b_chunk & 7u);
         bool alive = true;
-        uint32_t stage = 0, parity = 1;  // the parity a free stage shows
-        uint32_t deposited = 0;
-        (void)deposited;
-        auto deposit = [&](const float4 (&a_regs)[CHUNKS], const float4 (&b_regs)[CHUNKS]) -> bool {
+        uint32_t stage = 0, parity = 0;
+        for (uint32_t g = 0; g < total && alive; ++g) {
+            const char* raw = raw_blocks + stage * Wide::RAW_BYTES;
             char* a_tile = tiles + stage * Wide::STAGE_BYTES;
             char* b_tile = a_tile + Wide::A_BYTES;
-            // The stage is free once the MMAs that read its previous contents have completed.
-            if (tid == 0 && deposited < 24) WTRACE(64 + 2 * deposited);
-            if (!mbar_wait(smem_u32(&bars[STAGES + stage]), parity, abort_flag, args.status)) return false;
-            if (tid == 0 && deposited < 24) WTRACE(65 + 2 * deposited);
-            ++deposited;
+            if (tid == 0 && g < 24) WTRACE(64 + 2 * g);
+            // The raw block has landed, and the MMAs that read the stage's previous contents have completed.
+            alive = mbar_wait(smem_u32(&raw_full[stage]), parity, abort_flag, args.status) &&
+                    mbar_wait(smem_u32(&split_empty[stage]), parity ^ 1u, abort_flag, args.status);
+            if (!alive) break;
+            if (tid == 0 && g < 24) WTRACE(65 + 2 * g);
+            float4 av[CHUNKS], bv[CHUNKS];
 #pragma unroll
-            for (int i = 0; i < CHUNKS; ++i) store_split(a_tile, aoff + i * A_TILE_STEP, aoff + i * A_TILE_STEP + Wide::A_BYTES / 2, a_regs[i]);
+            for (int i = 0; i < CHUNKS; ++i) av[i] = *reinterpret_cast<const float4*>(raw + a_raw + i * A_RAW_STEP);
 #pragma unroll
-            for (int i = 0; i < CHUNKS; ++i) store_split(b_tile, boff + i * B_TILE_STEP, boff + i * B_TILE_STEP + Wide::B_BYTES / 2, b_regs[i]);
-            // Make the generic-proxy stores visible to the tensor core's async-proxy reads.
+            for (int i = 0; i < CHUNKS; ++i) bv[i] = *reinterpret_cast<const float4*>(raw + Wide::RAW_OPERAND_BYTES + b_raw + i * B_RAW_STEP);
+#pragma unroll
+            for (int i = 0; i < CHUNKS; ++i) store_split(a_tile, aoff + i * A_TILE_STEP, aoff + i * A_TILE_STEP + Wide::A_BYTES / 2, av[i]);
+#pragma unroll
+            for (int i = 0; i < CHUNKS; ++i) store_split(b_tile, boff + i * B_TILE_STEP, boff + i * B_TILE_STEP + Wide::B_BYTES / 2, bv[i]);
+            // The raw slot may be loaded again (its values are in registers or stored); the split
+            // stores are visible to the tensor core's async-proxy reads before the MMA warp is told.
+            mbar_arrive(smem_u32(&raw_empty[stage]));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(smem_u32(&bars[stage]));
+            mbar_arrive(smem_u32(&split_full[stage]));
             if (++stage == STAGES) { stage = 0; parity ^= 1u; }
-            return true;
-        };
-        for (uint32_t g0 = 0; g0 < total && alive; g0 += SETS) {
-#pragma unroll
-            for (int s = 0; s < SETS; ++s) {
-                const uint32_t g = g0 + s;
-                if (g >= total || !alive) break;
-                alive = deposit(av[s], bv[s]);
-                if (g + SETS - 1 < total) fetch_next(av[(s + SETS - 1) % SETS], bv[(s + SETS - 1) % SETS]);
-            }
         }
     } else if (warp < Wide::DRAIN_FIRST_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
         if (warp == 8) {
         // ---- the MMA warp ---------------------------------------------------------------------------
         // Instruction descriptors: f32 accumulator, tf32 A and B, their majors, N >> 3, M >> 4.
@@ -843,7 +777,7 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
             alive = mbar_wait(smem_u32(&acc_empty[acc]), ((turn >> 1) & 1u) ^ 1u, abort_flag, args.status);
             if (lane == 0 && turn < 8) WTRACE(33 + 3 * turn);
             for (uint32_t kb = 0; kb < kblocks && alive; ++kb) {
-                alive = mbar_wait(smem_u32(&bars[stage]), parity, abort_flag, args.status);
+                alive = mbar_wait(smem_u32(&split_full[stage]), parity, abort_flag, args.status);
                 if (!alive) break;
                 if (lane == 0 && turn < 8 && kb + 1 == kblocks) WTRACE(34 + 3 * turn);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -858,8 +792,45 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
                         mma_tf32(to, desc(a_high, a16 + a_at), desc(b_high, b16 + b_at), idesc_hi, (kb | ks) != 0u);
                         mma_tf32(to, desc(a_high, a16 + (Wide::A_BYTES >> 5) + a_at), desc(b_high, b16 + b_at), idesc_lo, 1u);
                     }
-                    mma_commit(smem_u32(&bars[STAGES + stage]));               // frees the stage when they finish
+                    mma_commit(smem_u32(&split_empty[stage]));                     // frees the stage when they finish
                     if (kb + 1 == kblocks) mma_commit(smem_u32(&acc_full[acc]));  // and, at the end, hands the tile to the drain
+                }
+                if (++stage == STAGES) { stage = 0; parity ^= 1u; }
+                __syncwarp();
+            }
+        }
+        } else if (warp == 9) {
+        // ---- the TMA warp: the raw k blocks of every tile of this CTA, in order ---------------------
+        bool alive = true;
+        uint32_t stage = 0, parity = 1;  // the parity a free slot shows
+        for (uint32_t u = blockIdx.x; u < units && alive; u += gridDim.x) {
+            const WideUnit w = wide_unit(args, u, down, across, kblocks_total);
+            for (uint32_t kb = 0; kb < w.kblocks && alive; ++kb) {
+                alive = mbar_wait(smem_u32(&raw_empty[stage]), parity, abort_flag, args.status);
+                if (!alive) break;
+                if (lane == 0) {
+                    const uint32_t bar = smem_u32(&raw_full[stage]);
+                    const uint32_t to_a = smem_u32(raw_blocks + stage * Wide::RAW_BYTES), to_b = to_a + Wide::RAW_OPERAND_BYTES;
+                    const uint32_t k0 = (kb * args.splits + w.split) * BK;
+                    tc::mbar_expect_tx(bar, Wide::RAW_BYTES);
+                    uint32_t upper[3] = {0u, 0u, 0u};
+                    if (A_T) {  // stored [k, m]: four boxes of 32 m by 32 k
+                        upper[args.a_order.row] = k0;
+#pragma unroll
+                        for (uint32_t p = 0; p < 4; ++p) tc::tma_load(to_a + p * 4096u, &maps.a[w.product], bar, w.m0 + 32u * p, upper);
+                    } else {    // stored [m, k]: one box of 32 k by 128 m
+                        upper[args.a_order.row] = w.m0;
+                        tc::tma_load(to_a, &maps.a[w.product], bar, k0, upper);
+                    }
+                    upper[0] = upper[1] = upper[2] = 0u;
+                    if (B_T) {  // stored [n, k]
+                        upper[args.b_order.row] = w.n0;
+                        tc::tma_load(to_b, &maps.b[w.product], bar, k0, upper);
+                    } else {    // stored [k, n]
+                        upper[args.b_order.row] = k0;
+#pragma unroll
+                        for (uint32_t p = 0; p < 4; ++p) tc::tma_load(to_b + p * 4096u, &maps.b[w.product], bar, w.n0 + 32u * p, upper);
+                    }
                 }
                 if (++stage == STAGES) { stage = 0; parity ^= 1u; }
                 __syncwarp();
@@ -867,7 +838,6 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
         }
         }
     } else {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;" ::: "memory");
         // ---- the drain warps: tensor memory -> a shared-memory slab -> C ---------------------------
         // A warp reads its lane quarter (the tensor-memory lanes a warp may read are 32 (warp % 4)
         // ..) 32 columns at a time: the sums of the two accumulator halves (and the bias) go row
@@ -883,7 +853,7 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
             if (w.kblocks == 0) continue;
             const uint32_t acc = turn & 1u;
             // The tile's 128 bias values, four per lane, fetched before the wait for the tile: a
-            // load issued inside the drain would queue behind the loaders' traffic.
+            // load issued inside the drain would queue behind everything else the SM has in flight.
             const float* __restrict__ bias_row = args.bias[w.product];
             float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
             if (bias_row) {
@@ -910,14 +880,11 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
 #pragma unroll 1
             for (uint32_t col = 0; col < 128; col += 32, ++filled) {
                 char* const slab = my_slabs + (filled & 1u) * Wide::SLAB_BYTES;
-                const bool traced = warp == Wide::DRAIN_FIRST_WARP && lane == 0 && turn == 3;
-                if (traced) WTRACE(128 + (col >> 5) * 5);
                 // The store that last read this slab (two chunks ago) has finished reading it.
                 if (args.c_tma) {
                     if (lane == 0) tc::tma_store_wait_read<1>();
                     __syncwarp();
                 }
-                if (traced) WTRACE(129 + (col >> 5) * 5);
                 uint32_t r1[32], r2[32];
                 const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * Wide::ACC_COLUMNS + col;
                 tmem_load32(taddr, r1);
@@ -930,7 +897,6 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
                     if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
                     if (warp == Wide::DRAIN_FIRST_WARP && lane == 0 && turn < 8) WTRACE(4 * turn + 2);
                 }
-                if (traced) WTRACE(130 + (col >> 5) * 5);
                 const uint32_t gn0 = w.n0 + col;
                 if (gn0 >= pn) continue;  // the same for the whole warp
 #pragma unroll
@@ -951,12 +917,10 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
                     }
                     *reinterpret_cast<float4*>(slab + tc::swizzled_chunk(lane, j >> 2)) = v;
                 }
-                if (traced) WTRACE(131 + (col >> 5) * 5);
                 if (args.c_tma) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0 && first_row < pm) tc::tma_store(&maps.c[w.product], smem_u32(slab), gn0, upper);
-                    if (traced) WTRACE(132 + (col >> 5) * 5);
                     continue;
                 }
                 __syncwarp();
@@ -1075,7 +1039,7 @@ bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0;
 // reduce launch. Narrow tiles win when the problem is small (more SMs share the latency-bound
 // work) or k is long (their loads run further ahead), wide ones when the product is large (less
 // operand re-reading).
-MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems, uint64_t group) {
+MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems, uint64_t group, bool wide_ok) {
     // Candidates: 64-row tiles of width 32, 64, 128 (two CTAs per SM) and the 128 x 128 tile.
     static const uint32_t rows[4] = {64, 64, 64, 128}, widths[4] = {32, 64, 128, 128};
     static const double per_block[4] = {MSX_TC_KB32, MSX_TC_KB64, MSX_TC_KB128, MSX_TC_KB_WIDE};
@@ -1090,7 +1054,7 @@ MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problem
         if (const char* forced = std::getenv("MSX_TC_FORCE_BM"))
             if (static_cast<uint32_t>(std::atoi(forced)) != rows[w]) continue;
 #endif
-        if (rows[w] == 128 && (problems > 1 || kblocks == 0)) continue;  // batched and empty products stay on the narrow tiles
+        if (rows[w] == 128 && (problems > 1 || kblocks == 0 || !wide_ok)) continue;  // batched and empty products stay on the narrow tiles, and operands TMA cannot address
         const uint64_t m_tiles = (m + rows[w] - 1) / rows[w], n_tiles = (n + widths[w] - 1) / widths[w];
         const uint64_t tiles = m_tiles * n_tiles * problems * group;
         const uint64_t most = problems > 1 ? 1 : (kblocks / 2 > 0 ? kblocks / 2 : 1);
@@ -1135,7 +1099,10 @@ void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t co
                      uint64_t k, uint32_t* status, bool leave_partials, MatmulPitches pitches) {
     if (m == 0 || n == 0 || count == 0) return;
     if (count > MAX_GROUP) throw std::invalid_argument("matmul_tc_group: more products than one launch carries");
-    MatmulTcPlan p = matmul_tc_plan(m, n, k, 1, count);
+    // The 128 x 128 tile loads its operands by TMA: bases on 16 bytes, rows a multiple of 16 bytes apart.
+    bool wide_ok = (pitches.a ? pitches.a : (a_t ? m : k)) % 4 == 0 && (pitches.b ? pitches.b : (b_t ? k : n)) % 4 == 0;
+    for (uint32_t g = 0; g < count; ++g) wide_ok = wide_ok && aligned16(products[g].a) && aligned16(products[g].b);
+    MatmulTcPlan p = matmul_tc_plan(m, n, k, 1, count, wide_ok);
     TcArgs args = {};
     args.m = static_cast<uint32_t>(m);
     args.n = static_cast<uint32_t>(n);
@@ -1168,6 +1135,13 @@ void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t co
     if (p.bm == 128) {
         // C through TMA stores when its rows can be addressed that way: the result as it is
         // stored, the split-k workspace as `splits` dense [m, n] matrices.
+        for (uint32_t g = 0; g < count; ++g) {
+            const HalfMatrix a_stored = {args.a[g], args.lda, 0, 0, false}, b_stored = {args.b[g], args.ldb, 0, 0, false};
+            // Rows of 32 floats: 128 of them for an operand stored with k along its rows, 32 for
+            // one stored with k down its columns (its tile is four such boxes side by side).
+            maps.a[g] = a_t ? tc::encode(a_stored, m, k, 1, 1, 32, &args.a_order, "A", true) : tc::encode(a_stored, k, m, 1, 1, 128, &args.a_order, "A", true);
+            maps.b[g] = b_t ? tc::encode(b_stored, k, n, 1, 1, 128, &args.b_order, "B", true) : tc::encode(b_stored, n, k, 1, 1, 32, &args.b_order, "B", true);
+        }
         const bool partial = p.splits > 1;
         bool addressable = true;
         for (uint32_t g = 0; g < count; ++g) {

@@ -268,7 +268,9 @@ struct MatmulTcPlan {
 // `problems` > 1: that many independent batched products in one launch (k is then not split);
 // `group` > 1: that many products of this shape in one launch of matmul_tc_group (the workspace
 // size is per product).
-MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems = 1, uint64_t group = 1);
+// `wide_ok`: the operands can be TMA sources (bases on 16 bytes, row pitches multiples of 4
+// floats), which the 128 x 128 tile needs.
+MatmulTcPlan matmul_tc_plan(uint64_t m, uint64_t n, uint64_t k, uint64_t problems = 1, uint64_t group = 1, bool wide_ok = true);
 void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_t, float* c, uint64_t m,
                uint64_t n, uint64_t k, float* workspace, uint32_t* status, const float* bias = nullptr,
                bool leave_partials = false);

@@ -1816,7 +1816,12 @@ struct Scheduler {
             return;
         }
         const uint32_t count = static_cast<uint32_t>(group.size());
-        const k::MatmulTcPlan tc = k::matmul_tc_plan(m, n, kk, 1, count);
+        // (The same rule as the launch applies: the 128 x 128 tile wants TMA sources; every base
+        // in a plan is on 256 bytes, so the row pitches decide.)
+        const bool a_stored_t = P->transposed(first.a) != first.flip_a, b_stored_t = P->transposed(first.b) != first.flip_b;
+        const uint64_t a_pitch = pitch_of(first.a) ? pitch_of(first.a) : (a_stored_t ? m : kk);
+        const uint64_t b_pitch = pitch_of(first.b) ? pitch_of(first.b) : (b_stored_t ? kk : n);
+        const k::MatmulTcPlan tc = k::matmul_tc_plan(m, n, kk, 1, count, a_pitch % 4 == 0 && b_pitch % 4 == 0);
         // A split k whose sum only the optimizer reads (a weight gradient) stays as partial
         // tiles: the finalize launch adds them with every other deferred sum.
         const bool defer = tc.workspace_floats != 0 && first.bias < 0 && deferrable(first.result);
@@ -3543,7 +3548,9 @@ int msx_op_matmul(const float* a, int a_transposed, const float* b, int b_transp
             k::matmul(s, a, a_transposed != 0, b, b_transposed != 0, c, m, n, k);
             return MSX_OK;
         }
-        uint64_t need = k::matmul_tc_plan(m, n, k).workspace_floats;
+        const bool wide_ok = (a_transposed ? m : k) % 4 == 0 && (b_transposed ? k : n) % 4 == 0 &&
+                             reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0;
+        uint64_t need = k::matmul_tc_plan(m, n, k, 1, 1, wide_ok).workspace_floats;
         if (need > workspace_floats || (need && !workspace) || !status)
             throw StatusError(MSX_BAD_ARGUMENT, "msx_op_matmul: the tensor-core kernel needs " + std::to_string(need) +
                                                     " workspace floats and a status word");
@@ -3552,7 +3559,10 @@ int msx_op_matmul(const float* a, int a_transposed, const float* b, int b_transp
     });
 }
 
-uint64_t msx_op_matmul_workspace(uint64_t m, uint64_t n, uint64_t k) { return k::matmul_tc_plan(m, n, k).workspace_floats; }
+uint64_t msx_op_matmul_workspace(uint64_t m, uint64_t n, uint64_t k) {
+    // Enough for either choice of tile (which one runs depends on how the operands are stored).
+    return std::max(k::matmul_tc_plan(m, n, k, 1, 1, true).workspace_floats, k::matmul_tc_plan(m, n, k, 1, 1, false).workspace_floats);
+}
 
 int msx_op_matmul_bf16(const void* a, int a_transposed, const void* b, int b_transposed, void* c, int c_is_bf16, uint64_t m, uint64_t n,
                        uint64_t k, float* workspace, uint64_t workspace_floats, uint32_t* status, void* stream) {
