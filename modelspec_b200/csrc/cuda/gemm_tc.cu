@@ -65,8 +65,8 @@ constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives
 #define MSX_TC_KB32 400.0
 #define MSX_TC_KB64 560.0
 #define MSX_TC_KB128 1100.0
-// The 128 x 128 tile (a persistent CTA per SM): per launch, per k block (four MMAs of
-// 128 x 256 x 8 and four of 128 x 128 x 8) and per tile.
+// The 128 x 128 tile (a persistent CTA per SM): per launch, per k block (twelve MMAs of
+// 128 x 128 x 8) and per tile.
 #define MSX_TC_FIXED_WIDE 8000.0
 #define MSX_TC_KB_WIDE 1550.0
 #define MSX_TC_TILE_WIDE 500.0
@@ -599,10 +599,9 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
 #endif
 
 // ---- the 128 x 128 tile as a persistent kernel ---------------------------------------------------
-// For products large enough to be bound by operand traffic. The hi and lo halves of A are two
-// 128-row operands; per 8-deep k slice one MMA of A_hi with the stacked B (N = 256: the hi and lo
-// columns) and one of A_lo with B_hi alone (N = 128) add hi*hi + lo*hi and hi*lo into the two
-// column halves of one accumulator (lo*lo, below 2^-20 of a product, is left out). One CTA per SM
+// For every product whose operands TMA can address. The hi and lo halves of A are two 128-row
+// operands, those of B two 128-column ones; per 8-deep k slice three MMAs of 128 x 128 x 8 add
+// hi*hi, hi*lo and lo*hi into one accumulator (lo*lo, below 2^-20 of a product, is left out). One CTA per SM
 // walks the launch's tiles (block b takes units b, b + grid, ...), so the set-up of a CTA is paid
 // once and the drain of a tile runs under the k loop of the next one. The raw f32 blocks come in
 // by TMA (zero-filled past the matrix edges, so no role checks bounds): loads issued by threads
@@ -610,7 +609,7 @@ __global__ void __launch_bounds__(THREADS, Config<BM, BN>::CTAS_PER_SM) matmul_t
 // and store against 1,070 for its MMAs).
 //   warps 0-7   split: read a raw k block (A 128 x 32, B 128 x 32) from its shared-memory slot,
 //               store the hi and lo halves in the layouts tcgen05 reads, free the slot;
-//   warp 8      issues the MMAs into one of two accumulators of 256 tensor-memory columns;
+//   warp 8      issues the MMAs into one of two accumulators of 128 tensor-memory columns;
 //   warp 9      issues the TMA loads of the k blocks of all the CTA's tiles as one sequence, two
 //               blocks ahead of the splitters;
 //   warps 12-15 drain the other accumulator: a lane quarter each, 32 columns at a time into a
@@ -628,7 +627,7 @@ struct Wide {
     static constexpr uint32_t SLAB_BYTES = 32 * 128;                     // 32 rows of 32 floats
     static constexpr uint32_t DRAIN_BYTES = DRAIN_WARPS * 2 * SLAB_BYTES;  // two slabs per drain warp
     static constexpr uint32_t TOTAL = STAGES * (STAGE_BYTES + RAW_BYTES) + DRAIN_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-    static constexpr uint32_t ACC_COLUMNS = 256, TMEM_COLUMNS = 512;
+    static constexpr uint32_t ACC_COLUMNS = 128, TMEM_COLUMNS = 256;
 };
 
 // Which tile, split and product unit `u` of a launch is: the tiles of one column of tiles are
@@ -755,9 +754,8 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
         if (warp == 8) {
         // ---- the MMA warp ---------------------------------------------------------------------------
         // Instruction descriptors: f32 accumulator, tf32 A and B, their majors, N >> 3, M >> 4.
-        const uint32_t idesc_lo = (1u << 4) | (2u << 7) | (2u << 10) | ((A_T ? 1u : 0u) << 15) | ((B_T ? 0u : 1u) << 16) |
-                                  (static_cast<uint32_t>(128 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
-        const uint32_t idesc_hi = (idesc_lo & ~(0x3Fu << 17)) | (static_cast<uint32_t>(256 >> 3) << 17);
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_T ? 1u : 0u) << 15) | ((B_T ? 0u : 1u) << 16) |
+                               (static_cast<uint32_t>(128 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
         constexpr uint32_t a_lbo = A_T ? BK * 128u : 16u, b_lbo = B_T ? 16u : BK * 128u;
         constexpr uint32_t a_sbo = A_T ? 512u : 1024u, b_sbo = B_T ? 1024u : 512u;
         constexpr uint32_t a_type = A_T ? 1u : 2u, b_type = B_T ? 2u : 1u;
@@ -789,8 +787,11 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
                     for (uint32_t ks = 0; ks < BK / 8; ++ks) {
                         const uint32_t a_at = (A_T ? ks * 1024u : ks * 32u) >> 4;
                         const uint32_t b_at = (B_T ? ks * 32u : ks * 1024u) >> 4;
-                        mma_tf32(to, desc(a_high, a16 + a_at), desc(b_high, b16 + b_at), idesc_hi, (kb | ks) != 0u);
-                        mma_tf32(to, desc(a_high, a16 + (Wide::A_BYTES >> 5) + a_at), desc(b_high, b16 + b_at), idesc_lo, 1u);
+                        const uint64_t a_hi = desc(a_high, a16 + a_at), a_lo = desc(a_high, a16 + (Wide::A_BYTES >> 5) + a_at);
+                        const uint64_t b_hi = desc(b_high, b16 + b_at), b_lo = desc(b_high, b16 + (Wide::B_BYTES >> 5) + b_at);
+                        mma_tf32(to, a_hi, b_hi, idesc, (kb | ks) != 0u);
+                        mma_tf32(to, a_hi, b_lo, idesc, 1u);
+                        mma_tf32(to, a_lo, b_hi, idesc, 1u);
                     }
                     mma_commit(smem_u32(&split_empty[stage]));                     // frees the stage when they finish
                     if (kb + 1 == kblocks) mma_commit(smem_u32(&acc_full[acc]));  // and, at the end, hands the tile to the drain
@@ -840,7 +841,7 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
     } else {
         // ---- the drain warps: tensor memory -> a shared-memory slab -> C ---------------------------
         // A warp reads its lane quarter (the tensor-memory lanes a warp may read are 32 (warp % 4)
-        // ..) 32 columns at a time: the sums of the two accumulator halves (and the bias) go row
+        // ..) 32 columns at a time: the sums (with the bias) go row
         // by row into a slab of 32 rows x 128 bytes in the 128-byte swizzle (the 16-byte chunks of
         // a row xor-ed with the row), which one TMA store then writes (what lies outside C is not
         // written), or, where C cannot be a TMA target, the warp itself as 128-byte row segments.
@@ -885,10 +886,8 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
                     if (lane == 0) tc::tma_store_wait_read<1>();
                     __syncwarp();
                 }
-                uint32_t r1[32], r2[32];
-                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * Wide::ACC_COLUMNS + col;
-                tmem_load32(taddr, r1);
-                tmem_load32(taddr + 128, r2);
+                uint32_t r[32];
+                tmem_load32(tmem_base + ((quarter * 32u) << 16) + acc * Wide::ACC_COLUMNS + col, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (col == 96) {
                     // The whole accumulator is in registers or stored: the MMA warp may write it again.
@@ -901,20 +900,22 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
                 if (gn0 >= pn) continue;  // the same for the whole warp
 #pragma unroll
                 for (uint32_t j = 0; j < 32; j += 4) {
-                    float4 v;
-                    // `x + 0` turns a -0 sum of zero products into the +0 a skipped term gives.
-                    v.x = (__uint_as_float(r1[j]) + __uint_as_float(r2[j])) + 0.0f;
-                    v.y = (__uint_as_float(r1[j + 1]) + __uint_as_float(r2[j + 1])) + 0.0f;
-                    v.z = (__uint_as_float(r1[j + 2]) + __uint_as_float(r2[j + 2])) + 0.0f;
-                    v.w = (__uint_as_float(r1[j + 3]) + __uint_as_float(r2[j + 3])) + 0.0f;
+                    // One addition an element: the bias (columns col + j .. + 3 are held by lane
+                    // (col + j) / 4, zeros past n), or the `x + 0` that turns a -0 sum of zero
+                    // products into the +0 a skipped term gives (as a bias of +0 does).
+                    float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (bias_row) {
-                        // Columns col + j .. + 3 are held by lane (col + j) / 4 (zeros past n).
                         const uint32_t holder = (col + j) >> 2;
-                        v.x = v.x + __shfl_sync(0xffffffffu, bias4.x, holder);
-                        v.y = v.y + __shfl_sync(0xffffffffu, bias4.y, holder);
-                        v.z = v.z + __shfl_sync(0xffffffffu, bias4.z, holder);
-                        v.w = v.w + __shfl_sync(0xffffffffu, bias4.w, holder);
+                        add.x = __shfl_sync(0xffffffffu, bias4.x, holder);
+                        add.y = __shfl_sync(0xffffffffu, bias4.y, holder);
+                        add.z = __shfl_sync(0xffffffffu, bias4.z, holder);
+                        add.w = __shfl_sync(0xffffffffu, bias4.w, holder);
                     }
+                    float4 v;
+                    v.x = __uint_as_float(r[j]) + add.x;
+                    v.y = __uint_as_float(r[j + 1]) + add.y;
+                    v.z = __uint_as_float(r[j + 2]) + add.z;
+                    v.w = __uint_as_float(r[j + 3]) + add.w;
                     *reinterpret_cast<float4*>(slab + tc::swizzled_chunk(lane, j >> 2)) = v;
                 }
                 if (args.c_tma) {
