@@ -122,8 +122,10 @@ struct TcArgs {
         const float* a;
         const float* b;
         float* c;  // C, or the job's split-K workspace
-        uint32_t m, n, k, lda, ldb, ldc, splits, first_block;
+        uint32_t m, n, k, lda, ldb, ldc, splits, first_block;  // first_block: the job's first block, or unit of the 128 x 128 tile
+        tc::CoordOrder c_order;                               // the 128 x 128 tile: as TcArgs::c_order, of this job's result
     } jobs[MAX_JOBS];
+    uint32_t units;  // the 128 x 128 tile: tiles x splits over all products or jobs of the launch
 };
 
 #ifdef MSX_TC_TRACE
@@ -630,20 +632,45 @@ struct Wide {
     static constexpr uint32_t ACC_COLUMNS = 128, TMEM_COLUMNS = 256;
 };
 
-// Which tile, split and product unit `u` of a launch is: the tiles of one column of tiles are
-// neighbours (they share their B block), then the splits of a tile, then the columns.
+// Which tile, split and product (or job) unit `u` of a launch is, with that product's sizes: the
+// tiles of one column of tiles are neighbours (they share their B block), then the splits of a
+// tile, then the columns; the jobs of a launch that carries several follow one another.
 struct WideUnit {
     uint32_t m0, n0, split, product, kblocks;
+    uint32_t m, n, ldc, splits;
+    float* c;
+    const float* bias;
+    tc::CoordOrder c_order;
 };
-__device__ __forceinline__ WideUnit wide_unit(const TcArgs& args, uint32_t u, uint32_t down, uint32_t across, uint32_t kblocks_total) {
+__device__ __forceinline__ WideUnit wide_unit(const TcArgs& args, uint32_t u) {
     WideUnit w;
+    uint32_t k;
+    if (args.job_count) {
+        uint32_t j = 0;
+        while (j + 1 < args.job_count && args.jobs[j + 1].first_block <= u) ++j;
+        const TcArgs::Job& job = args.jobs[j];
+        u -= job.first_block;
+        w.product = j;
+        w.m = job.m; w.n = job.n; k = job.k; w.ldc = job.ldc; w.splits = job.splits;
+        w.c = job.c;
+        w.bias = nullptr;
+        w.c_order = job.c_order;
+    } else {
+        w.m = args.m; w.n = args.n; k = args.k; w.ldc = args.ldc; w.splits = args.splits;
+        w.c_order = args.c_order;
+    }
+    const uint32_t down = (w.m + 127) / 128, across = (w.n + 127) / 128, kblocks_total = (k + BK - 1) / BK;
     w.m0 = (u % down) * 128u;
     u /= down;
-    w.split = u % args.splits;
-    u /= args.splits;
+    w.split = u % w.splits;
+    u /= w.splits;
     w.n0 = (u % across) * 128u;
-    w.product = u / across;
-    w.kblocks = kblocks_total > w.split ? (kblocks_total - w.split + args.splits - 1) / args.splits : 0u;
+    if (!args.job_count) {
+        w.product = u / across;
+        w.c = args.c[w.product];
+        w.bias = args.bias[w.product];
+    }
+    w.kblocks = kblocks_total > w.split ? (kblocks_total - w.split + w.splits - 1) / w.splits : 0u;
     return w;
 }
 
@@ -651,7 +678,7 @@ __device__ __forceinline__ WideUnit wide_unit(const TcArgs& args, uint32_t u, ui
 // for an operand stored with k along its rows, by 32 rows for one stored with k down its columns)
 // and the results (or their split-k workspaces).
 struct WideMaps {
-    CUtensorMap a[MAX_GROUP], b[MAX_GROUP], c[MAX_GROUP];
+    CUtensorMap a[MAX_JOBS], b[MAX_JOBS], c[MAX_JOBS];
 };
 
 template <bool A_T, bool B_T>
@@ -674,10 +701,7 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(acc_empty + 3);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t pm = args.m, pn = args.n, pk = args.k, pldc = args.ldc;
-    const uint32_t down = (pm + 127) / 128, across = (pn + 127) / 128;
-    const uint32_t kblocks_total = (pk + BK - 1) / BK;
-    const uint32_t units = down * across * args.splits * args.products;
+    const uint32_t units = args.units;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -706,7 +730,7 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
         // ---- the splitters: raw block -> (hi, lo) -> the swizzled tiles tcgen05 reads -------------
         // How many k blocks this CTA works through in all: the sequence the stages count along.
         uint32_t total = 0;
-        for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) total += wide_unit(args, u, down, across, kblocks_total).kblocks;
+        for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) total += wide_unit(args, u).kblocks;
         // A raw block lies as its TMA load left it, in the 128-byte swizzle: an operand stored
         // with k along its rows as 128 rows of 128 bytes, one stored with k down its columns as
         // four panels of 32 k rows of 128 bytes (32 of the 128 tile rows or columns each). Chunk i
@@ -767,7 +791,7 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
         bool alive = true;
         uint32_t stage = 0, parity = 0, turn = 0;
         for (uint32_t u = blockIdx.x; u < units && alive; u += gridDim.x, ++turn) {
-            const uint32_t kblocks = wide_unit(args, u, down, across, kblocks_total).kblocks;
+            const uint32_t kblocks = wide_unit(args, u).kblocks;
             if (kblocks == 0) continue;
             const uint32_t acc = turn & 1u;
             // The accumulator is free once the drain warps have read its previous tile.
@@ -805,14 +829,14 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
         bool alive = true;
         uint32_t stage = 0, parity = 1;  // the parity a free slot shows
         for (uint32_t u = blockIdx.x; u < units && alive; u += gridDim.x) {
-            const WideUnit w = wide_unit(args, u, down, across, kblocks_total);
+            const WideUnit w = wide_unit(args, u);
             for (uint32_t kb = 0; kb < w.kblocks && alive; ++kb) {
                 alive = mbar_wait(smem_u32(&raw_empty[stage]), parity, abort_flag, args.status);
                 if (!alive) break;
                 if (lane == 0) {
                     const uint32_t bar = smem_u32(&raw_full[stage]);
                     const uint32_t to_a = smem_u32(raw_blocks + stage * Wide::RAW_BYTES), to_b = to_a + Wide::RAW_OPERAND_BYTES;
-                    const uint32_t k0 = (kb * args.splits + w.split) * BK;
+                    const uint32_t k0 = (kb * w.splits + w.split) * BK;
                     tc::mbar_expect_tx(bar, Wide::RAW_BYTES);
                     uint32_t upper[3] = {0u, 0u, 0u};
                     if (A_T) {  // stored [k, m]: four boxes of 32 m by 32 k
@@ -850,12 +874,13 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
         bool alive = true;
         uint32_t turn = 0, filled = 0;
         for (uint32_t u = blockIdx.x; u < units && alive; u += gridDim.x, ++turn) {
-            const WideUnit w = wide_unit(args, u, down, across, kblocks_total);
+            const WideUnit w = wide_unit(args, u);
             if (w.kblocks == 0) continue;
             const uint32_t acc = turn & 1u;
             // The tile's 128 bias values, four per lane, fetched before the wait for the tile: a
             // load issued inside the drain would queue behind everything else the SM has in flight.
-            const float* __restrict__ bias_row = args.bias[w.product];
+            const float* __restrict__ bias_row = w.bias;
+            const uint32_t pm = w.m, pn = w.n, pldc = w.ldc;
             float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
             if (bias_row) {
                 const uint32_t at = w.n0 + 4 * lane;
@@ -873,11 +898,11 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
             if (!alive) break;
             if (warp == Wide::DRAIN_FIRST_WARP && lane == 0 && turn < 8) WTRACE(4 * turn + 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float* __restrict__ out = args.c[w.product] + static_cast<uint64_t>(w.split) * pm * pldc;
+            float* __restrict__ out = w.c + static_cast<uint64_t>(w.split) * pm * pldc;
             const uint32_t first_row = w.m0 + quarter * 32u;
             uint32_t upper[3] = {0u, 0u, 0u};
-            upper[args.c_order.row] = first_row;
-            upper[args.c_order.outer] = w.split;
+            upper[w.c_order.row] = first_row;
+            upper[w.c_order.outer] = w.split;
 #pragma unroll 1
             for (uint32_t col = 0; col < 128; col += 32, ++filled) {
                 char* const slab = my_slabs + (filled & 1u) * Wide::SLAB_BYTES;
@@ -1012,7 +1037,8 @@ template <bool A_T, bool B_T> void launch_wide(cudaStream_t s, const TcArgs& arg
 
 void launch_tile(cudaStream_t s, const TcArgs& args, dim3 grid, uint32_t bm, uint32_t bn, bool a_t, bool b_t, const WideMaps* maps = nullptr) {
     if (bm == 128) {
-        const uint32_t units = grid.x * grid.y * grid.z;
+        (void)grid;
+        const uint32_t units = args.units;
         if (a_t && b_t) launch_wide<true, true>(s, args, *maps, units);
         else if (a_t) launch_wide<true, false>(s, args, *maps, units);
         else if (b_t) launch_wide<false, true>(s, args, *maps, units);
@@ -1132,6 +1158,7 @@ void matmul_tc_group(cudaStream_t s, const MatmulOperands* products, uint32_t co
     }
     args.status = status;
     dim3 grid(static_cast<uint32_t>((n + p.bn - 1) / p.bn), static_cast<uint32_t>((m + p.bm - 1) / p.bm), p.splits * count);
+    args.units = grid.x * grid.y * grid.z;
     WideMaps maps = {};
     if (p.bm == 128) {
         // C through TMA stores when its rows can be addressed that way: the result as it is
@@ -1191,9 +1218,50 @@ MatmulTcPlan matmul_tc_job_plan(uint64_t m, uint64_t n, uint64_t k) {
     return p;
 }
 
+namespace {
+// The jobs of one launch on the persistent 128 x 128 tile, when TMA can address every operand and
+// every result (or split-k workspace); false when it cannot, and the 64 x 64 tiles take them.
+bool wide_jobs(cudaStream_t s, const MatmulJob* jobs, uint32_t count, bool a_t, bool b_t, uint32_t* status) {
+    TcArgs args = {};
+    WideMaps maps = {};
+    args.status = status;
+    args.c_tma = 1;
+    args.c_vec = 1;
+    for (uint32_t j = 0; j < count; ++j) {
+        const MatmulJob& job = jobs[j];
+        const MatmulTcPlan p = matmul_tc_job_plan(job.m, job.n, job.k);
+        const bool partial = p.splits > 1;
+        TcArgs::Job& to = args.jobs[args.job_count++];
+        to.a = job.a;
+        to.b = job.b;
+        to.c = partial ? job.workspace : job.c;
+        to.m = static_cast<uint32_t>(job.m);
+        to.n = static_cast<uint32_t>(job.n);
+        to.k = static_cast<uint32_t>(job.k);
+        to.lda = static_cast<uint32_t>(a_t ? job.m : job.k);
+        to.ldb = static_cast<uint32_t>(b_t ? job.k : job.n);
+        to.ldc = to.n;
+        to.splits = p.splits;
+        to.first_block = args.units;
+        args.units += static_cast<uint32_t>(((job.m + 127) / 128) * ((job.n + 127) / 128)) * p.splits;
+        const HalfMatrix a_stored = {to.a, to.lda, 0, 0, false}, b_stored = {to.b, to.ldb, 0, 0, false};
+        const HalfMatrix target = {to.c, to.ldc, partial ? job.m * job.n : 0, 0, false};
+        if (job.k == 0 || !tc::tma_addressable(a_stored, true) || !tc::tma_addressable(b_stored, true) || !tc::tma_addressable(target, true)) return false;
+        maps.a[j] = a_t ? tc::encode(a_stored, job.m, job.k, 1, 1, 32, &args.a_order, "A", true) : tc::encode(a_stored, job.k, job.m, 1, 1, 128, &args.a_order, "A", true);
+        maps.b[j] = b_t ? tc::encode(b_stored, job.k, job.n, 1, 1, 128, &args.b_order, "B", true) : tc::encode(b_stored, job.n, job.k, 1, 1, 32, &args.b_order, "B", true);
+        maps.c[j] = tc::encode(target, job.n, job.m, 1, partial ? p.splits : 1, 32, &to.c_order, "C", true);
+    }
+    launch_tile(s, args, dim3(args.units), 128, 128, a_t, b_t, &maps);
+    return true;
+}
+}  // namespace
+
 void matmul_tc_jobs(cudaStream_t s, const MatmulJob* jobs, uint32_t count, bool a_t, bool b_t, uint32_t* status) {
     if (count == 0) return;
     if (count > MAX_JOBS) throw std::invalid_argument("matmul_tc_jobs: more jobs than one launch carries");
+    for (uint32_t j = 0; j < count; ++j)
+        if (jobs[j].m == 0 || jobs[j].n == 0) throw std::invalid_argument("matmul_tc_jobs: an empty product");
+    if (wide_jobs(s, jobs, count, a_t, b_t, status)) return;
     TcArgs args = {};
     args.splits = 1;
     args.a_vec = args.b_vec = args.c_vec = 1;
