@@ -49,7 +49,7 @@ constexpr int BK = 32;
 constexpr int LOADER_THREADS = 256, THREADS = LOADER_THREADS + 32;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;  // try_wait polls before a wait gives up
 #ifndef MSX_TC_JOB_KBLOCKS
-#define MSX_TC_JOB_KBLOCKS 16  // k blocks a CTA of matmul_tc_jobs gets (8, 32 and 64 measured slower)
+#define MSX_TC_JOB_KBLOCKS 32  // k blocks a unit of matmul_tc_jobs gets (BERT-tiny's 13 weight gradients on the 128 x 128 tile: 33 us with 8, 43 with 16, 34 with 32, which leaves the fewest partial tiles)
 #endif
 
 // The cost model of matmul_tc_plan, in SM cycles (tuning builds may override).
@@ -1202,8 +1202,9 @@ void matmul_tc(cudaStream_t s, const float* a, bool a_t, const float* b, bool b_
     matmul_tc_group(s, &one, 1, a_t, b_t, m, n, k, status, leave_partials);
 }
 
-// One job of matmul_tc_jobs: 64 x 64 tiles, k split so that a CTA gets about 16 k blocks (the jobs
-// of a launch fill the device together, so a job does not have to on its own).
+// One job of matmul_tc_jobs: k split so that a unit (a 128 x 128 tile of one split, or a CTA of
+// the 64 x 64 tiles where TMA cannot address the job) gets about MSX_TC_JOB_KBLOCKS k blocks (the
+// jobs of a launch fill the device together, so a job does not have to on its own).
 MatmulTcPlan matmul_tc_job_plan(uint64_t m, uint64_t n, uint64_t k) {
     const uint64_t kblocks = (k + BK - 1) / BK;
     uint64_t splits = kblocks / MSX_TC_JOB_KBLOCKS;
