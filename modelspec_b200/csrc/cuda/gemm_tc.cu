@@ -7,11 +7,15 @@
 // in the 64-row tile) in f32 accumulators: two orders below the kernel tolerance 1e-5 + 1e-4 r.
 // The exact kernel (gemm.cu) stays for bit-level parity runs.
 //
-// One tcgen05.mma of this shape costs about the same 100-130 cycles whatever its width (its 128
-// rows of A are read 32 bytes at a time), so the four partial products are not four MMAs: the hi
-// and lo halves of A are stacked along M (64 rows each of one 128-row operand) and those of B
-// along N (BN columns each of one 2 BN-wide operand). One MMA per 8-deep k slice then yields all
-// four products, in four quadrants of tensor memory that the epilogue adds.
+// Two kernels. Products whose operands TMA can address (bases on 16 bytes, row pitches multiples
+// of 16 bytes: every product of a BERT-shaped step but the batched ones of its attention) run on
+// 128 x 128 tiles in a persistent kernel fed by TMA, described where it is defined further down.
+// The rest run on the 64-row tiles described here.
+//
+// On the 64-row tile the four partial products are not four MMAs: the hi and lo halves of A are
+// stacked along M (64 rows each of one 128-row operand) and those of B along N (BN columns each of
+// one 2 BN-wide operand). One MMA per 8-deep k slice then yields all four products, in four
+// quadrants of tensor memory that the epilogue adds.
 //
 // One CTA computes a 64 x BN tile (BN = 32, 64 or 128) over a range of 32-deep k blocks:
 //   warps 0-7  load the A and B blocks from global memory, split them and store hi and lo in the
@@ -21,11 +25,6 @@
 //              split-K workspace;
 //   warp 8     allocates tensor memory, issues 4 MMAs per k block from one thread, and releases
 //              each shared-memory stage with tcgen05.commit.
-// The split happens on the way from global to shared memory rather than after a TMA copy: a TMA
-// tile would be written, read back and written twice more, and shared-memory bandwidth (split
-// stores plus the operand reads of the MMAs) is what bounds a wide tile. Operands whose row
-// pitch is not a multiple of 16 bytes (a 30,522-wide logits matrix) could not be TMA sources in
-// any case.
 //
 // Shared memory stays under half an SM's (2 to 4 stages of 24 to 48 KB) and registers under
 // half its file, so two CTAs share an SM and one drains while the other loads. Stage hand-off is
