@@ -827,9 +827,10 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
         // ---- the TMA warp: the raw k blocks of every tile of this CTA, in order ---------------------
         bool alive = true;
         uint32_t stage = 0, parity = 1;  // the parity a free slot shows
+        uint32_t issued = 0;
         for (uint32_t u = blockIdx.x; u < units && alive; u += gridDim.x) {
             const WideUnit w = wide_unit(args, u);
-            for (uint32_t kb = 0; kb < w.kblocks && alive; ++kb) {
+            for (uint32_t kb = 0; kb < w.kblocks && alive; ++kb, ++issued) {
                 alive = mbar_wait(smem_u32(&raw_empty[stage]), parity, abort_flag, args.status);
                 if (!alive) break;
                 if (lane == 0) {
@@ -858,6 +859,15 @@ __global__ void __launch_bounds__(Wide::THREADS, 1) matmul_tc_wide_kernel(TcArgs
                 }
                 if (++stage == STAGES) { stage = 0; parity ^= 1u; }
                 __syncwarp();
+            }
+        }
+        // A role gave up: the loads still in flight land (a bounded wait each) before the CTA, and
+        // with it their shared-memory destination, goes away.
+        if (*abort_flag && lane == 0) {
+            for (uint32_t back = 0; back < static_cast<uint32_t>(STAGES) && back < issued; ++back) {
+                const uint32_t i = issued - 1 - back;
+                for (uint32_t spin = 0; spin < WAIT_LIMIT; ++spin)
+                    if (mbar_try_wait(smem_u32(&raw_full[i % STAGES]), (i / STAGES) & 1u)) break;
             }
         }
         }
