@@ -253,7 +253,17 @@ __global__ void __launch_bounds__(256) scatter_kernel(const TG* __restrict__ g, 
                     if (start + 2 * kHotChunk < count) fetch(start + 2 * kHotChunk, set);
                     if (threadIdx.x < span) {
                         const uint32_t here = min(kHotChunk, count - start);
-                        for (uint32_t r = 0; r < here; ++r) acc = acc + stage[r][threadIdx.x];
+                        if (here == kHotChunk) {
+                            // A whole chunk: every value is read before the first is added (the additions
+                            // are a chain; a read inside it would be a round trip each).
+                            float t[kHotChunk];
+#pragma unroll
+                            for (uint32_t r = 0; r < kHotChunk; ++r) t[r] = stage[r][threadIdx.x];
+#pragma unroll
+                            for (uint32_t r = 0; r < kHotChunk; ++r) acc = acc + t[r];
+                        } else {
+                            for (uint32_t r = 0; r < here; ++r) acc = acc + stage[r][threadIdx.x];
+                        }
                     }
                     __syncthreads();
                 }
@@ -262,6 +272,149 @@ __global__ void __launch_bounds__(256) scatter_kernel(const TG* __restrict__ g, 
                 const uint64_t where = static_cast<uint64_t>(row) * h + col0 + threadIdx.x;
                 store1(out + where, base ? base[where] + acc : acc);
             }
+        }
+    }
+}
+
+
+// The in-place form (a tied table: `out` already holds the dense gradient and only the rows some
+// id names change): one warp per sorted position instead of one per table row. The warp whose
+// position starts a run of equal ids owns that row: it counts the run (the lanes compare the next
+// 32 ids at a time) and adds `out[row] + (0 + g[n0] + g[n1] + ...)` exactly as the row walk above
+// does; the other positions have nothing to do. A step names a few thousand of a vocabulary's
+// 30,522 rows, so this visits n positions where the row walk visits every row twice (two
+// searches); a hot row's run is long, so two hot rows never start within one block's eight
+// positions and the block-wide path below takes at most one of them.
+template <int VEC, class TG, class TO>
+__global__ void __launch_bounds__(256) scatter_in_place_kernel(const TG* __restrict__ g, const int32_t* __restrict__ sorted_id,
+                                                               const int32_t* __restrict__ sorted_n, uint32_t n, TO* out, uint32_t rows,
+                                                               uint32_t h) {
+    constexpr uint32_t span = VEC * 32;
+    constexpr int LOADS = kHotChunk * span / VEC / 256;
+    __shared__ float stage[kHotChunk][span];
+    __shared__ uint32_t hot_row, hot_at, hot_count, hot_group;
+    const uint32_t groups = (h + span - 1) / span;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t group = 0; group < groups; ++group) {
+        if (threadIdx.x == 0) hot_count = 0;
+        __syncthreads();
+        const uint32_t p = blockIdx.x * 8 + warp, col = group * span + lane * VEC;
+        const bool in = col < h;
+        const int32_t id = p < n ? sorted_id[p] : -1;
+        const bool head = p < n && id >= 0 && static_cast<uint32_t>(id) < rows && (p == 0 || sorted_id[p - 1] != id);
+        if (head) {  // the same for the whole warp
+            // The run of this id: ids are sorted, so it ends at the first different one. The
+            // next 32 positions are looked at side by side (most runs end there); a longer run's
+            // end is searched for, 32 probes a round.
+            const uint32_t probe = p + 1 + lane;
+            const uint32_t same = __ballot_sync(0xffffffffu, probe < n && sorted_id[probe] == id);
+            const uint32_t count = same == 0xffffffffu ? warp_lower_bound(sorted_id, n, id + 1, lane) - p : __ffs(~same);
+            if (count > kHotRow) {
+                if (lane == 0) {
+                    hot_row = static_cast<uint32_t>(id);
+                    hot_at = p;
+                    hot_count = count;
+                    hot_group = group;
+                }
+            } else {
+                float acc[VEC];
+#pragma unroll
+                for (int q = 0; q < VEC; ++q) acc[q] = 0.0f;
+                for (uint32_t done = 0; done < count; done += 8) {
+                    const uint32_t here = min(8u, count - done);
+                    const int32_t entry = lane < here ? __ldg(sorted_n + p + done + lane) : 0;
+                    float v[8][VEC];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int32_t src = __shfl_sync(0xffffffffu, entry, e);
+                        const TG* from = g + static_cast<uint64_t>(src) * h + col;
+                        if (static_cast<uint32_t>(e) < here && in) {
+                            if (VEC == 4) {
+                                const float4 f = load4(from);
+                                v[e][0] = f.x; v[e][1 % VEC] = f.y; v[e][2 % VEC] = f.z; v[e][3 % VEC] = f.w;
+                            } else {
+                                v[e][0] = load1(from);
+                            }
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < VEC; ++q) v[e][q] = 0.0f;
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        if (static_cast<uint32_t>(e) < here) {
+#pragma unroll
+                            for (int q = 0; q < VEC; ++q) acc[q] = acc[q] + v[e][q];
+                        }
+                }
+                if (in) {
+                    TO* to = out + static_cast<uint64_t>(id) * h + col;
+                    if (VEC == 4) {
+                        const float4 b = *reinterpret_cast<const float4*>(to);
+                        store4(to, make_float4(b.x + acc[0], b.y + acc[1 % VEC], b.z + acc[2 % VEC], b.w + acc[3 % VEC]));
+                    } else {
+                        store1(to, static_cast<float>(*to) + acc[0]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        // The block's hot row, if one starts here, by the whole block: 32 occurrences at a time
+        // into shared memory, two chunks of loads in flight while a third is added in order.
+        const uint32_t count = hot_count;
+        if (count == 0) continue;
+        const uint32_t row = hot_row, at = hot_at, col0 = hot_group * span;
+        float4 held4[2][VEC == 4 ? LOADS : 1];
+        float held1[2][VEC == 1 ? LOADS : 1];
+        auto fetch = [&](uint32_t chunk_start, int set) {
+#pragma unroll
+            for (int j = 0; j < LOADS; ++j) {
+                const uint32_t f = threadIdx.x + 256 * j;
+                const uint32_t r = f / (span / VEC), c = (f % (span / VEC)) * VEC;
+                const bool wanted = chunk_start + r < count && col0 + c < h;
+                const int32_t src = wanted ? __ldg(sorted_n + at + chunk_start + r) : 0;
+                const TG* from = g + static_cast<uint64_t>(src) * h + col0 + c;
+                if (VEC == 4) held4[set][j % (VEC == 4 ? LOADS : 1)] = wanted ? load4(from) : make_float4(0.f, 0.f, 0.f, 0.f);
+                else held1[set][j % (VEC == 1 ? LOADS : 1)] = wanted ? load1(from) : 0.0f;
+            }
+        };
+        float acc = 0.0f;
+        fetch(0, 0);
+        if (kHotChunk < count) fetch(kHotChunk, 1);
+        for (uint32_t pair = 0; pair < count; pair += 2 * kHotChunk) {
+#pragma unroll
+            for (int set = 0; set < 2; ++set) {
+                const uint32_t start = pair + set * kHotChunk;
+                if (start >= count) break;
+#pragma unroll
+                for (int j = 0; j < LOADS; ++j) {
+                    const uint32_t f = threadIdx.x + 256 * j;
+                    const uint32_t r = f / (span / VEC), c = (f % (span / VEC)) * VEC;
+                    if (VEC == 4) *reinterpret_cast<float4*>(&stage[r][c]) = held4[set][j % (VEC == 4 ? LOADS : 1)];
+                    else stage[r][c] = held1[set][j % (VEC == 1 ? LOADS : 1)];
+                }
+                __syncthreads();
+                if (start + 2 * kHotChunk < count) fetch(start + 2 * kHotChunk, set);
+                if (threadIdx.x < span) {
+                    const uint32_t here = min(kHotChunk, count - start);
+                    if (here == kHotChunk) {
+                        // A whole chunk: every value is read before the first is added (the additions
+                        // are a chain; a read inside it would be a round trip each).
+                        float t[kHotChunk];
+#pragma unroll
+                        for (uint32_t r = 0; r < kHotChunk; ++r) t[r] = stage[r][threadIdx.x];
+#pragma unroll
+                        for (uint32_t r = 0; r < kHotChunk; ++r) acc = acc + t[r];
+                    } else {
+                        for (uint32_t r = 0; r < here; ++r) acc = acc + stage[r][threadIdx.x];
+                    }
+                }
+                __syncthreads();
+            }
+        }
+        if (threadIdx.x < span && col0 + threadIdx.x < h) {
+            const uint64_t where = static_cast<uint64_t>(row) * h + col0 + threadIdx.x;
+            store1(out + where, static_cast<float>(out[where]) + acc);
         }
     }
 }
@@ -301,6 +454,14 @@ void launch_scatter(cudaStream_t s, const TG* g, TO* out, uint64_t n, uint64_t r
     const int32_t* sorted_n = scratch + n;
     const bool vec = h % 4 == 0 && aligned4(g) && aligned4(out) && reinterpret_cast<uintptr_t>(base) % 16 == 0;
     const uint64_t span = vec ? 128 : 32;
+    if (n > 0 && static_cast<const void*>(base) == static_cast<const void*>(out)) {
+        // In place: only the rows some id names change, a warp per sorted position.
+        const uint32_t positions = static_cast<uint32_t>((n + 7) / 8);
+        if (vec) scatter_in_place_kernel<4><<<positions, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
+        else scatter_in_place_kernel<1><<<positions, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
+        check_launch("embedding_grad");
+        return;
+    }
     const uint64_t blocks = (rows * ((h + span - 1) / span) + 7) / 8;
     const uint32_t grid = static_cast<uint32_t>(blocks > 148 * 6 ? 148 * 6 : blocks);
     if (vec) scatter_kernel<4><<<grid, 256, 0, s>>>(g, sorted_id, sorted_n, static_cast<uint32_t>(n), base, out, static_cast<uint32_t>(rows), static_cast<uint32_t>(h));
