@@ -404,10 +404,10 @@ def main():
                     "hbm_view": {"achieved_gbs": top_bytes / (top_ms * 1e-3) / 1e9, "peak_gbs": pk["hbm_gbs"],
                                  "frac": top_bytes / (top_ms * 1e-3) / 1e9 / pk["hbm_gbs"]}}
         if not half:
-            # f32 products on the tf32 tensor cores take four partial products each (hi/lo split
-            # of both operands), and dense tf32 runs at half the bf16 rate: the ceiling of this
-            # kernel class is 1/8 of the measured bf16 peak.
-            roofline["frac_of_split_tf32_ceiling"] = achieved / (pk["bf16_tflops"] / 8)
+            # f32 products on the tf32 tensor cores take three partial products each (hi/lo split
+            # of both operands; lo x lo is left out), and dense tf32 runs at half the bf16 rate:
+            # the ceiling of this kernel class is 1/6 of the measured bf16 peak.
+            roofline["frac_of_split_tf32_ceiling"] = achieved / (pk["bf16_tflops"] / 6)
     else:
         achieved = top_bytes / (top_ms * 1e-3) / 1e9
         roofline = {"kernel": top_kernel, "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
