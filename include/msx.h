@@ -445,6 +445,43 @@ int msx_training_feed_packed(msx_training* training, uint64_t step);
 int msx_training_heldout_packed(msx_training* training, const char* dir);
 uint32_t msx_training_heldout_batches(const msx_training* training);
 
+/* ---- dense data (`train --data <directory>` without a binding file) ------------------------------
+ * The reference's dense directory (train/data.rs:14-35): `<dir>/<name>.f32` or `<dir>/<name>.i32`
+ * for every `input` and `target` declaration, row-major little-endian values without a header,
+ * and an optional `<dir>/order.u32`. msx_dense_open takes the declarations in source order (name,
+ * dtype, role, rank and shape: `shapes` holds the ranks[0] + ranks[1] + ... extents one after
+ * another) and the run's step count, and reads and checks the files as the reference does
+ * (read_files :837-876, read_tensor :1232-1290, dense :513-577): B is the leading dimension all
+ * declarations share, else 1; a file is a whole number of samples of finite values (E-DATA-007);
+ * all files hold the same number N of samples (E-DATA-007); an order holds at least steps x B
+ * indices, each below N (E-DATA-008). MSX_BAD_INPUT with the reference's reason otherwise
+ * (msx_dense_last_error(NULL)). msx_dense_check_bound refuses an i32 file that holds a value
+ * outside 0 .. bound - 1 (E-DATA-011, refuse_out_of_range :957-1004; `what` names the bound in
+ * the message: "the 6 rows of the `embedding` table `Named.table`"). msx_dense_step copies the
+ * batch of step `step` of declaration `index`: the samples order[(step B + i) mod len] with an
+ * order, (step B + i) mod N without one (fill_step :446-454). */
+typedef struct msx_dense msx_dense;
+int msx_dense_open(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
+                   const uint32_t* ranks, const uint64_t* shapes, uint64_t steps, msx_dense** out);
+void msx_dense_close(msx_dense* dense);
+const char* msx_dense_last_error(const msx_dense* dense);
+uint64_t msx_dense_batch(const msx_dense* dense);
+uint64_t msx_dense_samples(const msx_dense* dense);
+int msx_dense_has_order(const msx_dense* dense);
+uint32_t msx_dense_tensors(const msx_dense* dense);
+uint64_t msx_dense_batch_bytes(const msx_dense* dense, uint32_t index);
+int msx_dense_check_bound(msx_dense* dense, uint32_t index, uint64_t bound, const char* what);
+int msx_dense_step(const msx_dense* dense, uint32_t index, uint64_t step, void* out, uint64_t capacity_bytes);
+
+/* Binds a dense directory to the run's declarations (dense, read_dense :627-671): a declaration
+ * the loss does not read is E-DATA-003; then the files as msx_dense_open reads them; then every
+ * i32 file against the rows of the embedding table or the classes of the cross_entropy logits
+ * that read it (E-DATA-011). The training owns the data it read. msx_training_feed_dense makes
+ * the batch of step `step` the current batch (then msx_training_step); msx_training_run feeds a
+ * bound dense directory as it feeds a packed one. */
+int msx_training_bind_dense(msx_training* training, const char* dir);
+int msx_training_feed_dense(msx_training* training, uint64_t step);
+
 /* ---- a whole run and its standard output --------------------------------------------------------
  * `train --backend cuda` as one call: the steps `start` .. `start + steps` of the train block (the
  * run's `steps`; `start` > 0 after msx_training_resume), fed from the bound packed directory when

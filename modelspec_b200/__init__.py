@@ -109,6 +109,19 @@ SIGNATURES = {
     "msx_training_heldout_begin": (C.c_int, [_P, C.c_uint32, C.c_char_p, C.c_char_p]),
     "msx_training_heldout_set": (C.c_int, [_P, C.c_uint32, C.c_char_p, _P, C.c_uint64]),
     "msx_training_heldout_evaluate": (C.c_int, [_P, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
+    "msx_dense_open": (C.c_int, [C.c_char_p, C.c_uint32, C.POINTER(C.c_char_p), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
+                                 C.POINTER(C.c_uint32), C.POINTER(C.c_uint64), C.c_uint64, C.POINTER(_P)]),
+    "msx_dense_close": (None, [_P]),
+    "msx_dense_last_error": (C.c_char_p, [_P]),
+    "msx_dense_batch": (C.c_uint64, [_P]),
+    "msx_dense_samples": (C.c_uint64, [_P]),
+    "msx_dense_has_order": (C.c_int, [_P]),
+    "msx_dense_tensors": (C.c_uint32, [_P]),
+    "msx_dense_batch_bytes": (C.c_uint64, [_P, C.c_uint32]),
+    "msx_dense_check_bound": (C.c_int, [_P, C.c_uint32, C.c_uint64, C.c_char_p]),
+    "msx_dense_step": (C.c_int, [_P, C.c_uint32, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "msx_training_bind_dense": (C.c_int, [_P, C.c_char_p]),
+    "msx_training_feed_dense": (C.c_int, [_P, C.c_uint64]),
     "msx_packed_open": (C.c_int, [C.c_char_p, C.POINTER(_P)]),
     "msx_packed_close": (None, [_P]),
     "msx_packed_last_error": (C.c_char_p, [_P]),
@@ -464,6 +477,58 @@ class Checkpoint:
         return out
 
 
+class Dense:
+    """A dense data directory (msx_dense): `<name>.f32` / `<name>.i32` per declaration and an
+    optional `order.u32`. `declarations` = [(name, "f32" | "i32", "input" | "target", shape), ...] in
+    source order; `steps` = the run's step count (what an order must cover)."""
+
+    def __init__(self, directory, declarations, steps):
+        n = len(declarations)
+        names = (C.c_char_p * n)(*[d[0].encode() for d in declarations])
+        is_i32 = (C.c_uint32 * n)(*[1 if d[1] == "i32" else 0 for d in declarations])
+        is_target = (C.c_uint32 * n)(*[1 if d[2] == "target" else 0 for d in declarations])
+        ranks = (C.c_uint32 * n)(*[len(d[3]) for d in declarations])
+        flat = [int(x) for d in declarations for x in d[3]]
+        shapes = (C.c_uint64 * max(len(flat), 1))(*flat)
+        h = _P()
+        rc = lib().msx_dense_open(str(directory).encode(), n, names, is_i32, is_target, ranks, shapes, steps, C.byref(h))
+        if rc != OK:
+            raise MsxError(rc, lib().msx_dense_last_error(None).decode())
+        self.h = h
+        self.declarations = list(declarations)
+
+    def close(self):
+        if self.h:
+            lib().msx_dense_close(self.h)
+            self.h = None
+
+    @property
+    def batch(self):
+        return int(lib().msx_dense_batch(self.h))
+
+    @property
+    def samples(self):
+        return int(lib().msx_dense_samples(self.h))
+
+    @property
+    def has_order(self):
+        return bool(lib().msx_dense_has_order(self.h))
+
+    def check_bound(self, index, bound, what):
+        rc = lib().msx_dense_check_bound(self.h, index, bound, what.encode())
+        if rc != OK:
+            raise MsxError(rc, lib().msx_dense_last_error(self.h).decode())
+
+    def step(self, index, k):
+        """The batch of step `k` of declaration `index` as a flat array."""
+        nbytes = int(lib().msx_dense_batch_bytes(self.h, index))
+        out = np.empty(nbytes // 4, dtype=np.int32 if self.declarations[index][1] == "i32" else np.float32)
+        rc = lib().msx_dense_step(self.h, index, k, out.ctypes.data, nbytes)
+        if rc != OK:
+            raise MsxError(rc, "msx_dense_step")
+        return out
+
+
 class Packed:
     """A packed masked-language-model directory (msx_packed): the reference's `--data <packed>`."""
 
@@ -630,6 +695,14 @@ class Training:
         """Feeds the run from a packed directory; `packed` must stay open while the run lives."""
         self.check(lib().msx_training_bind_packed(self.h, packed.h))
         self._packed = packed
+
+    def bind_dense(self, directory):
+        """Feeds the run from a dense directory (`<name>.f32` / `<name>.i32`, optional `order.u32`)."""
+        self.check(lib().msx_training_bind_dense(self.h, str(directory).encode()))
+
+    def feed_dense(self, step):
+        """Makes the dense batch of `step` the current batch."""
+        self.check(lib().msx_training_feed_dense(self.h, step))
 
     def feed_packed(self, step):
         """Makes the Train batch of `step` the current batch."""

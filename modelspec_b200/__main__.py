@@ -2,14 +2,17 @@
 --backend cuda` on this backend, printing the reference's standard output for the run
 (crates/modelspec-cli/src/train.rs:7-17; crates/modelspec-cli/src/infer.rs:1-60).
 
-    python -m modelspec_b200 train FILE [--data PACKED_DIR] [--eval-every N] [--masked-rows N]
+    python -m modelspec_b200 train FILE [--data DIR] [--eval-every N] [--masked-rows N]
         [--resume IN.msckpt] [--checkpoint OUT.msckpt] [--stats] [--profile] [--bf16] [--device I]
     python -m modelspec_b200 infer FILE [--resume IN.msckpt] [--bf16] [--device I]
 
+`--data DIR` is a packed masked-language-model directory when it holds `binding.json`, else a dense
+one (`<name>.f32` / `<name>.i32` per declaration, optional `order.u32`; train/data.rs:1443-1483).
 Without `--data` the run trains on the reference's synthetic batch (one f32 input, one f32 target).
 Diagnostics go to standard error and the exit status is 1, as the reference's CLI answers.
 """
 import argparse
+import os
 import sys
 
 import modelspec_b200 as M
@@ -19,7 +22,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m modelspec_b200")
     ap.add_argument("command", choices=["train", "infer"])
     ap.add_argument("file")
-    ap.add_argument("--data", help="a packed masked-language-model directory")
+    ap.add_argument("--data", help="a packed masked-language-model directory (it holds binding.json) or a dense one")
     ap.add_argument("--eval-every", type=int, default=0, help="evaluate the HeldOut split of --data every N steps and at the last step")
     ap.add_argument("--masked-rows", type=int, default=0, help="capacity of the masked-row gather (0: none)")
     ap.add_argument("--resume", help="a .msckpt checkpoint to start from")
@@ -34,12 +37,15 @@ def main(argv=None):
         source = open(args.file).read()
         device = M.Device(args.device)
         run = M.Training(device, source, args.masked_rows, M.PLAN_BF16 if args.bf16 else M.PLAN_DEFAULT)
-        if args.data:
+        if args.data and os.path.exists(os.path.join(args.data, "binding.json")):
             packed = M.Packed(args.data)
             run.bind_packed(packed)
             if args.eval_every > 0:
                 run.heldout_packed()
             run.feed_packed(0)
+        elif args.data:
+            run.bind_dense(args.data)
+            run.feed_dense(0)
         else:
             run.synthetic()
         start = 0

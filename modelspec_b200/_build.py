@@ -9,7 +9,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libmsx.so")
 
 SOURCES = ["cuda/pointwise.cu", "cuda/reduce.cu", "cuda/rowwise.cu", "cuda/embedding.cu", "cuda/gemm.cu", "cuda/gemm_tc.cu", "cuda/gemm_bf16.cu",
-           "cuda/attention.cu", "cuda/attention_tc.cu", "cuda/attention_fused.cu", "cuda/optimizer.cu", "cuda/heldout.cu", "cuda/runtime.cu", "cuda/noalloc.cu", "cuda/peer_reduce.cu", "host/training.cpp", "host/packed.cpp", "host/checkpoint.cpp"]
+           "cuda/attention.cu", "cuda/attention_tc.cu", "cuda/attention_fused.cu", "cuda/optimizer.cu", "cuda/heldout.cu", "cuda/runtime.cu", "cuda/noalloc.cu", "cuda/peer_reduce.cu", "host/training.cpp", "host/packed.cpp", "host/dense.cpp", "host/checkpoint.cpp"]
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-fmad=false", "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function"]

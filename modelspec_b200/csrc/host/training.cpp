@@ -46,6 +46,7 @@ struct msx_training {
     std::vector<Replayed> since_snapshot;
     std::string report;  // the standard output of the last msx_training_run
     std::string schema;  // the schema hash of the training program's parameters, made on first use
+    msx_dense* dense = nullptr;  // a dense --data directory, owned (train/data.rs:513-577)
     msx_packed* packed = nullptr;
     uint64_t packed_batch = 0;
     std::vector<std::string> packed_bound;  // the declared batch tensors, in source order
@@ -182,6 +183,7 @@ int msx_training_create(msx_device* device, const char* source, uint64_t masked_
 
 void msx_training_destroy(msx_training* t) {
     if (!t) return;
+    if (t->dense) msx_dense_close(t->dense);
     if (t->heldout) msx_heldout_destroy(t->heldout);
     if (t->predict) msx_plan_destroy(t->predict);
     if (t->infer) msx_plan_destroy(t->infer);
@@ -688,6 +690,83 @@ int msx_training_heldout_packed(msx_training* t, const char* dir_for_messages) {
 
 uint32_t msx_training_heldout_batches(const msx_training* t) { return t ? static_cast<uint32_t>(t->heldout_batches.size()) : 0; }
 
+// ---- dense data (crates/modelspec-runtime/src/train/data.rs:513-577, :627-671) ---------------------
+
+int msx_training_bind_dense(msx_training* t, const char* dir) {
+    if (!t || !dir) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        const auto& decls = c.config.data;  // in source order
+        // refuse_unread (data.rs:307-338): every declaration has an Input node of the forward program.
+        const msx::Program& fwd = c.forward_with_dropout;
+        auto input_of = [&](const std::string& name) -> int64_t {
+            for (uint32_t in : fwd.inputs)
+                if (fwd.node(in).name == name) return in;
+            return -1;
+        };
+        for (const msx::DataDecl& d : decls)
+            if (input_of(d.name) < 0)
+                throw Fail{MSX_BAD_INPUT, std::string("E-DATA-003: the ") + (d.target ? "target" : "input") + " `" + d.name + "` is not read by the loss"};
+        std::vector<const char*> names;
+        std::vector<uint32_t> is_i32, is_target, ranks;
+        std::vector<uint64_t> shapes;
+        for (const msx::DataDecl& d : decls) {
+            names.push_back(d.name.c_str());
+            is_i32.push_back(d.ty.i32 ? 1u : 0u);
+            is_target.push_back(d.target ? 1u : 0u);
+            ranks.push_back(static_cast<uint32_t>(d.ty.shape.size()));
+            for (uint64_t n : d.ty.shape) shapes.push_back(n);
+        }
+        msx_dense* dense = nullptr;
+        if (msx_dense_open(dir, static_cast<uint32_t>(decls.size()), names.data(), is_i32.data(), is_target.data(), ranks.data(), shapes.data(),
+                           c.config.steps, &dense) != MSX_OK)
+            throw Fail{MSX_BAD_INPUT, msx_dense_last_error(nullptr)};
+        // index_bounds (data.rs:899-939): the ids of an embedding lie below the rows of its table,
+        // the labels of a cross_entropy below the classes of its logits; the tightest bound of a
+        // declaration is the one its file is held to.
+        for (uint32_t i = 0; i < decls.size(); ++i) {
+            if (!decls[i].ty.i32) continue;
+            const int64_t input = input_of(decls[i].name);
+            uint64_t tightest = 0;
+            std::string what;
+            for (const msx::Node& n : fwd.nodes) {
+                const bool table = n.op == msx::Op::Embedding, logits = n.op == msx::Op::CrossEntropy;
+                if ((!table && !logits) || n.operands.size() < 2 || n.operands[1] != static_cast<uint32_t>(input)) continue;
+                const msx::Node& value = fwd.node(n.operands[0]);
+                const size_t axis = table ? 0 : 1;
+                if (value.ty.shape.size() <= axis) continue;
+                const uint64_t bound = value.ty.shape[axis];
+                if (!what.empty() && bound >= tightest) continue;
+                std::string named = "%" + std::to_string(value.id);
+                if (value.op == msx::Op::ParamRead) named = fwd.params[value.param].path;
+                tightest = bound;
+                what = "the " + std::to_string(bound) + (table ? " rows of the `embedding` table `" : " classes of the `cross_entropy` logits `") + named + "`";
+            }
+            if (what.empty()) continue;
+            if (msx_dense_check_bound(dense, i, tightest, what.c_str()) != MSX_OK) {
+                const std::string why = msx_dense_last_error(dense);
+                msx_dense_close(dense);
+                throw Fail{MSX_BAD_INPUT, why};
+            }
+        }
+        if (t->dense) msx_dense_close(t->dense);
+        t->dense = dense;
+    });
+}
+
+int msx_training_feed_dense(msx_training* t, uint64_t step) {
+    if (!t) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        if (!t->dense) throw Fail{MSX_BAD_ARGUMENT, "no dense directory is bound"};
+        const auto& decls = t->compiled.config.data;
+        for (uint32_t i = 0; i < decls.size(); ++i) {
+            std::vector<char>& bytes = t->batch[decls[i].name];
+            bytes.resize(msx_dense_batch_bytes(t->dense, i));
+            if (msx_dense_step(t->dense, i, step, bytes.data(), bytes.size()) != MSX_OK) throw Fail{MSX_BAD_ARGUMENT, "the dense batch does not fit its declaration"};
+        }
+    });
+}
+
 // ---- checkpoints (crates/modelspec-runtime/src/train/checkpoint.rs:420-451, :519-609) --------------
 
 namespace {
@@ -905,6 +984,7 @@ int msx_training_run(msx_training* t, uint64_t start, uint64_t eval_every) {
                 evals[k] = {loss, accuracy};
             }
             if (t->packed && msx_training_feed_packed(t, k) != MSX_OK) throw Fail{MSX_BAD_INPUT, t->error};
+            if (t->dense && msx_training_feed_dense(t, k) != MSX_OK) throw Fail{MSX_BAD_INPUT, t->error};
             if (msx_training_step(t, k, end) != MSX_OK) throw Fail{MSX_LAUNCH_FAILED, t->error};
             while (next_read + kBehind <= k) read_loss(next_read++);
         }
@@ -912,6 +992,7 @@ int msx_training_run(msx_training* t, uint64_t start, uint64_t eval_every) {
         // The loss after the last update: the forward program without dropout on the batch of step
         // `end` (a packed run: the batch that step would train on; runner.rs:466-485).
         if (t->packed && msx_training_feed_packed(t, end) != MSX_OK) throw Fail{MSX_BAD_INPUT, t->error};
+        if (t->dense && msx_training_feed_dense(t, end) != MSX_OK) throw Fail{MSX_BAD_INPUT, t->error};
         if (evaluated(end)) {
             float loss = 0.0f, accuracy = 0.0f;
             if (msx_training_heldout_evaluate(t, &loss, &accuracy) != MSX_OK) throw Fail{MSX_LAUNCH_FAILED, t->error};
