@@ -472,6 +472,12 @@ uint32_t msx_dense_tensors(const msx_dense* dense);
 uint64_t msx_dense_batch_bytes(const msx_dense* dense, uint32_t index);
 int msx_dense_check_bound(msx_dense* dense, uint32_t index, uint64_t bound, const char* what);
 int msx_dense_step(const msx_dense* dense, uint32_t index, uint64_t step, void* out, uint64_t capacity_bytes);
+/* The directory of `--eval <dir>` (dense_eval, train/data.rs:582-600): the same files, `order.u32`
+ * is not read, and N is a multiple of B (E-DATA-009). msx_dense_eval_batch copies batch `batch`:
+ * the samples batch x B .. (batch + 1) x B (fill_eval_batch :456-460). */
+int msx_dense_open_eval(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
+                        const uint32_t* ranks, const uint64_t* shapes, msx_dense** out);
+int msx_dense_eval_batch(const msx_dense* dense, uint32_t index, uint64_t batch, void* out, uint64_t capacity_bytes);
 
 /* Binds a dense directory to the run's declarations (dense, read_dense :627-671): a declaration
  * the loss does not read is E-DATA-003; then the files as msx_dense_open reads them; then every
@@ -481,6 +487,16 @@ int msx_dense_step(const msx_dense* dense, uint32_t index, uint64_t step, void* 
  * bound dense directory as it feeds a packed one. */
 int msx_training_bind_dense(msx_training* training, const char* dir);
 int msx_training_feed_dense(msx_training* training, uint64_t step);
+/* `--eval <dir>` (evaluate_dense, train/runner.rs:571-624): the forward program, dropout the
+ * identity, on the current parameters over every batch of an eval directory. `loss` = the mean of
+ * the batch losses, summed in f64; `accuracy` = the fraction of target rows whose prediction row
+ * has its first maximum where the target row has its (a prediction row holding a NaN is never
+ * correct), defined (`has_accuracy` = 1) when the block declares exactly one target, that target is
+ * f32 and the loss is not the value `model.forward(...)` returns. The current batch is left as
+ * the last eval batch. msx_training_eval_line formats the line the CLI prints last:
+ * `eval loss=<loss>` and, when defined, ` accuracy=<accuracy>` (cli/src/train.rs:1553-1559). */
+int msx_training_eval_dense(msx_training* training, const char* dir, double* loss, double* accuracy, int* has_accuracy);
+uint64_t msx_training_eval_line(double loss, double accuracy, int has_accuracy, char* out, uint64_t capacity);
 
 /* ---- a whole run and its standard output --------------------------------------------------------
  * `train --backend cuda` as one call: the steps `start` .. `start + steps` of the train block (the

@@ -120,6 +120,11 @@ SIGNATURES = {
     "msx_dense_batch_bytes": (C.c_uint64, [_P, C.c_uint32]),
     "msx_dense_check_bound": (C.c_int, [_P, C.c_uint32, C.c_uint64, C.c_char_p]),
     "msx_dense_step": (C.c_int, [_P, C.c_uint32, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "msx_dense_open_eval": (C.c_int, [C.c_char_p, C.c_uint32, C.POINTER(C.c_char_p), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
+                                      C.POINTER(C.c_uint32), C.POINTER(C.c_uint64), C.POINTER(_P)]),
+    "msx_dense_eval_batch": (C.c_int, [_P, C.c_uint32, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "msx_training_eval_dense": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]),
+    "msx_training_eval_line": (C.c_uint64, [C.c_double, C.c_double, C.c_int, C.c_char_p, C.c_uint64]),
     "msx_training_bind_dense": (C.c_int, [_P, C.c_char_p]),
     "msx_training_feed_dense": (C.c_int, [_P, C.c_uint64]),
     "msx_packed_open": (C.c_int, [C.c_char_p, C.POINTER(_P)]),
@@ -477,12 +482,17 @@ class Checkpoint:
         return out
 
 
+def eval_line(loss, accuracy=None):
+    """The last line of a run with `--eval`: `eval loss=<loss>[ accuracy=<accuracy>]`."""
+    return _text(lambda buf, cap: lib().msx_training_eval_line(loss, accuracy if accuracy is not None else 0.0, 0 if accuracy is None else 1, buf, cap))
+
+
 class Dense:
     """A dense data directory (msx_dense): `<name>.f32` / `<name>.i32` per declaration and an
     optional `order.u32`. `declarations` = [(name, "f32" | "i32", "input" | "target", shape), ...] in
     source order; `steps` = the run's step count (what an order must cover)."""
 
-    def __init__(self, directory, declarations, steps):
+    def __init__(self, directory, declarations, steps, eval_directory=False):
         n = len(declarations)
         names = (C.c_char_p * n)(*[d[0].encode() for d in declarations])
         is_i32 = (C.c_uint32 * n)(*[1 if d[1] == "i32" else 0 for d in declarations])
@@ -491,7 +501,10 @@ class Dense:
         flat = [int(x) for d in declarations for x in d[3]]
         shapes = (C.c_uint64 * max(len(flat), 1))(*flat)
         h = _P()
-        rc = lib().msx_dense_open(str(directory).encode(), n, names, is_i32, is_target, ranks, shapes, steps, C.byref(h))
+        if eval_directory:   # `--eval <dir>`: no order, a whole number of batches
+            rc = lib().msx_dense_open_eval(str(directory).encode(), n, names, is_i32, is_target, ranks, shapes, C.byref(h))
+        else:
+            rc = lib().msx_dense_open(str(directory).encode(), n, names, is_i32, is_target, ranks, shapes, steps, C.byref(h))
         if rc != OK:
             raise MsxError(rc, lib().msx_dense_last_error(None).decode())
         self.h = h
@@ -518,6 +531,15 @@ class Dense:
         rc = lib().msx_dense_check_bound(self.h, index, bound, what.encode())
         if rc != OK:
             raise MsxError(rc, lib().msx_dense_last_error(self.h).decode())
+
+    def eval_batch(self, index, b):
+        """Batch `b` of declaration `index` of an eval directory as a flat array."""
+        nbytes = int(lib().msx_dense_batch_bytes(self.h, index))
+        out = np.empty(nbytes // 4, dtype=np.int32 if self.declarations[index][1] == "i32" else np.float32)
+        rc = lib().msx_dense_eval_batch(self.h, index, b, out.ctypes.data, nbytes)
+        if rc != OK:
+            raise MsxError(rc, "msx_dense_eval_batch")
+        return out
 
     def step(self, index, k):
         """The batch of step `k` of declaration `index` as a flat array."""
@@ -699,6 +721,12 @@ class Training:
     def bind_dense(self, directory):
         """Feeds the run from a dense directory (`<name>.f32` / `<name>.i32`, optional `order.u32`)."""
         self.check(lib().msx_training_bind_dense(self.h, str(directory).encode()))
+
+    def eval_dense(self, directory):
+        """`--eval <dir>`: (mean loss, accuracy or None) of the forward program over an eval directory."""
+        loss, accuracy, has = C.c_double(), C.c_double(), C.c_int()
+        self.check(lib().msx_training_eval_dense(self.h, str(directory).encode(), C.byref(loss), C.byref(accuracy), C.byref(has)))
+        return loss.value, (accuracy.value if has.value else None)
 
     def feed_dense(self, step):
         """Makes the dense batch of `step` the current batch."""

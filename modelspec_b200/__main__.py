@@ -2,7 +2,7 @@
 --backend cuda` on this backend, printing the reference's standard output for the run
 (crates/modelspec-cli/src/train.rs:7-17; crates/modelspec-cli/src/infer.rs:1-60).
 
-    python -m modelspec_b200 train FILE [--data DIR] [--eval-every N] [--masked-rows N]
+    python -m modelspec_b200 train FILE [--data DIR] [--eval DIR] [--eval-every N] [--masked-rows N]
         [--resume IN.msckpt] [--checkpoint OUT.msckpt] [--stats] [--profile] [--bf16] [--device I]
     python -m modelspec_b200 infer FILE [--resume IN.msckpt] [--bf16] [--device I]
 
@@ -23,6 +23,7 @@ def main(argv=None):
     ap.add_argument("command", choices=["train", "infer"])
     ap.add_argument("file")
     ap.add_argument("--data", help="a packed masked-language-model directory (it holds binding.json) or a dense one")
+    ap.add_argument("--eval", help="a dense directory to evaluate the trained parameters on (a last line `eval loss=... accuracy=...`)")
     ap.add_argument("--eval-every", type=int, default=0, help="evaluate the HeldOut split of --data every N steps and at the last step")
     ap.add_argument("--masked-rows", type=int, default=0, help="capacity of the masked-row gather (0: none)")
     ap.add_argument("--resume", help="a .msckpt checkpoint to start from")
@@ -61,6 +62,8 @@ def main(argv=None):
         except M.MsxError:
             sys.stdout.write(run.report())  # the lines through the failing step
             raise
+        if args.eval:
+            sys.stdout.write(M.eval_line(*run.eval_dense(args.eval)))
         if args.checkpoint:
             done = run.checkpoint(start + run.steps)
             done.write(args.checkpoint)

@@ -241,6 +241,27 @@ inline std::string f32_debug(float v) {
     return sign + plain_decimal(digits, exp10, true);
 }
 
+// Rust `{}` of an f64: the shortest digits that read back to the same f64, as a plain decimal.
+inline std::string f64_display(double v) {
+    if (std::isnan(v)) return "NaN";
+    if (std::isinf(v)) return v < 0 ? "-inf" : "inf";
+    std::string sign = std::signbit(v) ? "-" : "";
+    double a = std::fabs(v);
+    if (a == 0.0) return sign + "0";
+    char buf[64];
+    for (int prec = 0; prec < 17; ++prec) {
+        std::snprintf(buf, sizeof buf, "%.*e", prec, a);
+        if (std::strtod(buf, nullptr) == a) break;
+    }
+    std::string text(buf);
+    const size_t e = text.find('e');
+    std::string digits;
+    for (char c : text.substr(0, e))
+        if (c >= '0' && c <= '9') digits.push_back(c);
+    while (digits.size() > 1 && digits.back() == '0') digits.pop_back();
+    return sign + plain_decimal(digits, std::atoi(text.c_str() + e + 1) + 1, false);
+}
+
 // Rust `{}` of an f32.
 inline std::string f32_display(float v) {
     std::string special = f32_special(v);

@@ -110,12 +110,29 @@ void read_tensor(const std::string& dir, Tensor* t) {
     }
 }
 
+int open_dense(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
+               const uint32_t* ranks, const uint64_t* shapes, uint64_t steps, bool eval, msx_dense** out);
+
 }  // namespace
 
 extern "C" {
 
 int msx_dense_open(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
                    const uint32_t* ranks, const uint64_t* shapes, uint64_t steps, msx_dense** out) {
+    return open_dense(dir, count, names, is_i32, is_target, ranks, shapes, steps, false, out);
+}
+
+// dense_eval (data.rs:582-600): the same files, no order, a whole number of batches.
+int msx_dense_open_eval(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
+                        const uint32_t* ranks, const uint64_t* shapes, msx_dense** out) {
+    return open_dense(dir, count, names, is_i32, is_target, ranks, shapes, 0, true, out);
+}
+
+}  // extern "C"
+
+namespace {
+int open_dense(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
+               const uint32_t* ranks, const uint64_t* shapes, uint64_t steps, bool eval, msx_dense** out) {
     if (!dir || !out || (count && (!names || !is_i32 || !is_target || !ranks || !shapes))) return MSX_BAD_ARGUMENT;
     *out = nullptr;
     msx_dense* d = new msx_dense();
@@ -155,10 +172,13 @@ int msx_dense_open(const char* dir, uint32_t count, const char* const* names, co
             for (const Tensor& t : d->tensors) message += ", " + t.name + " " + std::to_string(t.count() / t.sample);
             throw Refused{MSX_BAD_INPUT, message + ")"};
         }
-        // dense (data.rs:513-577): the optional order.
+        if (eval && d->samples % d->batch != 0)
+            throw Refused{MSX_BAD_INPUT, "E-DATA-009: the eval data is not a whole number of batches (directory " + d->dir + ", samples " +
+                                             std::to_string(d->samples) + ", batch " + std::to_string(d->batch) + ")"};
+        // dense (data.rs:513-577): the optional order, which an eval directory does not read.
         const std::string path = d->dir + "/order.u32";
         std::vector<char> bytes;
-        if (read_file(path, &bytes)) {
+        if (!eval && read_file(path, &bytes)) {
             if (bytes.size() % 4 != 0)
                 throw Refused{MSX_BAD_INPUT, "E-DATA-007: the order file is not a whole number of u32 indices (file " + path + ", bytes " +
                                                  std::to_string(bytes.size()) + ")"};
@@ -189,6 +209,9 @@ int msx_dense_open(const char* dir, uint32_t count, const char* const* names, co
     *out = d;
     return MSX_OK;
 }
+}  // namespace
+
+extern "C" {
 
 void msx_dense_close(msx_dense* dense) { delete dense; }
 
@@ -231,6 +254,16 @@ int msx_dense_step(const msx_dense* dense, uint32_t index, uint64_t step, void* 
                                                  : static_cast<uint64_t>(position % dense->samples);
         std::memcpy(static_cast<char*>(out) + i * sample_bytes, t.values.data() + sample * sample_bytes, sample_bytes);
     }
+    return MSX_OK;
+}
+
+// fill_eval_batch (data.rs:456-460): the samples b B .. (b + 1) B.
+int msx_dense_eval_batch(const msx_dense* dense, uint32_t index, uint64_t batch, void* out, uint64_t capacity_bytes) {
+    if (!dense || index >= dense->tensors.size() || !out) return MSX_BAD_ARGUMENT;
+    const Tensor& t = dense->tensors[index];
+    const uint64_t bytes = t.sample * 4 * dense->batch;
+    if (capacity_bytes < bytes || (batch + 1) * dense->batch > dense->samples) return MSX_BAD_ARGUMENT;
+    std::memcpy(out, t.values.data() + batch * bytes, bytes);
     return MSX_OK;
 }
 

@@ -767,6 +767,90 @@ int msx_training_feed_dense(msx_training* t, uint64_t step) {
     });
 }
 
+int msx_training_eval_dense(msx_training* t, const char* dir, double* loss, double* accuracy, int* has_accuracy) {
+    if (!t || !dir || !loss || !accuracy || !has_accuracy) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        const auto& decls = c.config.data;
+        std::vector<const char*> names;
+        std::vector<uint32_t> is_i32, is_target, ranks;
+        std::vector<uint64_t> shapes;
+        for (const msx::DataDecl& d : decls) {
+            names.push_back(d.name.c_str());
+            is_i32.push_back(d.ty.i32 ? 1u : 0u);
+            is_target.push_back(d.target ? 1u : 0u);
+            ranks.push_back(static_cast<uint32_t>(d.ty.shape.size()));
+            for (uint64_t n : d.ty.shape) shapes.push_back(n);
+        }
+        msx_dense* data = nullptr;
+        if (msx_dense_open_eval(dir, static_cast<uint32_t>(decls.size()), names.data(), is_i32.data(), is_target.data(), ranks.data(), shapes.data(),
+                                &data) != MSX_OK)
+            throw Fail{MSX_BAD_INPUT, msx_dense_last_error(nullptr)};
+        std::unique_ptr<msx_dense, void (*)(msx_dense*)> owned(data, msx_dense_close);
+        // compared_target (data.rs:419-425, read_dense :640-655): the one target, when it is f32 and
+        // the loss is not the value the forward call returns.
+        int compared = -1;
+        uint32_t targets = 0;
+        for (uint32_t i = 0; i < decls.size(); ++i)
+            if (decls[i].target) {
+                ++targets;
+                compared = static_cast<int>(i);
+            }
+        const bool forward_value = !c.forward.outputs.empty() && c.forward.outputs[0].value == c.forward.node(c.prediction).id;
+        if (targets != 1 || forward_value || decls[static_cast<size_t>(compared)].ty.i32) compared = -1;
+        const uint64_t batches = msx_dense_samples(data) / msx_dense_batch(data);
+        std::vector<float> prediction(msx_training_prediction_count(t));
+        double sum = 0.0;
+        uint64_t correct = 0, rows = 0;
+        auto argmax = [](const float* row, uint64_t width, uint64_t* at) {
+            for (uint64_t i = 0; i < width; ++i)
+                if (row[i] != row[i]) return false;
+            uint64_t best = 0;
+            for (uint64_t i = 1; i < width; ++i)
+                if (row[i] > row[best]) best = i;
+            *at = best;
+            return true;
+        };
+        for (uint64_t b = 0; b < batches; ++b) {
+            for (uint32_t i = 0; i < decls.size(); ++i) {
+                std::vector<char>& bytes = t->batch[decls[i].name];
+                bytes.resize(msx_dense_batch_bytes(data, i));
+                if (msx_dense_eval_batch(data, i, b, bytes.data(), bytes.size()) != MSX_OK) throw Fail{MSX_BAD_ARGUMENT, "the eval batch does not fit its declaration"};
+            }
+            float batch_loss = 0.0f;
+            if (msx_training_infer(t, prediction.data(), prediction.size() * 4, &batch_loss) != MSX_OK) throw Fail{MSX_LAUNCH_FAILED, t->error};
+            sum += static_cast<double>(batch_loss);
+            if (compared < 0) continue;
+            // correct_rows (runner.rs:626-636): rows along the target's leading dimension.
+            const msx::DataDecl& target = decls[static_cast<size_t>(compared)];
+            const std::vector<char>& held = t->batch[target.name];
+            const float* wanted = reinterpret_cast<const float*>(held.data());
+            const uint64_t count = held.size() / 4, target_rows = target.ty.shape.empty() ? 1 : target.ty.shape[0];
+            const uint64_t width = target_rows ? count / target_rows : 0;
+            for (uint64_t r = 0; r < target_rows && width; ++r) {
+                uint64_t p = 0, w = 0;
+                if (argmax(prediction.data() + r * width, width, &p) && argmax(wanted + r * width, width, &w) && p == w) ++correct;
+            }
+            rows += target_rows;
+        }
+        *loss = sum / static_cast<double>(batches);
+        *has_accuracy = compared >= 0 ? 1 : 0;
+        *accuracy = compared >= 0 ? static_cast<double>(correct) / static_cast<double>(rows) : 0.0;
+    });
+}
+
+uint64_t msx_training_eval_line(double loss, double accuracy, int has_accuracy, char* out, uint64_t capacity) {
+    std::string text = "eval loss=" + msx::f64_display(loss);
+    if (has_accuracy) text += " accuracy=" + msx::f64_display(accuracy);
+    text += "\n";
+    if (out && capacity) {
+        const size_t n = std::min<size_t>(capacity - 1, text.size());
+        std::memcpy(out, text.data(), n);
+        out[n] = 0;
+    }
+    return text.size() + 1;
+}
+
 // ---- checkpoints (crates/modelspec-runtime/src/train/checkpoint.rs:420-451, :519-609) --------------
 
 namespace {

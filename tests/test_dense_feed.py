@@ -108,3 +108,28 @@ def test_the_refusals_of_the_order_and_of_an_id_outside_its_table(tmp_path):
     first = int(np.argmax(ids >= ids.max()))
     assert "E-DATA-011" in message and "outside the %d rows" % ids.max() in message and "position %d" % first in message
     d.close()
+
+
+def test_an_eval_directory_is_whole_batches_and_reads_no_order(tmp_path):
+    x, ids, y = directory_of(tmp_path, samples=12)
+    write(tmp_path, "order.u32", np.array([99], dtype=np.uint32))   # would be refused by a --data directory; --eval does not read it
+    d = M.Dense(tmp_path, DECLS, steps=0, eval_directory=True)
+    assert (d.batch, d.samples, d.has_order) == (4, 12, False)
+    for b in range(3):
+        assert np.array_equal(d.eval_batch(0, b), x[4 * b:4 * b + 4].reshape(-1))
+        assert np.array_equal(d.eval_batch(1, b), ids[4 * b:4 * b + 4])
+    with pytest.raises(M.MsxError):
+        d.eval_batch(0, 3)
+    d.close()
+    directory_of(tmp_path, samples=10)
+    with pytest.raises(M.MsxError) as e:
+        M.Dense(tmp_path, DECLS, steps=0, eval_directory=True)
+    message = str(e.value)
+    assert "E-DATA-009" in message and "not a whole number of batches" in message and "samples 10" in message and "batch 4" in message
+
+
+def test_the_eval_line_prints_f64_as_the_reference_does():
+    assert M.eval_line(0.125, 0.5) == "eval loss=0.125 accuracy=0.5\n"
+    assert M.eval_line(3.0, 1.0) == "eval loss=3 accuracy=1\n"
+    assert M.eval_line(1e-7) == "eval loss=0.0000001\n"
+    assert M.eval_line(0.1 + 0.2) == "eval loss=0.30000000000000004\n"

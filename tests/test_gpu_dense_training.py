@@ -106,3 +106,73 @@ def test_the_command_line_takes_a_dense_directory(tmp_path):
     done = subprocess.run([sys.executable, "-m", "modelspec_b200", "train", str(spec), "--data", str(tmp_path)], capture_output=True, text=True,
                           cwd=os.path.dirname(HERE))
     assert done.returncode == 1 and "E-DATA-007" in done.stderr and "the target `y`" in done.stderr
+
+
+WIDE_REGRESSION = """model LinearReg {
+    param w: Tensor<f32, [4, 3]> = xavier_uniform();
+    fn forward(x: Tensor<f32, [8, 4]>) -> Tensor<f32, [8, 3]> {
+        return matmul(x, w);
+    }
+}
+train Fit {
+    model = LinearReg;
+    input x: Tensor<f32, [8, 4]>;
+    target y: Tensor<f32, [8, 3]>;
+    loss = mse(model.forward(x), y);
+    optimizer = sgd(lr = 0.1);
+    steps = 6;
+    seed = 42;
+    device = cpu;
+}
+"""
+
+
+def test_an_eval_directory_gives_the_mean_batch_loss_and_the_accuracy(device, tmp_path):
+    """`--eval <dir>` (train/runner.rs:571-624): the mean of the batch losses summed in f64 and
+    the fraction of target rows whose prediction has its first maximum where the target has its."""
+    r = np.random.default_rng(8)
+    x = r.standard_normal((24, 4)).astype(np.float32)
+    y = r.standard_normal((24, 3)).astype(np.float32)
+    x.tofile(os.path.join(str(tmp_path), "x.f32"))
+    y.tofile(os.path.join(str(tmp_path), "y.f32"))
+    run = M.Training(device, WIDE_REGRESSION, 0, M.PLAN_EXACT_MATMUL)
+    try:
+        run.bind_dense(str(tmp_path))
+        run.run()
+        loss, accuracy = run.eval_dense(str(tmp_path))
+        total, correct = 0.0, 0
+        for b in range(3):
+            run.set_input("x", x[8 * b:8 * b + 8])
+            run.set_input("y", y[8 * b:8 * b + 8])
+            prediction, batch_loss = run.infer()
+            total += float(batch_loss)
+            correct += int((prediction.reshape(8, 3).argmax(axis=1) == y[8 * b:8 * b + 8].argmax(axis=1)).sum())
+        assert loss == total / 3 and accuracy == correct / 24
+        assert M.eval_line(loss, accuracy).startswith("eval loss=") and " accuracy=" in M.eval_line(loss, accuracy)
+        # A directory that is not a whole number of batches is refused.
+        x[:20].tofile(os.path.join(str(tmp_path), "x.f32"))
+        y[:20].tofile(os.path.join(str(tmp_path), "y.f32"))
+        with pytest.raises(M.MsxError) as e:
+            run.eval_dense(str(tmp_path))
+        assert "E-DATA-009" in str(e.value)
+    finally:
+        run.destroy()
+    # Labels that a cross_entropy reads are no compared target: no accuracy (data.rs:640-655).
+    vocab, seq, batch = 300, 16, 4
+    source = models.bert(name="BertTiny", hidden=32, heads=2, ffn=64, vocab=vocab, seq=seq, batch=batch, steps=2, warmup_steps=1)
+    ids = r.integers(5, vocab, size=(2 * batch, seq)).astype(np.int32)
+    files = {"ids.i32": ids.reshape(-1), "positions.i32": np.tile(np.arange(seq, dtype=np.int32), 2 * batch),
+             "key_mask.f32": np.ones((2 * batch, seq), dtype=np.float32), "labels.i32": ids.reshape(-1),
+             "weights.f32": (r.random(2 * batch * seq) < 0.15).astype(np.float32)}
+    where = tmp_path / "mlm"
+    where.mkdir()
+    for name, values in files.items():
+        values.tofile(os.path.join(str(where), name))
+    run = M.Training(device, source, 16)
+    try:
+        run.bind_dense(str(where))
+        run.run()
+        loss, accuracy = run.eval_dense(str(where))
+        assert accuracy is None and np.isfinite(loss) and loss > 0
+    finally:
+        run.destroy()
