@@ -257,7 +257,9 @@ int msx_training_synthetic(msx_training* t) {
         if (inputs != 1 || targets != 1)
             throw Fail{MSX_BAD_INPUT, "E-DATA-001: M0 synthetic data takes one input besides key masks and one target"};
         if (input->ty.i32 || target->ty.i32) throw Fail{MSX_BAD_INPUT, "E-DATA-004: M0 synthetic data cannot draw an i32 tensor"};
-        if (target->ty != fwd.node(c.prediction).ty) throw Fail{MSX_BAD_INPUT, "E-DATA-002: the target has not the type of the prediction"};
+        if (target->ty != fwd.node(c.prediction).ty)
+            throw Fail{MSX_BAD_INPUT, "E-DATA-002: the target is not of the model output type\n  target: " + target->ty.str() +
+                                          "\n  model output: " + fwd.node(c.prediction).ty.str()};
         std::vector<float> x = msx::standard_normal_draw(c.config.seed, msx::kStreamData, input->name, input->ty.count());
         t->batch[input->name].assign(reinterpret_cast<char*>(x.data()), reinterpret_cast<char*>(x.data()) + x.size() * 4);
         for (const msx::DataDecl& d : c.config.data)
@@ -692,21 +694,56 @@ uint32_t msx_training_heldout_batches(const msx_training* t) { return t ? static
 
 // ---- dense data (crates/modelspec-runtime/src/train/data.rs:513-577, :627-671) ---------------------
 
+namespace {
+
+// The Input node of `program` that reads the declaration `name`, or -1.
+int64_t input_named(const msx::Program& program, const std::string& name) {
+    for (uint32_t in : program.inputs)
+        if (program.node(in).name == name) return in;
+    return -1;
+}
+
+// What read_dense refuses before it opens a file (data.rs:627-668), in its order: the one target
+// the loss compares with the model output has the output's type (E-DATA-002), unless it is i32
+// labels a cross_entropy reads or the loss is the value the forward call returns; every
+// declaration is read by the loss (E-DATA-003, refuse_unread :307-338).
+void refuse_dense_declarations(const msx::Compiled& c) {
+    const auto& decls = c.config.data;  // in source order
+    const msx::Program& fwd = c.forward_with_dropout;
+    const msx::DataDecl* target = nullptr;
+    uint32_t targets = 0;
+    for (const msx::DataDecl& d : decls)
+        if (d.target) {
+            target = &d;
+            ++targets;
+        }
+    const bool forward_value = !c.forward.outputs.empty() && c.forward.outputs[0].value == c.forward.node(c.prediction).id;
+    if (targets == 1 && !forward_value) {
+        bool labels = false;
+        const int64_t input = input_named(fwd, target->name);
+        if (target->ty.i32 && input >= 0)
+            for (const msx::Node& n : fwd.nodes)
+                if (n.op == msx::Op::CrossEntropy && n.operands.size() >= 2 && n.operands[1] == static_cast<uint32_t>(input)) labels = true;
+        const msx::Type& output = c.forward.node(c.prediction).ty;
+        if (!labels && target->ty != output)
+            throw Fail{MSX_BAD_INPUT, "E-DATA-002: the target is not of the model output type\n  target: " + target->ty.str() +
+                                          "\n  model output: " + output.str()};
+    }
+    for (const msx::DataDecl& d : decls)
+        if (input_named(fwd, d.name) < 0)
+            throw Fail{MSX_BAD_INPUT, std::string("E-DATA-003: the ") + (d.target ? "target" : "input") + " `" + d.name + "` is not read by the loss"};
+}
+
+}  // namespace
+
 int msx_training_bind_dense(msx_training* t, const char* dir) {
     if (!t || !dir) return MSX_BAD_ARGUMENT;
     return guarded(t, [&] {
         const msx::Compiled& c = t->compiled;
         const auto& decls = c.config.data;  // in source order
-        // refuse_unread (data.rs:307-338): every declaration has an Input node of the forward program.
         const msx::Program& fwd = c.forward_with_dropout;
-        auto input_of = [&](const std::string& name) -> int64_t {
-            for (uint32_t in : fwd.inputs)
-                if (fwd.node(in).name == name) return in;
-            return -1;
-        };
-        for (const msx::DataDecl& d : decls)
-            if (input_of(d.name) < 0)
-                throw Fail{MSX_BAD_INPUT, std::string("E-DATA-003: the ") + (d.target ? "target" : "input") + " `" + d.name + "` is not read by the loss"};
+        auto input_of = [&](const std::string& name) { return input_named(fwd, name); };
+        refuse_dense_declarations(c);
         std::vector<const char*> names;
         std::vector<uint32_t> is_i32, is_target, ranks;
         std::vector<uint64_t> shapes;
@@ -772,6 +809,7 @@ int msx_training_eval_dense(msx_training* t, const char* dir, double* loss, doub
     return guarded(t, [&] {
         const msx::Compiled& c = t->compiled;
         const auto& decls = c.config.data;
+        refuse_dense_declarations(c);
         std::vector<const char*> names;
         std::vector<uint32_t> is_i32, is_target, ranks;
         std::vector<uint64_t> shapes;

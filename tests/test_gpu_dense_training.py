@@ -176,3 +176,52 @@ def test_an_eval_directory_gives_the_mean_batch_loss_and_the_accuracy(device, tm
         assert accuracy is None and np.isfinite(loss) and loss > 0
     finally:
         run.destroy()
+
+
+WEIGHTED_CLASSES = """model Classes {
+    param w: Tensor<f32, [3, 5]> = xavier_uniform();
+    fn forward(x: Tensor<f32, [6, 3]>) -> Tensor<f32, [6, 5]> {
+        return matmul(x, w);
+    }
+}
+train Fit {
+    model = Classes;
+    input x: Tensor<f32, [6, 3]>;
+    input labels: Tensor<i32, [6]>;
+    target weights: Tensor<f32, [6]>;
+    loss = cross_entropy(model.forward(x), labels, weights);
+    optimizer = sgd(lr = 0.1);
+    steps = 2;
+    seed = 7;
+    device = cpu;
+}
+"""
+
+
+def test_the_one_compared_target_is_held_to_the_model_output_type(device, tmp_path):
+    """read_dense (train/data.rs:640-662): a block's single target that is no cross_entropy's
+    labels has the type of the model output, else E-DATA-002 with both types, before any file
+    is opened (the directory here is empty); the same target as labels is accepted."""
+    run = M.Training(device, WEIGHTED_CLASSES, 0)
+    try:
+        for bind in (run.bind_dense, run.eval_dense):
+            with pytest.raises(M.MsxError) as e:
+                bind(str(tmp_path))
+            message = str(e.value)
+            assert e.value.status == M.BAD_INPUT and "E-DATA-002: the target is not of the model output type" in message
+            assert "target: Tensor<f32, [6]>" in message and "model output: Tensor<f32, [6, 5]>" in message
+    finally:
+        run.destroy()
+    labelled = WEIGHTED_CLASSES.replace("input labels", "target labels").replace("target weights", "input weights")
+    r = np.random.default_rng(2)
+    r.standard_normal((12, 3)).astype(np.float32).tofile(os.path.join(str(tmp_path), "x.f32"))
+    r.integers(0, 5, size=12).astype(np.int32).tofile(os.path.join(str(tmp_path), "labels.i32"))
+    np.ones(12, dtype=np.float32).tofile(os.path.join(str(tmp_path), "weights.f32"))
+    run = M.Training(device, labelled, 0)
+    try:
+        run.bind_dense(str(tmp_path))
+        run.run()
+        loss, accuracy = run.eval_dense(str(tmp_path))
+        assert accuracy is None and np.isfinite(loss)
+    finally:
+        run.destroy()
