@@ -110,27 +110,8 @@ void read_tensor(const std::string& dir, Tensor* t) {
     }
 }
 
-int open_dense(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
-               const uint32_t* ranks, const uint64_t* shapes, uint64_t steps, bool eval, msx_dense** out);
-
-}  // namespace
-
-extern "C" {
-
-int msx_dense_open(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
-                   const uint32_t* ranks, const uint64_t* shapes, uint64_t steps, msx_dense** out) {
-    return open_dense(dir, count, names, is_i32, is_target, ranks, shapes, steps, false, out);
-}
-
-// dense_eval (data.rs:582-600): the same files, no order, a whole number of batches.
-int msx_dense_open_eval(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
-                        const uint32_t* ranks, const uint64_t* shapes, msx_dense** out) {
-    return open_dense(dir, count, names, is_i32, is_target, ranks, shapes, 0, true, out);
-}
-
-}  // extern "C"
-
-namespace {
+// `dense` and `dense_eval` (data.rs:513-600): the files of every declaration, then either the
+// optional order of a run or the whole-batches rule of an evaluation.
 int open_dense(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
                const uint32_t* ranks, const uint64_t* shapes, uint64_t steps, bool eval, msx_dense** out) {
     if (!dir || !out || (count && (!names || !is_i32 || !is_target || !ranks || !shapes))) return MSX_BAD_ARGUMENT;
@@ -209,9 +190,21 @@ int open_dense(const char* dir, uint32_t count, const char* const* names, const 
     *out = d;
     return MSX_OK;
 }
+
 }  // namespace
 
 extern "C" {
+
+int msx_dense_open(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
+                   const uint32_t* ranks, const uint64_t* shapes, uint64_t steps, msx_dense** out) {
+    return open_dense(dir, count, names, is_i32, is_target, ranks, shapes, steps, false, out);
+}
+
+// dense_eval (data.rs:582-600): the same files, no order, a whole number of batches.
+int msx_dense_open_eval(const char* dir, uint32_t count, const char* const* names, const uint32_t* is_i32, const uint32_t* is_target,
+                        const uint32_t* ranks, const uint64_t* shapes, msx_dense** out) {
+    return open_dense(dir, count, names, is_i32, is_target, ranks, shapes, 0, true, out);
+}
 
 void msx_dense_close(msx_dense* dense) { delete dense; }
 
@@ -262,7 +255,7 @@ int msx_dense_eval_batch(const msx_dense* dense, uint32_t index, uint64_t batch,
     if (!dense || index >= dense->tensors.size() || !out) return MSX_BAD_ARGUMENT;
     const Tensor& t = dense->tensors[index];
     const uint64_t bytes = t.sample * 4 * dense->batch;
-    if (capacity_bytes < bytes || (batch + 1) * dense->batch > dense->samples) return MSX_BAD_ARGUMENT;
+    if (capacity_bytes < bytes || batch >= dense->samples / dense->batch) return MSX_BAD_ARGUMENT;
     std::memcpy(out, t.values.data() + batch * bytes, bytes);
     return MSX_OK;
 }
