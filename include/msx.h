@@ -449,8 +449,9 @@ uint32_t msx_training_heldout_batches(const msx_training* training);
  * The reference's dense directory (train/data.rs:14-35): `<dir>/<name>.f32` or `<dir>/<name>.i32`
  * for every `input` and `target` declaration, row-major little-endian values without a header,
  * and an optional `<dir>/order.u32`. msx_dense_open takes the declarations in source order (name,
- * dtype, role, rank and shape: `shapes` holds the ranks[0] + ranks[1] + ... extents one after
- * another) and the run's step count, and reads and checks the files as the reference does
+ * dtype, role, rank and shape: `is_target` is 0 for an input, 1 for a target and 2 for an argument
+ * of a model function run as an inference entry, which the messages name so; `shapes` holds the
+ * ranks[0] + ranks[1] + ... extents one after another) and the run's step count, and reads and checks the files as the reference does
  * (read_files :837-876, read_tensor :1232-1290, dense :513-577): B is the leading dimension all
  * declarations share, else 1; a file is a whole number of samples of finite values (E-DATA-007);
  * all files hold the same number N of samples (E-DATA-007); an order holds at least steps x B
@@ -641,6 +642,37 @@ const char* msx_static_last_error(void);
  * Mirrors compile::compile_training_with (crates/modelspec-core/src/compile.rs:85-116). */
 uint64_t msx_compile(const char* source, const char* which, uint64_t masked_rows, char* out,
                      uint64_t capacity);
+
+/* `infer --data <dir> --function <name> --out <path>` (crates/modelspec-cli/src/infer.rs:306-470):
+ * msx_training_create_function makes a run of the model function `name` as an inference entry
+ * (msx_compile_function below) instead of the train block: its arguments are the run's inputs, its
+ * result the prediction. A name the model does not declare is E-DATA-010 naming its functions
+ * (MSX_BAD_INPUT, text in msx_last_error(device)). msx_training_load_parameters loads a
+ * checkpoint's parameters without its optimizer (Checkpoint::parameters_for, checkpoint.rs:519-585:
+ * E-CKPT-003 at the first path, dtype or shape that differs in path order, then at a differing
+ * schema hash); `step` (may be NULL) receives the checkpoint's step.
+ * msx_training_refuse_out_reading refuses, before anything is read, an `out` that resolves to a
+ * file the run reads: `model`, `checkpoint` (either may be NULL) or an argument's file of `dir`
+ * (refuse_out_reading, train/data.rs:773-798; E-DATA-010; by canonical path, or by device and
+ * inode for a hard link). msx_training_infer_dense binds every argument to `<dir>/<name>.f32|.i32`
+ * as --eval binds a declaration (dense_function, train/data.rs:685-717: E-DATA-010 for a function
+ * without arguments, E-DATA-007, E-DATA-011, E-DATA-009 when the samples are no whole number of
+ * blocks of B), holds the result to one row per sample (row_elements :732-762, E-DATA-010), runs
+ * the function on every block in block order and writes the results, row-major little-endian f32
+ * without a header, to `out` through `.<name>.<pid>.tmp` beside it, synced and renamed over it, so
+ * an existing `out` is replaced whole or not at all. `blocks` and `rows` are what the CLI prints:
+ * `function <name> blocks <blocks> rows <rows> out <path>`. */
+int msx_training_create_function(msx_device* device, const char* source, const char* name, uint32_t flags, msx_training** out);
+int msx_training_load_parameters(msx_training* training, const msx_checkpoint* checkpoint, uint64_t* step);
+int msx_training_refuse_out_reading(msx_training* training, const char* dir, const char* out, const char* model, const char* checkpoint);
+int msx_training_infer_dense(msx_training* training, const char* dir, const char* out, uint64_t* blocks, uint64_t* rows);
+
+/* A model function as an inference entry (compile::compile_function,
+ * crates/modelspec-core/src/compile.rs:173-223): one input per argument, the function's result the
+ * prediction, the result itself (rank 0) or its mean the loss, every dropout the identity, sgd at
+ * the block's learning rate. `which` is "step", "forward" or "prediction" (the prediction's value
+ * id, `%n`). A name the model does not declare fails with E-DATA-010 naming its functions. */
+uint64_t msx_compile_function(const char* source, const char* name, const char* which, char* out, uint64_t capacity);
 
 #ifdef __cplusplus
 }

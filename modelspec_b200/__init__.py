@@ -181,6 +181,11 @@ SIGNATURES = {
     "msx_sum_rows_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, _P, _P]),
     "msx_static_last_error": (C.c_char_p, []),
     "msx_compile": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_uint64, C.c_char_p, C.c_uint64]),
+    "msx_compile_function": (C.c_uint64, [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.c_uint64]),
+    "msx_training_create_function": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.c_uint32, C.POINTER(_P)]),
+    "msx_training_load_parameters": (C.c_int, [_P, _P, C.POINTER(C.c_uint64)]),
+    "msx_training_refuse_out_reading": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p]),
+    "msx_training_infer_dense": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
 }
 
 _lib = None
@@ -217,6 +222,13 @@ def compile_mspec(source, which="step", masked_rows=0):
     """`.mspec` source to the text of its training step ("step"), its dropout-free forward
     program ("forward") or its lowered tensor program ("tensor")."""
     return _text(lambda buf, cap: lib().msx_compile(source.encode(), which.encode(), masked_rows, buf, cap))
+
+
+def compile_function(source, name, which="forward"):
+    """The model function `name` of `.mspec` source as an inference entry: the text of its
+    forward program ("forward") or step ("step"), or its prediction's value id ("prediction").
+    A name the model does not declare raises with E-DATA-010 naming the model's functions."""
+    return _text(lambda buf, cap: lib().msx_compile_function(source.encode(), name.encode(), which.encode(), buf, cap))
 
 
 def schedule_describe(ir_text, flags=PLAN_DEFAULT):
@@ -640,10 +652,16 @@ class HeldOut:
 class Training:
     """One training run (msx_training): the host loop of `train --backend cuda`."""
 
-    def __init__(self, device, source, masked_rows=0, flags=PLAN_DEFAULT):
+    def __init__(self, device, source, masked_rows=0, flags=PLAN_DEFAULT, function=None):
+        """The run of the train block of `source`, or with `function` the model function of that
+        name as an inference entry (`infer --data --function`): its arguments the inputs, its
+        result the prediction."""
         self.device = device
         h = _P()
-        device.check(lib().msx_training_create(device.h, source.encode(), masked_rows, flags, C.byref(h)))
+        if function is None:
+            device.check(lib().msx_training_create(device.h, source.encode(), masked_rows, flags, C.byref(h)))
+        else:
+            device.check(lib().msx_training_create_function(device.h, source.encode(), function.encode(), flags, C.byref(h)))
         self.h = h
         self.steps = lib().msx_training_steps(h)
         self.seed = lib().msx_training_seed(h)
@@ -771,6 +789,24 @@ class Training:
         start = C.c_uint64()
         self.check(lib().msx_training_resume(self.h, checkpoint.h, C.byref(start)))
         return int(start.value)
+
+    def load_parameters(self, checkpoint):
+        """Loads a checkpoint's parameters, whatever its optimizer (`infer`); returns its step."""
+        step = C.c_uint64()
+        self.check(lib().msx_training_load_parameters(self.h, checkpoint.h, C.byref(step)))
+        return int(step.value)
+
+    def refuse_out_reading(self, directory, out, model=None, checkpoint=None):
+        """E-DATA-010 when `out` resolves to a file the function's run reads."""
+        enc = lambda v: None if v is None else str(v).encode()
+        self.check(lib().msx_training_refuse_out_reading(self.h, str(directory).encode(), str(out).encode(), enc(model), enc(checkpoint)))
+
+    def infer_dense(self, directory, out):
+        """Runs the function over every block of a dense directory and writes its results, one
+        row per sample, to `out`; returns (blocks, rows)."""
+        blocks, rows = C.c_uint64(), C.c_uint64()
+        self.check(lib().msx_training_infer_dense(self.h, str(directory).encode(), str(out).encode(), C.byref(blocks), C.byref(rows)))
+        return int(blocks.value), int(rows.value)
 
     def schema_hash(self):
         return lib().msx_training_schema_hash(self.h).decode()

@@ -18,6 +18,35 @@ import sys
 import modelspec_b200 as M
 
 
+def infer_function(args):
+    """`infer <file> --resume <ckpt> --data <dir> --function <name> --out <path>`
+    (crates/modelspec-cli/src/infer.rs:306-470): one line,
+    `function <name> blocks <blocks> rows <rows> out <path>`."""
+    run = device = None
+    try:
+        source = open(args.file).read()
+        device = M.Device(args.device)
+        run = M.Training(device, source, 0, M.PLAN_BF16 if args.bf16 else M.PLAN_DEFAULT, function=args.function)
+        run.refuse_out_reading(args.data, args.out, args.file, args.resume)
+        if args.resume:
+            loaded = M.Checkpoint.read(args.resume)
+            try:
+                run.load_parameters(loaded)
+            finally:
+                loaded.destroy()
+        blocks, rows = run.infer_dense(args.data, args.out)
+        sys.stdout.write("function %s blocks %d rows %d out %s\n" % (args.function, blocks, rows, args.out))
+        return 0
+    except (M.MsxError, OSError) as error:
+        sys.stderr.write("error: %s\n" % error)
+        return 1
+    finally:
+        if run is not None:
+            run.destroy()
+        if device is not None:
+            device.close()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m modelspec_b200")
     ap.add_argument("command", choices=["train", "infer"])
@@ -31,8 +60,15 @@ def main(argv=None):
     ap.add_argument("--stats", action="store_true")
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--bf16", action="store_true", help="a mixed-precision plan (bf16 storage and products, f32 masters)")
+    ap.add_argument("--function", help="infer: run this model function over the dense directory --data (with --out)")
+    ap.add_argument("--out", help="infer --function: the file the function's results go to, one row per sample, f32")
     ap.add_argument("--device", type=int, default=0)
     args = ap.parse_args(argv)
+    if args.command == "infer" and (args.function or args.out):
+        # `--function` or `--out` without `--data`, and `--data` without both, is a usage error.
+        if not (args.data and args.function and args.out):
+            ap.error("infer --function needs --data, --function and --out together")
+        return infer_function(args)
     packed = run = device = None
     try:
         source = open(args.file).read()

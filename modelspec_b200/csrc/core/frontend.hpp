@@ -44,6 +44,8 @@ struct Compiled {
     TrainConfig config;
     uint64_t masked_rows = 0;      // capacity of the gather, 0 for none
     std::string masked_labels, masked_weights;
+    std::string function;                // compile_function: the entry; empty for the train block
+    std::vector<std::string> functions;  // compile_function: the model's functions in source order
 };
 
 namespace detail {
@@ -595,6 +597,70 @@ inline Compiled compile_training(const std::string& source, uint64_t masked_rows
             p = n.operands[0];
         }
         out.prediction = p;
+    }
+    out.forward = dce(std::move(fwd));
+    return out;
+}
+
+// The model function `name` as an inference entry (compile.rs:173-223, function_entry :239-288 of
+// the reference): one `input` per argument, named and typed as the argument; the prediction is the
+// function's result; the loss is the result itself when it is rank 0 and its mean otherwise; every
+// dropout is the identity; the parameter table is the file's, so a checkpoint of the file supplies
+// the parameters. The step differentiates that loss and attaches sgd at the block's learning rate
+// whatever the block's optimizer; nothing runs its update. The configuration keeps the block's
+// seed and steps. A name the model does not declare is E-DATA-010 with the functions it declares
+// (train/data.rs:719-730).
+inline Compiled compile_function(const std::string& source, const std::string& name) {
+    detail::Parser parser;
+    parser.t = detail::lex(source);
+    detail::Source src = parser.parse();
+    Compiled out;
+    for (const detail::Function& f : src.functions) out.functions.push_back(f.name);
+    const detail::Function* entry = nullptr;
+    for (const detail::Function& f : src.functions)
+        if (f.name == name) entry = &f;
+    if (!entry) {
+        std::string listed;
+        for (const std::string& f : out.functions) listed += (listed.empty() ? "" : ", ") + f;
+        throw Error("E-DATA-010: the model declares no function `" + name + "`\n  function: " + name + "\n  functions: " + listed);
+    }
+    src.train.data.clear();
+    for (const auto& arg : entry->args) src.train.data.push_back(DataDecl{arg.first, arg.second, false});
+    src.train.rule = Rule::Sgd;
+    detail::Lowering lo(src);
+    lo.b.program.params = src.params;
+    for (const DataDecl& d : src.train.data) lo.data.push_back(lo.b.input(d.name, d.ty));
+    for (size_t i = 0; i < src.params.size(); ++i) lo.reads.push_back(lo.b.param_read(static_cast<uint32_t>(i)));
+    detail::Expr call;
+    call.kind = detail::Expr::ModelCall;
+    call.name = name;
+    uint32_t result = lo.inline_call(call, lo.data);
+    uint32_t loss = result;
+    if (lo.b.type_of(result).rank() != 0) {
+        Node mean;
+        mean.op = Op::ReduceMean;
+        mean.operands = {result};
+        loss = lo.b.push(std::move(mean));
+    }
+    lo.b.program.outputs = {Output{loss, Role::Plain, 0, 0}};
+    const Program with_dropout = dce(std::move(lo.b.program));
+    Program lowered = without_dropout(with_dropout);
+    // The result may have been a Dropout: follow it to its operand.
+    while (lowered.position(result) < 0) {
+        const Node& n = with_dropout.node(result);
+        if (n.op != Op::Dropout) break;
+        result = n.operands[0];
+    }
+    out.config = src.train;
+    out.function = name;
+    out.prediction = result;
+    out.forward_with_dropout = lowered;
+    out.step = attach_sgd(without_stop_gradient(differentiate(lowered)), src.train.lr);
+    Program fwd = without_stop_gradient(lowered);
+    while (fwd.position(out.prediction) < 0) {
+        const Node& n = lowered.node(out.prediction);
+        if (n.op != Op::StopGradient) break;
+        out.prediction = n.operands[0];
     }
     out.forward = dce(std::move(fwd));
     return out;

@@ -3791,4 +3791,26 @@ uint64_t msx_compile(const char* source, const char* which, uint64_t masked_rows
     return text.size() + 1;
 }
 
+uint64_t msx_compile_function(const char* source, const char* name, const char* which, char* out, uint64_t capacity) {
+    if (!source || !name || !which) return 0;
+    std::string text;
+    try {
+        msx::Compiled c = msx::compile_function(source, name);
+        std::string w = which;
+        if (w == "step") text = msx::print_program(c.step);
+        else if (w == "forward") text = msx::print_program(c.forward);
+        else if (w == "prediction") text = "%" + std::to_string(c.prediction);
+        else throw msx::Error("msx_compile_function: `which` is step, forward or prediction");
+    } catch (const std::exception& e) {
+        g_open_error = e.what();
+        return 0;
+    }
+    if (out && capacity) {
+        size_t n = std::min<size_t>(capacity - 1, text.size());
+        std::memcpy(out, text.data(), n);
+        out[n] = 0;
+    }
+    return text.size() + 1;
+}
+
 }  // extern "C"

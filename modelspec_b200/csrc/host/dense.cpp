@@ -28,8 +28,10 @@ struct Refused {
 
 struct Tensor {
     std::string name;
-    bool i32 = false, target = false;
+    bool i32 = false;
+    uint32_t role = 0;           // 0 an input, 1 a target, 2 an argument of an inference entry
     uint64_t sample = 0;         // values of one sample
+    const char* role_name() const { return role == 1 ? "target" : role == 2 ? "argument" : "input"; }
     std::vector<char> values;    // the whole file: f32 or i32, 4 bytes a value
     uint64_t count() const { return values.size() / 4; }
 };
@@ -83,7 +85,7 @@ int refuse(msx_dense* d, const Refused& r) {
 
 // read_tensor (data.rs:1232-1290).
 void read_tensor(const std::string& dir, Tensor* t) {
-    const char* role = t->target ? "target" : "input";
+    const char* role = t->role_name();
     const std::string ext = t->i32 ? "i32" : "f32", other = t->i32 ? "f32" : "i32";
     const std::string path = dir + "/" + t->name + "." + ext;
     const std::string what = std::string("the data file of the ") + role + " `" + t->name + "`";
@@ -140,7 +142,7 @@ int open_dense(const char* dir, uint32_t count, const char* const* names, const 
             Tensor t;
             t.name = names[i];
             t.i32 = is_i32[i] != 0;
-            t.target = is_target[i] != 0;
+            t.role = is_target[i] <= 2 ? is_target[i] : 0;
             t.sample = shared ? elements[i] / d->batch : elements[i];
             read_tensor(d->dir, &t);
             d->tensors.push_back(std::move(t));
@@ -153,9 +155,11 @@ int open_dense(const char* dir, uint32_t count, const char* const* names, const 
             for (const Tensor& t : d->tensors) message += ", " + t.name + " " + std::to_string(t.count() / t.sample);
             throw Refused{MSX_BAD_INPUT, message + ")"};
         }
+        // dense_eval (:588-595) and dense_function (:707-714) word the same rule differently.
         if (eval && d->samples % d->batch != 0)
-            throw Refused{MSX_BAD_INPUT, "E-DATA-009: the eval data is not a whole number of batches (directory " + d->dir + ", samples " +
-                                             std::to_string(d->samples) + ", batch " + std::to_string(d->batch) + ")"};
+            throw Refused{MSX_BAD_INPUT, std::string("E-DATA-009: ") + (d->tensors[0].role == 2 ? "the data is not a whole number of blocks"
+                                                                                                 : "the eval data is not a whole number of batches") +
+                                             " (directory " + d->dir + ", samples " + std::to_string(d->samples) + ", batch " + std::to_string(d->batch) + ")"};
         // dense (data.rs:513-577): the optional order, which an eval directory does not read.
         const std::string path = d->dir + "/order.u32";
         std::vector<char> bytes;
@@ -226,7 +230,7 @@ int msx_dense_check_bound(msx_dense* dense, uint32_t index, uint64_t bound, cons
     const int32_t* v = reinterpret_cast<const int32_t*>(t.values.data());
     for (uint64_t p = 0; p < t.count(); ++p)
         if (v[p] < 0 || static_cast<uint64_t>(v[p]) >= bound)
-            return refuse(dense, Refused{MSX_BAD_INPUT, std::string("E-DATA-011: the data file of the ") + (t.target ? "target" : "input") + " `" + t.name +
+            return refuse(dense, Refused{MSX_BAD_INPUT, std::string("E-DATA-011: the data file of the ") + t.role_name() + " `" + t.name +
                                                             "` holds " + std::to_string(v[p]) + ", outside " + what + " (file " + dense->dir + "/" + t.name +
                                                             ".i32, position " + std::to_string(p) + ", value " + std::to_string(v[p]) +
                                                             ", bound 0 <= value < " + std::to_string(bound) + ")"});

@@ -13,6 +13,13 @@
 #include <memory>
 #include <set>
 
+#include <fcntl.h>
+#include <limits.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cerrno>
+
 #include "../../../include/msx.h"
 #include "../core/frontend.hpp"
 #include "../core/init.hpp"
@@ -138,18 +145,22 @@ void stage_batch(msx_training* t, msx_plan* plan, const std::set<std::string>& r
 
 extern "C" {
 
-int msx_training_create(msx_device* device, const char* source, uint64_t masked_rows, uint32_t flags,
-                        msx_training** out) {
-    if (!device || !source || !out) return MSX_BAD_ARGUMENT;
+extern "C++" {
+namespace {
+
+// The plans of a compiled entry (the train block, or a model function as an inference entry) and
+// its parameters as the run's seed initialises them.
+template <class Compile> int create_from(msx_device* device, uint32_t flags, msx_training** out, Compile compile) {
     *out = nullptr;
     msx_training* t = new msx_training;
     t->device = device;
     t->flags = flags;
     int rc = guarded(t, [&] {
         try {
-            t->compiled = msx::compile_training(source, masked_rows);
+            t->compiled = compile();
         } catch (const msx::Error& e) {
-            throw Fail{MSX_UNSUPPORTED, e.what()};
+            const std::string what = e.what();
+            throw Fail{what.rfind("E-DATA-", 0) == 0 ? MSX_BAD_INPUT : MSX_UNSUPPORTED, what};
         }
         const msx::Compiled& c = t->compiled;
         if (c.config.rule == msx::Rule::AdamW && c.config.steps > 0 && c.config.adamw.warmup_steps >= c.config.steps)
@@ -168,7 +179,8 @@ int msx_training_create(msx_device* device, const char* source, uint64_t masked_
             std::vector<float> value = msx::initial_parameter(c.step.params[p], c.config.seed, msx::kStreamInit);
             int rs = msx_param_upload(t->step, p, value.data(), value.size() * 4);
             int rf = msx_param_upload(t->forward, p, value.data(), value.size() * 4);
-            if (rs != MSX_OK && rf != MSX_OK) throw Fail{rs, msx_last_error(device)};
+            // (a model function as an entry may read a part of the file's parameters only)
+            if (rs != MSX_OK && rf != MSX_OK && c.function.empty()) throw Fail{rs, msx_last_error(device)};
         }
     });
     if (rc != MSX_OK) {
@@ -179,6 +191,19 @@ int msx_training_create(msx_device* device, const char* source, uint64_t masked_
     }
     *out = t;
     return MSX_OK;
+}
+
+}  // namespace
+}  // extern "C++"
+
+int msx_training_create(msx_device* device, const char* source, uint64_t masked_rows, uint32_t flags, msx_training** out) {
+    if (!device || !source || !out) return MSX_BAD_ARGUMENT;
+    return create_from(device, flags, out, [&] { return msx::compile_training(source, masked_rows); });
+}
+
+int msx_training_create_function(msx_device* device, const char* source, const char* name, uint32_t flags, msx_training** out) {
+    if (!device || !source || !name || !out) return MSX_BAD_ARGUMENT;
+    return create_from(device, flags, out, [&] { return msx::compile_function(source, name); });
 }
 
 void msx_training_destroy(msx_training* t) {
@@ -412,7 +437,9 @@ int msx_training_infer(msx_training* t, float* prediction, uint64_t bytes, float
             // The forward program (dropout the identity) with the model's output kept beside the
             // loss, on the run's parameter buffers.
             msx::Program program = c.forward;
-            program.outputs.push_back(msx::Output{c.prediction, msx::Role::Plain, 0, 0});
+            // (a function entry whose result is rank 0: the loss is the prediction already)
+            if (program.outputs.empty() || program.outputs[0].value != c.prediction)
+                program.outputs.push_back(msx::Output{c.prediction, msx::Role::Plain, 0, 0});
             std::string ir = msx::print_program(program);
             ok(t, msx_plan_create(t->device, ir.c_str(), c.config.seed, t->flags, t->forward, &t->infer));
         }
@@ -734,57 +761,71 @@ void refuse_dense_declarations(const msx::Compiled& c) {
             throw Fail{MSX_BAD_INPUT, std::string("E-DATA-003: the ") + (d.target ? "target" : "input") + " `" + d.name + "` is not read by the loss"};
 }
 
+// index_bounds (data.rs:899-939) over the files of `dense`, opened for the declarations of `c` in
+// source order: the ids of an embedding lie below the rows of its table, the labels of a
+// cross_entropy below the classes of its logits; the tightest bound of a declaration is the one
+// its file is held to (refuse_out_of_range :957-1004, E-DATA-011).
+void check_index_bounds(const msx::Compiled& c, msx_dense* dense) {
+    const auto& decls = c.config.data;
+    const msx::Program& fwd = c.forward_with_dropout;
+    for (uint32_t i = 0; i < decls.size(); ++i) {
+        if (!decls[i].ty.i32) continue;
+        const int64_t input = input_named(fwd, decls[i].name);
+        uint64_t tightest = 0;
+        std::string what;
+        for (const msx::Node& n : fwd.nodes) {
+            const bool table = n.op == msx::Op::Embedding, logits = n.op == msx::Op::CrossEntropy;
+            if ((!table && !logits) || n.operands.size() < 2 || input < 0 || n.operands[1] != static_cast<uint32_t>(input)) continue;
+            const msx::Node& value = fwd.node(n.operands[0]);
+            const size_t axis = table ? 0 : 1;
+            if (value.ty.shape.size() <= axis) continue;
+            const uint64_t bound = value.ty.shape[axis];
+            if (!what.empty() && bound >= tightest) continue;
+            std::string named = "%" + std::to_string(value.id);
+            if (value.op == msx::Op::ParamRead) named = fwd.params[value.param].path;
+            tightest = bound;
+            what = "the " + std::to_string(bound) + (table ? " rows of the `embedding` table `" : " classes of the `cross_entropy` logits `") + named + "`";
+        }
+        if (what.empty()) continue;
+        if (msx_dense_check_bound(dense, i, tightest, what.c_str()) != MSX_OK) throw Fail{MSX_BAD_INPUT, msx_dense_last_error(dense)};
+    }
+}
+
+// The declarations of `c` as the dense reader takes them; `role` 0 / 1 by the declaration, or 2
+// for the arguments of an inference entry.
+struct DenseDeclarations {
+    std::vector<const char*> names;
+    std::vector<uint32_t> is_i32, roles, ranks;
+    std::vector<uint64_t> shapes;
+    explicit DenseDeclarations(const msx::Compiled& c) {
+        for (const msx::DataDecl& d : c.config.data) {
+            names.push_back(d.name.c_str());
+            is_i32.push_back(d.ty.i32 ? 1u : 0u);
+            roles.push_back(!c.function.empty() ? 2u : d.target ? 1u : 0u);
+            ranks.push_back(static_cast<uint32_t>(d.ty.shape.size()));
+            for (uint64_t n : d.ty.shape) shapes.push_back(n);
+        }
+    }
+    uint32_t count() const { return static_cast<uint32_t>(names.size()); }
+};
+
 }  // namespace
 
 int msx_training_bind_dense(msx_training* t, const char* dir) {
     if (!t || !dir) return MSX_BAD_ARGUMENT;
     return guarded(t, [&] {
         const msx::Compiled& c = t->compiled;
-        const auto& decls = c.config.data;  // in source order
-        const msx::Program& fwd = c.forward_with_dropout;
-        auto input_of = [&](const std::string& name) { return input_named(fwd, name); };
         refuse_dense_declarations(c);
-        std::vector<const char*> names;
-        std::vector<uint32_t> is_i32, is_target, ranks;
-        std::vector<uint64_t> shapes;
-        for (const msx::DataDecl& d : decls) {
-            names.push_back(d.name.c_str());
-            is_i32.push_back(d.ty.i32 ? 1u : 0u);
-            is_target.push_back(d.target ? 1u : 0u);
-            ranks.push_back(static_cast<uint32_t>(d.ty.shape.size()));
-            for (uint64_t n : d.ty.shape) shapes.push_back(n);
-        }
+        const DenseDeclarations d(c);
         msx_dense* dense = nullptr;
-        if (msx_dense_open(dir, static_cast<uint32_t>(decls.size()), names.data(), is_i32.data(), is_target.data(), ranks.data(), shapes.data(),
-                           c.config.steps, &dense) != MSX_OK)
+        if (msx_dense_open(dir, d.count(), d.names.data(), d.is_i32.data(), d.roles.data(), d.ranks.data(), d.shapes.data(), c.config.steps, &dense) !=
+            MSX_OK)
             throw Fail{MSX_BAD_INPUT, msx_dense_last_error(nullptr)};
-        // index_bounds (data.rs:899-939): the ids of an embedding lie below the rows of its table,
-        // the labels of a cross_entropy below the classes of its logits; the tightest bound of a
-        // declaration is the one its file is held to.
-        for (uint32_t i = 0; i < decls.size(); ++i) {
-            if (!decls[i].ty.i32) continue;
-            const int64_t input = input_of(decls[i].name);
-            uint64_t tightest = 0;
-            std::string what;
-            for (const msx::Node& n : fwd.nodes) {
-                const bool table = n.op == msx::Op::Embedding, logits = n.op == msx::Op::CrossEntropy;
-                if ((!table && !logits) || n.operands.size() < 2 || n.operands[1] != static_cast<uint32_t>(input)) continue;
-                const msx::Node& value = fwd.node(n.operands[0]);
-                const size_t axis = table ? 0 : 1;
-                if (value.ty.shape.size() <= axis) continue;
-                const uint64_t bound = value.ty.shape[axis];
-                if (!what.empty() && bound >= tightest) continue;
-                std::string named = "%" + std::to_string(value.id);
-                if (value.op == msx::Op::ParamRead) named = fwd.params[value.param].path;
-                tightest = bound;
-                what = "the " + std::to_string(bound) + (table ? " rows of the `embedding` table `" : " classes of the `cross_entropy` logits `") + named + "`";
-            }
-            if (what.empty()) continue;
-            if (msx_dense_check_bound(dense, i, tightest, what.c_str()) != MSX_OK) {
-                const std::string why = msx_dense_last_error(dense);
-                msx_dense_close(dense);
-                throw Fail{MSX_BAD_INPUT, why};
-            }
+        try {
+            check_index_bounds(c, dense);
+        } catch (...) {
+            msx_dense_close(dense);
+            throw;
         }
         if (t->dense) msx_dense_close(t->dense);
         t->dense = dense;
@@ -810,19 +851,9 @@ int msx_training_eval_dense(msx_training* t, const char* dir, double* loss, doub
         const msx::Compiled& c = t->compiled;
         const auto& decls = c.config.data;
         refuse_dense_declarations(c);
-        std::vector<const char*> names;
-        std::vector<uint32_t> is_i32, is_target, ranks;
-        std::vector<uint64_t> shapes;
-        for (const msx::DataDecl& d : decls) {
-            names.push_back(d.name.c_str());
-            is_i32.push_back(d.ty.i32 ? 1u : 0u);
-            is_target.push_back(d.target ? 1u : 0u);
-            ranks.push_back(static_cast<uint32_t>(d.ty.shape.size()));
-            for (uint64_t n : d.ty.shape) shapes.push_back(n);
-        }
+        const DenseDeclarations d(c);
         msx_dense* data = nullptr;
-        if (msx_dense_open_eval(dir, static_cast<uint32_t>(decls.size()), names.data(), is_i32.data(), is_target.data(), ranks.data(), shapes.data(),
-                                &data) != MSX_OK)
+        if (msx_dense_open_eval(dir, d.count(), d.names.data(), d.is_i32.data(), d.roles.data(), d.ranks.data(), d.shapes.data(), &data) != MSX_OK)
             throw Fail{MSX_BAD_INPUT, msx_dense_last_error(nullptr)};
         std::unique_ptr<msx_dense, void (*)(msx_dense*)> owned(data, msx_dense_close);
         // compared_target (data.rs:419-425, read_dense :640-655): the one target, when it is f32 and
@@ -874,6 +905,129 @@ int msx_training_eval_dense(msx_training* t, const char* dir, double* loss, doub
         *loss = sum / static_cast<double>(batches);
         *has_accuracy = compared >= 0 ? 1 : 0;
         *accuracy = compared >= 0 ? static_cast<double>(correct) / static_cast<double>(rows) : 0.0;
+    });
+}
+
+// ---- a model function over a dense directory (cli/src/infer.rs:306-470; train/data.rs:676-815) ----
+
+namespace {
+
+std::string listed_functions(const msx::Compiled& c) {
+    std::string out;
+    for (const std::string& f : c.functions) out += (out.empty() ? "" : ", ") + f;
+    return out;
+}
+
+// `path` made canonical, or when it does not exist its canonical parent joined with its name
+// (resolved, data.rs:800-815); empty when neither resolves.
+std::string resolved(const std::string& path) {
+    char buffer[PATH_MAX];
+    if (realpath(path.c_str(), buffer)) return buffer;
+    const size_t slash = path.find_last_of('/');
+    const std::string parent = slash == std::string::npos ? "." : slash == 0 ? "/" : path.substr(0, slash);
+    const std::string name = slash == std::string::npos ? path : path.substr(slash + 1);
+    if (name.empty() || name == "." || name == "..") return "";
+    if (!realpath(parent.c_str(), buffer)) return "";
+    return std::string(buffer) + (std::string(buffer) == "/" ? "" : "/") + name;
+}
+
+bool same_file(const std::string& a, const std::string& b) {
+    struct stat sa, sb;
+    return stat(a.c_str(), &sa) == 0 && stat(b.c_str(), &sb) == 0 && sa.st_dev == sb.st_dev && sa.st_ino == sb.st_ino;
+}
+
+// replace (cli/src/infer.rs:455-490): the bytes go to `.<name>.<pid>.tmp` beside `out`, are synced
+// and renamed over it; on an error the temporary file is removed and `out` keeps its bytes.
+void replace_file(const std::string& out, const void* bytes, size_t size) {
+    const size_t slash = out.find_last_of('/');
+    const std::string dir = slash == std::string::npos ? "." : slash == 0 ? "/" : out.substr(0, slash);
+    const std::string name = slash == std::string::npos ? out : out.substr(slash + 1);
+    if (name.empty()) throw Fail{MSX_BAD_ARGUMENT, "cannot write " + out + ": the path names no file"};
+    const std::string temporary = dir + "/." + name + "." + std::to_string(getpid()) + ".tmp";
+    auto failed = [&](const char* what) {
+        const std::string why = std::strerror(errno);
+        unlink(temporary.c_str());
+        return Fail{MSX_BAD_INPUT, "cannot write " + out + ": " + what + ": " + why};
+    };
+    const int fd = open(temporary.c_str(), O_WRONLY | O_CREAT | O_EXCL, 0644);
+    if (fd < 0) throw Fail{MSX_BAD_INPUT, "cannot write " + out + ": " + temporary + ": " + std::strerror(errno)};
+    const char* at = static_cast<const char*>(bytes);
+    size_t left = size;
+    while (left > 0) {
+        const ssize_t wrote = write(fd, at, left);
+        if (wrote < 0) {
+            if (errno == EINTR) continue;
+            const Fail f = failed("write");
+            close(fd);
+            throw f;
+        }
+        at += wrote;
+        left -= static_cast<size_t>(wrote);
+    }
+    if (fsync(fd) != 0) {
+        const Fail f = failed("sync");
+        close(fd);
+        throw f;
+    }
+    close(fd);
+    if (rename(temporary.c_str(), out.c_str()) != 0) throw failed("rename");
+}
+
+}  // namespace
+
+// refuse_out_reading (data.rs:773-798): `--out` resolves to a file the run reads.
+int msx_training_refuse_out_reading(msx_training* t, const char* dir, const char* out, const char* model, const char* checkpoint) {
+    if (!t || !dir || !out) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        std::vector<std::pair<std::string, std::string>> reads;
+        if (model) reads.push_back({"model", model});
+        if (checkpoint) reads.push_back({"checkpoint", checkpoint});
+        for (const msx::DataDecl& d : t->compiled.config.data)
+            reads.push_back({"argument `" + d.name + "`", std::string(dir) + "/" + d.name + (d.ty.i32 ? ".i32" : ".f32")});
+        const std::string target = resolved(out);
+        if (target.empty()) return;
+        for (const auto& [what, file] : reads)
+            if (resolved(file) == target || same_file(out, file))
+                throw Fail{MSX_BAD_INPUT, std::string("E-DATA-010: `--out` names a file the run reads\n  --out: ") + out + "\n  " + what + ": " + file};
+    });
+}
+
+int msx_training_infer_dense(msx_training* t, const char* dir, const char* out, uint64_t* blocks, uint64_t* rows) {
+    if (!t || !dir || !out || !blocks || !rows) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        if (c.function.empty()) throw Fail{MSX_BAD_ARGUMENT, "this run is the train block's, not a model function's (msx_training_create_function)"};
+        // dense_function (data.rs:685-717).
+        if (c.config.data.empty())
+            throw Fail{MSX_BAD_INPUT, "E-DATA-010: the function `" + c.function + "` takes no argument a data file could bind\n  function: " + c.function +
+                                          "\n  functions: " + listed_functions(c)};
+        const DenseDeclarations d(c);
+        msx_dense* data = nullptr;
+        if (msx_dense_open_eval(dir, d.count(), d.names.data(), d.is_i32.data(), d.roles.data(), d.ranks.data(), d.shapes.data(), &data) != MSX_OK)
+            throw Fail{MSX_BAD_INPUT, msx_dense_last_error(nullptr)};
+        std::unique_ptr<msx_dense, void (*)(msx_dense*)> owned(data, msx_dense_close);
+        check_index_bounds(c, data);
+        // row_elements (data.rs:732-762): one row per sample of a block of B samples.
+        const msx::Type& result = c.forward.node(c.prediction).ty;
+        const uint64_t batch = msx_dense_batch(data), samples = msx_dense_samples(data);
+        if (result.i32) throw Fail{MSX_UNSUPPORTED, "the result of the function `" + c.function + "` is " + result.str() + ", not f32"};
+        if (batch != 1 && (result.shape.empty() || result.shape[0] != batch))
+            throw Fail{MSX_BAD_INPUT, "E-DATA-010: the result of the function `" + c.function + "` is not one row per sample\n  function: " + c.function +
+                                          "\n  result: " + result.str() + "\n  batch: " + std::to_string(batch) + "\n  functions: " + listed_functions(c)};
+        const uint64_t per_block = result.count(), count = samples / batch;
+        std::vector<float> values(static_cast<size_t>(per_block * count));
+        for (uint64_t b = 0; b < count; ++b) {
+            for (uint32_t i = 0; i < d.count(); ++i) {
+                std::vector<char>& bytes = t->batch[c.config.data[i].name];
+                bytes.resize(msx_dense_batch_bytes(data, i));
+                if (msx_dense_eval_batch(data, i, b, bytes.data(), bytes.size()) != MSX_OK) throw Fail{MSX_BAD_ARGUMENT, "the block does not fit its argument"};
+            }
+            float loss = 0.0f;
+            if (msx_training_infer(t, values.data() + b * per_block, per_block * 4, &loss) != MSX_OK) throw Fail{MSX_LAUNCH_FAILED, t->error};
+        }
+        replace_file(out, values.data(), values.size() * 4);
+        *blocks = count;
+        *rows = samples;
     });
 }
 
@@ -958,29 +1112,60 @@ int msx_training_checkpoint(msx_training* t, uint64_t step, msx_checkpoint** out
     });
 }
 
+namespace {
+
+Fail mismatch(const std::string& what) { return Fail{MSX_BAD_INPUT, "E-CKPT-003: the checkpoint does not match the compiled file: " + what}; }
+
+// parameters_for (checkpoint.rs:519-585): both sides in path order, the first difference named,
+// then the schema hash. Returns the run's parameters in path order.
+std::vector<uint32_t> matched_parameters(msx_training* t, const msx_checkpoint* ckpt) {
+    const msx::Compiled& c = t->compiled;
+    std::vector<uint32_t> ours(c.forward.params.size());
+    for (uint32_t p = 0; p < ours.size(); ++p) ours[p] = p;
+    std::sort(ours.begin(), ours.end(), [&](uint32_t a, uint32_t b) { return c.forward.params[a].path < c.forward.params[b].path; });
+    const uint32_t theirs = msx_checkpoint_count(ckpt, 0);
+    for (uint32_t i = 0; i < std::max<uint32_t>(theirs, static_cast<uint32_t>(ours.size())); ++i) {
+        const std::string their_path = i < theirs ? std::string("`") + msx_checkpoint_path(ckpt, 0, i) + "`" : "none";
+        const std::string our_path = i < ours.size() ? "`" + c.forward.params[ours[i]].path + "`" : "none";
+        if (their_path != our_path) throw mismatch("a parameter path differs (checkpoint " + their_path + ", compiled file " + our_path + ")");
+        const msx::Param& p = c.forward.params[ours[i]];
+        if (p.ty.i32) throw mismatch("parameter `" + p.path + "` has dtype f32 in the checkpoint and i32 in the compiled file");
+        const uint64_t* shape = msx_checkpoint_shape(ckpt, 0, i);
+        std::vector<uint64_t> their_shape(shape, shape + msx_checkpoint_rank(ckpt, 0, i));
+        if (their_shape != p.ty.shape)
+            throw mismatch("parameter `" + p.path + "` has another shape (checkpoint " + shape_text(their_shape) + ", compiled file " + p.ty.str() + ")");
+    }
+    if (std::string(msx_checkpoint_schema_hash(ckpt)) != msx_training_schema_hash(t))
+        throw mismatch(std::string("the schema hash differs (checkpoint ") + msx_checkpoint_schema_hash(ckpt) + ", compiled file " + t->schema + ")");
+    return ours;
+}
+
+}  // namespace
+
+// The parameters of a checkpoint without its optimizer (`infer`: Checkpoint::parameters_for,
+// checkpoint.rs:519-585; cli/src/infer.rs:361-363).
+int msx_training_load_parameters(msx_training* t, const msx_checkpoint* ckpt, uint64_t* step) {
+    if (!t || !ckpt) return MSX_BAD_ARGUMENT;
+    return guarded(t, [&] {
+        const msx::Compiled& c = t->compiled;
+        const std::vector<uint32_t> ours = matched_parameters(t, ckpt);
+        ok(t, msx_sync(t->step, 0));
+        for (uint32_t i = 0; i < ours.size(); ++i) {
+            const uint64_t bytes = c.forward.params[ours[i]].ty.count() * 4;
+            int rs = msx_param_upload(t->step, ours[i], msx_checkpoint_data(ckpt, 0, i), bytes);
+            int rf = msx_param_upload(t->forward, ours[i], msx_checkpoint_data(ckpt, 0, i), bytes);
+            (void)rs;
+            (void)rf;  // a parameter neither program reads has no buffer
+        }
+        if (step) *step = msx_checkpoint_step(ckpt);
+    });
+}
+
 int msx_training_resume(msx_training* t, const msx_checkpoint* ckpt, uint64_t* start_step) {
     if (!t || !ckpt || !start_step) return MSX_BAD_ARGUMENT;
     return guarded(t, [&] {
         const msx::Compiled& c = t->compiled;
-        auto mismatch = [](const std::string& what) { return Fail{MSX_BAD_INPUT, "E-CKPT-003: the checkpoint does not match the compiled file: " + what}; };
-        // parameters_for (checkpoint.rs:519-585): both sides in path order, the first difference named.
-        std::vector<uint32_t> ours(c.forward.params.size());
-        for (uint32_t p = 0; p < ours.size(); ++p) ours[p] = p;
-        std::sort(ours.begin(), ours.end(), [&](uint32_t a, uint32_t b) { return c.forward.params[a].path < c.forward.params[b].path; });
-        const uint32_t theirs = msx_checkpoint_count(ckpt, 0);
-        for (uint32_t i = 0; i < std::max<uint32_t>(theirs, static_cast<uint32_t>(ours.size())); ++i) {
-            const std::string their_path = i < theirs ? std::string("`") + msx_checkpoint_path(ckpt, 0, i) + "`" : "none";
-            const std::string our_path = i < ours.size() ? "`" + c.forward.params[ours[i]].path + "`" : "none";
-            if (their_path != our_path) throw mismatch("a parameter path differs (checkpoint " + their_path + ", compiled file " + our_path + ")");
-            const msx::Param& p = c.forward.params[ours[i]];
-            if (p.ty.i32) throw mismatch("parameter `" + p.path + "` has dtype f32 in the checkpoint and i32 in the compiled file");
-            const uint64_t* shape = msx_checkpoint_shape(ckpt, 0, i);
-            std::vector<uint64_t> their_shape(shape, shape + msx_checkpoint_rank(ckpt, 0, i));
-            if (their_shape != p.ty.shape)
-                throw mismatch("parameter `" + p.path + "` has another shape (checkpoint " + shape_text(their_shape) + ", compiled file " + p.ty.str() + ")");
-        }
-        if (std::string(msx_checkpoint_schema_hash(ckpt)) != msx_training_schema_hash(t))
-            throw mismatch(std::string("the schema hash differs (checkpoint ") + msx_checkpoint_schema_hash(ckpt) + ", compiled file " + t->schema + ")");
+        const std::vector<uint32_t> ours = matched_parameters(t, ckpt);
         // resume_into (checkpoint.rs:587-609): the optimizer is that of the compiled file.
         int kind, their_kind;
         double v[5], w[5];
