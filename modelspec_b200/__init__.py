@@ -501,14 +501,14 @@ def eval_line(loss, accuracy=None):
 
 class Dense:
     """A dense data directory (msx_dense): `<name>.f32` / `<name>.i32` per declaration and an
-    optional `order.u32`. `declarations` = [(name, "f32" | "i32", "input" | "target", shape), ...] in
-    source order; `steps` = the run's step count (what an order must cover)."""
+    optional `order.u32`. `declarations` = [(name, "f32" | "i32", "input" | "target" | "argument",
+    shape), ...] in source order ("argument": of a model function run as an inference entry); `steps` = the run's step count (what an order must cover)."""
 
     def __init__(self, directory, declarations, steps, eval_directory=False):
         n = len(declarations)
         names = (C.c_char_p * n)(*[d[0].encode() for d in declarations])
         is_i32 = (C.c_uint32 * n)(*[1 if d[1] == "i32" else 0 for d in declarations])
-        is_target = (C.c_uint32 * n)(*[1 if d[2] == "target" else 0 for d in declarations])
+        is_target = (C.c_uint32 * n)(*[{"target": 1, "argument": 2}.get(d[2], 0) for d in declarations])
         ranks = (C.c_uint32 * n)(*[len(d[3]) for d in declarations])
         flat = [int(x) for d in declarations for x in d[3]]
         shapes = (C.c_uint64 * max(len(flat), 1))(*flat)

@@ -1,6 +1,8 @@
 """The dense `--data` directory as the reference reads it (crates/modelspec-runtime/src/train/
 data.rs:14-35, dense :513-577, read_files :837-876, read_tensor :1232-1290, fill_step :446-454):
 host code, no GPU."""
+import os
+
 import numpy as np
 import pytest
 
@@ -126,6 +128,27 @@ def test_an_eval_directory_is_whole_batches_and_reads_no_order(tmp_path):
         M.Dense(tmp_path, DECLS, steps=0, eval_directory=True)
     message = str(e.value)
     assert "E-DATA-009" in message and "not a whole number of batches" in message and "samples 10" in message and "batch 4" in message
+
+
+def test_the_arguments_of_a_function_are_named_so_and_come_in_whole_blocks(tmp_path):
+    """dense_function (train/data.rs:685-717): the files of a function's arguments are read as an
+    eval directory's, the messages say `argument`, and E-DATA-009 speaks of blocks."""
+    arguments = [(name, dtype, "argument", shape) for name, dtype, _, shape in DECLS]
+    x, ids, y = directory_of(tmp_path, samples=8)
+    d = M.Dense(tmp_path, arguments, steps=0, eval_directory=True)
+    assert (d.batch, d.samples) == (4, 8)
+    with pytest.raises(M.MsxError) as e:
+        d.check_bound(1, 1, "the 1 rows of the `embedding` table `%0`")
+    assert "E-DATA-011: the data file of the argument `%s` holds" % arguments[1][0] in str(e.value)
+    d.close()
+    directory_of(tmp_path, samples=10)
+    with pytest.raises(M.MsxError) as e:
+        M.Dense(tmp_path, arguments, steps=0, eval_directory=True)
+    assert "E-DATA-009: the data is not a whole number of blocks (directory" in str(e.value) and "samples 10, batch 4" in str(e.value)
+    os.remove(os.path.join(str(tmp_path), "%s.f32" % arguments[0][0]))
+    with pytest.raises(M.MsxError) as e:
+        M.Dense(tmp_path, arguments, steps=0, eval_directory=True)
+    assert "E-DATA-007: cannot read the data file of the argument `%s`" % arguments[0][0] in str(e.value)
 
 
 def test_the_eval_line_prints_f64_as_the_reference_does():
