@@ -197,3 +197,70 @@ def test_the_command_line_runs_a_function_over_a_directory(trained, tmp_path):
     assert done.returncode == 1 and "E-DATA-010" in done.stderr
     done = subprocess.run(base + ["--function", "scores"], capture_output=True, text=True, env=env)
     assert done.returncode == 2
+
+
+CORNERS = """model Base {
+    param w: Tensor<f32, [3, 2]> = xavier_uniform();
+    fn forward(x: Tensor<f32, [4, 3]>) -> Tensor<f32, [4, 2]> {
+        return matmul(x, w);
+    }
+    fn same(x: Tensor<f32, [4, 3]>) -> Tensor<f32, [4, 3]> {
+        return x;
+    }
+    fn half_read(x: Tensor<f32, [4, 3]>, ids: Tensor<i32, [4]>) -> Tensor<f32, [4, 2]> {
+        return matmul(x, w);
+    }
+    fn scaled(x: Tensor<f32, [4, 3]>, y: Tensor<f32, []>) -> Tensor<f32, []> {
+        return mul(mean(x), y);
+    }
+}
+train Fit {
+    model = Base;
+    input x: Tensor<f32, [4, 3]>;
+    target y: Tensor<f32, [4, 2]>;
+    loss = mse(model.forward(x), y);
+    optimizer = sgd(lr = 0.1);
+    steps = 3;
+    seed = 5;
+    device = cpu;
+}
+"""
+
+
+def test_corner_functions_write_one_row_per_sample(device, tmp_path):
+    """Three of the reference's corner cases (crates/modelspec-cli/tests/adversary_infer_data.rs):
+    a function that returns its argument writes it back byte for byte; an argument the function
+    does not read is still bound by its file and shifts no row; arguments without a shared
+    leading dimension make a sample a whole block, and a rank-0 result is its one value."""
+    r = np.random.default_rng(9)
+    x = (r.integers(-8, 9, size=(8, 3)) / 4.0).astype(np.float32)   # multiples of 1/4: sums and products are exact
+    x.tofile(str(tmp_path / "x.f32"))
+    r.integers(-50, 50, size=8).astype(np.int32).tofile(str(tmp_path / "ids.i32"))   # unread: no bound holds it
+    run = M.Training(device, CORNERS, 0, M.PLAN_EXACT_MATMUL, function="same")
+    try:
+        assert run.infer_dense(tmp_path, tmp_path / "same.f32") == (2, 8)
+        assert (tmp_path / "same.f32").read_bytes() == x.tobytes()
+    finally:
+        run.destroy()
+    run = M.Training(device, CORNERS, 0, M.PLAN_EXACT_MATMUL, function="half_read")
+    try:
+        w = run.forward_plan.param_download(0).reshape(3, 2)
+        assert run.infer_dense(tmp_path, tmp_path / "half.f32") == (2, 8)
+        got = np.fromfile(str(tmp_path / "half.f32"), dtype=np.float32).reshape(8, 2)
+        np.testing.assert_allclose(got, x.astype(np.float64) @ w.astype(np.float64), rtol=1e-5, atol=1e-6)
+        os.remove(str(tmp_path / "ids.i32"))
+        with pytest.raises(M.MsxError) as e:
+            run.infer_dense(tmp_path, tmp_path / "half.f32")
+        assert "E-DATA-007: cannot read the data file of the argument `ids`" in str(e.value)
+    finally:
+        run.destroy()
+    y = np.array([0.5, -2.0], dtype=np.float32)
+    y.tofile(str(tmp_path / "y.f32"))
+    run = M.Training(device, CORNERS, 0, M.PLAN_EXACT_MATMUL, function="scaled")
+    try:
+        assert run.infer_dense(tmp_path, tmp_path / "scaled.f32") == (2, 2)   # B = 1: a sample is a block of 4 rows of x and one y
+        got = np.fromfile(str(tmp_path / "scaled.f32"), dtype=np.float32)
+        want = [np.float32(x[4 * s:4 * s + 4].astype(np.float64).mean()) * y[s] for s in range(2)]
+        np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-7)
+    finally:
+        run.destroy()
