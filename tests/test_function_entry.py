@@ -93,3 +93,12 @@ def test_an_unknown_function_names_the_functions_of_the_model():
     assert "functions: forward, scores, picked, noisy" in message
     with pytest.raises(M.MsxError):
         M.compile_function(SEVERAL.replace("matmul(x, w), b)", "matmul(w, x), b)"), "scores")
+
+
+def test_every_entry_schedules_in_f32_and_what_has_no_bf16_form_is_refused_loudly():
+    for name in ("forward", "scores", "picked", "noisy"):
+        for which in ("forward", "step"):
+            assert "launches" in M.schedule_describe(M.compile_function(SEVERAL, name, which), M.PLAN_DEFAULT)
+    with pytest.raises(M.MsxError) as e:
+        M.schedule_describe(M.compile_function(SEVERAL, "scores", "forward"), M.PLAN_BF16)
+    assert "E-TARGET-011" in str(e.value) and "has no CUDA kernel" in str(e.value)
